@@ -1,0 +1,535 @@
+"""Hand-scheduled training executor.
+
+Instead of tracing the model with autograd (or a compiler) the decoder stack is run by an
+explicit forward schedule that records what the backward needs, and an explicit backward
+schedule that consumes it.  That gives the executor what a B200 step needs and autograd
+cannot express:
+
+* all parameters, gradients and optimizer state live in flat arenas (one allocation each,
+  peer-mappable), ``q/k/v`` and ``gate/up`` are adjacent so one GEMM serves each group while
+  the checkpoint still sees the reference's separate tensors;
+* AttnRes source gradients are accumulated *in place* by the routing-backward kernel (no
+  per-call gradient tensors, no re-stacking of sources: the sources are passed by pointer);
+* a layer's gradients are final as soon as its backward is done, so the gradient
+  reduction of layer ``i`` is launched on the communication stream while layer ``i-1`` is
+  still in backward, and Muon work is owner-computes.
+
+Semantics follow the reference loop ``src/training/train.py:567-657`` (micro-steps, loss/GA,
+global-norm clip before both optimizers, Muon then AdamW) and the model
+``src/model/llama.py:666-716``.  Every op goes through an ops backend
+(``kotodama_b200.ops``): PyTorch on CPU, sm_100a kernels on CUDA.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import Any, Optional
+
+import torch
+import torch.nn as nn
+
+from .config import ModelConfig
+from .models.llama import KotodamaModel
+from .optim.muon import resolve_ns_coefficients
+from .ops import get_ops
+
+_ALIGN = 64  # elements; keeps every tensor 128-byte aligned in bf16
+
+
+def _round_up(x: int, a: int) -> int:
+    return (x + a - 1) // a * a
+
+
+@dataclass
+class _Slot:
+    name: str
+    param: nn.Parameter
+    offset: int
+    numel: int
+    shape: tuple
+    kind: str                      # "muon" | "adamw"
+    layer: int = -1
+    owner: int = 0                 # rank that runs Newton-Schulz for this matrix
+
+
+class ParamArena:
+    """Flat parameter/gradient storage with the model's parameters re-pointed into it.
+
+    Layout: per layer ``[q|k|v] [o] [gate|up] [down]`` (the Muon region), then the embedding,
+    then every 1-D parameter in ``named_parameters`` order (the AdamW region).  The Muon rule is
+    the reference's: 2-D and neither "embed" nor "lm_head" in the name (``muon.py:381``).
+    """
+
+    def __init__(self, model: KotodamaModel, device: torch.device, dtype: torch.dtype,
+                 allocator=None) -> None:
+        self.model = model
+        named = [(n, p) for n, p in model.named_parameters() if p.requires_grad]
+        self.names = [n for n, _ in named]
+        muon, adamw = [], []
+        for n, p in named:
+            (muon if (p.ndim == 2 and "embed" not in n and "lm_head" not in n) else adamw).append((n, p))
+        # Muon region in layer order with the fused groups adjacent.
+        order_in_layer = ["attn.q_proj", "attn.k_proj", "attn.v_proj", "attn.o_proj",
+                          "ffn.gate_proj", "ffn.up_proj", "ffn.down_proj"]
+
+        def key(item):
+            n = item[0]
+            parts = n.split(".")
+            li = int(parts[1]) if parts[0] == "layers" else 10 ** 6
+            sub = ".".join(parts[2:4]) if parts[0] == "layers" else n
+            return (li, order_in_layer.index(sub) if sub in order_in_layer else 99)
+
+        muon.sort(key=key)
+        self.slots: list[_Slot] = []
+        off = 0
+        for n, p in muon:
+            parts = n.split(".")
+            li = int(parts[1]) if parts[0] == "layers" else -1
+            fused_follow = any(s in n for s in ("k_proj", "v_proj", "up_proj"))
+            if not fused_follow:
+                off = _round_up(off, _ALIGN)
+            self.slots.append(_Slot(n, p, off, p.numel(), tuple(p.shape), "muon", li))
+            off += p.numel()
+        self.muon_end = off = _round_up(off, _ALIGN)
+        for n, p in adamw:
+            off = _round_up(off, _ALIGN)
+            self.slots.append(_Slot(n, p, off, p.numel(), tuple(p.shape), "adamw"))
+            off += p.numel()
+        self.total = _round_up(off, _ALIGN)
+        alloc = allocator or (lambda n: torch.zeros(n, device=device, dtype=dtype))
+        self.params = alloc(self.total)
+        self.grads = alloc(self.total)
+        self.by_name = {s.name: s for s in self.slots}
+        with torch.no_grad():
+            for s in self.slots:
+                view = self.params[s.offset:s.offset + s.numel].view(s.shape)
+                view.copy_(s.param.data)
+                s.param.data = view
+                s.param.grad = self.grads[s.offset:s.offset + s.numel].view(s.shape)
+        for b in model.buffers():
+            b.data = b.data.to(device)
+
+    def view(self, name: str, grads: bool = False) -> torch.Tensor:
+        s = self.by_name[name]
+        base = self.grads if grads else self.params
+        return base[s.offset:s.offset + s.numel].view(s.shape)
+
+    def fused(self, first: str, last: str, grads: bool = False) -> torch.Tensor:
+        """View spanning the adjacent tensors ``first..last`` as one ``[rows, in]`` matrix."""
+        a, b = self.by_name[first], self.by_name[last]
+        base = self.grads if grads else self.params
+        cols = a.shape[1]
+        return base[a.offset:b.offset + b.numel].view(-1, cols)
+
+    def muon_slots(self) -> list[_Slot]:
+        return [s for s in self.slots if s.kind == "muon"]
+
+    def adamw_range(self) -> tuple[int, int]:
+        return self.muon_end, self.total
+
+
+@dataclass
+class _LayerRec:
+    srcs1: list = field(default_factory=list)
+    stats1: Any = None
+    xn1: Any = None
+    qkv: Any = None
+    qk: Any = None
+    rstd_qk: Any = None
+    attn_o: Any = None
+    lse: Any = None
+    part_after_attn: Any = None
+    srcs2: list = field(default_factory=list)
+    stats2: Any = None
+    xn2: Any = None
+    gu: Any = None
+    act: Any = None
+    part_before_attn: Any = None   # None when the attention output starts a new block
+    part_after_mlp: Any = None
+
+
+class _OptView:
+    """What the LR scheduler and the checkpoint manager need from an optimizer."""
+
+    def __init__(self, lr: float, **hyper: Any) -> None:
+        self.defaults = dict(lr=lr, **hyper)
+        self.param_groups = [dict(lr=lr, **hyper)]
+
+
+class TrainEngine:
+    """Owns arenas, optimizer state and the fwd/bwd/optimizer schedule for one rank."""
+
+    def __init__(self, model: KotodamaModel, *, device: torch.device | str = "cpu",
+                 dtype: torch.dtype = torch.float32, comm=None, ops=None,
+                 muon_lr: float = 0.03, muon_momentum: float = 0.95, muon_weight_decay: float = 0.01,
+                 muon_ns_iterations: int = 5, muon_ns_coefficients: Optional[str] = None,
+                 adamw_lr: float = 6e-4, adamw_betas: tuple[float, float] = (0.9, 0.95),
+                 adamw_weight_decay: float = 0.1, adamw_eps: float = 1e-8, gradient_clip: float = 1.0,
+                 adamw_only: bool = False, ce_chunk: int = 4096) -> None:
+        from .parallel.comm import LocalComm
+
+        self.device = torch.device(device)
+        self.dtype = dtype
+        self.model = model
+        self.cfg: ModelConfig = model.config
+        self.comm = comm or LocalComm()
+        self.ops = ops or get_ops(self.device)
+        self.arena = ParamArena(model, self.device, dtype, allocator=self.comm.allocator(self.device, dtype))
+        self.comm.attach(self)
+        self.gradient_clip = gradient_clip
+        self.adamw_only = adamw_only
+        self.ce_chunk = ce_chunk
+        self.ns_coefficients = muon_ns_coefficients
+        self.muon_opt = _OptView(muon_lr, momentum=muon_momentum, nesterov=True,
+                                 weight_decay=muon_weight_decay, ns_iterations=muon_ns_iterations)
+        self.adamw_opt = _OptView(adamw_lr, betas=tuple(adamw_betas), eps=adamw_eps,
+                                  weight_decay=adamw_weight_decay)
+        resolve_ns_coefficients(muon_ns_coefficients, muon_ns_iterations)
+        # optimizer state
+        self.opt_step = 0
+        self._assign_owners()
+        a0, a1 = self.arena.adamw_range()
+        lo = 0 if adamw_only else a0
+        self.adamw_lo = lo
+        self.exp_avg = torch.zeros(a1 - lo, device=self.device, dtype=torch.float32)
+        self.exp_avg_sq = torch.zeros(a1 - lo, device=self.device, dtype=torch.float32)
+        self.momentum: dict[str, torch.Tensor] = {}
+        if not adamw_only:
+            for s in self.arena.muon_slots():
+                if s.owner == self.comm.rank or not self.comm.distributed_muon:
+                    self.momentum[s.name] = torch.zeros(s.shape, device=self.device, dtype=dtype)
+        self._wcache: dict[str, torch.Tensor] = {}
+        self._gather_weights()
+
+    # ------------------------------------------------------------ helpers
+    def _assign_owners(self) -> None:
+        """Greedy balance of Newton-Schulz FLOPs over ranks (largest first)."""
+        world = self.comm.world
+        load = [0.0] * world
+        slots = self.arena.muon_slots()
+        def ns_flops(s):
+            r, c = min(s.shape), max(s.shape)
+            return 2.0 * r * r * c * 2 + 2.0 * r * r * r
+        for s in sorted(slots, key=lambda s: (-ns_flops(s), s.offset)):
+            o = min(range(world), key=lambda r: (load[r], r))
+            s.owner = o
+            load[o] += ns_flops(s)
+
+    def _gather_weights(self) -> None:
+        m, ar = self.model, self.arena
+        self.layer_w = []
+        for i in range(self.cfg.num_layers):
+            p = f"layers.{i}."
+            self.layer_w.append(dict(
+                wqkv=ar.fused(p + "attn.q_proj.weight", p + "attn.v_proj.weight"),
+                wo=ar.view(p + "attn.o_proj.weight"),
+                wgu=ar.fused(p + "ffn.gate_proj.weight", p + "ffn.up_proj.weight"),
+                wd=ar.view(p + "ffn.down_proj.weight"),
+                g_wqkv=ar.fused(p + "attn.q_proj.weight", p + "attn.v_proj.weight", grads=True),
+                g_wo=ar.view(p + "attn.o_proj.weight", grads=True),
+                g_wgu=ar.fused(p + "ffn.gate_proj.weight", p + "ffn.up_proj.weight", grads=True),
+                g_wd=ar.view(p + "ffn.down_proj.weight", grads=True),
+            ))
+
+    def _p(self, name: str) -> torch.Tensor:
+        return self.arena.view(name)
+
+    def _g(self, name: str) -> torch.Tensor:
+        return self.arena.view(name, grads=True)
+
+    def _acc_small(self, name: str, val: Optional[torch.Tensor]) -> None:
+        if val is None:
+            return
+        g = self._g(name)
+        if self._first_micro:
+            g.copy_(val.view(g.shape))
+        else:
+            g.add_(val.view(g.shape).to(g.dtype))
+
+    # ------------------------------------------------------------ forward
+    @torch.no_grad()
+    def forward_backward(self, input_ids: torch.Tensor, loss_scale: float = 1.0, first_micro: bool = True,
+                         last_micro: bool = True, need_grad: bool = True):
+        """One micro-batch ``input_ids[B,T]``: returns ``(loss, z_loss)`` as 0-dim device tensors
+        (``loss`` includes the z-loss) and leaves gradients of ``loss_scale * loss`` in the arena
+        (overwritten on the first micro-step, accumulated afterwards)."""
+        ops, cfg, ar = self.ops, self.cfg, self.arena
+        self._first_micro = first_micro
+        B, T = input_ids.shape
+        N = B * T
+        H, KV, hd, D, F_ = cfg.num_attention_heads, cfg.num_kv_heads, cfg.head_dim, cfg.hidden_size, cfg.intermediate_size
+        if self.comm.tp_size > 1:
+            H, KV, F_ = H // self.comm.tp_size, KV // self.comm.tp_size, F_ // self.comm.tp_size
+        eps = cfg.norm_eps
+        ids = input_ids.reshape(-1)
+        labels = torch.roll(input_ids, -1, dims=1)
+        labels[:, -1] = -100
+        labels = labels.reshape(-1)
+        wemb = self._p("embed_tokens.weight")
+        cos, sin = self.model.rope_cos, self.model.rope_sin
+        attn_res = cfg.attn_res
+        bset = self.model._attn_res_boundary_set if attn_res else frozenset()
+        qw = lambda n: self._p(n) if attn_res else None
+
+        embed = ops.embedding_fwd(ids, wemb)
+        committed: list[torch.Tensor] = []
+        partial: Optional[torch.Tensor] = embed
+        recs: list[_LayerRec] = []
+        for i in range(cfg.num_layers):
+            lw = self.layer_w[i]
+            p = f"layers.{i}."
+            r = _LayerRec()
+            r.srcs1 = committed + [partial]
+            r.xn1, r.stats1 = ops.route_norm_fwd(r.srcs1, qw(p + "attn_res_query"), qw(p + "attn_res_norm.weight"),
+                                                 self._p(p + "attn_norm.weight"), eps)
+            if i in bset:
+                committed = committed + [partial]
+                partial = None
+            r.part_before_attn = partial
+            xin = self.comm.sp_gather(r.xn1)
+            r.qkv = ops.gemm_nt(xin, lw["wqkv"])
+            r.qk, r.rstd_qk = ops.qknorm_rope_fwd(
+                r.qkv, self._p(p + "attn.q_norm.weight") if cfg.qk_norm else None,
+                self._p(p + "attn.k_norm.weight") if cfg.qk_norm else None, cos, sin, T, H, KV, hd, eps)
+            Nq = r.qkv.shape[0]
+            q4 = r.qk[:, : H * hd].view(Nq // T, T, H, hd)
+            k4 = r.qk[:, H * hd:].view(Nq // T, T, KV, hd)
+            v4 = r.qkv[:, (H + KV) * hd:].view(Nq // T, T, KV, hd)
+            r.attn_o, r.lse = ops.attention_fwd(q4, k4, v4)
+            partial = self.comm.row_linear(ops, r.attn_o.view(Nq, H * hd), lw["wo"], residual=partial)
+            r.part_after_attn = partial
+            r.srcs2 = committed + [partial]
+            r.xn2, r.stats2 = ops.route_norm_fwd(r.srcs2, qw(p + "mlp_res_query"), qw(p + "mlp_res_norm.weight"),
+                                                 self._p(p + "ffn_norm.weight"), eps)
+            xin2 = self.comm.sp_gather(r.xn2)
+            r.gu = ops.gemm_nt(xin2, lw["wgu"])
+            r.act = ops.swiglu_fwd(r.gu)
+            partial = self.comm.row_linear(ops, r.act, lw["wd"], residual=partial)
+            r.part_after_mlp = partial
+            if not need_grad:
+                r = _LayerRec()
+            recs.append(r)
+        fsrcs = committed + [partial]
+        xf, fstats = ops.route_norm_fwd(fsrcs, qw("final_res_query"), qw("final_res_norm.weight"),
+                                        self._p("norm.weight"), eps)
+        wl = self.model.get_lm_head_weight()
+        g_wl = self._g("embed_tokens.weight") if self.model.lm_head is None else self._g("lm_head.weight")
+        ce, zl, dxf = ops.linear_ce(xf, wl, labels, cfg.z_loss_weight, loss_scale,
+                                    g_wl if need_grad else None, dw_accumulate=not first_micro,
+                                    chunk=self.ce_chunk, need_grad=need_grad)
+        loss = ce + zl
+        if not need_grad:
+            return loss, zl
+        if self.model.lm_head is not None and first_micro:
+            self._g("embed_tokens.weight").zero_()
+
+        # ---------------------------------------------------------- backward
+        grads: dict[int, torch.Tensor] = {}
+
+        def dsrc_list(srcs):
+            out, acc = [], []
+            for s in srcs:
+                k = id(s)
+                if k in grads:
+                    out.append(grads[k]); acc.append(True)
+                else:
+                    g = torch.empty_like(s)
+                    grads[k] = g
+                    out.append(g); acc.append(False)
+            return out, acc
+
+        ds, acc = dsrc_list(fsrcs)
+        dq, drn, dnw = ops.route_norm_bwd(dxf, fsrcs, qw("final_res_query"), qw("final_res_norm.weight"),
+                                          self._p("norm.weight"), eps, fstats, ds, acc)
+        self._acc_small("norm.weight", dnw)
+        if attn_res:
+            self._acc_small("final_res_query", dq)
+            self._acc_small("final_res_norm.weight", drn)
+        del dxf, xf
+        for i in reversed(range(cfg.num_layers)):
+            lw, r, p = self.layer_w[i], recs[i], f"layers.{i}."
+            # ---- MLP sub-layer
+            dP = grads[id(r.part_after_mlp)]
+            dact = self.comm.row_linear_bwd_input(ops, dP, lw["wd"])
+            dPg = self.comm.sp_gather(dP)
+            ops.gemm_tn(dPg, r.act, out=lw["g_wd"], accumulate=not first_micro)
+            dgu = ops.swiglu_bwd(r.gu, dact)
+            del dact
+            ops.gemm_tn(dgu, self.comm.sp_gather(r.xn2), out=lw["g_wgu"], accumulate=not first_micro)
+            dxn2 = self.comm.col_linear_bwd_input(ops, dgu, lw["wgu"])
+            del dgu
+            grads[id(r.part_after_attn)] = dP                      # residual add: gradient passes through
+            ds, acc = dsrc_list(r.srcs2)
+            dq, drn, dnw = ops.route_norm_bwd(dxn2, r.srcs2, qw(p + "mlp_res_query"), qw(p + "mlp_res_norm.weight"),
+                                              self._p(p + "ffn_norm.weight"), eps, r.stats2, ds, acc)
+            self._acc_small(p + "ffn_norm.weight", dnw)
+            if attn_res:
+                self._acc_small(p + "mlp_res_query", dq)
+                self._acc_small(p + "mlp_res_norm.weight", drn)
+            del dxn2
+            # ---- attention sub-layer
+            dP = grads[id(r.part_after_attn)]
+            Nq = r.qkv.shape[0]
+            dattn = self.comm.row_linear_bwd_input(ops, dP, lw["wo"])
+            ops.gemm_tn(self.comm.sp_gather(dP), r.attn_o.view(Nq, H * hd), out=lw["g_wo"], accumulate=not first_micro)
+            dqkv = torch.empty_like(r.qkv)
+            dqk = torch.empty_like(r.qk)
+            q4 = r.qk[:, : H * hd].view(Nq // T, T, H, hd)
+            k4 = r.qk[:, H * hd:].view(Nq // T, T, KV, hd)
+            v4 = r.qkv[:, (H + KV) * hd:].view(Nq // T, T, KV, hd)
+            ops.attention_bwd(dattn.view(Nq // T, T, H, hd), q4, k4, v4, r.attn_o, r.lse,
+                              dqk[:, : H * hd].view(Nq // T, T, H, hd), dqk[:, H * hd:].view(Nq // T, T, KV, hd),
+                              dqkv[:, (H + KV) * hd:].view(Nq // T, T, KV, hd))
+            del dattn
+            dqw, dkw = ops.qknorm_rope_bwd(
+                dqk, r.qkv, self._p(p + "attn.q_norm.weight") if cfg.qk_norm else None,
+                self._p(p + "attn.k_norm.weight") if cfg.qk_norm else None, cos, sin, r.rstd_qk, T, H, KV, hd, dqkv)
+            if cfg.qk_norm:
+                self._acc_small(p + "attn.q_norm.weight", dqw)
+                self._acc_small(p + "attn.k_norm.weight", dkw)
+            del dqk
+            ops.gemm_tn(dqkv, self.comm.sp_gather(r.xn1), out=lw["g_wqkv"], accumulate=not first_micro)
+            dxn1 = self.comm.col_linear_bwd_input(ops, dqkv, lw["wqkv"])
+            del dqkv
+            if r.part_before_attn is not None:
+                grads[id(r.part_before_attn)] = dP
+            ds, acc = dsrc_list(r.srcs1)
+            dq, drn, dnw = ops.route_norm_bwd(dxn1, r.srcs1, qw(p + "attn_res_query"), qw(p + "attn_res_norm.weight"),
+                                              self._p(p + "attn_norm.weight"), eps, r.stats1, ds, acc)
+            self._acc_small(p + "attn_norm.weight", dnw)
+            if attn_res:
+                self._acc_small(p + "attn_res_query", dq)
+                self._acc_small(p + "attn_res_norm.weight", drn)
+            del dxn1
+            recs[i] = None  # free activations of this layer
+            if last_micro:
+                self.comm.layer_grads_ready(i)
+        ops.embedding_bwd(grads[id(embed)], ids, self._g("embed_tokens.weight"))
+        if last_micro:
+            self.comm.small_grads_ready()
+        return loss, zl
+
+    # ---------------------------------------------------------- optimizer
+    @torch.no_grad()
+    def optimizer_step(self) -> torch.Tensor:
+        """Clip by global norm, Muon on matrices (owner-computes when distributed), AdamW on the
+        rest.  Returns the pre-clip gradient norm (0-dim device tensor)."""
+        ops, ar, comm = self.ops, self.arena, self.comm
+        comm.finish_grad_reduce()
+        total_sq = comm.grad_sumsq(ops)
+        norm = total_sq.sqrt()
+        if self.gradient_clip > 0:
+            coef = (self.gradient_clip / (norm + 1e-6)).clamp(max=1.0)
+        else:
+            coef = torch.ones((), device=self.device, dtype=torch.float32)
+        self.opt_step += 1
+        if not self.adamw_only:
+            g = self.muon_opt.param_groups[0]
+            coeffs = resolve_ns_coefficients(self.ns_coefficients, g["ns_iterations"])
+            for s in ar.muon_slots():
+                if comm.distributed_muon and s.owner != comm.rank:
+                    continue
+                grad = ar.view(s.name, grads=True)
+                x, sq = ops.muon_momentum(grad, self.momentum[s.name], g["momentum"], g["nesterov"], coef)
+                rows, cols = comm.full_shape(s)
+                transposed = x.shape[0] > x.shape[1]
+                x = comm.muon_gather(s, x)
+                if transposed:
+                    x = ops.transpose(x)
+                if comm.tp_size > 1:
+                    sq = ops.sumsq(x)
+                x = ops.ns_normalize(x, sq)
+                for (a, b, c) in coeffs:
+                    x = ops.ns_iteration(x, a, b, c)
+                x = comm.muon_scatter(s, x, transposed)
+                scale = max(1.0, (rows / cols) ** 0.5)
+                ops.muon_apply(ar.view(s.name), x, g["lr"], g["weight_decay"], scale, transposed)
+                comm.publish_param(s)
+        ga = self.adamw_opt.param_groups[0]
+        lo, hi = self.adamw_lo, ar.total
+        ops.adamw_step(ar.params[lo:hi], ar.grads[lo:hi], self.exp_avg, self.exp_avg_sq, self.opt_step,
+                       ga["lr"], ga["betas"][0], ga["betas"][1], ga["eps"], ga["weight_decay"], coef)
+        comm.finish_param_publish()
+        return norm
+
+    def train_step(self, micro_batches: list[torch.Tensor]) -> dict[str, torch.Tensor]:
+        """One optimizer step over ``len(micro_batches)`` micro-batches (host tensors are copied
+        to the device asynchronously).  Returns device scalars ``loss``, ``z_loss``, ``grad_norm``."""
+        ga = len(micro_batches)
+        loss_acc = zl_acc = None
+        for j, mb in enumerate(micro_batches):
+            mb = mb.to(self.device, non_blocking=True)
+            loss, zl = self.forward_backward(mb, 1.0 / (ga * self.comm.dp_size), j == 0, j == ga - 1)
+            loss_acc = loss if loss_acc is None else loss_acc + loss
+            zl_acc = zl if zl_acc is None else zl_acc + zl
+        norm = self.optimizer_step()
+        return {"loss": loss_acc / ga, "z_loss": zl_acc / ga, "grad_norm": norm}
+
+    @torch.no_grad()
+    def eval_loss(self, input_ids: torch.Tensor) -> torch.Tensor:
+        return self.forward_backward(input_ids.to(self.device), need_grad=False)[0]
+
+    # ------------------------------------------------------- checkpoint IO
+    def muon_state_dict(self) -> dict[str, Any]:
+        """torch-optimizer layout with one ``momentum_buffer`` per Muon parameter in
+        ``named_parameters`` order, plus ``ns_coefficients`` (``muon.py:231-234``)."""
+        if self.adamw_only:
+            return {}
+        names = [n for n in self.arena.names if self.arena.by_name[n].kind == "muon"]
+        state = {}
+        for i, n in enumerate(names):
+            buf = self.comm.gather_momentum(self.arena.by_name[n], self.momentum.get(n))
+            if buf is not None and self.opt_step > 0:
+                state[i] = {"momentum_buffer": buf.detach().cpu().clone()}
+        g = dict(self.muon_opt.param_groups[0])
+        g["params"] = list(range(len(names)))
+        return {"state": state, "param_groups": [g], "ns_coefficients": self.ns_coefficients}
+
+    def load_muon_state_dict(self, sd: dict[str, Any]) -> None:
+        if not sd or self.adamw_only:
+            return
+        names = [n for n in self.arena.names if self.arena.by_name[n].kind == "muon"]
+        if sd.get("ns_coefficients") is not None:
+            self.ns_coefficients = sd["ns_coefficients"]
+        for i, n in enumerate(names):
+            st = sd.get("state", {}).get(i)
+            if st is not None and n in self.momentum:
+                self.momentum[n].copy_(self.comm.shard_like(self.arena.by_name[n], st["momentum_buffer"]))
+        if sd.get("param_groups"):
+            for k in ("lr", "momentum", "weight_decay", "ns_iterations", "nesterov"):
+                if k in sd["param_groups"][0]:
+                    self.muon_opt.param_groups[0][k] = sd["param_groups"][0][k]
+
+    def adamw_state_dict(self) -> dict[str, Any]:
+        names = [n for n in self.arena.names if self.adamw_only or self.arena.by_name[n].kind == "adamw"]
+        state = {}
+        if self.opt_step > 0:
+            for i, n in enumerate(names):
+                s = self.arena.by_name[n]
+                o = s.offset - self.adamw_lo
+                state[i] = {"step": torch.tensor(float(self.opt_step)),
+                            "exp_avg": self.exp_avg[o:o + s.numel].view(s.shape).cpu().clone(),
+                            "exp_avg_sq": self.exp_avg_sq[o:o + s.numel].view(s.shape).cpu().clone()}
+        g = dict(self.adamw_opt.param_groups[0])
+        g.update(amsgrad=False, maximize=False, foreach=None, capturable=False, differentiable=False,
+                 fused=None, params=list(range(len(names))))
+        return {"state": state, "param_groups": [g]}
+
+    def load_adamw_state_dict(self, sd: dict[str, Any]) -> None:
+        if not sd:
+            return
+        names = [n for n in self.arena.names if self.adamw_only or self.arena.by_name[n].kind == "adamw"]
+        for i, n in enumerate(names):
+            st = sd.get("state", {}).get(i)
+            if st is None:
+                continue
+            s = self.arena.by_name[n]
+            o = s.offset - self.adamw_lo
+            self.exp_avg[o:o + s.numel].copy_(st["exp_avg"].reshape(-1))
+            self.exp_avg_sq[o:o + s.numel].copy_(st["exp_avg_sq"].reshape(-1))
+            self.opt_step = int(float(st["step"]))
+        if sd.get("param_groups"):
+            for k in ("lr", "betas", "eps", "weight_decay"):
+                if k in sd["param_groups"][0]:
+                    v = sd["param_groups"][0][k]
+                    self.adamw_opt.param_groups[0][k] = tuple(v) if k == "betas" else v

@@ -1,0 +1,328 @@
+"""Plain-PyTorch implementations of every fused op the training/serving executors use.
+
+These define the numerics (statistics in fp32, outputs in the activation dtype) and are
+the oracle for the sm_100a kernels in ``csrc/``; they are also the backend used on CPU
+(fp32, gloo) runs.  Each function documents the tensor contract shared with its CUDA twin.
+
+Math sources in the reference project: routing ``src/model/llama.py:630-644`` and its
+Triton backward ``src/model/flash_attn_res/kernels/phase_1.py:204-249``; RMSNorm
+``llama.py:143-153``; RoPE ``llama.py:172-203``; loss ``llama.py:837-849``.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional, Sequence
+
+import torch
+import torch.nn.functional as F
+
+
+def _f(x: torch.Tensor) -> torch.Tensor:
+    """Statistics dtype: fp32, or fp64 when the caller already works in fp64 (gradient checks)."""
+    return x if x.dtype in (torch.float32, torch.float64) else x.float()
+
+
+class TorchOps:
+    """Backend object; ``CudaOps`` derives from it and overrides methods with kernels."""
+
+    name = "torch"
+
+    # ------------------------------------------------------------------ GEMM
+    def gemm_nt(self, a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None,
+                residual: Optional[torch.Tensor] = None, accumulate: bool = False) -> torch.Tensor:
+        """``a[M,K] @ b[N,K]^T (+ residual) -> [M,N]``; ``accumulate`` adds into ``out``."""
+        r = a @ b.t()
+        if residual is not None:
+            r = r + residual
+        if out is None:
+            return r
+        if accumulate:
+            out.add_(r)
+        else:
+            out.copy_(r)
+        return out
+
+    def gemm_nn(self, a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``a[M,K] @ b[K,N] -> [M,N]`` (data-gradient GEMM)."""
+        r = a @ b
+        if out is None:
+            return r
+        out.copy_(r)
+        return out
+
+    def gemm_tn(self, a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None,
+                accumulate: bool = False) -> torch.Tensor:
+        """``a[K,M]^T @ b[K,N] -> [M,N]`` (weight-gradient GEMM, fp32 accumulation)."""
+        r = (a.t() @ b)
+        if out is None:
+            return r
+        if accumulate:
+            out.add_(r.to(out.dtype))
+        else:
+            out.copy_(r)
+        return out
+
+    # --------------------------------------------------- AttnRes route + norm
+    def route_norm_fwd(self, srcs: Sequence[torch.Tensor], q: Optional[torch.Tensor],
+                       rn_w: Optional[torch.Tensor], n_w: torch.Tensor, eps: float):
+        """Fused depth-routing and RMSNorm.
+
+        ``srcs``: S tensors ``[N,D]`` (committed blocks oldest first, then the partial).
+        ``q``/``rn_w``: pseudo-query and key-norm weight ``[D]``; ``None`` means "no routing"
+        (S must be 1, the source passes through).  ``n_w``: weight of the RMSNorm applied to the
+        routed mixture.  Returns ``xn[N,D]`` and ``stats = (alpha[N,S], r[N,S], logit[N,S],
+        rstd[N])`` in fp32.  The mixture itself is never materialised for the caller.
+        """
+        u = torch.stack([_f(s) for s in srcs], 1)              # [N,S,D]
+        n, s, d = u.shape
+        if q is None:
+            assert s == 1
+            alpha = torch.ones(n, 1, dtype=u.dtype, device=u.device)
+            r = torch.zeros_like(alpha)
+            logit = torch.zeros_like(alpha)
+        else:
+            w = _f((q * rn_w))
+            r = torch.rsqrt(u.pow(2).mean(-1) + eps)
+            logit = (u * w).sum(-1) * r
+            alpha = torch.softmax(logit, 1)
+        h = (alpha.unsqueeze(-1) * u).sum(1)
+        rstd = torch.rsqrt(h.pow(2).mean(-1) + eps)
+        xn = (h * rstd.unsqueeze(-1) * _f(n_w)).to(srcs[0].dtype)
+        return xn, (alpha, r, logit, rstd)
+
+    def route_norm_bwd(self, dxn: torch.Tensor, srcs: Sequence[torch.Tensor], q: Optional[torch.Tensor],
+                       rn_w: Optional[torch.Tensor], n_w: torch.Tensor, eps: float, stats,
+                       dsrcs: Sequence[torch.Tensor], acc: Sequence[bool]):
+        """Backward of :meth:`route_norm_fwd`.
+
+        Writes (``acc[s]`` False) or accumulates (True) the gradient of source ``s`` into
+        ``dsrcs[s]`` and returns fp32 ``(dq, drn_w, dn_w)`` (the first two ``None`` without routing).
+        """
+        alpha, r, logit, rstd = stats
+        u = torch.stack([_f(s) for s in srcs], 1)
+        n, s, d = u.shape
+        h = (alpha.unsqueeze(-1) * u).sum(1)
+        hn = h * rstd.unsqueeze(-1)
+        g = _f(dxn)
+        dn_w = (g * hn).sum(0)
+        gw = g * _f(n_w)
+        dh = rstd.unsqueeze(-1) * (gw - hn * (gw * hn).mean(-1, keepdim=True))
+        if q is None:
+            du = dh.unsqueeze(1)
+            dq = drn = None
+        else:
+            w = _f((q * rn_w))
+            a = (dh.unsqueeze(1) * u).sum(-1)                           # [N,S]
+            abar = (alpha * a).sum(1, keepdim=True)
+            dl = alpha * (a - abar)
+            du = alpha.unsqueeze(-1) * dh.unsqueeze(1) + dl.unsqueeze(-1) * (
+                r.unsqueeze(-1) * w - (logit * r * r / d).unsqueeze(-1) * u)
+            dw = ((dl * r).unsqueeze(-1) * u).sum((0, 1))
+            dq, drn = dw * _f(rn_w), dw * _f(q)
+        for j in range(s):
+            if acc[j]:
+                dsrcs[j].add_(du[:, j].to(dsrcs[j].dtype))
+            else:
+                dsrcs[j].copy_(du[:, j])
+        return dq, drn, dn_w
+
+    # ------------------------------------------------------ QK-norm + RoPE
+    def qknorm_rope_fwd(self, qkv: torch.Tensor, qw: Optional[torch.Tensor], kw: Optional[torch.Tensor],
+                        cos: torch.Tensor, sin: torch.Tensor, seq_len: int, n_q: int, n_kv: int, hd: int,
+                        eps: float, pos_offset: int = 0):
+        """Per-head RMSNorm (weight shared by heads) then rotate-half RoPE on the q and k parts of a
+        fused ``qkv[N,(n_q+2*n_kv)*hd]`` projection.  Token ``n`` sits at position
+        ``pos_offset + n % seq_len``.  Returns ``qk[N,(n_q+n_kv)*hd]`` and ``rstd[N,n_q+n_kv]`` (fp32)."""
+        n = qkv.shape[0]
+        nh = n_q + n_kv
+        x = _f(qkv[:, : nh * hd].reshape(n, nh, hd))
+        if qw is not None:
+            rstd = torch.rsqrt(x.pow(2).mean(-1) + eps)
+            w = torch.cat([_f(qw).expand(n_q, hd), _f(kw).expand(n_kv, hd)], 0)
+            y = x * rstd.unsqueeze(-1) * w
+        else:
+            rstd = torch.ones(n, nh, dtype=x.dtype, device=qkv.device)
+            y = x
+        pos = (torch.arange(n, device=qkv.device) % seq_len) + pos_offset
+        c, s = _f(cos[pos]).unsqueeze(1), _f(sin[pos]).unsqueeze(1)
+        h2 = hd // 2
+        rot = torch.cat([-y[..., h2:], y[..., :h2]], -1)
+        out = (y * c + rot * s).to(qkv.dtype).reshape(n, nh * hd)
+        return out, rstd
+
+    def qknorm_rope_bwd(self, dqk: torch.Tensor, qkv: torch.Tensor, qw, kw, cos, sin, rstd, seq_len: int,
+                        n_q: int, n_kv: int, hd: int, dqkv_out: torch.Tensor, pos_offset: int = 0):
+        """Backward: writes the q/k columns of ``dqkv_out[N,(n_q+2n_kv)*hd]`` and returns fp32
+        ``(dqw, dkw)`` of shape ``[hd]`` (``None`` without QK-norm)."""
+        n = qkv.shape[0]
+        nh = n_q + n_kv
+        pos = (torch.arange(n, device=qkv.device) % seq_len) + pos_offset
+        c, s = _f(cos[pos]).unsqueeze(1), _f(sin[pos]).unsqueeze(1)
+        g = _f(dqk.reshape(n, nh, hd))
+        h2 = hd // 2
+        gs = g * s
+        dy = g * c + torch.cat([gs[..., h2:], -gs[..., :h2]], -1)   # transpose of the rotation
+        if qw is None:
+            dqkv_out[:, : nh * hd] = dy.reshape(n, nh * hd)
+            return None, None
+        x = _f(qkv[:, : nh * hd].reshape(n, nh, hd))
+        xh = x * rstd.unsqueeze(-1)
+        w = torch.cat([_f(qw).expand(n_q, hd), _f(kw).expand(n_kv, hd)], 0)
+        dw_all = (dy * xh).sum(0)                                    # [nh,hd]
+        dqw, dkw = dw_all[:n_q].sum(0), dw_all[n_q:].sum(0)
+        gy = dy * w
+        dx = rstd.unsqueeze(-1) * (gy - xh * (gy * xh).mean(-1, keepdim=True))
+        dqkv_out[:, : nh * hd] = dx.reshape(n, nh * hd)
+        return dqw, dkw
+
+    # ------------------------------------------------------------ attention
+    def attention_fwd(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor):
+        """Causal GQA attention.  ``q[B,T,H,hd]``, ``k,v[B,T,KV,hd]`` (may be strided views);
+        returns ``o[B,T,H,hd]`` contiguous and ``lse[B,H,T]`` fp32 (natural log)."""
+        b, t, h, hd = q.shape
+        kv = k.shape[2]
+        g = h // kv
+        qf = _f(q).permute(0, 2, 1, 3)
+        kf = _f(k).permute(0, 2, 1, 3).repeat_interleave(g, 1)
+        vf = _f(v).permute(0, 2, 1, 3).repeat_interleave(g, 1)
+        sc = (qf @ kf.transpose(-1, -2)) / math.sqrt(hd)
+        mask = torch.ones(t, t, dtype=torch.bool, device=q.device).tril()
+        sc = sc.masked_fill(~mask, float("-inf"))
+        lse = torch.logsumexp(sc, -1)
+        o = torch.softmax(sc, -1) @ vf
+        return o.permute(0, 2, 1, 3).contiguous().to(q.dtype), lse
+
+    def attention_bwd(self, do, q, k, v, o, lse, dq_out, dk_out, dv_out) -> None:
+        """Gradients of :meth:`attention_fwd` written into the (possibly strided) ``d*_out`` views."""
+        b, t, h, hd = q.shape
+        kv = k.shape[2]
+        g = h // kv
+        qf = _f(q).permute(0, 2, 1, 3)
+        kf = _f(k).permute(0, 2, 1, 3).repeat_interleave(g, 1)
+        vf = _f(v).permute(0, 2, 1, 3).repeat_interleave(g, 1)
+        dof = _f(do).permute(0, 2, 1, 3)
+        of = _f(o).permute(0, 2, 1, 3)
+        scale = 1.0 / math.sqrt(hd)
+        sc = (qf @ kf.transpose(-1, -2)) * scale
+        mask = torch.ones(t, t, dtype=torch.bool, device=q.device).tril()
+        p = torch.exp(sc - lse.unsqueeze(-1)).masked_fill(~mask, 0.0)
+        dv = p.transpose(-1, -2) @ dof
+        dp = dof @ vf.transpose(-1, -2)
+        delta = (dof * of).sum(-1, keepdim=True)
+        ds = p * (dp - delta) * scale
+        dq = ds @ kf
+        dk = ds.transpose(-1, -2) @ qf
+        dq_out.copy_(dq.permute(0, 2, 1, 3))
+        dk_out.copy_(dk.view(b, kv, g, t, hd).sum(2).permute(0, 2, 1, 3))
+        dv_out.copy_(dv.view(b, kv, g, t, hd).sum(2).permute(0, 2, 1, 3))
+
+    # -------------------------------------------------------------- SwiGLU
+    def swiglu_fwd(self, gu: torch.Tensor) -> torch.Tensor:
+        """``silu(gate) * up`` for ``gu = [gate | up]`` of shape ``[N,2F]``."""
+        f = gu.shape[1] // 2
+        g, u = _f(gu[:, :f]), _f(gu[:, f:])
+        return (F.silu(g) * u).to(gu.dtype)
+
+    def swiglu_bwd(self, gu: torch.Tensor, dact: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        f = gu.shape[1] // 2
+        g, u, d = _f(gu[:, :f]), _f(gu[:, f:]), _f(dact)
+        sg = torch.sigmoid(g)
+        dg = d * u * sg * (1 + g * (1 - sg))
+        du = d * g * sg
+        r = torch.cat([dg, du], 1).to(gu.dtype)
+        if out is None:
+            return r
+        out.copy_(r)
+        return out
+
+    # ------------------------------------------------- LM head + CE + z-loss
+    def linear_ce(self, h: torch.Tensor, w: torch.Tensor, labels: torch.Tensor, z_weight: float,
+                  grad_scale: float, dw: Optional[torch.Tensor], dw_accumulate: bool, chunk: int = 4096,
+                  need_grad: bool = True):
+        """Chunked LM-head GEMM + cross-entropy + z-loss without materialising all logits.
+
+        ``labels[N]`` uses -100 for ignored rows.  Losses are means over the valid rows:
+        returns ``(ce_mean, z_mean_weighted, dh)`` where ``dh`` (and ``dw``, accumulated into the
+        given buffer) are gradients of ``grad_scale * (ce + z)``.
+        """
+        n = h.shape[0]
+        valid = labels >= 0
+        nv = valid.sum().clamp(min=1).to(torch.float64 if h.dtype == torch.float64 else torch.float32)
+        acc_dt = torch.float64 if h.dtype == torch.float64 else torch.float32
+        ce_sum = torch.zeros((), dtype=acc_dt, device=h.device)
+        z_sum = torch.zeros((), dtype=acc_dt, device=h.device)
+        dh = torch.empty_like(h) if need_grad else None
+        first = not dw_accumulate
+        for s in range(0, n, chunk):
+            hc, lc, vc = h[s:s + chunk], labels[s:s + chunk], valid[s:s + chunk]
+            logits = _f(self.gemm_nt(hc, w))
+            lse = torch.logsumexp(logits, -1)
+            tgt = logits.gather(1, lc.clamp(min=0).unsqueeze(1)).squeeze(1)
+            ce_sum += ((lse - tgt) * vc).sum()
+            z_sum += ((lse * lse) * vc).sum()
+            if need_grad:
+                p = torch.softmax(logits, -1)
+                dl = p * (1.0 + 2.0 * z_weight * lse).unsqueeze(1)
+                dl.scatter_add_(1, lc.clamp(min=0).unsqueeze(1), -torch.ones_like(lse).unsqueeze(1))
+                dl = (dl * (vc.to(nv.dtype) * grad_scale / nv).unsqueeze(1)).to(h.dtype)
+                self.gemm_nn(dl, w, out=dh[s:s + chunk])
+                if dw is not None:
+                    self.gemm_tn(dl, hc, out=dw, accumulate=not first)
+                    first = False
+        return ce_sum / nv, z_weight * z_sum / nv, dh
+
+    # ----------------------------------------------------------- embedding
+    def embedding_fwd(self, ids: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+        return w[ids]
+
+    def embedding_bwd(self, dout: torch.Tensor, ids: torch.Tensor, dw: torch.Tensor) -> None:
+        """``dw[ids[n]] += dout[n]`` (duplicates sum)."""
+        dw.index_add_(0, ids, dout.to(dw.dtype))
+
+    # ------------------------------------------------------- optimizer math
+    def sumsq(self, x: torch.Tensor) -> torch.Tensor:
+        return _f(x).pow(2).sum()
+
+    def adamw_step(self, p: torch.Tensor, g: torch.Tensor, m: torch.Tensor, v: torch.Tensor, step: int,
+                   lr: float, b1: float, b2: float, eps: float, wd: float, gscale) -> None:
+        """Decoupled AdamW on flat tensors; ``gscale`` (float or 0-dim tensor) multiplies the gradient."""
+        gf = _f(g) * gscale
+        m.mul_(b1).add_(gf.to(m.dtype), alpha=1 - b1)
+        v.mul_(b2).add_((gf * gf).to(v.dtype), alpha=1 - b2)
+        bc1, bc2 = 1 - b1 ** step, 1 - b2 ** step
+        pf = _f(p) * (1 - lr * wd)
+        pf = pf - (lr / bc1) * _f(m) / (_f(v).sqrt() / math.sqrt(bc2) + eps)
+        p.copy_(pf)
+
+    def muon_momentum(self, g: torch.Tensor, buf: torch.Tensor, momentum: float, nesterov: bool, gscale):
+        """``buf = m*buf + g*gscale``; returns the Nesterov update ``m*buf + g*gscale`` in fp16 together with
+        its squared Frobenius norm (fp32, 0-dim)."""
+        gf = (_f(g) * gscale).to(g.dtype)
+        buf.mul_(momentum).add_(gf)
+        upd = (momentum * buf + gf) if nesterov else buf.clone()
+        x = upd.half()
+        return x, _f(x).pow(2).sum()
+
+    def ns_normalize(self, x: torch.Tensor, sumsq: torch.Tensor) -> torch.Tensor:
+        """``x / (||x||_F + 1e-7)`` with the squared norm supplied (``muon.py:142``)."""
+        return (_f(x) / (sumsq.sqrt() + 1e-7)).to(x.dtype)
+
+    def ns_iteration(self, x: torch.Tensor, a: float, b: float, c: float) -> torch.Tensor:
+        """One Newton-Schulz step on ``x[R,C]`` (R<=C), fp16 operands (``muon.py:144-147``)."""
+        A = x @ x.t()
+        B = b * A + c * (A @ A)
+        return a * x + B @ x
+
+    def muon_apply(self, p: torch.Tensor, orth: torch.Tensor, lr: float, wd: float, scale: float,
+                   transposed: bool) -> None:
+        """``p = p*(1-lr*wd) - lr*scale*orth`` (orth given transposed when the matrix was tall)."""
+        o = orth.t() if transposed else orth
+        if wd > 0:
+            p.mul_(1 - lr * wd)
+        p.add_(o.to(p.dtype), alpha=-lr * scale)
+
+    def transpose(self, x: torch.Tensor) -> torch.Tensor:
+        return x.t().contiguous()
+
+
+TORCH_OPS = TorchOps()
