@@ -1,0 +1,80 @@
+// Shared device helpers for the sm_100a kernels: vector bf16 access, reductions, the
+// status-word convention of bounded waits, and thin wrappers over the PTX used by the
+// tensor-core kernels (mbarrier, TMA, tcgen05/TMEM).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define KB_API extern "C" __attribute__((visibility("default")))
+
+// Status codes written to a status word by kernels whose waits are bounded.
+enum KbStatus : int { KB_OK = 0, KB_TIMEOUT_TMA = 1, KB_TIMEOUT_MMA = 2, KB_TIMEOUT_EPI = 3, KB_TIMEOUT_PEER = 4,
+                      KB_BAD_ARG = 5 };
+
+struct __align__(16) bf16x8 {
+    __nv_bfloat162 v[4];
+};
+
+__device__ __forceinline__ bf16x8 ld8(const __nv_bfloat16* p) {
+    return *reinterpret_cast<const bf16x8*>(p);
+}
+__device__ __forceinline__ void st8(__nv_bfloat16* p, const bf16x8& x) {
+    *reinterpret_cast<bf16x8*>(p) = x;
+}
+__device__ __forceinline__ void unpack8(const bf16x8& x, float* f) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        float2 t = __bfloat1622float2(x.v[i]);
+        f[2 * i] = t.x;
+        f[2 * i + 1] = t.y;
+    }
+}
+__device__ __forceinline__ bf16x8 pack8(const float* f) {
+    bf16x8 r;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) r.v[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+    return r;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum NV values across the block; every thread gets the totals.  `scratch` holds
+// NV * 32 floats.  Contains two __syncthreads, so it may be reused back to back.
+template <int NV>
+__device__ __forceinline__ void block_sum(float* vals, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = (blockDim.x + 31) >> 5;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) vals[i] = warp_sum(vals[i]);
+    __syncthreads();
+    if (lane == 0) {
+#pragma unroll
+        for (int i = 0; i < NV; ++i) scratch[i * 32 + warp] = vals[i];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        float v = lane < nwarp ? scratch[i * 32 + lane] : 0.f;
+        vals[i] = warp_sum(v);
+    }
+}
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ uint64_t global_timer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
