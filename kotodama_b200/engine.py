@@ -100,14 +100,36 @@ class ParamArena:
         self.params = alloc(self.total)
         self.grads = alloc(self.total)
         self.by_name = {s.name: s for s in self.slots}
+        owners = {}
+        for mod_name, mod in model.named_modules():
+            for pn in mod._parameters:
+                owners[(mod_name + "." if mod_name else "") + pn] = (mod, pn)
         with torch.no_grad():
             for s in self.slots:
                 view = self.params[s.offset:s.offset + s.numel].view(s.shape)
-                view.copy_(s.param.data)
-                s.param.data = view
-                s.param.grad = self.grads[s.offset:s.offset + s.numel].view(s.shape)
-        for b in model.buffers():
-            b.data = b.data.to(device)
+                if not s.param.is_meta:
+                    view.copy_(s.param.data)
+                mod, pn = owners[s.name]
+                newp = nn.Parameter(view, requires_grad=True)
+                newp.grad = self.grads[s.offset:s.offset + s.numel].view(s.shape)
+                mod._parameters[pn] = newp
+                s.param = newp
+        model.materialize_buffers(device)
+
+    @torch.no_grad()
+    def init_weights(self, num_layers: int, seed: int) -> None:
+        """Reference initialisation (``llama.py:583-598``) written straight into the arena."""
+        gen = torch.Generator(device=self.params.device).manual_seed(seed)
+        scale = 1.0 / math.sqrt(2 * num_layers)
+        for s in self.slots:
+            v = self.params[s.offset:s.offset + s.numel].view(s.shape)
+            if len(s.shape) == 2:
+                std = 0.02 * (scale if ("o_proj" in s.name or "down_proj" in s.name) else 1.0)
+                v.copy_(torch.randn(s.shape, device=v.device, generator=gen) * std)
+            elif "query" in s.name:
+                v.zero_()
+            else:
+                v.fill_(1.0)
 
     def view(self, name: str, grads: bool = False) -> torch.Tensor:
         s = self.by_name[name]
@@ -200,6 +222,15 @@ class TrainEngine:
                     self.momentum[s.name] = torch.zeros(s.shape, device=self.device, dtype=dtype)
         self._wcache: dict[str, torch.Tensor] = {}
         self._gather_weights()
+
+    @classmethod
+    def from_meta(cls, model: KotodamaModel, cfg: ModelConfig, *, seed: int = 0, **kw: Any) -> "TrainEngine":
+        """Build from a model whose parameters are on the meta device: weights are initialised on
+        the target device directly in the arena (no host copy of a multi-billion-parameter model)."""
+        eng = cls(model, **kw)
+        eng.arena.init_weights(cfg.num_layers, seed)
+        eng.comm.attach(eng)   # re-broadcast: ranks must start from identical weights
+        return eng
 
     # ------------------------------------------------------------ helpers
     def _assign_owners(self) -> None:

@@ -228,11 +228,25 @@ class KotodamaModel(nn.Module):
                 masks[2 * i + 1, : n + 1] = True
             masks[2 * config.num_layers, : n + 1] = True
             self.register_buffer("_attn_res_masks", masks, persistent=False)
-            self._attn_res_active_counts = [int(m.sum()) for m in masks]
+            self._attn_res_active_counts = [n for _, _, n in self.routing_table()]
         cos, sin = rope_tables(config.head_dim, config.max_position_embeddings, config.rope_theta)
         self.register_buffer("rope_cos", cos, persistent=False)
         self.register_buffer("rope_sin", sin, persistent=False)
         self._init_weights()
+
+    def materialize_buffers(self, device: torch.device | str) -> None:
+        """(Re)create the non-persistent buffers on ``device``; needed after meta-device construction."""
+        c = self.config
+        cos, sin = rope_tables(c.head_dim, c.max_position_embeddings, c.rope_theta, device=torch.device(device))
+        self.rope_cos, self.rope_sin = cos, sin
+        if c.attn_res:
+            m = self._attn_res_masks
+            if m.is_meta:
+                masks = torch.zeros(2 * c.num_layers + 1, self._attn_res_max_sources, dtype=torch.bool)
+                for j, (_, _, n) in enumerate(self.routing_table()):
+                    masks[j, :n] = True
+                m = masks
+            self._attn_res_masks = m.to(device)
 
     # ---- initialisation -------------------------------------------------
     def _init_weights(self) -> None:

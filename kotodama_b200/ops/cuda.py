@@ -1,0 +1,302 @@
+"""sm_100a backend: the same op contract as :class:`TorchOps`, carried out by the kernels in
+``csrc/`` through ``ctypes`` (raw pointers + the current CUDA stream).
+
+Activations and parameters are bf16, statistics fp32, Newton-Schulz operands fp16.  A GEMM
+whose operands break the TMA rules (16-byte aligned base, leading dimension a multiple of 8
+elements) raises instead of taking another path.  Kernels that wait (mbarrier pipelines) bound
+their waits and report through a device status word, read by :meth:`CudaOps.check_status`.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from typing import Optional, Sequence
+
+import torch
+
+from . import _build
+from .reference import TorchOps
+
+_VP = ctypes.c_void_p
+_I = ctypes.c_int
+_LL = ctypes.c_longlong
+_F = ctypes.c_float
+
+_FMT = {torch.float16: 0, torch.bfloat16: 1}
+_OUT = {torch.float16: 0, torch.bfloat16: 1, torch.float32: 2}
+
+
+def _p(t: Optional[torch.Tensor]) -> _VP:
+    return _VP(t.data_ptr()) if t is not None else _VP(None)
+
+
+def _st() -> _VP:
+    return _VP(torch.cuda.current_stream().cuda_stream)
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+class CudaOps(TorchOps):
+    name = "sm100"
+
+    def __init__(self, gemm_backend: str = "tcgen05", attention_backend: str = "auto") -> None:
+        self.lib = _build.load()
+        import os
+        self.gemm_backend = os.environ.get("KOTODAMA_GEMM", gemm_backend)   # "cublas" = library baseline
+        self.attention_backend = attention_backend
+        self.mn_major = os.environ.get("KOTODAMA_MN_MAJOR", "1") == "1"   # MN-major GEMM operands (no transposes)
+        self.launches = 0              # launches of kernels from this library
+        self._status: dict[int, torch.Tensor] = {}
+        self.gemm_max_ctas = 0
+        for name in ("kb_route_bwd_grid", "kb_qknorm_grid_warps"):
+            getattr(self.lib, name).restype = _I
+
+    # ------------------------------------------------------------------ utils
+    def _rc(self, rc: int, what: str) -> None:
+        self.launches += 1
+        if rc != 0:
+            raise KernelError(f"{what}: launcher returned {rc}")
+
+    def status(self, device: torch.device) -> torch.Tensor:
+        idx = device.index if device.index is not None else torch.cuda.current_device()
+        if idx not in self._status:
+            self._status[idx] = torch.zeros(1, dtype=torch.int32, device=device)
+        return self._status[idx]
+
+    def check_status(self, device: Optional[torch.device] = None) -> None:
+        """Host-side check of the bounded-wait status word (synchronises)."""
+        for idx, t in self._status.items():
+            v = int(t.item())
+            if v != 0:
+                t.zero_()
+                raise KernelError(f"device {idx}: a kernel wait timed out (status {v})")
+
+    # ------------------------------------------------------------------ GEMM
+    def _gemm(self, a: torch.Tensor, b: torch.Tensor, M: int, N: int, K: int, a_mn: bool, b_mn: bool,
+              out: Optional[torch.Tensor] = None, cin: Optional[torch.Tensor] = None, alpha: float = 1.0,
+              beta: float = 0.0, out_dtype: Optional[torch.dtype] = None, batch: int = 1) -> torch.Tensor:
+        out_dtype = out_dtype or (out.dtype if out is not None else a.dtype)
+        lead = (batch,) if batch > 1 else ()
+        if out is None:
+            out = torch.empty(*lead, M, N, device=a.device, dtype=out_dtype)
+        if self.gemm_backend == "cublas":
+            am = a.transpose(-1, -2) if a_mn else a
+            bm = b if b_mn else b.transpose(-1, -2)
+            r = torch.matmul(am, bm).float() * alpha
+            if cin is not None:
+                r = r + beta * cin.float()
+            out.copy_(r)
+            return out
+        for t in (a, b):
+            if t.stride(-1) != 1 or t.stride(-2) % 8 or t.data_ptr() % 16 or t.dtype not in _FMT:
+                raise KernelError(f"GEMM operand not TMA-compatible: shape {tuple(t.shape)} stride {t.stride()} {t.dtype}")
+        if out.stride(-1) != 1 or (cin is not None and (cin.stride(-1) != 1 or cin.dtype != out.dtype)):
+            raise KernelError("GEMM output/addend must be row-major and of one dtype")
+        bs = lambda t: t.stride(0) if batch > 1 else 0
+        rc = self.lib.kb_gemm(_p(a), _p(b), _p(out), _p(cin), _I(M), _I(N), _I(K), _I(batch),
+                              _LL(a.stride(-2)), _LL(b.stride(-2)), _LL(out.stride(-2)),
+                              _LL(cin.stride(-2) if cin is not None else 0),
+                              _LL(bs(a)), _LL(bs(b)), _LL(bs(out)), _LL(bs(cin) if cin is not None else 0),
+                              _I(int(a_mn)), _I(int(b_mn)), _I(_FMT[a.dtype]), _I(_FMT[b.dtype]), _I(_OUT[out.dtype]),
+                              _F(alpha), _F(beta), _p(self.status(a.device)), _I(self.gemm_max_ctas), _st())
+        self._rc(rc, "kb_gemm")
+        return out
+
+    def gemm_nt(self, a, b, out=None, residual=None, accumulate=False):
+        cin = residual if residual is not None else (out if accumulate else None)
+        return self._gemm(a, b, a.shape[0], b.shape[0], a.shape[1], False, False, out, cin, 1.0, 1.0)
+
+    def gemm_nn(self, a, b, out=None):
+        if self.mn_major:
+            return self._gemm(a, b, a.shape[0], b.shape[1], a.shape[1], False, True, out)
+        return self._gemm(a, self.transpose(b), a.shape[0], b.shape[1], a.shape[1], False, False, out)
+
+    def gemm_tn(self, a, b, out=None, accumulate=False):
+        cin = out if accumulate else None
+        if self.mn_major:
+            return self._gemm(a, b, a.shape[1], b.shape[1], a.shape[0], True, True, out, cin, 1.0, 1.0)
+        return self._gemm(self.transpose(a), self.transpose(b), a.shape[1], b.shape[1], a.shape[0], False, False,
+                          out, cin, 1.0, 1.0)
+
+    # ------------------------------------------------------------------ routing
+    def route_norm_fwd(self, srcs: Sequence[torch.Tensor], q, rn_w, n_w, eps: float):
+        S = len(srcs)
+        N, D = srcs[0].shape
+        dev = srcs[0].device
+        xn = torch.empty(N, D, device=dev, dtype=torch.bfloat16)
+        routing = q is not None
+        alpha = torch.empty(N, S, device=dev, dtype=torch.float32) if routing else None
+        r = torch.empty(N, S, device=dev, dtype=torch.float32) if routing else None
+        logit = torch.empty(N, S, device=dev, dtype=torch.float32) if routing else None
+        rstd = torch.empty(N, device=dev, dtype=torch.float32)
+        arr = (_VP * S)(*[s.data_ptr() for s in srcs])
+        rc = self.lib.kb_route_norm_fwd(arr, _I(S), _p(q), _p(rn_w), _p(n_w), _p(xn), _p(alpha), _p(r), _p(logit),
+                                        _p(rstd), _I(N), _I(D), _F(eps), _st())
+        self._rc(rc, "kb_route_norm_fwd")
+        return xn, (alpha, r, logit, rstd)
+
+    def route_norm_bwd(self, dxn, srcs, q, rn_w, n_w, eps, stats, dsrcs, acc):
+        alpha, r, logit, rstd = stats
+        S = len(srcs)
+        N, D = srcs[0].shape
+        dev = dxn.device
+        grid = self.lib.kb_route_bwd_grid(_I(N))
+        routing = q is not None
+        dnw_part = torch.empty(grid, D, device=dev, dtype=torch.float32)
+        dw_part = torch.empty(grid, D, device=dev, dtype=torch.float32) if routing else None
+        sa = (_VP * S)(*[s.data_ptr() for s in srcs])
+        da = (_VP * S)(*[d.data_ptr() for d in dsrcs])
+        mask = sum(1 << i for i, a in enumerate(acc) if a)
+        rc = self.lib.kb_route_norm_bwd(sa, da, ctypes.c_uint(mask), _I(S), _p(dxn), _p(q), _p(rn_w), _p(n_w),
+                                        _p(alpha), _p(r), _p(logit), _p(rstd), _p(dw_part), _p(dnw_part), _I(N),
+                                        _I(D), _st())
+        self._rc(rc, "kb_route_norm_bwd")
+        dn_w = self._colsum(dnw_part)
+        if not routing:
+            return None, None, dn_w
+        dw = self._colsum(dw_part)
+        return dw * rn_w.float(), dw * q.float(), dn_w
+
+    def _colsum(self, part: torch.Tensor) -> torch.Tensor:
+        out = torch.empty(part.shape[1], device=part.device, dtype=torch.float32)
+        self._rc(self.lib.kb_colsum(_p(part), _p(out), _I(part.shape[0]), _I(part.shape[1]), _st()), "kb_colsum")
+        return out
+
+    # ------------------------------------------------------------------ QK-norm + RoPE
+    def qknorm_rope_fwd(self, qkv, qw, kw, cos, sin, seq_len, n_q, n_kv, hd, eps, pos_offset=0):
+        N = qkv.shape[0]
+        out = torch.empty(N, (n_q + n_kv) * hd, device=qkv.device, dtype=qkv.dtype)
+        rstd = torch.empty(N, n_q + n_kv, device=qkv.device, dtype=torch.float32)
+        rc = self.lib.kb_qknorm_rope_fwd(_p(qkv), _p(qw), _p(kw), _p(cos), _p(sin), _p(out), _p(rstd), _I(N),
+                                         _I(seq_len), _I(n_q), _I(n_kv), _I(hd), _I(pos_offset), _F(eps), _st())
+        self._rc(rc, "kb_qknorm_rope_fwd")
+        return out, rstd
+
+    def qknorm_rope_bwd(self, dqk, qkv, qw, kw, cos, sin, rstd, seq_len, n_q, n_kv, hd, dqkv_out, pos_offset=0):
+        N = qkv.shape[0]
+        norm = qw is not None
+        warps = self.lib.kb_qknorm_grid_warps()
+        part = torch.empty(warps, 2 * hd, device=qkv.device, dtype=torch.float32) if norm else None
+        rc = self.lib.kb_qknorm_rope_bwd(_p(dqk), _p(qkv), _p(qw), _p(kw), _p(cos), _p(sin), _p(rstd), _p(dqkv_out),
+                                         _p(part), _I(N), _I(seq_len), _I(n_q), _I(n_kv), _I(hd), _I(pos_offset), _st())
+        self._rc(rc, "kb_qknorm_rope_bwd")
+        if not norm:
+            return None, None
+        dw = self._colsum(part)
+        return dw[:hd], dw[hd:]
+
+    # ------------------------------------------------------------------ attention
+    def attention_fwd(self, q, k, v):
+        from .attention import attention_fwd
+        return attention_fwd(self, q, k, v)
+
+    def attention_bwd(self, do, q, k, v, o, lse, dq_out, dk_out, dv_out):
+        from .attention import attention_bwd
+        return attention_bwd(self, do, q, k, v, o, lse, dq_out, dk_out, dv_out)
+
+    # ------------------------------------------------------------------ SwiGLU
+    def swiglu_fwd(self, gu):
+        N, F2 = gu.shape
+        act = torch.empty(N, F2 // 2, device=gu.device, dtype=gu.dtype)
+        self._rc(self.lib.kb_swiglu_fwd(_p(gu), _p(act), _LL(N), _I(F2 // 2), _st()), "kb_swiglu_fwd")
+        return act
+
+    def swiglu_bwd(self, gu, dact, out=None):
+        N, F2 = gu.shape
+        out = out if out is not None else torch.empty_like(gu)
+        self._rc(self.lib.kb_swiglu_bwd(_p(gu), _p(dact), _p(out), _LL(N), _I(F2 // 2), _st()), "kb_swiglu_bwd")
+        return out
+
+    # ------------------------------------------------------------------ loss head
+    def linear_ce(self, h, w, labels, z_weight, grad_scale, dw, dw_accumulate, chunk=4096, need_grad=True):
+        N, D = h.shape
+        V = w.shape[0]
+        dev = h.device
+        row_ce = torch.empty(N, device=dev, dtype=torch.float32)
+        row_z = torch.empty(N, device=dev, dtype=torch.float32)
+        nv = (labels >= 0).sum().clamp(min=1).float()
+        inv = (1.0 / nv).reshape(1)
+        dh = torch.empty_like(h) if need_grad else None
+        first = not dw_accumulate
+        logits = torch.empty(min(chunk, N), V, device=dev, dtype=h.dtype)
+        for s in range(0, N, chunk):
+            e = min(N, s + chunk)
+            lg = logits[: e - s]
+            self.gemm_nt(h[s:e], w, out=lg)
+            rc = self.lib.kb_ce_zloss(_p(lg), _p(labels[s:e]), _p(row_ce[s:e]), _p(row_z[s:e]), _p(inv),
+                                      _F(z_weight), _F(grad_scale), _I(e - s), _I(V), _I(int(need_grad)), _st())
+            self._rc(rc, "kb_ce_zloss")
+            if need_grad:
+                self.gemm_nn(lg, w, out=dh[s:e])
+                if dw is not None:
+                    self.gemm_tn(lg, h[s:e], out=dw, accumulate=not first)
+                    first = False
+        sums = torch.empty(2, device=dev, dtype=torch.float32)
+        self._rc(self.lib.kb_sum_f32(_p(row_ce), _I(N), _p(sums[0:1]), _st()), "kb_sum_f32")
+        self._rc(self.lib.kb_sum_f32(_p(row_z), _I(N), _p(sums[1:2]), _st()), "kb_sum_f32")
+        return sums[0] * inv[0], sums[1] * (z_weight * inv[0]), dh
+
+    # ------------------------------------------------------------------ embedding
+    def embedding_fwd(self, ids, w):
+        N, D = ids.numel(), w.shape[1]
+        out = torch.empty(N, D, device=w.device, dtype=w.dtype)
+        self._rc(self.lib.kb_embedding_fwd(_p(ids), _p(w), _p(out), _I(N), _I(D), _st()), "kb_embedding_fwd")
+        return out
+
+    def embedding_bwd(self, dout, ids, dw):
+        self._rc(self.lib.kb_embedding_bwd(_p(ids), _p(dout), _p(dw), _I(ids.numel()), _I(dw.shape[1]), _st()),
+                 "kb_embedding_bwd")
+
+    # ------------------------------------------------------------------ optimizer math
+    def sumsq(self, x, out: Optional[torch.Tensor] = None, accumulate: bool = False):
+        dt = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}[x.dtype]
+        partial = torch.empty(1024, device=x.device, dtype=torch.float32)
+        res = out if out is not None else torch.empty(1, device=x.device, dtype=torch.float32)
+        self._rc(self.lib.kb_sumsq(_p(x), _LL(x.numel()), _I(dt), _p(partial), _p(res), _I(int(accumulate)), _st()),
+                 "kb_sumsq")
+        self.launches += 1
+        return res[0] if out is None else res
+
+    def adamw_step(self, p, g, m, v, step, lr, b1, b2, eps, wd, gscale):
+        gs = gscale.reshape(1).float() if isinstance(gscale, torch.Tensor) else None
+        if gs is None and gscale != 1.0:
+            gs = torch.full((1,), float(gscale), device=p.device)
+        self._rc(self.lib.kb_adamw(_p(p), _p(g), _p(m), _p(v), _LL(p.numel()), _p(gs), _F(lr), _F(b1), _F(b2),
+                                   _F(eps), _F(wd), _I(step), _st()), "kb_adamw")
+
+    def muon_momentum(self, g, buf, momentum, nesterov, gscale):
+        gs = gscale.reshape(1).float() if isinstance(gscale, torch.Tensor) else None
+        x = torch.empty(g.shape, device=g.device, dtype=torch.float16)
+        partial = torch.empty(1024, device=g.device, dtype=torch.float32)
+        sq = torch.empty(1, device=g.device, dtype=torch.float32)
+        self._rc(self.lib.kb_muon_momentum(_p(g), _p(buf), _p(x), _LL(g.numel()), _p(gs), _F(momentum),
+                                           _I(int(nesterov)), _p(partial), _p(sq), _st()), "kb_muon_momentum")
+        self.launches += 1
+        return x, sq
+
+    def ns_normalize(self, x, sumsq):
+        self._rc(self.lib.kb_ns_normalize(_p(x), _LL(x.numel()), _p(sumsq.reshape(1)), _st()), "kb_ns_normalize")
+        return x
+
+    def ns_iteration(self, x, a, b, c):
+        R, C = x.shape[-2], x.shape[-1]
+        batch = x.shape[0] if x.ndim == 3 else 1
+        A = self._gemm(x, x, R, R, C, False, False, batch=batch)
+        B = self._gemm(A, A, R, R, R, False, False, cin=A, alpha=c, beta=b, batch=batch)
+        if self.mn_major:
+            return self._gemm(B, x, R, C, R, False, True, cin=x, alpha=1.0, beta=a, batch=batch)
+        xt = self.transpose(x)
+        return self._gemm(B, xt, R, C, R, False, False, cin=x, alpha=1.0, beta=a, batch=batch)
+
+    def muon_apply(self, p, orth, lr, wd, scale, transposed):
+        R, C = p.shape
+        self._rc(self.lib.kb_muon_apply(_p(p), _p(orth), _I(R), _I(C), _F(lr), _F(wd), _F(scale),
+                                        _I(int(transposed)), _st()), "kb_muon_apply")
+
+    def transpose(self, x):
+        assert x.ndim == 2 and x.is_contiguous() and x.element_size() == 2
+        out = torch.empty(x.shape[1], x.shape[0], device=x.device, dtype=x.dtype)
+        self._rc(self.lib.kb_transpose16(_p(x), _p(out), _I(x.shape[0]), _I(x.shape[1]), _st()), "kb_transpose16")
+        return out

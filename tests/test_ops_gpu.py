@@ -1,0 +1,195 @@
+"""Every sm_100a kernel against the plain-PyTorch fp32 reference of the same op."""
+import math
+
+import pytest
+import torch
+
+from kotodama_b200.ops.reference import TORCH_OPS
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from kotodama_b200.ops import get_ops
+    o = get_ops("cuda")
+    assert o.name == "sm100"
+    return o
+
+
+def rel_err(a, b):
+    a, b = a.float(), b.float()
+    return float((a - b).norm() / (b.norm() + 1e-12))
+
+
+def bf(*shape, scale=1.0, seed=0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    return (torch.randn(*shape, device="cuda", generator=g) * scale).bfloat16()
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (384, 768, 3072), (200, 136, 72), (1024, 3072, 8192)])
+def test_gemm_nt(ops, M, N, K):
+    a, b = bf(M, K, seed=1), bf(N, K, seed=2)
+    c = ops.gemm_nt(a, b)
+    ref = a.float() @ b.float().t()
+    ops.check_status()
+    assert rel_err(c, ref) < 1e-2, rel_err(c, ref)
+
+
+def test_gemm_nt_epilogues(ops):
+    M, N, K = 256, 512, 192
+    a, b, r = bf(M, K, seed=1), bf(N, K, seed=2), bf(M, N, seed=3)
+    ref = a.float() @ b.float().t()
+    assert rel_err(ops.gemm_nt(a, b, residual=r), ref + r.float()) < 1e-2
+    out = r.clone()
+    ops.gemm_nt(a, b, out=out, accumulate=True)
+    assert rel_err(out, ref + r.float()) < 1e-2
+    o32 = torch.zeros(M, N, device="cuda")
+    ops._gemm(a, b, M, N, K, False, False, out=o32)
+    assert rel_err(o32, ref) < 1e-3
+    ah, bh = a.half(), b.half()
+    ch = ops._gemm(ah, bh, M, N, K, False, False, cin=r.half(), alpha=0.5, beta=2.0)
+    assert rel_err(ch, 0.5 * (ah.float() @ bh.float().t()) + 2.0 * r.half().float()) < 1e-2
+    ops.check_status()
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 320), (200, 136, 72)])
+def test_gemm_mn_major(ops, M, N, K):
+    a, b = bf(M, K, seed=1), bf(K, N, seed=2)
+    ops.mn_major = True
+    c = ops.gemm_nn(a, b)                      # B stored [K,N]
+    ops.check_status()
+    assert rel_err(c, a.float() @ b.float()) < 1e-2
+    at = bf(K, M, seed=3)
+    c2 = ops.gemm_tn(at, b)                    # both stored [K, *]
+    ops.check_status()
+    assert rel_err(c2, at.float().t() @ b.float()) < 1e-2
+
+
+def test_gemm_batched(ops):
+    x = (torch.randn(3, 128, 320, device="cuda") * 0.1).half()
+    A = ops._gemm(x, x, 128, 128, 320, False, False, batch=3)
+    ops.check_status()
+    assert rel_err(A, x.float() @ x.float().transpose(1, 2)) < 1e-2
+
+
+@pytest.mark.parametrize("S,D,routing", [(1, 256, True), (3, 3072, True), (8, 3072, True), (9, 4096, True),
+                                          (1, 3072, False), (5, 512, True)])
+def test_route_norm(ops, S, D, routing):
+    N = 777
+    srcs = [bf(N, D, seed=10 + i) for i in range(S)]
+    q = bf(D, scale=0.3, seed=3) if routing else None
+    rn = (1 + 0.1 * torch.randn(D, device="cuda")).bfloat16() if routing else None
+    nw = (1 + 0.1 * torch.randn(D, device="cuda")).bfloat16()
+    xn, st = ops.route_norm_fwd(srcs, q, rn, nw, 1e-5)
+    f = lambda t: t.float() if t is not None else None
+    xr, sr = TORCH_OPS.route_norm_fwd([f(s) for s in srcs], f(q), f(rn), f(nw), 1e-5)
+    assert rel_err(xn, xr) < 1e-2
+    if routing:
+        assert torch.allclose(st[0], sr[0], atol=2e-3)
+    dxn = bf(N, D, seed=77)
+    ds = [bf(N, D, seed=50 + i) for i in range(S)]
+    ds_ref = [d.float().clone() for d in ds]
+    acc = [i % 2 == 0 for i in range(S)]
+    dq, drn, dnw = ops.route_norm_bwd(dxn, srcs, q, rn, nw, 1e-5, st, ds, acc)
+    dqr, drnr, dnwr = TORCH_OPS.route_norm_bwd(f(dxn), [f(s) for s in srcs], f(q), f(rn), f(nw), 1e-5, sr, ds_ref, acc)
+    for a, b in zip(ds, ds_ref):
+        assert rel_err(a, b) < 1.5e-2
+    assert rel_err(dnw, dnwr) < 1e-2
+    if routing:
+        assert rel_err(dq, dqr) < 2e-2 and rel_err(drn, drnr) < 2e-2
+
+
+@pytest.mark.parametrize("hd,nq,nkv,norm", [(128, 6, 2, True), (64, 4, 2, True), (128, 3, 1, False)])
+def test_qknorm_rope(ops, hd, nq, nkv, norm):
+    from kotodama_b200.models.llama import rope_tables
+    B, T = 2, 96
+    N = B * T
+    qkv = bf(N, (nq + 2 * nkv) * hd, seed=4)
+    qw = (1 + 0.1 * torch.randn(hd, device="cuda")).bfloat16() if norm else None
+    kw = (1 + 0.1 * torch.randn(hd, device="cuda")).bfloat16() if norm else None
+    cos, sin = rope_tables(hd, 128, device=torch.device("cuda"))
+    out, rstd = ops.qknorm_rope_fwd(qkv, qw, kw, cos, sin, T, nq, nkv, hd, 1e-5)
+    f = lambda t: t.float() if t is not None else None
+    outr, rstdr = TORCH_OPS.qknorm_rope_fwd(f(qkv), f(qw), f(kw), cos, sin, T, nq, nkv, hd, 1e-5)
+    assert rel_err(out, outr) < 1e-2
+    dqk = bf(N, (nq + nkv) * hd, seed=5)
+    dqkv = torch.zeros_like(qkv)
+    dref = torch.zeros(N, (nq + 2 * nkv) * hd, device="cuda")
+    dqw, dkw = ops.qknorm_rope_bwd(dqk, qkv, qw, kw, cos, sin, rstd, T, nq, nkv, hd, dqkv)
+    dqwr, dkwr = TORCH_OPS.qknorm_rope_bwd(f(dqk), f(qkv), f(qw), f(kw), cos, sin, rstdr, T, nq, nkv, hd, dref)
+    assert rel_err(dqkv[:, : (nq + nkv) * hd], dref[:, : (nq + nkv) * hd]) < 1e-2
+    if norm:
+        assert rel_err(dqw, dqwr) < 2e-2 and rel_err(dkw, dkwr) < 2e-2
+
+
+def test_swiglu(ops):
+    gu = bf(300, 2 * 688, seed=6)
+    act = ops.swiglu_fwd(gu)
+    assert rel_err(act, TORCH_OPS.swiglu_fwd(gu.float())) < 1e-2
+    d = bf(300, 688, seed=7)
+    assert rel_err(ops.swiglu_bwd(gu, d), TORCH_OPS.swiglu_bwd(gu.float(), d.float())) < 1e-2
+
+
+def test_linear_ce(ops):
+    N, D, V = 700, 256, 4096
+    h, w = bf(N, D, seed=8), bf(V, D, scale=0.05, seed=9)
+    labels = torch.randint(0, V, (N,), device="cuda")
+    labels[::7] = -100
+    dw = torch.zeros(V, D, device="cuda", dtype=torch.bfloat16)
+    ce, z, dh = ops.linear_ce(h, w, labels, 1e-3, 0.5, dw, False, chunk=256)
+    dwr = torch.zeros(V, D, device="cuda")
+    cer, zr, dhr = TORCH_OPS.linear_ce(h.float(), w.float(), labels, 1e-3, 0.5, dwr, False, chunk=256)
+    ops.check_status()
+    assert abs(float(ce) - float(cer)) < 2e-2 and abs(float(z) - float(zr)) < 1e-3
+    assert rel_err(dh, dhr) < 3e-2 and rel_err(dw, dwr) < 3e-2
+
+
+def test_embedding(ops):
+    V, D, N = 1000, 256, 5000
+    w = bf(V, D, seed=11)
+    ids = torch.randint(0, V, (N,), device="cuda")
+    assert torch.equal(ops.embedding_fwd(ids, w), w[ids])
+    dout = bf(N, D, scale=0.1, seed=12)
+    dw = torch.zeros(V, D, device="cuda", dtype=torch.bfloat16)
+    ops.embedding_bwd(dout, ids, dw)
+    ref = torch.zeros(V, D, device="cuda").index_add_(0, ids, dout.float())
+    assert rel_err(dw, ref) < 2e-2
+
+
+def test_optimizer_kernels(ops):
+    n = 100_003
+    p, g = bf(n, seed=13), bf(n, scale=0.1, seed=14)
+    m = torch.zeros(n, device="cuda"); v = torch.zeros(n, device="cuda")
+    pr, mr, vr = p.float().clone(), m.clone(), v.clone()
+    coef = torch.tensor(0.7, device="cuda")
+    for step in (1, 2):
+        ops.adamw_step(p, g, m, v, step, 1e-3, 0.9, 0.95, 1e-8, 0.1, coef)
+        TORCH_OPS.adamw_step(pr, g.float(), mr, vr, step, 1e-3, 0.9, 0.95, 1e-8, 0.1, coef)
+    assert rel_err(p, pr) < 1e-2 and rel_err(m, mr) < 1e-3
+    assert abs(float(ops.sumsq(g)) - float(g.float().pow(2).sum())) / float(g.float().pow(2).sum()) < 1e-4
+    G = bf(256, 512, scale=0.02, seed=15)
+    buf = torch.zeros_like(G); bufr = torch.zeros_like(G)
+    x, sq = ops.muon_momentum(G, buf, 0.95, True, coef)
+    xr, sqr = TORCH_OPS.muon_momentum(G, bufr, 0.95, True, coef)
+    assert rel_err(x, xr) < 1e-2 and abs(float(sq) - float(sqr)) / float(sqr) < 1e-2
+    xt = ops.transpose(x)
+    assert torch.equal(xt, x.t().contiguous())
+    P = bf(512, 256, seed=16); Pr = P.clone()
+    ops.muon_apply(P, x, 0.02, 0.01, 1.4, True)
+    TORCH_OPS.muon_apply(Pr, x, 0.02, 0.01, 1.4, True)
+    assert rel_err(P, Pr) < 1e-2
+
+
+def test_newton_schulz_matches_reference(ops):
+    from kotodama_b200.optim.muon import newton_schulz_orthogonalize, resolve_ns_coefficients
+    G = bf(256, 640, scale=0.02, seed=17)
+    x = G.half()
+    x = ops.ns_normalize(x.clone(), ops.sumsq(x).reshape(1))
+    for a, b, c in resolve_ns_coefficients("gram_ns", 5):
+        x = ops.ns_iteration(x, a, b, c)
+    ops.check_status()
+    ref = newton_schulz_orthogonalize(G, 5, "gram_ns")
+    assert rel_err(x, ref) < 5e-2
+    s = torch.linalg.svdvals(x.float())
+    assert 0.5 < float(s.min()) and float(s.max()) < 1.5
