@@ -171,11 +171,23 @@ class _LayerRec:
 
 
 class _OptView:
-    """What the LR scheduler and the checkpoint manager need from an optimizer."""
+    """What the LR scheduler and the checkpoint manager need from an optimizer: ``defaults``,
+    ``param_groups`` and the torch-layout ``state_dict`` / ``load_state_dict``."""
 
-    def __init__(self, lr: float, **hyper: Any) -> None:
+    def __init__(self, lr: float, state_fn=None, load_fn=None, **hyper: Any) -> None:
         self.defaults = dict(lr=lr, **hyper)
         self.param_groups = [dict(lr=lr, **hyper)]
+        self._state_fn, self._load_fn = state_fn, load_fn
+
+    def state_dict(self) -> dict[str, Any]:
+        return self._state_fn() if self._state_fn else {}
+
+    def load_state_dict(self, sd: dict[str, Any]) -> None:
+        if self._load_fn:
+            self._load_fn(sd)
+
+    def zero_grad(self, set_to_none: bool = False) -> None:
+        return None
 
 
 class TrainEngine:
@@ -187,7 +199,8 @@ class TrainEngine:
                  muon_ns_iterations: int = 5, muon_ns_coefficients: Optional[str] = None,
                  adamw_lr: float = 6e-4, adamw_betas: tuple[float, float] = (0.9, 0.95),
                  adamw_weight_decay: float = 0.1, adamw_eps: float = 1e-8, gradient_clip: float = 1.0,
-                 adamw_only: bool = False, ce_chunk: int = 4096) -> None:
+                 adamw_only: bool = False, ce_chunk: int = 4096, fp8: bool = False,
+                 fp8_recipe: str = "block128") -> None:
         from .parallel.comm import LocalComm
 
         self.device = torch.device(device)
@@ -201,10 +214,11 @@ class TrainEngine:
         self.gradient_clip = gradient_clip
         self.adamw_only = adamw_only
         self.ce_chunk = ce_chunk
+        self.fp8, self.fp8_recipe = fp8, fp8_recipe
         self.ns_coefficients = muon_ns_coefficients
-        self.muon_opt = _OptView(muon_lr, momentum=muon_momentum, nesterov=True,
+        self.muon_opt = _OptView(muon_lr, self.muon_state_dict, self.load_muon_state_dict, momentum=muon_momentum, nesterov=True,
                                  weight_decay=muon_weight_decay, ns_iterations=muon_ns_iterations)
-        self.adamw_opt = _OptView(adamw_lr, betas=tuple(adamw_betas), eps=adamw_eps,
+        self.adamw_opt = _OptView(adamw_lr, self.adamw_state_dict, self.load_adamw_state_dict, betas=tuple(adamw_betas), eps=adamw_eps,
                                   weight_decay=adamw_weight_decay)
         resolve_ns_coefficients(muon_ns_coefficients, muon_ns_iterations)
         # optimizer state
@@ -483,7 +497,7 @@ class TrainEngine:
         comm.finish_param_publish()
         return norm
 
-    def train_step(self, micro_batches: list[torch.Tensor]) -> dict[str, torch.Tensor]:
+    def train_step(self, micro_batches: list[torch.Tensor], keep_grads: bool = True) -> dict[str, torch.Tensor]:
         """One optimizer step over ``len(micro_batches)`` micro-batches (host tensors are copied
         to the device asynchronously).  Returns device scalars ``loss``, ``z_loss``, ``grad_norm``."""
         ga = len(micro_batches)
@@ -495,6 +509,15 @@ class TrainEngine:
             zl_acc = zl if zl_acc is None else zl_acc + zl
         norm = self.optimizer_step()
         return {"loss": loss_acc / ga, "z_loss": zl_acc / ga, "grad_norm": norm}
+
+    def after_load(self) -> None:
+        """Hook after a checkpoint was copied into the arena (derived copies are refreshed here)."""
+        self.comm.attach(self)
+
+    def check(self) -> None:
+        """Raise if a kernel reported a timed-out wait."""
+        if hasattr(self.ops, "check_status"):
+            self.ops.check_status()
 
     @torch.no_grad()
     def eval_loss(self, input_ids: torch.Tensor) -> torch.Tensor:
