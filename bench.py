@@ -138,6 +138,16 @@ def run_native(args, rank, world, local):
     for i in range(W):
         eng.train_step([dev_batches[i]])
     eng.ops.check_status()
+    if args.op_times:
+        # separate, untimed-by-the-benchmark pass that attributes device time to ops
+        from kotodama_b200.utils.optimer import TimedOps
+        plain = eng.ops
+        eng.ops = TimedOps(plain)
+        eng.train_step([dev_batches[0]])
+        if rank == 0:
+            with open(args.op_times, "w") as fh:
+                fh.write(eng.ops.table(1) + "\n")
+        eng.ops = plain
     sampler = ClockSampler(local)
     # ---- pass 1: device-timed
     sync_all(world)
@@ -265,6 +275,7 @@ def main() -> None:
     ap.add_argument("--attn-res-blocks", type=int, default=7)
     ap.add_argument("--backend", default="auto", choices=["auto", "native", "nccl"])
     ap.add_argument("--ref-compile", type=int, default=1)
+    ap.add_argument("--op-times", default="", help="write a per-op device-time table to this file")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     rank, world, local = dist_setup(args.gpus)

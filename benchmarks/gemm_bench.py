@@ -1,0 +1,111 @@
+#!/usr/bin/env python
+"""GEMM micro-benchmark: the tcgen05 kernel against cuBLAS (torch.matmul) on the projection
+shapes of the 3B/8B models, for the forward (NT), data-gradient (NN) and weight-gradient (TN)
+products.  CUDA events, warm-up, L2 flushed between iterations.
+
+    python benchmarks/gemm_bench.py                       # table for the 3B shapes
+    python benchmarks/gemm_bench.py --single 4096 8192 3072 nt --iters 3   # small case for ncu
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+from kotodama_b200.ops import get_ops  # noqa: E402
+
+
+def time_fn(fn, iters: int, flush: torch.Tensor) -> float:
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        flush.zero_()                    # 256 MB write: evicts the 126 MB L2
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1))
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def operands(M, N, K, mode, dtype=torch.bfloat16):
+    g = torch.Generator(device="cuda").manual_seed(0)
+    r = lambda *s: (torch.randn(*s, device="cuda", generator=g) * 0.05).to(dtype)
+    if mode == "nt":
+        return r(M, K), r(N, K)
+    if mode == "nn":
+        return r(M, K), r(K, N)
+    return r(K, M), r(K, N)
+
+
+def run(ops, M, N, K, mode, iters, flush):
+    a, b = operands(M, N, K, mode)
+    out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    mine = {"nt": lambda: ops.gemm_nt(a, b, out=out), "nn": lambda: ops.gemm_nn(a, b, out=out),
+            "tn": lambda: ops.gemm_tn(a, b, out=out)}[mode]
+    lib = {"nt": lambda: torch.matmul(a, b.t(), out=out), "nn": lambda: torch.matmul(a, b, out=out),
+           "tn": lambda: torch.matmul(a.t(), b, out=out)}[mode]
+    t_mine = time_fn(mine, iters, flush)
+    ref = out.clone().float()
+    t_lib = time_fn(lib, iters, flush)
+    err = float((out.float() - ref).norm() / (out.float().norm() + 1e-9))
+    fl = 2.0 * M * N * K
+    return dict(M=M, N=N, K=K, mode=mode, ms=round(t_mine, 4), tflops=round(fl / t_mine / 1e9, 1),
+                cublas_ms=round(t_lib, 4), cublas_tflops=round(fl / t_lib / 1e9, 1),
+                ratio=round(t_lib / t_mine, 3), rel_diff=err)
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--single", nargs=4, default=None, metavar=("M", "N", "K", "MODE"))
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--tokens", type=int, default=32768)
+    ap.add_argument("--model", default="3b")
+    ap.add_argument("--out", default="")
+    args = ap.parse_args()
+    ops = get_ops("cuda")
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    if args.single:
+        M, N, K = map(int, args.single[:3])
+        a, b = operands(M, N, K, args.single[3])
+        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        fn = {"nt": ops.gemm_nt, "nn": ops.gemm_nn, "tn": ops.gemm_tn}[args.single[3]]
+        for _ in range(args.iters):
+            fn(a, b, out=out)
+        torch.cuda.synchronize()
+        ops.check_status()
+        print("ok")
+        return
+    from kotodama_b200.config import MODEL_PRESETS
+    c = MODEL_PRESETS[args.model]
+    D, F = c["hidden_size"], c["intermediate_size"]
+    QKV = (c["num_attention_heads"] + 2 * c["num_kv_heads"]) * c["head_dim"]
+    Q = c["num_attention_heads"] * c["head_dim"]
+    T = args.tokens
+    shapes = []
+    for (n, k) in ((QKV, D), (D, Q), (2 * F, D), (D, F)):
+        shapes += [(T, n, k, "nt"), (T, k, n, "nn"), (n, k, T, "tn")]
+    shapes += [(4096, c["vocab_size"], D, "nt"), (4096, D, c["vocab_size"], "nn"), (c["vocab_size"], D, 4096, "tn")]
+    rows = [run(ops, *s, args.iters, flush) for s in shapes]
+    ops.check_status()
+    for r in rows:
+        print(json.dumps(r))
+    tot_m = sum(r["ms"] for r in rows)
+    tot_l = sum(r["cublas_ms"] for r in rows)
+    print(json.dumps({"total_ms": round(tot_m, 3), "cublas_total_ms": round(tot_l, 3), "ratio": round(tot_l / tot_m, 3)}))
+    if args.out:
+        with open(args.out, "w") as fh:
+            for r in rows:
+                fh.write(json.dumps(r) + "\n")
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,226 @@
+// In-kernel collectives over NVLink peer memory (symmetric heap: the same buffer mapped at a
+// per-rank address on every GPU).  Data moves by plain loads/stores on peer pointers; ordering
+// is by epoch flags written with release semantics after a system fence and polled with
+// acquire loads.  Every poll is bounded by a time limit; a wait that runs out records
+// KB_TIMEOUT_PEER in the status word and the kernel returns normally, so the context survives
+// and the host can raise.  Epochs only grow: flags are never reset.
+//
+//   kb_flag_signal      this rank raises flag[slot][rank] on every peer
+//   kb_flag_wait        wait until flag[slot][r] >= epoch for every r (local memory)
+//   kb_reduce_to_owner  owner sums a gradient range over all ranks (fp32), scales, stores bf16
+//   kb_allreduce_slices two-shot all-reduce: each rank reduces its slice, stores it to every peer
+//   kb_scalar_allreduce sum of one float per rank (also a full barrier)
+//   kb_muon_apply_bcast p_new = p*decay - alpha*orth written into every rank's parameter arena
+//                       (the all-gather of the updated matrix is the parameter write itself)
+#include "common.cuh"
+
+typedef __nv_bfloat16 bf16;
+
+struct PeerPtrs {
+    void* p[8];
+};
+
+__device__ __forceinline__ void st_release_sys(int* p, int v) {
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+    int v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+// Bounded poll on a local flag.  Returns false on timeout.
+__device__ __forceinline__ bool wait_flag(const int* flag, int epoch, uint64_t limit_ns) {
+    if (ld_acquire_sys(flag) >= epoch) return true;
+    const uint64_t t0 = global_timer_ns();
+    while (ld_acquire_sys(flag) < epoch) {
+        if (global_timer_ns() - t0 > limit_ns) return false;
+        __nanosleep(200);
+    }
+    return true;
+}
+
+// flags layout on every rank: int flags[slots][8]
+__global__ void flag_signal_kernel(PeerPtrs flags, int world, int rank, int slot, int epoch) {
+    if (threadIdx.x < world) {
+        __threadfence_system();
+        st_release_sys(reinterpret_cast<int*>(flags.p[threadIdx.x]) + slot * 8 + rank, epoch);
+    }
+}
+__global__ void flag_wait_kernel(const int* flags, int world, int slot, int epoch, unsigned long long limit_ns,
+                                 int* status) {
+    if (threadIdx.x < world) {
+        if (!wait_flag(flags + slot * 8 + threadIdx.x, epoch, limit_ns)) atomicMax(status, (int)KB_TIMEOUT_PEER);
+    }
+}
+
+KB_API int kb_flag_signal(void* const* peer_flags, int world, int rank, int slot, int epoch, cudaStream_t st) {
+    if (world < 1 || world > 8) return 5;
+    PeerPtrs pp;
+    for (int i = 0; i < 8; ++i) pp.p[i] = i < world ? peer_flags[i] : nullptr;
+    flag_signal_kernel<<<1, 32, 0, st>>>(pp, world, rank, slot, epoch);
+    return 0;
+}
+KB_API int kb_flag_wait(const int* flags, int world, int slot, int epoch, double limit_s, int* status,
+                        cudaStream_t st) {
+    if (world < 1 || world > 8) return 5;
+    flag_wait_kernel<<<1, 32, 0, st>>>(flags, world, slot, epoch, (unsigned long long)(limit_s * 1e9), status);
+    return 0;
+}
+
+// out[i] = scale * sum_r peer[r][offset + i]  for i in [0, n); out is this rank's own buffer range.
+__global__ void reduce_to_owner_kernel(PeerPtrs bufs, int world, long long offset, long long n, float scale,
+                                       bf16* __restrict__ out) {
+    const long long nvec = n >> 3;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec;
+         i += (long long)gridDim.x * blockDim.x) {
+        float acc[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+        for (int r = 0; r < world; ++r) {
+            const uint4 raw = __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(bufs.p[r]) + offset) + i);
+            float t[8];
+            unpack8(*reinterpret_cast<const bf16x8*>(&raw), t);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] += t[j];
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] *= scale;
+        st8(out + i * 8, pack8(acc));
+    }
+    // tail (n not a multiple of 8)
+    for (long long i = (nvec << 3) + (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+         i += (long long)gridDim.x * blockDim.x) {
+        float a = 0.f;
+        for (int r = 0; r < world; ++r) a += __bfloat162float(reinterpret_cast<const bf16*>(bufs.p[r])[offset + i]);
+        out[i] = __float2bfloat16(a * scale);
+    }
+}
+KB_API int kb_reduce_to_owner(void* const* peer_bufs, int world, long long offset, long long n, float scale,
+                              void* out, int max_ctas, cudaStream_t st) {
+    if (world < 1 || world > 8 || (offset & 7)) return 5;
+    PeerPtrs pp;
+    for (int i = 0; i < 8; ++i) pp.p[i] = i < world ? peer_bufs[i] : nullptr;
+    long long blocks = ((n >> 3) + 255) / 256;
+    if (blocks < 1) blocks = 1;
+    if (blocks > max_ctas) blocks = max_ctas;
+    reduce_to_owner_kernel<<<(int)blocks, 256, 0, st>>>(pp, world, offset, n, scale, (bf16*)out);
+    return 0;
+}
+
+// Two-shot all-reduce of [offset, offset+n): rank r owns the r-th of `world` equal slices
+// (8-element granularity), reduces it over all ranks and stores the result to every rank.
+__global__ void allreduce_slices_kernel(PeerPtrs bufs, int world, int rank, long long offset, long long n,
+                                        float scale) {
+    const long long nvec = (n + 7) >> 3;                 // caller pads the range to a multiple of 8
+    const long long per = (nvec + world - 1) / world;
+    const long long lo = per * rank, hi = min(nvec, lo + per);
+    for (long long i = lo + (long long)blockIdx.x * blockDim.x + threadIdx.x; i < hi;
+         i += (long long)gridDim.x * blockDim.x) {
+        float acc[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+        for (int r = 0; r < world; ++r) {
+            const uint4 raw = __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(bufs.p[r]) + offset) + i);
+            float t[8];
+            unpack8(*reinterpret_cast<const bf16x8*>(&raw), t);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] += t[j];
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] *= scale;
+        const bf16x8 o = pack8(acc);
+        for (int r = 0; r < world; ++r)
+            *(reinterpret_cast<bf16x8*>(reinterpret_cast<bf16*>(bufs.p[r]) + offset) + i) = o;
+    }
+}
+KB_API int kb_allreduce_slices(void* const* peer_bufs, int world, int rank, long long offset, long long n,
+                               float scale, int max_ctas, cudaStream_t st) {
+    if (world < 1 || world > 8 || (offset & 7) || (n & 7)) return 5;
+    PeerPtrs pp;
+    for (int i = 0; i < 8; ++i) pp.p[i] = i < world ? peer_bufs[i] : nullptr;
+    long long blocks = ((n >> 3) / world + 255) / 256;
+    if (blocks < 1) blocks = 1;
+    if (blocks > max_ctas) blocks = max_ctas;
+    allreduce_slices_kernel<<<(int)blocks, 256, 0, st>>>(pp, world, rank, offset, n, scale);
+    return 0;
+}
+
+// Sum of one float per rank; doubles as a barrier.  vals layout on every rank: float vals[2][8]
+// (double-buffered by epoch parity), flags as above.
+__global__ void scalar_allreduce_kernel(PeerPtrs vals, PeerPtrs flags, int world, int rank, int slot, int epoch,
+                                        const float* __restrict__ in, float* __restrict__ out,
+                                        unsigned long long limit_ns, int* status) {
+    __shared__ int ok;
+    if (threadIdx.x == 0) ok = 1;
+    __syncthreads();
+    const int par = epoch & 1;
+    if (threadIdx.x < world) {
+        const float v = in ? in[0] : 0.f;
+        reinterpret_cast<float*>(vals.p[threadIdx.x])[par * 8 + rank] = v;
+        __threadfence_system();
+        st_release_sys(reinterpret_cast<int*>(flags.p[threadIdx.x]) + slot * 8 + rank, epoch);
+        if (!wait_flag(reinterpret_cast<const int*>(flags.p[rank]) + slot * 8 + threadIdx.x, epoch, limit_ns)) {
+            atomicMax(status, (int)KB_TIMEOUT_PEER);
+            ok = 0;
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0 && out) {
+        float s = 0.f;
+        if (ok) {
+            const volatile float* mine = reinterpret_cast<const volatile float*>(vals.p[rank]) + par * 8;
+            for (int r = 0; r < world; ++r) s += mine[r];
+        }
+        out[0] = s;
+    }
+}
+KB_API int kb_scalar_allreduce(void* const* peer_vals, void* const* peer_flags, int world, int rank, int slot,
+                               int epoch, const float* in, float* out, double limit_s, int* status,
+                               cudaStream_t st) {
+    if (world < 1 || world > 8) return 5;
+    PeerPtrs pv, pf;
+    for (int i = 0; i < 8; ++i) {
+        pv.p[i] = i < world ? peer_vals[i] : nullptr;
+        pf.p[i] = i < world ? peer_flags[i] : nullptr;
+    }
+    scalar_allreduce_kernel<<<1, 32, 0, st>>>(pv, pf, world, rank, slot, epoch, in, out,
+                                              (unsigned long long)(limit_s * 1e9), status);
+    return 0;
+}
+
+// Owner's Muon parameter write, broadcast: every rank's arena gets p*decay - alpha*orth.
+// params.p[r] is rank r's arena base; the matrix sits at `offset`, shape [R,C]; orth is fp16
+// [R,C], or [C,R] when `transposed`.
+__global__ void muon_apply_bcast_kernel(PeerPtrs params, int world, int rank, long long offset,
+                                        const __half* __restrict__ o, int R, int C, float decay, float alpha,
+                                        int transposed) {
+    __shared__ float tile[32][33];
+    const int bx = blockIdx.x * 32, by = blockIdx.y * 32;
+    const bf16* mine = reinterpret_cast<const bf16*>(params.p[rank]) + offset;
+    if (transposed) {
+        for (int j = threadIdx.y; j < 32; j += blockDim.y) {
+            const int oc = bx + j, orow = by + threadIdx.x;
+            tile[j][threadIdx.x] = (oc < C && orow < R) ? __half2float(o[(size_t)oc * R + orow]) : 0.f;
+        }
+        __syncthreads();
+    }
+    for (int j = threadIdx.y; j < 32; j += blockDim.y) {
+        const int r = by + j, c = bx + threadIdx.x;
+        if (r < R && c < C) {
+            const size_t idx = (size_t)r * C + c;
+            const float ov = transposed ? tile[threadIdx.x][j] : __half2float(o[idx]);
+            const bf16 v = __float2bfloat16(__bfloat162float(mine[idx]) * decay - alpha * ov);
+            for (int q = 0; q < world; ++q) (reinterpret_cast<bf16*>(params.p[q]) + offset)[idx] = v;
+        }
+    }
+}
+KB_API int kb_muon_apply_bcast(void* const* peer_params, int world, int rank, long long offset, const void* orth,
+                               int R, int C, float lr, float wd, float scale, int transposed, cudaStream_t st) {
+    if (world < 1 || world > 8) return 5;
+    PeerPtrs pp;
+    for (int i = 0; i < 8; ++i) pp.p[i] = i < world ? peer_params[i] : nullptr;
+    dim3 grid((C + 31) / 32, (R + 31) / 32), block(32, 8);
+    muon_apply_bcast_kernel<<<grid, block, 0, st>>>(pp, world, rank, offset, (const __half*)orth, R, C,
+                                                    wd > 0 ? 1.f - lr * wd : 1.f, lr * scale, transposed);
+    return 0;
+}
