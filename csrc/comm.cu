@@ -155,8 +155,7 @@ __global__ void scalar_allreduce_kernel(PeerPtrs vals, PeerPtrs flags, int world
     __syncthreads();
     const int par = epoch & 1;
     if (threadIdx.x < world) {
-        const float v = in ? in[0] : 0.f;
-        reinterpret_cast<float*>(vals.p[threadIdx.x])[par * 8 + rank] = v;
+        if (in) reinterpret_cast<float*>(vals.p[threadIdx.x])[par * 8 + rank] = in[0];
         __threadfence_system();
         st_release_sys(reinterpret_cast<int*>(flags.p[threadIdx.x]) + slot * 8 + rank, epoch);
         if (!wait_flag(reinterpret_cast<const int*>(flags.p[rank]) + slot * 8 + threadIdx.x, epoch, limit_ns)) {

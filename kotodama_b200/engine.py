@@ -488,8 +488,7 @@ class TrainEngine:
                     x = ops.ns_iteration(x, a, b, c)
                 x = comm.muon_scatter(s, x, transposed)
                 scale = max(1.0, (rows / cols) ** 0.5)
-                ops.muon_apply(ar.view(s.name), x, g["lr"], g["weight_decay"], scale, transposed)
-                comm.publish_param(s)
+                comm.muon_apply(ops, s, x, g["lr"], g["weight_decay"], scale, transposed)
         ga = self.adamw_opt.param_groups[0]
         lo, hi = self.adamw_lo, ar.total
         ops.adamw_step(ar.params[lo:hi], ar.grads[lo:hi], self.exp_avg, self.exp_avg_sq, self.opt_step,

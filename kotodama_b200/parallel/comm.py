@@ -74,8 +74,9 @@ class LocalComm:
     def muon_scatter(self, slot, x, transposed: bool):
         return x
 
-    def publish_param(self, slot) -> None:
-        pass
+    def muon_apply(self, ops, slot, orth, lr: float, wd: float, scale: float, transposed: bool) -> None:
+        """Write the Muon update of one matrix (strategies that own the write may also publish it)."""
+        ops.muon_apply(self.engine.arena.view(slot.name), orth, lr, wd, scale, transposed)
 
     def finish_param_publish(self) -> None:
         pass
@@ -137,10 +138,6 @@ class LibraryComm(LocalComm):
         for w in self._pending:
             w.wait()
         self._pending.clear()
-
-    def publish_param(self, slot) -> None:
-        # under distributed Muon non-owners receive the owner's new matrix
-        pass
 
     def finish_param_publish(self) -> None:
         if not self.distributed_muon:

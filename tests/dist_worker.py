@@ -1,0 +1,68 @@
+"""Worker launched by the distributed tests (one process per rank)."""
+import argparse
+import json
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from kotodama_b200.config import MODEL_PRESETS, ModelConfig  # noqa: E402
+from kotodama_b200.engine import TrainEngine  # noqa: E402
+from kotodama_b200.models.llama import KotodamaModel  # noqa: E402
+from kotodama_b200.parallel.comm import LibraryComm  # noqa: E402
+
+
+def build(cfg, device, dtype, comm, seed=0):
+    torch.manual_seed(seed)
+    model = KotodamaModel(cfg)
+    return TrainEngine(model, device=device, dtype=dtype, comm=comm, muon_lr=0.02, adamw_lr=1e-3)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--mode", required=True)
+    ap.add_argument("--out", required=True)
+    ap.add_argument("--steps", type=int, default=3)
+    a = ap.parse_args()
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    cuda = a.mode.startswith("gpu")
+    if cuda:
+        torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
+    dist.init_process_group("nccl" if cuda else "gloo")
+    device = torch.device("cuda", torch.cuda.current_device()) if cuda else torch.device("cpu")
+    dtype = torch.bfloat16 if cuda else torch.float32
+    preset = "smoke" if cuda else "tiny"
+    cfg = ModelConfig(**MODEL_PRESETS[preset], attn_res=True, attn_res_n_blocks=2)
+    seq = 256
+    g = torch.Generator().manual_seed(100 + rank)
+    batch = torch.randint(0, cfg.vocab_size, (2, seq), generator=g)
+    result = {"rank": rank}
+    if a.mode in ("cpu_ddp", "gpu_library", "gpu_native"):
+        if a.mode == "gpu_native":
+            from kotodama_b200.parallel.native import NativeComm
+            comm = NativeComm(distributed_muon=True)
+        else:
+            comm = LibraryComm(distributed_muon=True)
+        eng = build(cfg, device, dtype, comm)
+        losses = [float(eng.train_step([batch])["loss"]) for _ in range(a.steps)]
+        eng.check()
+        p = eng.arena.params.float()
+        gathered = [torch.empty_like(p) for _ in range(world)]
+        dist.all_gather(gathered, p)
+        result.update(losses=losses, ranks_match=all(torch.equal(gathered[0], t) for t in gathered),
+                      checksum=float(p.double().abs().sum()))
+        if a.mode != "cpu_ddp":
+            torch.save(p.cpu(), f"{a.out}.params.{a.mode}.{rank}.pt")
+        sd = eng.muon_state_dict()
+        result["momentum_entries"] = len(sd["state"])
+    with open(f"{a.out}.{a.mode}.{rank}.json", "w") as fh:
+        json.dump(result, fh)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,26 @@
+"""Two GPU ranks: in-kernel NVLink collectives against the NCCL strategy."""
+import os
+
+import pytest
+import torch
+
+from test_distributed_cpu import _launch
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+
+
+def test_native_comm_matches_library_comm(tmp_path):
+    out = str(tmp_path / "r")
+    env_backup = dict(os.environ)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    try:
+        lib = _launch("gpu_library", out, steps=3)
+        nat = _launch("gpu_native", out, steps=3)
+    finally:
+        os.environ.clear(); os.environ.update(env_backup)
+    assert all(r["ranks_match"] for r in lib) and all(r["ranks_match"] for r in nat)
+    for a, b in zip(lib[0]["losses"], nat[0]["losses"]):
+        assert abs(a - b) < 5e-2, (lib[0]["losses"], nat[0]["losses"])
+    pl = torch.load(f"{out}.params.gpu_library.0.pt")
+    pn = torch.load(f"{out}.params.gpu_native.0.pt")
+    assert float((pl - pn).norm() / pl.norm()) < 2e-2
