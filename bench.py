@@ -143,11 +143,13 @@ def run_native(args, rank, world, local):
         from kotodama_b200.utils.optimer import TimedOps
         plain = eng.ops
         eng.ops = TimedOps(plain)
+        plain_comm = eng.comm
+        eng.comm = TimedOps(plain_comm, prefix="comm.")
         eng.train_step([dev_batches[0]])
         if rank == 0:
             with open(args.op_times, "w") as fh:
-                fh.write(eng.ops.table(1) + "\n")
-        eng.ops = plain
+                fh.write(eng.ops.table(1) + "\n\n" + eng.comm.table(1) + "\n")
+        eng.ops, eng.comm = plain, plain_comm
     sampler = ClockSampler(local)
     # ---- pass 1: device-timed
     sync_all(world)

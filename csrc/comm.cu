@@ -68,25 +68,49 @@ KB_API int kb_flag_wait(const int* flags, int world, int slot, int epoch, double
 }
 
 // out[i] = scale * sum_r peer[r][offset + i]  for i in [0, n); out is this rank's own buffer range.
-__global__ void reduce_to_owner_kernel(PeerPtrs bufs, int world, long long offset, long long n, float scale,
-                                       bf16* __restrict__ out) {
-    const long long nvec = n >> 3;
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec;
-         i += (long long)gridDim.x * blockDim.x) {
+template <int U>
+__device__ __forceinline__ void reduce_vecs(const PeerPtrs& bufs, int world, long long offset, long long i0,
+                                            long long stride, long long nvec, float scale, bf16* __restrict__ out) {
+    // U independent 16-byte loads per rank are issued before any is consumed: NVLink reads are
+    // latency-bound, so bytes in flight per thread set the bandwidth.
+    uint4 raw[U][8];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+        const long long i = i0 + u * stride;
+#pragma unroll
+        for (int r = 0; r < 8; ++r)
+            if (r < world && i < nvec)
+                raw[u][r] = __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(bufs.p[r]) + offset) + i);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+        const long long i = i0 + u * stride;
+        if (i >= nvec) continue;
         float acc[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-        for (int r = 0; r < world; ++r) {
-            const uint4 raw = __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(bufs.p[r]) + offset) + i);
-            float t[8];
-            unpack8(*reinterpret_cast<const bf16x8*>(&raw), t);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) acc[j] += t[j];
+        for (int r = 0; r < 8; ++r) {
+            if (r < world) {
+                float t[8];
+                unpack8(*reinterpret_cast<const bf16x8*>(&raw[u][r]), t);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[j] += t[j];
+            }
         }
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc[j] *= scale;
         st8(out + i * 8, pack8(acc));
     }
+}
+
+__global__ void __launch_bounds__(256)
+reduce_to_owner_kernel(PeerPtrs bufs, int world, long long offset, long long n, float scale,
+                       bf16* __restrict__ out) {
+    const long long nvec = n >> 3;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += 2 * stride)
+        reduce_vecs<2>(bufs, world, offset, i, stride, nvec, scale, out);
     // tail (n not a multiple of 8)
     for (long long i = (nvec << 3) + (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
          i += (long long)gridDim.x * blockDim.x) {
@@ -190,26 +214,52 @@ KB_API int kb_scalar_allreduce(void* const* peer_vals, void* const* peer_flags, 
 // Owner's Muon parameter write, broadcast: every rank's arena gets p*decay - alpha*orth.
 // params.p[r] is rank r's arena base; the matrix sits at `offset`, shape [R,C]; orth is fp16
 // [R,C], or [C,R] when `transposed`.
-__global__ void muon_apply_bcast_kernel(PeerPtrs params, int world, int rank, long long offset,
-                                        const __half* __restrict__ o, int R, int C, float decay, float alpha,
-                                        int transposed) {
-    __shared__ float tile[32][33];
-    const int bx = blockIdx.x * 32, by = blockIdx.y * 32;
+// 64x64 tiles, block (8, 32): thread (x, y) owns 8 consecutive columns of rows y and y+32.
+__global__ void __launch_bounds__(256)
+muon_apply_bcast_kernel(PeerPtrs params, int world, int rank, long long offset, const __half* __restrict__ o,
+                        int R, int C, float decay, float alpha, int transposed) {
+    __shared__ float tile[64][65];
+    const int bx = blockIdx.x * 64, by = blockIdx.y * 64;
     const bf16* mine = reinterpret_cast<const bf16*>(params.p[rank]) + offset;
     if (transposed) {
-        for (int j = threadIdx.y; j < 32; j += blockDim.y) {
-            const int oc = bx + j, orow = by + threadIdx.x;
-            tile[j][threadIdx.x] = (oc < C && orow < R) ? __half2float(o[(size_t)oc * R + orow]) : 0.f;
+        // o is [C,R]: tile[j][i] = o[bx + j][by + i]
+        for (int j = threadIdx.y; j < 64; j += 32) {
+            const int oc = bx + j;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const int orow = by + threadIdx.x * 8 + e;
+                tile[j][threadIdx.x * 8 + e] = (oc < C && orow < R) ? __half2float(o[(size_t)oc * R + orow]) : 0.f;
+            }
         }
         __syncthreads();
     }
-    for (int j = threadIdx.y; j < 32; j += blockDim.y) {
-        const int r = by + j, c = bx + threadIdx.x;
-        if (r < R && c < C) {
-            const size_t idx = (size_t)r * C + c;
-            const float ov = transposed ? tile[threadIdx.x][j] : __half2float(o[idx]);
-            const bf16 v = __float2bfloat16(__bfloat162float(mine[idx]) * decay - alpha * ov);
-            for (int q = 0; q < world; ++q) (reinterpret_cast<bf16*>(params.p[q]) + offset)[idx] = v;
+    const bool vec = (C & 7) == 0 && (offset & 7) == 0;
+    for (int j = threadIdx.y; j < 64; j += 32) {
+        const int r = by + j, c0 = bx + threadIdx.x * 8;
+        if (r >= R || c0 >= C) continue;
+        const size_t idx = (size_t)r * C + c0;
+        if (vec && c0 + 8 <= C) {
+            float p[8], ov[8];
+            unpack8(ld8(mine + idx), p);
+            if (transposed) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) ov[e] = tile[threadIdx.x * 8 + e][j];
+            } else {
+                const uint4 raw = *reinterpret_cast<const uint4*>(o + idx);
+                const __half* h = reinterpret_cast<const __half*>(&raw);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) ov[e] = __half2float(h[e]);
+            }
+#pragma unroll
+            for (int e = 0; e < 8; ++e) p[e] = p[e] * decay - alpha * ov[e];
+            const bf16x8 v = pack8(p);
+            for (int q = 0; q < world; ++q) st8(reinterpret_cast<bf16*>(params.p[q]) + offset + idx, v);
+        } else {
+            for (int e = 0; e < 8 && c0 + e < C; ++e) {
+                const float ov = transposed ? tile[threadIdx.x * 8 + e][j] : __half2float(o[idx + e]);
+                const bf16 v = __float2bfloat16(__bfloat162float(mine[idx + e]) * decay - alpha * ov);
+                for (int q = 0; q < world; ++q) (reinterpret_cast<bf16*>(params.p[q]) + offset)[idx + e] = v;
+            }
         }
     }
 }
@@ -218,7 +268,7 @@ KB_API int kb_muon_apply_bcast(void* const* peer_params, int world, int rank, lo
     if (world < 1 || world > 8) return 5;
     PeerPtrs pp;
     for (int i = 0; i < 8; ++i) pp.p[i] = i < world ? peer_params[i] : nullptr;
-    dim3 grid((C + 31) / 32, (R + 31) / 32), block(32, 8);
+    dim3 grid((C + 63) / 64, (R + 63) / 64), block(8, 32);
     muon_apply_bcast_kernel<<<grid, block, 0, st>>>(pp, world, rank, offset, (const __half*)orth, R, C,
                                                     wd > 0 ? 1.f - lr * wd : 1.f, lr * scale, transposed);
     return 0;

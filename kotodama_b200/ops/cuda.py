@@ -50,7 +50,7 @@ class CudaOps(TorchOps):
         self.launches = 0              # launches of kernels from this library
         self._status: dict[int, torch.Tensor] = {}
         self.gemm_max_ctas = 0
-        for name in ("kb_route_bwd_grid", "kb_qknorm_grid_warps"):
+        for name in ("kb_route_bwd_grid", "kb_qknorm_grid_warps", "kb_route_pipe_grid"):
             getattr(self.lib, name).restype = _I
 
     # ------------------------------------------------------------------ utils
@@ -132,9 +132,14 @@ class CudaOps(TorchOps):
         logit = torch.empty(N, S, device=dev, dtype=torch.float32) if routing else None
         rstd = torch.empty(N, device=dev, dtype=torch.float32)
         arr = (_VP * S)(*[s.data_ptr() for s in srcs])
-        rc = self.lib.kb_route_norm_fwd(arr, _I(S), _p(q), _p(rn_w), _p(n_w), _p(xn), _p(alpha), _p(r), _p(logit),
-                                        _p(rstd), _I(N), _I(D), _F(eps), _st())
-        self._rc(rc, "kb_route_norm_fwd")
+        if self.lib.kb_route_pipe_grid(_I(N), _I(S), _I(D), _I(0)) > 0:
+            rc = self.lib.kb_route_pipe_fwd(arr, _I(S), _p(q), _p(rn_w), _p(n_w), _p(xn), _p(alpha), _p(r), _p(logit),
+                                            _p(rstd), _I(N), _I(D), _F(eps), _p(self.status(dev)), _st())
+            self._rc(rc, "kb_route_pipe_fwd")
+        else:       # rows too large for the shared-memory ring: register-resident kernel
+            rc = self.lib.kb_route_norm_fwd(arr, _I(S), _p(q), _p(rn_w), _p(n_w), _p(xn), _p(alpha), _p(r), _p(logit),
+                                            _p(rstd), _I(N), _I(D), _F(eps), _st())
+            self._rc(rc, "kb_route_norm_fwd")
         return xn, (alpha, r, logit, rstd)
 
     def route_norm_bwd(self, dxn, srcs, q, rn_w, n_w, eps, stats, dsrcs, acc):
@@ -142,17 +147,24 @@ class CudaOps(TorchOps):
         S = len(srcs)
         N, D = srcs[0].shape
         dev = dxn.device
-        grid = self.lib.kb_route_bwd_grid(_I(N))
+        pipe_grid = self.lib.kb_route_pipe_grid(_I(N), _I(S), _I(D), _I(1))
+        grid = pipe_grid if pipe_grid > 0 else self.lib.kb_route_bwd_grid(_I(N))
         routing = q is not None
         dnw_part = torch.empty(grid, D, device=dev, dtype=torch.float32)
         dw_part = torch.empty(grid, D, device=dev, dtype=torch.float32) if routing else None
         sa = (_VP * S)(*[s.data_ptr() for s in srcs])
         da = (_VP * S)(*[d.data_ptr() for d in dsrcs])
         mask = sum(1 << i for i, a in enumerate(acc) if a)
-        rc = self.lib.kb_route_norm_bwd(sa, da, ctypes.c_uint(mask), _I(S), _p(dxn), _p(q), _p(rn_w), _p(n_w),
-                                        _p(alpha), _p(r), _p(logit), _p(rstd), _p(dw_part), _p(dnw_part), _I(N),
-                                        _I(D), _st())
-        self._rc(rc, "kb_route_norm_bwd")
+        if pipe_grid > 0:
+            rc = self.lib.kb_route_pipe_bwd(sa, da, ctypes.c_uint(mask), _I(S), _p(dxn), _p(q), _p(rn_w), _p(n_w),
+                                            _p(alpha), _p(r), _p(logit), _p(rstd), _p(dw_part), _p(dnw_part), _I(N),
+                                            _I(D), _p(self.status(dev)), _st())
+            self._rc(rc, "kb_route_pipe_bwd")
+        else:
+            rc = self.lib.kb_route_norm_bwd(sa, da, ctypes.c_uint(mask), _I(S), _p(dxn), _p(q), _p(rn_w), _p(n_w),
+                                            _p(alpha), _p(r), _p(logit), _p(rstd), _p(dw_part), _p(dnw_part), _I(N),
+                                            _I(D), _st())
+            self._rc(rc, "kb_route_norm_bwd")
         dn_w = self._colsum(dnw_part)
         if not routing:
             return None, None, dn_w

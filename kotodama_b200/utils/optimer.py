@@ -10,14 +10,15 @@ import torch
 
 
 class TimedOps:
-    def __init__(self, inner: Any) -> None:
+    def __init__(self, inner: Any, prefix: str = "") -> None:
         self._inner = inner
+        self._prefix = prefix
         self._events: list[tuple[str, torch.cuda.Event, torch.cuda.Event]] = []
         self.enabled = True
 
     def __getattr__(self, name: str) -> Any:
         attr = getattr(self._inner, name)
-        if not callable(attr) or name.startswith("_") or name in ("check_status", "status"):
+        if not callable(attr) or name.startswith("_") or name in ("check_status", "status", "allocator", "attach"):
             return attr
 
         def wrapped(*a: Any, **k: Any) -> Any:
@@ -27,7 +28,7 @@ class TimedOps:
             e0.record()
             out = attr(*a, **k)
             e1.record()
-            label = name
+            label = self._prefix + name
             if name.startswith("gemm") and a:
                 label = f"{name}[{'x'.join(map(str, a[0].shape))}|{'x'.join(map(str, a[1].shape))}]"
             self._events.append((label, e0, e1))
