@@ -112,6 +112,9 @@ class ParamArena:
                 mod, pn = owners[s.name]
                 newp = nn.Parameter(view, requires_grad=True)
                 newp.grad = self.grads[s.offset:s.offset + s.numel].view(s.shape)
+                for k, v in vars(s.param).items():          # keep tags such as the tensor-parallel shard info
+                    if k.startswith("_tp_"):
+                        setattr(newp, k, v)
                 mod._parameters[pn] = newp
                 s.param = newp
         model.materialize_buffers(device)
@@ -209,6 +212,8 @@ class TrainEngine:
         self.cfg: ModelConfig = model.config
         self.comm = comm or LocalComm()
         self.ops = ops or get_ops(self.device)
+        if hasattr(self.comm, "prepare_model"):
+            self.comm.prepare_model(model)          # tensor parallelism shards the projections first
         self.arena = ParamArena(model, self.device, dtype, allocator=self.comm.allocator(self.device, dtype))
         self.comm.attach(self)
         self.gradient_clip = gradient_clip
@@ -306,10 +311,11 @@ class TrainEngine:
         if self.comm.tp_size > 1:
             H, KV, F_ = H // self.comm.tp_size, KV // self.comm.tp_size, F_ // self.comm.tp_size
         eps = cfg.norm_eps
-        ids = input_ids.reshape(-1)
         labels = torch.roll(input_ids, -1, dims=1)
         labels[:, -1] = -100
-        labels = labels.reshape(-1)
+        ids = self.comm.shard_tokens(input_ids.reshape(-1))          # sequence parallelism: this rank's tokens
+        labels = self.comm.shard_tokens(labels.reshape(-1))
+        n_valid = self.comm.loss_reduce((labels >= 0).sum().float().reshape(1)).clamp(min=1)
         wemb = self._p("embed_tokens.weight")
         cos, sin = self.model.rope_cos, self.model.rope_sin
         attn_res = cfg.attn_res
@@ -361,7 +367,10 @@ class TrainEngine:
         g_wl = self._g("embed_tokens.weight") if self.model.lm_head is None else self._g("lm_head.weight")
         ce, zl, dxf = ops.linear_ce(xf, wl, labels, cfg.z_loss_weight, loss_scale,
                                     g_wl if need_grad else None, dw_accumulate=not first_micro,
-                                    chunk=self.ce_chunk, need_grad=need_grad)
+                                    chunk=self.ce_chunk, need_grad=need_grad, count=n_valid)
+        if self.comm.tp_size > 1:
+            both = self.comm.loss_reduce(torch.stack([ce.reshape(()), zl.reshape(())]).float())
+            ce, zl = both[0], both[1]
         loss = ce + zl
         if not need_grad:
             return loss, zl
@@ -395,9 +404,10 @@ class TrainEngine:
             lw, r, p = self.layer_w[i], recs[i], f"layers.{i}."
             # ---- MLP sub-layer
             dP = grads[id(r.part_after_mlp)]
-            dact = self.comm.row_linear_bwd_input(ops, dP, lw["wd"])
             dPg = self.comm.sp_gather(dP)
+            dact = ops.gemm_nn(dPg, lw["wd"])
             ops.gemm_tn(dPg, r.act, out=lw["g_wd"], accumulate=not first_micro)
+            del dPg
             dgu = ops.swiglu_bwd(r.gu, dact)
             del dact
             ops.gemm_tn(dgu, self.comm.sp_gather(r.xn2), out=lw["g_wgu"], accumulate=not first_micro)
@@ -415,8 +425,10 @@ class TrainEngine:
             # ---- attention sub-layer
             dP = grads[id(r.part_after_attn)]
             Nq = r.qkv.shape[0]
-            dattn = self.comm.row_linear_bwd_input(ops, dP, lw["wo"])
-            ops.gemm_tn(self.comm.sp_gather(dP), r.attn_o.view(Nq, H * hd), out=lw["g_wo"], accumulate=not first_micro)
+            dPg = self.comm.sp_gather(dP)
+            dattn = ops.gemm_nn(dPg, lw["wo"])
+            ops.gemm_tn(dPg, r.attn_o.view(Nq, H * hd), out=lw["g_wo"], accumulate=not first_micro)
+            del dPg
             dqkv = torch.empty_like(r.qkv)
             dqk = torch.empty_like(r.qk)
             q4 = r.qk[:, : H * hd].view(Nq // T, T, H, hd)
@@ -477,16 +489,19 @@ class TrainEngine:
                 grad = ar.view(s.name, grads=True)
                 x, sq = ops.muon_momentum(grad, self.momentum[s.name], g["momentum"], g["nesterov"], coef)
                 rows, cols = comm.full_shape(s)
-                transposed = x.shape[0] > x.shape[1]
+                transposed = rows > cols
                 x = comm.muon_gather(s, x)
-                if transposed:
-                    x = ops.transpose(x)
-                if comm.tp_size > 1:
-                    sq = ops.sumsq(x)
-                x = ops.ns_normalize(x, sq)
-                for (a, b, c) in coeffs:
-                    x = ops.ns_iteration(x, a, b, c)
+                if comm.runs_ns(s):                       # under TP one rank orthogonalises the gathered matrix
+                    if comm.tp_size > 1:
+                        sq = ops.sumsq(x)
+                    if transposed:
+                        x = ops.transpose(x)
+                    x = ops.ns_normalize(x, sq)
+                    for (a, b, c) in coeffs:
+                        x = ops.ns_iteration(x, a, b, c)
                 x = comm.muon_scatter(s, x, transposed)
+                if comm.tp_size > 1:
+                    transposed = False                    # shards come back in the parameter's orientation
                 scale = max(1.0, (rows / cols) ** 0.5)
                 comm.muon_apply(ops, s, x, g["lr"], g["weight_decay"], scale, transposed)
         ga = self.adamw_opt.param_groups[0]

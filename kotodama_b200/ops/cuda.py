@@ -222,13 +222,14 @@ class CudaOps(TorchOps):
         return out
 
     # ------------------------------------------------------------------ loss head
-    def linear_ce(self, h, w, labels, z_weight, grad_scale, dw, dw_accumulate, chunk=4096, need_grad=True):
+    def linear_ce(self, h, w, labels, z_weight, grad_scale, dw, dw_accumulate, chunk=4096, need_grad=True,
+                  count=None):
         N, D = h.shape
         V = w.shape[0]
         dev = h.device
         row_ce = torch.empty(N, device=dev, dtype=torch.float32)
         row_z = torch.empty(N, device=dev, dtype=torch.float32)
-        nv = (labels >= 0).sum().clamp(min=1).float()
+        nv = (labels >= 0).sum().clamp(min=1).float() if count is None else count.reshape(()).float()
         inv = (1.0 / nv).reshape(1)
         dh = torch.empty_like(h) if need_grad else None
         first = not dw_accumulate

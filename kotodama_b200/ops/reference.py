@@ -238,7 +238,7 @@ class TorchOps:
     # ------------------------------------------------- LM head + CE + z-loss
     def linear_ce(self, h: torch.Tensor, w: torch.Tensor, labels: torch.Tensor, z_weight: float,
                   grad_scale: float, dw: Optional[torch.Tensor], dw_accumulate: bool, chunk: int = 4096,
-                  need_grad: bool = True):
+                  need_grad: bool = True, count: Optional[torch.Tensor] = None):
         """Chunked LM-head GEMM + cross-entropy + z-loss without materialising all logits.
 
         ``labels[N]`` uses -100 for ignored rows.  Losses are means over the valid rows:
@@ -248,6 +248,8 @@ class TorchOps:
         n = h.shape[0]
         valid = labels >= 0
         nv = valid.sum().clamp(min=1).to(torch.float64 if h.dtype == torch.float64 else torch.float32)
+        if count is not None:          # the batch is split over ranks: normalise by the global count
+            nv = count.reshape(()).to(nv.dtype)
         acc_dt = torch.float64 if h.dtype == torch.float64 else torch.float32
         ce_sum = torch.zeros((), dtype=acc_dt, device=h.device)
         z_sum = torch.zeros((), dtype=acc_dt, device=h.device)

@@ -42,6 +42,16 @@ class LocalComm:
     def sp_gather(self, x: torch.Tensor) -> torch.Tensor:
         return x
 
+    def shard_tokens(self, x: torch.Tensor) -> torch.Tensor:
+        return x
+
+    def loss_reduce(self, t: torch.Tensor) -> torch.Tensor:
+        """Sum of per-rank loss terms / token counts over the ranks that split one batch."""
+        return t
+
+    def runs_ns(self, slot) -> bool:
+        return True
+
     def row_linear(self, ops, x, w, residual=None):
         return ops.gemm_nt(x, w, residual=residual)
 

@@ -57,9 +57,11 @@ def cleanup_distributed() -> None:
 
 
 def setup_logging(rank: int) -> None:
-    logging.basicConfig(level=logging.INFO if rank == 0 else logging.WARNING,
-                        format=f"[rank {rank}] %(asctime)s %(levelname)s %(name)s: %(message)s", datefmt="%H:%M:%S",
-                        force=True)
+    """INFO on rank 0, WARNING elsewhere (``train.py:180-187``)."""
+    level = logging.INFO if rank == 0 else logging.WARNING
+    logging.basicConfig(level=level, format=f"[rank {rank}] %(asctime)s %(levelname)s %(name)s: %(message)s",
+                        datefmt="%H:%M:%S")
+    logging.getLogger("kotodama_b200").setLevel(level)
 
 
 def per_layer_grad_norms(model: torch.nn.Module) -> dict[str, float]:

@@ -58,6 +58,40 @@ def main():
             torch.save(p.cpu(), f"{a.out}.params.{a.mode}.{rank}.pt")
         sd = eng.muon_state_dict()
         result["momentum_entries"] = len(sd["state"])
+    if a.mode in ("cpu_tp_sp", "cpu_tp"):
+        from kotodama_b200.parallel.tp import TensorParallelComm, create_process_groups, gather_full_state_dict
+        tp_group, _ = create_process_groups(world, world)
+        comm = TensorParallelComm(tp_group, None, sequence_parallel=(a.mode == "cpu_tp_sp"))
+        cfg = ModelConfig(**MODEL_PRESETS["smoke"], attn_res=True, attn_res_n_blocks=2)
+        shared = torch.randint(0, cfg.vocab_size, (2, 64), generator=torch.Generator().manual_seed(7))
+        eng = build(cfg, device, dtype, comm)
+        losses = [float(eng.train_step([shared])["loss"]) for _ in range(a.steps)]
+        full = gather_full_state_dict(eng.model, tp_group)
+        result.update(losses=losses, checksum=float(sum(v.double().abs().sum() for v in full.values())),
+                      q_shape=list(full["layers.0.attn.q_proj.weight"].shape),
+                      local_q_shape=list(eng.model.layers[0].attn.q_proj.weight.shape),
+                      momentum_shape=list(eng.muon_state_dict()["state"][0]["momentum_buffer"].shape))
+    if a.mode == "cpu_tp_autograd":
+        from kotodama_b200.optim.muon import build_hybrid_optimizer
+        from kotodama_b200.parallel.tp import (apply_tensor_parallelism, create_process_groups, gather_full_state_dict,
+                                               sync_tp_replicated_grads, tp_clip_grad_norm)
+        tp_group, _ = create_process_groups(world, world)
+        cfg = ModelConfig(**MODEL_PRESETS["smoke"], attn_res=True, attn_res_n_blocks=2)
+        torch.manual_seed(0)
+        model = KotodamaModel(cfg)
+        apply_tensor_parallelism(model, tp_group)
+        muon, adamw = build_hybrid_optimizer(model, muon_lr=0.02, adamw_lr=1e-3)
+        shared = torch.randint(0, cfg.vocab_size, (2, 64), generator=torch.Generator().manual_seed(7))
+        losses = []
+        for _ in range(a.steps):
+            out = model(shared, labels=shared)
+            out["loss"].backward()
+            sync_tp_replicated_grads(model, tp_group)
+            tp_clip_grad_norm(model, 1.0, tp_group)
+            muon.step(); adamw.step(); muon.zero_grad(); adamw.zero_grad()
+            losses.append(float(out["loss"]))
+        full = gather_full_state_dict(model, tp_group)
+        result.update(losses=losses, checksum=float(sum(v.double().abs().sum() for v in full.values())))
     with open(f"{a.out}.{a.mode}.{rank}.json", "w") as fh:
         json.dump(result, fh)
     dist.barrier()

@@ -43,3 +43,36 @@ def test_two_ranks_equal_one_rank_with_accumulation(tmp_path):
         eng.train_step(batches)
     single = float(eng.arena.params.double().abs().sum())
     assert abs(single - res[0]["checksum"]) / single < 2e-4, (single, res[0]["checksum"])
+
+
+def _single_process_reference(steps):
+    from kotodama_b200.config import MODEL_PRESETS, ModelConfig
+    from kotodama_b200.engine import TrainEngine
+    from kotodama_b200.models.llama import KotodamaModel
+    cfg = ModelConfig(**MODEL_PRESETS["smoke"], attn_res=True, attn_res_n_blocks=2)
+    torch.manual_seed(0)
+    model = KotodamaModel(cfg)
+    eng = TrainEngine(model, device="cpu", dtype=torch.float32, muon_lr=0.02, adamw_lr=1e-3)
+    shared = torch.randint(0, cfg.vocab_size, (2, 64), generator=torch.Generator().manual_seed(7))
+    losses = [float(eng.train_step([shared])["loss"]) for _ in range(steps)]
+    return losses, float(sum(v.double().abs().sum() for v in model.state_dict().values()))
+
+
+def test_tensor_parallel_with_sequence_parallel_matches_single_process(tmp_path):
+    res = _launch("cpu_tp_sp", str(tmp_path / "r"), steps=3)
+    losses, checksum = _single_process_reference(3)
+    assert res[0]["q_shape"] == [256, 256] and res[0]["local_q_shape"] == [128, 256]
+    assert res[0]["momentum_shape"] == [256, 256]
+    for a, b in zip(res[0]["losses"], losses):
+        assert abs(a - b) < 2e-3, (res[0]["losses"], losses)
+    assert abs(res[0]["checksum"] - checksum) / checksum < 5e-4
+    assert res[0]["checksum"] == res[1]["checksum"]
+
+
+def test_tensor_parallel_allreduce_mode_and_autograd_api(tmp_path):
+    losses, checksum = _single_process_reference(2)
+    for mode in ("cpu_tp", "cpu_tp_autograd"):
+        res = _launch(mode, str(tmp_path / mode), steps=2)
+        for a, b in zip(res[0]["losses"], losses):
+            assert abs(a - b) < 2e-3, (mode, res[0]["losses"], losses)
+        assert abs(res[0]["checksum"] - checksum) / checksum < 5e-4, mode
