@@ -1,0 +1,78 @@
+#!/usr/bin/env python
+"""Serving benchmark: N concurrent requests with prompt lengths uniform in [128, 2048]
+(uniform-random token ids from a seed, random-init weights), greedy decoding of 256 new tokens
+each, paged KV cache with 16-token pages.  Reports prefill tok/s, decode tok/s and the p50
+per-token (decode step) latency, all timed with CUDA events around the engine's steps.
+
+    python benchmarks/serve_bench.py --model 3b --requests 64 --new-tokens 256
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+from kotodama_b200.config import MODEL_PRESETS, ModelConfig  # noqa: E402
+from kotodama_b200.models.llama import KotodamaModel  # noqa: E402
+from kotodama_b200.serve.engine import SamplingParams, ServingEngine  # noqa: E402
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--model", default="3b")
+    ap.add_argument("--requests", type=int, default=64)
+    ap.add_argument("--new-tokens", type=int, default=256)
+    ap.add_argument("--min-prompt", type=int, default=128)
+    ap.add_argument("--max-prompt", type=int, default=2048)
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--device", default="cuda")
+    a = ap.parse_args()
+    cuda = a.device == "cuda"
+    cfg = ModelConfig(**MODEL_PRESETS[a.model], attn_res=True, attn_res_n_blocks=7 if a.model != "tiny" else 2)
+    with torch.device("meta"):
+        model = KotodamaModel(cfg)
+    eng = ServingEngine(model, device=a.device, dtype=torch.bfloat16 if cuda else torch.float32,
+                        max_batch=a.requests, max_ctx=a.max_prompt + a.new_tokens + 16)
+    eng.arena.init_weights(cfg.num_layers, a.seed)
+    g = torch.Generator().manual_seed(a.seed)
+    lens = torch.randint(a.min_prompt, a.max_prompt + 1, (a.requests,), generator=g).tolist()
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in lens]
+    # warm-up on a short request (kernel attribute setup, allocator)
+    eng.generate([prompts[0][:64]], SamplingParams(max_new_tokens=4, temperature=0.0))
+    sync = torch.cuda.synchronize if cuda else (lambda: None)
+    import time
+    reqs = [eng.add_request(p, SamplingParams(max_new_tokens=a.new_tokens, temperature=0.0)) for p in prompts]
+    sync()
+    t0 = time.perf_counter()
+    eng.step()                       # admits and prefills every request, then one decode step
+    sync()
+    t_first = time.perf_counter() - t0
+    step_ms = []
+    while eng.has_work():
+        sync()
+        t = time.perf_counter()
+        eng.step()
+        sync()
+        step_ms.append((time.perf_counter() - t) * 1e3)
+    total_decode_s = sum(step_ms) / 1e3
+    decode_tokens = sum(len(r.generated) for r in reqs) - 2 * len(reqs)   # minus prefill token and first step
+    out = {"model": a.model, "requests": a.requests, "prompt_tokens": sum(lens), "new_tokens": a.new_tokens,
+           "prefill_plus_first_step_s": round(t_first, 3),
+           "prefill_tok_s": round(sum(lens) / max(eng.stats["prefill_s"], 1e-9), 1),
+           "decode_tok_s": round(decode_tokens / max(total_decode_s, 1e-9), 1),
+           "p50_token_latency_ms": round(statistics.median(step_ms), 3) if step_ms else None,
+           "p95_token_latency_ms": round(sorted(step_ms)[int(0.95 * (len(step_ms) - 1))], 3) if step_ms else None,
+           "kernel_launches": getattr(eng.ops, "launches", None),
+           "attention_library_calls": getattr(eng.ops, "attention_library_calls", 0)}
+    if hasattr(eng.ops, "check_status"):
+        eng.ops.check_status()
+    print(json.dumps(out))
+
+
+if __name__ == "__main__":
+    main()

@@ -401,7 +401,7 @@ __global__ void qknorm_rope_fwd_kernel(const bf16* __restrict__ qkv, const bf16*
                                        const bf16* __restrict__ kw, const float* __restrict__ cosT,
                                        const float* __restrict__ sinT, bf16* __restrict__ out,
                                        float* __restrict__ rstd_o, int N, int T, int nq, int nkv, int pos_offset,
-                                       float eps) {
+                                       float eps, const int* __restrict__ positions) {
     constexpr int HD = 64 * E;
     const int nh = nq + nkv;
     const int lane = threadIdx.x & 31;
@@ -434,7 +434,7 @@ __global__ void qknorm_rope_fwd_kernel(const bf16* __restrict__ qkv, const bf16*
         } else if (lane == 0) {
             rstd_o[w] = 1.f;
         }
-        const int pos = tok % T + pos_offset;
+        const int pos = positions ? positions[tok] : tok % T + pos_offset;
         bf16* dst = out + (size_t)tok * out_stride + head * HD;
 #pragma unroll
         for (int i = 0; i < E; ++i) {
@@ -518,13 +518,14 @@ KB_API int kb_qknorm_grid_warps() { return kb_num_sms() * 8 * 8; }
 
 KB_API int kb_qknorm_rope_fwd(const void* qkv, const void* qw, const void* kw, const float* cosT, const float* sinT,
                               void* out, float* rstd, int N, int T, int nq, int nkv, int hd, int pos_offset,
-                              float eps, cudaStream_t st) {
+                              float eps, const int* positions, cudaStream_t st) {
     const long long total = (long long)N * (nq + nkv);
     long long blocks = (total + 7) / 8;
     if (blocks > kb_num_sms() * 16) blocks = kb_num_sms() * 16;
     const bool norm = qw != nullptr;
 #define QK_FWD(E, NORM) qknorm_rope_fwd_kernel<E, NORM><<<(int)blocks, 256, 0, st>>>( \
-        (const bf16*)qkv, (const bf16*)qw, (const bf16*)kw, cosT, sinT, (bf16*)out, rstd, N, T, nq, nkv, pos_offset, eps)
+        (const bf16*)qkv, (const bf16*)qw, (const bf16*)kw, cosT, sinT, (bf16*)out, rstd, N, T, nq, nkv, pos_offset, eps, \
+        positions)
     if (hd == 128) { if (norm) QK_FWD(2, true); else QK_FWD(2, false); }
     else if (hd == 64) { if (norm) QK_FWD(1, true); else QK_FWD(1, false); }
     else return 5;

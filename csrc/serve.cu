@@ -1,0 +1,244 @@
+// Serving kernels: paged KV cache append, split-KV paged decode attention (GQA), greedy argmax.
+//
+// Cache layout: k_pages / v_pages [num_pages, PAGE, n_kv, hd] bf16 with PAGE = 16 tokens;
+// keys are stored post QK-norm and post RoPE (as the reference caches them,
+// src/model/llama.py:333-337).  A request's pages are listed in page_table[req][i].
+#include "common.cuh"
+
+typedef __nv_bfloat16 bf16;
+constexpr int PAGE = 16;
+
+// k, v: [N, n_kv*hd] rows with the given strides; slot[n] = page * PAGE + offset in page, or < 0 to skip.
+__global__ void kv_append_kernel(const bf16* __restrict__ k, const bf16* __restrict__ v, long long k_stride,
+                                 long long v_stride, bf16* __restrict__ k_pages, bf16* __restrict__ v_pages,
+                                 const long long* __restrict__ slot, int N, int row_elems) {
+    const int chunks = row_elems >> 3;
+    const long long total = (long long)N * chunks;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const int n = (int)(i / chunks), c = (int)(i % chunks);
+        const long long s = slot[n];
+        if (s < 0) continue;
+        st8(k_pages + s * row_elems + (size_t)c * 8, ld8(k + (size_t)n * k_stride + (size_t)c * 8));
+        st8(v_pages + s * row_elems + (size_t)c * 8, ld8(v + (size_t)n * v_stride + (size_t)c * 8));
+    }
+}
+KB_API int kb_kv_append(const void* k, const void* v, long long k_stride, long long v_stride, void* k_pages,
+                        void* v_pages, const long long* slot, int N, int row_elems, cudaStream_t st) {
+    if (row_elems % 8 || k_stride % 8 || v_stride % 8) return 5;
+    long long blocks = ((long long)N * (row_elems / 8) + 255) / 256;
+    if (blocks < 1) blocks = 1;
+    if (blocks > 4096) blocks = 4096;
+    kv_append_kernel<<<(int)blocks, 256, 0, st>>>((const bf16*)k, (const bf16*)v, k_stride, v_stride, (bf16*)k_pages,
+                                                  (bf16*)v_pages, slot, N, row_elems);
+    return 0;
+}
+
+// One CTA per (request, kv head, split of SPLIT tokens).  G = query heads per kv head.
+// Phase 1: scores (8 lanes per token, 16 elements each for hd=128; 4 lanes x 16 for hd=64).
+// Phase 2: softmax statistics over the split.  Phase 3: thread d accumulates sum_t p[t] V[t][d].
+template <int HD, int G>
+__global__ void __launch_bounds__(128)
+paged_decode_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* __restrict__ k_pages,
+                    const bf16* __restrict__ v_pages, const int* __restrict__ page_table, int max_pages,
+                    const int* __restrict__ ctx_lens, int n_kv, int split_tokens, float scale,
+                    float* __restrict__ part_o, float* __restrict__ part_ml, int nsplit) {
+    extern __shared__ float sm[];
+    float* sc = sm;                       // [G][split_tokens]
+    __shared__ float qs[G][HD];
+    __shared__ float red[2][G][4];
+    const int req = blockIdx.x, kvh = blockIdx.y, sp = blockIdx.z;
+    const int ctx = ctx_lens[req];
+    const int t0 = sp * split_tokens;
+    const int nt = min(split_tokens, ctx - t0);
+    const int H = n_kv * G;
+    const size_t pbase = ((size_t)(req * n_kv + kvh) * nsplit + sp);
+    if (nt <= 0) {
+        if (threadIdx.x < G) {
+            part_ml[(pbase * G + threadIdx.x) * 2] = -INFINITY;
+            part_ml[(pbase * G + threadIdx.x) * 2 + 1] = 0.f;
+        }
+        return;
+    }
+    for (int i = threadIdx.x; i < G * HD; i += blockDim.x) {
+        const int g = i / HD, d = i % HD;
+        qs[g][d] = __bfloat162float(q[(size_t)req * q_stride + (size_t)(kvh * G + g) * HD + d]) * scale;
+    }
+    __syncthreads();
+    constexpr int LPT = HD / 16;          // lanes per token
+    constexpr int TPW = 32 / LPT;         // tokens per warp iteration
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int sub = lane % LPT, tw = lane / LPT;
+    const int row = n_kv * HD;
+    for (int t = warp * TPW + tw; t < ((nt + TPW - 1) / TPW) * TPW; t += 4 * TPW) {
+        float acc[G];
+#pragma unroll
+        for (int g = 0; g < G; ++g) acc[g] = 0.f;
+        if (t < nt) {
+            const int tok = t0 + t;
+            const int page = page_table[(size_t)req * max_pages + tok / PAGE];
+            const bf16* kp = k_pages + ((size_t)page * PAGE + tok % PAGE) * row + (size_t)kvh * HD + sub * 16;
+            float kf[16];
+            unpack8(ld8(kp), kf);
+            unpack8(ld8(kp + 8), kf + 8);
+#pragma unroll
+            for (int g = 0; g < G; ++g)
+#pragma unroll
+                for (int i = 0; i < 16; ++i) acc[g] += kf[i] * qs[g][sub * 16 + i];
+        }
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+#pragma unroll
+            for (int o = LPT / 2; o > 0; o >>= 1) acc[g] += __shfl_xor_sync(0xffffffffu, acc[g], o);
+            if (sub == 0 && t < nt) sc[g * split_tokens + t] = acc[g];
+        }
+    }
+    __syncthreads();
+    // softmax statistics per query head
+    float mx[G], sum[G];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        float m = -INFINITY;
+        for (int t = threadIdx.x; t < nt; t += blockDim.x) m = fmaxf(m, sc[g * split_tokens + t]);
+        m = warp_max(m);
+        if (lane == 0) red[0][g][warp] = m;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        mx[g] = fmaxf(fmaxf(red[0][g][0], red[0][g][1]), fmaxf(red[0][g][2], red[0][g][3]));
+        float s = 0.f;
+        for (int t = threadIdx.x; t < nt; t += blockDim.x) {
+            const float p = __expf(sc[g * split_tokens + t] - mx[g]);
+            sc[g * split_tokens + t] = p;
+            s += p;
+        }
+        s = warp_sum(s);
+        if (lane == 0) red[1][g][warp] = s;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int g = 0; g < G; ++g) sum[g] = red[1][g][0] + red[1][g][1] + red[1][g][2] + red[1][g][3];
+    // weighted sum of V: thread d (two threads per pair when HD = 64 is handled by the bound below)
+    if (threadIdx.x < HD) {
+        float o[G];
+#pragma unroll
+        for (int g = 0; g < G; ++g) o[g] = 0.f;
+        const int d = threadIdx.x;
+        for (int t = 0; t < nt; ++t) {
+            const int tok = t0 + t;
+            const int page = page_table[(size_t)req * max_pages + tok / PAGE];
+            const float vv = __bfloat162float(v_pages[((size_t)page * PAGE + tok % PAGE) * row + (size_t)kvh * HD + d]);
+#pragma unroll
+            for (int g = 0; g < G; ++g) o[g] += sc[g * split_tokens + t] * vv;
+        }
+#pragma unroll
+        for (int g = 0; g < G; ++g) part_o[(pbase * G + g) * HD + d] = o[g];
+    }
+    if (threadIdx.x < G) {
+        part_ml[(pbase * G + threadIdx.x) * 2] = mx[threadIdx.x];
+        part_ml[(pbase * G + threadIdx.x) * 2 + 1] = sum[threadIdx.x];
+    }
+    (void)H;
+}
+
+// Merge the splits: out[req][head][d] = sum_s e^{m_s - M} o_s[d] / sum_s e^{m_s - M} l_s
+template <int HD>
+__global__ void paged_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                   bf16* __restrict__ out, long long out_stride, int n_kv, int G, int nsplit) {
+    const int req = blockIdx.x, head = blockIdx.y;
+    const int kvh = head / G, g = head % G;
+    const int d = threadIdx.x;
+    float M = -INFINITY;
+    for (int s = 0; s < nsplit; ++s) {
+        const size_t pb = ((size_t)(req * n_kv + kvh) * nsplit + s);
+        M = fmaxf(M, part_ml[(pb * G + g) * 2]);
+    }
+    float num = 0.f, den = 0.f;
+    for (int s = 0; s < nsplit; ++s) {
+        const size_t pb = ((size_t)(req * n_kv + kvh) * nsplit + s);
+        const float m = part_ml[(pb * G + g) * 2], l = part_ml[(pb * G + g) * 2 + 1];
+        if (l <= 0.f) continue;
+        const float w = __expf(m - M);
+        den += w * l;
+        if (d < HD) num += w * part_o[(pb * G + g) * HD + d];
+    }
+    if (d < HD) out[(size_t)req * out_stride + (size_t)head * HD + d] = __float2bfloat16(den > 0.f ? num / den : 0.f);
+}
+
+// Workspace sizes (floats) for B requests: part_o = B*n_kv*nsplit*G*hd, part_ml = B*n_kv*nsplit*G*2.
+KB_API int kb_paged_decode(const void* q, long long q_stride, const void* k_pages, const void* v_pages,
+                           const int* page_table, int max_pages, const int* ctx_lens, int B, int n_q, int n_kv, int hd,
+                           int max_ctx, int split_tokens, float scale, float* part_o, float* part_ml, void* out,
+                           long long out_stride, cudaStream_t st) {
+    const int G = n_q / n_kv;
+    if (n_q % n_kv || split_tokens % PAGE || split_tokens > 2048) return 5;
+    const int nsplit = (max_ctx + split_tokens - 1) / split_tokens;
+    dim3 grid(B, n_kv, nsplit);
+    const size_t smem = (size_t)G * split_tokens * sizeof(float);
+#define DEC(HD_, G_)                                                                                          \
+    paged_decode_kernel<HD_, G_><<<grid, 128, smem, st>>>((const bf16*)q, q_stride, (const bf16*)k_pages,      \
+                                                          (const bf16*)v_pages, page_table, max_pages, ctx_lens, \
+                                                          n_kv, split_tokens, scale, part_o, part_ml, nsplit)
+    if (hd == 128) {
+        switch (G) {
+            case 1: DEC(128, 1); break;
+            case 2: DEC(128, 2); break;
+            case 3: DEC(128, 3); break;
+            case 4: DEC(128, 4); break;
+            case 8: DEC(128, 8); break;
+            default: return 5;
+        }
+        paged_merge_kernel<128><<<dim3(B, n_q), 128, 0, st>>>(part_o, part_ml, (bf16*)out, out_stride, n_kv, G, nsplit);
+    } else if (hd == 64) {
+        switch (G) {
+            case 1: DEC(64, 1); break;
+            case 2: DEC(64, 2); break;
+            case 3: DEC(64, 3); break;
+            case 4: DEC(64, 4); break;
+            case 8: DEC(64, 8); break;
+            default: return 5;
+        }
+        paged_merge_kernel<64><<<dim3(B, n_q), 64, 0, st>>>(part_o, part_ml, (bf16*)out, out_stride, n_kv, G, nsplit);
+    } else {
+        return 5;
+    }
+    return 0;
+}
+
+// Greedy sampling: out[row] = argmax_j logits[row][j] (first index on ties).
+__global__ void argmax_kernel(const bf16* __restrict__ logits, long long stride, int V, long long* __restrict__ out) {
+    __shared__ float bv[32];
+    __shared__ int bi[32];
+    const bf16* lg = logits + (size_t)blockIdx.x * stride;
+    float best = -INFINITY;
+    int idx = 0x7fffffff;
+    for (int j = threadIdx.x; j < V; j += blockDim.x) {
+        const float v = __bfloat162float(lg[j]);
+        if (v > best || (v == best && j < idx)) { best = v; idx = j; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+        if (ov > best || (ov == best && oi < idx)) { best = ov; idx = oi; }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) { bv[warp] = best; bi[warp] = idx; }
+    __syncthreads();
+    if (warp == 0) {
+        best = lane < (blockDim.x >> 5) ? bv[lane] : -INFINITY;
+        idx = lane < (blockDim.x >> 5) ? bi[lane] : 0x7fffffff;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+            if (ov > best || (ov == best && oi < idx)) { best = ov; idx = oi; }
+        }
+        if (lane == 0) out[blockIdx.x] = idx;
+    }
+}
+KB_API int kb_argmax(const void* logits, long long stride, int rows, int V, long long* out, cudaStream_t st) {
+    argmax_kernel<<<rows, 512, 0, st>>>((const bf16*)logits, stride, V, out);
+    return 0;
+}

@@ -61,7 +61,7 @@ class ParamArena:
     """
 
     def __init__(self, model: KotodamaModel, device: torch.device, dtype: torch.dtype,
-                 allocator=None) -> None:
+                 allocator=None, with_grads: bool = True) -> None:
         self.model = model
         named = [(n, p) for n, p in model.named_parameters() if p.requires_grad]
         self.names = [n for n, _ in named]
@@ -98,7 +98,7 @@ class ParamArena:
         self.total = _round_up(off, _ALIGN)
         alloc = allocator or (lambda n: torch.zeros(n, device=device, dtype=dtype))
         self.params = alloc(self.total)
-        self.grads = alloc(self.total)
+        self.grads = alloc(self.total) if with_grads else None
         self.by_name = {s.name: s for s in self.slots}
         owners = {}
         for mod_name, mod in model.named_modules():
@@ -110,8 +110,9 @@ class ParamArena:
                 if not s.param.is_meta:
                     view.copy_(s.param.data)
                 mod, pn = owners[s.name]
-                newp = nn.Parameter(view, requires_grad=True)
-                newp.grad = self.grads[s.offset:s.offset + s.numel].view(s.shape)
+                newp = nn.Parameter(view, requires_grad=with_grads)
+                if with_grads:
+                    newp.grad = self.grads[s.offset:s.offset + s.numel].view(s.shape)
                 for k, v in vars(s.param).items():          # keep tags such as the tensor-parallel shard info
                     if k.startswith("_tp_"):
                         setattr(newp, k, v)

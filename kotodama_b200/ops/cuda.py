@@ -177,12 +177,13 @@ class CudaOps(TorchOps):
         return out
 
     # ------------------------------------------------------------------ QK-norm + RoPE
-    def qknorm_rope_fwd(self, qkv, qw, kw, cos, sin, seq_len, n_q, n_kv, hd, eps, pos_offset=0):
+    def qknorm_rope_fwd(self, qkv, qw, kw, cos, sin, seq_len, n_q, n_kv, hd, eps, pos_offset=0, positions=None):
         N = qkv.shape[0]
         out = torch.empty(N, (n_q + n_kv) * hd, device=qkv.device, dtype=qkv.dtype)
         rstd = torch.empty(N, n_q + n_kv, device=qkv.device, dtype=torch.float32)
         rc = self.lib.kb_qknorm_rope_fwd(_p(qkv), _p(qw), _p(kw), _p(cos), _p(sin), _p(out), _p(rstd), _I(N),
-                                         _I(seq_len), _I(n_q), _I(n_kv), _I(hd), _I(pos_offset), _F(eps), _st())
+                                         _I(seq_len), _I(n_q), _I(n_kv), _I(hd), _I(pos_offset), _F(eps), _p(positions),
+                                         _st())
         self._rc(rc, "kb_qknorm_rope_fwd")
         return out, rstd
 
@@ -312,4 +313,33 @@ class CudaOps(TorchOps):
         assert x.ndim == 2 and x.is_contiguous() and x.element_size() == 2
         out = torch.empty(x.shape[1], x.shape[0], device=x.device, dtype=x.dtype)
         self._rc(self.lib.kb_transpose16(_p(x), _p(out), _I(x.shape[0]), _I(x.shape[1]), _st()), "kb_transpose16")
+        return out
+
+    # ------------------------------------------------------------------ serving
+    def kv_append(self, k, v, k_pages, v_pages, slots):
+        """Copy rows ``k[n], v[n]`` (``[N, n_kv*hd]`` views) into cache slot ``slots[n]`` (page*16 + offset)."""
+        N, row = k.shape
+        self._rc(self.lib.kb_kv_append(_p(k), _p(v), _LL(k.stride(0)), _LL(v.stride(0)), _p(k_pages), _p(v_pages),
+                                       _p(slots), _I(N), _I(row), _st()), "kb_kv_append")
+
+    def paged_decode_attention(self, q, k_pages, v_pages, page_table, ctx_lens, max_ctx, n_q, n_kv, hd, split=256):
+        """``q[B, n_q*hd]`` (one new token per request) against the paged cache; returns ``[B, n_q*hd]``."""
+        B = q.shape[0]
+        nsplit = (max_ctx + split - 1) // split
+        G = n_q // n_kv
+        part_o = torch.empty(B * n_kv * nsplit * G * hd, device=q.device, dtype=torch.float32)
+        part_ml = torch.empty(B * n_kv * nsplit * G * 2, device=q.device, dtype=torch.float32)
+        out = torch.empty(B, n_q * hd, device=q.device, dtype=q.dtype)
+        rc = self.lib.kb_paged_decode(_p(q), _LL(q.stride(0)), _p(k_pages), _p(v_pages), _p(page_table),
+                                      _I(page_table.shape[1]), _p(ctx_lens), _I(B), _I(n_q), _I(n_kv), _I(hd),
+                                      _I(max_ctx), _I(split), _F(1.0 / math.sqrt(hd)), _p(part_o), _p(part_ml),
+                                      _p(out), _LL(out.stride(0)), _st())
+        self._rc(rc, "kb_paged_decode")
+        self.launches += 1
+        return out
+
+    def argmax(self, logits):
+        out = torch.empty(logits.shape[0], device=logits.device, dtype=torch.long)
+        self._rc(self.lib.kb_argmax(_p(logits), _LL(logits.stride(0)), _I(logits.shape[0]), _I(logits.shape[1]),
+                                    _p(out), _st()), "kb_argmax")
         return out

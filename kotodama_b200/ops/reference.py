@@ -129,7 +129,7 @@ class TorchOps:
     # ------------------------------------------------------ QK-norm + RoPE
     def qknorm_rope_fwd(self, qkv: torch.Tensor, qw: Optional[torch.Tensor], kw: Optional[torch.Tensor],
                         cos: torch.Tensor, sin: torch.Tensor, seq_len: int, n_q: int, n_kv: int, hd: int,
-                        eps: float, pos_offset: int = 0):
+                        eps: float, pos_offset: int = 0, positions: Optional[torch.Tensor] = None):
         """Per-head RMSNorm (weight shared by heads) then rotate-half RoPE on the q and k parts of a
         fused ``qkv[N,(n_q+2*n_kv)*hd]`` projection.  Token ``n`` sits at position
         ``pos_offset + n % seq_len``.  Returns ``qk[N,(n_q+n_kv)*hd]`` and ``rstd[N,n_q+n_kv]`` (fp32)."""
@@ -143,7 +143,7 @@ class TorchOps:
         else:
             rstd = torch.ones(n, nh, dtype=x.dtype, device=qkv.device)
             y = x
-        pos = (torch.arange(n, device=qkv.device) % seq_len) + pos_offset
+        pos = (torch.arange(n, device=qkv.device) % seq_len) + pos_offset if positions is None else positions.long()
         c, s = _f(cos[pos]).unsqueeze(1), _f(sin[pos]).unsqueeze(1)
         h2 = hd // 2
         rot = torch.cat([-y[..., h2:], y[..., :h2]], -1)
@@ -325,6 +325,33 @@ class TorchOps:
 
     def transpose(self, x: torch.Tensor) -> torch.Tensor:
         return x.t().contiguous()
+
+
+    # ------------------------------------------------------------- serving
+    def kv_append(self, k, v, k_pages, v_pages, slots) -> None:
+        """Copy rows ``k[n], v[n]`` (``[N, n_kv*hd]``) into cache slot ``slots[n]`` (= page*16 + offset)."""
+        row = k.shape[1]
+        ok = slots >= 0
+        k_pages.view(-1, row)[slots[ok]] = k[ok]
+        v_pages.view(-1, row)[slots[ok]] = v[ok]
+
+    def paged_decode_attention(self, q, k_pages, v_pages, page_table, ctx_lens, max_ctx, n_q, n_kv, hd, split=256):
+        """One query token per request against its pages (``k_pages[P,16,n_kv,hd]``)."""
+        B = q.shape[0]
+        g = n_q // n_kv
+        out = torch.empty(B, n_q * hd, device=q.device, dtype=q.dtype)
+        for b in range(B):
+            n = int(ctx_lens[b])
+            pages = page_table[b, : (n + 15) // 16].long()
+            k = _f(k_pages[pages].reshape(-1, n_kv, hd)[:n]).permute(1, 0, 2).repeat_interleave(g, 0)
+            v = _f(v_pages[pages].reshape(-1, n_kv, hd)[:n]).permute(1, 0, 2).repeat_interleave(g, 0)
+            qb = _f(q[b]).view(n_q, 1, hd)
+            p = torch.softmax((qb @ k.transpose(1, 2)) / math.sqrt(hd), -1)
+            out[b] = (p @ v).reshape(-1).to(q.dtype)
+        return out
+
+    def argmax(self, logits: torch.Tensor) -> torch.Tensor:
+        return logits.float().argmax(-1)
 
 
 TORCH_OPS = TorchOps()

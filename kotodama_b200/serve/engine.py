@@ -1,0 +1,293 @@
+"""Serving engine: paged KV cache (16-token pages), continuous batching, greedy / sampled
+decoding on the device.
+
+The reference server (``serve.py:322-391``) handles one request at a time with a contiguous KV
+cache grown by ``torch.cat``.  Here any number of requests run concurrently: a request is
+prefilled in one pass over its prompt (writing post-norm, post-RoPE keys and values straight
+into its pages), then joins the decode batch, where every step advances all running requests
+by one token with the split-KV paged attention kernel.  Pages return to the free list when a
+request finishes.
+
+AttnRes needs no cross-token state at inference: the sources of a routing call are that
+token's own block summaries, rebuilt layer by layer (``src/model/llama.py:718-763``), so only
+keys and values are cached.
+
+The layer pipeline is the executor's forward schedule (same ops backend: PyTorch on CPU,
+sm_100a kernels on CUDA); sampling follows the reference order repetition penalty ->
+temperature -> top-k -> top-p -> multinomial, greedy at temperature 0 (``serve.py:266-304``).
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import Any, Optional
+
+import torch
+
+from ..config import ModelConfig
+from ..engine import ParamArena
+from ..models.llama import KotodamaModel
+from ..ops import get_ops
+
+PAGE = 16
+
+
+@dataclass
+class SamplingParams:
+    max_new_tokens: int = 256
+    temperature: float = 0.7
+    top_k: int = 50
+    top_p: float = 0.0
+    repetition_penalty: float = 1.0
+    eos_token_id: Optional[int] = None
+
+
+@dataclass
+class Request:
+    rid: int
+    prompt: list[int]
+    params: SamplingParams
+    pages: list[int] = field(default_factory=list)
+    generated: list[int] = field(default_factory=list)
+    ctx_len: int = 0
+    finished: bool = False
+    finish_reason: str = ""
+
+
+class PagedKVCache:
+    """Per-layer key/value page pools and a free list shared by all layers (a page index means
+    the same slot in every layer)."""
+
+    def __init__(self, cfg: ModelConfig, num_pages: int, device: torch.device, dtype: torch.dtype,
+                 n_kv_local: Optional[int] = None) -> None:
+        self.n_kv = n_kv_local or cfg.num_kv_heads
+        self.hd = cfg.head_dim
+        self.num_pages = num_pages
+        shape = (cfg.num_layers, num_pages, PAGE, self.n_kv, self.hd)
+        self.k = torch.zeros(shape, device=device, dtype=dtype)
+        self.v = torch.zeros(shape, device=device, dtype=dtype)
+        self.free = list(range(num_pages - 1, -1, -1))
+
+    def pages_for(self, tokens: int) -> int:
+        return (tokens + PAGE - 1) // PAGE
+
+    def can_allocate(self, n: int) -> bool:
+        return len(self.free) >= n
+
+    def allocate(self, n: int) -> list[int]:
+        if len(self.free) < n:
+            raise RuntimeError("KV cache exhausted")
+        return [self.free.pop() for _ in range(n)]
+
+    def release(self, pages: list[int]) -> None:
+        self.free.extend(reversed(pages))
+
+
+def sample_tokens(logits: torch.Tensor, reqs: list[Request], ops: Any) -> torch.Tensor:
+    """Next token per row of ``logits[B,V]``.  All-greedy batches use the argmax kernel."""
+    if all(r.params.temperature == 0 and r.params.repetition_penalty == 1.0 for r in reqs):
+        return ops.argmax(logits)
+    out = torch.empty(len(reqs), dtype=torch.long, device=logits.device)
+    for i, r in enumerate(reqs):
+        lg = logits[i].float()
+        p = r.params
+        if p.repetition_penalty != 1.0:
+            seen = torch.tensor(sorted(set(r.prompt + r.generated)), device=lg.device, dtype=torch.long)
+            if seen.numel():
+                vals = lg[seen]
+                lg[seen] = torch.where(vals > 0, vals / p.repetition_penalty, vals * p.repetition_penalty)
+        if p.temperature == 0:
+            out[i] = lg.argmax()
+            continue
+        lg = lg / p.temperature
+        if p.top_k > 0:
+            kth = torch.topk(lg, min(p.top_k, lg.numel())).values[-1]
+            lg = torch.where(lg < kth, torch.full_like(lg, float("-inf")), lg)
+        if 0.0 < p.top_p < 1.0:
+            srt, idx = torch.sort(lg, descending=True)
+            cum = torch.softmax(srt, -1).cumsum(-1)
+            remove = cum - torch.softmax(srt, -1) > p.top_p
+            srt = srt.masked_fill(remove, float("-inf"))
+            lg = torch.full_like(lg, float("-inf")).scatter(0, idx, srt)
+        out[i] = torch.multinomial(torch.softmax(lg, -1), 1)[0]
+    return out
+
+
+class ServingEngine:
+    def __init__(self, model: KotodamaModel, *, device: torch.device | str = "cpu",
+                 dtype: torch.dtype = torch.float32, max_batch: int = 64, num_pages: Optional[int] = None,
+                 max_ctx: Optional[int] = None, ops: Any = None, tp: Any = None) -> None:
+        self.device = torch.device(device)
+        self.dtype = dtype
+        self.model = model.eval()
+        self.cfg: ModelConfig = model.config
+        self.ops = ops or get_ops(self.device)
+        self.tp = tp                                  # tensor-parallel helper (``serve.tp``) or None
+        if tp is not None:
+            tp.prepare_model(model)
+        self.arena = ParamArena(model, self.device, dtype, with_grads=False)
+        cfg = self.cfg
+        self.max_ctx = max_ctx or cfg.max_position_embeddings
+        self.max_batch = max_batch
+        tpn = tp.size if tp is not None else 1
+        self.H, self.KV = cfg.num_attention_heads // tpn, cfg.num_kv_heads // tpn
+        self.hd, self.D = cfg.head_dim, cfg.hidden_size
+        pages = num_pages or max_batch * ((self.max_ctx + PAGE - 1) // PAGE)
+        self.cache = PagedKVCache(cfg, pages, self.device, dtype, n_kv_local=self.KV)
+        self.max_pages_per_req = (self.max_ctx + PAGE - 1) // PAGE
+        self.waiting: list[Request] = []
+        self.running: list[Request] = []
+        self._next_id = 0
+        self.stats = {"prefill_tokens": 0, "decode_tokens": 0, "prefill_s": 0.0, "decode_s": 0.0, "steps": 0}
+        ar = self.arena
+        self.layers = []
+        for i in range(cfg.num_layers):
+            p = f"layers.{i}."
+            g = lambda n: ar.view(p + n) if (p + n) in ar.by_name else None
+            self.layers.append(dict(
+                wqkv=ar.fused(p + "attn.q_proj.weight", p + "attn.v_proj.weight"), wo=ar.view(p + "attn.o_proj.weight"),
+                wgu=ar.fused(p + "ffn.gate_proj.weight", p + "ffn.up_proj.weight"), wd=ar.view(p + "ffn.down_proj.weight"),
+                attn_norm=g("attn_norm.weight"), ffn_norm=g("ffn_norm.weight"), qn=g("attn.q_norm.weight"),
+                kn=g("attn.k_norm.weight"), aq=g("attn_res_query"), an=g("attn_res_norm.weight"),
+                mq=g("mlp_res_query"), mn=g("mlp_res_norm.weight")))
+        self.boundaries = frozenset(cfg.boundaries()) if cfg.attn_res else frozenset()
+
+    # ------------------------------------------------------------------ requests
+    def add_request(self, prompt: list[int], params: Optional[SamplingParams] = None) -> Request:
+        params = params or SamplingParams()
+        if len(prompt) == 0:
+            raise ValueError("empty prompt")
+        if len(prompt) + 1 > self.max_ctx:
+            raise ValueError(f"prompt of {len(prompt)} tokens does not fit the context of {self.max_ctx}")
+        r = Request(self._next_id, list(prompt), params)
+        self._next_id += 1
+        self.waiting.append(r)
+        return r
+
+    def has_work(self) -> bool:
+        return bool(self.waiting or self.running)
+
+    # ------------------------------------------------------------------ model pass
+    @torch.no_grad()
+    def _forward(self, ids: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor, decode: Optional[dict],
+                 last_rows: torch.Tensor) -> torch.Tensor:
+        """Runs all layers on ``ids[N]``; keys/values go to ``slots``.  ``decode`` holds the page table
+        and context lengths for paged attention; ``None`` means a causal prefill of one request.
+        Returns logits for ``last_rows``."""
+        ops, cfg, ar = self.ops, self.cfg, self.arena
+        H, KV, hd = self.H, self.KV, self.hd
+        eps = cfg.norm_eps
+        cos, sin = self.model.rope_cos, self.model.rope_sin
+        N = ids.numel()
+        x = ops.embedding_fwd(ids, ar.view("embed_tokens.weight"))
+        committed: list[torch.Tensor] = []
+        partial: Optional[torch.Tensor] = x
+        for i, lw in enumerate(self.layers):
+            xn, _ = ops.route_norm_fwd(committed + [partial], lw["aq"], lw["an"], lw["attn_norm"], eps)
+            if i in self.boundaries:
+                committed = committed + [partial]
+                partial = None
+            qkv = ops.gemm_nt(xn, lw["wqkv"])
+            qk, _ = ops.qknorm_rope_fwd(qkv, lw["qn"], lw["kn"], cos, sin, N, H, KV, hd, eps, positions=positions)
+            k_rows = qk[:, H * hd:]
+            v_rows = qkv[:, (H + KV) * hd:]
+            ops.kv_append(k_rows, v_rows, self.cache.k[i], self.cache.v[i], slots)
+            if decode is None:
+                o, _ = ops.attention_fwd(qk[:, : H * hd].view(1, N, H, hd), k_rows.view(1, N, KV, hd),
+                                         v_rows.view(1, N, KV, hd))
+                attn = o.reshape(N, H * hd)
+            else:
+                attn = ops.paged_decode_attention(qk[:, : H * hd], self.cache.k[i], self.cache.v[i],
+                                                  decode["page_table"], decode["ctx_lens"], decode["max_ctx"], H, KV, hd)
+            partial = self._row_linear(attn, lw["wo"], partial)
+            xn2, _ = ops.route_norm_fwd(committed + [partial], lw["mq"], lw["mn"], lw["ffn_norm"], eps)
+            act = ops.swiglu_fwd(ops.gemm_nt(xn2, lw["wgu"]))
+            partial = self._row_linear(act, lw["wd"], partial)
+        g = lambda n: ar.view(n) if n in ar.by_name else None
+        xf, _ = ops.route_norm_fwd([s[last_rows] for s in committed + [partial]], g("final_res_query"),
+                                   g("final_res_norm.weight"), ar.view("norm.weight"), eps)
+        return ops.gemm_nt(xf, self.model.get_lm_head_weight())
+
+    def _row_linear(self, x: torch.Tensor, w: torch.Tensor, residual: Optional[torch.Tensor]) -> torch.Tensor:
+        if self.tp is None:
+            return self.ops.gemm_nt(x, w, residual=residual)
+        return self.tp.row_linear(self.ops, x, w, residual)
+
+    # ------------------------------------------------------------------ scheduling
+    def _prefill(self, r: Request) -> None:
+        n = len(r.prompt)
+        r.pages = self.cache.allocate(self.cache.pages_for(min(n + r.params.max_new_tokens, self.max_ctx)))
+        ids = torch.tensor(r.prompt, dtype=torch.long, device=self.device)
+        pos = torch.arange(n, dtype=torch.int32, device=self.device)
+        pages = torch.tensor(r.pages, dtype=torch.long, device=self.device)
+        slots = pages[pos.long() // PAGE] * PAGE + pos.long() % PAGE
+        logits = self._forward(ids, pos, slots, None, torch.tensor([n - 1], device=self.device))
+        r.ctx_len = n
+        tok = int(sample_tokens(logits, [r], self.ops)[0])
+        self._accept(r, tok)
+        self.stats["prefill_tokens"] += n
+
+    def _accept(self, r: Request, tok: int) -> None:
+        r.generated.append(tok)
+        p = r.params
+        if p.eos_token_id is not None and tok == p.eos_token_id:
+            r.finished, r.finish_reason = True, "eos"
+        elif len(r.generated) >= p.max_new_tokens:
+            r.finished, r.finish_reason = True, "length"
+        elif r.ctx_len + 1 >= self.max_ctx:
+            r.finished, r.finish_reason = True, "context"
+
+    def _decode(self) -> None:
+        reqs = self.running
+        B = len(reqs)
+        ids = torch.tensor([r.generated[-1] for r in reqs], dtype=torch.long, device=self.device)
+        pos = torch.tensor([r.ctx_len for r in reqs], dtype=torch.int32, device=self.device)
+        table = torch.zeros(B, self.max_pages_per_req, dtype=torch.int32)
+        for i, r in enumerate(reqs):
+            table[i, : len(r.pages)] = torch.tensor(r.pages, dtype=torch.int32)
+        table = table.to(self.device, non_blocking=True)
+        slots = torch.tensor([r.pages[r.ctx_len // PAGE] * PAGE + r.ctx_len % PAGE for r in reqs], dtype=torch.long,
+                             device=self.device)
+        ctx = pos + 1
+        decode = {"page_table": table, "ctx_lens": ctx, "max_ctx": max(r.ctx_len for r in reqs) + 1}
+        logits = self._forward(ids, pos, slots, decode, torch.arange(B, device=self.device))
+        toks = sample_tokens(logits, reqs, self.ops).tolist()
+        for r, t in zip(reqs, toks):
+            r.ctx_len += 1
+            self._accept(r, int(t))
+        self.stats["decode_tokens"] += B
+
+    def step(self) -> list[Request]:
+        """Admit and prefill what fits, advance every running request by one token, retire the
+        finished.  Returns the requests that finished in this step."""
+        import time
+        t0 = time.perf_counter()
+        while self.waiting and len(self.running) < self.max_batch:
+            r = self.waiting[0]
+            if not self.cache.can_allocate(self.cache.pages_for(min(len(r.prompt) + r.params.max_new_tokens, self.max_ctx))):
+                break
+            self.waiting.pop(0)
+            self._prefill(r)
+            self.running.append(r)
+        t1 = time.perf_counter()
+        live = [r for r in self.running if not r.finished]
+        done = [r for r in self.running if r.finished]
+        self.running = live
+        if live:
+            self._decode()
+        done += [r for r in self.running if r.finished]
+        self.running = [r for r in self.running if not r.finished]
+        for r in done:
+            self.cache.release(r.pages)
+            r.pages = []
+        self.stats["prefill_s"] += t1 - t0
+        self.stats["decode_s"] += time.perf_counter() - t1
+        self.stats["steps"] += 1
+        return done
+
+    def generate(self, prompts: list[list[int]], params: Optional[SamplingParams] = None) -> list[list[int]]:
+        """Convenience: run a set of prompts to completion; returns the generated ids per prompt."""
+        reqs = [self.add_request(p, params) for p in prompts]
+        while self.has_work():
+            self.step()
+        return [r.generated for r in reqs]
