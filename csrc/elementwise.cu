@@ -887,4 +887,19 @@ KB_API int kb_axpby_half(void* y, const void* x, long long n, float a, float b, 
     return 0;
 }
 
+// dst = bf16(src + beta * addend)  (addend optional): finishes a split-K GEMM.
+__global__ void f32_to_bf16_add_kernel(const float* __restrict__ src, const bf16* __restrict__ addend, float beta,
+                                       bf16* __restrict__ dst, long long n) {
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        float v = src[i];
+        if (addend) v += beta * __bfloat162float(addend[i]);
+        dst[i] = __float2bfloat16(v);
+    }
+}
+KB_API int kb_f32_to_bf16_add(const float* src, const void* addend, float beta, void* dst, long long n,
+                              cudaStream_t st) {
+    f32_to_bf16_add_kernel<<<ew_grid(n, 256), 256, 0, st>>>(src, (const bf16*)addend, beta, (bf16*)dst, n);
+    return 0;
+}
+
 KB_API int kb_last_error() { return (int)cudaGetLastError(); }

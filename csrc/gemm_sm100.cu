@@ -34,6 +34,7 @@ struct GemmParams {
     long long ldc, c_batch_stride;
     long long ldcin, cin_batch_stride;
     int* status;
+    int split_k;               // > 1: each tile's K range is cut into split_k parts, fp32 atomic accumulation
 };
 
 __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& b, int& tm, int& tn) {
@@ -136,8 +137,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tiles_m = (p.M + BM - 1) / BM, tiles_n = (p.N + BN - 1) / BN;
-    const int num_tiles = tiles_m * tiles_n * p.batch;
-    const int kblocks = (p.K + BK - 1) / BK;
+    const int num_tiles = tiles_m * tiles_n * p.batch * p.split_k;   // work items (tile, k-part)
+    const int kblocks_total = (p.K + BK - 1) / BK;
+    const int kb_per = (kblocks_total + p.split_k - 1) / p.split_k;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -171,8 +173,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             bool ok = true;
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
                 int b, tm, tn;
-                tile_coords(tile, tiles_m, tiles_n, b, tm, tn);
-                for (int kb = 0; kb < kblocks; ++kb) {
+                tile_coords(tile / p.split_k, tiles_m, tiles_n, b, tm, tn);
+                const int kb0 = (tile % p.split_k) * kb_per, kb1 = min(kblocks_total, kb0 + kb_per);
+                for (int kb = kb0; kb < kb1; ++kb) {
                     if (!tc::mbar_wait(&empty[stage], phase ^ 1, abort_flag)) {
                         atomicMax(p.status, (int)KB_TIMEOUT_TMA);
                         ok = false;
@@ -229,7 +232,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 }
                 tc::tc_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * BN;
-                for (int kb = 0; kb < kblocks; ++kb) {
+                const int kb0 = (tile % p.split_k) * kb_per, kb1 = min(kblocks_total, kb0 + kb_per);
+                for (int kb = kb0; kb < kb1; ++kb) {
                     if (!tc::mbar_wait(&full[stage], phase, abort_flag)) {
                         atomicMax(p.status, (int)KB_TIMEOUT_MMA);
                         ok = false;
@@ -244,7 +248,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                                                    : tc::smem_desc_sw128(a_addr + k * 32, 16, 1024);
                         const uint64_t bd = p.b_mn ? tc::smem_desc_sw128(b_addr + k * 2048, 64 * BK * 2, 1024)
                                                    : tc::smem_desc_sw128(b_addr + k * 32, 16, 1024);
-                        tc::mma_f16(d_tmem, ad, bd, idesc, (kb | k) != 0);
+                        tc::mma_f16(d_tmem, ad, bd, idesc, ((kb - kb0) | k) != 0);
                     }
                     tc::tc_commit(&empty[stage]);   // stage reusable once these MMAs have read it
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -259,7 +263,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         bool ok = true;
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
             int b, tm, tn;
-            tile_coords(tile, tiles_m, tiles_n, b, tm, tn);
+            tile_coords(tile / p.split_k, tiles_m, tiles_n, b, tm, tn);
+            const bool has_k = (tile % p.split_k) * kb_per < kblocks_total;
             const int buf = it & 1;
             const uint32_t acc_phase = (it >> 1) & 1;
             if (!tc::mbar_wait(&acc_full[buf], acc_phase, abort_flag)) {
@@ -277,7 +282,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 tc::tmem_ld_wait();
                 const int col = tn * BN + c0;
                 const int ncols = min(32, p.N - col);
-                if (row < p.M && ncols > 0) {
+                if (p.split_k > 1) {
+                    if (row < p.M && ncols > 0 && has_k) {
+                        float* dst = reinterpret_cast<float*>(p.C) + (long long)b * p.c_batch_stride +
+                                     (long long)row * p.ldc + col;
+                        for (int j = 0; j < ncols; ++j) atomicAdd(dst + j, p.alpha * __uint_as_float(acc[j]));
+                    }
+                } else if (row < p.M && ncols > 0) {
                     const long long off = (long long)b * p.c_batch_stride + (long long)row * p.ldc + col;
                     const long long offin = (long long)b * p.cin_batch_stride + (long long)row * p.ldcin + col;
                     if (p.out_type == 2) {
@@ -355,7 +366,9 @@ int make_tmap(CUtensorMap* m, const void* base, int fmt, long long cols, long lo
 KB_API int kb_gemm(const void* A, const void* B, void* C, const void* Cin, int M, int N, int K, int batch,
                    long long lda, long long ldb, long long ldc, long long ldcin, long long a_bs, long long b_bs,
                    long long c_bs, long long cin_bs, int a_mn, int b_mn, int a_fmt, int b_fmt, int out_type,
-                   float alpha, float beta, int* status, int max_ctas, cudaStream_t st) {
+                   float alpha, float beta, int* status, int max_ctas, int split_k, cudaStream_t st) {
+    if (split_k < 1) split_k = 1;
+    if (split_k > 1 && out_type != 2) return 5;
     if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return 5;
     if ((lda & 7) || (ldb & 7) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15)) return 6;
     if (batch > 1 && ((a_bs & 7) || (b_bs & 7))) return 6;
@@ -380,11 +393,12 @@ KB_API int kb_gemm(const void* A, const void* B, void* C, const void* Cin, int M
     p.alpha = alpha; p.beta = beta; p.C = C; p.Cin = Cin;
     p.ldc = ldc; p.c_batch_stride = c_bs; p.ldcin = ldcin; p.cin_batch_stride = cin_bs;
     p.status = status;
+    p.split_k = split_k;
     int sms = 0, dev = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     if (max_ctas > 0 && max_ctas < sms) sms = max_ctas;
-    const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN) * batch;
+    const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN) * batch * split_k;
     const int grid = tiles < sms ? tiles : sms;
     gemm_tcgen05_kernel<<<grid, 192, SMEM_BYTES, st>>>(tmA, tmB, p);
     return 0;

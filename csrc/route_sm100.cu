@@ -402,9 +402,13 @@ PipeCfg pipe_cfg(int S, int D, bool bwd) {
 #define PIPE_CASE(MAXS_, CPT_)                                                                              \
     {                                                                                                       \
         auto kern = route_pipe_kernel<MAXS_, CPT_, BWD>;                                                    \
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)cfg.smem) !=       \
-            cudaSuccess)                                                                                    \
-            return 7;                                                                                       \
+        static size_t attr_smem = 0; /* per instantiation: raise the limit only when it grows */           \
+        if (cfg.smem > attr_smem) {                                                                         \
+            if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) !=      \
+                cudaSuccess)                                                                                \
+                return 7;                                                                                   \
+            attr_smem = 200 * 1024;                                                                         \
+        }                                                                                                   \
         kern<<<grid, cfg.threads, cfg.smem, st>>>(rs, ds, S, (const bf16*)dxn, (const bf16*)q,              \
                                                    (const bf16*)rn_w, (const bf16*)n_w, (bf16*)xn, alpha, r, \
                                                    logit, rstd, dw_part, dnw_part, N, D, eps, cfg.stages,  \

@@ -15,11 +15,15 @@ def _native_ok(ops, q: torch.Tensor) -> bool:
     return getattr(ops, "native_attention", False) and q.shape[-1] in (64, 128) and q.shape[1] % 128 == 0
 
 
-def attention_fwd(ops, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor):
+def attention_fwd(ops, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, need_grad: bool = True):
     if _native_ok(ops, q):
         from .flash import flash_fwd
         return flash_fwd(ops, q, k, v)
     ops.attention_library_calls = getattr(ops, "attention_library_calls", 0) + 1
+    if not need_grad:
+        o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=True,
+                                           enable_gqa=q.shape[2] != k.shape[2])
+        return o.transpose(1, 2).contiguous(), None
     with torch.enable_grad():
         ql = q.detach().transpose(1, 2).requires_grad_(True)
         kl = k.detach().transpose(1, 2).requires_grad_(True)

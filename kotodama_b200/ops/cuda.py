@@ -50,6 +50,7 @@ class CudaOps(TorchOps):
         self.launches = 0              # launches of kernels from this library
         self._status: dict[int, torch.Tensor] = {}
         self.gemm_max_ctas = 0
+        self.split_k_small_m = True
         for name in ("kb_route_bwd_grid", "kb_qknorm_grid_warps", "kb_route_pipe_grid"):
             getattr(self.lib, name).restype = _I
 
@@ -95,12 +96,29 @@ class CudaOps(TorchOps):
         if out.stride(-1) != 1 or (cin is not None and (cin.stride(-1) != 1 or cin.dtype != out.dtype)):
             raise KernelError("GEMM output/addend must be row-major and of one dtype")
         bs = lambda t: t.stride(0) if batch > 1 else 0
+        tiles = ((M + 127) // 128) * ((N + 255) // 256)
+        kblocks = (K + 63) // 64
+        if (batch == 1 and M <= 128 and tiles <= 74 and kblocks >= 8 and out.dtype == torch.bfloat16
+                and out.is_contiguous() and (cin is None or cin.is_contiguous()) and self.split_k_small_m):
+            # skinny (decode-size) products: too few output tiles to fill the GPU, so the K range is
+            # split over CTAs with fp32 atomic accumulation and a small finishing kernel
+            split = max(2, min(148 // tiles, kblocks // 2, 16))
+            ws = torch.zeros(M, N, device=a.device, dtype=torch.float32)
+            rc = self.lib.kb_gemm(_p(a), _p(b), _p(ws), _p(None), _I(M), _I(N), _I(K), _I(1),
+                                  _LL(a.stride(-2)), _LL(b.stride(-2)), _LL(N), _LL(0), _LL(0), _LL(0), _LL(0), _LL(0),
+                                  _I(int(a_mn)), _I(int(b_mn)), _I(_FMT[a.dtype]), _I(_FMT[b.dtype]), _I(2),
+                                  _F(alpha), _F(0.0), _p(self.status(a.device)), _I(self.gemm_max_ctas), _I(split),
+                                  _st())
+            self._rc(rc, "kb_gemm(split-k)")
+            self._rc(self.lib.kb_f32_to_bf16_add(_p(ws), _p(cin), _F(beta), _p(out), _LL(M * N), _st()),
+                     "kb_f32_to_bf16_add")
+            return out
         rc = self.lib.kb_gemm(_p(a), _p(b), _p(out), _p(cin), _I(M), _I(N), _I(K), _I(batch),
                               _LL(a.stride(-2)), _LL(b.stride(-2)), _LL(out.stride(-2)),
                               _LL(cin.stride(-2) if cin is not None else 0),
                               _LL(bs(a)), _LL(bs(b)), _LL(bs(out)), _LL(bs(cin) if cin is not None else 0),
                               _I(int(a_mn)), _I(int(b_mn)), _I(_FMT[a.dtype]), _I(_FMT[b.dtype]), _I(_OUT[out.dtype]),
-                              _F(alpha), _F(beta), _p(self.status(a.device)), _I(self.gemm_max_ctas), _st())
+                              _F(alpha), _F(beta), _p(self.status(a.device)), _I(self.gemm_max_ctas), _I(1), _st())
         self._rc(rc, "kb_gemm")
         return out
 
@@ -201,9 +219,9 @@ class CudaOps(TorchOps):
         return dw[:hd], dw[hd:]
 
     # ------------------------------------------------------------------ attention
-    def attention_fwd(self, q, k, v):
+    def attention_fwd(self, q, k, v, need_grad=True):
         from .attention import attention_fwd
-        return attention_fwd(self, q, k, v)
+        return attention_fwd(self, q, k, v, need_grad)
 
     def attention_bwd(self, do, q, k, v, o, lse, dq_out, dk_out, dv_out):
         from .attention import attention_bwd

@@ -176,7 +176,7 @@ class TorchOps:
         return dqw, dkw
 
     # ------------------------------------------------------------ attention
-    def attention_fwd(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor):
+    def attention_fwd(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, need_grad: bool = True):
         """Causal GQA attention.  ``q[B,T,H,hd]``, ``k,v[B,T,KV,hd]`` (may be strided views);
         returns ``o[B,T,H,hd]`` contiguous and ``lse[B,H,T]`` fp32 (natural log)."""
         b, t, h, hd = q.shape

@@ -138,6 +138,8 @@ class ServingEngine:
         self.waiting: list[Request] = []
         self.running: list[Request] = []
         self._next_id = 0
+        self._dec_state = None
+        self.use_cuda_graphs = True          # decode steps are replayed from captured graphs on CUDA
         self.stats = {"prefill_tokens": 0, "decode_tokens": 0, "prefill_s": 0.0, "decode_s": 0.0, "steps": 0}
         ar = self.arena
         self.layers = []
@@ -194,7 +196,7 @@ class ServingEngine:
             ops.kv_append(k_rows, v_rows, self.cache.k[i], self.cache.v[i], slots)
             if decode is None:
                 o, _ = ops.attention_fwd(qk[:, : H * hd].view(1, N, H, hd), k_rows.view(1, N, KV, hd),
-                                         v_rows.view(1, N, KV, hd))
+                                         v_rows.view(1, N, KV, hd), need_grad=False)
                 attn = o.reshape(N, H * hd)
             else:
                 attn = ops.paged_decode_attention(qk[:, : H * hd], self.cache.k[i], self.cache.v[i],
@@ -237,21 +239,63 @@ class ServingEngine:
         elif r.ctx_len + 1 >= self.max_ctx:
             r.finished, r.finish_reason = True, "context"
 
+    def _decode_inputs(self, reqs: list[Request]):
+        """Static device buffers for a decode step; the page table is rebuilt only when the set of
+        running requests changes (pages are assigned once, at admission)."""
+        B = len(reqs)
+        key = tuple(r.rid for r in reqs)
+        st = self._dec_state
+        if st is None or st["key"] != key:
+            table = torch.zeros(B, self.max_pages_per_req, dtype=torch.int32)
+            for i, r in enumerate(reqs):
+                table[i, : len(r.pages)] = torch.tensor(r.pages, dtype=torch.int32)
+            if st is None or st["B"] != B:
+                dev = self.device
+                st = {"B": B, "ids": torch.zeros(B, dtype=torch.long, device=dev),
+                      "pos": torch.zeros(B, dtype=torch.int32, device=dev),
+                      "slots": torch.zeros(B, dtype=torch.long, device=dev),
+                      "ctx": torch.zeros(B, dtype=torch.int32, device=dev),
+                      "table": torch.zeros(B, self.max_pages_per_req, dtype=torch.int32, device=dev),
+                      "rows": torch.arange(B, device=dev), "graphs": {}}
+            st["table"].copy_(table, non_blocking=True)
+            st["host_table"] = table
+            st["key"] = key
+            self._dec_state = st
+        lens = torch.tensor([r.ctx_len for r in reqs], dtype=torch.int32)
+        last = torch.tensor([r.generated[-1] for r in reqs], dtype=torch.long)
+        idx = torch.arange(B)
+        slots = st["host_table"][idx, (lens // PAGE).long()].long() * PAGE + (lens % PAGE).long()
+        st["ids"].copy_(last, non_blocking=True)
+        st["pos"].copy_(lens, non_blocking=True)
+        st["ctx"].copy_(lens + 1, non_blocking=True)
+        st["slots"].copy_(slots, non_blocking=True)
+        return st
+
     def _decode(self) -> None:
         reqs = self.running
         B = len(reqs)
-        ids = torch.tensor([r.generated[-1] for r in reqs], dtype=torch.long, device=self.device)
-        pos = torch.tensor([r.ctx_len for r in reqs], dtype=torch.int32, device=self.device)
-        table = torch.zeros(B, self.max_pages_per_req, dtype=torch.int32)
-        for i, r in enumerate(reqs):
-            table[i, : len(r.pages)] = torch.tensor(r.pages, dtype=torch.int32)
-        table = table.to(self.device, non_blocking=True)
-        slots = torch.tensor([r.pages[r.ctx_len // PAGE] * PAGE + r.ctx_len % PAGE for r in reqs], dtype=torch.long,
-                             device=self.device)
-        ctx = pos + 1
-        decode = {"page_table": table, "ctx_lens": ctx, "max_ctx": max(r.ctx_len for r in reqs) + 1}
-        logits = self._forward(ids, pos, slots, decode, torch.arange(B, device=self.device))
-        toks = sample_tokens(logits, reqs, self.ops).tolist()
+        st = self._decode_inputs(reqs)
+        max_ctx = max(r.ctx_len for r in reqs) + 1
+        bucket = min(self.max_ctx, ((max_ctx + 511) // 512) * 512)       # grid of the split-KV kernel
+        decode = {"page_table": st["table"], "ctx_lens": st["ctx"], "max_ctx": bucket}
+        greedy = all(r.params.temperature == 0 and r.params.repetition_penalty == 1.0 for r in reqs)
+        if self.device.type == "cuda" and self.use_cuda_graphs:
+            g = st["graphs"].get(bucket)
+            if g is None:
+                # one eager pass first: lazy initialisation must not happen under capture
+                self._forward(st["ids"], st["pos"], st["slots"], decode, st["rows"])
+                torch.cuda.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    logits = self._forward(st["ids"], st["pos"], st["slots"], decode, st["rows"])
+                    toks = self.ops.argmax(logits)
+                g = st["graphs"][bucket] = (graph, logits, toks)
+            g[0].replay()
+            logits, toks = g[1], g[2]
+            toks = toks.tolist() if greedy else sample_tokens(logits, reqs, self.ops).tolist()
+        else:
+            logits = self._forward(st["ids"], st["pos"], st["slots"], decode, st["rows"])
+            toks = sample_tokens(logits, reqs, self.ops).tolist()
         for r, t in zip(reqs, toks):
             r.ctx_len += 1
             self._accept(r, int(t))

@@ -244,3 +244,12 @@ def test_serving_engine_gpu_matches_cpu_tokens():
     gpu_eng.ops.check_status()
     agree = sum(a == b for x, y in zip(cpu, gpu) for a, b in zip(x, y))
     assert agree >= 18, (cpu, gpu)          # bf16 vs fp32 may flip a near-tie late in a sequence
+
+
+@pytest.mark.parametrize("M,N,K", [(64, 3072, 3072), (64, 5120, 3072), (17, 3072, 8192), (128, 512, 1024)])
+def test_gemm_split_k_small_m(ops, M, N, K):
+    a, b, r = bf(M, K, seed=1), bf(N, K, scale=0.05, seed=2), bf(M, N, seed=3)
+    ref = a.float() @ b.float().t()
+    assert rel_err(ops.gemm_nt(a, b), ref) < 1e-2
+    assert rel_err(ops.gemm_nt(a, b, residual=r), ref + r.float()) < 1e-2
+    ops.check_status()
