@@ -1,0 +1,292 @@
+"""Evaluation helpers shared by analysis scripts: model/registry loading, forward passes that
+expose per-layer states and attention weights, text generation, memmap perplexity and JSONL
+metrics access.
+
+API parity with the reference's ``src/eval`` package (``src/eval/__init__.py:7-32``):
+``load_model``, ``load_model_config``, ``load_checkpoint_registry``, ``CheckpointInfo``,
+``forward_with_states``, ``compute_attention_weights``, ``ForwardResult``, ``generate``,
+``generate_text``, ``compute_perplexity``, ``load_metrics``, ``get_nearest_step``,
+``extract_series``.  One deliberate difference: the AttnRes forward here resets the partial sum
+at block boundaries exactly like the model does; the reference's analysis copy forgets that
+reset (``src/eval/forward.py:199-201`` against ``src/model/llama.py:701-703``).
+"""
+from __future__ import annotations
+
+import json
+import logging
+import math
+from dataclasses import dataclass, field
+from pathlib import Path
+from typing import Any, Optional
+
+import numpy as np
+import torch
+import torch.nn.functional as F
+
+from ..ckpt.manager import clean_state_dict, load_checkpoint_file
+from ..config import MODEL_PRESETS, ModelConfig
+from ..models.llama import KotodamaModel, route_sources
+
+logger = logging.getLogger(__name__)
+
+
+# ------------------------------------------------------------------------------ loading
+@dataclass
+class CheckpointInfo:
+    name: str
+    path: str
+    model_section: str = "proxy"
+    attn_res: bool = False
+    attn_res_boundaries: Optional[list[int]] = None
+    description: str = ""
+    extra: dict[str, Any] = field(default_factory=dict)
+
+
+def load_model_config(config_path: Optional[str | Path] = None, section: str = "proxy", **overrides: Any) -> ModelConfig:
+    """Model description from a YAML file with named sections (``model`` / ``proxy`` / ``8b`` /
+    ``intermediate``) or, without a file, from the built-in presets."""
+    kw: dict[str, Any] = {}
+    if config_path is not None and Path(config_path).exists():
+        import yaml
+        raw = yaml.safe_load(open(config_path)) or {}
+        sec = raw.get(section, raw.get("model", {}))
+        fields = ModelConfig.__dataclass_fields__
+        kw = {k: v for k, v in sec.items() if k in fields}
+    else:
+        alias = {"model": "3b", "full": "3b"}
+        kw = dict(MODEL_PRESETS[alias.get(section, section)])
+    kw.update(overrides)
+    return ModelConfig(**kw)
+
+
+def load_checkpoint_registry(path: str | Path) -> dict[str, CheckpointInfo]:
+    """``checkpoints.yaml``: ``{name: {path, model_section, attn_res, attn_res_boundaries, description}}``."""
+    import yaml
+    raw = yaml.safe_load(open(path)) or {}
+    raw = raw.get("checkpoints", raw)
+    out = {}
+    known = {"path", "model_section", "attn_res", "attn_res_boundaries", "description"}
+    for name, e in raw.items():
+        out[name] = CheckpointInfo(name=name, path=e["path"], model_section=e.get("model_section", "proxy"),
+                                   attn_res=bool(e.get("attn_res", False)),
+                                   attn_res_boundaries=e.get("attn_res_boundaries"),
+                                   description=e.get("description", ""),
+                                   extra={k: v for k, v in e.items() if k not in known})
+    return out
+
+
+def detect_attn_res(state_dict: dict[str, torch.Tensor]) -> bool:
+    return any(k.endswith("attn_res_query") or k == "final_res_query" for k in state_dict)
+
+
+def load_model(checkpoint: str | Path, config: Optional[ModelConfig] = None, device: str = "cpu",
+               dtype: Optional[torch.dtype] = None, section: str = "proxy", config_path: Optional[str] = None,
+               attn_res_boundaries: Optional[list[int]] = None) -> tuple[KotodamaModel, dict[str, Any]]:
+    """Load a checkpoint (``.pt`` / ``.pt.zst``) into a model; AttnRes is auto-detected from the keys.
+    Wrapper prefixes (``_orig_mod.``, ``module.``) are stripped, loading is non-strict."""
+    ckpt = load_checkpoint_file(Path(checkpoint), map_location="cpu")
+    sd = clean_state_dict(ckpt.get("model", ckpt))
+    if config is None:
+        config = load_model_config(config_path, section, attn_res=detect_attn_res(sd))
+        if attn_res_boundaries is not None:
+            config.attn_res_boundaries = list(attn_res_boundaries)
+        emb = sd.get("embed_tokens.weight")
+        if emb is not None:
+            config.vocab_size = emb.shape[0]
+    model = KotodamaModel(config)
+    missing, unexpected = model.load_state_dict(sd, strict=False)
+    if missing or unexpected:
+        logger.warning("load_model: %d missing, %d unexpected keys", len(missing), len(unexpected))
+    model = model.to(device)
+    if dtype is not None:
+        model = model.to(dtype)
+    meta = {k: ckpt.get(k) for k in ("step", "tokens_consumed") if isinstance(ckpt, dict)}
+    return model.eval(), meta
+
+
+# ------------------------------------------------------------------------------ forward
+@dataclass
+class ForwardResult:
+    logits: torch.Tensor
+    states: list[torch.Tensor]                    # states[0] = embeddings, states[i+1] = after layer i
+    attention: dict[int, torch.Tensor] = field(default_factory=dict)
+    route_weights: dict[str, torch.Tensor] = field(default_factory=dict)
+
+
+@torch.no_grad()
+def compute_attention_weights(layer: Any, x_normed: torch.Tensor, rope_cos: torch.Tensor, rope_sin: torch.Tensor
+                              ) -> torch.Tensor:
+    """Causal attention probabilities ``[B, heads, T, T]`` of one layer for its normalised input."""
+    q, k, _ = layer.attn.project_qkv(x_normed, rope_cos, rope_sin)
+    g = q.shape[1] // k.shape[1]
+    sc = (q.float() @ k.repeat_interleave(g, 1).float().transpose(-1, -2)) / math.sqrt(q.shape[-1])
+    T = x_normed.shape[1]
+    mask = torch.ones(T, T, dtype=torch.bool, device=x_normed.device).tril()
+    return torch.softmax(sc.masked_fill(~mask, float("-inf")), -1)
+
+
+@torch.no_grad()
+def forward_with_states(model: KotodamaModel, input_ids: torch.Tensor, attention_layers: Optional[list[int]] = None
+                        ) -> ForwardResult:
+    m, cfg = model, model.config
+    want = set(attention_layers or [])
+    x = m.embed_tokens(input_ids)
+    states, attn, routes = [x], {}, {}
+    if not cfg.attn_res:
+        for i, layer in enumerate(m.layers):
+            h = layer.attn_norm(x)
+            if i in want:
+                attn[i] = compute_attention_weights(layer, h, m.rope_cos, m.rope_sin)
+            x = x + layer.attn(h, m.rope_cos, m.rope_sin)
+            x = x + layer.ffn(layer.ffn_norm(x))
+            states.append(x)
+        xf = m.norm(x)
+    else:
+        def weights(srcs, q, norm):
+            u = torch.stack(srcs, 0).float()
+            r = torch.rsqrt(u.pow(2).mean(-1) + norm.eps)
+            return torch.softmax((u * (q * norm.weight).float()).sum(-1) * r, 0)
+        committed: list[torch.Tensor] = []
+        partial: Optional[torch.Tensor] = x
+        for i, layer in enumerate(m.layers):
+            srcs = committed + [partial]
+            routes[f"attn_{i}"] = weights(srcs, layer.attn_res_query, layer.attn_res_norm).mean(dim=(1, 2))
+            h = route_sources(srcs, layer.attn_res_query, layer.attn_res_norm.weight, layer.attn_res_norm.eps)
+            if i in m._attn_res_boundary_set:
+                committed.append(partial)
+                partial = None
+            hn = layer.attn_norm(h)
+            if i in want:
+                attn[i] = compute_attention_weights(layer, hn, m.rope_cos, m.rope_sin)
+            a = layer.attn(hn, m.rope_cos, m.rope_sin)
+            partial = a if partial is None else partial + a
+            srcs = committed + [partial]
+            routes[f"mlp_{i}"] = weights(srcs, layer.mlp_res_query, layer.mlp_res_norm).mean(dim=(1, 2))
+            h = route_sources(srcs, layer.mlp_res_query, layer.mlp_res_norm.weight, layer.mlp_res_norm.eps)
+            partial = partial + layer.ffn(layer.ffn_norm(h))
+            states.append(h)
+        srcs = committed + [partial]
+        routes["final"] = weights(srcs, m.final_res_query, m.final_res_norm).mean(dim=(1, 2))
+        xf = m.norm(route_sources(srcs, m.final_res_query, m.final_res_norm.weight, m.final_res_norm.eps))
+        states[-1] = xf
+    return ForwardResult(F.linear(xf, m.get_lm_head_weight()), states, attn, routes)
+
+
+# ------------------------------------------------------------------------------ generation
+def _top_p_filter(logits: torch.Tensor, top_p: float) -> torch.Tensor:
+    srt, idx = torch.sort(logits, descending=True)
+    probs = torch.softmax(srt, -1)
+    remove = probs.cumsum(-1) - probs > top_p
+    return torch.full_like(logits, float("-inf")).scatter(-1, idx, srt.masked_fill(remove, float("-inf")))
+
+
+@torch.no_grad()
+def generate(model: KotodamaModel, input_ids: torch.Tensor, max_new_tokens: int = 64, temperature: float = 0.8,
+             top_k: int = 50, top_p: float = 0.0, repetition_penalty: float = 1.0, eos_token_id: Optional[int] = None,
+             use_cache: bool = True) -> torch.Tensor:
+    """Batch-1 autoregressive generation with the model's own KV cache; returns prompt + new tokens."""
+    ids = input_ids.clone()
+    past = None
+    cur = ids
+    for _ in range(max_new_tokens):
+        if ids.shape[1] >= model.config.max_position_embeddings:
+            break
+        out = model(cur if use_cache else ids, use_cache=use_cache, past_kv=past)
+        past = out.get("past_kv") if use_cache else None
+        lg = out["logits"][:, -1].float()
+        if repetition_penalty != 1.0:
+            seen = ids[0].unique()
+            v = lg[0, seen]
+            lg[0, seen] = torch.where(v > 0, v / repetition_penalty, v * repetition_penalty)
+        if temperature <= 0:
+            nxt = lg.argmax(-1, keepdim=True)
+        else:
+            lg = lg / temperature
+            if top_k > 0:
+                kth = torch.topk(lg, min(top_k, lg.shape[-1])).values[..., -1:]
+                lg = lg.masked_fill(lg < kth, float("-inf"))
+            if 0 < top_p < 1:
+                lg = _top_p_filter(lg, top_p)
+            nxt = torch.multinomial(torch.softmax(lg, -1), 1)
+        ids = torch.cat([ids, nxt], 1)
+        cur = nxt
+        if eos_token_id is not None and int(nxt) == eos_token_id:
+            break
+    return ids
+
+
+def generate_text(model: KotodamaModel, tokenizer: Any, prompt: str, **kw: Any) -> str:
+    dev = next(model.parameters()).device
+    ids = torch.tensor([tokenizer.encode(prompt)], device=dev)
+    out = generate(model, ids, eos_token_id=getattr(tokenizer, "eos_token_id", None), **kw)
+    return tokenizer.decode(out[0, ids.shape[1]:].tolist(), skip_special_tokens=True)
+
+
+# ------------------------------------------------------------------------------ perplexity
+@torch.no_grad()
+def compute_perplexity(model: KotodamaModel, data_path: str | Path, seq_len: int = 2048, max_tokens: int = 1_000_000,
+                       batch_size: int = 4, device: Optional[str] = None) -> dict[str, float]:
+    """Token-level perplexity over the head of a flat uint16 token file (non-overlapping windows)."""
+    dev = torch.device(device) if device else next(model.parameters()).device
+    data = np.memmap(data_path, dtype=np.uint16, mode="r")
+    n_win = min(len(data), max_tokens) // seq_len
+    if n_win == 0:
+        raise ValueError(f"{data_path}: fewer than {seq_len} tokens")
+    nll, count = 0.0, 0
+    for s in range(0, n_win, batch_size):
+        rows = [np.asarray(data[w * seq_len:(w + 1) * seq_len]).astype(np.int64) for w in range(s, min(n_win, s + batch_size))]
+        ids = torch.from_numpy(np.stack(rows)).to(dev)
+        logits = model(ids)["logits"].float()
+        loss = F.cross_entropy(logits[:, :-1].reshape(-1, logits.shape[-1]), ids[:, 1:].reshape(-1), reduction="sum")
+        nll += float(loss)
+        count += ids[:, 1:].numel()
+    mean = nll / max(count, 1)
+    return {"loss": mean, "perplexity": math.exp(min(mean, 50)), "tokens": float(count)}
+
+
+# ------------------------------------------------------------------------------ metrics IO
+def load_metrics(path: str | Path, merge: bool = True) -> dict[int, dict[str, float]]:
+    """JSONL metrics -> ``{step: {key: value}}``; records of one step are merged, malformed lines skipped."""
+    path = Path(path)
+    if not path.exists():
+        raise FileNotFoundError(f"Metrics file not found: {path}")
+    out: dict[int, dict[str, float]] = {}
+    for line in open(path):
+        line = line.strip()
+        if not line:
+            continue
+        try:
+            rec = json.loads(line)
+        except json.JSONDecodeError:
+            continue
+        step = rec.pop("step", None)
+        if step is None:
+            continue
+        rec.pop("timestamp", None)
+        if merge and int(step) in out:
+            out[int(step)].update(rec)
+        else:
+            out[int(step)] = dict(rec)
+    return out
+
+
+def get_nearest_step(data: dict[int, dict[str, float]], target: int, tolerance: int = 500) -> Optional[int]:
+    if not data:
+        return None
+    if target in data:
+        return target
+    best = min(data, key=lambda s: abs(s - target))
+    return best if abs(best - target) <= tolerance else None
+
+
+def extract_series(data: dict[int, dict[str, float]], key: str) -> list[tuple[int, float]]:
+    """``[(step, value), ...]`` in step order for the steps that carry ``key``."""
+    return [(s, float(data[s][key])) for s in sorted(data) if key in data[s] and data[s][key] is not None]
+
+
+def extract_keys_matching(data: dict[int, dict[str, float]], prefix: str) -> list[str]:
+    return sorted({k for r in data.values() for k in r if k.startswith(prefix)})
+
+
+def load_multiple(paths: dict[str, str | Path]) -> dict[str, dict[int, dict[str, float]]]:
+    return {name: load_metrics(p) for name, p in paths.items() if Path(p).exists()}
