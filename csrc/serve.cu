@@ -119,21 +119,44 @@ paged_decode_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* 
     __syncthreads();
 #pragma unroll
     for (int g = 0; g < G; ++g) sum[g] = red[1][g][0] + red[1][g][1] + red[1][g][2] + red[1][g][3];
-    // weighted sum of V: thread d (two threads per pair when HD = 64 is handled by the bound below)
-    if (threadIdx.x < HD) {
-        float o[G];
+    // weighted sum of V: thread (c, tg) owns the 8-element chunk c of the head dimension for tokens
+    // tg, tg + NTG, ...; 16-byte loads, then the NTG partial rows are summed through shared memory
+    {
+        constexpr int NCH = HD / 8;            // chunks per row: 16 (hd 128) or 8 (hd 64)
+        constexpr int NTG = 128 / NCH;         // token groups: 8 or 16
+        const int c = threadIdx.x % NCH, tg = threadIdx.x / NCH;
+        float o[G][8];
 #pragma unroll
-        for (int g = 0; g < G; ++g) o[g] = 0.f;
-        const int d = threadIdx.x;
-        for (int t = 0; t < nt; ++t) {
+        for (int g = 0; g < G; ++g)
+#pragma unroll
+            for (int i = 0; i < 8; ++i) o[g][i] = 0.f;
+#pragma unroll 4
+        for (int t = tg; t < nt; t += NTG) {
             const int tok = t0 + t;
             const int page = page_table[(size_t)req * max_pages + tok / PAGE];
-            const float vv = __bfloat162float(v_pages[((size_t)page * PAGE + tok % PAGE) * row + (size_t)kvh * HD + d]);
+            float vf[8];
+            unpack8(ld8(v_pages + ((size_t)page * PAGE + tok % PAGE) * row + (size_t)kvh * HD + c * 8), vf);
 #pragma unroll
-            for (int g = 0; g < G; ++g) o[g] += sc[g * split_tokens + t] * vv;
+            for (int g = 0; g < G; ++g) {
+                const float pw = sc[g * split_tokens + t];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) o[g][i] += pw * vf[i];
+            }
         }
+        __syncthreads();                       // scores are dead from here: reuse their space? no: separate buffer
+        __shared__ float vred[128 / NCH][G][HD];
 #pragma unroll
-        for (int g = 0; g < G; ++g) part_o[(pbase * G + g) * HD + d] = o[g];
+        for (int g = 0; g < G; ++g)
+#pragma unroll
+            for (int i = 0; i < 8; ++i) vred[tg][g][c * 8 + i] = o[g][i];
+        __syncthreads();
+        for (int i = threadIdx.x; i < G * HD; i += blockDim.x) {
+            const int g = i / HD, d = i % HD;
+            float acc = 0.f;
+#pragma unroll
+            for (int j = 0; j < NTG; ++j) acc += vred[j][g][d];
+            part_o[(pbase * G + g) * HD + d] = acc;
+        }
     }
     if (threadIdx.x < G) {
         part_ml[(pbase * G + threadIdx.x) * 2] = mx[threadIdx.x];
@@ -241,4 +264,69 @@ __global__ void argmax_kernel(const bf16* __restrict__ logits, long long stride,
 KB_API int kb_argmax(const void* logits, long long stride, int rows, int V, long long* out, cudaStream_t st) {
     argmax_kernel<<<rows, 512, 0, st>>>((const bf16*)logits, stride, V, out);
     return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant of kb_paged_decode (declared and documented in no_alloc.h): the
+// split-KV partial results live in a fixed device array owned by this file.
+#include <stdio.h>
+
+#include <mutex>
+
+#include "no_alloc.h"
+
+static __device__ __align__(256) float g_noalloc_scratch[KB_NOALLOC_SCRATCH_FLOATS];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float* g_noalloc_ptr[kMaxDevices] = {nullptr};
+std::mutex g_noalloc_mutex;
+
+// Device address of the scratch array on the current device.  In host code the array's name is
+// only a handle for the runtime; the address a kernel can use comes from cudaGetSymbolAddress.
+float* noalloc_scratch_for_current_device() {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    if (g_noalloc_ptr[dev] == nullptr) {
+        float* p = nullptr;
+        const cudaError_t rc = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_noalloc_scratch);
+        if (rc != cudaSuccess || p == nullptr) {
+            fprintf(stderr, "kb_paged_decode_noalloc: cudaGetSymbolAddress failed on device %d: %s\n", dev,
+                    cudaGetErrorString(rc));
+            return nullptr;
+        }
+        g_noalloc_ptr[dev] = p;
+    }
+    return g_noalloc_ptr[dev];
+}
+}  // namespace
+
+KB_API int kb_paged_decode_noalloc(const void* q, long long q_stride, const void* k_pages, const void* v_pages,
+                                   const int* page_table, int max_pages, const int* ctx_lens, int B, int n_q,
+                                   int n_kv, int hd, int max_ctx, int split_tokens, float scale, void* out,
+                                   long long out_stride, cudaStream_t stream) {
+    if (B <= 0 || n_q <= 0 || n_kv <= 0 || hd <= 0 || max_ctx <= 0 || split_tokens <= 0) return 5;
+    const long long nsplit = (max_ctx + split_tokens - 1) / split_tokens;
+    const long long need_o = (long long)B * n_q * nsplit * hd;       // partial outputs
+    const long long need_ml = (long long)B * n_q * nsplit * 2;       // running max and sum per split
+    if (need_o + need_ml > (long long)KB_NOALLOC_SCRATCH_FLOATS) {
+        fprintf(stderr,
+                "kb_paged_decode_noalloc: request needs %lld floats of scratch (B=%d heads=%d splits=%lld hd=%d) "
+                "but the built-in array holds %d; use kb_paged_decode with caller workspaces, a larger "
+                "split_tokens, or a smaller batch\n",
+                need_o + need_ml, B, n_q, nsplit, hd, KB_NOALLOC_SCRATCH_FLOATS);
+        return KB_NOALLOC_TOO_LARGE;
+    }
+    float* scratch = noalloc_scratch_for_current_device();
+    if (scratch == nullptr) return KB_NOALLOC_SETUP_FAILED;
+    // part_ml starts on a 256-byte boundary after part_o
+    const long long ml_off = (need_o + 63) / 64 * 64;
+    if (ml_off + need_ml > (long long)KB_NOALLOC_SCRATCH_FLOATS) {
+        fprintf(stderr, "kb_paged_decode_noalloc: request needs %lld floats of scratch but the built-in array holds %d\n",
+                ml_off + need_ml, KB_NOALLOC_SCRATCH_FLOATS);
+        return KB_NOALLOC_TOO_LARGE;
+    }
+    return kb_paged_decode(q, q_stride, k_pages, v_pages, page_table, max_pages, ctx_lens, B, n_q, n_kv, hd, max_ctx,
+                           split_tokens, scale, scratch, scratch + ml_off, out, out_stride, stream);
 }
