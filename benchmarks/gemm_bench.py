@@ -70,8 +70,11 @@ def main() -> None:
     ap.add_argument("--tokens", type=int, default=32768)
     ap.add_argument("--model", default="3b")
     ap.add_argument("--out", default="")
+    ap.add_argument("--two-cta", type=int, default=-1, help="force the CTA-pair kernel on (1) or off (0)")
     args = ap.parse_args()
     ops = get_ops("cuda")
+    if args.two_cta >= 0:
+        ops.gemm_2cta = bool(args.two_cta)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
     if args.single:
         M, N, K = map(int, args.single[:3])

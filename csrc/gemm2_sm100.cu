@@ -1,0 +1,402 @@
+// Two-CTA variant of the persistent tcgen05 GEMM: a cluster of two CTAs (one per SM of a pair)
+// computes one 256x256 tile with `tcgen05.mma.cta_group::2` (instruction shape 256x256x16).
+// Each CTA stages its own 128 rows of A and half (128 rows) of the B tile, so the shared-memory
+// fill per SM drops from 48 KB to 32 KB per 64-deep K block, which is what limited the one-CTA
+// kernel.  No load names another CTA as a destination: every CTA fetches its own operand slices;
+// only barrier traffic crosses the pair (TMA completion bytes counted on the leader's barrier,
+// commits from the leader to both CTAs, epilogue arrivals from the peer to the leader).
+//
+// Roles per CTA (192 threads): warp 0 = TMA producer, warp 1 = TMEM allocation (+ MMA issue in
+// the leader CTA only), warps 2-5 = epilogue.  Same operand majors, batching and fused
+// alpha*acc + beta*Cin epilogue as the one-CTA kernel.
+#include <cuda.h>
+
+#include "tc.cuh"
+
+namespace {
+
+constexpr int BM = 128;            // rows per CTA (256 per pair)
+constexpr int BN = 256;            // tile columns (128 staged per CTA)
+constexpr int BNH = 128;
+constexpr int BK = 64, STAGES = 6;
+constexpr int A_STAGE = BM * BK * 2, B_STAGE = BNH * BK * 2;
+constexpr int SMEM_BYTES = STAGES * (A_STAGE + B_STAGE) + 1024 + 256;
+constexpr int GROUP_M = 8;
+
+struct Gemm2Params {
+    int M, N, K, batch;
+    int a_mn, b_mn, a_fmt, b_fmt, out_type;
+    float alpha, beta;
+    void* C;
+    const void* Cin;
+    long long ldc, c_batch_stride, ldcin, cin_batch_stride;
+    int* status;
+};
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t mapa(uint32_t smem_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tma_load_3d_pair(void* dst, const CUtensorMap* m, uint32_t bar_cluster_addr, int x,
+                                                 int y, int z) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_cluster_addr), "r"(x), "r"(y), "r"(z)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_alloc2(uint32_t* dst_smem, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)),
+                 "r"(ncols)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish2() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc2(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void mma2_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                         uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// Arrive on a barrier (cluster address) once all MMAs issued so far by this thread are done.
+__device__ __forceinline__ void commit2(uint32_t bar_cluster_addr) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr)
+                 : "memory");
+}
+
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& b, int& tm, int& tn) {
+    const int per_batch = tiles_m * tiles_n;
+    b = tile / per_batch;
+    int t = tile % per_batch;
+    const int group = GROUP_M * tiles_n;
+    const int g = t / group;
+    const int first_m = g * GROUP_M;
+    const int gm = min(GROUP_M, tiles_m - first_m);
+    t -= g * group;
+    tm = first_m + t % gm;
+    tn = t / gm;
+}
+
+template <typename T>
+__device__ __forceinline__ float h2f(T x);
+template <> __device__ __forceinline__ float h2f<__nv_bfloat16>(__nv_bfloat16 x) { return __bfloat162float(x); }
+template <> __device__ __forceinline__ float h2f<__half>(__half x) { return __half2float(x); }
+template <typename T>
+__device__ __forceinline__ T f2h(float x);
+template <> __device__ __forceinline__ __nv_bfloat16 f2h<__nv_bfloat16>(float x) { return __float2bfloat16(x); }
+template <> __device__ __forceinline__ __half f2h<__half>(float x) { return __float2half(x); }
+
+template <typename T>
+__device__ __forceinline__ void store32_16(T* dst, const T* cin, const uint32_t* acc, float alpha, float beta,
+                                           int ncols, bool vec_ok) {
+    if (ncols == 32 && vec_ok) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            float v[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = alpha * __uint_as_float(acc[8 * j + i]);
+            if (cin) {
+                const uint4 raw = *reinterpret_cast<const uint4*>(cin + 8 * j);
+                const T* c = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] += beta * h2f<T>(c[i]);
+            }
+            uint4 o;
+            T* op = reinterpret_cast<T*>(&o);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) op[i] = f2h<T>(v[i]);
+            *reinterpret_cast<uint4*>(dst + 8 * j) = o;
+        }
+    } else {
+        for (int j = 0; j < ncols; ++j) {
+            float v = alpha * __uint_as_float(acc[j]);
+            if (cin) v += beta * h2f<T>(cin[j]);
+            dst[j] = f2h<T>(v);
+        }
+    }
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
+gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                         const Gemm2Params p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* sA = smem;
+    uint8_t* sB = smem + STAGES * A_STAGE;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * (A_STAGE + B_STAGE));
+    uint64_t* full = bars;                          // [STAGES] in the leader: both CTAs' TMA bytes
+    uint64_t* empty = bars + STAGES;                // [STAGES] per CTA: leader's commit
+    uint64_t* acc_full = bars + 2 * STAGES;         // [2] per CTA: leader's commit
+    uint64_t* acc_empty = bars + 2 * STAGES + 2;    // [2] in the leader: 8 epilogue warps
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const bool leader = rank == 0;
+    const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+    const int tiles_m = (p.M + 2 * BM - 1) / (2 * BM), tiles_n = (p.N + BN - 1) / BN;
+    const int num_tiles = tiles_m * tiles_n * p.batch;
+    const int kblocks = (p.K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            tc::mbar_init(&full[s], 1);
+            tc::mbar_init(&empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            tc::mbar_init(&acc_full[b], 1);
+            tc::mbar_init(&acc_empty[b], 8);
+        }
+        *abort_flag = 0;
+        tc::fence_barrier_init();
+    }
+    if (warp == 1) {
+        tmem_alloc2(tmem_slot, 512);
+        tmem_relinquish2();
+    }
+    tc::tc_fence_before();
+    __syncthreads();
+    cluster_sync();                                  // peer barriers are initialised before anyone signals them
+    tc::tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            tc::prefetch_tmap(&tmA);
+            tc::prefetch_tmap(&tmB);
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = pair; tile < num_tiles && ok; tile += npairs) {
+                int b, tm, tn;
+                tile_coords(tile, tiles_m, tiles_n, b, tm, tn);
+                const int m0 = tm * 2 * BM + (int)rank * BM, n0 = tn * BN + (int)rank * BNH;
+                for (int kb = 0; kb < kblocks; ++kb) {
+                    if (!tc::mbar_wait(&empty[stage], phase ^ 1, abort_flag)) {
+                        atomicMax(p.status, (int)KB_TIMEOUT_TMA);
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t full_leader = mapa(smem_u32(&full[stage]), 0);
+                    if (leader) tc::mbar_expect_tx(&full[stage], 2 * (A_STAGE + B_STAGE));
+                    uint8_t* a_dst = sA + stage * A_STAGE;
+                    uint8_t* b_dst = sB + stage * B_STAGE;
+                    if (p.a_mn) {
+#pragma unroll
+                        for (int c = 0; c < BM / 64; ++c)
+                            tma_load_3d_pair(a_dst + c * (64 * BK * 2), &tmA, full_leader, m0 + c * 64, kb * BK, b);
+                    } else {
+                        tma_load_3d_pair(a_dst, &tmA, full_leader, kb * BK, m0, b);
+                    }
+                    if (p.b_mn) {
+#pragma unroll
+                        for (int c = 0; c < BNH / 64; ++c)
+                            tma_load_3d_pair(b_dst + c * (64 * BK * 2), &tmB, full_leader, n0 + c * 64, kb * BK, b);
+                    } else {
+                        tma_load_3d_pair(b_dst, &tmB, full_leader, kb * BK, n0, b);
+                    }
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && leader) {
+            const uint32_t idesc = tc::instr_desc_f16(2 * BM, BN, p.a_fmt, p.b_fmt, p.a_mn, p.b_mn);
+            int stage = 0;
+            uint32_t phase = 0;
+            int it = 0;
+            bool ok = true;
+            for (int tile = pair; tile < num_tiles && ok; tile += npairs, ++it) {
+                const int buf = it & 1;
+                const uint32_t acc_phase = (it >> 1) & 1;
+                if (!tc::mbar_wait(&acc_empty[buf], acc_phase ^ 1, abort_flag)) {
+                    atomicMax(p.status, (int)KB_TIMEOUT_MMA);
+                    ok = false;
+                    break;
+                }
+                tc::tc_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * BN;
+                for (int kb = 0; kb < kblocks; ++kb) {
+                    if (!tc::mbar_wait(&full[stage], phase, abort_flag)) {
+                        atomicMax(p.status, (int)KB_TIMEOUT_MMA);
+                        ok = false;
+                        break;
+                    }
+                    tc::tc_fence_after();
+                    const uint32_t a_addr = smem_u32(sA + stage * A_STAGE);
+                    const uint32_t b_addr = smem_u32(sB + stage * B_STAGE);
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k) {
+                        const uint64_t ad = p.a_mn ? tc::smem_desc_sw128(a_addr + k * 2048, 64 * BK * 2, 1024)
+                                                   : tc::smem_desc_sw128(a_addr + k * 32, 16, 1024);
+                        const uint64_t bd = p.b_mn ? tc::smem_desc_sw128(b_addr + k * 2048, 64 * BK * 2, 1024)
+                                                   : tc::smem_desc_sw128(b_addr + k * 32, 16, 1024);
+                        mma2_f16(d_tmem, ad, bd, idesc, (kb | k) != 0);
+                    }
+                    // the stage is reusable in both CTAs once these MMAs have read it
+                    commit2(mapa(smem_u32(&empty[stage]), 0));
+                    commit2(mapa(smem_u32(&empty[stage]), 1));
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+                if (ok) {
+                    commit2(mapa(smem_u32(&acc_full[buf]), 0));
+                    commit2(mapa(smem_u32(&acc_full[buf]), 1));
+                }
+            }
+        }
+    } else {
+        const int quarter = warp & 3;
+        int it = 0;
+        bool ok = true;
+        for (int tile = pair; tile < num_tiles && ok; tile += npairs, ++it) {
+            int b, tm, tn;
+            tile_coords(tile, tiles_m, tiles_n, b, tm, tn);
+            const int buf = it & 1;
+            const uint32_t acc_phase = (it >> 1) & 1;
+            if (!tc::mbar_wait(&acc_full[buf], acc_phase, abort_flag)) {
+                if (lane == 0) atomicMax(p.status, (int)KB_TIMEOUT_EPI);
+                ok = false;
+                break;
+            }
+            tc::tc_fence_after();
+            const int row = tm * 2 * BM + (int)rank * BM + quarter * 32 + lane;
+            const uint32_t taddr = tmem_base + buf * BN + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t acc[32];
+                tc::tmem_ld32(taddr + c0, acc);
+                tc::tmem_ld_wait();
+                const int col = tn * BN + c0;
+                const int ncols = min(32, p.N - col);
+                if (row < p.M && ncols > 0) {
+                    const long long off = (long long)b * p.c_batch_stride + (long long)row * p.ldc + col;
+                    const long long offin = (long long)b * p.cin_batch_stride + (long long)row * p.ldcin + col;
+                    if (p.out_type == 2) {
+                        float* dst = reinterpret_cast<float*>(p.C) + off;
+                        const float* cin = p.Cin ? reinterpret_cast<const float*>(p.Cin) + offin : nullptr;
+                        for (int j = 0; j < ncols; ++j) {
+                            float v = p.alpha * __uint_as_float(acc[j]);
+                            if (cin) v += p.beta * cin[j];
+                            dst[j] = v;
+                        }
+                    } else {
+                        const bool vec = ((p.ldc | p.ldcin | col) & 7) == 0;
+                        if (p.out_type == 1) {
+                            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + off;
+                            const __nv_bfloat16* cin =
+                                p.Cin ? reinterpret_cast<const __nv_bfloat16*>(p.Cin) + offin : nullptr;
+                            store32_16<__nv_bfloat16>(dst, cin, acc, p.alpha, p.beta, ncols, vec);
+                        } else {
+                            __half* dst = reinterpret_cast<__half*>(p.C) + off;
+                            const __half* cin = p.Cin ? reinterpret_cast<const __half*>(p.Cin) + offin : nullptr;
+                            store32_16<__half>(dst, cin, acc, p.alpha, p.beta, ncols, vec);
+                        }
+                    }
+                }
+            }
+            tc::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(mapa(smem_u32(&acc_empty[buf]), 0));
+        }
+    }
+    tc::tc_fence_before();
+    __syncthreads();
+    cluster_sync();                                  // no remote arrival may target a CTA that has left
+    if (warp == 1) {
+        tc::tc_fence_after();
+        tmem_dealloc2(tmem_base, 512);
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode2() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+    return fn;
+}
+
+int make_tmap2(CUtensorMap* m, const void* base, int fmt, long long cols, long long rows, long long ld,
+               long long batch, long long batch_stride, int box_cols, int box_rows) {
+    EncodeTiledFn enc = get_encode2();
+    if (!enc) return 100;
+    cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)batch};
+    cuuint64_t strides[2] = {(cuuint64_t)ld * 2, (cuuint64_t)(batch > 1 ? batch_stride : rows * ld) * 2};
+    cuuint32_t box[3] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    const CUresult r = enc(m, fmt == 1 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
+                           const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : 200 + (int)r;
+}
+
+}  // namespace
+
+// Same contract as kb_gemm (no split-K); launched as clusters of two CTAs.
+KB_API int kb_gemm_2cta(const void* A, const void* B, void* C, const void* Cin, int M, int N, int K, int batch,
+                        long long lda, long long ldb, long long ldc, long long ldcin, long long a_bs, long long b_bs,
+                        long long c_bs, long long cin_bs, int a_mn, int b_mn, int a_fmt, int b_fmt, int out_type,
+                        float alpha, float beta, int* status, int max_ctas, cudaStream_t st) {
+    if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return 5;
+    if ((lda & 7) || (ldb & 7) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15)) return 6;
+    if (batch > 1 && ((a_bs & 7) || (b_bs & 7))) return 6;
+    static bool attr_set = false;
+    if (!attr_set) {
+        if (cudaFuncSetAttribute(gemm_tcgen05_2cta_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) !=
+            cudaSuccess)
+            return 7;
+        attr_set = true;
+    }
+    CUtensorMap tmA, tmB;
+    int r;
+    if (a_mn) r = make_tmap2(&tmA, A, a_fmt, M, K, lda, batch, a_bs, 64, BK);
+    else r = make_tmap2(&tmA, A, a_fmt, K, M, lda, batch, a_bs, BK, BM);
+    if (r) return r;
+    if (b_mn) r = make_tmap2(&tmB, B, b_fmt, N, K, ldb, batch, b_bs, 64, BK);
+    else r = make_tmap2(&tmB, B, b_fmt, K, N, ldb, batch, b_bs, BK, BNH);
+    if (r) return r;
+    Gemm2Params p;
+    p.M = M; p.N = N; p.K = K; p.batch = batch;
+    p.a_mn = a_mn; p.b_mn = b_mn; p.a_fmt = a_fmt; p.b_fmt = b_fmt; p.out_type = out_type;
+    p.alpha = alpha; p.beta = beta; p.C = C; p.Cin = Cin;
+    p.ldc = ldc; p.c_batch_stride = c_bs; p.ldcin = ldcin; p.cin_batch_stride = cin_bs;
+    p.status = status;
+    int sms = 0, dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (max_ctas > 0 && max_ctas < sms) sms = max_ctas;
+    const int tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN) * batch;
+    int pairs = sms / 2;
+    if (tiles < pairs) pairs = tiles;
+    gemm_tcgen05_2cta_kernel<<<2 * pairs, 192, SMEM_BYTES, st>>>(tmA, tmB, p);
+    return 0;
+}

@@ -51,6 +51,7 @@ class CudaOps(TorchOps):
         self._status: dict[int, torch.Tensor] = {}
         self.gemm_max_ctas = 0
         self.split_k_small_m = True
+        self.gemm_2cta = os.environ.get("KOTODAMA_GEMM_2CTA", "1") == "1"   # CTA-pair kernel for large products
         for name in ("kb_route_bwd_grid", "kb_qknorm_grid_warps", "kb_route_pipe_grid"):
             getattr(self.lib, name).restype = _I
 
@@ -112,6 +113,17 @@ class CudaOps(TorchOps):
             self._rc(rc, "kb_gemm(split-k)")
             self._rc(self.lib.kb_f32_to_bf16_add(_p(ws), _p(cin), _F(beta), _p(out), _LL(M * N), _st()),
                      "kb_f32_to_bf16_add")
+            return out
+        if self.gemm_2cta and M >= 256 and N >= 256:
+            # large products: CTA pairs (256x256 tiles, tcgen05 cta_group::2)
+            rc = self.lib.kb_gemm_2cta(_p(a), _p(b), _p(out), _p(cin), _I(M), _I(N), _I(K), _I(batch),
+                                       _LL(a.stride(-2)), _LL(b.stride(-2)), _LL(out.stride(-2)),
+                                       _LL(cin.stride(-2) if cin is not None else 0),
+                                       _LL(bs(a)), _LL(bs(b)), _LL(bs(out)), _LL(bs(cin) if cin is not None else 0),
+                                       _I(int(a_mn)), _I(int(b_mn)), _I(_FMT[a.dtype]), _I(_FMT[b.dtype]),
+                                       _I(_OUT[out.dtype]), _F(alpha), _F(beta), _p(self.status(a.device)),
+                                       _I(self.gemm_max_ctas), _st())
+            self._rc(rc, "kb_gemm_2cta")
             return out
         rc = self.lib.kb_gemm(_p(a), _p(b), _p(out), _p(cin), _I(M), _I(N), _I(K), _I(batch),
                               _LL(a.stride(-2)), _LL(b.stride(-2)), _LL(out.stride(-2)),

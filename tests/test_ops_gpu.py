@@ -253,3 +253,27 @@ def test_gemm_split_k_small_m(ops, M, N, K):
     assert rel_err(ops.gemm_nt(a, b), ref) < 1e-2
     assert rel_err(ops.gemm_nt(a, b, residual=r), ref + r.float()) < 1e-2
     ops.check_status()
+
+
+@pytest.mark.parametrize("mode,M,N,K", [("nt", 512, 512, 256), ("nt", 1024, 768, 3072), ("nn", 512, 1024, 320),
+                                        ("tn", 768, 512, 1024), ("nt", 300, 520, 200)])
+def test_gemm_two_cta(ops, mode, M, N, K):
+    prev = ops.gemm_2cta
+    ops.gemm_2cta = True
+    try:
+        if mode == "nt":
+            a, b = bf(M, K, seed=1), bf(N, K, seed=2)
+            c, ref = ops.gemm_nt(a, b), a.float() @ b.float().t()
+            r = bf(M, N, seed=3)
+            c2 = ops.gemm_nt(a, b, residual=r)
+            assert rel_err(c2, ref + r.float()) < 1e-2
+        elif mode == "nn":
+            a, b = bf(M, K, seed=1), bf(K, N, seed=2)
+            c, ref = ops.gemm_nn(a, b), a.float() @ b.float()
+        else:
+            a, b = bf(K, M, seed=1), bf(K, N, seed=2)
+            c, ref = ops.gemm_tn(a, b), a.float().t() @ b.float()
+        ops.check_status()
+        assert rel_err(c, ref) < 1e-2, rel_err(c, ref)
+    finally:
+        ops.gemm_2cta = prev
