@@ -183,28 +183,16 @@ def run_native(args, rank, world, local):
                     "comm": type(comm).__name__})
 
 
-def run_reference(args, rank, world, local):
-    """The unmodified reference (baseline/_ref): its model, its hybrid optimizer, stock DDP."""
-    import importlib
-    ref_dir = os.path.join(ROOT, "baseline")
-    if not os.path.isdir(os.path.join(ref_dir, "_ref", "model")):
-        return {"unavailable": "baseline/_ref is not installed"}
-    sys.path.insert(0, ref_dir)
-    pkg = importlib.import_module("_ref")
-    sys.modules["src"] = pkg            # the reference imports itself as ``src.*``
-    llama = importlib.import_module("src.model.llama")
-    muon = importlib.import_module("src.training.muon")
+def _reference_attempt(args, rank, world, local, llama, muon, mb, ga, compile_model):
+    """One try at the reference's step with micro-batch ``mb`` x ``ga`` accumulation steps."""
     from kotodama_b200.config import MODEL_PRESETS
-    kw = dict(MODEL_PRESETS[args.model])
     notes = {}
-    cfg = llama.LuxiaModelConfig(**kw, qk_norm=True, use_liger=True, attn_impl="auto", attn_res=True,
-                                 attn_res_n_blocks=args.attn_res_blocks, activation_checkpointing=True)
+    cfg = llama.LuxiaModelConfig(**dict(MODEL_PRESETS[args.model]), qk_norm=True, use_liger=True, attn_impl="auto",
+                                 attn_res=True, attn_res_n_blocks=args.attn_res_blocks, activation_checkpointing=True)
     torch.manual_seed(1234)
     model = llama.LuxiaBaseModel(cfg).to(device=f"cuda:{local}", dtype=torch.bfloat16)
     torch.set_float32_matmul_precision("high")
-    run_model = model
-    if args.ref_compile:
-        run_model = torch.compile(model)
+    run_model = torch.compile(model) if compile_model else model
     if world > 1:
         from torch.nn.parallel import DistributedDataParallel as DDP
         run_model = DDP(run_model, device_ids=[local], gradient_as_bucket_view=True)
@@ -212,31 +200,36 @@ def run_reference(args, rank, world, local):
     K, W = args.steps, args.warmup
     dev_batches = [b.cuda() for b in token_batches(W + K, args.micro_batch, args.seq, cfg.vocab_size, 42 + rank, False)]
     host_batches = token_batches(K, args.micro_batch, args.seq, cfg.vocab_size, 4242 + rank, True)
+    from contextlib import nullcontext
 
     def step(ids):
-        with torch.autocast("cuda", dtype=torch.bfloat16):
-            out = run_model(ids, labels=ids)
-        out["loss"].backward()
+        total = None
+        for j, chunk in enumerate(ids.split(mb, dim=0)):
+            sync = nullcontext() if (j == ga - 1 or not hasattr(run_model, "no_sync")) else run_model.no_sync()
+            with sync:
+                with torch.autocast("cuda", dtype=torch.bfloat16):
+                    out = run_model(chunk, labels=chunk)
+                (out["loss"] / ga).backward()
+            total = out["loss"].detach() if total is None else total + out["loss"].detach()
         torch.nn.utils.clip_grad_norm_(model.parameters(), 1.0)
         mopt.step(); aopt.step()
         mopt.zero_grad(set_to_none=True); aopt.zero_grad(set_to_none=True)
-        return out["loss"].detach()
+        return total / ga
 
     run_model.train()
     try:
         step(dev_batches[0])
+    except torch.cuda.OutOfMemoryError:
+        raise
     except Exception as e:  # the Triton routing kernel needs a power-of-two hidden size
-        msg = f"{type(e).__name__}: {str(e)[:160]}"
-        if not getattr(llama, "_TRITON_ATTN_RES_AVAILABLE", False) or "out of memory" in msg.lower():
-            return {"unavailable": "reference step failed: " + msg.replace("\n", " ")}
-        notes["attnres_path"] = "reference PyTorch routing (its Triton kernel failed: " + msg.replace("\n", " ")[:100] + ")"
+        msg = f"{type(e).__name__}: {str(e)[:160]}".replace("\n", " ")
+        if not getattr(llama, "_TRITON_ATTN_RES_AVAILABLE", False):
+            raise RuntimeError("reference step failed: " + msg)
+        notes["attnres_path"] = "reference PyTorch routing (its Triton kernel failed: " + msg[:100] + ")"
         llama._TRITON_ATTN_RES_AVAILABLE = False
         mopt.zero_grad(set_to_none=True); aopt.zero_grad(set_to_none=True)
         torch.cuda.empty_cache()
-        try:
-            step(dev_batches[0])
-        except Exception as e2:
-            return {"unavailable": "reference step failed: " + f"{type(e2).__name__}: {str(e2)[:160]}".replace("\n", " ")}
+        step(dev_batches[0])
     for i in range(1, W):
         step(dev_batches[i])
     sampler = ClockSampler(local)
@@ -258,11 +251,93 @@ def run_reference(args, rank, world, local):
     sync_all(world)
     e2e_s = max_over_ranks(time.perf_counter() - t0, world)
     clocks = sampler.stop() if rank == 0 else {}
-    notes.update(compile=bool(args.ref_compile), liger=bool(llama._LIGER_AVAILABLE), fa2=bool(llama._FA2_AVAILABLE),
-                 triton_attnres=bool(llama._TRITON_ATTN_RES_AVAILABLE))
+    notes.update(compile=bool(compile_model), liger=bool(llama._LIGER_AVAILABLE), fa2=bool(llama._FA2_AVAILABLE),
+                 triton_attnres=bool(llama._TRITON_ATTN_RES_AVAILABLE), reference_micro_batch=mb,
+                 reference_grad_accum=ga)
     return dict(dev_ms=dev_ms, e2e_s=e2e_s, tokens=K * args.micro_batch * args.seq * world, launches=None,
                 clocks=clocks, loss=last, mem_gb=torch.cuda.max_memory_allocated() / 1e9,
                 flops_per_token=None, extra=notes)
+
+
+def run_reference(args, rank, world, local):
+    """The unmodified reference (baseline/_ref): its model, its hybrid optimizer, stock DDP, driven the
+    way its training loop drives them.  The optimizer step always covers ``--micro-batch`` sequences
+    per GPU; when those do not fit in memory as one micro-batch (the reference re-stacks its AttnRes
+    sources at every routing call) they are split into accumulation steps, which the result records."""
+    import gc
+    import importlib
+    ref_dir = os.path.join(ROOT, "baseline")
+    if not os.path.isdir(os.path.join(ref_dir, "_ref", "model")):
+        return {"unavailable": "baseline/_ref is not installed"}
+    sys.path.insert(0, ref_dir)
+    pkg = importlib.import_module("_ref")
+    sys.modules["src"] = pkg            # the reference imports itself as ``src.*``
+    llama = importlib.import_module("src.model.llama")
+    muon = importlib.import_module("src.training.muon")
+    mb, ga = args.micro_batch, 1
+    compile_model = bool(args.ref_compile)
+    last_err = "unknown"
+    # Memory probe without any collective: the largest micro-batch (halving from --micro-batch) whose
+    # forward+backward fits; ranks then agree on the smallest, so an out-of-memory error can never
+    # leave them at different points of a collective sequence.
+    from kotodama_b200.config import MODEL_PRESETS
+    pcfg = llama.LuxiaModelConfig(**dict(MODEL_PRESETS[args.model]), qk_norm=True, use_liger=True, attn_impl="auto",
+                                  attn_res=True, attn_res_n_blocks=args.attn_res_blocks, activation_checkpointing=True)
+    probe = llama.LuxiaBaseModel(pcfg).to(device=f"cuda:{local}", dtype=torch.bfloat16).train()
+    reserve = torch.empty(int(14e9), dtype=torch.uint8, device=f"cuda:{local}")   # optimizer state + NS workspace
+    while mb >= 1:
+        try:
+            ids = torch.randint(0, pcfg.vocab_size, (mb, args.seq), device=f"cuda:{local}")
+            try:
+                with torch.autocast("cuda", dtype=torch.bfloat16):
+                    out = probe(ids, labels=ids)
+                out["loss"].backward()
+            except torch.cuda.OutOfMemoryError:
+                raise
+            except Exception:       # noqa: BLE001 - the Triton routing kernel rejects non-power-of-two widths
+                llama._TRITON_ATTN_RES_AVAILABLE = False
+                probe.zero_grad(set_to_none=True)
+                with torch.autocast("cuda", dtype=torch.bfloat16):
+                    out = probe(ids, labels=ids)
+                out["loss"].backward()
+            torch.cuda.synchronize()
+            break
+        except torch.cuda.OutOfMemoryError:
+            out = None
+            probe.zero_grad(set_to_none=True)
+            gc.collect()
+            torch.cuda.empty_cache()
+            mb, ga = mb // 2, ga * 2
+    del probe, reserve
+    out = None
+    gc.collect()
+    torch.cuda.empty_cache()
+    torch.cuda.reset_peak_memory_stats()
+    if mb < 1:
+        return {"unavailable": "reference ran out of device memory even at micro-batch 1"}
+    if world > 1:
+        t = torch.tensor([mb], device=f"cuda:{local}")
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        mb = int(t.item())
+        ga = args.micro_batch // mb
+    while mb >= 1:
+        try:
+            return _reference_attempt(args, rank, world, local, llama, muon, mb, ga, compile_model)
+        except torch.cuda.OutOfMemoryError as e:
+            last_err = "out of device memory at micro-batch %d: %s" % (mb, str(e)[:80].replace("\n", " "))
+        except Exception as e:      # noqa: BLE001 - report instead of crashing the driver's run
+            last_err = f"{type(e).__name__}: {str(e)[:160]}".replace("\n", " ")
+            if compile_model:
+                compile_model = False       # compiled graph failed: the eager path is still the stock code
+                continue
+            return {"unavailable": "reference step failed: " + last_err}
+        gc.collect()
+        torch.cuda.empty_cache()
+        torch.cuda.reset_peak_memory_stats()
+        if world > 1:
+            return {"unavailable": "reference ran " + last_err}     # ranks must not diverge in geometry
+        mb, ga = mb // 2, ga * 2
+    return {"unavailable": "reference ran " + last_err}
 
 
 def main() -> None:
