@@ -887,6 +887,36 @@ KB_API int kb_axpby_half(void* y, const void* x, long long n, float a, float b, 
     return 0;
 }
 
+// Mirror the upper triangle of square 16-bit matrices into the lower one: A[i][j] = A[j][i], i > j.
+// 64x64 tiles; only tiles on or below the diagonal do work.  Batched with a fixed stride.
+__global__ void mirror_upper16_kernel(uint16_t* __restrict__ a, int R, long long ld, long long batch_stride) {
+    __shared__ uint16_t tile[64][66];
+    const int ti = blockIdx.y, tj = blockIdx.x;      // destination tile (rows ti, cols tj), tj <= ti
+    if (tj > ti) return;
+    uint16_t* base = a + (long long)blockIdx.z * batch_stride;
+    // source tile is (tj, ti): rows tj*64.., cols ti*64..
+    for (int j = threadIdx.y; j < 64; j += blockDim.y) {
+        const int r = tj * 64 + j;
+        for (int i = threadIdx.x; i < 64; i += blockDim.x) {
+            const int c = ti * 64 + i;
+            tile[j][i] = (r < R && c < R) ? base[(long long)r * ld + c] : (uint16_t)0;
+        }
+    }
+    __syncthreads();
+    for (int j = threadIdx.y; j < 64; j += blockDim.y) {
+        const int r = ti * 64 + j;
+        for (int i = threadIdx.x; i < 64; i += blockDim.x) {
+            const int c = tj * 64 + i;
+            if (r < R && c < R && r > c) base[(long long)r * ld + c] = tile[i][j];
+        }
+    }
+}
+KB_API int kb_mirror_upper16(void* a, int R, long long ld, int batch, long long batch_stride, cudaStream_t st) {
+    dim3 grid((R + 63) / 64, (R + 63) / 64, batch), block(32, 8);
+    mirror_upper16_kernel<<<grid, block, 0, st>>>((uint16_t*)a, R, ld, batch_stride);
+    return 0;
+}
+
 // dst = bf16(src + beta * addend)  (addend optional): finishes a split-K GEMM.
 __global__ void f32_to_bf16_add_kernel(const float* __restrict__ src, const bf16* __restrict__ addend, float beta,
                                        bf16* __restrict__ dst, long long n) {

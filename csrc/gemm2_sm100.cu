@@ -31,6 +31,7 @@ struct Gemm2Params {
     const void* Cin;
     long long ldc, c_batch_stride, ldcin, cin_batch_stride;
     int* status;
+    int sym_upper;             // square symmetric result: tiles strictly below the diagonal are skipped
 };
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -190,6 +191,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
             for (int tile = pair; tile < num_tiles && ok; tile += npairs) {
                 int b, tm, tn;
                 tile_coords(tile, tiles_m, tiles_n, b, tm, tn);
+                if (p.sym_upper && tn * BN + BN <= tm * 2 * BM) continue;
                 const int m0 = tm * 2 * BM + (int)rank * BM, n0 = tn * BN + (int)rank * BNH;
                 for (int kb = 0; kb < kblocks; ++kb) {
                     if (!tc::mbar_wait(&empty[stage], phase ^ 1, abort_flag)) {
@@ -226,9 +228,15 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
             uint32_t phase = 0;
             int it = 0;
             bool ok = true;
-            for (int tile = pair; tile < num_tiles && ok; tile += npairs, ++it) {
+            for (int tile = pair; tile < num_tiles && ok; tile += npairs) {
+                if (p.sym_upper) {
+                    int b_, tm_, tn_;
+                    tile_coords(tile, tiles_m, tiles_n, b_, tm_, tn_);
+                    if (tn_ * BN + BN <= tm_ * 2 * BM) continue;
+                }
                 const int buf = it & 1;
                 const uint32_t acc_phase = (it >> 1) & 1;
+                ++it;
                 if (!tc::mbar_wait(&acc_empty[buf], acc_phase ^ 1, abort_flag)) {
                     atomicMax(p.status, (int)KB_TIMEOUT_MMA);
                     ok = false;
@@ -268,11 +276,13 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         const int quarter = warp & 3;
         int it = 0;
         bool ok = true;
-        for (int tile = pair; tile < num_tiles && ok; tile += npairs, ++it) {
+        for (int tile = pair; tile < num_tiles && ok; tile += npairs) {
             int b, tm, tn;
             tile_coords(tile, tiles_m, tiles_n, b, tm, tn);
+            if (p.sym_upper && tn * BN + BN <= tm * 2 * BM) continue;
             const int buf = it & 1;
             const uint32_t acc_phase = (it >> 1) & 1;
+            ++it;
             if (!tc::mbar_wait(&acc_full[buf], acc_phase, abort_flag)) {
                 if (lane == 0) atomicMax(p.status, (int)KB_TIMEOUT_EPI);
                 ok = false;
@@ -365,8 +375,9 @@ int make_tmap2(CUtensorMap* m, const void* base, int fmt, long long cols, long l
 KB_API int kb_gemm_2cta(const void* A, const void* B, void* C, const void* Cin, int M, int N, int K, int batch,
                         long long lda, long long ldb, long long ldc, long long ldcin, long long a_bs, long long b_bs,
                         long long c_bs, long long cin_bs, int a_mn, int b_mn, int a_fmt, int b_fmt, int out_type,
-                        float alpha, float beta, int* status, int max_ctas, cudaStream_t st) {
+                        float alpha, float beta, int* status, int max_ctas, int sym_upper, cudaStream_t st) {
     if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return 5;
+    if (sym_upper && M != N) return 5;
     if ((lda & 7) || (ldb & 7) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15)) return 6;
     if (batch > 1 && ((a_bs & 7) || (b_bs & 7))) return 6;
     static bool attr_set = false;
@@ -390,6 +401,7 @@ KB_API int kb_gemm_2cta(const void* A, const void* B, void* C, const void* Cin, 
     p.alpha = alpha; p.beta = beta; p.C = C; p.Cin = Cin;
     p.ldc = ldc; p.c_batch_stride = c_bs; p.ldcin = ldcin; p.cin_batch_stride = cin_bs;
     p.status = status;
+    p.sym_upper = sym_upper;
     int sms = 0, dev = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);

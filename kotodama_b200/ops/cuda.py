@@ -78,7 +78,8 @@ class CudaOps(TorchOps):
     # ------------------------------------------------------------------ GEMM
     def _gemm(self, a: torch.Tensor, b: torch.Tensor, M: int, N: int, K: int, a_mn: bool, b_mn: bool,
               out: Optional[torch.Tensor] = None, cin: Optional[torch.Tensor] = None, alpha: float = 1.0,
-              beta: float = 0.0, out_dtype: Optional[torch.dtype] = None, batch: int = 1) -> torch.Tensor:
+              beta: float = 0.0, out_dtype: Optional[torch.dtype] = None, batch: int = 1,
+              sym_upper: bool = False) -> torch.Tensor:
         out_dtype = out_dtype or (out.dtype if out is not None else a.dtype)
         lead = (batch,) if batch > 1 else ()
         if out is None:
@@ -122,8 +123,11 @@ class CudaOps(TorchOps):
                                        _LL(bs(a)), _LL(bs(b)), _LL(bs(out)), _LL(bs(cin) if cin is not None else 0),
                                        _I(int(a_mn)), _I(int(b_mn)), _I(_FMT[a.dtype]), _I(_FMT[b.dtype]),
                                        _I(_OUT[out.dtype]), _F(alpha), _F(beta), _p(self.status(a.device)),
-                                       _I(self.gemm_max_ctas), _st())
+                                       _I(self.gemm_max_ctas), _I(int(sym_upper)), _st())
             self._rc(rc, "kb_gemm_2cta")
+            if sym_upper:       # only tiles on/above the diagonal were computed: mirror them down
+                self._rc(self.lib.kb_mirror_upper16(_p(out), _I(M), _LL(out.stride(-2)), _I(batch), _LL(bs(out)),
+                                                    _st()), "kb_mirror_upper16")
             return out
         rc = self.lib.kb_gemm(_p(a), _p(b), _p(out), _p(cin), _I(M), _I(N), _I(K), _I(batch),
                               _LL(a.stride(-2)), _LL(b.stride(-2)), _LL(out.stride(-2)),
@@ -325,10 +329,14 @@ class CudaOps(TorchOps):
         return x
 
     def ns_iteration(self, x, a, b, c):
+        """``A = X X^T``, ``B = bA + cA^2``, ``X' = aX + BX``: three tcgen05 GEMMs with the polynomial
+        terms fused into their epilogues.  ``A`` and ``A^2`` are symmetric, so only the tiles on and
+        above the diagonal are computed and then mirrored."""
         R, C = x.shape[-2], x.shape[-1]
         batch = x.shape[0] if x.ndim == 3 else 1
-        A = self._gemm(x, x, R, R, C, False, False, batch=batch)
-        B = self._gemm(A, A, R, R, R, False, False, cin=A, alpha=c, beta=b, batch=batch)
+        sym = self.gemm_2cta and R >= 512 and x.element_size() == 2
+        A = self._gemm(x, x, R, R, C, False, False, batch=batch, sym_upper=sym)
+        B = self._gemm(A, A, R, R, R, False, False, cin=A, alpha=c, beta=b, batch=batch, sym_upper=sym)
         if self.mn_major:
             return self._gemm(B, x, R, C, R, False, True, cin=x, alpha=1.0, beta=a, batch=batch)
         xt = self.transpose(x)

@@ -277,3 +277,27 @@ def test_gemm_two_cta(ops, mode, M, N, K):
         assert rel_err(c, ref) < 1e-2, rel_err(c, ref)
     finally:
         ops.gemm_2cta = prev
+
+
+def test_newton_schulz_symmetric_tiles_and_batch(ops):
+    """R >= 512 takes the upper-triangle-only path (+ mirror); batched and single must agree with fp32 math."""
+    from kotodama_b200.optim.muon import resolve_ns_coefficients
+    prev = ops.gemm_2cta
+    ops.gemm_2cta = True
+    try:
+        g = torch.Generator(device="cuda").manual_seed(5)
+        X = (torch.randn(2, 1024, 1536, device="cuda", generator=g) * 0.02).half()
+        X = X / X.float().flatten(1).norm(dim=1).view(2, 1, 1).half()
+        a, b, c = resolve_ns_coefficients("gram_ns", 1)[0]
+        out = ops.ns_iteration(X.clone(), a, b, c)
+        ops.check_status()
+        Xf = X.float()
+        A = Xf @ Xf.transpose(1, 2)
+        ref = a * Xf + (b * A + c * (A @ A)) @ Xf
+        assert rel_err(out, ref) < 2e-2, rel_err(out, ref)
+        single = ops.ns_iteration(X[1].clone(), a, b, c)
+        assert rel_err(single, ref[1]) < 2e-2
+        A_k = ops._gemm(X[0], X[0], 1024, 1024, 1536, False, False, sym_upper=True)
+        assert torch.equal(A_k, A_k.t())          # mirrored exactly
+    finally:
+        ops.gemm_2cta = prev
