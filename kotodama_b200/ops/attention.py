@@ -1,9 +1,11 @@
 """Causal GQA attention for the CUDA backend.
 
-Dispatches to the tcgen05 flash-attention kernels in ``csrc/attn_sm100.cu`` when the shape
-is one they cover (head_dim 128 or 64, sequence length a multiple of the tile); any other
-shape goes to PyTorch's fused scaled-dot-product attention, which is a library kernel and is
-reported as such by ``CudaOps.attention_library_calls``.
+Inference (prefill, evaluation) runs the tcgen05 flash-attention forward in
+``csrc/attn_sm100.cu`` when the shape is one it covers (head_dim 128, sequence length a multiple
+of 128).  The training path needs a backward as well; until the native one lands it uses PyTorch's
+fused scaled-dot-product attention for both directions (a library kernel, reported as such by
+``CudaOps.attention_library_calls``); ``KOTODAMA_FLASH_TRAIN=1`` switches training to the native
+forward with the ``flash_attn`` library's backward.
 """
 from __future__ import annotations
 
@@ -11,12 +13,16 @@ import torch
 import torch.nn.functional as F
 
 
-def _native_ok(ops, q: torch.Tensor) -> bool:
-    return getattr(ops, "native_attention", False) and q.shape[-1] in (64, 128) and q.shape[1] % 128 == 0
+def _native_ok(ops, q: torch.Tensor, need_grad: bool) -> bool:
+    from .flash import supported
+    if not getattr(ops, "native_attention", True) or not supported(q):
+        return False
+    # training keeps forward and backward in one library call pair unless asked otherwise
+    return (not need_grad) or getattr(ops, "native_attention_train", False)
 
 
 def attention_fwd(ops, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, need_grad: bool = True):
-    if _native_ok(ops, q):
+    if _native_ok(ops, q, need_grad):
         from .flash import flash_fwd
         return flash_fwd(ops, q, k, v)
     ops.attention_library_calls = getattr(ops, "attention_library_calls", 0) + 1
