@@ -28,15 +28,26 @@ __device__ __forceinline__ int ld_acquire_sys(const int* p) {
     asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
-// Bounded poll on a local flag.  Returns false on timeout.
+__device__ __forceinline__ int ld_relaxed_sys(const int* p) {
+    int v;
+    asm volatile("ld.relaxed.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+// Bounded poll on a local flag.  Returns false on timeout.  The loop polls with relaxed loads
+// and a growing sleep, and fences once at the end: a tight loop of system-scope acquire loads
+// from a kernel that waits on a side stream was measured to slow concurrently running GEMMs
+// by 1.5x at 4 and 8 ranks.
 __device__ __forceinline__ bool wait_flag(const int* flag, int epoch, uint64_t limit_ns) {
     if (ld_acquire_sys(flag) >= epoch) return true;
     const uint64_t t0 = global_timer_ns();
-    while (ld_acquire_sys(flag) < epoch) {
+    unsigned sleep_ns = 128;
+    while (ld_relaxed_sys(flag) < epoch) {
         if (global_timer_ns() - t0 > limit_ns) return false;
-        __nanosleep(200);
+        __nanosleep(sleep_ns);
+        if (sleep_ns < 2048) sleep_ns <<= 1;
     }
-    return true;
+    __threadfence_system();
+    return ld_acquire_sys(flag) >= epoch;
 }
 
 // flags layout on every rank: int flags[slots][8]
