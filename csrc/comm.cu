@@ -10,6 +10,11 @@
 //   kb_reduce_to_owner  owner sums a gradient range over all ranks (fp32), scales, stores bf16
 //   kb_allreduce_slices two-shot all-reduce: each rank reduces its slice, stores it to every peer
 //   kb_scalar_allreduce sum of one float per rank (also a full barrier)
+//   kb_ag_push          all-gather producer: this rank's shard into every peer's staging slot, then
+//                       the shard's ready flag (consumed by kb_gemm_ag's TMA producer)
+//   kb_rs_reduce        reduce-scatter consumer: waits for the arrival counters that kb_gemm_rs's
+//                       epilogue raises, sums the per-source slabs (+ residual), frees the slabs
+//   kb_allreduce_oneshot small all-reduce for decode: every rank reads every peer's partial
 //   kb_muon_apply_bcast p_new = p*decay - alpha*orth written into every rank's parameter arena
 //                       (the all-gather of the updated matrix is the parameter write itself)
 #include "common.cuh"
@@ -282,5 +287,207 @@ KB_API int kb_muon_apply_bcast(void* const* peer_params, int world, int rank, lo
     dim3 grid((C + 63) / 64, (R + 63) / 64), block(8, 32);
     muon_apply_bcast_kernel<<<grid, block, 0, st>>>(pp, world, rank, offset, (const __half*)orth, R, C,
                                                     wd > 0 ? 1.f - lr * wd : 1.f, lr * scale, transposed);
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Tensor-parallel collectives fused with the GEMMs (sequence parallelism).
+
+// Last-block election: returns true in every thread of the block that finishes last.
+__device__ __forceinline__ bool last_block_done(unsigned* counter) {
+    __shared__ int s_last;
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned prev = atomicAdd(counter, 1u);
+        s_last = prev == gridDim.x - 1;
+        if (s_last) *counter = 0;
+    }
+    __syncthreads();
+    return s_last != 0;
+}
+
+// Shard push.  stage.p[q] = peer q's staging slot for this source rank; ready.p[q] = address of
+// this rank's ready flag on peer q.  `done[q]` (local) is the last call whose staging buffer peer q
+// has finished reading; the slot may be overwritten once done[q] >= need.  Targets are the
+// `count` ranks starting at `first` (cyclically): the caller pushes to itself first (a local
+// copy, so its GEMM can start at once) and to the peers from a side stream.
+__global__ void __launch_bounds__(256)
+ag_push_kernel(const uint4* __restrict__ src, long long nvec, PeerPtrs stage, PeerPtrs ready, int world, int first,
+               int count, int epoch, const int* done, int need, unsigned* counter, unsigned long long limit_ns,
+               int* status) {
+    __shared__ int ok;
+    if (threadIdx.x == 0) ok = 1;
+    __syncthreads();
+    if (need > 0 && threadIdx.x < count) {
+        if (!wait_flag(done + (first + threadIdx.x) % world, need, limit_ns)) {
+            atomicMax(status, (int)KB_TIMEOUT_PEER);
+            ok = 0;
+        }
+    }
+    __syncthreads();
+    const bool good = ok != 0;
+    if (good) {
+        const long long stride = (long long)gridDim.x * blockDim.x;
+        for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+            const uint4 v = __ldg(src + i);
+            for (int t = 0; t < count; ++t) {
+                int q = first + t;
+                if (q >= world) q -= world;
+                reinterpret_cast<uint4*>(stage.p[q])[i] = v;
+            }
+        }
+    }
+    if (last_block_done(counter) && good && threadIdx.x < count) {
+        __threadfence_system();
+        st_release_sys(reinterpret_cast<int*>(ready.p[(first + threadIdx.x) % world]), epoch);
+    }
+}
+KB_API int kb_ag_push(const void* src, long long n_elems, void* const* peer_stage, void* const* peer_ready, int world,
+                      int first, int count, int epoch, const int* done, int need, unsigned* counter, double limit_s,
+                      int* status, int max_ctas, cudaStream_t st) {
+    if (world < 1 || world > 8 || (n_elems & 7) || ((uintptr_t)src & 15)) return 5;
+    if (first < 0 || first >= world || count < 1 || count > world) return 5;
+    PeerPtrs ps, pr;
+    for (int i = 0; i < 8; ++i) {
+        ps.p[i] = i < world ? peer_stage[i] : nullptr;
+        pr.p[i] = i < world ? peer_ready[i] : nullptr;
+    }
+    const long long nvec = n_elems >> 3;
+    long long blocks = (nvec + 255) / 256;
+    if (blocks < 1) blocks = 1;
+    if (blocks > max_ctas) blocks = max_ctas;
+    ag_push_kernel<<<(int)blocks, 256, 0, st>>>((const uint4*)src, nvec, ps, pr, world, first, count, epoch, done,
+                                                need, counter, (unsigned long long)(limit_s * 1e9), status);
+    return 0;
+}
+
+// out[i] = sum_s slab[s][i] (+ residual[i]) once cnt[s] >= expected (arrivals of this call) for
+// every source s; then the counters are zeroed and
+// `done_epoch` is written to this rank's slot on every peer: the slabs may be reused.
+__global__ void __launch_bounds__(256)
+rs_reduce_kernel(const bf16* __restrict__ slabs, long long slab_elems, int* cnt, int expected, int world,
+                 const bf16* __restrict__ residual, bf16* __restrict__ out, PeerPtrs done, int done_epoch,
+                 unsigned* counter, unsigned long long limit_ns, int* status) {
+    __shared__ int ok;
+    if (threadIdx.x == 0) ok = 1;
+    __syncthreads();
+    if (threadIdx.x < world) {
+        if (!wait_flag(cnt + threadIdx.x, expected, limit_ns)) {
+            atomicMax(status, (int)KB_TIMEOUT_PEER);
+            ok = 0;
+        }
+    }
+    __syncthreads();
+    const bool good = ok != 0;
+    if (good) {
+        const long long nvec = slab_elems >> 3;
+        const long long stride = (long long)gridDim.x * blockDim.x;
+        for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+            float acc[8];
+            if (residual) unpack8(ld8(residual + i * 8), acc);
+            else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+            }
+#pragma unroll
+            for (int s = 0; s < 8; ++s) {
+                if (s < world) {
+                    float t[8];
+                    const uint4 raw = __ldcg(reinterpret_cast<const uint4*>(slabs + s * slab_elems) + i);
+                    unpack8(*reinterpret_cast<const bf16x8*>(&raw), t);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) acc[j] += t[j];
+                }
+            }
+            st8(out + i * 8, pack8(acc));
+        }
+    }
+    if (last_block_done(counter) && good && threadIdx.x < world) {
+        // every block has read the slabs: zero the arrival counters for the call after next (its
+        // producers start only after they have seen the done flag below), then release the slabs
+        cnt[threadIdx.x] = 0;
+        __threadfence_system();
+        __syncwarp(__activemask());
+        st_release_sys(reinterpret_cast<int*>(done.p[threadIdx.x]), done_epoch);
+    }
+}
+KB_API int kb_rs_reduce(const void* slabs, long long slab_elems, int* cnt, int expected, int world,
+                        const void* residual, void* out, void* const* peer_done, int done_epoch, unsigned* counter,
+                        double limit_s, int* status, int max_ctas, cudaStream_t st) {
+    if (world < 1 || world > 8 || (slab_elems & 7)) return 5;
+    PeerPtrs pd;
+    for (int i = 0; i < 8; ++i) pd.p[i] = i < world ? peer_done[i] : nullptr;
+    long long blocks = ((slab_elems >> 3) + 255) / 256;
+    if (blocks < 1) blocks = 1;
+    if (blocks > max_ctas) blocks = max_ctas;
+    rs_reduce_kernel<<<(int)blocks, 256, 0, st>>>((const bf16*)slabs, slab_elems, cnt, expected, world,
+                                                  (const bf16*)residual, (bf16*)out, pd, done_epoch, counter,
+                                                  (unsigned long long)(limit_s * 1e9), status);
+    return 0;
+}
+
+// One-shot all-reduce of a small bf16 vector (decode-time row-parallel outputs): every rank's
+// partial already sits in its own symmetric buffer (the GEMM wrote it there); block 0 raises this
+// rank's flag on every peer, every block waits for all flags, then each rank sums all partials for
+// itself.  out = sum_r partial_r (+ residual).  Buffers alternate by call parity on the host side.
+__global__ void __launch_bounds__(256)
+allreduce_oneshot_kernel(PeerPtrs parts, PeerPtrs flags, int world, int rank, int slot, int epoch, long long n,
+                         const bf16* __restrict__ residual, bf16* __restrict__ out, unsigned long long limit_ns,
+                         int* status) {
+    __shared__ int ok;
+    if (threadIdx.x == 0) ok = 1;
+    __syncthreads();
+    if (threadIdx.x < world) {
+        if (blockIdx.x == 0) {
+            __threadfence_system();
+            st_release_sys(reinterpret_cast<int*>(flags.p[threadIdx.x]) + slot * 8 + rank, epoch);
+        }
+        if (!wait_flag(reinterpret_cast<const int*>(flags.p[rank]) + slot * 8 + threadIdx.x, epoch, limit_ns)) {
+            atomicMax(status, (int)KB_TIMEOUT_PEER);
+            ok = 0;
+        }
+    }
+    __syncthreads();
+    if (!ok) return;
+    const long long nvec = n >> 3;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec;
+         i += (long long)gridDim.x * blockDim.x) {
+        uint4 raw[8];
+#pragma unroll
+        for (int r = 0; r < 8; ++r)
+            if (r < world) raw[r] = __ldcg(reinterpret_cast<const uint4*>(parts.p[r]) + i);
+        float acc[8];
+        if (residual) unpack8(ld8(residual + i * 8), acc);
+        else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+        }
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+            if (r < world) {
+                float t[8];
+                unpack8(*reinterpret_cast<const bf16x8*>(&raw[r]), t);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[j] += t[j];
+            }
+        }
+        st8(out + i * 8, pack8(acc));
+    }
+}
+KB_API int kb_allreduce_oneshot(void* const* peer_parts, void* const* peer_flags, int world, int rank, int slot,
+                                int epoch, long long n, const void* residual, void* out, double limit_s, int* status,
+                                int max_ctas, cudaStream_t st) {
+    if (world < 1 || world > 8 || (n & 7)) return 5;
+    PeerPtrs pp, pf;
+    for (int i = 0; i < 8; ++i) {
+        pp.p[i] = i < world ? peer_parts[i] : nullptr;
+        pf.p[i] = i < world ? peer_flags[i] : nullptr;
+    }
+    long long blocks = ((n >> 3) + 255) / 256;
+    if (blocks < 1) blocks = 1;
+    if (blocks > max_ctas) blocks = max_ctas;
+    allreduce_oneshot_kernel<<<(int)blocks, 256, 0, st>>>(pp, pf, world, rank, slot, epoch, n, (const bf16*)residual,
+                                                          (bf16*)out, (unsigned long long)(limit_s * 1e9), status);
     return 0;
 }

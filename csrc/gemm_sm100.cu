@@ -13,6 +13,7 @@
 // The epilogue computes alpha*acc + beta*Cin with Cin of the output type: residual adds,
 // gradient accumulation and the Newton-Schulz polynomials are all fused here.
 #include <cuda.h>
+#include <string.h>
 
 #include "tc.cuh"
 
@@ -20,7 +21,9 @@ namespace {
 
 constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
 constexpr int A_STAGE = BM * BK * 2, B_STAGE = BN * BK * 2;
-constexpr int SMEM_BYTES = STAGES * (A_STAGE + B_STAGE) + 1024 /*align*/ + 256 /*barriers*/;
+constexpr int EPI_PITCH = 144;                       // bytes per staged row: 64 bf16 + 16 (bank spread)
+constexpr int EPI_WARP_BYTES = 32 * EPI_PITCH;       // one 32x64 bf16 chunk per epilogue warp
+constexpr int SMEM_BYTES = STAGES * (A_STAGE + B_STAGE) + 1024 /*align*/ + 256 /*barriers*/ + 4 * EPI_WARP_BYTES;
 constexpr int GROUP_M = 8;
 
 struct GemmParams {
@@ -36,6 +39,52 @@ struct GemmParams {
     int* status;
     int split_k;               // > 1: each tile's K range is cut into split_k parts, fp32 atomic accumulation
 };
+
+// Optional coupling of the GEMM to a collective over NVLink peer memory (tensor parallelism with
+// sequence parallelism):
+//   * all-gather side: the gathered operand sits in a local staging buffer that the peers fill
+//     shard by shard; the TMA producer waits (bounded) for a shard's ready flag before it loads
+//     the first tile that touches it, and visits its own shard first.  Shards are row ranges
+//     of A (ag_dim 0) or K ranges of both operands (ag_dim 1, the weight-gradient product);
+//   * reduce-scatter side: the epilogue stores each bf16 output tile into the slab that the
+//     tile's owner rank keeps for this source rank (plain peer stores), then adds one arrival
+//     per epilogue warp to the owner's counter; the owner's reduce kernel sums the slabs.
+struct GemmComm {
+    const int* ag_flags;
+    int ag_epoch, ag_rows, ag_dim;
+    int rot;                       // visiting order starts at this M tile (ag_dim 0 / rs) or k-block (ag_dim 1)
+    void* rs_out[8];
+    int* rs_cnt[8];
+    int rs_rows;
+    unsigned long long limit_ns;
+};
+
+__device__ __forceinline__ int ld_relaxed_sys_i32(const int* p) {
+    int v;
+    asm volatile("ld.relaxed.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+// Bounded wait for flag >= epoch: relaxed polls with back-off, one acquire fence at the end, and a
+// proxy fence so that the TMA (async proxy) reads what the peer's stores wrote.
+__device__ __forceinline__ bool wait_shard(const int* flag, int epoch, unsigned long long limit_ns,
+                                           volatile int* abort_flag) {
+    if (ld_relaxed_sys_i32(flag) < epoch) {
+        const uint64_t t0 = global_timer_ns();
+        unsigned sleep_ns = 64;
+        while (ld_relaxed_sys_i32(flag) < epoch) {
+            if (*abort_flag) return false;
+            if (global_timer_ns() - t0 > limit_ns) {
+                *abort_flag = 1;
+                return false;
+            }
+            __nanosleep(sleep_ns);
+            if (sleep_ns < 1024) sleep_ns <<= 1;
+        }
+    }
+    __threadfence_system();
+    asm volatile("fence.proxy.async;" ::: "memory");
+    return true;
+}
 
 __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& b, int& tm, int& tn) {
     const int per_batch = tiles_m * tiles_n;
@@ -120,9 +169,10 @@ __device__ __forceinline__ void store_row32_16(T* dst, const T* cin, const uint3
     }
 }
 
+template <bool COMM>
 __global__ void __launch_bounds__(192, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                    const GemmParams p) {
+                    const GemmParams p, const GemmComm cm) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* sA = smem;
@@ -171,11 +221,42 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             uint32_t phase = 0;
             int issued = 0;
             bool ok = true;
+            unsigned ready_mask = 0;       // shards already seen ready
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
                 int b, tm, tn;
                 tile_coords(tile / p.split_k, tiles_m, tiles_n, b, tm, tn);
+                if (COMM && cm.ag_dim == 0) {
+                    tm += cm.rot;
+                    if (tm >= tiles_m) tm -= tiles_m;
+                    if (cm.ag_flags) {
+                        const int s0 = (tm * BM) / cm.ag_rows, s1 = (min(tm * BM + BM, p.M) - 1) / cm.ag_rows;
+                        for (int sh = s0; sh <= s1 && ok; ++sh) {
+                            if (ready_mask >> sh & 1) continue;
+                            if (!wait_shard(cm.ag_flags + sh, cm.ag_epoch, cm.limit_ns, abort_flag)) {
+                                atomicMax(p.status, (int)KB_TIMEOUT_PEER);
+                                ok = false;
+                            }
+                            ready_mask |= 1u << sh;
+                        }
+                        if (!ok) break;
+                    }
+                }
                 const int kb0 = (tile % p.split_k) * kb_per, kb1 = min(kblocks_total, kb0 + kb_per);
-                for (int kb = kb0; kb < kb1; ++kb) {
+                for (int kbi = kb0; kbi < kb1; ++kbi) {
+                    int kb = kbi;
+                    if (COMM && cm.ag_dim == 1) {
+                        kb += cm.rot;
+                        if (kb >= kblocks_total) kb -= kblocks_total;
+                        const int sh = (kb * BK) / cm.ag_rows;
+                        if (cm.ag_flags && !(ready_mask >> sh & 1)) {
+                            if (!wait_shard(cm.ag_flags + sh, cm.ag_epoch, cm.limit_ns, abort_flag)) {
+                                atomicMax(p.status, (int)KB_TIMEOUT_PEER);
+                                ok = false;
+                                break;
+                            }
+                            ready_mask |= 1u << sh;
+                        }
+                    }
                     if (!tc::mbar_wait(&empty[stage], phase ^ 1, abort_flag)) {
                         atomicMax(p.status, (int)KB_TIMEOUT_TMA);
                         ok = false;
@@ -264,6 +345,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
             int b, tm, tn;
             tile_coords(tile / p.split_k, tiles_m, tiles_n, b, tm, tn);
+            if (COMM && cm.ag_dim == 0) {
+                tm += cm.rot;
+                if (tm >= tiles_m) tm -= tiles_m;
+            }
             const bool has_k = (tile % p.split_k) * kb_per < kblocks_total;
             const int buf = it & 1;
             const uint32_t acc_phase = (it >> 1) & 1;
@@ -275,6 +360,42 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             tc::tc_fence_after();
             const int row = tm * BM + quarter * 32 + lane;
             const uint32_t taddr = tmem_base + buf * BN + ((uint32_t)(quarter * 32) << 16);
+            if (COMM && cm.rs_rows > 0) {
+                // Reduce-scatter store.  Peer stores should be wide and contiguous (a 16-byte store
+                // per lane to 32 different rows becomes 32 small NVLink writes), so each 32x64 chunk
+                // is transposed through shared memory and leaves as 128-byte row segments.
+                uint8_t* stg = smem + STAGES * (A_STAGE + B_STAGE) + 256 + (warp - 2) * EPI_WARP_BYTES;
+                const int owner = (tm * BM) / cm.rs_rows;
+                __nv_bfloat16* obase = reinterpret_cast<__nv_bfloat16*>(cm.rs_out[owner]) +
+                                       (long long)(tm * BM + quarter * 32 - owner * cm.rs_rows) * p.ldc;
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN; c0 += 64) {
+                    uint32_t acc[64];
+                    tc::tmem_ld32(taddr + c0, acc);
+                    tc::tmem_ld32(taddr + c0 + 32, acc + 32);
+                    tc::tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        uint4 o;
+                        __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i)
+                            op[i] = __floats2bfloat162_rn(p.alpha * __uint_as_float(acc[8 * j + 2 * i]),
+                                                          p.alpha * __uint_as_float(acc[8 * j + 2 * i + 1]));
+                        *reinterpret_cast<uint4*>(stg + lane * EPI_PITCH + j * 16) = o;
+                    }
+                    __syncwarp();
+                    const int seg = lane & 7, col = tn * BN + c0 + seg * 8;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const int rr = i * 4 + (lane >> 3);
+                        const uint4 v = *reinterpret_cast<const uint4*>(stg + rr * EPI_PITCH + seg * 16);
+                        if (tm * BM + quarter * 32 + rr < p.M && col < p.N)
+                            *reinterpret_cast<uint4*>(obase + (long long)rr * p.ldc + col) = v;
+                    }
+                    __syncwarp();
+                }
+            } else
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 32) {
                 uint32_t acc[32];
@@ -314,6 +435,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             tc::tc_fence_before();
             __syncwarp();
             if (lane == 0) tc::mbar_arrive(&acc_empty[buf]);
+            if (COMM && cm.rs_rows > 0) {
+                // this warp's part of the tile has been stored to the owner: publish one arrival
+                __threadfence_system();
+                __syncwarp();
+                if (lane == 0) {
+                    int* cnt = cm.rs_cnt[(tm * BM) / cm.rs_rows];
+                    asm volatile("red.release.sys.global.add.s32 [%0], 1;" ::"l"(cnt) : "memory");
+                }
+            }
         }
     }
     tc::tc_fence_before();
@@ -356,17 +486,11 @@ int make_tmap(CUtensorMap* m, const void* base, int fmt, long long cols, long lo
     return r == CUDA_SUCCESS ? 0 : 200 + (int)r;
 }
 
-}  // namespace
-
-// C[b][M,N] = alpha * op(A[b]) * op(B[b])^T + beta * Cin[b].
-//   a_mn = 0: A is [M,K] (lda = row stride);  a_mn = 1: A is stored [K,M].
-//   b_mn = 0: B is [N,K];                      b_mn = 1: B is stored [K,N].
-//   fmt: 0 fp16, 1 bf16.  out_type: 0 fp16, 1 bf16, 2 fp32.  status: device int, set on a wait timeout.
-// Requirements: 16-byte aligned bases, lda/ldb multiples of 8 elements.
-KB_API int kb_gemm(const void* A, const void* B, void* C, const void* Cin, int M, int N, int K, int batch,
-                   long long lda, long long ldb, long long ldc, long long ldcin, long long a_bs, long long b_bs,
-                   long long c_bs, long long cin_bs, int a_mn, int b_mn, int a_fmt, int b_fmt, int out_type,
-                   float alpha, float beta, int* status, int max_ctas, int split_k, cudaStream_t st) {
+static int launch_gemm(const void* A, const void* B, void* C, const void* Cin, int M, int N, int K, int batch,
+                       long long lda, long long ldb, long long ldc, long long ldcin, long long a_bs, long long b_bs,
+                       long long c_bs, long long cin_bs, int a_mn, int b_mn, int a_fmt, int b_fmt, int out_type,
+                       float alpha, float beta, int* status, int max_ctas, int split_k, const GemmComm* cm,
+                       cudaStream_t st) {
     if (split_k < 1) split_k = 1;
     if (split_k > 1 && out_type != 2) return 5;
     if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return 5;
@@ -374,8 +498,10 @@ KB_API int kb_gemm(const void* A, const void* B, void* C, const void* Cin, int M
     if (batch > 1 && ((a_bs & 7) || (b_bs & 7))) return 6;
     static bool attr_set = false;
     if (!attr_set) {
-        if (cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) !=
-            cudaSuccess)
+        if (cudaFuncSetAttribute(gemm_tcgen05_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 SMEM_BYTES) != cudaSuccess ||
+            cudaFuncSetAttribute(gemm_tcgen05_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 SMEM_BYTES) != cudaSuccess)
             return 7;
         attr_set = true;
     }
@@ -400,6 +526,71 @@ KB_API int kb_gemm(const void* A, const void* B, void* C, const void* Cin, int M
     if (max_ctas > 0 && max_ctas < sms) sms = max_ctas;
     const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN) * batch * split_k;
     const int grid = tiles < sms ? tiles : sms;
-    gemm_tcgen05_kernel<<<grid, 192, SMEM_BYTES, st>>>(tmA, tmB, p);
+    if (cm) {
+        gemm_tcgen05_kernel<true><<<grid, 192, SMEM_BYTES, st>>>(tmA, tmB, p, *cm);
+    } else {
+        GemmComm none;
+        memset(&none, 0, sizeof(none));
+        gemm_tcgen05_kernel<false><<<grid, 192, SMEM_BYTES, st>>>(tmA, tmB, p, none);
+    }
     return 0;
 }
+
+}  // namespace
+
+// C[b][M,N] = alpha * op(A[b]) * op(B[b])^T + beta * Cin[b].
+//   a_mn = 0: A is [M,K] (lda = row stride);  a_mn = 1: A is stored [K,M].
+//   b_mn = 0: B is [N,K];                      b_mn = 1: B is stored [K,N].
+//   fmt: 0 fp16, 1 bf16.  out_type: 0 fp16, 1 bf16, 2 fp32.  status: device int, set on a wait timeout.
+// Requirements: 16-byte aligned bases, lda/ldb multiples of 8 elements.
+KB_API int kb_gemm(const void* A, const void* B, void* C, const void* Cin, int M, int N, int K, int batch,
+                   long long lda, long long ldb, long long ldc, long long ldcin, long long a_bs, long long b_bs,
+                   long long c_bs, long long cin_bs, int a_mn, int b_mn, int a_fmt, int b_fmt, int out_type,
+                   float alpha, float beta, int* status, int max_ctas, int split_k, cudaStream_t st) {
+    return launch_gemm(A, B, C, Cin, M, N, K, batch, lda, ldb, ldc, ldcin, a_bs, b_bs, c_bs, cin_bs, a_mn, b_mn,
+                       a_fmt, b_fmt, out_type, alpha, beta, status, max_ctas, split_k, nullptr, st);
+}
+
+// All-gather -> GEMM.  One operand is a local staging buffer filled shard by shard by the peers
+// (kb_ag_push): `ag_dim` 0 = A's rows come in `world` shards of `ag_rows` rows, 1 = the K
+// dimension of both operands does (A local and complete, B staged).  ag_flags[s] >= ag_epoch marks
+// shard s as landed; `own` is this rank's shard, visited first.  bf16 in, bf16 out;
+// C = alpha*A*B^T + beta*Cin with Cin (nullable) laid out like C.
+KB_API int kb_gemm_ag(const void* A, const void* B, void* C, const void* Cin, int M, int N, int K, long long lda,
+                      long long ldb, long long ldc, int a_mn, int b_mn, float alpha, float beta,
+                      const int* ag_flags, int ag_epoch,
+                      int ag_rows, int ag_dim, int own, double limit_s, int* status, cudaStream_t st) {
+    if (!ag_flags || ag_rows <= 0 || own < 0 || own > 7) return 5;
+    if (ag_dim == 0 ? (ag_rows % BM) != 0 : (ag_rows % BK) != 0) return 5;
+    if ((ag_dim == 0 ? M : K) > 8 * (long long)ag_rows) return 5;
+    GemmComm cm;
+    memset(&cm, 0, sizeof(cm));
+    cm.ag_flags = ag_flags; cm.ag_epoch = ag_epoch; cm.ag_rows = ag_rows; cm.ag_dim = ag_dim;
+    cm.rot = own * (ag_rows / (ag_dim == 0 ? BM : BK));
+    cm.limit_ns = (unsigned long long)(limit_s * 1e9);
+    return launch_gemm(A, B, C, Cin, M, N, K, 1, lda, ldb, ldc, ldc, 0, 0, 0, 0, a_mn, b_mn, 1, 1, 1, alpha, beta,
+                       status, 0, 1, &cm, st);
+}
+
+// GEMM -> reduce-scatter, producer half.  Rows [o*rs_rows, (o+1)*rs_rows) of the bf16 product
+// belong to rank o: they are stored to rs_out[o] (that rank's slab for this source, row stride
+// ldc) while the other tiles are still being computed, and every epilogue warp adds one arrival
+// to rs_cnt[o] when its quarter tile is out.  kb_gemm_rs_arrivals gives the arrivals per owner;
+// kb_rs_reduce is the consumer half.  Tiles for rank+1 are computed first, the own ones last.
+KB_API int kb_gemm_rs(const void* A, const void* B, int M, int N, int K, long long lda, long long ldb,
+                      long long ldc, int a_mn, int b_mn, float alpha, void* const* rs_out, int* const* rs_cnt,
+                      int world, int rank, int rs_rows, int* status, cudaStream_t st) {
+    if (world < 1 || world > 8 || rs_rows <= 0 || (rs_rows % BM) != 0 || M != world * rs_rows) return 5;
+    if ((N & 7) || (ldc & 7)) return 6;
+    GemmComm cm;
+    memset(&cm, 0, sizeof(cm));
+    for (int i = 0; i < world; ++i) {
+        cm.rs_out[i] = rs_out[i];
+        cm.rs_cnt[i] = rs_cnt[i];
+    }
+    cm.rs_rows = rs_rows;
+    cm.rot = ((rank + 1) % world) * (rs_rows / BM);
+    return launch_gemm(A, B, rs_out[rank], nullptr, M, N, K, 1, lda, ldb, ldc, 0, 0, 0, 0, 0, a_mn, b_mn, 1, 1, 1,
+                       alpha, 0.f, status, 0, 1, &cm, st);
+}
+KB_API int kb_gemm_rs_arrivals(int N, int rs_rows) { return (rs_rows / BM) * ((N + BN - 1) / BN) * 4; }

@@ -338,8 +338,7 @@ class TrainEngine:
                 committed = committed + [partial]
                 partial = None
             r.part_before_attn = partial
-            xin = self.comm.sp_gather(r.xn1)
-            r.qkv = ops.gemm_nt(xin, lw["wqkv"])
+            r.qkv = self.comm.col_linear(ops, r.xn1, lw["wqkv"])
             r.qk, r.rstd_qk = ops.qknorm_rope_fwd(
                 r.qkv, self._p(p + "attn.q_norm.weight") if cfg.qk_norm else None,
                 self._p(p + "attn.k_norm.weight") if cfg.qk_norm else None, cos, sin, T, H, KV, hd, eps)
@@ -353,8 +352,7 @@ class TrainEngine:
             r.srcs2 = committed + [partial]
             r.xn2, r.stats2 = ops.route_norm_fwd(r.srcs2, qw(p + "mlp_res_query"), qw(p + "mlp_res_norm.weight"),
                                                  self._p(p + "ffn_norm.weight"), eps)
-            xin2 = self.comm.sp_gather(r.xn2)
-            r.gu = ops.gemm_nt(xin2, lw["wgu"])
+            r.gu = self.comm.col_linear(ops, r.xn2, lw["wgu"])
             r.act = ops.swiglu_fwd(r.gu)
             partial = self.comm.row_linear(ops, r.act, lw["wd"], residual=partial)
             r.part_after_mlp = partial
@@ -405,14 +403,10 @@ class TrainEngine:
             lw, r, p = self.layer_w[i], recs[i], f"layers.{i}."
             # ---- MLP sub-layer
             dP = grads[id(r.part_after_mlp)]
-            dPg = self.comm.sp_gather(dP)
-            dact = ops.gemm_nn(dPg, lw["wd"])
-            ops.gemm_tn(dPg, r.act, out=lw["g_wd"], accumulate=not first_micro)
-            del dPg
+            dact = self.comm.row_linear_bwd(ops, dP, lw["wd"], r.act, lw["g_wd"], not first_micro)
             dgu = ops.swiglu_bwd(r.gu, dact)
             del dact
-            ops.gemm_tn(dgu, self.comm.sp_gather(r.xn2), out=lw["g_wgu"], accumulate=not first_micro)
-            dxn2 = self.comm.col_linear_bwd_input(ops, dgu, lw["wgu"])
+            dxn2 = self.comm.col_linear_bwd(ops, dgu, lw["wgu"], r.xn2, lw["g_wgu"], not first_micro)
             del dgu
             grads[id(r.part_after_attn)] = dP                      # residual add: gradient passes through
             ds, acc = dsrc_list(r.srcs2)
@@ -426,10 +420,7 @@ class TrainEngine:
             # ---- attention sub-layer
             dP = grads[id(r.part_after_attn)]
             Nq = r.qkv.shape[0]
-            dPg = self.comm.sp_gather(dP)
-            dattn = ops.gemm_nn(dPg, lw["wo"])
-            ops.gemm_tn(dPg, r.attn_o.view(Nq, H * hd), out=lw["g_wo"], accumulate=not first_micro)
-            del dPg
+            dattn = self.comm.row_linear_bwd(ops, dP, lw["wo"], r.attn_o.view(Nq, H * hd), lw["g_wo"], not first_micro)
             dqkv = torch.empty_like(r.qkv)
             dqk = torch.empty_like(r.qk)
             q4 = r.qk[:, : H * hd].view(Nq // T, T, H, hd)
@@ -446,8 +437,7 @@ class TrainEngine:
                 self._acc_small(p + "attn.q_norm.weight", dqw)
                 self._acc_small(p + "attn.k_norm.weight", dkw)
             del dqk
-            ops.gemm_tn(dqkv, self.comm.sp_gather(r.xn1), out=lw["g_wqkv"], accumulate=not first_micro)
-            dxn1 = self.comm.col_linear_bwd_input(ops, dqkv, lw["wqkv"])
+            dxn1 = self.comm.col_linear_bwd(ops, dqkv, lw["wqkv"], r.xn1, lw["g_wqkv"], not first_micro)
             del dqkv
             if r.part_before_attn is not None:
                 grads[id(r.part_before_attn)] = dP

@@ -61,6 +61,25 @@ class LocalComm:
     def col_linear_bwd_input(self, ops, dy, w):
         return ops.gemm_nn(dy, w)
 
+    # Composite hooks the executor calls; strategies with fused GEMM+collective kernels override
+    # these, everything else inherits the compositions of the primitive hooks above.
+    def col_linear(self, ops, x, w):
+        """Column-parallel projection of a sequence-sharded activation: all-gather -> GEMM."""
+        return ops.gemm_nt(self.sp_gather(x), w)
+
+    def row_linear_bwd(self, ops, dy, w, x_saved, g_out, accumulate: bool):
+        """Backward of a row-parallel projection: all-gather(dy) -> data gradient and weight gradient."""
+        dyg = self.sp_gather(dy)
+        dx = ops.gemm_nn(dyg, w)
+        ops.gemm_tn(dyg, x_saved, out=g_out, accumulate=accumulate)
+        return dx
+
+    def col_linear_bwd(self, ops, dy, w, x, g_out, accumulate: bool):
+        """Backward of a column-parallel projection: weight gradient from the re-gathered input,
+        data gradient GEMM -> reduce-scatter."""
+        ops.gemm_tn(dy, self.sp_gather(x), out=g_out, accumulate=accumulate)
+        return self.col_linear_bwd_input(ops, dy, w)
+
     # gradient reduction
     def layer_grads_ready(self, layer: int) -> None:
         pass

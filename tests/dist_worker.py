@@ -71,6 +71,25 @@ def main():
                       q_shape=list(full["layers.0.attn.q_proj.weight"].shape),
                       local_q_shape=list(eng.model.layers[0].attn.q_proj.weight.shape),
                       momentum_shape=list(eng.muon_state_dict()["state"][0]["momentum_buffer"].shape))
+    if a.mode in ("gpu_tp_library", "gpu_tp_fused"):
+        from kotodama_b200.parallel.tp import TensorParallelComm, create_process_groups, gather_full_state_dict
+        tp_group, _ = create_process_groups(world, world)
+        if a.mode == "gpu_tp_fused":
+            from kotodama_b200.parallel.tp_native import FusedTensorParallelComm
+            comm = FusedTensorParallelComm(tp_group, None)
+        else:
+            comm = TensorParallelComm(tp_group, None, sequence_parallel=True)
+        cfg = ModelConfig(**MODEL_PRESETS["smoke"], attn_res=True, attn_res_n_blocks=2)
+        shared = torch.randint(0, cfg.vocab_size, (2, 128 * world), generator=torch.Generator().manual_seed(7))
+        eng = build(cfg, device, dtype, comm)
+        losses = [float(eng.train_step([shared])["loss"]) for _ in range(a.steps)]
+        eng.check()
+        full = gather_full_state_dict(eng.model, tp_group)
+        flat = torch.cat([v.float().flatten() for _, v in sorted(full.items())])
+        if rank == 0:
+            torch.save(flat.cpu(), f"{a.out}.params.{a.mode}.pt")
+        result.update(losses=losses, fused_calls=getattr(comm, "fused_calls", 0),
+                      fallback_calls=getattr(comm, "fallback_calls", 0))
     if a.mode == "cpu_tp_autograd":
         from kotodama_b200.optim.muon import build_hybrid_optimizer
         from kotodama_b200.parallel.tp import (apply_tensor_parallelism, create_process_groups, gather_full_state_dict,

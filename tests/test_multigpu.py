@@ -24,3 +24,21 @@ def test_native_comm_matches_library_comm(tmp_path):
     pl = torch.load(f"{out}.params.gpu_library.0.pt")
     pn = torch.load(f"{out}.params.gpu_native.0.pt")
     assert float((pl - pn).norm() / pl.norm()) < 2e-2
+
+
+def test_fused_tp_kernels_match_library_tp(tmp_path):
+    """all-gather->GEMM and GEMM->reduce-scatter kernels against NCCL collectives around plain GEMMs."""
+    out = str(tmp_path / "t")
+    env_backup = dict(os.environ)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    try:
+        lib = _launch("gpu_tp_library", out, steps=3)
+        fused = _launch("gpu_tp_fused", out, steps=3)
+    finally:
+        os.environ.clear(); os.environ.update(env_backup)
+    assert fused[0]["fused_calls"] > 0 and fused[0]["fallback_calls"] == 0, fused[0]
+    for a, b in zip(lib[0]["losses"], fused[0]["losses"]):
+        assert abs(a - b) < 5e-2, (lib[0]["losses"], fused[0]["losses"])
+    pl = torch.load(f"{out}.params.gpu_tp_library.pt")
+    pf = torch.load(f"{out}.params.gpu_tp_fused.pt")
+    assert float((pl - pf).norm() / pl.norm()) < 2e-2
