@@ -63,6 +63,36 @@ def run(ops, M, N, K, mode, iters, flush):
                 ratio=round(t_lib / t_mine, 3), rel_diff=err)
 
 
+def fp8_table(ops, args, flush) -> None:
+    """Forward-shaped products of the preset: fp8 GEMM alone, with the activation quantiser, and the
+    bf16 tcgen05 GEMM / cuBLAS on the same shape."""
+    from kotodama_b200.config import MODEL_PRESETS
+    c = MODEL_PRESETS[args.model]
+    D, F = c["hidden_size"], c["intermediate_size"]
+    QKV = (c["num_attention_heads"] + 2 * c["num_kv_heads"]) * c["head_dim"]
+    T = args.tokens
+    shapes = [(T, QKV, D), (T, D, c["num_attention_heads"] * c["head_dim"]), (T, 2 * F, D), (T, D, F)]
+    if args.single:
+        shapes = [tuple(map(int, args.single[:3]))]
+    for (M, N, K) in shapes:
+        a, b = operands(M, N, K, "nt")
+        qa, sa = ops.quant_rows(a)
+        qb, sb = ops.quant_blocks(b)
+        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        t_g = time_fn(lambda: ops.gemm_fp8(qa, sa, qb, sb, 128, out=out), args.iters, flush)
+        t_q = time_fn(lambda: ops.quant_rows(a), args.iters, flush)
+        qat, sat = ops.quant_cols_t(a)
+        t_w = time_fn(lambda: ops.gemm_fp8(qat[:, :], sat, qat, sat, 1), 3, flush) if M % 128 == 0 and args.single else 0.0
+        t_b = time_fn(lambda: ops.gemm_nt(a, b, out=out), args.iters, flush)
+        t_l = time_fn(lambda: torch.matmul(a, b.t(), out=out), args.iters, flush)
+        fl = 2.0 * M * N * K
+        print(json.dumps(dict(M=M, N=N, K=K, fp8_ms=round(t_g, 4), fp8_tflops=round(fl / t_g / 1e9, 1),
+                              quant_rows_ms=round(t_q, 4), quant_gbs=round(M * K * 3 / t_q / 1e6, 1),
+                              bf16_ms=round(t_b, 4), cublas_bf16_ms=round(t_l, 4),
+                              fp8_vs_bf16=round(t_b / t_g, 3), fp8_plus_quant_vs_bf16=round(t_b / (t_g + t_q), 3))))
+    ops.check_status()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--single", nargs=4, default=None, metavar=("M", "N", "K", "MODE"))
@@ -71,11 +101,15 @@ def main() -> None:
     ap.add_argument("--model", default="3b")
     ap.add_argument("--out", default="")
     ap.add_argument("--two-cta", type=int, default=-1, help="force the CTA-pair kernel on (1) or off (0)")
+    ap.add_argument("--fp8", action="store_true", help="block-scaled e4m3 GEMM (quantisation timed separately)")
     args = ap.parse_args()
     ops = get_ops("cuda")
     if args.two_cta >= 0:
         ops.gemm_2cta = bool(args.two_cta)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    if args.fp8:
+        fp8_table(ops, args, flush)
+        return
     if args.single:
         M, N, K = map(int, args.single[:3])
         a, b = operands(M, N, K, args.single[3])

@@ -32,6 +32,7 @@ from .config import ModelConfig
 from .models.llama import KotodamaModel
 from .optim.muon import resolve_ns_coefficients
 from .ops import get_ops
+from .ops.reference import Fp8Weight
 
 _ALIGN = 64  # elements; keeps every tensor 128-byte aligned in bf16
 
@@ -242,6 +243,7 @@ class TrainEngine:
                     self.momentum[s.name] = torch.zeros(s.shape, device=self.device, dtype=dtype)
         self._wcache: dict[str, torch.Tensor] = {}
         self._gather_weights()
+        self.refresh_fp8()
 
     @classmethod
     def from_meta(cls, model: KotodamaModel, cfg: ModelConfig, *, seed: int = 0, **kw: Any) -> "TrainEngine":
@@ -250,6 +252,7 @@ class TrainEngine:
         eng = cls(model, **kw)
         eng.arena.init_weights(cfg.num_layers, seed)
         eng.comm.attach(eng)   # re-broadcast: ranks must start from identical weights
+        eng.refresh_fp8()
         return eng
 
     # ------------------------------------------------------------ helpers
@@ -268,19 +271,33 @@ class TrainEngine:
 
     def _gather_weights(self) -> None:
         m, ar = self.model, self.arena
+        # fp8: the four projections of every layer run in block-scaled e4m3 (forward, data gradient and
+        # weight gradient); masters, gradients, optimizer and everything else stay bf16/fp32
+        wrap = (lambda t: Fp8Weight(t)) if self.fp8 else (lambda t: t)
         self.layer_w = []
         for i in range(self.cfg.num_layers):
             p = f"layers.{i}."
             self.layer_w.append(dict(
-                wqkv=ar.fused(p + "attn.q_proj.weight", p + "attn.v_proj.weight"),
-                wo=ar.view(p + "attn.o_proj.weight"),
-                wgu=ar.fused(p + "ffn.gate_proj.weight", p + "ffn.up_proj.weight"),
-                wd=ar.view(p + "ffn.down_proj.weight"),
+                wqkv=wrap(ar.fused(p + "attn.q_proj.weight", p + "attn.v_proj.weight")),
+                wo=wrap(ar.view(p + "attn.o_proj.weight")),
+                wgu=wrap(ar.fused(p + "ffn.gate_proj.weight", p + "ffn.up_proj.weight")),
+                wd=wrap(ar.view(p + "ffn.down_proj.weight")),
                 g_wqkv=ar.fused(p + "attn.q_proj.weight", p + "attn.v_proj.weight", grads=True),
                 g_wo=ar.view(p + "attn.o_proj.weight", grads=True),
                 g_wgu=ar.fused(p + "ffn.gate_proj.weight", p + "ffn.up_proj.weight", grads=True),
                 g_wd=ar.view(p + "ffn.down_proj.weight", grads=True),
             ))
+
+    def refresh_fp8(self) -> None:
+        """Re-quantise the projection weights from their bf16 masters (after every optimizer step and
+        after a checkpoint load)."""
+        if not self.fp8:
+            return
+        for lw in self.layer_w:
+            for k in ("wqkv", "wo", "wgu", "wd"):
+                w = lw[k]
+                if all(d % 128 == 0 for d in w.shape):
+                    w.refresh(self.ops)
 
     def _p(self, name: str) -> torch.Tensor:
         return self.arena.view(name)
@@ -500,6 +517,7 @@ class TrainEngine:
         ops.adamw_step(ar.params[lo:hi], ar.grads[lo:hi], self.exp_avg, self.exp_avg_sq, self.opt_step,
                        ga["lr"], ga["betas"][0], ga["betas"][1], ga["eps"], ga["weight_decay"], coef)
         comm.finish_param_publish()
+        self.refresh_fp8()
         return norm
 
     def train_step(self, micro_batches: list[torch.Tensor], keep_grads: bool = True) -> dict[str, torch.Tensor]:
@@ -518,6 +536,7 @@ class TrainEngine:
     def after_load(self) -> None:
         """Hook after a checkpoint was copied into the arena (derived copies are refreshed here)."""
         self.comm.attach(self)
+        self.refresh_fp8()
 
     def check(self) -> None:
         """Raise if a kernel reported a timed-out wait."""

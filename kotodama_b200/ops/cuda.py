@@ -15,7 +15,7 @@ from typing import Optional, Sequence
 import torch
 
 from . import _build
-from .reference import TorchOps
+from .reference import Fp8Weight, TorchOps
 
 _VP = ctypes.c_void_p
 _I = ctypes.c_int
@@ -62,6 +62,9 @@ class CudaOps(TorchOps):
         self.launches += 1
         if rc != 0:
             raise KernelError(f"{what}: launcher returned {rc}")
+
+    def _call(self, fn: str, *args) -> None:
+        self._rc(getattr(self.lib, fn)(*args), fn)
 
     def status(self, device: torch.device) -> torch.Tensor:
         idx = device.index if device.index is not None else torch.cuda.current_device()
@@ -140,16 +143,71 @@ class CudaOps(TorchOps):
         self._rc(rc, "kb_gemm")
         return out
 
+    # ------------------------------------------------------------------ block-scaled fp8
+    def quant_rows(self, x):
+        M, K = x.shape
+        x = x.contiguous()
+        q = torch.empty(M, K, device=x.device, dtype=torch.float8_e4m3fn)
+        s = torch.empty(K // 128, M, device=x.device, dtype=torch.float32)
+        self._call("kb_quant_rows", _p(x), _LL(K), _p(q), _LL(K), _p(s), _I(M), _I(K), _st())
+        return q, s
+
+    def quant_blocks(self, w, transposed=False):
+        N, K = w.shape
+        w = w.contiguous()
+        dev = w.device
+        q = torch.empty(N, K, device=dev, dtype=torch.float8_e4m3fn)
+        s = torch.empty(K // 128, N // 128, device=dev, dtype=torch.float32)
+        qt = torch.empty(K, N, device=dev, dtype=torch.float8_e4m3fn) if transposed else None
+        st = torch.empty(N // 128, K // 128, device=dev, dtype=torch.float32) if transposed else None
+        self._call("kb_quant_blocks", _p(w), _LL(K), _p(q), _p(s), _p(qt), _p(st), _I(N), _I(K), _st())
+        return (q, s, qt, st) if transposed else (q, s)
+
+    def quant_cols_t(self, x):
+        M, N = x.shape
+        x = x.contiguous()
+        qt = torch.empty(N, M, device=x.device, dtype=torch.float8_e4m3fn)
+        s = torch.empty(M // 128, N, device=x.device, dtype=torch.float32)
+        self._call("kb_quant_cols_t", _p(x), _LL(N), _p(qt), _p(s), _I(M), _I(N), _st())
+        return qt, s
+
+    def gemm_fp8(self, qa, sa, qb, sb, b_gran, out=None, accumulate=False, out_dtype=torch.bfloat16, residual=None):
+        M, K = qa.shape
+        N = qb.shape[0]
+        if out is None:
+            out = torch.empty(M, N, device=qa.device, dtype=out_dtype)
+        cin = residual if residual is not None else (out if accumulate else None)
+        otype = {torch.bfloat16: 1, torch.float32: 2}[out.dtype]
+        self._call("kb_gemm_fp8", _p(qa), _p(qb), _p(sa), _p(sb), _p(out), _p(cin), _I(M), _I(N), _I(K), _LL(K), _LL(K),
+                   _LL(out.stride(0)), _I(b_gran), _I(sb.shape[1]), _I(otype), _F(1.0), _F(1.0 if cin is not None else 0.0),
+                   _p(self.status(qa.device)), _I(0), _st())
+        return out
+
     def gemm_nt(self, a, b, out=None, residual=None, accumulate=False):
+        if isinstance(b, Fp8Weight):
+            if self.fp8_ok(a.shape[0], a.shape[1], b.shape[0]) and a.dtype == torch.bfloat16 and not (
+                    accumulate and residual is not None):
+                qa, sa = self.quant_rows(a)
+                return self.gemm_fp8(qa, sa, b.q, b.s, 128, out=out, accumulate=accumulate, residual=residual)
+            b = b.w
         cin = residual if residual is not None else (out if accumulate else None)
         return self._gemm(a, b, a.shape[0], b.shape[0], a.shape[1], False, False, out, cin, 1.0, 1.0)
 
     def gemm_nn(self, a, b, out=None):
+        if isinstance(b, Fp8Weight):
+            if self.fp8_ok(a.shape[0], a.shape[1], b.shape[1]) and a.dtype == torch.bfloat16:
+                qa, sa = self.quant_rows(a)
+                return self.gemm_fp8(qa, sa, b.qt, b.st, 128, out=out)
+            b = b.w
         if self.mn_major:
             return self._gemm(a, b, a.shape[0], b.shape[1], a.shape[1], False, True, out)
         return self._gemm(a, self.transpose(b), a.shape[0], b.shape[1], a.shape[1], False, False, out)
 
-    def gemm_tn(self, a, b, out=None, accumulate=False):
+    def gemm_tn(self, a, b, out=None, accumulate=False, fp8=False):
+        if fp8 and self.fp8_ok(a.shape[0], a.shape[1], b.shape[1]) and a.dtype == torch.bfloat16:
+            qa, sa = self.quant_cols_t(a)
+            qb, sb = self.quant_cols_t(b)
+            return self.gemm_fp8(qa, sa, qb, sb, 1, out=out, accumulate=accumulate)
         cin = out if accumulate else None
         if self.mn_major:
             return self._gemm(a, b, a.shape[1], b.shape[1], a.shape[0], True, True, out, cin, 1.0, 1.0)

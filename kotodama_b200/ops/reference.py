@@ -22,15 +22,100 @@ def _f(x: torch.Tensor) -> torch.Tensor:
     return x if x.dtype in (torch.float32, torch.float64) else x.float()
 
 
+FP8_MAX = 448.0        # largest finite e4m3 value
+
+
+class Fp8Weight:
+    """A projection weight under the block-scaled fp8 recipe: the bf16 master (a view of the
+    parameter arena) plus its e4m3 copies, 128x128-block scaled - ``q``/``s`` in the weight's own
+    layout for the forward product, ``qt``/``st`` transposed for the data gradient.  ``refresh``
+    re-quantises after the optimizer has changed the master.  Passing one of these where the GEMM
+    ops expect the weight selects the fp8 path."""
+
+    def __init__(self, w: torch.Tensor) -> None:
+        self.w = w
+        self.q = self.s = self.qt = self.st = None
+
+    @property
+    def shape(self):
+        return self.w.shape
+
+    def refresh(self, ops: "TorchOps") -> None:
+        self.q, self.s, self.qt, self.st = ops.quant_blocks(self.w, transposed=True)
+
+
+def _to_e4m3(x: torch.Tensor) -> torch.Tensor:
+    return x.clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn)
+
+
 class TorchOps:
     """Backend object; ``CudaOps`` derives from it and overrides methods with kernels."""
 
     name = "torch"
 
+    # ------------------------------------------------------------------ block-scaled fp8
+    def quant_rows(self, x: torch.Tensor):
+        """``x[M,K]`` -> e4m3 ``q[M,K]`` and scales ``s[K/128, M]`` (one per row and 128 columns)."""
+        M, K = x.shape
+        xb = x.float().view(M, K // 128, 128)
+        s = xb.abs().amax(-1).clamp_min(1e-12) / FP8_MAX
+        q = _to_e4m3(xb / s[..., None]).view(M, K)
+        return q, s.t().contiguous()
+
+    def quant_blocks(self, w: torch.Tensor, transposed: bool = False):
+        """``w[N,K]`` -> e4m3 ``q[N,K]``, ``s[K/128, N/128]`` (128x128 blocks); with ``transposed``
+        also ``qt[K,N]`` and ``st[N/128, K/128]``."""
+        N, K = w.shape
+        wb = w.float().view(N // 128, 128, K // 128, 128)
+        s = wb.abs().amax((1, 3)).clamp_min(1e-12) / FP8_MAX            # [N/128, K/128]
+        q = _to_e4m3(wb / s[:, None, :, None]).view(N, K)
+        if not transposed:
+            return q, s.t().contiguous()
+        return q, s.t().contiguous(), q.t().contiguous(), s.contiguous()
+
+    def quant_cols_t(self, x: torch.Tensor):
+        """``x[M,N]`` -> e4m3 ``qt[N,M]`` and scales ``s[M/128, N]`` (one per column and 128 rows)."""
+        M, N = x.shape
+        xb = x.float().view(M // 128, 128, N)
+        s = xb.abs().amax(1).clamp_min(1e-12) / FP8_MAX                 # [M/128, N]
+        q = _to_e4m3(xb / s[:, None, :]).view(M, N)
+        return q.t().contiguous(), s.contiguous()
+
+    def gemm_fp8(self, qa, sa, qb, sb, b_gran: int, out: Optional[torch.Tensor] = None, accumulate: bool = False,
+                 out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+        """``sum_kb (qa_kb @ qb_kb^T) * sa[kb, m] * sb[kb, n // b_gran]`` with fp32 accumulation."""
+        M, K = qa.shape
+        N = qb.shape[0]
+        a = qa.float().view(M, K // 128, 128) * sa.t()[..., None]
+        sbe = sb if b_gran == 1 else sb.repeat_interleave(b_gran, dim=1)[:, :N]
+        b = qb.float().view(N, K // 128, 128) * sbe.t()[..., None]
+        r = a.view(M, K) @ b.view(N, K).t()
+        if out is None:
+            return r.to(out_dtype)
+        if accumulate:
+            out.add_(r.to(out.dtype))
+        else:
+            out.copy_(r)
+        return out
+
+    def fp8_ok(self, *dims: int) -> bool:
+        return all(d % 128 == 0 for d in dims)
+
     # ------------------------------------------------------------------ GEMM
-    def gemm_nt(self, a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None,
+    def gemm_nt(self, a: torch.Tensor, b, out: Optional[torch.Tensor] = None,
                 residual: Optional[torch.Tensor] = None, accumulate: bool = False) -> torch.Tensor:
-        """``a[M,K] @ b[N,K]^T (+ residual) -> [M,N]``; ``accumulate`` adds into ``out``."""
+        """``a[M,K] @ b[N,K]^T (+ residual) -> [M,N]``; ``accumulate`` adds into ``out``.  ``b`` may be
+        an ``Fp8Weight``: the product then runs in block-scaled fp8."""
+        if isinstance(b, Fp8Weight):
+            if self.fp8_ok(a.shape[0], a.shape[1], b.shape[0]) and not accumulate:
+                r = self.gemm_fp8(*self.quant_rows(a), b.q, b.s, 128, out_dtype=a.dtype)
+                if residual is not None:
+                    r = r + residual
+                if out is not None:
+                    out.copy_(r)
+                    return out
+                return r
+            b = b.w
         r = a @ b.t()
         if residual is not None:
             r = r + residual
@@ -42,8 +127,12 @@ class TorchOps:
             out.copy_(r)
         return out
 
-    def gemm_nn(self, a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """``a[M,K] @ b[K,N] -> [M,N]`` (data-gradient GEMM)."""
+    def gemm_nn(self, a: torch.Tensor, b, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``a[M,K] @ b[K,N] -> [M,N]`` (data-gradient GEMM); ``b`` may be an ``Fp8Weight``."""
+        if isinstance(b, Fp8Weight):
+            if self.fp8_ok(a.shape[0], a.shape[1], b.shape[1]):
+                return self.gemm_fp8(*self.quant_rows(a), b.qt, b.st, 128, out=out, out_dtype=a.dtype)
+            b = b.w
         r = a @ b
         if out is None:
             return r
@@ -51,8 +140,13 @@ class TorchOps:
         return out
 
     def gemm_tn(self, a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None,
-                accumulate: bool = False) -> torch.Tensor:
-        """``a[K,M]^T @ b[K,N] -> [M,N]`` (weight-gradient GEMM, fp32 accumulation)."""
+                accumulate: bool = False, fp8: bool = False) -> torch.Tensor:
+        """``a[K,M]^T @ b[K,N] -> [M,N]`` (weight-gradient GEMM, fp32 accumulation).  With ``fp8`` both
+        operands are quantised in 128-token tiles and the product runs in block-scaled fp8."""
+        if fp8 and self.fp8_ok(a.shape[0], a.shape[1], b.shape[1]):
+            qa, sa = self.quant_cols_t(a)
+            qb, sb = self.quant_cols_t(b)
+            return self.gemm_fp8(qa, sa, qb, sb, 1, out=out, accumulate=accumulate, out_dtype=a.dtype)
         r = (a.t() @ b)
         if out is None:
             return r

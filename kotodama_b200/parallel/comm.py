@@ -25,6 +25,11 @@ import torch
 import torch.distributed as dist
 
 
+def _fp8_kw(w: Any) -> dict:
+    """Weight gradients follow the precision of their weight: fp8 when the weight is an ``Fp8Weight``."""
+    return {} if isinstance(w, torch.Tensor) else {"fp8": True}
+
+
 class LocalComm:
     world = 1
     rank = 0
@@ -71,13 +76,13 @@ class LocalComm:
         """Backward of a row-parallel projection: all-gather(dy) -> data gradient and weight gradient."""
         dyg = self.sp_gather(dy)
         dx = ops.gemm_nn(dyg, w)
-        ops.gemm_tn(dyg, x_saved, out=g_out, accumulate=accumulate)
+        ops.gemm_tn(dyg, x_saved, out=g_out, accumulate=accumulate, **_fp8_kw(w))
         return dx
 
     def col_linear_bwd(self, ops, dy, w, x, g_out, accumulate: bool):
         """Backward of a column-parallel projection: weight gradient from the re-gathered input,
         data gradient GEMM -> reduce-scatter."""
-        ops.gemm_tn(dy, self.sp_gather(x), out=g_out, accumulate=accumulate)
+        ops.gemm_tn(dy, self.sp_gather(x), out=g_out, accumulate=accumulate, **_fp8_kw(w))
         return self.col_linear_bwd_input(ops, dy, w)
 
     # gradient reduction

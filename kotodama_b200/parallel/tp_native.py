@@ -167,7 +167,7 @@ class FusedTensorParallelComm(TensorParallelComm):
         self._ck(rc, "kb_gemm_ag")
 
     def col_linear(self, ops, x, w):
-        if not (self._usable(x) and w.dtype == torch.bfloat16 and w.is_contiguous()):
+        if not (isinstance(w, torch.Tensor) and self._usable(x) and w.dtype == torch.bfloat16 and w.is_contiguous()):
             self.fallback_calls += 1
             return super().col_linear(ops, x, w)
         rows, K = x.shape
@@ -180,7 +180,7 @@ class FusedTensorParallelComm(TensorParallelComm):
         return out
 
     def row_linear_bwd(self, ops, dy, w, x_saved, g_out, accumulate: bool):
-        if not (self._usable(dy) and w.dtype == torch.bfloat16 and w.is_contiguous()):
+        if not (isinstance(w, torch.Tensor) and self._usable(dy) and w.dtype == torch.bfloat16 and w.is_contiguous()):
             self.fallback_calls += 1
             return super().row_linear_bwd(ops, dy, w, x_saved, g_out, accumulate)
         rows, D = dy.shape
@@ -226,8 +226,8 @@ class FusedTensorParallelComm(TensorParallelComm):
         return out
 
     def _rs_usable(self, x: torch.Tensor, w: torch.Tensor) -> bool:
-        return (x.is_cuda and x.dtype == torch.bfloat16 and x.is_contiguous() and w.is_contiguous()
-                and w.dtype == torch.bfloat16 and x.shape[0] % (self.tp_size * _BM) == 0 and hasattr(self, "lib"))
+        return (isinstance(w, torch.Tensor) and x.is_cuda and x.dtype == torch.bfloat16 and x.is_contiguous()
+                and w.is_contiguous() and w.dtype == torch.bfloat16 and x.shape[0] % (self.tp_size * _BM) == 0 and hasattr(self, "lib"))
 
     def row_linear(self, ops, x, w, residual=None):
         if not self._rs_usable(x, w) or w.shape[0] % 8 or (residual is not None and not residual.is_contiguous()):

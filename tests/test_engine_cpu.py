@@ -99,3 +99,24 @@ def test_arena_keeps_reference_parameter_order_and_fused_views():
     assert torch.equal(eng.layer_w[1]["wgu"][512:], model.layers[1].ffn.up_proj.weight)
     sd = model.state_dict()
     assert "layers.0.attn.q_proj.weight" in sd and "rope_cos" not in sd
+
+
+def test_fp8_block_scaled_training_tracks_full_precision():
+    """--fp8: projections run through the block-scaled e4m3 path (quantisers + scaled GEMM, here the
+    PyTorch restatement); losses stay close to the unquantised run and fall."""
+    cfg = ModelConfig(**MODEL_PRESETS["smoke"], attn_res=True, attn_res_n_blocks=2)
+    batch = torch.randint(0, cfg.vocab_size, (2, 128), generator=torch.Generator().manual_seed(1))
+
+    def run(fp8):
+        torch.manual_seed(0)
+        eng = TrainEngine(KotodamaModel(cfg), device="cpu", dtype=torch.float32, muon_lr=0.02, adamw_lr=1e-3, fp8=fp8)
+        if fp8:
+            from kotodama_b200.ops.reference import Fp8Weight
+            assert isinstance(eng.layer_w[0]["wqkv"], Fp8Weight) and eng.layer_w[0]["wqkv"].q.dtype == torch.float8_e4m3fn
+        return [float(eng.train_step([batch])["loss"]) for _ in range(4)]
+
+    full, q = run(False), run(True)
+    assert q[-1] < q[0] - 2.0
+    for a, b in zip(full, q):
+        assert abs(a - b) < 0.05, (full, q)
+    assert full != q

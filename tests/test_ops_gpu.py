@@ -318,3 +318,70 @@ def test_flash_attention_forward(ops, B, T, H, KV):
     oref, lref = TORCH_OPS.attention_fwd(q.float(), k.float(), v.float())
     assert rel_err(o, oref) < 2e-2, rel_err(o, oref)
     assert float((lse - lref).abs().max()) < 2e-2
+
+
+# ----------------------------------------------------------------------------- block-scaled fp8
+def _fp8_inputs(M, N, K, seed=0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    x = (torch.randn(M, K, device="cuda", generator=g) * 0.7).to(torch.bfloat16)
+    w = (torch.randn(N, K, device="cuda", generator=g) * 0.05).to(torch.bfloat16)
+    # a few outliers so that tile scales differ by orders of magnitude
+    x[::37, ::53] *= 30
+    w[::11, ::29] *= 12
+    return x, w
+
+
+def test_fp8_quantisers_match_reference(ops):
+    x, w = _fp8_inputs(256, 384, 512)
+    q, s = ops.quant_rows(x)
+    qr, sr = TORCH_OPS.quant_rows(x)
+    assert torch.allclose(s, sr, rtol=1e-6) and torch.equal(q.view(torch.uint8), qr.view(torch.uint8))
+    q, s, qt, st = ops.quant_blocks(w, transposed=True)
+    qr, sr, qtr, str_ = TORCH_OPS.quant_blocks(w, transposed=True)
+    assert torch.allclose(s, sr, rtol=1e-6) and torch.allclose(st, str_, rtol=1e-6)
+    assert torch.equal(q.view(torch.uint8), qr.view(torch.uint8)) and torch.equal(qt.view(torch.uint8), qtr.view(torch.uint8))
+    qt, s = ops.quant_cols_t(x)
+    qtr, sr = TORCH_OPS.quant_cols_t(x)
+    assert torch.allclose(s, sr, rtol=1e-6) and torch.equal(qt.view(torch.uint8), qtr.view(torch.uint8))
+    ops.check_status()
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 384, 512), (1024, 5120, 3072), (384, 128, 128)])
+def test_fp8_gemm_matches_dequantised_fp32(ops, M, N, K):
+    """The kernel's promotion (per-K-block scale * partial sum, fp32) against the same sum in PyTorch fp32."""
+    x, w = _fp8_inputs(M, N, K, seed=1)
+    qa, sa = ops.quant_rows(x)
+    qb, sb = ops.quant_blocks(w)
+    got = ops.gemm_fp8(qa, sa, qb, sb, 128, out_dtype=torch.float32)
+    ref = TORCH_OPS.gemm_fp8(qa, sa, qb, sb, 128, out_dtype=torch.float32)
+    assert float((got - ref).norm() / ref.norm()) < 1e-5
+    # against the unquantised product: fp8 noise only
+    exact = x.float() @ w.float().t()
+    assert float((got - exact).norm() / exact.norm()) < 0.06
+    # per-row scales on both sides (weight-gradient form), accumulation into bf16
+    qa, sa = ops.quant_cols_t(x.t().contiguous())          # [M, K] operand with scales along K
+    qb, sb = ops.quant_cols_t(w.t().contiguous())
+    base = torch.randn(M, N, device="cuda").to(torch.bfloat16)
+    out = base.clone()
+    ops.gemm_fp8(qa, sa, qb, sb, 1, out=out, accumulate=True)
+    ref = TORCH_OPS.gemm_fp8(qa, sa, qb, sb, 1, out_dtype=torch.float32) + base.float()
+    assert float((out.float() - ref).norm() / ref.norm()) < 6e-3
+    ops.check_status()
+
+
+def test_fp8_weight_paths_in_gemm_ops(ops):
+    from kotodama_b200.ops.reference import Fp8Weight
+    x, w = _fp8_inputs(512, 768, 1024, seed=2)
+    W8 = Fp8Weight(w)
+    W8.refresh(ops)
+    y = ops.gemm_nt(x, W8)
+    assert float((y.float() - x.float() @ w.float().t()).norm() / (x.float() @ w.float().t()).norm()) < 0.06
+    dy = torch.randn(512, 768, device="cuda").to(torch.bfloat16)
+    dx = ops.gemm_nn(dy, W8)
+    ref = dy.float() @ w.float()
+    assert float((dx.float() - ref).norm() / ref.norm()) < 0.06
+    gw = torch.zeros(768, 1024, device="cuda", dtype=torch.bfloat16)
+    ops.gemm_tn(dy, x, out=gw, fp8=True)
+    ref = dy.float().t() @ x.float()
+    assert float((gw.float() - ref).norm() / ref.norm()) < 0.06
+    ops.check_status()
