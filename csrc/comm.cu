@@ -491,3 +491,88 @@ KB_API int kb_allreduce_oneshot(void* const* peer_parts, void* const* peer_flags
                                                           (bf16*)out, (unsigned long long)(limit_s * 1e9), status);
     return 0;
 }
+
+// Graph-replayable all-reduce for decode-sized activations (row-parallel projections under tensor
+// parallelism: 2 per layer and step, latency-bound).  Nothing on the host changes between calls:
+// the call number lives in device memory (`epoch_ptr`, advanced by the last block on the way
+// out), so a captured launch can be replayed.  Push protocol: every rank stores its partial into
+// slot [parity][rank] of every rank's receive buffer, the last block to finish its stores raises
+// this rank's flag [parity][rank] everywhere, all blocks then wait (bounded) for the `world` flags
+// and sum the local slots in rank order (bitwise identical on every rank) plus the residual.
+// The grid must be co-resident (<= one block per SM): blocks wait for each other's stores.
+__global__ void __launch_bounds__(256)
+allreduce_push_kernel(const uint4* __restrict__ x, long long nvec, long long slot_vecs, PeerPtrs recv, PeerPtrs flags,
+                      int world, int rank, const bf16* __restrict__ residual, bf16* __restrict__ out, int* epoch_ptr,
+                      unsigned* counters, unsigned long long limit_ns, int* status) {
+    __shared__ int ok;
+    const int epoch = *reinterpret_cast<volatile int*>(epoch_ptr) + 1;
+    const int par = epoch & 1;
+    if (threadIdx.x == 0) ok = 1;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    const long long my_slot = ((long long)par * world + rank) * slot_vecs;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+        const uint4 v = x[i];
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+            if (q < world) (reinterpret_cast<uint4*>(recv.p[q]) + my_slot)[i] = v;
+    }
+    if (last_block_done(counters) && threadIdx.x < world) {
+        __threadfence_system();
+        st_release_sys(reinterpret_cast<int*>(flags.p[threadIdx.x]) + par * 8 + rank, epoch);
+    }
+    if (threadIdx.x < world) {
+        if (!wait_flag(reinterpret_cast<const int*>(flags.p[rank]) + par * 8 + threadIdx.x, epoch, limit_ns)) {
+            atomicMax(status, (int)KB_TIMEOUT_PEER);
+            ok = 0;
+        }
+    }
+    __syncthreads();
+    if (ok) {
+        const uint4* mine = reinterpret_cast<const uint4*>(recv.p[rank]) + (long long)par * world * slot_vecs;
+        for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+            float acc[8];
+            if (residual) unpack8(ld8(residual + i * 8), acc);
+            else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+            }
+#pragma unroll
+            for (int r = 0; r < 8; ++r) {
+                if (r < world) {
+                    float t[8];
+                    const uint4 raw = __ldcg(mine + r * slot_vecs + i);
+                    unpack8(*reinterpret_cast<const bf16x8*>(&raw), t);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) acc[j] += t[j];
+                }
+            }
+            st8(out + i * 8, pack8(acc));
+        }
+    }
+    if (last_block_done(counters + 1) && threadIdx.x == 0) *epoch_ptr = epoch;
+}
+// x: this rank's partial (n bf16 elements, 16-byte aligned, n % 8 == 0); peer_recv[q]: rank q's
+// receive buffer of 2 * world * slot_elems elements; peer_flags[q]: rank q's 16 flag ints;
+// epoch_ptr / counters (2 unsigned, zero-initialised): local device memory.
+KB_API int kb_allreduce_push(const void* x, long long n, long long slot_elems, void* const* peer_recv,
+                             void* const* peer_flags, int world, int rank, const void* residual, void* out,
+                             int* epoch_ptr, unsigned* counters, double limit_s, int* status, int max_ctas,
+                             cudaStream_t st) {
+    if (world < 1 || world > 8 || (n & 7) || (slot_elems & 7) || n > slot_elems || ((uintptr_t)x & 15)) return 5;
+    PeerPtrs pr, pf;
+    for (int i = 0; i < 8; ++i) {
+        pr.p[i] = i < world ? peer_recv[i] : nullptr;
+        pf.p[i] = i < world ? peer_flags[i] : nullptr;
+    }
+    int sms = 0, dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (max_ctas < 1 || max_ctas > sms) max_ctas = sms;
+    long long blocks = ((n >> 3) + 255) / 256;
+    if (blocks < 1) blocks = 1;
+    if (blocks > max_ctas) blocks = max_ctas;
+    allreduce_push_kernel<<<(int)blocks, 256, 0, st>>>((const uint4*)x, n >> 3, slot_elems >> 3, pr, pf, world, rank,
+                                                       (const bf16*)residual, (bf16*)out, epoch_ptr, counters,
+                                                       (unsigned long long)(limit_s * 1e9), status);
+    return 0;
+}

@@ -1,0 +1,140 @@
+"""Tensor-parallel serving: one process per GPU, every rank runs the same ``ServingEngine`` on its
+shard of the heads / MLP columns and of the paged KV cache (KV heads are sharded with the
+attention heads), and the two row-parallel projections of each layer are all-reduced.
+
+* ``ServeTP`` is the helper the engine calls: ``prepare_model`` shards the projections,
+  ``row_linear`` is GEMM -> all-reduce (+ residual).  On CUDA the all-reduce is our own
+  push kernel over symmetric memory (``kb_allreduce_push``): its call counter lives in device
+  memory, so decode steps that contain it can be captured in a CUDA graph and replayed; activations
+  larger than the receive slots (long prefills) and the CPU path use the library all-reduce.
+* ranks stay in lock-step by construction: rank 0 owns the request queue, ``TPLeader.step``
+  broadcasts the requests admitted since the last step and then every rank executes the same
+  ``engine.step()``; sampling is a function of the all-reduced (bitwise identical) logits and of
+  per-request seeds, so all ranks pick the same tokens.  ``run_follower`` is the loop of ranks > 0.
+
+The reference serves one request at a time on one GPU (``serve.py:322-391``).
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Any, Optional
+
+import torch
+import torch.distributed as dist
+
+_VP, _I, _LL, _D = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_double
+
+
+class ServeTP:
+    WAIT_LIMIT_S = 20.0
+
+    def __init__(self, group: Any = None, native: Optional[bool] = None, slot_rows: int = 4096,
+                 max_ctas: int = 16) -> None:
+        self.group = group or dist.group.WORLD
+        self.size, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        self.native = native
+        self.slot_rows = slot_rows
+        self.max_ctas = max_ctas
+        self.native_calls = 0
+        self.library_calls = 0
+        self._ready = False
+
+    def prepare_model(self, model: torch.nn.Module) -> None:
+        from ..parallel.tp import apply_tensor_parallelism
+        if not any(hasattr(p, "_tp_shard_dim") for p in model.parameters()):
+            apply_tensor_parallelism(model, self.group)
+
+    # ------------------------------------------------------------------ native all-reduce
+    def _setup(self, device: torch.device, width: int, ops: Any) -> None:
+        import torch.distributed._symmetric_memory as symm_mem
+        from ..ops import _build
+        self.lib = _build.load()
+        self.ops = ops
+        self.slot_elems = self.slot_rows * width
+        self.recv = symm_mem.empty(2 * self.size * self.slot_elems, dtype=torch.bfloat16, device=device)
+        self.flags = symm_mem.empty(16, dtype=torch.int32, device=device)
+        self.flags.zero_()
+        h_r = symm_mem.rendezvous(self.recv, self.group)
+        h_f = symm_mem.rendezvous(self.flags, self.group)
+        self._handles = (h_r, h_f)
+        arr = lambda ptrs: (_VP * 8)(*([int(p) for p in ptrs] + [0] * (8 - len(ptrs))))
+        self.recv_ptrs, self.flag_ptrs = arr(h_r.buffer_ptrs), arr(h_f.buffer_ptrs)
+        self.epoch = torch.zeros(1, dtype=torch.int32, device=device)
+        self.counters = torch.zeros(2, dtype=torch.int32, device=device)
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)
+        self._ready = True
+
+    def all_reduce(self, ops: Any, y: torch.Tensor, residual: Optional[torch.Tensor]) -> torch.Tensor:
+        use_native = self.native if self.native is not None else y.is_cuda
+        if use_native and y.is_cuda and y.dtype == torch.bfloat16 and y.shape[-1] % 8 == 0:
+            if not self._ready:
+                self._setup(y.device, y.shape[-1], ops)
+            if y.numel() <= self.slot_elems and y.is_contiguous() and (residual is None or residual.is_contiguous()):
+                out = torch.empty_like(y)
+                rc = self.lib.kb_allreduce_push(
+                    _VP(y.data_ptr()), _LL(y.numel()), _LL(self.slot_elems), self.recv_ptrs, self.flag_ptrs,
+                    _I(self.size), _I(self.rank), _VP(residual.data_ptr() if residual is not None else None),
+                    _VP(out.data_ptr()), _VP(self.epoch.data_ptr()), _VP(self.counters.data_ptr()),
+                    _D(self.WAIT_LIMIT_S), _VP(ops.status(y.device).data_ptr()), _I(self.max_ctas),
+                    _VP(torch.cuda.current_stream().cuda_stream))
+                ops.launches += 1
+                if rc != 0:
+                    raise RuntimeError(f"kb_allreduce_push: launcher returned {rc}")
+                self.native_calls += 1
+                return out
+        self.library_calls += 1
+        y = y.contiguous()
+        dist.all_reduce(y, group=self.group)
+        return y if residual is None else y + residual
+
+    def row_linear(self, ops: Any, x: torch.Tensor, w: torch.Tensor, residual: Optional[torch.Tensor]) -> torch.Tensor:
+        return self.all_reduce(ops, ops.gemm_nt(x, w), residual)
+
+
+# ---------------------------------------------------------------------------- lock-step driving
+class TPLeader:
+    """Rank 0's view of a tensor-parallel engine: requests are queued here and shipped to the
+    followers at the start of the next step."""
+
+    def __init__(self, engine: Any, tp: ServeTP) -> None:
+        self.engine, self.tp = engine, tp
+        self._pending: list = []
+
+    def add_request(self, prompt: list[int], params: Any = None):
+        r = self.engine.add_request(prompt, params)
+        self._pending.append((list(prompt), params))
+        return r
+
+    def step(self):
+        msg = [{"stop": False, "new": self._pending}]
+        dist.broadcast_object_list(msg, src=dist.get_global_rank(self.tp.group, 0), group=self.tp.group)
+        self._pending = []
+        return self.engine.step()
+
+    def has_work(self) -> bool:
+        return self.engine.has_work()
+
+    def shutdown(self) -> None:
+        dist.broadcast_object_list([{"stop": True, "new": []}], src=dist.get_global_rank(self.tp.group, 0),
+                                   group=self.tp.group)
+
+    def generate(self, prompts: list[list[int]], params: Any = None) -> list[list[int]]:
+        reqs = [self.add_request(p, params) for p in prompts]
+        while self.has_work():
+            self.step()
+        return [r.generated for r in reqs]
+
+
+def run_follower(engine: Any, tp: ServeTP) -> list:
+    """Loop of the ranks other than 0: mirror the leader's admissions, run the same steps.
+    Returns the mirrored requests in admission order."""
+    reqs = []
+    while True:
+        msg = [None]
+        dist.broadcast_object_list(msg, src=dist.get_global_rank(tp.group, 0), group=tp.group)
+        if msg[0]["stop"]:
+            return reqs
+        for prompt, params in msg[0]["new"]:
+            reqs.append(engine.add_request(prompt, params))
+        engine.step()

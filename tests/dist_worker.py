@@ -90,6 +90,45 @@ def main():
             torch.save(flat.cpu(), f"{a.out}.params.{a.mode}.pt")
         result.update(losses=losses, fused_calls=getattr(comm, "fused_calls", 0),
                       fallback_calls=getattr(comm, "fallback_calls", 0))
+    if a.mode in ("cpu_tp_serve", "gpu_tp_serve"):
+        import copy
+        from kotodama_b200.serve.engine import SamplingParams, ServingEngine
+        from kotodama_b200.serve.tp import ServeTP, TPLeader, run_follower
+        cfg = ModelConfig(**MODEL_PRESETS["smoke"], attn_res=True, attn_res_n_blocks=2)
+        torch.manual_seed(0)
+        full = KotodamaModel(cfg)
+        prompts = [[(7 * i + 3 * j) % cfg.vocab_size for j in range(5 + 3 * i)] for i in range(5)]
+        params = SamplingParams(max_new_tokens=6, temperature=0.0)
+        ref = ServingEngine(copy.deepcopy(full), device=device, dtype=dtype, max_batch=8, max_ctx=256).generate(prompts, params)
+        tp = ServeTP()
+        eng = ServingEngine(full, device=device, dtype=dtype, max_batch=8, max_ctx=256, tp=tp)
+        if rank == 0:
+            lead = TPLeader(eng, tp)
+            gen = lead.generate(prompts, params)
+            lead.shutdown()
+        else:
+            gen = [r.generated for r in run_follower(eng, tp)]
+        # every rank ran the same requests: compare what each rank generated
+        gathered = [None] * world
+        dist.all_gather_object(gathered, [list(g) for g in gen])
+        result.update(ref=ref, tp=gathered[0], ranks_equal=all(g == gathered[0] for g in gathered),
+                      native_calls=tp.native_calls, library_calls=tp.library_calls,
+                      local_heads=eng.H, local_kv=eng.KV)
+        if cuda:
+            eng.ops.check_status()
+            # the all-reduce kernel alone, against an exact fp32 sum of the gathered partials
+            g = torch.Generator(device="cuda").manual_seed(10 + rank)
+            y = torch.randn(48, cfg.hidden_size, device="cuda", generator=g).to(torch.bfloat16)
+            res = torch.randn(48, cfg.hidden_size, device="cuda", generator=torch.Generator(device="cuda").manual_seed(5)).to(torch.bfloat16)
+            parts = [torch.empty_like(y) for _ in range(world)]
+            dist.all_gather(parts, y)
+            exact = (sum(p.float() for p in parts) + res.float()).to(torch.bfloat16)
+            errs = []
+            for _ in range(5):                      # repeated calls walk through both parities
+                got = tp.all_reduce(eng.ops, y, res)
+                errs.append(float((got.float() - exact.float()).abs().max()))
+            eng.ops.check_status()
+            result.update(allreduce_max_err=max(errs))
     if a.mode == "cpu_tp_autograd":
         from kotodama_b200.optim.muon import build_hybrid_optimizer
         from kotodama_b200.parallel.tp import (apply_tensor_parallelism, create_process_groups, gather_full_state_dict,

@@ -76,3 +76,14 @@ def test_tensor_parallel_allreduce_mode_and_autograd_api(tmp_path):
         for a, b in zip(res[0]["losses"], losses):
             assert abs(a - b) < 2e-3, (mode, res[0]["losses"], losses)
         assert abs(res[0]["checksum"] - checksum) / checksum < 5e-4, mode
+
+
+def test_tensor_parallel_serving_matches_single_process(tmp_path):
+    """TP=2 serving over gloo: sharded heads / KV cache / MLP, all-reduced row projections, leader and
+    follower in lock-step - same greedy tokens as the unsharded engine (fp32)."""
+    res = _launch("cpu_tp_serve", str(tmp_path / "s"))
+    for r in res:
+        assert r["ranks_equal"]
+        assert r["tp"] == r["ref"], (r["tp"], r["ref"])
+        assert r["local_heads"] == 2 and r["local_kv"] == 1
+        assert r["library_calls"] > 0 and r["native_calls"] == 0

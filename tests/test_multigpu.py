@@ -42,3 +42,21 @@ def test_fused_tp_kernels_match_library_tp(tmp_path):
     pl = torch.load(f"{out}.params.gpu_tp_library.pt")
     pf = torch.load(f"{out}.params.gpu_tp_fused.pt")
     assert float((pl - pf).norm() / pl.norm()) < 2e-2
+
+
+def test_tensor_parallel_serving_native_allreduce(tmp_path):
+    """TP=2 serving on two GPUs: decode steps run from CUDA graphs that contain the push all-reduce
+    kernel; ranks stay in lock-step; the kernel matches an exact fp32 sum."""
+    env_backup = dict(os.environ)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    try:
+        res = _launch("gpu_tp_serve", str(tmp_path / "s"))
+    finally:
+        os.environ.clear(); os.environ.update(env_backup)
+    for r in res:
+        assert r["ranks_equal"]
+        assert r["native_calls"] > 0
+        assert r["allreduce_max_err"] == 0.0
+        assert all(len(t) == 6 for t in r["tp"])
+    same = sum(a == b for ta, tb in zip(res[0]["tp"], res[0]["ref"]) for a, b in zip(ta, tb))
+    assert same >= 0.6 * 30, (res[0]["tp"], res[0]["ref"])     # bf16: sharded sums round differently
