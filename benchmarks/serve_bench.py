@@ -5,6 +5,10 @@ each, paged KV cache with 16-token pages.  Reports prefill tok/s, decode tok/s a
 per-token (decode step) latency, all timed with CUDA events around the engine's steps.
 
     python benchmarks/serve_bench.py --model 3b --requests 64 --new-tokens 256
+    python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 benchmarks/serve_bench.py ...
+
+Under ``torchrun`` the engine is tensor-parallel over all ranks (every rank runs the same
+requests; rank 0 prints; times are the slowest rank's).
 """
 from __future__ import annotations
 
@@ -31,13 +35,26 @@ def main() -> None:
     ap.add_argument("--max-prompt", type=int, default=2048)
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--device", default="cuda")
+    ap.add_argument("--op-times", default="", help="after the run: per-op device times of 8 eager decode steps, to this file")
     a = ap.parse_args()
     cuda = a.device == "cuda"
+    world, rank = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0"))
+    tp = None
+    if world > 1:
+        import torch.distributed as dist
+        from kotodama_b200.serve.tp import ServeTP
+        if cuda:
+            torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
+            a.device = f"cuda:{torch.cuda.current_device()}"
+            dist.init_process_group("nccl", device_id=torch.device(a.device))
+        else:
+            dist.init_process_group("gloo")
+        tp = ServeTP()
     cfg = ModelConfig(**MODEL_PRESETS[a.model], attn_res=True, attn_res_n_blocks=7 if a.model != "tiny" else 2)
     with torch.device("meta"):
         model = KotodamaModel(cfg)
     eng = ServingEngine(model, device=a.device, dtype=torch.bfloat16 if cuda else torch.float32,
-                        max_batch=a.requests, max_ctx=a.max_prompt + a.new_tokens + 16)
+                        max_batch=a.requests, max_ctx=a.max_prompt + a.new_tokens + 16, tp=tp)
     eng.arena.init_weights(cfg.num_layers, a.seed)
     g = torch.Generator().manual_seed(a.seed)
     lens = torch.randint(a.min_prompt, a.max_prompt + 1, (a.requests,), generator=g).tolist()
@@ -51,6 +68,7 @@ def main() -> None:
     t0 = time.perf_counter()
     eng.step()                       # admits and prefills every request, then one decode step
     sync()
+    print(f"[rank {rank}] prefill + first step done in {time.perf_counter() - t0:.2f}s", file=sys.stderr, flush=True)
     t_first = time.perf_counter() - t0
     step_ms = []
     while eng.has_work():
@@ -59,6 +77,25 @@ def main() -> None:
         eng.step()
         sync()
         step_ms.append((time.perf_counter() - t) * 1e3)
+    if a.op_times and cuda:
+        # a second, eager pass (no graphs) over a few decode steps with every op bracketed by events
+        from kotodama_b200.utils.optimer import TimedOps
+        for p_ in prompts:
+            eng.add_request(p_, SamplingParams(max_new_tokens=12, temperature=0.0))
+        eng.step()
+        eng.use_cuda_graphs = False
+        plain = eng.ops
+        eng.ops = TimedOps(plain)
+        n_steps = 0
+        while eng.has_work() and n_steps < 8:
+            eng.step()
+            n_steps += 1
+        if rank == 0:
+            with open(a.op_times, "w") as fh:
+                fh.write(eng.ops.table(max(n_steps, 1)) + "\n")
+        eng.ops = plain
+        while eng.has_work():
+            eng.step()
     total_decode_s = sum(step_ms) / 1e3
     decode_tokens = sum(len(r.generated) for r in reqs) - 2 * len(reqs)   # minus prefill token and first step
     out = {"model": a.model, "requests": a.requests, "prompt_tokens": sum(lens), "new_tokens": a.new_tokens,
@@ -68,10 +105,24 @@ def main() -> None:
            "p50_token_latency_ms": round(statistics.median(step_ms), 3) if step_ms else None,
            "p95_token_latency_ms": round(sorted(step_ms)[int(0.95 * (len(step_ms) - 1))], 3) if step_ms else None,
            "kernel_launches": getattr(eng.ops, "launches", None),
-           "attention_library_calls": getattr(eng.ops, "attention_library_calls", 0)}
+           "attention_library_calls": getattr(eng.ops, "attention_library_calls", 0), "tp": world}
+    if tp is not None:
+        out.update(native_allreduce_calls=tp.native_calls, library_allreduce_calls=tp.library_calls)
     if hasattr(eng.ops, "check_status"):
         eng.ops.check_status()
-    print(json.dumps(out))
+    if tp is not None:
+        import torch.distributed as dist
+        t = torch.tensor([out["prefill_plus_first_step_s"], total_decode_s, statistics.median(step_ms)],
+                         dtype=torch.float64, device=a.device if cuda else "cpu")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        out["prefill_plus_first_step_s"] = round(float(t[0]), 3)
+        out["decode_tok_s"] = round(decode_tokens / max(float(t[1]), 1e-9), 1)
+        out["p50_token_latency_ms"] = round(float(t[2]), 3)
+        dist.barrier()
+    if rank == 0:
+        print(json.dumps(out))
+    if tp is not None:
+        dist.destroy_process_group()
 
 
 if __name__ == "__main__":

@@ -226,6 +226,8 @@ class ServingEngine:
         logits = self._forward(ids, pos, slots, None, torch.tensor([n - 1], device=self.device))
         r.ctx_len = n
         tok = int(sample_tokens(logits, [r], self.ops)[0])
+        if self.tp is not None:
+            tok = self.tp.sync_tokens([tok], self.device)[0]
         self._accept(r, tok)
         self.stats["prefill_tokens"] += n
 
@@ -296,6 +298,8 @@ class ServingEngine:
         else:
             logits = self._forward(st["ids"], st["pos"], st["slots"], decode, st["rows"])
             toks = sample_tokens(logits, reqs, self.ops).tolist()
+        if self.tp is not None:
+            toks = self.tp.sync_tokens(toks, self.device)
         for r, t in zip(reqs, toks):
             r.ctx_len += 1
             self._accept(r, int(t))

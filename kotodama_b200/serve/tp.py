@@ -88,6 +88,14 @@ class ServeTP:
         dist.all_reduce(y, group=self.group)
         return y if residual is None else y + residual
 
+    def sync_tokens(self, toks: Any, device: torch.device) -> list[int]:
+        """Rank 0's sampled tokens for every rank.  Replicated work is not bitwise identical across
+        ranks (split-K products add in atomic order), so near-ties could otherwise be broken
+        differently and the ranks' request sets would drift apart."""
+        t = torch.as_tensor(toks, dtype=torch.int64).to(device)
+        dist.broadcast(t, src=dist.get_global_rank(self.group, 0), group=self.group)
+        return t.tolist()
+
     def row_linear(self, ops: Any, x: torch.Tensor, w: torch.Tensor, residual: Optional[torch.Tensor]) -> torch.Tensor:
         return self.all_reduce(ops, ops.gemm_nt(x, w), residual)
 
@@ -100,6 +108,9 @@ class TPLeader:
     def __init__(self, engine: Any, tp: ServeTP) -> None:
         self.engine, self.tp = engine, tp
         self._pending: list = []
+
+    def __getattr__(self, name: str) -> Any:        # everything else (cache, stats, ...) is the engine's
+        return getattr(self.engine, name)
 
     def add_request(self, prompt: list[int], params: Any = None):
         r = self.engine.add_request(prompt, params)

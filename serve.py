@@ -2,6 +2,10 @@
 """Inference server entry point.
 
     python serve.py --checkpoint checkpoints/run/step_00045775.pt [--device cuda] [--host 0.0.0.0] [--port 2222]
+    torchrun --nproc-per-node 8 --master-addr 127.0.0.1 serve.py --model_size 3b ...    # tensor-parallel
+
+Under ``torchrun`` the model is sharded over the ranks (tensor parallelism: heads, KV cache and MLP
+columns); rank 0 hosts the HTTP app and drives the other ranks in lock-step.
 
 Same flags as the reference server (``serve.py:601-615``: ``--checkpoint --device --compile --host
 --port``; ``--compile`` is accepted and ignored, the native kernel path is always on) plus the
@@ -69,10 +73,28 @@ def main() -> None:
     args = ap.parse_args()
     logging.basicConfig(level=logging.INFO, format="%(asctime)s %(levelname)s %(name)s: %(message)s")
     device = "cuda" if args.device == "cuda" and torch.cuda.is_available() else "cpu"
+    world, rank = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0"))
+    tp = None
+    if world > 1:
+        import torch.distributed as dist
+        from kotodama_b200.serve.tp import ServeTP, TPLeader, run_follower
+        local = int(os.environ.get("LOCAL_RANK", rank))
+        if device == "cuda":
+            torch.cuda.set_device(local)
+            device = f"cuda:{local}"
+            dist.init_process_group("nccl", device_id=torch.device(device))
+        else:
+            dist.init_process_group("gloo")
+        tp = ServeTP()
     model = load_model(args.checkpoint, args.model_size, args.attn_res_boundaries, args.attn_res_n_blocks,
                        not args.no_attn_res, args.random_init)
-    engine = ServingEngine(model, device=device, dtype=torch.bfloat16 if device == "cuda" else torch.float32,
-                           max_batch=args.max_batch, max_ctx=args.max_ctx)
+    engine = ServingEngine(model, device=device, dtype=torch.bfloat16 if device.startswith("cuda") else torch.float32,
+                           max_batch=args.max_batch, max_ctx=args.max_ctx, tp=tp)
+    if tp is not None and rank > 0:
+        run_follower(engine, tp)
+        return
+    if tp is not None:
+        engine = TPLeader(engine, tp)
     tok = load_tokenizer(args.tokenizer)
     logger.info("Device %s, tokenizer %s, paged KV cache with %d pages", device, type(tok).__name__,
                 engine.cache.num_pages)
