@@ -80,18 +80,31 @@ def main() -> None:
     if a.op_times and cuda:
         # a second, eager pass (no graphs) over a few decode steps with every op bracketed by events
         from kotodama_b200.utils.optimer import TimedOps
-        for p_ in prompts:
-            eng.add_request(p_, SamplingParams(max_new_tokens=12, temperature=0.0))
-        eng.step()
         eng.use_cuda_graphs = False
         plain = eng.ops
         eng.ops = TimedOps(plain)
+        for p_ in prompts[:16]:
+            eng.add_request(p_, SamplingParams(max_new_tokens=12, temperature=0.0))
+        sync()
+        t = time.perf_counter()
+        eng.step()                   # 16 prefills + one decode step
+        sync()
+        wall_prefill = time.perf_counter() - t
+        table_prefill = eng.ops.table(1)
+        eng.ops.reset()
         n_steps = 0
+        sync()
+        t = time.perf_counter()
         while eng.has_work() and n_steps < 8:
             eng.step()
             n_steps += 1
+        sync()
+        wall_decode = (time.perf_counter() - t) / max(n_steps, 1)
         if rank == 0:
             with open(a.op_times, "w") as fh:
+                fh.write(f"== 16 prefills ({sum(lens[:16])} tokens) + 1 decode step, eager: wall {wall_prefill * 1e3:.1f} ms\n")
+                fh.write(table_prefill + "\n\n")
+                fh.write(f"== decode step (batch 16), eager, mean of {n_steps}: wall {wall_decode * 1e3:.2f} ms\n")
                 fh.write(eng.ops.table(max(n_steps, 1)) + "\n")
         eng.ops = plain
         while eng.has_work():
