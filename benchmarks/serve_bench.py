@@ -36,6 +36,8 @@ def main() -> None:
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--device", default="cuda")
     ap.add_argument("--passes", type=int, default=2, help="2: report the second (warm) pass, the first one separately")
+    ap.add_argument("--profile-decode-step", type=int, default=-1,
+                    help="bracket this decode step of the last pass with cudaProfilerStart/Stop (ncu --profile-from-start off)")
     ap.add_argument("--op-times", default="", help="after the run: per-op device times of 8 eager decode steps, to this file")
     a = ap.parse_args()
     cuda = a.device == "cuda"
@@ -65,7 +67,7 @@ def main() -> None:
     sync = torch.cuda.synchronize if cuda else (lambda: None)
     import time
 
-    def one_pass():
+    def one_pass(profile_step: int = -1):
         """The whole workload once: admit + prefill all requests, decode to completion."""
         before = dict(eng.stats)
         reqs = [eng.add_request(p, SamplingParams(max_new_tokens=a.new_tokens, temperature=0.0)) for p in prompts]
@@ -78,16 +80,21 @@ def main() -> None:
         step_ms = []
         while eng.has_work():
             sync()
+            prof = cuda and len(step_ms) == profile_step
+            if prof:
+                torch.cuda.profiler.start()
             t = time.perf_counter()
             eng.step()
             sync()
             step_ms.append((time.perf_counter() - t) * 1e3)
+            if prof:
+                torch.cuda.profiler.stop()
         decode_tokens = sum(len(r.generated) for r in reqs) - 2 * len(reqs)   # minus prefill token and first step
         return dict(t_first=t_first, step_ms=step_ms, decode_tokens=decode_tokens,
                     prefill_s=eng.stats["prefill_s"] - before["prefill_s"])
 
     cold = one_pass()                    # first pass: allocator growth, graph capture, first-use set-up
-    res = one_pass() if a.passes > 1 else cold
+    res = one_pass(a.profile_decode_step) if a.passes > 1 else cold
     t_first, step_ms, decode_tokens = res["t_first"], res["step_ms"], res["decode_tokens"]
     if a.op_times and cuda:
         # a second, eager pass (no graphs) over a few decode steps with every op bracketed by events

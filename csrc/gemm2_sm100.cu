@@ -10,6 +10,7 @@
 // the leader CTA only), warps 2-5 = epilogue.  Same operand majors, batching and fused
 // alpha*acc + beta*Cin epilogue as the one-CTA kernel.
 #include <cuda.h>
+#include <stdlib.h>
 
 #include "tc.cuh"
 
@@ -20,7 +21,9 @@ constexpr int BN = 256;            // tile columns (128 staged per CTA)
 constexpr int BNH = 128;
 constexpr int BK = 64, STAGES = 6;
 constexpr int A_STAGE = BM * BK * 2, B_STAGE = BNH * BK * 2;
-constexpr int SMEM_BYTES = STAGES * (A_STAGE + B_STAGE) + 1024 + 256;
+constexpr int EPI_PITCH = 144;                      // staged row: 64 bf16 + 16 bytes (bank spread)
+constexpr int EPI_WARP_BYTES = 32 * EPI_PITCH;
+constexpr int SMEM_BYTES = STAGES * (A_STAGE + B_STAGE) + 1024 + 256 + 4 * EPI_WARP_BYTES;
 constexpr int GROUP_M = 8;
 
 struct Gemm2Params {
@@ -32,6 +35,8 @@ struct Gemm2Params {
     long long ldc, c_batch_stride, ldcin, cin_batch_stride;
     int* status;
     int sym_upper;             // square symmetric result: tiles strictly below the diagonal are skipped
+    int group_m;               // raster: tiles are visited in column sweeps over groups of this many tile rows
+    int epi_staged;            // 16-bit output without addend: transpose chunks through shared memory, store 128-byte row segments
 };
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -84,14 +89,15 @@ __device__ __forceinline__ void commit2(uint32_t bar_cluster_addr) {
                  : "memory");
 }
 
-__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& b, int& tm, int& tn) {
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& b, int& tm, int& tn,
+                                            int group_m = GROUP_M) {
     const int per_batch = tiles_m * tiles_n;
     b = tile / per_batch;
     int t = tile % per_batch;
-    const int group = GROUP_M * tiles_n;
+    const int group = group_m * tiles_n;
     const int g = t / group;
-    const int first_m = g * GROUP_M;
-    const int gm = min(GROUP_M, tiles_m - first_m);
+    const int first_m = g * group_m;
+    const int gm = min(group_m, tiles_m - first_m);
     t -= g * group;
     tm = first_m + t % gm;
     tn = t / gm;
@@ -190,7 +196,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
             bool ok = true;
             for (int tile = pair; tile < num_tiles && ok; tile += npairs) {
                 int b, tm, tn;
-                tile_coords(tile, tiles_m, tiles_n, b, tm, tn);
+                tile_coords(tile, tiles_m, tiles_n, b, tm, tn, p.group_m);
                 if (p.sym_upper && tn * BN + BN <= tm * 2 * BM) continue;
                 const int m0 = tm * 2 * BM + (int)rank * BM, n0 = tn * BN + (int)rank * BNH;
                 for (int kb = 0; kb < kblocks; ++kb) {
@@ -231,7 +237,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
             for (int tile = pair; tile < num_tiles && ok; tile += npairs) {
                 if (p.sym_upper) {
                     int b_, tm_, tn_;
-                    tile_coords(tile, tiles_m, tiles_n, b_, tm_, tn_);
+                    tile_coords(tile, tiles_m, tiles_n, b_, tm_, tn_, p.group_m);
                     if (tn_ * BN + BN <= tm_ * 2 * BM) continue;
                 }
                 const int buf = it & 1;
@@ -278,7 +284,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         bool ok = true;
         for (int tile = pair; tile < num_tiles && ok; tile += npairs) {
             int b, tm, tn;
-            tile_coords(tile, tiles_m, tiles_n, b, tm, tn);
+            tile_coords(tile, tiles_m, tiles_n, b, tm, tn, p.group_m);
             if (p.sym_upper && tn * BN + BN <= tm * 2 * BM) continue;
             const int buf = it & 1;
             const uint32_t acc_phase = (it >> 1) & 1;
@@ -291,6 +297,48 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
             tc::tc_fence_after();
             const int row = tm * 2 * BM + (int)rank * BM + quarter * 32 + lane;
             const uint32_t taddr = tmem_base + buf * BN + ((uint32_t)(quarter * 32) << 16);
+            if (p.epi_staged) {
+                // no addend, 16-bit output: each 32x64 chunk goes through shared memory so that a warp
+                // store covers four 128-byte row segments instead of 32 scattered 16-byte pieces
+                uint8_t* stg = smem + STAGES * (A_STAGE + B_STAGE) + 256 + (warp - 2) * EPI_WARP_BYTES;
+                const int row0 = tm * 2 * BM + (int)rank * BM + quarter * 32;
+                uint16_t* obase = reinterpret_cast<uint16_t*>(p.C) + (long long)b * p.c_batch_stride + (long long)row0 * p.ldc;
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN; c0 += 64) {
+                    uint32_t acc[64];
+                    tc::tmem_ld32(taddr + c0, acc);
+                    tc::tmem_ld32(taddr + c0 + 32, acc + 32);
+                    tc::tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        uint4 o;
+                        if (p.out_type == 1) {
+                            __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+                            for (int i = 0; i < 4; ++i)
+                                op[i] = __floats2bfloat162_rn(p.alpha * __uint_as_float(acc[8 * j + 2 * i]),
+                                                              p.alpha * __uint_as_float(acc[8 * j + 2 * i + 1]));
+                        } else {
+                            __half2* op = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+                            for (int i = 0; i < 4; ++i)
+                                op[i] = __floats2half2_rn(p.alpha * __uint_as_float(acc[8 * j + 2 * i]),
+                                                          p.alpha * __uint_as_float(acc[8 * j + 2 * i + 1]));
+                        }
+                        *reinterpret_cast<uint4*>(stg + lane * EPI_PITCH + j * 16) = o;
+                    }
+                    __syncwarp();
+                    const int seg = lane & 7, col = tn * BN + c0 + seg * 8;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const int rr = i * 4 + (lane >> 3);
+                        const uint4 v = *reinterpret_cast<const uint4*>(stg + rr * EPI_PITCH + seg * 16);
+                        if (row0 + rr < p.M && col < p.N)
+                            *reinterpret_cast<uint4*>(obase + (long long)rr * p.ldc + col) = v;
+                    }
+                    __syncwarp();
+                }
+            } else
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 32) {
                 uint32_t acc[32];
@@ -402,6 +450,18 @@ KB_API int kb_gemm_2cta(const void* A, const void* B, void* C, const void* Cin, 
     p.ldc = ldc; p.c_batch_stride = c_bs; p.ldcin = ldcin; p.cin_batch_stride = cin_bs;
     p.status = status;
     p.sym_upper = sym_upper;
+    {
+        static int group_m = 0, staged = -1;
+        if (!group_m) {
+            const char* g = getenv("KB_GEMM2_GROUP_M");
+            group_m = g ? atoi(g) : GROUP_M;
+            if (group_m < 1) group_m = GROUP_M;
+            const char* e = getenv("KB_GEMM2_EPI_STAGED");
+            staged = e ? atoi(e) : 1;
+        }
+        p.group_m = group_m;
+        p.epi_staged = staged && !Cin && out_type != 2 && !(N & 7) && !(ldc & 7) && !(c_bs & 7);
+    }
     int sms = 0, dev = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
