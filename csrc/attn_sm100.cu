@@ -214,21 +214,27 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (ok && tc::mbar_wait(o_done, (n_tiles - 1) & 1, abort_flag)) {
             tc::tc_fence_after();
             const float inv = 1.f / l;
+            // T need not be a multiple of the tile: rows past the end of this sequence (zero-filled by
+            // TMA, or the first rows of the next sequence) are computed but never stored; for the valid
+            // rows the causal mask already excludes every key at or beyond the end
+            const bool valid = qt * BQ + r < p.T;
             __nv_bfloat16* dst = p.out + ((size_t)(row0 + r) * p.H + head) * HD;
 #pragma unroll 1
             for (int c = 0; c < HD; c += 32) {
                 uint32_t o[32];
                 tc::tmem_ld32(tmem_o + lane_base + c, o);
                 tc::tmem_ld_wait();
+                if (valid) {
 #pragma unroll
-                for (int i = 0; i < 32; i += 8) {
-                    float f8[8];
+                    for (int i = 0; i < 32; i += 8) {
+                        float f8[8];
 #pragma unroll
-                    for (int e = 0; e < 8; ++e) f8[e] = __uint_as_float(o[i + e]) * inv;
-                    st8(dst + c + i, pack8(f8));
+                        for (int e = 0; e < 8; ++e) f8[e] = __uint_as_float(o[i + e]) * inv;
+                        st8(dst + c + i, pack8(f8));
+                    }
                 }
             }
-            p.lse[((size_t)b * p.H + head) * p.T + qt * BQ + r] = (m_used + log2f(l)) * 0.6931471805599453f;
+            if (valid) p.lse[((size_t)b * p.H + head) * p.T + qt * BQ + r] = (m_used + log2f(l)) * 0.6931471805599453f;
         } else if (ok && lane == 0) {
             atomicMax(p.status, (int)KB_TIMEOUT_EPI);
         }
@@ -278,7 +284,7 @@ int make_rows_tmap(CUtensorMap* m, const void* base, long long rows, long long c
 KB_API int kb_flash_fwd(const void* q, long long q_stride, int q_cols, int q_col0, const void* k, long long k_stride,
                         int k_cols, int k_col0, const void* v, long long v_stride, int v_cols, int v_col0, void* out,
                         float* lse, int B, int T, int H, int KV, int hd, float scale, int* status, cudaStream_t st) {
-    if (hd != HD || T % BQ != 0 || H % KV != 0) return 5;
+    if (hd != HD || T < 1 || H % KV != 0) return 5;
     if ((q_stride & 7) || (k_stride & 7) || (v_stride & 7) || (q_col0 & 63) || (k_col0 & 63) || (v_col0 & 63)) return 6;
     if (((uintptr_t)q & 15) || ((uintptr_t)k & 15) || ((uintptr_t)v & 15)) return 6;
     static bool attr_set = false;
@@ -301,7 +307,7 @@ KB_API int kb_flash_fwd(const void* q, long long q_stride, int q_cols, int q_col
     p.lse = lse;
     p.q_col0 = q_col0; p.k_col0 = k_col0; p.v_col0 = v_col0;
     p.status = status;
-    dim3 grid(T / BQ, H, B);
+    dim3 grid((T + BQ - 1) / BQ, H, B);
     flash_fwd_kernel<<<grid, 160, SMEM_BYTES, st>>>(tmQ, tmK, tmV, p);
     return 0;
 }

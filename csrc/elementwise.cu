@@ -917,18 +917,21 @@ KB_API int kb_mirror_upper16(void* a, int R, long long ld, int batch, long long 
     return 0;
 }
 
-// dst = bf16(src + beta * addend)  (addend optional): finishes a split-K GEMM.
-__global__ void f32_to_bf16_add_kernel(const float* __restrict__ src, const bf16* __restrict__ addend, float beta,
-                                       bf16* __restrict__ dst, long long n) {
+// dst = bf16(src + beta * addend)  (addend optional): finishes a split-K GEMM.  With `rezero` the
+// fp32 workspace is cleared on the way out, so the next split-K product that accumulates into it
+// needs no separate fill.
+__global__ void f32_to_bf16_add_kernel(float* __restrict__ src, const bf16* __restrict__ addend, float beta,
+                                       bf16* __restrict__ dst, long long n, int rezero) {
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
         float v = src[i];
+        if (rezero) src[i] = 0.f;
         if (addend) v += beta * __bfloat162float(addend[i]);
         dst[i] = __float2bfloat16(v);
     }
 }
-KB_API int kb_f32_to_bf16_add(const float* src, const void* addend, float beta, void* dst, long long n,
+KB_API int kb_f32_to_bf16_add(float* src, const void* addend, float beta, void* dst, long long n, int rezero,
                               cudaStream_t st) {
-    f32_to_bf16_add_kernel<<<ew_grid(n, 256), 256, 0, st>>>(src, (const bf16*)addend, beta, (bf16*)dst, n);
+    f32_to_bf16_add_kernel<<<ew_grid(n, 256), 256, 0, st>>>(src, (const bf16*)addend, beta, (bf16*)dst, n, rezero);
     return 0;
 }
 

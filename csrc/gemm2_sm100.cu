@@ -114,7 +114,9 @@ template <> __device__ __forceinline__ __half f2h<__half>(float x) { return __fl
 
 template <typename T>
 __device__ __forceinline__ void store32_16(T* dst, const T* cin, const uint32_t* acc, float alpha, float beta,
-                                           int ncols, bool vec_ok) {
+                                           int ncols, bool vec_ok, T* mdst = nullptr, long long mld = 0) {
+    // mdst (symmetric results): this lane's element (row, col + j) is also written to (col + j, row);
+    // for a fixed j the 32 lanes of the warp then write 32 consecutive elements of one row.
     if (ncols == 32 && vec_ok) {
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -132,12 +134,17 @@ __device__ __forceinline__ void store32_16(T* dst, const T* cin, const uint32_t*
 #pragma unroll
             for (int i = 0; i < 8; ++i) op[i] = f2h<T>(v[i]);
             *reinterpret_cast<uint4*>(dst + 8 * j) = o;
+            if (mdst) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) mdst[(long long)(8 * j + i) * mld] = op[i];
+            }
         }
     } else {
         for (int j = 0; j < ncols; ++j) {
             float v = alpha * __uint_as_float(acc[j]);
             if (cin) v += beta * h2f<T>(cin[j]);
             dst[j] = f2h<T>(v);
+            if (mdst) mdst[(long long)j * mld] = f2h<T>(v);
         }
     }
 }
@@ -297,6 +304,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
             tc::tc_fence_after();
             const int row = tm * 2 * BM + (int)rank * BM + quarter * 32 + lane;
             const uint32_t taddr = tmem_base + buf * BN + ((uint32_t)(quarter * 32) << 16);
+            const bool mirror = p.sym_upper && tn > tm;     // pair tiles are 256 x 256: tn > tm is strictly above the diagonal
             if (p.epi_staged) {
                 // no addend, 16-bit output: each 32x64 chunk goes through shared memory so that a warp
                 // store covers four 128-byte row segments instead of 32 scattered 16-byte pieces
@@ -309,6 +317,19 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
                     tc::tmem_ld32(taddr + c0, acc);
                     tc::tmem_ld32(taddr + c0 + 32, acc + 32);
                     tc::tmem_ld_wait();
+                    if (mirror && row0 + lane < p.M) {
+                        // symmetric result, tile above the diagonal: element (row, col) also goes to (col, row)
+                        uint16_t* mb = reinterpret_cast<uint16_t*>(p.C) + (long long)b * p.c_batch_stride + row0 + lane;
+#pragma unroll
+                        for (int j = 0; j < 64; ++j) {
+                            const int cc = tn * BN + c0 + j;
+                            if (cc < p.N) {
+                                const float v = p.alpha * __uint_as_float(acc[j]);
+                                mb[(long long)cc * p.ldc] = p.out_type == 1 ? __bfloat16_as_ushort(__float2bfloat16(v))
+                                                                            : __half_as_ushort(__float2half(v));
+                            }
+                        }
+                    }
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
                         uint4 o;
@@ -363,11 +384,15 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
                             __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + off;
                             const __nv_bfloat16* cin =
                                 p.Cin ? reinterpret_cast<const __nv_bfloat16*>(p.Cin) + offin : nullptr;
-                            store32_16<__nv_bfloat16>(dst, cin, acc, p.alpha, p.beta, ncols, vec);
+                            store32_16<__nv_bfloat16>(dst, cin, acc, p.alpha, p.beta, ncols, vec,
+                                                      mirror ? reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)b * p.c_batch_stride + (long long)col * p.ldc + row : nullptr,
+                                                      p.ldc);
                         } else {
                             __half* dst = reinterpret_cast<__half*>(p.C) + off;
                             const __half* cin = p.Cin ? reinterpret_cast<const __half*>(p.Cin) + offin : nullptr;
-                            store32_16<__half>(dst, cin, acc, p.alpha, p.beta, ncols, vec);
+                            store32_16<__half>(dst, cin, acc, p.alpha, p.beta, ncols, vec,
+                                               mirror ? reinterpret_cast<__half*>(p.C) + (long long)b * p.c_batch_stride + (long long)col * p.ldc + row : nullptr,
+                                               p.ldc);
                         }
                     }
                 }

@@ -404,10 +404,36 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 const int col = tn * BN + c0;
                 const int ncols = min(32, p.N - col);
                 if (p.split_k > 1) {
-                    if (row < p.M && ncols > 0 && has_k) {
-                        float* dst = reinterpret_cast<float*>(p.C) + (long long)b * p.c_batch_stride +
-                                     (long long)row * p.ldc + col;
-                        for (int j = 0; j < ncols; ++j) atomicAdd(dst + j, p.alpha * __uint_as_float(acc[j]));
+                    const int row0 = tm * BM + quarter * 32;
+                    if (has_k && row0 < p.M && ncols > 0) {
+                        if (ncols == 32 && ((p.ldc | col) & 3) == 0) {
+                            // A lane that adds its own row issues 32 scattered atomics per instruction.  The
+                            // 32x32 chunk is transposed through shared memory instead, so one instruction adds
+                            // four 128-byte row segments with 16-byte vector atomics.
+                            float* stg = reinterpret_cast<float*>(smem + STAGES * (A_STAGE + B_STAGE) + 256 +
+                                                                  (warp - 2) * EPI_WARP_BYTES);
+#pragma unroll
+                            for (int j = 0; j < 8; ++j)
+                                *reinterpret_cast<float4*>(stg + lane * (EPI_PITCH / 4) + 4 * j) =
+                                    make_float4(p.alpha * __uint_as_float(acc[4 * j]), p.alpha * __uint_as_float(acc[4 * j + 1]),
+                                                p.alpha * __uint_as_float(acc[4 * j + 2]), p.alpha * __uint_as_float(acc[4 * j + 3]));
+                            __syncwarp();
+                            float* dst0 = reinterpret_cast<float*>(p.C) + (long long)b * p.c_batch_stride +
+                                          (long long)row0 * p.ldc + col + (lane & 7) * 4;
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) {
+                                const int rr = i * 4 + (lane >> 3);
+                                if (row0 + rr < p.M) {
+                                    const float4 v = *reinterpret_cast<const float4*>(stg + rr * (EPI_PITCH / 4) + (lane & 7) * 4);
+                                    atomicAdd(reinterpret_cast<float4*>(dst0 + (long long)rr * p.ldc), v);
+                                }
+                            }
+                            __syncwarp();
+                        } else if (row < p.M) {
+                            float* dst = reinterpret_cast<float*>(p.C) + (long long)b * p.c_batch_stride +
+                                         (long long)row * p.ldc + col;
+                            for (int j = 0; j < ncols; ++j) atomicAdd(dst + j, p.alpha * __uint_as_float(acc[j]));
+                        }
                     }
                 } else if (row < p.M && ncols > 0) {
                     const long long off = (long long)b * p.c_batch_stride + (long long)row * p.ldc + col;

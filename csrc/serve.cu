@@ -47,6 +47,7 @@ paged_decode_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* 
     float* sc = sm;                       // [G][split_tokens]
     __shared__ float qs[G][HD];
     __shared__ float red[2][G][4];
+    __shared__ int spage[2048 / PAGE];    // page numbers of this split (split_tokens <= 2048)
     const int req = blockIdx.x, kvh = blockIdx.y, sp = blockIdx.z;
     const int ctx = ctx_lens[req];
     const int t0 = sp * split_tokens;
@@ -64,33 +65,52 @@ paged_decode_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* 
         const int g = i / HD, d = i % HD;
         qs[g][d] = __bfloat162float(q[(size_t)req * q_stride + (size_t)(kvh * G + g) * HD + d]) * scale;
     }
+    for (int i = threadIdx.x; i < (nt + PAGE - 1) / PAGE; i += blockDim.x)
+        spage[i] = page_table[(size_t)req * max_pages + t0 / PAGE + i];
     __syncthreads();
     constexpr int LPT = HD / 16;          // lanes per token
     constexpr int TPW = 32 / LPT;         // tokens per warp iteration
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int sub = lane % LPT, tw = lane / LPT;
     const int row = n_kv * HD;
-    for (int t = warp * TPW + tw; t < ((nt + TPW - 1) / TPW) * TPW; t += 4 * TPW) {
-        float acc[G];
+    // K pass.  Bandwidth here is set by the loads in flight, so every thread issues the 32-byte loads
+    // of KU tokens before it touches any of them, and page numbers come from shared memory (a
+    // dependent global load per token would double the latency of every step).
+    constexpr int KU = 4;
+    constexpr int KSTEP = 4 * TPW;        // tokens covered by the CTA per unrolled slot
+    for (int tb = warp * TPW + tw; tb < ((nt + KSTEP * KU - 1) / (KSTEP * KU)) * (KSTEP * KU); tb += KSTEP * KU) {
+        bf16x8 kr[KU][2];
 #pragma unroll
-        for (int g = 0; g < G; ++g) acc[g] = 0.f;
-        if (t < nt) {
-            const int tok = t0 + t;
-            const int page = page_table[(size_t)req * max_pages + tok / PAGE];
-            const bf16* kp = k_pages + ((size_t)page * PAGE + tok % PAGE) * row + (size_t)kvh * HD + sub * 16;
-            float kf[16];
-            unpack8(ld8(kp), kf);
-            unpack8(ld8(kp + 8), kf + 8);
-#pragma unroll
-            for (int g = 0; g < G; ++g)
-#pragma unroll
-                for (int i = 0; i < 16; ++i) acc[g] += kf[i] * qs[g][sub * 16 + i];
+        for (int u = 0; u < KU; ++u) {
+            const int t = tb + u * KSTEP;
+            if (t < nt) {
+                const int tok = t0 + t;
+                const bf16* kp = k_pages + ((size_t)spage[t / PAGE] * PAGE + tok % PAGE) * row + (size_t)kvh * HD + sub * 16;
+                kr[u][0] = ld8(kp);
+                kr[u][1] = ld8(kp + 8);
+            }
         }
 #pragma unroll
-        for (int g = 0; g < G; ++g) {
+        for (int u = 0; u < KU; ++u) {
+            const int t = tb + u * KSTEP;
+            float acc[G];
 #pragma unroll
-            for (int o = LPT / 2; o > 0; o >>= 1) acc[g] += __shfl_xor_sync(0xffffffffu, acc[g], o);
-            if (sub == 0 && t < nt) sc[g * split_tokens + t] = acc[g];
+            for (int g = 0; g < G; ++g) acc[g] = 0.f;
+            if (t < nt) {
+                float kf[16];
+                unpack8(kr[u][0], kf);
+                unpack8(kr[u][1], kf + 8);
+#pragma unroll
+                for (int g = 0; g < G; ++g)
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) acc[g] += kf[i] * qs[g][sub * 16 + i];
+            }
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+#pragma unroll
+                for (int o = LPT / 2; o > 0; o >>= 1) acc[g] += __shfl_xor_sync(0xffffffffu, acc[g], o);
+                if (sub == 0 && t < nt) sc[g * split_tokens + t] = acc[g];
+            }
         }
     }
     __syncthreads();
@@ -130,17 +150,30 @@ paged_decode_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* 
         for (int g = 0; g < G; ++g)
 #pragma unroll
             for (int i = 0; i < 8; ++i) o[g][i] = 0.f;
-#pragma unroll 4
-        for (int t = tg; t < nt; t += NTG) {
-            const int tok = t0 + t;
-            const int page = page_table[(size_t)req * max_pages + tok / PAGE];
-            float vf[8];
-            unpack8(ld8(v_pages + ((size_t)page * PAGE + tok % PAGE) * row + (size_t)kvh * HD + c * 8), vf);
+        constexpr int VU = 8;
+        for (int tb = tg; tb < nt; tb += NTG * VU) {
+            bf16x8 vr[VU];
 #pragma unroll
-            for (int g = 0; g < G; ++g) {
-                const float pw = sc[g * split_tokens + t];
+            for (int u = 0; u < VU; ++u) {
+                const int t = tb + u * NTG;
+                if (t < nt) {
+                    const int tok = t0 + t;
+                    vr[u] = ld8(v_pages + ((size_t)spage[t / PAGE] * PAGE + tok % PAGE) * row + (size_t)kvh * HD + c * 8);
+                }
+            }
 #pragma unroll
-                for (int i = 0; i < 8; ++i) o[g][i] += pw * vf[i];
+            for (int u = 0; u < VU; ++u) {
+                const int t = tb + u * NTG;
+                if (t < nt) {
+                    float vf[8];
+                    unpack8(vr[u], vf);
+#pragma unroll
+                    for (int g = 0; g < G; ++g) {
+                        const float pw = sc[g * split_tokens + t];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) o[g][i] += pw * vf[i];
+                    }
+                }
             }
         }
         __syncthreads();                       // scores are dead from here: reuse their space? no: separate buffer

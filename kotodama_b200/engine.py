@@ -223,6 +223,7 @@ class TrainEngine:
         self.ce_chunk = ce_chunk
         self.fp8, self.fp8_recipe = fp8, fp8_recipe
         self.ns_coefficients = muon_ns_coefficients
+        self.ns_batch = 14                 # same-shape matrices per batched Newton-Schulz product
         self.muon_opt = _OptView(muon_lr, self.muon_state_dict, self.load_muon_state_dict, momentum=muon_momentum, nesterov=True,
                                  weight_decay=muon_weight_decay, ns_iterations=muon_ns_iterations)
         self.adamw_opt = _OptView(adamw_lr, self.adamw_state_dict, self.load_adamw_state_dict, betas=tuple(adamw_betas), eps=adamw_eps,
@@ -491,9 +492,35 @@ class TrainEngine:
         if not self.adamw_only:
             g = self.muon_opt.param_groups[0]
             coeffs = resolve_ns_coefficients(self.ns_coefficients, g["ns_iterations"])
-            for s in ar.muon_slots():
-                if comm.distributed_muon and s.owner != comm.rank:
-                    continue
+            owned = [s for s in ar.muon_slots() if not (comm.distributed_muon and s.owner != comm.rank)]
+            if comm.tp_size == 1:
+                # Same-shape matrices are orthogonalised as one batched product: a single 3072x3072
+                # Gram matrix is 78 upper-triangle tiles for 74 CTA pairs (two waves, the second almost
+                # empty), a batch fills the waves.  Memory is bounded by ``ns_batch`` matrices at a time.
+                prepared = []
+                for s in owned:
+                    grad = ar.view(s.name, grads=True)
+                    x, sq = ops.muon_momentum(grad, self.momentum[s.name], g["momentum"], g["nesterov"], coef)
+                    rows, cols = s.shape
+                    transposed = rows > cols
+                    if transposed:
+                        x = ops.transpose(x)
+                    prepared.append([s, ops.ns_normalize(x, sq), transposed, rows, cols])
+                groups: dict[tuple, list] = {}
+                for it in prepared:
+                    groups.setdefault(tuple(it[1].shape), []).append(it)
+                for items in groups.values():
+                    for c0 in range(0, len(items), self.ns_batch):
+                        chunk = items[c0:c0 + self.ns_batch]
+                        xb = torch.stack([it[1] for it in chunk]) if len(chunk) > 1 else chunk[0][1]
+                        for (a, b, c) in coeffs:
+                            xb = ops.ns_iteration(xb, a, b, c)
+                        for i, it in enumerate(chunk):
+                            it[1] = xb[i] if len(chunk) > 1 else xb
+                for s, x, transposed, rows, cols in prepared:
+                    comm.muon_apply(ops, s, x, g["lr"], g["weight_decay"], max(1.0, (rows / cols) ** 0.5), transposed)
+                owned = []
+            for s in owned:
                 grad = ar.view(s.name, grads=True)
                 x, sq = ops.muon_momentum(grad, self.momentum[s.name], g["momentum"], g["nesterov"], coef)
                 rows, cols = comm.full_shape(s)

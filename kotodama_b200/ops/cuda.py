@@ -51,6 +51,7 @@ class CudaOps(TorchOps):
         self._status: dict[int, torch.Tensor] = {}
         self.gemm_max_ctas = 0
         self.split_k_small_m = True
+        self._splitk_ws: dict = {}
         self.native_attention = os.environ.get("KOTODAMA_FLASH", "1") == "1"
         self.native_attention_train = os.environ.get("KOTODAMA_FLASH_TRAIN", "0") == "1"
         self.gemm_2cta = os.environ.get("KOTODAMA_GEMM_2CTA", "1") == "1"   # CTA-pair kernel for large products
@@ -110,14 +111,18 @@ class CudaOps(TorchOps):
             # skinny (decode-size) products: too few output tiles to fill the GPU, so the K range is
             # split over CTAs with fp32 atomic accumulation and a small finishing kernel
             split = max(2, min(148 // tiles, kblocks // 2, 16))
-            ws = torch.zeros(M, N, device=a.device, dtype=torch.float32)
+            # one fp32 workspace per output size, zeroed once: the finishing kernel clears it again
+            key = (M * N, a.device.index)
+            ws = self._splitk_ws.get(key)
+            if ws is None:
+                ws = self._splitk_ws[key] = torch.zeros(M * N, device=a.device, dtype=torch.float32)
             rc = self.lib.kb_gemm(_p(a), _p(b), _p(ws), _p(None), _I(M), _I(N), _I(K), _I(1),
                                   _LL(a.stride(-2)), _LL(b.stride(-2)), _LL(N), _LL(0), _LL(0), _LL(0), _LL(0), _LL(0),
                                   _I(int(a_mn)), _I(int(b_mn)), _I(_FMT[a.dtype]), _I(_FMT[b.dtype]), _I(2),
                                   _F(alpha), _F(0.0), _p(self.status(a.device)), _I(self.gemm_max_ctas), _I(split),
                                   _st())
             self._rc(rc, "kb_gemm(split-k)")
-            self._rc(self.lib.kb_f32_to_bf16_add(_p(ws), _p(cin), _F(beta), _p(out), _LL(M * N), _st()),
+            self._rc(self.lib.kb_f32_to_bf16_add(_p(ws), _p(cin), _F(beta), _p(out), _LL(M * N), _I(1), _st()),
                      "kb_f32_to_bf16_add")
             return out
         if self.gemm_2cta and M >= 256 and N >= 256:
@@ -130,7 +135,9 @@ class CudaOps(TorchOps):
                                        _I(_OUT[out.dtype]), _F(alpha), _F(beta), _p(self.status(a.device)),
                                        _I(self.gemm_max_ctas), _I(int(sym_upper)), _st())
             self._rc(rc, "kb_gemm_2cta")
-            if sym_upper:       # only tiles on/above the diagonal were computed: mirror them down
+            # sym_upper: only tiles on/above the diagonal are computed; the epilogue writes each of them
+            # to its mirrored position as well (16-bit outputs)
+            if sym_upper and out.dtype == torch.float32:
                 self._rc(self.lib.kb_mirror_upper16(_p(out), _I(M), _LL(out.stride(-2)), _I(batch), _LL(bs(out)),
                                                     _st()), "kb_mirror_upper16")
             return out

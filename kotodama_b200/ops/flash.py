@@ -17,7 +17,7 @@ _VP, _I, _LL, _F = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_fl
 
 
 def supported(q: torch.Tensor) -> bool:
-    return (q.is_cuda and q.dtype == torch.bfloat16 and q.ndim == 4 and q.shape[-1] == 128 and q.shape[1] % 128 == 0
+    return (q.is_cuda and q.dtype == torch.bfloat16 and q.ndim == 4 and q.shape[-1] == 128
             and q.stride(-1) == 1 and q.stride(2) == 128 and q.stride(0) == q.shape[1] * q.stride(1))
 
 

@@ -404,8 +404,9 @@ class TorchOps:
         return (_f(x) / (sumsq.sqrt() + 1e-7)).to(x.dtype)
 
     def ns_iteration(self, x: torch.Tensor, a: float, b: float, c: float) -> torch.Tensor:
-        """One Newton-Schulz step on ``x[R,C]`` (R<=C), fp16 operands (``muon.py:144-147``)."""
-        A = x @ x.t()
+        """One Newton-Schulz step on ``x[R,C]`` (R<=C) or a batch ``x[n,R,C]`` of same-shape matrices,
+        fp16 operands (``muon.py:144-147``, batching as in ``muon.py:155-188``)."""
+        A = x @ x.transpose(-1, -2)
         B = b * A + c * (A @ A)
         return a * x + B @ x
 

@@ -303,7 +303,7 @@ def test_newton_schulz_symmetric_tiles_and_batch(ops):
         ops.gemm_2cta = prev
 
 
-@pytest.mark.parametrize("B,T,H,KV", [(1, 128, 2, 1), (2, 512, 6, 2), (1, 1024, 3, 3)])
+@pytest.mark.parametrize("B,T,H,KV", [(1, 128, 2, 1), (2, 512, 6, 2), (1, 1024, 3, 3), (1, 200, 3, 1), (2, 333, 4, 2), (1, 77, 2, 2)])
 def test_flash_attention_forward(ops, B, T, H, KV):
     from kotodama_b200.ops.flash import flash_fwd, supported
     hd = 128
