@@ -170,7 +170,7 @@ __global__ void allreduce_slices_kernel(PeerPtrs bufs, int world, int rank, long
         for (int j = 0; j < 8; ++j) acc[j] *= scale;
         const bf16x8 o = pack8(acc);
         for (int r = 0; r < world; ++r)
-            *(reinterpret_cast<bf16x8*>(reinterpret_cast<bf16*>(bufs.p[r]) + offset) + i) = o;
+            st8(reinterpret_cast<bf16*>(bufs.p[r]) + offset + i * 8, o);
     }
 }
 KB_API int kb_allreduce_slices(void* const* peer_bufs, int world, int rank, long long offset, long long n,

@@ -126,7 +126,7 @@ quant_cols_t_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, uint8_t*
 #pragma unroll
                 for (int i = 0; i < 4; ++i) v.v[i] = __floats2bfloat162_rn(0.f, 0.f);
             }
-            *reinterpret_cast<bf16x8*>(&tile[r][c0 + j * 8]) = v;
+            *reinterpret_cast<uint4*>(&tile[r][c0 + j * 8]) = *reinterpret_cast<const uint4*>(&v);
         }
     }
     __syncthreads();

@@ -3,6 +3,8 @@
 // Cache layout: k_pages / v_pages [num_pages, PAGE, n_kv, hd] bf16 with PAGE = 16 tokens;
 // keys are stored post QK-norm and post RoPE (as the reference caches them,
 // src/model/llama.py:333-337).  A request's pages are listed in page_table[req][i].
+#include <stdlib.h>
+
 #include "common.cuh"
 
 typedef __nv_bfloat16 bf16;
@@ -48,7 +50,9 @@ paged_decode_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* 
     __shared__ float qs[G][HD];
     __shared__ float red[2][G][4];
     __shared__ int spage[2048 / PAGE];    // page numbers of this split (split_tokens <= 2048)
-    const int req = blockIdx.x, kvh = blockIdx.y, sp = blockIdx.z;
+    // kv head is the fastest-varying block index: the CTAs that read the eight 256-byte head slices of
+    // the same token rows are launched together
+    const int kvh = blockIdx.x, req = blockIdx.y, sp = blockIdx.z;
     const int ctx = ctx_lens[req];
     const int t0 = sp * split_tokens;
     const int nt = min(split_tokens, ctx - t0);
@@ -198,6 +202,165 @@ paged_decode_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* 
     (void)H;
 }
 
+// Streaming variant of the split kernel: one pass over the tokens with an online softmax, K and V
+// of a step loaded together, no score buffer and no block-wide barrier inside the loop.
+// Lane layout: 8 lanes per token (8 elements of each half of the head row), 4 tokens per warp and step; every lane
+// keeps running (max, sum) and its 16-element slice of the output for the tokens of its lane
+// group; groups and warps are merged at the end.  Scores are kept in log2 units.
+template <int HD, int G>
+__global__ void __launch_bounds__(128, 2)
+paged_decode_stream_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* __restrict__ k_pages,
+                           const bf16* __restrict__ v_pages, const int* __restrict__ page_table, int max_pages,
+                           const int* __restrict__ ctx_lens, int n_kv, int split_tokens, float scale,
+                           float* __restrict__ part_o, float* __restrict__ part_ml, int nsplit) {
+    constexpr int LPT = HD / 16, TPW = 32 / LPT, U = 4, STEP = 4 * TPW;
+    __shared__ float qs[G][HD];
+    __shared__ int spage[2048 / PAGE];
+    __shared__ float wo[4][G][HD];
+    __shared__ float wml[4][G][2];
+    const int kvh = blockIdx.x, req = blockIdx.y, sp = blockIdx.z;
+    const int ctx = ctx_lens[req];
+    const int t0 = sp * split_tokens;
+    const int nt = min(split_tokens, ctx - t0);
+    const size_t pbase = ((size_t)(req * n_kv + kvh) * nsplit + sp);
+    if (nt <= 0) {
+        if (threadIdx.x < G) {
+            part_ml[(pbase * G + threadIdx.x) * 2] = -INFINITY;
+            part_ml[(pbase * G + threadIdx.x) * 2 + 1] = 0.f;
+        }
+        return;
+    }
+    const float qscale = scale * 1.4426950408889634f;
+    for (int i = threadIdx.x; i < G * HD; i += blockDim.x) {
+        const int g = i / HD, d = i % HD;
+        qs[g][d] = __bfloat162float(q[(size_t)req * q_stride + (size_t)(kvh * G + g) * HD + d]) * qscale;
+    }
+    for (int i = threadIdx.x; i < (nt + PAGE - 1) / PAGE; i += blockDim.x)
+        spage[i] = page_table[(size_t)req * max_pages + t0 / PAGE + i];
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int sub = lane % LPT, tw = lane / LPT;
+    const int row = n_kv * HD;
+    float qr[G][16], o[G][16], m[G], l[G];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        m[g] = -INFINITY;
+        l[g] = 0.f;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            qr[g][i] = qs[g][(i < 8 ? 0 : HD / 2) + sub * 8 + (i & 7)];
+            o[g][i] = 0.f;
+        }
+    }
+    const int span = STEP * U;
+    for (int tb = warp * TPW + tw; tb < ((nt + span - 1) / span) * span; tb += span) {
+        bf16x8 kr[U][2], vr[U][2];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int t = tb + u * STEP;
+            if (t < nt) {
+                // lane `sub` owns elements [8 sub, 8 sub + 8) of each half of the row, so the eight lanes of
+                // a token read 128 contiguous bytes per instruction (whole sectors)
+                const size_t off = ((size_t)spage[t / PAGE] * PAGE + (t0 + t) % PAGE) * row + (size_t)kvh * HD + sub * 8;
+                kr[u][0] = ld8(k_pages + off);
+                kr[u][1] = ld8(k_pages + off + HD / 2);
+                vr[u][0] = ld8(v_pages + off);
+                vr[u][1] = ld8(v_pages + off + HD / 2);
+            }
+        }
+        float sc[U][G];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const bool valid = tb + u * STEP < nt;
+            float kf[16];
+            if (valid) {
+                unpack8(kr[u][0], kf);
+                unpack8(kr[u][1], kf + 8);
+            }
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                float a = 0.f;
+                if (valid) {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) a += kf[i] * qr[g][i];
+                }
+#pragma unroll
+                for (int x = LPT / 2; x > 0; x >>= 1) a += __shfl_xor_sync(0xffffffffu, a, x);
+                sc[u][g] = valid ? a : -INFINITY;
+            }
+        }
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            float mn = m[g];
+#pragma unroll
+            for (int u = 0; u < U; ++u) mn = fmaxf(mn, sc[u][g]);
+            if (mn == -INFINITY) continue;          // no valid token for this lane group yet
+            const float f = exp2f(m[g] - mn);
+            m[g] = mn;
+            l[g] *= f;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) o[g][i] *= f;
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            if (tb + u * STEP < nt) {
+                float vf[16];
+                unpack8(vr[u][0], vf);
+                unpack8(vr[u][1], vf + 8);
+#pragma unroll
+                for (int g = 0; g < G; ++g) {
+                    const float pw = exp2f(sc[u][g] - m[g]);
+                    l[g] += pw;
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) o[g][i] += pw * vf[i];
+                }
+            }
+        }
+    }
+    // merge the lane groups of the warp (lanes with equal `sub`)
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        float mg = m[g];
+#pragma unroll
+        for (int x = LPT; x < 32; x <<= 1) mg = fmaxf(mg, __shfl_xor_sync(0xffffffffu, mg, x));
+        const float f = mg == -INFINITY ? 0.f : exp2f(m[g] - mg);
+        float lg = l[g] * f;
+#pragma unroll
+        for (int x = LPT; x < 32; x <<= 1) lg += __shfl_xor_sync(0xffffffffu, lg, x);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            float v = o[g][i] * f;
+#pragma unroll
+            for (int x = LPT; x < 32; x <<= 1) v += __shfl_xor_sync(0xffffffffu, v, x);
+            if (tw == 0) wo[warp][g][(i < 8 ? 0 : HD / 2) + sub * 8 + (i & 7)] = v;
+        }
+        if (lane == 0) {
+            wml[warp][g][0] = mg;
+            wml[warp][g][1] = lg;
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < G * HD; i += blockDim.x) {
+        const int g = i / HD, d = i % HD;
+        float mx = fmaxf(fmaxf(wml[0][g][0], wml[1][g][0]), fmaxf(wml[2][g][0], wml[3][g][0]));
+        float acc = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w)
+            if (wml[w][g][0] != -INFINITY) acc += wo[w][g][d] * exp2f(wml[w][g][0] - mx);
+        part_o[(pbase * G + g) * HD + d] = acc;
+    }
+    if (threadIdx.x < G) {
+        const int g = threadIdx.x;
+        const float mx = fmaxf(fmaxf(wml[0][g][0], wml[1][g][0]), fmaxf(wml[2][g][0], wml[3][g][0]));
+        float sum = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w)
+            if (wml[w][g][0] != -INFINITY) sum += wml[w][g][1] * exp2f(wml[w][g][0] - mx);
+        part_ml[(pbase * G + g) * 2] = mx * 0.6931471805599453f;       // back to natural-log units for the merge
+        part_ml[(pbase * G + g) * 2 + 1] = sum;
+    }
+}
+
 // Merge the splits: out[req][head][d] = sum_s e^{m_s - M} o_s[d] / sum_s e^{m_s - M} l_s
 template <int HD>
 __global__ void paged_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
@@ -230,12 +393,24 @@ KB_API int kb_paged_decode(const void* q, long long q_stride, const void* k_page
     const int G = n_q / n_kv;
     if (n_q % n_kv || split_tokens % PAGE || split_tokens > 2048) return 5;
     const int nsplit = (max_ctx + split_tokens - 1) / split_tokens;
-    dim3 grid(B, n_kv, nsplit);
+    dim3 grid(n_kv, B, nsplit);
     const size_t smem = (size_t)G * split_tokens * sizeof(float);
+    // KB_DECODE_KERNEL=phases selects the three-phase kernel (scores in shared memory); the default is
+    // the streaming online-softmax kernel
+    static int streaming = -1;
+    if (streaming < 0) {
+        const char* e = getenv("KB_DECODE_KERNEL");
+        streaming = !(e && e[0] == 'p');
+    }
 #define DEC(HD_, G_)                                                                                          \
-    paged_decode_kernel<HD_, G_><<<grid, 128, smem, st>>>((const bf16*)q, q_stride, (const bf16*)k_pages,      \
-                                                          (const bf16*)v_pages, page_table, max_pages, ctx_lens, \
-                                                          n_kv, split_tokens, scale, part_o, part_ml, nsplit)
+    if (streaming && (G_) <= 4)                                                                                \
+        paged_decode_stream_kernel<HD_, G_><<<grid, 128, 0, st>>>((const bf16*)q, q_stride, (const bf16*)k_pages, \
+                                                              (const bf16*)v_pages, page_table, max_pages, ctx_lens, \
+                                                              n_kv, split_tokens, scale, part_o, part_ml, nsplit); \
+    else                                                                                                       \
+        paged_decode_kernel<HD_, G_><<<grid, 128, smem, st>>>((const bf16*)q, q_stride, (const bf16*)k_pages,  \
+                                                              (const bf16*)v_pages, page_table, max_pages, ctx_lens, \
+                                                              n_kv, split_tokens, scale, part_o, part_ml, nsplit)
     if (hd == 128) {
         switch (G) {
             case 1: DEC(128, 1); break;
