@@ -35,8 +35,8 @@ def main() -> None:
     pages_per = (ctx + 15) // 16
     total_pages = int(pages_per.sum())
     maxp = int(pages_per.max())
-    k_pages = (torch.randn(total_pages, 16, a.kv, hd, device="cuda", generator=g) * 0.5).to(torch.bfloat16)
-    v_pages = (torch.randn(total_pages, 16, a.kv, hd, device="cuda", generator=g) * 0.5).to(torch.bfloat16)
+    k_pages = (torch.randn(total_pages, a.kv, 16, hd, device="cuda", generator=g) * 0.5).to(torch.bfloat16)
+    v_pages = (torch.randn(total_pages, a.kv, 16, hd, device="cuda", generator=g) * 0.5).to(torch.bfloat16)
     perm = torch.randperm(total_pages, device="cuda", generator=g).int()
     table = torch.zeros(B, maxp, dtype=torch.int32, device="cuda")
     o = 0

@@ -1,7 +1,8 @@
 // Serving kernels: paged KV cache append, split-KV paged decode attention (GQA), greedy argmax.
 //
-// Cache layout: k_pages / v_pages [num_pages, PAGE, n_kv, hd] bf16 with PAGE = 16 tokens;
-// keys are stored post QK-norm and post RoPE (as the reference caches them,
+// Cache layout: k_pages / v_pages [num_pages, n_kv, PAGE, hd] bf16 with PAGE = 16 tokens: the 16 rows
+// of one (page, kv head) are 4 KB (hd 128) of contiguous memory, which is what the decode kernel
+// streams; keys are stored post QK-norm and post RoPE (as the reference caches them,
 // src/model/llama.py:333-337).  A request's pages are listed in page_table[req][i].
 #include <stdlib.h>
 
@@ -13,26 +14,29 @@ constexpr int PAGE = 16;
 // k, v: [N, n_kv*hd] rows with the given strides; slot[n] = page * PAGE + offset in page, or < 0 to skip.
 __global__ void kv_append_kernel(const bf16* __restrict__ k, const bf16* __restrict__ v, long long k_stride,
                                  long long v_stride, bf16* __restrict__ k_pages, bf16* __restrict__ v_pages,
-                                 const long long* __restrict__ slot, int N, int row_elems) {
+                                 const long long* __restrict__ slot, int N, int row_elems, int hd) {
     const int chunks = row_elems >> 3;
+    const int n_kv = row_elems / hd;
     const long long total = (long long)N * chunks;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
          i += (long long)gridDim.x * blockDim.x) {
         const int n = (int)(i / chunks), c = (int)(i % chunks);
         const long long s = slot[n];
         if (s < 0) continue;
-        st8(k_pages + s * row_elems + (size_t)c * 8, ld8(k + (size_t)n * k_stride + (size_t)c * 8));
-        st8(v_pages + s * row_elems + (size_t)c * 8, ld8(v + (size_t)n * v_stride + (size_t)c * 8));
+        const int kvh = (c * 8) / hd, d = (c * 8) % hd;
+        const size_t dst = (((size_t)(s / PAGE) * n_kv + kvh) * PAGE + (size_t)(s % PAGE)) * hd + d;
+        st8(k_pages + dst, ld8(k + (size_t)n * k_stride + (size_t)c * 8));
+        st8(v_pages + dst, ld8(v + (size_t)n * v_stride + (size_t)c * 8));
     }
 }
 KB_API int kb_kv_append(const void* k, const void* v, long long k_stride, long long v_stride, void* k_pages,
-                        void* v_pages, const long long* slot, int N, int row_elems, cudaStream_t st) {
-    if (row_elems % 8 || k_stride % 8 || v_stride % 8) return 5;
+                        void* v_pages, const long long* slot, int N, int row_elems, int hd, cudaStream_t st) {
+    if (row_elems % 8 || k_stride % 8 || v_stride % 8 || hd % 8 || row_elems % hd) return 5;
     long long blocks = ((long long)N * (row_elems / 8) + 255) / 256;
     if (blocks < 1) blocks = 1;
     if (blocks > 4096) blocks = 4096;
     kv_append_kernel<<<(int)blocks, 256, 0, st>>>((const bf16*)k, (const bf16*)v, k_stride, v_stride, (bf16*)k_pages,
-                                                  (bf16*)v_pages, slot, N, row_elems);
+                                                  (bf16*)v_pages, slot, N, row_elems, hd);
     return 0;
 }
 
@@ -76,7 +80,6 @@ paged_decode_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* 
     constexpr int TPW = 32 / LPT;         // tokens per warp iteration
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int sub = lane % LPT, tw = lane / LPT;
-    const int row = n_kv * HD;
     // K pass.  Bandwidth here is set by the loads in flight, so every thread issues the 32-byte loads
     // of KU tokens before it touches any of them, and page numbers come from shared memory (a
     // dependent global load per token would double the latency of every step).
@@ -89,7 +92,7 @@ paged_decode_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* 
             const int t = tb + u * KSTEP;
             if (t < nt) {
                 const int tok = t0 + t;
-                const bf16* kp = k_pages + ((size_t)spage[t / PAGE] * PAGE + tok % PAGE) * row + (size_t)kvh * HD + sub * 16;
+                const bf16* kp = k_pages + (((size_t)spage[t / PAGE] * n_kv + kvh) * PAGE + tok % PAGE) * HD + sub * 16;
                 kr[u][0] = ld8(kp);
                 kr[u][1] = ld8(kp + 8);
             }
@@ -162,7 +165,7 @@ paged_decode_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* 
                 const int t = tb + u * NTG;
                 if (t < nt) {
                     const int tok = t0 + t;
-                    vr[u] = ld8(v_pages + ((size_t)spage[t / PAGE] * PAGE + tok % PAGE) * row + (size_t)kvh * HD + c * 8);
+                    vr[u] = ld8(v_pages + (((size_t)spage[t / PAGE] * n_kv + kvh) * PAGE + tok % PAGE) * HD + c * 8);
                 }
             }
 #pragma unroll
@@ -207,13 +210,13 @@ paged_decode_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* 
 // Lane layout: 8 lanes per token (8 elements of each half of the head row), 4 tokens per warp and step; every lane
 // keeps running (max, sum) and its 16-element slice of the output for the tokens of its lane
 // group; groups and warps are merged at the end.  Scores are kept in log2 units.
-template <int HD, int G>
-__global__ void __launch_bounds__(128, 2)
+template <int HD, int G, int U>
+__global__ void __launch_bounds__(128, U >= 4 ? 2 : 3)
 paged_decode_stream_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* __restrict__ k_pages,
                            const bf16* __restrict__ v_pages, const int* __restrict__ page_table, int max_pages,
                            const int* __restrict__ ctx_lens, int n_kv, int split_tokens, float scale,
                            float* __restrict__ part_o, float* __restrict__ part_ml, int nsplit) {
-    constexpr int LPT = HD / 16, TPW = 32 / LPT, U = 4, STEP = 4 * TPW;
+    constexpr int LPT = HD / 16, TPW = 32 / LPT, STEP = 4 * TPW;
     __shared__ float qs[G][HD];
     __shared__ int spage[2048 / PAGE];
     __shared__ float wo[4][G][HD];
@@ -240,7 +243,6 @@ paged_decode_stream_kernel(const bf16* __restrict__ q, long long q_stride, const
     __syncthreads();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int sub = lane % LPT, tw = lane / LPT;
-    const int row = n_kv * HD;
     float qr[G][16], o[G][16], m[G], l[G];
 #pragma unroll
     for (int g = 0; g < G; ++g) {
@@ -261,7 +263,7 @@ paged_decode_stream_kernel(const bf16* __restrict__ q, long long q_stride, const
             if (t < nt) {
                 // lane `sub` owns elements [8 sub, 8 sub + 8) of each half of the row, so the eight lanes of
                 // a token read 128 contiguous bytes per instruction (whole sectors)
-                const size_t off = ((size_t)spage[t / PAGE] * PAGE + (t0 + t) % PAGE) * row + (size_t)kvh * HD + sub * 8;
+                const size_t off = (((size_t)spage[t / PAGE] * n_kv + kvh) * PAGE + (t0 + t) % PAGE) * HD + sub * 8;
                 kr[u][0] = ld8(k_pages + off);
                 kr[u][1] = ld8(k_pages + off + HD / 2);
                 vr[u][0] = ld8(v_pages + off);
@@ -397,14 +399,20 @@ KB_API int kb_paged_decode(const void* q, long long q_stride, const void* k_page
     const size_t smem = (size_t)G * split_tokens * sizeof(float);
     // KB_DECODE_KERNEL=phases selects the three-phase kernel (scores in shared memory); the default is
     // the streaming online-softmax kernel
-    static int streaming = -1;
+    static int streaming = -1, unroll = 4;
     if (streaming < 0) {
         const char* e = getenv("KB_DECODE_KERNEL");
         streaming = !(e && e[0] == 'p');
+        const char* u = getenv("KB_DECODE_UNROLL");     // tokens per lane group and iteration: 4 (default) or 2
+        if (u && atoi(u) == 2) unroll = 2;
     }
 #define DEC(HD_, G_)                                                                                          \
-    if (streaming && (G_) <= 4)                                                                                \
-        paged_decode_stream_kernel<HD_, G_><<<grid, 128, 0, st>>>((const bf16*)q, q_stride, (const bf16*)k_pages, \
+    if (streaming && (G_) <= 4 && unroll == 4)                                                                 \
+        paged_decode_stream_kernel<HD_, G_, 4><<<grid, 128, 0, st>>>((const bf16*)q, q_stride, (const bf16*)k_pages, \
+                                                              (const bf16*)v_pages, page_table, max_pages, ctx_lens, \
+                                                              n_kv, split_tokens, scale, part_o, part_ml, nsplit); \
+    else if (streaming && (G_) <= 4)                                                                           \
+        paged_decode_stream_kernel<HD_, G_, 2><<<grid, 128, 0, st>>>((const bf16*)q, q_stride, (const bf16*)k_pages, \
                                                               (const bf16*)v_pages, page_table, max_pages, ctx_lens, \
                                                               n_kv, split_tokens, scale, part_o, part_ml, nsplit); \
     else                                                                                                       \

@@ -425,7 +425,7 @@ class CudaOps(TorchOps):
         """Copy rows ``k[n], v[n]`` (``[N, n_kv*hd]`` views) into cache slot ``slots[n]`` (page*16 + offset)."""
         N, row = k.shape
         self._rc(self.lib.kb_kv_append(_p(k), _p(v), _LL(k.stride(0)), _LL(v.stride(0)), _p(k_pages), _p(v_pages),
-                                       _p(slots), _I(N), _I(row), _st()), "kb_kv_append")
+                                       _p(slots), _I(N), _I(row), _I(k_pages.shape[-1]), _st()), "kb_kv_append")
 
     def paged_decode_attention(self, q, k_pages, v_pages, page_table, ctx_lens, max_ctx, n_q, n_kv, hd, split=256):
         """``q[B, n_q*hd]`` (one new token per request) against the paged cache; returns ``[B, n_q*hd]``."""

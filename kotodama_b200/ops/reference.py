@@ -425,21 +425,22 @@ class TorchOps:
     # ------------------------------------------------------------- serving
     def kv_append(self, k, v, k_pages, v_pages, slots) -> None:
         """Copy rows ``k[n], v[n]`` (``[N, n_kv*hd]``) into cache slot ``slots[n]`` (= page*16 + offset)."""
-        row = k.shape[1]
+        n_kv, hd = k_pages.shape[1], k_pages.shape[3]          # cache layout [pages, n_kv, 16, hd]
         ok = slots >= 0
-        k_pages.view(-1, row)[slots[ok]] = k[ok]
-        v_pages.view(-1, row)[slots[ok]] = v[ok]
+        s = slots[ok]
+        k_pages[s // 16, :, s % 16] = k[ok].reshape(-1, n_kv, hd)
+        v_pages[s // 16, :, s % 16] = v[ok].reshape(-1, n_kv, hd)
 
     def paged_decode_attention(self, q, k_pages, v_pages, page_table, ctx_lens, max_ctx, n_q, n_kv, hd, split=256):
-        """One query token per request against its pages (``k_pages[P,16,n_kv,hd]``)."""
+        """One query token per request against its pages (``k_pages[P,n_kv,16,hd]``)."""
         B = q.shape[0]
         g = n_q // n_kv
         out = torch.empty(B, n_q * hd, device=q.device, dtype=q.dtype)
         for b in range(B):
             n = int(ctx_lens[b])
             pages = page_table[b, : (n + 15) // 16].long()
-            k = _f(k_pages[pages].reshape(-1, n_kv, hd)[:n]).permute(1, 0, 2).repeat_interleave(g, 0)
-            v = _f(v_pages[pages].reshape(-1, n_kv, hd)[:n]).permute(1, 0, 2).repeat_interleave(g, 0)
+            k = _f(k_pages[pages].permute(1, 0, 2, 3).reshape(n_kv, -1, hd)[:, :n]).repeat_interleave(g, 0)
+            v = _f(v_pages[pages].permute(1, 0, 2, 3).reshape(n_kv, -1, hd)[:, :n]).repeat_interleave(g, 0)
             qb = _f(q[b]).view(n_q, 1, hd)
             p = torch.softmax((qb @ k.transpose(1, 2)) / math.sqrt(hd), -1)
             out[b] = (p @ v).reshape(-1).to(q.dtype)

@@ -63,7 +63,7 @@ class PagedKVCache:
         self.n_kv = n_kv_local or cfg.num_kv_heads
         self.hd = cfg.head_dim
         self.num_pages = num_pages
-        shape = (cfg.num_layers, num_pages, PAGE, self.n_kv, self.hd)
+        shape = (cfg.num_layers, num_pages, self.n_kv, PAGE, self.hd)      # 16 rows of one (page, head) are contiguous
         self.k = torch.zeros(shape, device=device, dtype=dtype)
         self.v = torch.zeros(shape, device=device, dtype=dtype)
         self.free = list(range(num_pages - 1, -1, -1))

@@ -199,7 +199,7 @@ def test_paged_decode_and_kv_append(ops):
     B, n_q, n_kv, hd, P = 5, 6, 2, 128, 64
     ctx = torch.tensor([1, 16, 17, 300, 513], dtype=torch.int32, device="cuda")
     maxp = 40
-    k_pages = torch.zeros(P + 200, 16, n_kv, hd, device="cuda", dtype=torch.bfloat16)
+    k_pages = torch.zeros(P + 200, n_kv, 16, hd, device="cuda", dtype=torch.bfloat16)
     v_pages = torch.zeros_like(k_pages)
     table = torch.zeros(B, maxp, dtype=torch.int32, device="cuda")
     perm = torch.randperm(P + 200, device="cuda")

@@ -29,8 +29,8 @@ def _case(seed, B, n_q, n_kv, hd, ctx_list):
     ctx = torch.tensor(ctx_list, dtype=torch.int32, device="cuda")
     pages_per = (max(ctx_list) + 15) // 16
     n_pages = B * pages_per + 3
-    k_pages = (torch.randn(n_pages, 16, n_kv, hd, device="cuda", generator=g)).bfloat16()
-    v_pages = (torch.randn(n_pages, 16, n_kv, hd, device="cuda", generator=g)).bfloat16()
+    k_pages = (torch.randn(n_pages, n_kv, 16, hd, device="cuda", generator=g)).bfloat16()
+    v_pages = (torch.randn(n_pages, n_kv, 16, hd, device="cuda", generator=g)).bfloat16()
     perm = torch.randperm(n_pages, device="cuda", generator=g)[: B * pages_per].int()
     table = perm.view(B, pages_per).contiguous()
     q = torch.randn(B, n_q * hd, device="cuda", generator=g).bfloat16()
