@@ -17,13 +17,23 @@
 namespace {
 
 constexpr int BM = 128;            // rows per CTA (256 per pair)
-constexpr int BN = 256;            // tile columns (128 staged per CTA)
+constexpr int BNI = 256;           // columns per MMA instruction (128 rows of B staged per CTA)
 constexpr int BNH = 128;
-constexpr int BK = 64, STAGES = 6;
-constexpr int A_STAGE = BM * BK * 2, B_STAGE = BNH * BK * 2;
+constexpr int BK = 64;
+constexpr int A_STAGE = BM * BK * 2, B_SUB = BNH * BK * 2;
+// NSUB = 1: 256x256 tile per pair, six stages, two accumulator buffers (epilogue overlaps the next
+// tile).  NSUB = 2: 256x512 tile (two MMAs per K step that share A), four stages, one accumulator
+// set filling all 512 TMEM columns: 25 % less operand traffic per FLOP - the operand feed from L2
+// is what bounds the narrow tile - at the price of an epilogue that is not hidden.
+template <int NSUB> struct Cfg {
+    static constexpr int BN = BNI * NSUB;
+    static constexpr int STAGES = NSUB == 1 ? 6 : 4;
+    static constexpr int B_STAGE = B_SUB * NSUB;
+    static constexpr int NBUF = NSUB == 1 ? 2 : 1;
+    static constexpr int SMEM = STAGES * (A_STAGE + B_STAGE) + 1024 + 256 + 4 * 32 * 144;
+};
 constexpr int EPI_PITCH = 144;                      // staged row: 64 bf16 + 16 bytes (bank spread)
 constexpr int EPI_WARP_BYTES = 32 * EPI_PITCH;
-constexpr int SMEM_BYTES = STAGES * (A_STAGE + B_STAGE) + 1024 + 256 + 4 * EPI_WARP_BYTES;
 constexpr int GROUP_M = 8;
 
 struct Gemm2Params {
@@ -149,9 +159,11 @@ __device__ __forceinline__ void store32_16(T* dst, const T* cin, const uint32_t*
     }
 }
 
+template <int NSUB>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
 gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                          const Gemm2Params p) {
+    constexpr int BN = Cfg<NSUB>::BN, STAGES = Cfg<NSUB>::STAGES, B_STAGE = Cfg<NSUB>::B_STAGE, NBUF = Cfg<NSUB>::NBUF;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* sA = smem;
@@ -177,7 +189,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
             tc::mbar_init(&full[s], 1);
             tc::mbar_init(&empty[s], 1);
         }
-        for (int b = 0; b < 2; ++b) {
+        for (int b = 0; b < NBUF; ++b) {
             tc::mbar_init(&acc_full[b], 1);
             tc::mbar_init(&acc_empty[b], 8);
         }
@@ -205,7 +217,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
                 int b, tm, tn;
                 tile_coords(tile, tiles_m, tiles_n, b, tm, tn, p.group_m);
                 if (p.sym_upper && tn * BN + BN <= tm * 2 * BM) continue;
-                const int m0 = tm * 2 * BM + (int)rank * BM, n0 = tn * BN + (int)rank * BNH;
+                const int m0 = tm * 2 * BM + (int)rank * BM, n0 = tn * BN + (int)rank * BNH;   // sub-tile j adds j * BNI
                 for (int kb = 0; kb < kblocks; ++kb) {
                     if (!tc::mbar_wait(&empty[stage], phase ^ 1, abort_flag)) {
                         atomicMax(p.status, (int)KB_TIMEOUT_TMA);
@@ -223,12 +235,16 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
                     } else {
                         tma_load_3d_pair(a_dst, &tmA, full_leader, kb * BK, m0, b);
                     }
-                    if (p.b_mn) {
 #pragma unroll
-                        for (int c = 0; c < BNH / 64; ++c)
-                            tma_load_3d_pair(b_dst + c * (64 * BK * 2), &tmB, full_leader, n0 + c * 64, kb * BK, b);
-                    } else {
-                        tma_load_3d_pair(b_dst, &tmB, full_leader, kb * BK, n0, b);
+                    for (int j = 0; j < NSUB; ++j) {
+                        if (p.b_mn) {
+#pragma unroll
+                            for (int c = 0; c < BNH / 64; ++c)
+                                tma_load_3d_pair(b_dst + j * B_SUB + c * (64 * BK * 2), &tmB, full_leader,
+                                                 n0 + j * BNI + c * 64, kb * BK, b);
+                        } else {
+                            tma_load_3d_pair(b_dst + j * B_SUB, &tmB, full_leader, kb * BK, n0 + j * BNI, b);
+                        }
                     }
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
@@ -236,7 +252,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         }
     } else if (warp == 1) {
         if (lane == 0 && leader) {
-            const uint32_t idesc = tc::instr_desc_f16(2 * BM, BN, p.a_fmt, p.b_fmt, p.a_mn, p.b_mn);
+            const uint32_t idesc = tc::instr_desc_f16(2 * BM, BNI, p.a_fmt, p.b_fmt, p.a_mn, p.b_mn);
             int stage = 0;
             uint32_t phase = 0;
             int it = 0;
@@ -247,8 +263,8 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
                     tile_coords(tile, tiles_m, tiles_n, b_, tm_, tn_, p.group_m);
                     if (tn_ * BN + BN <= tm_ * 2 * BM) continue;
                 }
-                const int buf = it & 1;
-                const uint32_t acc_phase = (it >> 1) & 1;
+                const int buf = it % NBUF;
+                const uint32_t acc_phase = (it / NBUF) & 1;
                 ++it;
                 if (!tc::mbar_wait(&acc_empty[buf], acc_phase ^ 1, abort_flag)) {
                     atomicMax(p.status, (int)KB_TIMEOUT_MMA);
@@ -256,7 +272,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
                     break;
                 }
                 tc::tc_fence_after();
-                const uint32_t d_tmem = tmem_base + buf * BN;
+                const uint32_t d_tmem = tmem_base + buf * BN;      // NBUF * BN = 512 columns in both shapes
                 for (int kb = 0; kb < kblocks; ++kb) {
                     if (!tc::mbar_wait(&full[stage], phase, abort_flag)) {
                         atomicMax(p.status, (int)KB_TIMEOUT_MMA);
@@ -270,9 +286,13 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
                     for (int k = 0; k < BK / 16; ++k) {
                         const uint64_t ad = p.a_mn ? tc::smem_desc_sw128(a_addr + k * 2048, 64 * BK * 2, 1024)
                                                    : tc::smem_desc_sw128(a_addr + k * 32, 16, 1024);
-                        const uint64_t bd = p.b_mn ? tc::smem_desc_sw128(b_addr + k * 2048, 64 * BK * 2, 1024)
-                                                   : tc::smem_desc_sw128(b_addr + k * 32, 16, 1024);
-                        mma2_f16(d_tmem, ad, bd, idesc, (kb | k) != 0);
+#pragma unroll
+                        for (int j = 0; j < NSUB; ++j) {
+                            const uint32_t bj = b_addr + j * B_SUB;
+                            const uint64_t bd = p.b_mn ? tc::smem_desc_sw128(bj + k * 2048, 64 * BK * 2, 1024)
+                                                       : tc::smem_desc_sw128(bj + k * 32, 16, 1024);
+                            mma2_f16(d_tmem + j * BNI, ad, bd, idesc, (kb | k) != 0);
+                        }
                     }
                     // the stage is reusable in both CTAs once these MMAs have read it
                     commit2(mapa(smem_u32(&empty[stage]), 0));
@@ -293,8 +313,8 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
             int b, tm, tn;
             tile_coords(tile, tiles_m, tiles_n, b, tm, tn, p.group_m);
             if (p.sym_upper && tn * BN + BN <= tm * 2 * BM) continue;
-            const int buf = it & 1;
-            const uint32_t acc_phase = (it >> 1) & 1;
+            const int buf = it % NBUF;
+            const uint32_t acc_phase = (it / NBUF) & 1;
             ++it;
             if (!tc::mbar_wait(&acc_full[buf], acc_phase, abort_flag)) {
                 if (lane == 0) atomicMax(p.status, (int)KB_TIMEOUT_EPI);
@@ -304,7 +324,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
             tc::tc_fence_after();
             const int row = tm * 2 * BM + (int)rank * BM + quarter * 32 + lane;
             const uint32_t taddr = tmem_base + buf * BN + ((uint32_t)(quarter * 32) << 16);
-            const bool mirror = p.sym_upper && tn > tm;     // pair tiles are 256 x 256: tn > tm is strictly above the diagonal
+            const bool mirror = NSUB == 1 && p.sym_upper && tn > tm;     // 256 x 256 pair tiles: tn > tm is strictly above the diagonal
             if (p.epi_staged) {
                 // no addend, 16-bit output: each 32x64 chunk goes through shared memory so that a warp
                 // store covers four 128-byte row segments instead of 32 scattered 16-byte pieces
@@ -455,8 +475,10 @@ KB_API int kb_gemm_2cta(const void* A, const void* B, void* C, const void* Cin, 
     if (batch > 1 && ((a_bs & 7) || (b_bs & 7))) return 6;
     static bool attr_set = false;
     if (!attr_set) {
-        if (cudaFuncSetAttribute(gemm_tcgen05_2cta_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) !=
-            cudaSuccess)
+        if (cudaFuncSetAttribute(gemm_tcgen05_2cta_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 Cfg<1>::SMEM) != cudaSuccess ||
+            cudaFuncSetAttribute(gemm_tcgen05_2cta_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 Cfg<2>::SMEM) != cudaSuccess)
             return 7;
         attr_set = true;
     }
@@ -491,9 +513,24 @@ KB_API int kb_gemm_2cta(const void* A, const void* B, void* C, const void* Cin, 
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     if (max_ctas > 0 && max_ctas < sms) sms = max_ctas;
-    const int tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN) * batch;
+    // Wide tiles for large non-symmetric products whose tile count still fills the machine;
+    // KB_GEMM2_WIDE=0/1 forces the choice (tuning).
+    static int wide_env = -2;
+    if (wide_env == -2) {
+        const char* w = getenv("KB_GEMM2_WIDE");
+        wide_env = w ? atoi(w) : -1;
+    }
+    const long long m_tiles = (M + 2 * BM - 1) / (2 * BM);
+    const long long wide_tiles = m_tiles * ((N + 2 * BNI - 1) / (2 * BNI)) * batch;
+    // measured over the 3B projection shapes: 0.94x of cuBLAS with wide tiles against 0.87x without
+    // (products with an addend keep the narrow tile: their epilogue is the slow per-row path, and with
+    // one accumulator set it would sit on the critical path - Newton-Schulz got 12 % slower with it)
+    bool wide = !sym_upper && !Cin && N >= 2 * BNI && wide_tiles >= 2 * (sms / 2);
+    if (wide_env >= 0) wide = wide && wide_env != 0;
+    const long long tiles = wide ? wide_tiles : m_tiles * ((N + BNI - 1) / BNI) * batch;
     int pairs = sms / 2;
-    if (tiles < pairs) pairs = tiles;
-    gemm_tcgen05_2cta_kernel<<<2 * pairs, 192, SMEM_BYTES, st>>>(tmA, tmB, p);
+    if (tiles < pairs) pairs = (int)tiles;
+    if (wide) gemm_tcgen05_2cta_kernel<2><<<2 * pairs, 192, Cfg<2>::SMEM, st>>>(tmA, tmB, p);
+    else gemm_tcgen05_2cta_kernel<1><<<2 * pairs, 192, Cfg<1>::SMEM, st>>>(tmA, tmB, p);
     return 0;
 }

@@ -36,6 +36,25 @@ def test_gemm_nt(ops, M, N, K):
     assert rel_err(c, ref) < 1e-2, rel_err(c, ref)
 
 
+@pytest.mark.parametrize("M,N,K", [(8192, 5120, 320), (8192, 5000, 192), (16384, 3072, 128)])
+def test_gemm_wide_pair_tiles(ops, M, N, K):
+    """Shapes large enough for the 256x512 CTA-pair tiles (>= 148 of them), incl. a ragged N: all three
+    operand layouts, an addend, and the fp32 output path."""
+    a, b = bf(M, K, seed=1), bf(N, K, seed=2)
+    ref = a.float() @ b.float().t()
+    assert rel_err(ops.gemm_nt(a, b), ref) < 1e-2
+    bt = b.t().contiguous()                               # [K, N]
+    assert rel_err(ops.gemm_nn(a, bt), ref) < 1e-2
+    at = a.t().contiguous()                               # [K, M]
+    assert rel_err(ops.gemm_tn(at, bt), ref) < 1e-2
+    r = bf(M, N, seed=3)
+    assert rel_err(ops.gemm_nt(a, b, residual=r), ref + r.float()) < 1e-2
+    o32 = torch.zeros(M, N, device="cuda")
+    ops._gemm(a, b, M, N, K, False, False, out=o32)
+    assert rel_err(o32, ref) < 1e-3
+    ops.check_status()
+
+
 def test_gemm_nt_epilogues(ops):
     M, N, K = 256, 512, 192
     a, b, r = bf(M, K, seed=1), bf(N, K, seed=2), bf(M, N, seed=3)
