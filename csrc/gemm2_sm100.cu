@@ -47,6 +47,7 @@ struct Gemm2Params {
     int sym_upper;             // square symmetric result: tiles strictly below the diagonal are skipped
     int group_m;               // raster: tiles are visited in column sweeps over groups of this many tile rows
     int epi_staged;            // 16-bit output without addend: transpose chunks through shared memory, store 128-byte row segments
+    float diag_add;            // added to the diagonal of the result (after alpha/beta): folds the a*X term of Newton-Schulz into B
 };
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -387,6 +388,12 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
                 tc::tmem_ld_wait();
                 const int col = tn * BN + c0;
                 const int ncols = min(32, p.N - col);
+                if (p.diag_add != 0.f && row >= col && row < col + 32) {
+                    const float d = p.diag_add / p.alpha;      // the stores below scale by alpha
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (col + j == row) acc[j] = __float_as_uint(__uint_as_float(acc[j]) + d);
+                }
                 if (row < p.M && ncols > 0) {
                     const long long off = (long long)b * p.c_batch_stride + (long long)row * p.ldc + col;
                     const long long offin = (long long)b * p.cin_batch_stride + (long long)row * p.ldcin + col;
@@ -468,7 +475,8 @@ int make_tmap2(CUtensorMap* m, const void* base, int fmt, long long cols, long l
 KB_API int kb_gemm_2cta(const void* A, const void* B, void* C, const void* Cin, int M, int N, int K, int batch,
                         long long lda, long long ldb, long long ldc, long long ldcin, long long a_bs, long long b_bs,
                         long long c_bs, long long cin_bs, int a_mn, int b_mn, int a_fmt, int b_fmt, int out_type,
-                        float alpha, float beta, int* status, int max_ctas, int sym_upper, cudaStream_t st) {
+                        float alpha, float beta, int* status, int max_ctas, int sym_upper, float diag_add,
+                        cudaStream_t st) {
     if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return 5;
     if (sym_upper && M != N) return 5;
     if ((lda & 7) || (ldb & 7) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15)) return 6;
@@ -497,6 +505,8 @@ KB_API int kb_gemm_2cta(const void* A, const void* B, void* C, const void* Cin, 
     p.ldc = ldc; p.c_batch_stride = c_bs; p.ldcin = ldcin; p.cin_batch_stride = cin_bs;
     p.status = status;
     p.sym_upper = sym_upper;
+    p.diag_add = diag_add;
+    if (diag_add != 0.f && (alpha == 0.f || !Cin)) return 5;     // implemented on the addend epilogue only
     {
         static int group_m = 0, staged = -1;
         if (!group_m) {

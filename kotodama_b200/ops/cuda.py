@@ -85,7 +85,9 @@ class CudaOps(TorchOps):
     def _gemm(self, a: torch.Tensor, b: torch.Tensor, M: int, N: int, K: int, a_mn: bool, b_mn: bool,
               out: Optional[torch.Tensor] = None, cin: Optional[torch.Tensor] = None, alpha: float = 1.0,
               beta: float = 0.0, out_dtype: Optional[torch.dtype] = None, batch: int = 1,
-              sym_upper: bool = False) -> torch.Tensor:
+              sym_upper: bool = False, diag: float = 0.0) -> torch.Tensor:
+        """``diag`` is added to the diagonal of the result (fused into the CTA-pair kernel's epilogue when
+        there is an addend, a separate in-place add otherwise)."""
         out_dtype = out_dtype or (out.dtype if out is not None else a.dtype)
         lead = (batch,) if batch > 1 else ()
         if out is None:
@@ -97,6 +99,8 @@ class CudaOps(TorchOps):
             if cin is not None:
                 r = r + beta * cin.float()
             out.copy_(r)
+            if diag:
+                out.diagonal(dim1=-2, dim2=-1).add_(diag)
             return out
         for t in (a, b):
             if t.stride(-1) != 1 or t.stride(-2) % 8 or t.data_ptr() % 16 or t.dtype not in _FMT:
@@ -124,6 +128,8 @@ class CudaOps(TorchOps):
             self._rc(rc, "kb_gemm(split-k)")
             self._rc(self.lib.kb_f32_to_bf16_add(_p(ws), _p(cin), _F(beta), _p(out), _LL(M * N), _I(1), _st()),
                      "kb_f32_to_bf16_add")
+            if diag:
+                out.diagonal(dim1=-2, dim2=-1).add_(diag)
             return out
         if self.gemm_2cta and M >= 256 and N >= 256:
             # large products: CTA pairs (256x256 tiles, tcgen05 cta_group::2)
@@ -133,8 +139,10 @@ class CudaOps(TorchOps):
                                        _LL(bs(a)), _LL(bs(b)), _LL(bs(out)), _LL(bs(cin) if cin is not None else 0),
                                        _I(int(a_mn)), _I(int(b_mn)), _I(_FMT[a.dtype]), _I(_FMT[b.dtype]),
                                        _I(_OUT[out.dtype]), _F(alpha), _F(beta), _p(self.status(a.device)),
-                                       _I(self.gemm_max_ctas), _I(int(sym_upper)), _st())
+                                       _I(self.gemm_max_ctas), _I(int(sym_upper)), _F(diag if cin is not None else 0.0), _st())
             self._rc(rc, "kb_gemm_2cta")
+            if diag and cin is None:
+                out.diagonal(dim1=-2, dim2=-1).add_(diag)
             # sym_upper: only tiles on/above the diagonal are computed; the epilogue writes each of them
             # to its mirrored position as well (16-bit outputs)
             if sym_upper and out.dtype == torch.float32:
@@ -148,6 +156,8 @@ class CudaOps(TorchOps):
                               _I(int(a_mn)), _I(int(b_mn)), _I(_FMT[a.dtype]), _I(_FMT[b.dtype]), _I(_OUT[out.dtype]),
                               _F(alpha), _F(beta), _p(self.status(a.device)), _I(self.gemm_max_ctas), _I(1), _st())
         self._rc(rc, "kb_gemm")
+        if diag:
+            out.diagonal(dim1=-2, dim2=-1).add_(diag)
         return out
 
     # ------------------------------------------------------------------ block-scaled fp8
@@ -403,11 +413,13 @@ class CudaOps(TorchOps):
         batch = x.shape[0] if x.ndim == 3 else 1
         sym = self.gemm_2cta and R >= 512 and x.element_size() == 2
         A = self._gemm(x, x, R, R, C, False, False, batch=batch, sym_upper=sym)
-        B = self._gemm(A, A, R, R, R, False, False, cin=A, alpha=c, beta=b, batch=batch, sym_upper=sym)
+        # aX + BX = (B + aI) X: the identity term goes onto B's diagonal in the epilogue that produces B,
+        # so the last (largest) product needs no addend
+        B = self._gemm(A, A, R, R, R, False, False, cin=A, alpha=c, beta=b, batch=batch, sym_upper=sym, diag=a)
         if self.mn_major:
-            return self._gemm(B, x, R, C, R, False, True, cin=x, alpha=1.0, beta=a, batch=batch)
-        xt = self.transpose(x)
-        return self._gemm(B, xt, R, C, R, False, False, cin=x, alpha=1.0, beta=a, batch=batch)
+            return self._gemm(B, x, R, C, R, False, True, batch=batch)
+        xt = self.transpose(x) if x.ndim == 2 else x.transpose(-1, -2).contiguous()
+        return self._gemm(B, xt, R, C, R, False, False, batch=batch)
 
     def muon_apply(self, p, orth, lr, wd, scale, transposed):
         R, C = p.shape
