@@ -47,6 +47,7 @@ struct Gemm2Params {
     int sym_upper;             // square symmetric result: tiles strictly below the diagonal are skipped
     int group_m;               // raster: tiles are visited in column sweeps over groups of this many tile rows
     int epi_staged;            // 16-bit output without addend: transpose chunks through shared memory, store 128-byte row segments
+    int epi_cin_staged;        // 16-bit output and addend, no symmetry/diagonal: coalesced addend reads and stores
     float diag_add;            // added to the diagonal of the result (after alpha/beta): folds the a*X term of Newton-Schulz into B
 };
 
@@ -380,6 +381,55 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
                     }
                     __syncwarp();
                 }
+            } else if (p.epi_cin_staged) {
+                // 16-bit output with a 16-bit addend: each 32x32 fp32 chunk is transposed through shared
+                // memory; a lane then owns four consecutive columns of one row, so addend reads and result
+                // stores are 64-byte row segments (eight lanes per row) instead of one row per lane
+                float* stg = reinterpret_cast<float*>(smem + STAGES * (A_STAGE + B_STAGE) + 256 + (warp - 2) * EPI_WARP_BYTES);
+                const int row0 = tm * 2 * BM + (int)rank * BM + quarter * 32;
+                const long long obase = (long long)b * p.c_batch_stride + (long long)row0 * p.ldc;
+                const long long ibase = (long long)b * p.cin_batch_stride + (long long)row0 * p.ldcin;
+                const uint16_t* cin16 = reinterpret_cast<const uint16_t*>(p.Cin);
+                uint16_t* out16 = reinterpret_cast<uint16_t*>(p.C);
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN; c0 += 32) {
+                    uint32_t acc[32];
+                    tc::tmem_ld32(taddr + c0, acc);
+                    tc::tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        *reinterpret_cast<float4*>(stg + lane * (EPI_PITCH / 4) + 4 * j) =
+                            make_float4(p.alpha * __uint_as_float(acc[4 * j]), p.alpha * __uint_as_float(acc[4 * j + 1]),
+                                        p.alpha * __uint_as_float(acc[4 * j + 2]), p.alpha * __uint_as_float(acc[4 * j + 3]));
+                    __syncwarp();
+                    const int col = tn * BN + c0 + (lane & 7) * 4;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const int rr = i * 4 + (lane >> 3);
+                        if (row0 + rr < p.M && col < p.N) {
+                            float4 v = *reinterpret_cast<const float4*>(stg + rr * (EPI_PITCH / 4) + (lane & 7) * 4);
+                            const uint2 craw = *reinterpret_cast<const uint2*>(cin16 + ibase + (long long)rr * p.ldcin + col);
+                            uint2 o;
+                            if (p.out_type == 1) {
+                                const __nv_bfloat162* c2 = reinterpret_cast<const __nv_bfloat162*>(&craw);
+                                const float2 c01 = __bfloat1622float2(c2[0]), c23 = __bfloat1622float2(c2[1]);
+                                __nv_bfloat162 r0 = __floats2bfloat162_rn(v.x + p.beta * c01.x, v.y + p.beta * c01.y);
+                                __nv_bfloat162 r1 = __floats2bfloat162_rn(v.z + p.beta * c23.x, v.w + p.beta * c23.y);
+                                o.x = *reinterpret_cast<uint32_t*>(&r0);
+                                o.y = *reinterpret_cast<uint32_t*>(&r1);
+                            } else {
+                                const __half2* c2 = reinterpret_cast<const __half2*>(&craw);
+                                const float2 c01 = __half22float2(c2[0]), c23 = __half22float2(c2[1]);
+                                __half2 r0 = __floats2half2_rn(v.x + p.beta * c01.x, v.y + p.beta * c01.y);
+                                __half2 r1 = __floats2half2_rn(v.z + p.beta * c23.x, v.w + p.beta * c23.y);
+                                o.x = *reinterpret_cast<uint32_t*>(&r0);
+                                o.y = *reinterpret_cast<uint32_t*>(&r1);
+                            }
+                            *reinterpret_cast<uint2*>(out16 + obase + (long long)rr * p.ldc + col) = o;
+                        }
+                    }
+                    __syncwarp();
+                }
             } else
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 32) {
@@ -518,6 +568,15 @@ KB_API int kb_gemm_2cta(const void* A, const void* B, void* C, const void* Cin, 
         }
         p.group_m = group_m;
         p.epi_staged = staged && !Cin && out_type != 2 && !(N & 7) && !(ldc & 7) && !(c_bs & 7);
+        // off unless KB_GEMM2_CIN_STAGED=1: measured slower (1-GPU step 861 -> 904 ms) - an addend read costs a
+        // memory round trip per chunk, which only the narrow tile's second accumulator buffer hides
+        static int cin_staged = -1;
+        if (cin_staged < 0) {
+            const char* e = getenv("KB_GEMM2_CIN_STAGED");
+            cin_staged = e ? atoi(e) : 0;
+        }
+        p.epi_cin_staged = cin_staged && staged && Cin && out_type != 2 && !sym_upper && diag_add == 0.f && !(N & 3) && !(ldc & 3) &&
+                           !(ldcin & 3) && !(c_bs & 3) && !(cin_bs & 3) && !((uintptr_t)C & 7) && !((uintptr_t)Cin & 7);
     }
     int sms = 0, dev = 0;
     cudaGetDevice(&dev);
@@ -533,8 +592,8 @@ KB_API int kb_gemm_2cta(const void* A, const void* B, void* C, const void* Cin, 
     const long long m_tiles = (M + 2 * BM - 1) / (2 * BM);
     const long long wide_tiles = m_tiles * ((N + 2 * BNI - 1) / (2 * BNI)) * batch;
     // measured over the 3B projection shapes: 0.94x of cuBLAS with wide tiles against 0.87x without
-    // (products with an addend keep the narrow tile: their epilogue is the slow per-row path, and with
-    // one accumulator set it would sit on the critical path - Newton-Schulz got 12 % slower with it)
+    // (products with an addend keep the narrow tile: reading the addend in an epilogue that is not hidden
+    // behind the next tile cost more than the wide tile gains)
     bool wide = !sym_upper && !Cin && N >= 2 * BNI && wide_tiles >= 2 * (sms / 2);
     if (wide_env >= 0) wide = wide && wide_env != 0;
     const long long tiles = wide ? wide_tiles : m_tiles * ((N + BNI - 1) / BNI) * batch;
