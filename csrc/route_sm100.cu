@@ -38,7 +38,7 @@ constexpr int MAX_STAGES = 4;
 
 // Shared-memory layout: [stages][rows][D] bf16, then barriers.
 template <int MAXS, int CPT, bool BWD>
-__global__ void __launch_bounds__(BWD ? 512 : 256)
+__global__ void __launch_bounds__(BWD ? 384 : 256)
 route_pipe_kernel(RouteSrcs srcs, RouteDsts dsts, int S, const bf16* __restrict__ dxn, const bf16* __restrict__ q,
                   const bf16* __restrict__ rn_w, const bf16* __restrict__ n_w, bf16* __restrict__ xn,
                   float* __restrict__ alpha_g, float* __restrict__ r_g, float* __restrict__ logit_g,
@@ -370,7 +370,7 @@ struct PipeCfg {
 PipeCfg pipe_cfg(int S, int D, bool bwd) {
     PipeCfg c{};
     const int nchunks = D / 8;
-    const int max_threads = bwd ? 512 : 256;
+    const int max_threads = bwd ? 384 : 256;      // 384 x 8 elements = D 3072 in one pass; leaves 170 registers per thread
     c.cpt = (nchunks + max_threads - 1) / max_threads;
     c.threads = ((nchunks + c.cpt - 1) / c.cpt + 31) / 32 * 32;
     const size_t stage = (size_t)(S + (bwd ? 1 : 0)) * D * 2;

@@ -6,7 +6,7 @@
 // src/model/llama.py:333-337).  A request's pages are listed in page_table[req][i].
 #include <stdlib.h>
 
-#include "common.cuh"
+#include "tc.cuh"
 
 typedef __nv_bfloat16 bf16;
 constexpr int PAGE = 16;
@@ -387,6 +387,210 @@ __global__ void paged_merge_kernel(const float* __restrict__ part_o, const float
     if (d < HD) out[(size_t)req * out_stride + (size_t)head * HD + d] = __float2bfloat16(den > 0.f ? num / den : 0.f);
 }
 
+// Bulk-copy variant of the streaming kernel (the default for head_dim 128): with the head-major page layout
+// the 16 K rows (and the 16 V rows) of one page are one contiguous 4 KB block, so one thread streams
+// pages into a shared-memory ring with cp.async.bulk + mbarrier transaction counts and all threads
+// compute from shared memory.  Bytes in flight are set by the ring (64 KB per CTA), not by registers.
+// A stage holds two pages (K0 K1 V0 V1); waits are bounded: on a timeout the split contributes
+// nothing and kb_decode_status() reports it.
+__device__ int g_decode_status = 0;
+
+__device__ __forceinline__ void bulk_g2s_dec(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     smem_u32(dst)),
+                 "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+
+template <int HD, int G>
+__global__ void __launch_bounds__(128, 3)
+paged_decode_bulk_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* __restrict__ k_pages,
+                         const bf16* __restrict__ v_pages, const int* __restrict__ page_table, int max_pages,
+                         const int* __restrict__ ctx_lens, int n_kv, int split_tokens, float scale,
+                         float* __restrict__ part_o, float* __restrict__ part_ml, int nsplit) {
+    constexpr int LPT = HD / 16, TPW = 32 / LPT, NST = 4;
+    constexpr int PG = PAGE * HD;                       // elements of one (page, head) block
+    extern __shared__ __align__(128) uint8_t ring_raw[];
+    bf16* ring = reinterpret_cast<bf16*>(ring_raw);     // [NST][4][PG]: K0 K1 V0 V1
+    __shared__ float qs[G][HD];
+    __shared__ int spage[2048 / PAGE];
+    __shared__ float wo[4][G][HD];
+    __shared__ float wml[4][G][2];
+    __shared__ uint64_t full[NST];
+    __shared__ int abort_flag;
+    const int kvh = blockIdx.x, req = blockIdx.y, sp = blockIdx.z;
+    const int ctx = ctx_lens[req];
+    const int t0 = sp * split_tokens;
+    const int nt = min(split_tokens, ctx - t0);
+    const size_t pbase = ((size_t)(req * n_kv + kvh) * nsplit + sp);
+    if (nt <= 0) {
+        if (threadIdx.x < G) {
+            part_ml[(pbase * G + threadIdx.x) * 2] = -INFINITY;
+            part_ml[(pbase * G + threadIdx.x) * 2 + 1] = 0.f;
+        }
+        return;
+    }
+    const int npages = (nt + PAGE - 1) / PAGE, niter = (npages + 1) / 2;
+    const float qscale = scale * 1.4426950408889634f;
+    for (int i = threadIdx.x; i < G * HD; i += blockDim.x) {
+        const int g = i / HD, d = i % HD;
+        qs[g][d] = __bfloat162float(q[(size_t)req * q_stride + (size_t)(kvh * G + g) * HD + d]) * qscale;
+    }
+    for (int i = threadIdx.x; i < npages; i += blockDim.x)
+        spage[i] = page_table[(size_t)req * max_pages + t0 / PAGE + i];
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < NST; ++s) tc::mbar_init(&full[s], 1);
+        abort_flag = 0;
+        tc::fence_barrier_init();
+    }
+    __syncthreads();
+    auto issue = [&](int it) {
+        const int st = it % NST;
+        const int np = min(2, npages - 2 * it);
+        tc::mbar_expect_tx(&full[st], (uint32_t)(np * 2 * PG * 2));
+        for (int j = 0; j < np; ++j) {
+            const size_t src = ((size_t)spage[2 * it + j] * n_kv + kvh) * PG;
+            bulk_g2s_dec(ring + ((size_t)st * 4 + j) * PG, k_pages + src, PG * 2, &full[st]);
+            bulk_g2s_dec(ring + ((size_t)st * 4 + 2 + j) * PG, v_pages + src, PG * 2, &full[st]);
+        }
+    };
+    if (threadIdx.x == 0)
+        for (int it = 0; it < NST && it < niter; ++it) issue(it);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int sub = lane % LPT, tw = lane / LPT;
+    float qr[G][16], o[G][16], m[G], l[G];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        m[g] = -INFINITY;
+        l[g] = 0.f;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            qr[g][i] = qs[g][(i < 8 ? 0 : HD / 2) + sub * 8 + (i & 7)];
+            o[g][i] = 0.f;
+        }
+    }
+    bool ok = true;
+    for (int it = 0; it < niter; ++it) {
+        const int st = it % NST;
+        if (!tc::mbar_wait(&full[st], (uint32_t)(it / NST) & 1u, &abort_flag)) {
+            ok = false;
+            break;
+        }
+        const int tin = warp * TPW + tw;                 // token within a page (HD 128: 4 warps x 4 = 16)
+        float sc[2][G];
+        bf16x8 vr[2][2];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const bool valid = tin < PAGE && (2 * it + u) * PAGE + tin < nt;
+            float kf[16];
+            if (valid) {
+                const bf16* kp = ring + ((size_t)st * 4 + u) * PG + (size_t)tin * HD + sub * 8;
+                unpack8(ld8(kp), kf);
+                unpack8(ld8(kp + HD / 2), kf + 8);
+                const bf16* vp = ring + ((size_t)st * 4 + 2 + u) * PG + (size_t)tin * HD + sub * 8;
+                vr[u][0] = ld8(vp);
+                vr[u][1] = ld8(vp + HD / 2);
+            }
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                float a = 0.f;
+                if (valid) {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) a += kf[i] * qr[g][i];
+                }
+#pragma unroll
+                for (int x = LPT / 2; x > 0; x >>= 1) a += __shfl_xor_sync(0xffffffffu, a, x);
+                sc[u][g] = valid ? a : -INFINITY;
+            }
+        }
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            const float mn = fmaxf(m[g], fmaxf(sc[0][g], sc[1][g]));
+            if (mn == -INFINITY) continue;
+            const float f = exp2f(m[g] - mn);
+            m[g] = mn;
+            l[g] *= f;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) o[g][i] *= f;
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            if (tin < PAGE && (2 * it + u) * PAGE + tin < nt) {
+                float vf[16];
+                unpack8(vr[u][0], vf);
+                unpack8(vr[u][1], vf + 8);
+#pragma unroll
+                for (int g = 0; g < G; ++g) {
+                    const float pw = exp2f(sc[u][g] - m[g]);
+                    l[g] += pw;
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) o[g][i] += pw * vf[i];
+                }
+            }
+        }
+        __syncthreads();                                 // every thread is done with this stage
+        if (threadIdx.x == 0 && it + NST < niter) issue(it + NST);
+    }
+    if (!ok) {
+        // a copy did not arrive in time: report, contribute nothing, and let copies in flight land
+        if (threadIdx.x == 0) {
+            atomicMax(&g_decode_status, (int)KB_TIMEOUT_TMA);
+            const uint64_t t_0 = global_timer_ns();
+            while (global_timer_ns() - t_0 < 2000000ull) {}
+        }
+        __syncthreads();
+#pragma unroll
+        for (int g = 0; g < G; ++g) { m[g] = -INFINITY; l[g] = 0.f; }
+    }
+    // merge the lane groups of the warp, then the warps (same as the streaming kernel)
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        float mg = m[g];
+#pragma unroll
+        for (int x = LPT; x < 32; x <<= 1) mg = fmaxf(mg, __shfl_xor_sync(0xffffffffu, mg, x));
+        const float f = (mg == -INFINITY || m[g] == -INFINITY) ? 0.f : exp2f(m[g] - mg);
+        float lg = l[g] * f;
+#pragma unroll
+        for (int x = LPT; x < 32; x <<= 1) lg += __shfl_xor_sync(0xffffffffu, lg, x);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            float v = o[g][i] * f;
+#pragma unroll
+            for (int x = LPT; x < 32; x <<= 1) v += __shfl_xor_sync(0xffffffffu, v, x);
+            if (tw == 0) wo[warp][g][(i < 8 ? 0 : HD / 2) + sub * 8 + (i & 7)] = v;
+        }
+        if (lane == 0) {
+            wml[warp][g][0] = mg;
+            wml[warp][g][1] = lg;
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < G * HD; i += blockDim.x) {
+        const int g = i / HD, d = i % HD;
+        const float mx = fmaxf(fmaxf(wml[0][g][0], wml[1][g][0]), fmaxf(wml[2][g][0], wml[3][g][0]));
+        float acc = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w)
+            if (wml[w][g][0] != -INFINITY) acc += wo[w][g][d] * exp2f(wml[w][g][0] - mx);
+        part_o[(pbase * G + g) * HD + d] = acc;
+    }
+    if (threadIdx.x < G) {
+        const int g = threadIdx.x;
+        const float mx = fmaxf(fmaxf(wml[0][g][0], wml[1][g][0]), fmaxf(wml[2][g][0], wml[3][g][0]));
+        float sum = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w)
+            if (wml[w][g][0] != -INFINITY) sum += wml[w][g][1] * exp2f(wml[w][g][0] - mx);
+        part_ml[(pbase * G + g) * 2] = mx == -INFINITY ? -INFINITY : mx * 0.6931471805599453f;
+        part_ml[(pbase * G + g) * 2 + 1] = sum;
+    }
+}
+KB_API int kb_decode_status() {
+    int v = 0;
+    cudaMemcpyFromSymbol(&v, g_decode_status, sizeof(int));
+    return v;
+}
+
 // Workspace sizes (floats) for B requests: part_o = B*n_kv*nsplit*G*hd, part_ml = B*n_kv*nsplit*G*2.
 KB_API int kb_paged_decode(const void* q, long long q_stride, const void* k_pages, const void* v_pages,
                            const int* page_table, int max_pages, const int* ctx_lens, int B, int n_q, int n_kv, int hd,
@@ -397,19 +601,30 @@ KB_API int kb_paged_decode(const void* q, long long q_stride, const void* k_page
     const int nsplit = (max_ctx + split_tokens - 1) / split_tokens;
     dim3 grid(n_kv, B, nsplit);
     const size_t smem = (size_t)G * split_tokens * sizeof(float);
-    // KB_DECODE_KERNEL=phases selects the three-phase kernel (scores in shared memory); the default is
-    // the streaming online-softmax kernel
+    // KB_DECODE_KERNEL: "bulk" (default for head_dim 128: pages streamed into a shared-memory ring by
+    // cp.async.bulk, measured 0.114 ms against 0.136 ms), "stream" (online softmax from registers) or
+    // "phases" (three-phase kernel with the scores in shared memory)
     static int streaming = -1, unroll = 2;
     if (streaming < 0) {
         const char* e = getenv("KB_DECODE_KERNEL");
-        streaming = !(e && e[0] == 'p');
+        streaming = (e && e[0] == 'p') ? 0 : (e && e[0] == 's') ? 1 : 2;     // phases | stream | bulk (default)
         // tokens per lane group and iteration: 2 (default: 168 registers, three CTAs per SM; measured
         // 0.136 ms against 0.155 ms for 4, which needs 237 registers and leaves two CTAs per SM)
         const char* u = getenv("KB_DECODE_UNROLL");
         if (u && atoi(u) == 4) unroll = 4;
     }
 #define DEC(HD_, G_)                                                                                          \
-    if (streaming && (G_) <= 4 && unroll == 4)                                                                 \
+    if (streaming == 2 && (HD_) == 128 && (G_) <= 4) {                                                         \
+        static bool attr = false;                                                                              \
+        if (!attr) {                                                                                           \
+            if (cudaFuncSetAttribute(paged_decode_bulk_kernel<HD_, G_>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                     4 * 4 * PAGE * (HD_) * 2) != cudaSuccess) return 7;                       \
+            attr = true;                                                                                       \
+        }                                                                                                      \
+        paged_decode_bulk_kernel<HD_, G_><<<grid, 128, 4 * 4 * PAGE * (HD_) * 2, st>>>(                        \
+            (const bf16*)q, q_stride, (const bf16*)k_pages, (const bf16*)v_pages, page_table, max_pages, ctx_lens, \
+            n_kv, split_tokens, scale, part_o, part_ml, nsplit);                                               \
+    } else if (streaming && (G_) <= 4 && unroll == 4)                                                          \
         paged_decode_stream_kernel<HD_, G_, 4><<<grid, 128, 0, st>>>((const bf16*)q, q_stride, (const bf16*)k_pages, \
                                                               (const bf16*)v_pages, page_table, max_pages, ctx_lens, \
                                                               n_kv, split_tokens, scale, part_o, part_ml, nsplit); \

@@ -80,6 +80,11 @@ class CudaOps(TorchOps):
             if v != 0:
                 t.zero_()
                 raise KernelError(f"device {idx}: a kernel wait timed out (status {v})")
+        if self._status:        # the decode kernels keep their own status word (no status argument)
+            torch.cuda.synchronize()
+            v = int(self.lib.kb_decode_status())
+            if v != 0:
+                raise KernelError(f"paged decode attention: a bulk copy did not arrive in time (status {v})")
 
     # ------------------------------------------------------------------ GEMM
     def _gemm(self, a: torch.Tensor, b: torch.Tensor, M: int, N: int, K: int, a_mn: bool, b_mn: bool,
@@ -439,7 +444,7 @@ class CudaOps(TorchOps):
         self._rc(self.lib.kb_kv_append(_p(k), _p(v), _LL(k.stride(0)), _LL(v.stride(0)), _p(k_pages), _p(v_pages),
                                        _p(slots), _I(N), _I(row), _I(k_pages.shape[-1]), _st()), "kb_kv_append")
 
-    def paged_decode_attention(self, q, k_pages, v_pages, page_table, ctx_lens, max_ctx, n_q, n_kv, hd, split=256):
+    def paged_decode_attention(self, q, k_pages, v_pages, page_table, ctx_lens, max_ctx, n_q, n_kv, hd, split=512):
         """``q[B, n_q*hd]`` (one new token per request) against the paged cache; returns ``[B, n_q*hd]``."""
         B = q.shape[0]
         nsplit = (max_ctx + split - 1) // split

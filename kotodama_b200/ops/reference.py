@@ -431,7 +431,7 @@ class TorchOps:
         k_pages[s // 16, :, s % 16] = k[ok].reshape(-1, n_kv, hd)
         v_pages[s // 16, :, s % 16] = v[ok].reshape(-1, n_kv, hd)
 
-    def paged_decode_attention(self, q, k_pages, v_pages, page_table, ctx_lens, max_ctx, n_q, n_kv, hd, split=256):
+    def paged_decode_attention(self, q, k_pages, v_pages, page_table, ctx_lens, max_ctx, n_q, n_kv, hd, split=512):
         """One query token per request against its pages (``k_pages[P,n_kv,16,hd]``)."""
         B = q.shape[0]
         g = n_q // n_kv
