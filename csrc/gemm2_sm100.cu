@@ -48,6 +48,11 @@ struct Gemm2Params {
     int group_m;               // raster: tiles are visited in column sweeps over groups of this many tile rows
     int epi_staged;            // 16-bit output without addend: transpose chunks through shared memory, store 128-byte row segments
     int epi_cin_staged;        // 16-bit output and addend, no symmetry/diagonal: coalesced addend reads and stores
+    // all-gather coupling (see kb_gemm_ag in gemm_sm100.cu): the gathered operand sits in a local staging
+    // buffer that peers fill shard by shard; producers wait (bounded) for a shard's flag before its first tile
+    const int* ag_flags;       // null: none
+    int ag_epoch, ag_rows, ag_dim, ag_rot;   // rows per shard; 0 = shards along M (A rows), 1 = along K; own-first rotation
+    unsigned long long ag_limit_ns;
     float diag_add;            // added to the diagonal of the result (after alpha/beta): folds the a*X term of Newton-Schulz into B
 };
 
@@ -113,6 +118,30 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
     t -= g * group;
     tm = first_m + t % gm;
     tn = t / gm;
+}
+
+__device__ __forceinline__ bool wait_shard2(const int* flag, int epoch, unsigned long long limit_ns,
+                                            volatile int* abort_flag) {
+    int v;
+    asm volatile("ld.relaxed.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+    if (v < epoch) {
+        const uint64_t t0 = global_timer_ns();
+        unsigned sleep_ns = 64;
+        for (;;) {
+            asm volatile("ld.relaxed.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+            if (v >= epoch) break;
+            if (*abort_flag) return false;
+            if (global_timer_ns() - t0 > limit_ns) {
+                *abort_flag = 1;
+                return false;
+            }
+            __nanosleep(sleep_ns);
+            if (sleep_ns < 1024) sleep_ns <<= 1;
+        }
+    }
+    __threadfence_system();
+    asm volatile("fence.proxy.async;" ::: "memory");
+    return true;
 }
 
 template <typename T>
@@ -215,12 +244,41 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
+            unsigned ready_mask = 0;        // shards already seen ready
             for (int tile = pair; tile < num_tiles && ok; tile += npairs) {
                 int b, tm, tn;
                 tile_coords(tile, tiles_m, tiles_n, b, tm, tn, p.group_m);
                 if (p.sym_upper && tn * BN + BN <= tm * 2 * BM) continue;
+                if (p.ag_flags && p.ag_dim == 0) {
+                    tm += p.ag_rot;
+                    if (tm >= tiles_m) tm -= tiles_m;
+                    const int s0 = (tm * 2 * BM) / p.ag_rows, s1 = (min(tm * 2 * BM + 2 * BM, p.M) - 1) / p.ag_rows;
+                    for (int sh = s0; sh <= s1 && ok; ++sh) {
+                        if (ready_mask >> sh & 1) continue;
+                        if (!wait_shard2(p.ag_flags + sh, p.ag_epoch, p.ag_limit_ns, abort_flag)) {
+                            atomicMax(p.status, (int)KB_TIMEOUT_PEER);
+                            ok = false;
+                        }
+                        ready_mask |= 1u << sh;
+                    }
+                    if (!ok) break;
+                }
                 const int m0 = tm * 2 * BM + (int)rank * BM, n0 = tn * BN + (int)rank * BNH;   // sub-tile j adds j * BNI
-                for (int kb = 0; kb < kblocks; ++kb) {
+                for (int kbi = 0; kbi < kblocks; ++kbi) {
+                    int kb = kbi;
+                    if (p.ag_flags && p.ag_dim == 1) {
+                        kb += p.ag_rot;
+                        if (kb >= kblocks) kb -= kblocks;
+                        const int sh = (kb * BK) / p.ag_rows;
+                        if (!(ready_mask >> sh & 1)) {
+                            if (!wait_shard2(p.ag_flags + sh, p.ag_epoch, p.ag_limit_ns, abort_flag)) {
+                                atomicMax(p.status, (int)KB_TIMEOUT_PEER);
+                                ok = false;
+                                break;
+                            }
+                            ready_mask |= 1u << sh;
+                        }
+                    }
                     if (!tc::mbar_wait(&empty[stage], phase ^ 1, abort_flag)) {
                         atomicMax(p.status, (int)KB_TIMEOUT_TMA);
                         ok = false;
@@ -315,6 +373,10 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
             int b, tm, tn;
             tile_coords(tile, tiles_m, tiles_n, b, tm, tn, p.group_m);
             if (p.sym_upper && tn * BN + BN <= tm * 2 * BM) continue;
+            if (p.ag_flags && p.ag_dim == 0) {
+                tm += p.ag_rot;
+                if (tm >= tiles_m) tm -= tiles_m;
+            }
             const int buf = it % NBUF;
             const uint32_t acc_phase = (it / NBUF) & 1;
             ++it;
@@ -521,12 +583,17 @@ int make_tmap2(CUtensorMap* m, const void* base, int fmt, long long cols, long l
 
 }  // namespace
 
-// Same contract as kb_gemm (no split-K); launched as clusters of two CTAs.
-KB_API int kb_gemm_2cta(const void* A, const void* B, void* C, const void* Cin, int M, int N, int K, int batch,
+struct AgArgs {
+    const int* flags;
+    int epoch, rows, dim, own;
+    double limit_s;
+};
+
+static int launch_gemm2(const void* A, const void* B, void* C, const void* Cin, int M, int N, int K, int batch,
                         long long lda, long long ldb, long long ldc, long long ldcin, long long a_bs, long long b_bs,
                         long long c_bs, long long cin_bs, int a_mn, int b_mn, int a_fmt, int b_fmt, int out_type,
                         float alpha, float beta, int* status, int max_ctas, int sym_upper, float diag_add,
-                        cudaStream_t st) {
+                        const AgArgs* ag, cudaStream_t st) {
     if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return 5;
     if (sym_upper && M != N) return 5;
     if ((lda & 7) || (ldb & 7) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15)) return 6;
@@ -556,6 +623,14 @@ KB_API int kb_gemm_2cta(const void* A, const void* B, void* C, const void* Cin, 
     p.status = status;
     p.sym_upper = sym_upper;
     p.diag_add = diag_add;
+    p.ag_flags = nullptr;
+    p.ag_epoch = p.ag_rows = p.ag_dim = p.ag_rot = 0;
+    p.ag_limit_ns = 0;
+    if (ag) {
+        p.ag_flags = ag->flags; p.ag_epoch = ag->epoch; p.ag_rows = ag->rows; p.ag_dim = ag->dim;
+        p.ag_rot = ag->own * (ag->rows / (ag->dim == 0 ? 2 * BM : BK));
+        p.ag_limit_ns = (unsigned long long)(ag->limit_s * 1e9);
+    }
     if (diag_add != 0.f && (alpha == 0.f || !Cin)) return 5;     // implemented on the addend epilogue only
     {
         static int group_m = 0, staged = -1;
@@ -602,4 +677,30 @@ KB_API int kb_gemm_2cta(const void* A, const void* B, void* C, const void* Cin, 
     if (wide) gemm_tcgen05_2cta_kernel<2><<<2 * pairs, 192, Cfg<2>::SMEM, st>>>(tmA, tmB, p);
     else gemm_tcgen05_2cta_kernel<1><<<2 * pairs, 192, Cfg<1>::SMEM, st>>>(tmA, tmB, p);
     return 0;
+}
+
+// Same contract as kb_gemm (no split-K); launched as clusters of two CTAs.
+KB_API int kb_gemm_2cta(const void* A, const void* B, void* C, const void* Cin, int M, int N, int K, int batch,
+                        long long lda, long long ldb, long long ldc, long long ldcin, long long a_bs, long long b_bs,
+                        long long c_bs, long long cin_bs, int a_mn, int b_mn, int a_fmt, int b_fmt, int out_type,
+                        float alpha, float beta, int* status, int max_ctas, int sym_upper, float diag_add,
+                        cudaStream_t st) {
+    return launch_gemm2(A, B, C, Cin, M, N, K, batch, lda, ldb, ldc, ldcin, a_bs, b_bs, c_bs, cin_bs, a_mn, b_mn,
+                        a_fmt, b_fmt, out_type, alpha, beta, status, max_ctas, sym_upper, diag_add, nullptr, st);
+}
+
+// All-gather -> GEMM on the CTA-pair kernel; same contract as kb_gemm_ag (shards of `ag_rows` rows of A
+// for ag_dim 0, of the contraction dimension for ag_dim 1; ag_flags[s] >= ag_epoch marks shard s as landed;
+// the own shard is visited first).  ag_rows must be a multiple of the 256-row tile (ag_dim 0) or of 64.
+KB_API int kb_gemm_2cta_ag(const void* A, const void* B, void* C, const void* Cin, int M, int N, int K,
+                           long long lda, long long ldb, long long ldc, int a_mn, int b_mn, float alpha, float beta,
+                           const int* ag_flags, int ag_epoch, int ag_rows, int ag_dim, int own, double limit_s,
+                           int* status, cudaStream_t st) {
+    if (!ag_flags || ag_rows <= 0 || own < 0 || own > 7) return 5;
+    if (ag_dim == 0 ? (ag_rows % (2 * BM)) != 0 : (ag_rows % BK) != 0) return 5;
+    if ((ag_dim == 0 ? M : K) > 8 * (long long)ag_rows) return 5;
+    if ((ag_dim == 0 ? M : K) % ag_rows || (long long)own * ag_rows >= (ag_dim == 0 ? M : K)) return 5;
+    AgArgs ag{ag_flags, ag_epoch, ag_rows, ag_dim, own, limit_s};
+    return launch_gemm2(A, B, C, Cin, M, N, K, 1, lda, ldb, ldc, ldc, 0, 0, 0, 0, a_mn, b_mn, 1, 1, 1, alpha, beta,
+                        status, 0, 0, 0.f, &ag, st);
 }

@@ -26,6 +26,7 @@ The reference has no counterpart: its tensor parallelism all-reduces replicated 
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Any
 
 import torch
@@ -54,6 +55,8 @@ class FusedTensorParallelComm(TensorParallelComm):
         self._bufs: dict = {}
         self.fused_calls = 0
         self.fallback_calls = 0
+        # KB_TP_AG_PAIR=0 keeps the all-gather products on the 1-CTA kernel (tuning / comparison)
+        self.pair_gemm = os.environ.get("KB_TP_AG_PAIR", "1") != "0"
 
     # ------------------------------------------------------------------ set-up
     def attach(self, engine: Any) -> None:
@@ -159,12 +162,15 @@ class FusedTensorParallelComm(TensorParallelComm):
 
     def _gemm_ag(self, a, b, out, M, N, K, lda, ldb, a_mn, b_mn, par, c, rows, dim, cin=None, beta=0.0) -> None:
         flags = self.sync.data_ptr() + 4 * ((_AG_READY + par) * 8)
-        rc = self.lib.kb_gemm_ag(_VP(a.data_ptr()), _VP(b.data_ptr()), _VP(out.data_ptr()),
+        # the CTA-pair kernel (wider tiles, faster) takes shards that are whole 256-row tiles
+        pair = self.pair_gemm and (rows % (2 * _BM) == 0 if dim == 0 else rows % _BK == 0)
+        fn = self.lib.kb_gemm_2cta_ag if pair else self.lib.kb_gemm_ag
+        rc = fn(_VP(a.data_ptr()), _VP(b.data_ptr()), _VP(out.data_ptr()),
                                  _VP(cin.data_ptr() if cin is not None else None), _I(M), _I(N), _I(K), _LL(lda),
                                  _LL(ldb), _LL(N), _I(a_mn), _I(b_mn), _F(1.0), _F(beta), _VP(flags), _I(c),
                                  _I(rows), _I(dim), _I(self.tp_rank), _D(self.WAIT_LIMIT_S), self._status(),
                                  self._st())
-        self._ck(rc, "kb_gemm_ag")
+        self._ck(rc, "kb_gemm_2cta_ag" if pair else "kb_gemm_ag")
 
     def col_linear(self, ops, x, w):
         if not (isinstance(w, torch.Tensor) and self._usable(x) and w.dtype == torch.bfloat16 and w.is_contiguous()):

@@ -140,7 +140,9 @@ class ServingEngine:
         self._next_id = 0
         self._dec_state = None
         self.use_cuda_graphs = True          # decode steps are replayed from captured graphs on CUDA
-        self.stats = {"prefill_tokens": 0, "decode_tokens": 0, "prefill_s": 0.0, "decode_s": 0.0, "steps": 0}
+        self.prefill_batch_tokens = 8192     # rows of one (padded) prefill pass over several prompts
+        self.stats = {"prefill_tokens": 0, "decode_tokens": 0, "prefill_s": 0.0, "decode_s": 0.0, "steps": 0,
+                      "prefill_passes": 0}
         ar = self.arena
         self.layers = []
         for i in range(cfg.num_layers):
@@ -172,9 +174,10 @@ class ServingEngine:
     # ------------------------------------------------------------------ model pass
     @torch.no_grad()
     def _forward(self, ids: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor, decode: Optional[dict],
-                 last_rows: torch.Tensor) -> torch.Tensor:
-        """Runs all layers on ``ids[N]``; keys/values go to ``slots``.  ``decode`` holds the page table
-        and context lengths for paged attention; ``None`` means a causal prefill of one request.
+                 last_rows: torch.Tensor, prompts: int = 1) -> torch.Tensor:
+        """Runs all layers on ``ids[N]``; keys/values go to ``slots`` (negative = padding, dropped).
+        ``decode`` holds the page table and context lengths for paged attention; ``None`` means a
+        causal prefill of ``prompts`` requests, each padded to ``N / prompts`` rows.
         Returns logits for ``last_rows``."""
         ops, cfg, ar = self.ops, self.cfg, self.arena
         H, KV, hd = self.H, self.KV, self.hd
@@ -195,8 +198,9 @@ class ServingEngine:
             v_rows = qkv[:, (H + KV) * hd:]
             ops.kv_append(k_rows, v_rows, self.cache.k[i], self.cache.v[i], slots)
             if decode is None:
-                o, _ = ops.attention_fwd(qk[:, : H * hd].view(1, N, H, hd), k_rows.view(1, N, KV, hd),
-                                         v_rows.view(1, N, KV, hd), need_grad=False)
+                T = N // prompts
+                o, _ = ops.attention_fwd(qk[:, : H * hd].view(prompts, T, H, hd), k_rows.view(prompts, T, KV, hd),
+                                         v_rows.view(prompts, T, KV, hd), need_grad=False)
                 attn = o.reshape(N, H * hd)
             else:
                 attn = ops.paged_decode_attention(qk[:, : H * hd], self.cache.k[i], self.cache.v[i],
@@ -216,20 +220,58 @@ class ServingEngine:
         return self.tp.row_linear(self.ops, x, w, residual)
 
     # ------------------------------------------------------------------ scheduling
-    def _prefill(self, r: Request) -> None:
-        n = len(r.prompt)
-        r.pages = self.cache.allocate(self.cache.pages_for(min(n + r.params.max_new_tokens, self.max_ctx)))
-        ids = torch.tensor(r.prompt, dtype=torch.long, device=self.device)
-        pos = torch.arange(n, dtype=torch.int32, device=self.device)
-        pages = torch.tensor(r.pages, dtype=torch.long, device=self.device)
-        slots = pages[pos.long() // PAGE] * PAGE + pos.long() % PAGE
-        logits = self._forward(ids, pos, slots, None, torch.tensor([n - 1], device=self.device))
-        r.ctx_len = n
-        tok = int(sample_tokens(logits, [r], self.ops)[0])
+    def _prefill(self, reqs: list[Request]) -> None:
+        """One pass over the prompts of ``reqs``: they are laid out as a ``[len(reqs), T]`` batch padded
+        at the end to the longest prompt (causal attention never looks at the padding, and padded rows
+        carry slot -1 so that they are not written to the cache)."""
+        B, ns = len(reqs), [len(r.prompt) for r in reqs]
+        T = max(ns)
+        ids = torch.zeros(B, T, dtype=torch.long)
+        slots = torch.full((B, T), -1, dtype=torch.long)
+        for b, r in enumerate(reqs):
+            n = ns[b]
+            r.pages = self.cache.allocate(self.cache.pages_for(min(n + r.params.max_new_tokens, self.max_ctx)))
+            ids[b, :n] = torch.tensor(r.prompt, dtype=torch.long)
+            t = torch.arange(n)
+            slots[b, :n] = torch.tensor(r.pages, dtype=torch.long)[t // PAGE] * PAGE + t % PAGE
+        pos = torch.arange(T, dtype=torch.int32).repeat(B)
+        last = torch.tensor([b * T + n - 1 for b, n in enumerate(ns)])
+        dev = self.device
+        logits = self._forward(ids.view(-1).to(dev), pos.to(dev), slots.view(-1).to(dev), None, last.to(dev), prompts=B)
+        toks = sample_tokens(logits, reqs, self.ops).tolist()
         if self.tp is not None:
-            tok = self.tp.sync_tokens([tok], self.device)[0]
-        self._accept(r, tok)
-        self.stats["prefill_tokens"] += n
+            toks = self.tp.sync_tokens(toks, self.device)
+        for r, n, tok in zip(reqs, ns, toks):
+            r.ctx_len = n
+            self._accept(r, int(tok))
+        self.stats["prefill_tokens"] += sum(ns)
+        self.stats["prefill_passes"] += 1
+
+    def _admit(self) -> list[list[Request]]:
+        """Moves the waiting requests that fit (batch slots, pages) to ``running`` and groups them
+        into prefill passes: consecutive requests share a pass while the padded batch stays within
+        ``prefill_batch_tokens`` rows and at most a quarter of it is padding."""
+        groups: list[list[Request]] = []
+        cur: list[Request] = []
+        reserved = 0
+        while self.waiting and len(self.running) < self.max_batch:
+            r = self.waiting[0]
+            need = self.cache.pages_for(min(len(r.prompt) + r.params.max_new_tokens, self.max_ctx))
+            if not self.cache.can_allocate(reserved + need):
+                break
+            reserved += need
+            self.waiting.pop(0)
+            self.running.append(r)
+            if cur:
+                lens = [len(q.prompt) for q in cur] + [len(r.prompt)]
+                padded = max(lens) * len(lens)
+                if padded > self.prefill_batch_tokens or 4 * (padded - sum(lens)) > padded:
+                    groups.append(cur)
+                    cur = []
+            cur.append(r)
+        if cur:
+            groups.append(cur)
+        return groups
 
     def _accept(self, r: Request, tok: int) -> None:
         r.generated.append(tok)
@@ -310,13 +352,8 @@ class ServingEngine:
         finished.  Returns the requests that finished in this step."""
         import time
         t0 = time.perf_counter()
-        while self.waiting and len(self.running) < self.max_batch:
-            r = self.waiting[0]
-            if not self.cache.can_allocate(self.cache.pages_for(min(len(r.prompt) + r.params.max_new_tokens, self.max_ctx))):
-                break
-            self.waiting.pop(0)
-            self._prefill(r)
-            self.running.append(r)
+        for group in self._admit():
+            self._prefill(group)
         t1 = time.perf_counter()
         live = [r for r in self.running if not r.finished]
         done = [r for r in self.running if r.finished]

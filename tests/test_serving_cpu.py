@@ -45,6 +45,22 @@ def test_paged_engine_matches_contiguous_cache_greedy():
         assert eng.stats["prefill_tokens"] == sum(map(len, prompts))
 
 
+def test_prompts_of_similar_length_share_a_padded_prefill_pass():
+    import copy
+    cfg, model = _model()
+    g = torch.Generator().manual_seed(2)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (30, 33, 28, 31, 9)]
+    ref = [_greedy_reference(model, p, 6) for p in prompts]
+    eng = ServingEngine(copy.deepcopy(model), device="cpu", dtype=torch.float32, max_batch=8, max_ctx=128)
+    got = eng.generate(prompts, SamplingParams(max_new_tokens=6, temperature=0.0))
+    assert got == ref
+    assert eng.stats["prefill_passes"] == 1                        # 165 padded rows, 34 of them padding
+    eng.prefill_batch_tokens = 64                                  # only 28 and 31 still fit one pass (62 rows)
+    eng.stats["prefill_passes"] = 0
+    assert eng.generate(prompts, SamplingParams(max_new_tokens=6, temperature=0.0)) == ref
+    assert eng.stats["prefill_passes"] == 4
+
+
 def test_continuous_batching_admits_when_pages_free_up():
     cfg, model = _model()
     eng = ServingEngine(model, device="cpu", dtype=torch.float32, max_batch=8, num_pages=6, max_ctx=64)
