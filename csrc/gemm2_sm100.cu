@@ -51,8 +51,14 @@ struct Gemm2Params {
     // all-gather coupling (see kb_gemm_ag in gemm_sm100.cu): the gathered operand sits in a local staging
     // buffer that peers fill shard by shard; producers wait (bounded) for a shard's flag before its first tile
     const int* ag_flags;       // null: none
-    int ag_epoch, ag_rows, ag_dim, ag_rot;   // rows per shard; 0 = shards along M (A rows), 1 = along K; own-first rotation
+    int ag_epoch, ag_rows, ag_dim, ag_rot;   // rows per shard; 0 = shards along M (A rows), 1 = along K; ag_rot: first k-block (ag_dim 1)
     unsigned long long ag_limit_ns;
+    int m_rot;                 // tile rows are visited starting from this one (own shard first / next rank's rows first)
+    // reduce-scatter coupling (see kb_gemm_rs in gemm_sm100.cu): rows [o*rs_rows, (o+1)*rs_rows) are stored to
+    // rs_out[o] (row stride ldc) and every epilogue warp adds one arrival to rs_cnt[o] per tile
+    void* rs_out[8];
+    int* rs_cnt[8];
+    int rs_rows;               // 0: none
     float diag_add;            // added to the diagonal of the result (after alpha/beta): folds the a*X term of Newton-Schulz into B
 };
 
@@ -249,9 +255,11 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
                 int b, tm, tn;
                 tile_coords(tile, tiles_m, tiles_n, b, tm, tn, p.group_m);
                 if (p.sym_upper && tn * BN + BN <= tm * 2 * BM) continue;
-                if (p.ag_flags && p.ag_dim == 0) {
-                    tm += p.ag_rot;
+                if (p.m_rot) {
+                    tm += p.m_rot;
                     if (tm >= tiles_m) tm -= tiles_m;
+                }
+                if (p.ag_flags && p.ag_dim == 0) {
                     const int s0 = (tm * 2 * BM) / p.ag_rows, s1 = (min(tm * 2 * BM + 2 * BM, p.M) - 1) / p.ag_rows;
                     for (int sh = s0; sh <= s1 && ok; ++sh) {
                         if (ready_mask >> sh & 1) continue;
@@ -373,8 +381,8 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
             int b, tm, tn;
             tile_coords(tile, tiles_m, tiles_n, b, tm, tn, p.group_m);
             if (p.sym_upper && tn * BN + BN <= tm * 2 * BM) continue;
-            if (p.ag_flags && p.ag_dim == 0) {
-                tm += p.ag_rot;
+            if (p.m_rot) {
+                tm += p.m_rot;
                 if (tm >= tiles_m) tm -= tiles_m;
             }
             const int buf = it % NBUF;
@@ -395,6 +403,11 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
                 uint8_t* stg = smem + STAGES * (A_STAGE + B_STAGE) + 256 + (warp - 2) * EPI_WARP_BYTES;
                 const int row0 = tm * 2 * BM + (int)rank * BM + quarter * 32;
                 uint16_t* obase = reinterpret_cast<uint16_t*>(p.C) + (long long)b * p.c_batch_stride + (long long)row0 * p.ldc;
+                if (p.rs_rows > 0) {
+                    // reduce-scatter: these 32 rows go to their owner's slab, as 128-byte row segments over NVLink
+                    const int owner = row0 / p.rs_rows;
+                    obase = reinterpret_cast<uint16_t*>(p.rs_out[owner]) + (long long)(row0 - owner * p.rs_rows) * p.ldc;
+                }
 #pragma unroll 1
                 for (int c0 = 0; c0 < BN; c0 += 64) {
                     uint32_t acc[64];
@@ -539,6 +552,15 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
             tc::tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(mapa(smem_u32(&acc_empty[buf]), 0));
+            if (p.rs_rows > 0) {
+                // this warp's 32 rows of the tile are with their owner: publish one arrival
+                __threadfence_system();
+                __syncwarp();
+                if (lane == 0) {
+                    int* cnt = p.rs_cnt[(tm * 2 * BM + (int)rank * BM) / p.rs_rows];
+                    asm volatile("red.release.sys.global.add.s32 [%0], 1;" ::"l"(cnt) : "memory");
+                }
+            }
         }
     }
     tc::tc_fence_before();
@@ -588,12 +610,50 @@ struct AgArgs {
     int epoch, rows, dim, own;
     double limit_s;
 };
+struct RsArgs {
+    void* const* out;
+    int* const* cnt;
+    int world, rank, rows;
+};
+
+// Wide (256 x 512) tiles for large non-symmetric products without addend whose tile count still fills the
+// machine; KB_GEMM2_WIDE=0/1 forces the choice (tuning).  Measured over the 3B projection shapes: 0.94x of
+// cuBLAS with wide tiles against 0.87x without (products with an addend keep the narrow tile: reading the
+// addend in an epilogue that is not hidden behind the next tile cost more than the wide tile gains).
+static bool choose_wide(int M, int N, int batch, bool sym_upper, bool addend, int sms) {
+    static int wide_env = -2;
+    if (wide_env == -2) {
+        const char* w = getenv("KB_GEMM2_WIDE");
+        wide_env = w ? atoi(w) : -1;
+    }
+    const long long m_tiles = (M + 2 * BM - 1) / (2 * BM);
+    const long long wide_tiles = m_tiles * ((N + 2 * BNI - 1) / (2 * BNI)) * batch;
+    bool wide = !sym_upper && !addend && N >= 2 * BNI && wide_tiles >= 2 * (sms / 2);
+    if (wide_env >= 0) wide = wide && wide_env != 0;
+    return wide;
+}
+// Reduce-scatter products keep the narrow tile unless KB_GEMM2_RS_WIDE=1: its two accumulator buffers hide the
+// slow peer stores of one tile behind the math of the next.
+static bool rs_wide() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("KB_GEMM2_RS_WIDE");
+        v = e ? (atoi(e) != 0) : 0;
+    }
+    return v != 0;
+}
+static int device_sms() {
+    int sms = 0, dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    return sms;
+}
 
 static int launch_gemm2(const void* A, const void* B, void* C, const void* Cin, int M, int N, int K, int batch,
                         long long lda, long long ldb, long long ldc, long long ldcin, long long a_bs, long long b_bs,
                         long long c_bs, long long cin_bs, int a_mn, int b_mn, int a_fmt, int b_fmt, int out_type,
                         float alpha, float beta, int* status, int max_ctas, int sym_upper, float diag_add,
-                        const AgArgs* ag, cudaStream_t st) {
+                        const AgArgs* ag, const RsArgs* rs, cudaStream_t st) {
     if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return 5;
     if (sym_upper && M != N) return 5;
     if ((lda & 7) || (ldb & 7) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15)) return 6;
@@ -626,10 +686,19 @@ static int launch_gemm2(const void* A, const void* B, void* C, const void* Cin, 
     p.ag_flags = nullptr;
     p.ag_epoch = p.ag_rows = p.ag_dim = p.ag_rot = 0;
     p.ag_limit_ns = 0;
+    p.m_rot = 0;
+    p.rs_rows = 0;
+    for (int i = 0; i < 8; ++i) { p.rs_out[i] = nullptr; p.rs_cnt[i] = nullptr; }
     if (ag) {
         p.ag_flags = ag->flags; p.ag_epoch = ag->epoch; p.ag_rows = ag->rows; p.ag_dim = ag->dim;
-        p.ag_rot = ag->own * (ag->rows / (ag->dim == 0 ? 2 * BM : BK));
+        if (ag->dim == 0) p.m_rot = ag->own * (ag->rows / (2 * BM));
+        else p.ag_rot = ag->own * (ag->rows / BK);
         p.ag_limit_ns = (unsigned long long)(ag->limit_s * 1e9);
+    }
+    if (rs) {
+        for (int i = 0; i < rs->world; ++i) { p.rs_out[i] = rs->out[i]; p.rs_cnt[i] = rs->cnt[i]; }
+        p.rs_rows = rs->rows;
+        p.m_rot = ((rs->rank + 1) % rs->world) * (rs->rows / (2 * BM));
     }
     if (diag_add != 0.f && (alpha == 0.f || !Cin)) return 5;     // implemented on the addend epilogue only
     {
@@ -643,6 +712,7 @@ static int launch_gemm2(const void* A, const void* B, void* C, const void* Cin, 
         }
         p.group_m = group_m;
         p.epi_staged = staged && !Cin && out_type != 2 && !(N & 7) && !(ldc & 7) && !(c_bs & 7);
+        if (rs) p.epi_staged = 1;      // the reduce-scatter stores exist on this epilogue only (its conditions were checked by the caller)
         // off unless KB_GEMM2_CIN_STAGED=1: measured slower (1-GPU step 861 -> 904 ms) - an addend read costs a
         // memory round trip per chunk, which only the narrow tile's second accumulator buffer hides
         static int cin_staged = -1;
@@ -653,24 +723,11 @@ static int launch_gemm2(const void* A, const void* B, void* C, const void* Cin, 
         p.epi_cin_staged = cin_staged && staged && Cin && out_type != 2 && !sym_upper && diag_add == 0.f && !(N & 3) && !(ldc & 3) &&
                            !(ldcin & 3) && !(c_bs & 3) && !(cin_bs & 3) && !((uintptr_t)C & 7) && !((uintptr_t)Cin & 7);
     }
-    int sms = 0, dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    int sms = device_sms();
     if (max_ctas > 0 && max_ctas < sms) sms = max_ctas;
-    // Wide tiles for large non-symmetric products whose tile count still fills the machine;
-    // KB_GEMM2_WIDE=0/1 forces the choice (tuning).
-    static int wide_env = -2;
-    if (wide_env == -2) {
-        const char* w = getenv("KB_GEMM2_WIDE");
-        wide_env = w ? atoi(w) : -1;
-    }
     const long long m_tiles = (M + 2 * BM - 1) / (2 * BM);
     const long long wide_tiles = m_tiles * ((N + 2 * BNI - 1) / (2 * BNI)) * batch;
-    // measured over the 3B projection shapes: 0.94x of cuBLAS with wide tiles against 0.87x without
-    // (products with an addend keep the narrow tile: reading the addend in an epilogue that is not hidden
-    // behind the next tile cost more than the wide tile gains)
-    bool wide = !sym_upper && !Cin && N >= 2 * BNI && wide_tiles >= 2 * (sms / 2);
-    if (wide_env >= 0) wide = wide && wide_env != 0;
+    const bool wide = choose_wide(M, N, batch, sym_upper != 0, Cin != nullptr, sms) && (!rs || rs_wide());
     const long long tiles = wide ? wide_tiles : m_tiles * ((N + BNI - 1) / BNI) * batch;
     int pairs = sms / 2;
     if (tiles < pairs) pairs = (int)tiles;
@@ -686,7 +743,7 @@ KB_API int kb_gemm_2cta(const void* A, const void* B, void* C, const void* Cin, 
                         float alpha, float beta, int* status, int max_ctas, int sym_upper, float diag_add,
                         cudaStream_t st) {
     return launch_gemm2(A, B, C, Cin, M, N, K, batch, lda, ldb, ldc, ldcin, a_bs, b_bs, c_bs, cin_bs, a_mn, b_mn,
-                        a_fmt, b_fmt, out_type, alpha, beta, status, max_ctas, sym_upper, diag_add, nullptr, st);
+                        a_fmt, b_fmt, out_type, alpha, beta, status, max_ctas, sym_upper, diag_add, nullptr, nullptr, st);
 }
 
 // All-gather -> GEMM on the CTA-pair kernel; same contract as kb_gemm_ag (shards of `ag_rows` rows of A
@@ -702,5 +759,25 @@ KB_API int kb_gemm_2cta_ag(const void* A, const void* B, void* C, const void* Ci
     if ((ag_dim == 0 ? M : K) % ag_rows || (long long)own * ag_rows >= (ag_dim == 0 ? M : K)) return 5;
     AgArgs ag{ag_flags, ag_epoch, ag_rows, ag_dim, own, limit_s};
     return launch_gemm2(A, B, C, Cin, M, N, K, 1, lda, ldb, ldc, ldc, 0, 0, 0, 0, a_mn, b_mn, 1, 1, 1, alpha, beta,
-                        status, 0, 0, 0.f, &ag, st);
+                        status, 0, 0, 0.f, &ag, nullptr, st);
+}
+
+// GEMM -> reduce-scatter (producer half) on the CTA-pair kernel; same contract as kb_gemm_rs, rs_rows a
+// multiple of the 256-row tile.  kb_gemm_2cta_rs_arrivals gives the arrivals each owner's counter receives.
+KB_API int kb_gemm_2cta_rs(const void* A, const void* B, int M, int N, int K, long long lda, long long ldb,
+                           long long ldc, int a_mn, int b_mn, float alpha, void* const* rs_out, int* const* rs_cnt,
+                           int world, int rank, int rs_rows, int* status, cudaStream_t st) {
+    if (world < 1 || world > 8 || rank < 0 || rank >= world || rs_rows <= 0 || (rs_rows % (2 * BM)) != 0 ||
+        M != world * rs_rows)
+        return 5;
+    if ((N & 7) || (ldc & 7)) return 6;
+    for (int i = 0; i < world; ++i)
+        if (!rs_out[i] || !rs_cnt[i] || ((uintptr_t)rs_out[i] & 15)) return 6;
+    RsArgs rs{rs_out, rs_cnt, world, rank, rs_rows};
+    return launch_gemm2(A, B, rs_out[rank], nullptr, M, N, K, 1, lda, ldb, ldc, 0, 0, 0, 0, 0, a_mn, b_mn, 1, 1, 1,
+                        alpha, 0.f, status, 0, 0, 0.f, nullptr, &rs, st);
+}
+KB_API int kb_gemm_2cta_rs_arrivals(int M, int N, int rs_rows) {
+    const int bn = choose_wide(M, N, 1, false, false, device_sms()) && rs_wide() ? 2 * BNI : BNI;
+    return (rs_rows / BM) * ((N + bn - 1) / bn) * 4;
 }

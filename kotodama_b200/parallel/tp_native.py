@@ -55,7 +55,7 @@ class FusedTensorParallelComm(TensorParallelComm):
         self._bufs: dict = {}
         self.fused_calls = 0
         self.fallback_calls = 0
-        # KB_TP_AG_PAIR=0 keeps the all-gather products on the 1-CTA kernel (tuning / comparison)
+        # KB_TP_AG_PAIR=0 keeps the coupled products on the 1-CTA kernel (tuning / comparison)
         self.pair_gemm = os.environ.get("KB_TP_AG_PAIR", "1") != "0"
 
     # ------------------------------------------------------------------ set-up
@@ -216,11 +216,14 @@ class FusedTensorParallelComm(TensorParallelComm):
             self._ck(rc, "kb_flag_wait")
         outs = [ptrs[o] + 2 * (base_off + r * slab) for o in range(W)]
         cnts = [self._sync_addr(o, _RS_CNT + par, r) for o in range(W)]
-        rc = self.lib.kb_gemm_rs(_VP(a.data_ptr()), _VP(b.data_ptr()), _I(M), _I(N), _I(K), _LL(lda), _LL(ldb), _LL(N),
-                                 _I(a_mn), _I(b_mn), _F(1.0), self._arr(outs), self._arr(cnts), _I(W), _I(r),
-                                 _I(rows), self._status(), self._st())
-        self._ck(rc, "kb_gemm_rs")
-        expected = int(self.lib.kb_gemm_rs_arrivals(_I(N), _I(rows)))
+        pair = self.pair_gemm and rows % (2 * _BM) == 0
+        fn = self.lib.kb_gemm_2cta_rs if pair else self.lib.kb_gemm_rs
+        rc = fn(_VP(a.data_ptr()), _VP(b.data_ptr()), _I(M), _I(N), _I(K), _LL(lda), _LL(ldb), _LL(N),
+                _I(a_mn), _I(b_mn), _F(1.0), self._arr(outs), self._arr(cnts), _I(W), _I(r),
+                _I(rows), self._status(), self._st())
+        self._ck(rc, "kb_gemm_2cta_rs" if pair else "kb_gemm_rs")
+        expected = int(self.lib.kb_gemm_2cta_rs_arrivals(_I(M), _I(N), _I(rows)) if pair
+                       else self.lib.kb_gemm_rs_arrivals(_I(N), _I(rows)))
         out = torch.empty(rows, N, device=a.device, dtype=torch.bfloat16)
         done = [self._sync_addr(q, _RS_DONE, r) for q in range(W)]
         rc = self.lib.kb_rs_reduce(_VP(buf.data_ptr() + 2 * base_off), _LL(slab),
