@@ -249,10 +249,9 @@ class ServingEngine:
 
     def _admit(self) -> list[list[Request]]:
         """Moves the waiting requests that fit (batch slots, pages) to ``running`` and groups them
-        into prefill passes: consecutive requests share a pass while the padded batch stays within
-        ``prefill_batch_tokens`` rows and at most a quarter of it is padding."""
-        groups: list[list[Request]] = []
-        cur: list[Request] = []
+        into prefill passes: sorted by prompt length, neighbours share a pass while the padded batch
+        stays within ``prefill_batch_tokens`` rows and at most a quarter of it is padding."""
+        admitted: list[Request] = []
         reserved = 0
         while self.waiting and len(self.running) < self.max_batch:
             r = self.waiting[0]
@@ -262,10 +261,14 @@ class ServingEngine:
             reserved += need
             self.waiting.pop(0)
             self.running.append(r)
+            admitted.append(r)
+        groups: list[list[Request]] = []
+        cur: list[Request] = []
+        for r in sorted(admitted, key=lambda q: len(q.prompt)):
             if cur:
-                lens = [len(q.prompt) for q in cur] + [len(r.prompt)]
-                padded = max(lens) * len(lens)
-                if padded > self.prefill_batch_tokens or 4 * (padded - sum(lens)) > padded:
+                total = sum(len(q.prompt) for q in cur) + len(r.prompt)
+                padded = len(r.prompt) * (len(cur) + 1)             # sorted: the newcomer is the longest
+                if padded > self.prefill_batch_tokens or 4 * (padded - total) > padded:
                     groups.append(cur)
                     cur = []
             cur.append(r)

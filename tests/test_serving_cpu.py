@@ -54,8 +54,8 @@ def test_prompts_of_similar_length_share_a_padded_prefill_pass():
     eng = ServingEngine(copy.deepcopy(model), device="cpu", dtype=torch.float32, max_batch=8, max_ctx=128)
     got = eng.generate(prompts, SamplingParams(max_new_tokens=6, temperature=0.0))
     assert got == ref
-    assert eng.stats["prefill_passes"] == 1                        # 165 padded rows, 34 of them padding
-    eng.prefill_batch_tokens = 64                                  # only 28 and 31 still fit one pass (62 rows)
+    assert eng.stats["prefill_passes"] == 2                        # the short one alone, four padded to 33 rows
+    eng.prefill_batch_tokens = 64                                  # only 28 and 30 still fit one pass (60 rows)
     eng.stats["prefill_passes"] = 0
     assert eng.generate(prompts, SamplingParams(max_new_tokens=6, temperature=0.0)) == ref
     assert eng.stats["prefill_passes"] == 4
