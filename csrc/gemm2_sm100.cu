@@ -242,6 +242,9 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     cluster_sync();                                  // peer barriers are initialised before anyone signals them
     tc::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // every pipeline wait sits behind the producer's wait for a peer's shard when the kernel is coupled to an
+    // all-gather: give them that wait's limit on top of their own
+    const uint64_t wait_ns = p.ag_flags ? p.ag_limit_ns + 2000000000ull : 2000000000ull;
 
     if (warp == 0) {
         if (lane == 0) {
@@ -287,7 +290,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
                             ready_mask |= 1u << sh;
                         }
                     }
-                    if (!tc::mbar_wait(&empty[stage], phase ^ 1, abort_flag)) {
+                    if (!tc::mbar_wait(&empty[stage], phase ^ 1, abort_flag, wait_ns)) {
                         atomicMax(p.status, (int)KB_TIMEOUT_TMA);
                         ok = false;
                         break;
@@ -334,7 +337,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
                 const int buf = it % NBUF;
                 const uint32_t acc_phase = (it / NBUF) & 1;
                 ++it;
-                if (!tc::mbar_wait(&acc_empty[buf], acc_phase ^ 1, abort_flag)) {
+                if (!tc::mbar_wait(&acc_empty[buf], acc_phase ^ 1, abort_flag, wait_ns)) {
                     atomicMax(p.status, (int)KB_TIMEOUT_MMA);
                     ok = false;
                     break;
@@ -342,7 +345,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
                 tc::tc_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * BN;      // NBUF * BN = 512 columns in both shapes
                 for (int kb = 0; kb < kblocks; ++kb) {
-                    if (!tc::mbar_wait(&full[stage], phase, abort_flag)) {
+                    if (!tc::mbar_wait(&full[stage], phase, abort_flag, wait_ns)) {
                         atomicMax(p.status, (int)KB_TIMEOUT_MMA);
                         ok = false;
                         break;
@@ -388,7 +391,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
             const int buf = it % NBUF;
             const uint32_t acc_phase = (it / NBUF) & 1;
             ++it;
-            if (!tc::mbar_wait(&acc_full[buf], acc_phase, abort_flag)) {
+            if (!tc::mbar_wait(&acc_full[buf], acc_phase, abort_flag, wait_ns)) {
                 if (lane == 0) atomicMax(p.status, (int)KB_TIMEOUT_EPI);
                 ok = false;
                 break;

@@ -211,6 +211,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     __syncthreads();
     tc::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // every pipeline wait sits behind the producer's wait for a peer's shard when the kernel is coupled to an
+    // all-gather: give them that wait's limit on top of their own
+    const uint64_t wait_ns = (COMM && cm.ag_flags) ? cm.limit_ns + 2000000000ull : 2000000000ull;
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
@@ -257,7 +260,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                             ready_mask |= 1u << sh;
                         }
                     }
-                    if (!tc::mbar_wait(&empty[stage], phase ^ 1, abort_flag)) {
+                    if (!tc::mbar_wait(&empty[stage], phase ^ 1, abort_flag, wait_ns)) {
                         atomicMax(p.status, (int)KB_TIMEOUT_TMA);
                         ok = false;
                         break;
@@ -306,7 +309,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
                 const int buf = it & 1;
                 const uint32_t acc_phase = (it >> 1) & 1;
-                if (!tc::mbar_wait(&acc_empty[buf], acc_phase ^ 1, abort_flag)) {
+                if (!tc::mbar_wait(&acc_empty[buf], acc_phase ^ 1, abort_flag, wait_ns)) {
                     atomicMax(p.status, (int)KB_TIMEOUT_MMA);
                     ok = false;
                     break;
@@ -315,7 +318,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 const uint32_t d_tmem = tmem_base + buf * BN;
                 const int kb0 = (tile % p.split_k) * kb_per, kb1 = min(kblocks_total, kb0 + kb_per);
                 for (int kb = kb0; kb < kb1; ++kb) {
-                    if (!tc::mbar_wait(&full[stage], phase, abort_flag)) {
+                    if (!tc::mbar_wait(&full[stage], phase, abort_flag, wait_ns)) {
                         atomicMax(p.status, (int)KB_TIMEOUT_MMA);
                         ok = false;
                         break;
@@ -352,7 +355,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             const bool has_k = (tile % p.split_k) * kb_per < kblocks_total;
             const int buf = it & 1;
             const uint32_t acc_phase = (it >> 1) & 1;
-            if (!tc::mbar_wait(&acc_full[buf], acc_phase, abort_flag)) {
+            if (!tc::mbar_wait(&acc_full[buf], acc_phase, abort_flag, wait_ns)) {
                 if (lane == 0) atomicMax(p.status, (int)KB_TIMEOUT_EPI);
                 ok = false;
                 break;
