@@ -4,7 +4,8 @@ decoding on the device.
 The reference server (``serve.py:322-391``) handles one request at a time with a contiguous KV
 cache grown by ``torch.cat``.  Here any number of requests run concurrently: a request is
 prefilled in one pass over its prompt (writing post-norm, post-RoPE keys and values straight
-into its pages), then joins the decode batch, where every step advances all running requests
+into its pages; requests admitted in the same step whose prompts have similar lengths share
+that pass as a padded batch), then joins the decode batch, where every step advances all running requests
 by one token with the split-KV paged attention kernel.  Pages return to the free list when a
 request finishes.
 
