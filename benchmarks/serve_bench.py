@@ -34,6 +34,8 @@ def main() -> None:
     ap.add_argument("--min-prompt", type=int, default=128)
     ap.add_argument("--max-prompt", type=int, default=2048)
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--prefill-batch-tokens", type=int, default=8192,
+                    help="rows of one padded prefill pass shared by several prompts (0: one prompt per pass)")
     ap.add_argument("--device", default="cuda")
     ap.add_argument("--passes", type=int, default=2, help="2: report the second (warm) pass, the first one separately")
     ap.add_argument("--profile-decode-step", type=int, default=-1,
@@ -57,7 +59,8 @@ def main() -> None:
     with torch.device("meta"):
         model = KotodamaModel(cfg)
     eng = ServingEngine(model, device=a.device, dtype=torch.bfloat16 if cuda else torch.float32,
-                        max_batch=a.requests, max_ctx=a.max_prompt + a.new_tokens + 16, tp=tp)
+                        max_batch=a.requests, max_ctx=a.max_prompt + a.new_tokens + 16, tp=tp,
+                        prefill_batch_tokens=a.prefill_batch_tokens)
     eng.arena.init_weights(cfg.num_layers, a.seed)
     g = torch.Generator().manual_seed(a.seed)
     lens = torch.randint(a.min_prompt, a.max_prompt + 1, (a.requests,), generator=g).tolist()
@@ -138,7 +141,8 @@ def main() -> None:
            "p50_token_latency_ms": round(statistics.median(step_ms), 3) if step_ms else None,
            "p95_token_latency_ms": round(sorted(step_ms)[int(0.95 * (len(step_ms) - 1))], 3) if step_ms else None,
            "kernel_launches": getattr(eng.ops, "launches", None),
-           "attention_library_calls": getattr(eng.ops, "attention_library_calls", 0), "tp": world}
+           "attention_library_calls": getattr(eng.ops, "attention_library_calls", 0), "tp": world,
+           "prefill_passes": eng.stats["prefill_passes"], "prefill_batch_tokens": a.prefill_batch_tokens}
     if tp is not None:
         out.update(native_allreduce_calls=tp.native_calls, library_allreduce_calls=tp.library_calls)
     if hasattr(eng.ops, "check_status"):

@@ -117,7 +117,8 @@ def sample_tokens(logits: torch.Tensor, reqs: list[Request], ops: Any) -> torch.
 class ServingEngine:
     def __init__(self, model: KotodamaModel, *, device: torch.device | str = "cpu",
                  dtype: torch.dtype = torch.float32, max_batch: int = 64, num_pages: Optional[int] = None,
-                 max_ctx: Optional[int] = None, ops: Any = None, tp: Any = None) -> None:
+                 max_ctx: Optional[int] = None, ops: Any = None, tp: Any = None,
+                 prefill_batch_tokens: int = 8192) -> None:
         self.device = torch.device(device)
         self.dtype = dtype
         self.model = model.eval()
@@ -141,7 +142,7 @@ class ServingEngine:
         self._next_id = 0
         self._dec_state = None
         self.use_cuda_graphs = True          # decode steps are replayed from captured graphs on CUDA
-        self.prefill_batch_tokens = 8192     # rows of one (padded) prefill pass over several prompts
+        self.prefill_batch_tokens = prefill_batch_tokens     # rows of one (padded) prefill pass over several prompts; 0: one prompt per pass
         self.stats = {"prefill_tokens": 0, "decode_tokens": 0, "prefill_s": 0.0, "decode_s": 0.0, "steps": 0,
                       "prefill_passes": 0}
         ar = self.arena

@@ -67,6 +67,8 @@ def main() -> None:
     ap.add_argument("--attn_res_boundaries", default=DDV1_BOUNDARIES)
     ap.add_argument("--attn_res_n_blocks", type=int, default=7)
     ap.add_argument("--max_batch", type=int, default=64)
+    ap.add_argument("--prefill_batch_tokens", type=int, default=8192,
+                    help="rows of one padded prefill pass shared by several prompts (0: one prompt per pass)")
     ap.add_argument("--max_ctx", type=int, default=None)
     ap.add_argument("--tokenizer", default=TOKENIZER_NAME)
     ap.add_argument("--random_init", action="store_true", help="serve random weights (smoke tests)")
@@ -89,7 +91,8 @@ def main() -> None:
     model = load_model(args.checkpoint, args.model_size, args.attn_res_boundaries, args.attn_res_n_blocks,
                        not args.no_attn_res, args.random_init)
     engine = ServingEngine(model, device=device, dtype=torch.bfloat16 if device.startswith("cuda") else torch.float32,
-                           max_batch=args.max_batch, max_ctx=args.max_ctx, tp=tp)
+                           max_batch=args.max_batch, max_ctx=args.max_ctx, tp=tp,
+                           prefill_batch_tokens=args.prefill_batch_tokens)
     if tp is not None and rank > 0:
         run_follower(engine, tp)
         return
