@@ -232,7 +232,6 @@ class ServingEngine:
         slots = torch.full((B, T), -1, dtype=torch.long)
         for b, r in enumerate(reqs):
             n = ns[b]
-            r.pages = self.cache.allocate(self.cache.pages_for(min(n + r.params.max_new_tokens, self.max_ctx)))
             ids[b, :n] = torch.tensor(r.prompt, dtype=torch.long)
             t = torch.arange(n)
             slots[b, :n] = torch.tensor(r.pages, dtype=torch.long)[t // PAGE] * PAGE + t % PAGE
@@ -254,13 +253,14 @@ class ServingEngine:
         into prefill passes: sorted by prompt length, neighbours share a pass while the padded batch
         stays within ``prefill_batch_tokens`` rows and at most a quarter of it is padding."""
         admitted: list[Request] = []
-        reserved = 0
         while self.waiting and len(self.running) < self.max_batch:
             r = self.waiting[0]
             need = self.cache.pages_for(min(len(r.prompt) + r.params.max_new_tokens, self.max_ctx))
-            if not self.cache.can_allocate(reserved + need):
+            if not self.cache.can_allocate(need):
                 break
-            reserved += need
+            # pages are handed out in admission order, which is also the order of the decode batch:
+            # neighbouring requests of a decode step then read neighbouring pages
+            r.pages = self.cache.allocate(need)
             self.waiting.pop(0)
             self.running.append(r)
             admitted.append(r)
