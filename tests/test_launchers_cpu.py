@@ -1,0 +1,72 @@
+"""Host-side argument checks of the native launchers.
+
+Every launcher validates shapes, alignment and the collective-coupling parameters before it
+touches the device and returns a small error code instead of launching; a wrong shard size or a
+misaligned slab must never reach a kernel that stores into a peer's memory.  These checks run
+without a GPU: the library is loaded and the launchers are called with arguments that must be
+refused (no pointer is dereferenced on the refusing paths).
+"""
+import ctypes
+
+import pytest
+
+VP, I, LL, F, D = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float, ctypes.c_double
+PTR = 4096          # an aligned, never dereferenced address
+
+
+@pytest.fixture(scope="module")
+def lib():
+    try:
+        from kotodama_b200.ops import _build
+        return _build.load()
+    except Exception as e:                                   # no compiler and no built library
+        pytest.skip(f"native library unavailable: {e}")
+
+
+def _ag(lib, M, K, rows, dim, own, flags=True):
+    fl = (ctypes.c_int * 8)() if flags else None
+    return lib.kb_gemm_2cta_ag(VP(PTR), VP(PTR), VP(PTR), VP(None), I(M), I(256), I(K), LL(K), LL(K), LL(256),
+                               I(0), I(0), F(1.0), F(0.0), fl, I(1), I(rows), I(dim), I(own), D(1.0), VP(None),
+                               VP(None))
+
+
+def test_all_gather_gemm_refuses_bad_shards(lib):
+    assert _ag(lib, 1024, 256, 512, 0, 0, flags=False) == 5          # no flag array
+    assert _ag(lib, 1024, 256, 128, 0, 0) == 5                       # shard is not whole 256-row tiles
+    assert _ag(lib, 1024, 256, 96, 1, 0) == 5                        # K shard is not whole 64-wide k-blocks
+    assert _ag(lib, 1024, 256, 512, 0, 8) == 5                       # rank out of range
+    assert _ag(lib, 1024, 256, 512, 0, 2) == 5                       # rank's shard lies beyond M
+    assert _ag(lib, 1280, 256, 512, 0, 0) == 5                       # M is not a whole number of shards
+    assert _ag(lib, 8192, 256, 256, 0, 0) == 5                       # more than eight shards
+
+
+def _rs(lib, M, N, rows, world, rank, slabs=None, ldc=None):
+    arr = lambda v: (VP * 8)(*(list(v) + [None] * (8 - len(v))))
+    slabs = slabs if slabs is not None else [PTR] * world
+    return lib.kb_gemm_2cta_rs(VP(PTR), VP(PTR), I(M), I(N), I(64), LL(64), LL(64), LL(ldc or N), I(0), I(0),
+                               F(1.0), arr(slabs), arr([PTR] * world), I(world), I(rank), I(rows), VP(None),
+                               VP(None))
+
+
+def test_gemm_reduce_scatter_refuses_bad_slabs(lib):
+    assert _rs(lib, 1024, 256, 128, 8, 0) == 5                       # slab rows are not whole 256-row tiles
+    assert _rs(lib, 1024, 256, 256, 2, 0) == 5                       # M != world * rows
+    assert _rs(lib, 512, 256, 256, 2, 2) == 5                        # rank out of range
+    assert _rs(lib, 512, 252, 256, 2, 0) == 6                        # row segments would not be 16-byte pieces
+    assert _rs(lib, 512, 256, 256, 2, 0, ldc=260) == 6
+    assert _rs(lib, 512, 256, 256, 2, 0, slabs=[PTR, None]) == 6     # a peer slab is missing
+    assert _rs(lib, 512, 256, 256, 2, 0, slabs=[PTR, PTR + 8]) == 6  # or misaligned
+
+
+def test_arrival_counts(lib):
+    # narrow (256-column) tiles: every 128-row block of a slab, tile column and epilogue warp arrives once
+    assert lib.kb_gemm_2cta_rs_arrivals(I(4096), I(3072), I(2048)) == (2048 // 128) * (3072 // 256) * 4
+    assert lib.kb_gemm_2cta_rs_arrivals(I(512), I(300), I(256)) == 2 * 2 * 4
+    # 1-CTA kernel: 128 x 256 tiles
+    assert lib.kb_gemm_rs_arrivals(I(3072), I(2048)) == (2048 // 128) * (3072 // 256) * 4
+
+
+def test_quantisers_refuse_ragged_shapes(lib):
+    assert lib.kb_quant_rows(VP(PTR), LL(200), VP(PTR), LL(200), VP(PTR), I(4), I(200), VP(None)) == 5      # K % 128
+    assert lib.kb_quant_blocks(VP(PTR), LL(256), VP(PTR), VP(PTR), VP(None), VP(None), I(100), I(256), VP(None)) == 5
+    assert lib.kb_quant_cols_t(VP(PTR), LL(256), VP(PTR), VP(PTR), I(100), I(256), VP(None)) == 5           # M % 128
