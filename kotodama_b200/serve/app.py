@@ -187,6 +187,13 @@ def create_app(engine: ServingEngine, tokenizer: Any = None, model_name: str = "
                 "dtype": str(engine.dtype).replace("torch.", ""), "kv_cache": "paged-16",
                 "max_batch": engine.max_batch, "tokenizer": getattr(tok, "name", type(tok).__name__)}
 
+    @app.get("/stats")
+    def stats() -> dict[str, Any]:
+        """Scheduler counters since start-up (not a reference route): tokens and seconds spent in prefill
+        and decode, prefill passes (several prompts may share one), steps, free KV pages."""
+        return {**engine.stats, "free_pages": len(engine.cache.free), "num_pages": engine.cache.num_pages,
+                "running": len(engine.running), "waiting": len(engine.waiting)}
+
     @app.post("/generate")
     async def generate(req: GenerateRequest):
         ids = encode(req.prompt)

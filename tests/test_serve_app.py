@@ -40,6 +40,8 @@ def test_generate_json_and_limits(client):
     assert set(body) == {"text", "prompt_tokens", "completion_tokens", "tokens_per_second"}
     again = client.post("/generate", json={"prompt": "hello", "max_new_tokens": 5, "temperature": 0}).json()
     assert again["text"] == body["text"]                      # greedy is deterministic
+    st = client.get("/stats").json()
+    assert st["prefill_tokens"] >= 10 and st["prefill_passes"] >= 2 and st["free_pages"] == st["num_pages"]
     assert client.post("/generate", json={"prompt": "x" * 80}).status_code == 400
     assert client.post("/generate", json={"prompt": "x", "temperature": 3.0}).status_code == 422
 
