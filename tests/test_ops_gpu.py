@@ -404,3 +404,29 @@ def test_fp8_weight_paths_in_gemm_ops(ops):
     ref = dy.float().t() @ x.float()
     assert float((gw.float() - ref).norm() / ref.norm()) < 0.06
     ops.check_status()
+
+
+def test_bounded_wait_reports_status_and_context_survives(ops):
+    """Failure detection on the device: a wait on a flag that nothing sets gives up after its limit,
+    records the peer-timeout code in the status word and returns - the host reads the status, the
+    context stays usable and later kernels run.  (This is how a rank that never arrives shows up.)"""
+    import ctypes
+    import time
+    from kotodama_b200.ops.cuda import KernelError
+    VP, I, D = ctypes.c_void_p, ctypes.c_int, ctypes.c_double
+    flags = torch.zeros(8 * 8, dtype=torch.int32, device="cuda")          # int flags[slots][8], all unset
+    st = ops.status(flags.device)
+    stream = VP(torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    assert ops.lib.kb_flag_wait(VP(flags.data_ptr()), I(2), I(0), I(1), D(0.2), VP(st.data_ptr()), stream) == 0
+    with pytest.raises(KernelError, match="status 4"):
+        ops.check_status()
+    dt = time.perf_counter() - t0
+    assert 0.15 < dt < 5.0, dt                                            # it waited its limit, not forever
+    a = bf(256, 256, seed=4)
+    assert rel_err(ops.gemm_nt(a, a), a.float() @ a.float().t()) < 1e-2    # the context is intact
+    ops.check_status()                                                    # and the status word was cleared
+    flags[:2] = 1                                                          # both "ranks" have signalled epoch 1
+    assert ops.lib.kb_flag_wait(VP(flags.data_ptr()), I(2), I(0), I(1), D(0.2), VP(st.data_ptr()), stream) == 0
+    ops.check_status()
