@@ -133,7 +133,24 @@ def train(args: argparse.Namespace) -> dict[str, Any]:
     if tp_size > 1:
         from .parallel.tp import TensorParallelComm, create_process_groups
         tp_group, dp_group = create_process_groups(world, tp_size)
-        comm = TensorParallelComm(tp_group, dp_group, sequence_parallel=args.sequence_parallel)
+        comm = None
+        # fused all-gather -> GEMM / GEMM -> reduce-scatter kernels over NVLink peer memory: the default on
+        # CUDA with sequence parallelism when the TP group is the whole job (the measured configuration);
+        # `--backend native` asks for them with data-parallel replicas too, `--backend nccl` never uses them
+        want_fused = (device_kind == "cuda" and args.sequence_parallel
+                      and (args.backend == "native" or (args.backend == "auto" and tp_size == world)))
+        if want_fused:
+            try:
+                from .parallel.tp_native import FusedTensorParallelComm
+                comm = FusedTensorParallelComm(tp_group, dp_group)
+            except Exception as e:
+                if args.backend == "native":
+                    raise
+                logger.warning("fused tensor-parallel kernels unavailable (%s): library collectives", e)
+        if comm is None:
+            comm = TensorParallelComm(tp_group, dp_group, sequence_parallel=args.sequence_parallel)
+        if is_main:
+            logger.info("Tensor parallelism: tp=%d, %s", tp_size, type(comm).__name__)
     else:
         backend = args.backend
         if device_kind == "cpu" or backend in ("gloo", "nccl"):
