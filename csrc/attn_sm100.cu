@@ -1,175 +1,219 @@
-// Causal GQA flash-attention forward for sm_100a (head_dim 128, bf16).
+// Causal GQA flash-attention forward for sm_100a (head_dim 64 or 128, bf16), fixed-length
+// batches or packed variable-length sequences (cu_seqlens).
 //
-// One CTA per (128-row query tile, head, batch); two CTAs share an SM so that one CTA's
-// softmax overlaps the other's tensor-core work.  Per key/value tile of 128 tokens:
-//   S = Q K^T      tcgen05.mma, both operands K-major in shared memory (TMA, 128-byte swizzle),
-//                  fp32 scores in tensor memory (128 lanes x 128 columns)
-//   softmax        thread = query row: tcgen05.ld the row, online max / sum in base 2, write
-//                  P as packed bf16 back into the score columns (tcgen05.st)
-//   O += P V       tcgen05.mma with the A operand read from tensor memory and V as an MN-major
-//                  shared-memory operand; O stays in tensor memory for the whole row of tiles
-// The running maximum is refreshed lazily: O (in tensor memory) and the running sum are rescaled
-// only when a row's maximum grows by more than 2^8, which is rare after the first tiles.
+// One CTA owns two consecutive 128-row query tiles of one head and walks the key/value tiles
+// they share.  Ten warps: two softmax warpgroups (one per query tile, thread = query row), one
+// MMA-issuing warp, one TMA warp.  Tensor memory holds both score tiles and both output
+// accumulators (512 columns), so the tensor pipe alternates between the two query tiles:
+//
+//   tensor pipe:   PV0(j)  S0(j+1)  PV1(j)  S1(j+1)  PV0(j+1) ...
+//   warpgroup 0:   ........softmax of S0(j+1)........
+//   warpgroup 1:   ...softmax of S1(j)....  ........softmax of S1(j+1)...
+//
+//   S = Q K^T      tcgen05.mma, both operands K-major in shared memory (TMA, 128-byte swizzle)
+//   softmax        tcgen05.ld the row, online max / sum in base 2, P written back over the score
+//                  columns as packed bf16 (tcgen05.st); a share of the exponentials is evaluated
+//                  on the FMA pipe so that the special-function unit is not the only source
+//   O += P V       tcgen05.mma with A read from tensor memory and V as an MN-major shared operand
+// K and V tiles move through two-stage rings.  The running maximum is refreshed lazily: O and
+// the running sum are rescaled only when a row's maximum grows by more than 2^8.
 // Every wait is bounded (status word on timeout).
-#include <cuda.h>
-
-#include "tc.cuh"
+#include "attn_common.cuh"
 
 namespace {
 
-constexpr int BQ = 128, BKV = 128, HD = 128;
-constexpr int TILE_BYTES = BQ * HD * 2;            // 32 KB, stored as two 64-column halves of 16 KB
-constexpr int HALF_BYTES = BQ * 64 * 2;
-constexpr int SMEM_BYTES = 3 * TILE_BYTES + 1024 + 128;
+using namespace attn;
+
+constexpr int KST = 2, VST = 2;                    // ring depths
 constexpr float RESCALE_THRESHOLD = 8.0f;          // in log2 units
+constexpr int EMU = 4;                             // every EMU-th exponential runs on the FMA pipe
+constexpr int FWD_THREADS = 320;
 
 struct FlashParams {
     int B, T, H, KV;
+    const int* cu_seqlens;                         // [B + 1] token offsets, or null: sequence b = rows [b*T, (b+1)*T)
     float scale_log2;                              // softmax scale * log2(e)
-    __nv_bfloat16* out;                            // [B, T, H, HD]
-    float* lse;                                    // [B, H, T], natural log
+    __nv_bfloat16* out;                            // token-major, heads side by side
+    long long out_stride;                          // elements between tokens of `out`
+    float* lse;                                    // natural log; index head * lse_hs + (b * lse_bs | cu[b]) + t
+    long long lse_hs, lse_bs;
     int q_col0, k_col0, v_col0;                    // first column of head 0 inside each operand's rows
+    int n_pairs;                                   // query-tile pairs per sequence (grid decode)
     int* status;
 };
 
-__global__ void __launch_bounds__(160, 2)
+template <int HD>
+constexpr int fwd_smem_bytes() {
+    return (2 + KST + VST) * Tile<HD>::BYTES + 1024 + 256;
+}
+
+template <int HD>
+__global__ void __launch_bounds__(FWD_THREADS, 1)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const FlashParams p) {
+    constexpr int TB = Tile<HD>::BYTES;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t* sQ = smem;
-    uint8_t* sK = smem + TILE_BYTES;
-    uint8_t* sV = smem + 2 * TILE_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 3 * TILE_BYTES);
+    uint8_t* sQ = smem;                            // two query tiles
+    uint8_t* sK = smem + 2 * TB;
+    uint8_t* sV = sK + KST * TB;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sV + VST * TB);
     uint64_t* q_full = bars + 0;
-    uint64_t* k_full = bars + 1;
-    uint64_t* v_full = bars + 2;
-    uint64_t* s_full = bars + 3;
-    uint64_t* p_ready = bars + 4;
-    uint64_t* o_done = bars + 5;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6);
+    uint64_t* k_full = bars + 1;                   // [KST]
+    uint64_t* k_empty = k_full + KST;
+    uint64_t* v_full = k_empty + KST;              // [VST]
+    uint64_t* v_empty = v_full + VST;
+    uint64_t* s_full = v_empty + VST;              // [2] one per query tile
+    uint64_t* p_ready = s_full + 2;                // [2]
+    uint64_t* o_done = p_ready + 2;                // [2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int qt = (int)gridDim.x - 1 - (int)blockIdx.x;       // heavy tiles first
-    const int head = blockIdx.y, b = blockIdx.z;
+    // heavy pairs (late query tiles) first
+    const int HB = p.H * p.B;
+    const int pair = p.n_pairs - 1 - (int)(blockIdx.x / HB);
+    const int hb = blockIdx.x % HB;
+    const int head = hb % p.H, b = hb / p.H;
     const int kvh = head / (p.H / p.KV);
-    const int n_tiles = qt + 1;
-    const int row0 = b * p.T + qt * BQ;                        // first token row of this query tile
+    int seq_row0, Tb;
+    if (p.cu_seqlens) {
+        seq_row0 = p.cu_seqlens[b];
+        Tb = p.cu_seqlens[b + 1] - seq_row0;
+    } else {
+        seq_row0 = b * p.T;
+        Tb = p.T;
+    }
+    const int nkv = (Tb + BT - 1) / BT;
+    // tile counts of the two query tiles; a tile that starts past the sequence end has none
+    const int qt0 = 2 * pair, qt1 = 2 * pair + 1;
+    const int n0 = qt0 < nkv ? qt0 + 1 : 0;
+    const int n1 = qt1 < nkv ? qt1 + 1 : 0;
+    const int n = n0 > n1 ? n0 : n1;
 
     if (threadIdx.x == 0) {
         tc::mbar_init(q_full, 1);
-        tc::mbar_init(k_full, 1);
-        tc::mbar_init(v_full, 1);
-        tc::mbar_init(s_full, 1);
-        tc::mbar_init(p_ready, 4);
-        tc::mbar_init(o_done, 1);
+        for (int i = 0; i < KST; ++i) { tc::mbar_init(k_full + i, 1); tc::mbar_init(k_empty + i, 1); }
+        for (int i = 0; i < VST; ++i) { tc::mbar_init(v_full + i, 1); tc::mbar_init(v_empty + i, 1); }
+        for (int i = 0; i < 2; ++i) {
+            tc::mbar_init(s_full + i, 1);
+            tc::mbar_init(p_ready + i, 4);
+            tc::mbar_init(o_done + i, 1);
+        }
         *abort_flag = 0;
         tc::fence_barrier_init();
     }
-    if (warp == 4) {
-        tc::tmem_alloc(tmem_slot, 256);
+    if (warp == 8) {
+        tc::tmem_alloc(tmem_slot, 512);
         tc::tmem_relinquish();
     }
     tc::tc_fence_before();
     __syncthreads();
     tc::tc_fence_after();
-    const uint32_t tmem_s = *tmem_slot;            // scores / probabilities
-    const uint32_t tmem_o = tmem_s + 128;          // output accumulator
+    const uint32_t tmem0 = *tmem_slot;
+    // scores of tile t at columns t*128, output accumulator of tile t at 256 + t*128
 
-    if (warp == 4) {
-        // ------------------------------------------------------------ TMA + MMA issue (one thread)
+    if (n == 0) {
+        // nothing to do for this pair (sequence shorter than the grid was sized for)
+    } else if (warp == 9) {
+        // ------------------------------------------------------------ TMA
         if (lane == 0) {
             tc::prefetch_tmap(&tmQ);
             tc::prefetch_tmap(&tmK);
             tc::prefetch_tmap(&tmV);
             const int qx = p.q_col0 + head * HD, kx = p.k_col0 + kvh * HD, vx = p.v_col0 + kvh * HD;
-            tc::mbar_expect_tx(q_full, TILE_BYTES);
-            tc::tma_load_3d(sQ, &tmQ, q_full, qx, row0, 0);
-            tc::tma_load_3d(sQ + HALF_BYTES, &tmQ, q_full, qx + 64, row0, 0);
-            auto load_k = [&](int j) {
-                tc::mbar_expect_tx(k_full, TILE_BYTES);
-                tc::tma_load_3d(sK, &tmK, k_full, kx, b * p.T + j * BKV, 0);
-                tc::tma_load_3d(sK + HALF_BYTES, &tmK, k_full, kx + 64, b * p.T + j * BKV, 0);
-            };
-            auto load_v = [&](int j) {
-                tc::mbar_expect_tx(v_full, TILE_BYTES);
-                tc::tma_load_3d(sV, &tmV, v_full, vx, b * p.T + j * BKV, 0);
-                tc::tma_load_3d(sV + HALF_BYTES, &tmV, v_full, vx + 64, b * p.T + j * BKV, 0);
-            };
-            load_k(0);
-            load_v(0);
-            const uint32_t idesc_s = tc::instr_desc_f16(BQ, BKV, 1, 1, 0, 0);
-            const uint32_t idesc_o = tc::instr_desc_f16(BQ, HD, 1, 1, 0, 1);
+            tc::mbar_expect_tx(q_full, (n1 > 0 ? 2 : 1) * TB);
+            load_tile<HD>(sQ, &tmQ, q_full, qx, seq_row0 + qt0 * BT);
+            if (n1 > 0) load_tile<HD>(sQ + TB, &tmQ, q_full, qx, seq_row0 + qt1 * BT);
+            for (int j = 0; j < n; ++j) {
+                const int ks = j % KST, vs = j % VST;
+                if (!tc::mbar_wait(k_empty + ks, ((j / KST) & 1) ^ 1, abort_flag)) { atomicMax(p.status, (int)KB_TIMEOUT_TMA); break; }
+                tc::mbar_expect_tx(k_full + ks, TB);
+                load_tile<HD>(sK + ks * TB, &tmK, k_full + ks, kx, seq_row0 + j * BT);
+                if (!tc::mbar_wait(v_empty + vs, ((j / VST) & 1) ^ 1, abort_flag)) { atomicMax(p.status, (int)KB_TIMEOUT_TMA); break; }
+                tc::mbar_expect_tx(v_full + vs, TB);
+                load_tile<HD>(sV + vs * TB, &tmV, v_full + vs, vx, seq_row0 + j * BT);
+            }
+        }
+    } else if (warp == 8) {
+        // ------------------------------------------------------------ MMA issue (one thread)
+        if (lane == 0) {
+            const uint32_t idesc_s = tc::instr_desc_f16(BT, BT, 1, 1, 0, 0);
+            const uint32_t idesc_o = tc::instr_desc_f16(BT, HD, 1, 1, 0, 1);
             const uint32_t q_addr = smem_u32(sQ), k_addr = smem_u32(sK), v_addr = smem_u32(sV);
-            bool ok = tc::mbar_wait(q_full, 0, abort_flag);
+            bool ok = tc::mbar_wait(q_full, 0, abort_flag) && tc::mbar_wait(k_full, 0, abort_flag);
             if (!ok) atomicMax(p.status, (int)KB_TIMEOUT_TMA);
-            for (int j = 0; j < n_tiles && ok; ++j) {
+            if (ok) {
+                tc::tc_fence_after();
+                if (n0 > 0) { mma_nt_tiles<HD>(tmem0, q_addr, k_addr, idesc_s); tc::tc_commit(s_full + 0); }
+                if (n1 > 0) { mma_nt_tiles<HD>(tmem0 + 128, q_addr + TB, k_addr, idesc_s); tc::tc_commit(s_full + 1); }
+                tc::tc_commit(k_empty + 0);
+            }
+            for (int j = 0; j < n && ok; ++j) {
                 const uint32_t ph = j & 1;
-                if (!tc::mbar_wait(k_full, ph, abort_flag)) { atomicMax(p.status, (int)KB_TIMEOUT_TMA); break; }
-                tc::tc_fence_after();
-#pragma unroll
-                for (int k = 0; k < HD / 16; ++k) {
-                    const uint32_t off = (k >> 2) * HALF_BYTES + (k & 3) * 32;
-                    tc::mma_f16(tmem_s, tc::smem_desc_sw128(q_addr + off, 16, 1024),
-                                tc::smem_desc_sw128(k_addr + off, 16, 1024), idesc_s, k != 0);
+                const int vs = j % VST, ks1 = (j + 1) % KST;
+                const uint32_t vj = v_addr + vs * TB, k1 = k_addr + ks1 * TB;
+                if (!tc::mbar_wait(v_full + vs, (j / VST) & 1, abort_flag)) { atomicMax(p.status, (int)KB_TIMEOUT_TMA); break; }
+                if (j + 1 < n && !tc::mbar_wait(k_full + ks1, ((j + 1) / KST) & 1, abort_flag)) { atomicMax(p.status, (int)KB_TIMEOUT_TMA); break; }
+                if (j < n0) {
+                    if (!tc::mbar_wait(p_ready + 0, ph, abort_flag)) { atomicMax(p.status, (int)KB_TIMEOUT_MMA); break; }
+                    tc::tc_fence_after();
+                    mma_ts_tile<HD>(tmem0 + 256, tmem0, 32, vj, idesc_o, j != 0);
+                    tc::tc_commit(o_done + 0);
+                    if (j + 1 < n0) { mma_nt_tiles<HD>(tmem0, q_addr, k1, idesc_s); tc::tc_commit(s_full + 0); }
                 }
-                tc::tc_commit(s_full);
-                // K may be overwritten once the score MMAs have read it
-                if (!tc::mbar_wait(s_full, ph, abort_flag)) { atomicMax(p.status, (int)KB_TIMEOUT_MMA); break; }
-                if (j + 1 < n_tiles) load_k(j + 1);
-                if (!tc::mbar_wait(p_ready, ph, abort_flag)) { atomicMax(p.status, (int)KB_TIMEOUT_MMA); break; }
-                if (!tc::mbar_wait(v_full, ph, abort_flag)) { atomicMax(p.status, (int)KB_TIMEOUT_TMA); break; }
-                tc::tc_fence_after();
-#pragma unroll
-                for (int k = 0; k < BKV / 16; ++k) {
-                    // A: 16 bf16 = 8 packed columns per step; B: V as [kv rows][hd], MN-major, 16 rows per step
-                    tc::mma_f16_ts(tmem_o, tmem_s + k * 8, tc::smem_desc_sw128(v_addr + k * 2048, HALF_BYTES, 1024),
-                                   idesc_o, (j | k) != 0);
+                if (j < n1) {
+                    if (!tc::mbar_wait(p_ready + 1, ph, abort_flag)) { atomicMax(p.status, (int)KB_TIMEOUT_MMA); break; }
+                    tc::tc_fence_after();
+                    mma_ts_tile<HD>(tmem0 + 384, tmem0 + 128, 32, vj, idesc_o, j != 0);
+                    tc::tc_commit(o_done + 1);
+                    tc::tc_commit(v_empty + vs);
+                    if (j + 1 < n1) { mma_nt_tiles<HD>(tmem0 + 128, q_addr + TB, k1, idesc_s); tc::tc_commit(s_full + 1); }
+                } else {
+                    tc::tc_commit(v_empty + vs);
                 }
-                tc::tc_commit(o_done);
-                if (j + 1 < n_tiles) {
-                    if (!tc::mbar_wait(o_done, ph, abort_flag)) { atomicMax(p.status, (int)KB_TIMEOUT_MMA); break; }
-                    load_v(j + 1);
-                }
+                if (j + 1 < n) tc::tc_commit(k_empty + ks1);
             }
         }
     } else {
         // ------------------------------------------------------------ softmax: thread = query row
-        const int r = warp * 32 + lane;                            // row inside the tile
-        const uint32_t lane_base = ((uint32_t)(warp * 32) << 16);
+        const int t = warp >> 2;                                   // which query tile
+        const int qt = t ? qt1 : qt0, nt = t ? n1 : n0;
+        const int r = (warp & 3) * 32 + lane;                      // row inside the tile
+        const uint32_t lane_base = ((uint32_t)((warp & 3) * 32) << 16);
+        const uint32_t tmem_s = tmem0 + t * 128 + lane_base, tmem_o = tmem0 + 256 + t * 128 + lane_base;
         float m_used = -INFINITY, l = 0.f;
         bool ok = true;
-        for (int j = 0; j < n_tiles && ok; ++j) {
+        for (int j = 0; j < nt && ok; ++j) {
             const uint32_t ph = j & 1;
-            if (!tc::mbar_wait(s_full, ph, abort_flag)) {
+            if (!tc::mbar_wait(s_full + t, ph, abort_flag)) {
                 if (lane == 0) atomicMax(p.status, (int)KB_TIMEOUT_EPI);
                 ok = false;
                 break;
             }
             tc::tc_fence_after();
-            float s[BKV];
+            float s[BT];
 #pragma unroll
-            for (int c = 0; c < BKV; c += 32) tc::tmem_ld32(tmem_s + lane_base + c, reinterpret_cast<uint32_t*>(s + c));
+            for (int c = 0; c < BT; c += 32) tc::tmem_ld32(tmem_s + c, reinterpret_cast<uint32_t*>(s + c));
             tc::tmem_ld_wait();
             float mx = -INFINITY;
             if (j == qt) {                                          // diagonal tile: causal mask
 #pragma unroll
-                for (int c = 0; c < BKV; ++c) {
-                    s[c] = c <= r ? s[c] * p.scale_log2 : -INFINITY;
+                for (int c = 0; c < BT; ++c) {
+                    s[c] = c <= r ? s[c] : -INFINITY;
                     mx = fmaxf(mx, s[c]);
                 }
             } else {
 #pragma unroll
-                for (int c = 0; c < BKV; ++c) {
-                    s[c] *= p.scale_log2;
-                    mx = fmaxf(mx, s[c]);
-                }
+                for (int c = 0; c < BT; ++c) mx = fmaxf(mx, s[c]);
             }
+            mx *= p.scale_log2;
             const bool grow = mx > m_used + RESCALE_THRESHOLD;      // first tile: m_used = -inf -> true
-            if (__any_sync(0xffffffffu, grow) && j > 0) {
+            if (j == 0) {
+                m_used = mx;
+            } else if (__any_sync(0xffffffffu, grow)) {
                 // O holds sums of p * v with p relative to m_used: move it to the new maximum
-                if (!tc::mbar_wait(o_done, (j - 1) & 1, abort_flag)) {
+                if (!tc::mbar_wait(o_done + t, (j - 1) & 1, abort_flag)) {
                     if (lane == 0) atomicMax(p.status, (int)KB_TIMEOUT_EPI);
                     ok = false;
                     break;
@@ -180,134 +224,135 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll 1
                 for (int c = 0; c < HD; c += 32) {
                     uint32_t o[32];
-                    tc::tmem_ld32(tmem_o + lane_base + c, o);
+                    tc::tmem_ld32(tmem_o + c, o);
                     tc::tmem_ld_wait();
 #pragma unroll
                     for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
-                    tc::tmem_st32(tmem_o + lane_base + c, o);
+                    tc::tmem_st32(tmem_o + c, o);
                 }
                 tc::tmem_st_wait();
                 l *= f;
                 m_used = m_new;
-            } else if (j == 0) {
-                m_used = mx;
             }
-            float sum = 0.f;
+            float sum0 = 0.f, sum1 = 0.f;
 #pragma unroll
-            for (int half = 0; half < 2; ++half) {                  // 64 scores -> 32 packed columns at a time
-                uint32_t pk[32];
+            for (int q4 = 0; q4 < 4; ++q4) {                        // 32 scores -> 16 packed columns at a time
+                uint32_t pk[16];
 #pragma unroll
-                for (int c = 0; c < 64; c += 2) {
-                    const float p0 = exp2f(s[half * 64 + c] - m_used), p1 = exp2f(s[half * 64 + c + 1] - m_used);
-                    sum += p0 + p1;
-                    const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-                    pk[c >> 1] = *reinterpret_cast<const uint32_t*>(&h);
+                for (int c = 0; c < 32; c += 2) {
+                    const float x0 = fmaf(s[q4 * 32 + c], p.scale_log2, -m_used);
+                    const float x1 = fmaf(s[q4 * 32 + c + 1], p.scale_log2, -m_used);
+                    const float p0 = exp2f(x0);
+                    const float p1 = (EMU > 0 && (c + 1) % (EMU > 0 ? EMU : 1) == EMU - 1) ? exp2_poly(x1) : exp2f(x1);
+                    sum0 += p0;
+                    sum1 += p1;
+                    pk[c >> 1] = pack_bf16(p0, p1);
                 }
-                tc::tmem_st32(tmem_s + lane_base + half * 32, pk);
+                tc::tmem_st16(tmem_s + q4 * 16, pk);
             }
-            l += sum;
+            l += sum0 + sum1;
             tc::tmem_st_wait();
             tc::tc_fence_before();
             __syncwarp();
-            if (lane == 0) tc::mbar_arrive(p_ready);
+            if (lane == 0) tc::mbar_arrive(p_ready + t);
         }
-        if (ok && tc::mbar_wait(o_done, (n_tiles - 1) & 1, abort_flag)) {
-            tc::tc_fence_after();
-            const float inv = 1.f / l;
-            // T need not be a multiple of the tile: rows past the end of this sequence (zero-filled by
-            // TMA, or the first rows of the next sequence) are computed but never stored; for the valid
-            // rows the causal mask already excludes every key at or beyond the end
-            const bool valid = qt * BQ + r < p.T;
-            __nv_bfloat16* dst = p.out + ((size_t)(row0 + r) * p.H + head) * HD;
+        if (ok && nt > 0) {
+            if (tc::mbar_wait(o_done + t, (nt - 1) & 1, abort_flag)) {
+                tc::tc_fence_after();
+                const float inv = 1.f / l;
+                // Rows past the end of the sequence (zero-filled by TMA, or the first rows of the next
+                // sequence) are computed but never stored; for the valid rows the causal mask already
+                // excludes every key at or beyond the end.
+                const bool valid = qt * BT + r < Tb;
+                __nv_bfloat16* dst = p.out + (size_t)(seq_row0 + qt * BT + r) * p.out_stride + head * HD;
 #pragma unroll 1
-            for (int c = 0; c < HD; c += 32) {
-                uint32_t o[32];
-                tc::tmem_ld32(tmem_o + lane_base + c, o);
-                tc::tmem_ld_wait();
-                if (valid) {
+                for (int c = 0; c < HD; c += 32) {
+                    uint32_t o[32];
+                    tc::tmem_ld32(tmem_o + c, o);
+                    tc::tmem_ld_wait();
+                    if (valid) {
 #pragma unroll
-                    for (int i = 0; i < 32; i += 8) {
-                        float f8[8];
+                        for (int i = 0; i < 32; i += 8) {
+                            float f8[8];
 #pragma unroll
-                        for (int e = 0; e < 8; ++e) f8[e] = __uint_as_float(o[i + e]) * inv;
-                        st8(dst + c + i, pack8(f8));
+                            for (int e = 0; e < 8; ++e) f8[e] = __uint_as_float(o[i + e]) * inv;
+                            st8(dst + c + i, pack8(f8));
+                        }
                     }
                 }
+                if (valid) {
+                    const long long base = p.cu_seqlens ? (long long)seq_row0 : (long long)b * p.lse_bs;
+                    p.lse[(long long)head * p.lse_hs + base + qt * BT + r] = (m_used + log2f(l)) * LN2;
+                }
+            } else if (lane == 0) {
+                atomicMax(p.status, (int)KB_TIMEOUT_EPI);
             }
-            if (valid) p.lse[((size_t)b * p.H + head) * p.T + qt * BQ + r] = (m_used + log2f(l)) * 0.6931471805599453f;
-        } else if (ok && lane == 0) {
-            atomicMax(p.status, (int)KB_TIMEOUT_EPI);
         }
     }
     tc::tc_fence_before();
     __syncthreads();
-    if (warp == 4) {
+    if (warp == 8) {
         tc::tc_fence_after();
-        tc::tmem_dealloc(tmem_s, 256);
+        tc::tmem_dealloc(tmem0, 512);
     }
 }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn get_encode_attn() {
-    static EncodeTiledFn fn = nullptr;
-    if (!fn) {
-        void* ptr = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+// Per-device opt-in to the kernel's dynamic shared memory (an attribute of the function on one
+// device: a second device in the same process needs its own call).
+template <typename K>
+int ensure_smem(K kernel, int bytes, bool* done_for_device) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 7;
+    if (!done_for_device[dev]) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess) return 7;
+        done_for_device[dev] = true;
     }
-    return fn;
+    return 0;
 }
 
-// rows x cols bf16 matrix with the given row stride; box = 64 columns x 128 rows
-int make_rows_tmap(CUtensorMap* m, const void* base, long long rows, long long cols, long long row_stride) {
-    EncodeTiledFn enc = get_encode_attn();
-    if (!enc) return 100;
-    cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, 1};
-    cuuint64_t strides[2] = {(cuuint64_t)row_stride * 2, (cuuint64_t)rows * row_stride * 2};
-    cuuint32_t box[3] = {64, 128, 1};
-    cuuint32_t estr[3] = {1, 1, 1};
-    const CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
-                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? 0 : 200 + (int)r;
+template <int HD>
+int launch_fwd(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV, const FlashParams& p,
+               int max_T, cudaStream_t st) {
+    static bool attr[64] = {};
+    int r = ensure_smem(flash_fwd_kernel<HD>, fwd_smem_bytes<HD>(), attr);
+    if (r) return r;
+    const int grid = p.n_pairs * p.H * p.B;
+    flash_fwd_kernel<HD><<<grid, FWD_THREADS, fwd_smem_bytes<HD>(), st>>>(tmQ, tmK, tmV, p);
+    return cudaGetLastError() == cudaSuccess ? 0 : 8;
 }
 
 }  // namespace
 
-// q/k/v: token-major matrices [B*T, *] whose rows hold the heads side by side (row strides in
-// elements; *_col0 = column of head 0).  out [B,T,H,128] bf16, lse [B,H,T] fp32.
+// q/k/v: token-major matrices [total tokens, *] whose rows hold the heads side by side (row strides
+// in elements; *_col0 = column of head 0).  out: token-major with `out_stride` elements per token.
+// Fixed-length batches: cu_seqlens null, B sequences of T tokens, lse[B, H, T].  Packed sequences:
+// cu_seqlens[B + 1] (device), `total` tokens, max_T the longest sequence, lse[H, total].
 KB_API int kb_flash_fwd(const void* q, long long q_stride, int q_cols, int q_col0, const void* k, long long k_stride,
                         int k_cols, int k_col0, const void* v, long long v_stride, int v_cols, int v_col0, void* out,
-                        float* lse, int B, int T, int H, int KV, int hd, float scale, int* status, cudaStream_t st) {
-    if (hd != HD || T < 1 || H % KV != 0) return 5;
-    if ((q_stride & 7) || (k_stride & 7) || (v_stride & 7) || (q_col0 & 63) || (k_col0 & 63) || (v_col0 & 63)) return 6;
-    if (((uintptr_t)q & 15) || ((uintptr_t)k & 15) || ((uintptr_t)v & 15)) return 6;
-    static bool attr_set = false;
-    if (!attr_set) {
-        if (cudaFuncSetAttribute(flash_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
-            return 7;
-        attr_set = true;
-    }
+                        long long out_stride, float* lse, const int* cu_seqlens, long long total, int B, int max_T, int H,
+                        int KV, int hd, float scale, int* status, cudaStream_t st) {
+    if ((hd != 128 && hd != 64) || max_T < 1 || B < 1 || KV < 1 || H % KV != 0) return 5;
+    if (!operand_ok(q, q_stride, q_col0) || !operand_ok(k, k_stride, k_col0) || !operand_ok(v, v_stride, v_col0)) return 6;
+    if (((uintptr_t)out & 15) || (out_stride & 7)) return 6;
+    const long long rows = cu_seqlens ? total : (long long)B * max_T;
     CUtensorMap tmQ, tmK, tmV;
-    int r = make_rows_tmap(&tmQ, q, (long long)B * T, q_cols, q_stride);
+    int r = make_rows_tmap(&tmQ, q, rows, q_cols, q_stride);
     if (r) return r;
-    r = make_rows_tmap(&tmK, k, (long long)B * T, k_cols, k_stride);
+    r = make_rows_tmap(&tmK, k, rows, k_cols, k_stride);
     if (r) return r;
-    r = make_rows_tmap(&tmV, v, (long long)B * T, v_cols, v_stride);
+    r = make_rows_tmap(&tmV, v, rows, v_cols, v_stride);
     if (r) return r;
     FlashParams p;
-    p.B = B; p.T = T; p.H = H; p.KV = KV;
-    p.scale_log2 = scale * 1.4426950408889634f;
+    p.B = B; p.T = max_T; p.H = H; p.KV = KV;
+    p.cu_seqlens = cu_seqlens;
+    p.scale_log2 = scale * LOG2E;
     p.out = (__nv_bfloat16*)out;
+    p.out_stride = out_stride;
     p.lse = lse;
+    p.lse_hs = cu_seqlens ? total : max_T;
+    p.lse_bs = cu_seqlens ? 0 : (long long)H * max_T;
     p.q_col0 = q_col0; p.k_col0 = k_col0; p.v_col0 = v_col0;
+    p.n_pairs = (max_T + 2 * BT - 1) / (2 * BT);
     p.status = status;
-    dim3 grid((T + BQ - 1) / BQ, H, B);
-    flash_fwd_kernel<<<grid, 160, SMEM_BYTES, st>>>(tmQ, tmK, tmV, p);
-    return 0;
+    return hd == 128 ? launch_fwd<128>(tmQ, tmK, tmV, p, max_T, st) : launch_fwd<64>(tmQ, tmK, tmV, p, max_T, st);
 }

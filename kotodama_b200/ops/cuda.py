@@ -52,8 +52,7 @@ class CudaOps(TorchOps):
         self.gemm_max_ctas = 0
         self.split_k_small_m = True
         self._splitk_ws: dict = {}
-        self.native_attention = os.environ.get("KOTODAMA_FLASH", "1") == "1"
-        self.native_attention_train = os.environ.get("KOTODAMA_FLASH_TRAIN", "0") == "1"
+        self.attention_library_calls = 0   # stays 0: attention runs on the native kernels in both directions
         self.gemm_2cta = os.environ.get("KOTODAMA_GEMM_2CTA", "1") == "1"   # CTA-pair kernel for large products
         for name in ("kb_route_bwd_grid", "kb_qknorm_grid_warps", "kb_route_pipe_grid"):
             getattr(self.lib, name).restype = _I
