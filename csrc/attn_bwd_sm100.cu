@@ -15,10 +15,10 @@
 // exchange dQ needs no fp32 atomics, no fp32 staging buffer and no conversion pass.
 //
 // Tensor memory (512 columns) per CTA:
-//   attn_dq    S[0] | S[1] | dP | dQ        dS(j) overwrites the first 32 columns of each half of S[j&1]
+//   attn_dq    S[0] | S[1] | dP | dQ        dS(j) overwrites the first 16 columns of each quarter of S[j&1]
 //   attn_dkdv  S^T  | dP^T | dV | dK        P^T and dS^T overwrite their own score tiles the same way
-// Each of the two compute warpgroups handles 64 of a tile's 128 columns and writes its packed
-// result into its own half, so neither warpgroup overwrites scores the other has not read yet.
+// Each of the four compute warpgroups handles 32 of a tile's 128 columns and writes its packed
+// result at the start of its own quarter, so no warpgroup overwrites scores another has not read yet.
 // Every wait is bounded (status word on timeout).
 #include "attn_common.cuh"
 
@@ -26,8 +26,8 @@ namespace {
 
 using namespace attn;
 
-constexpr int BWD_THREADS = 320;                   // 8 compute warps, MMA warp, TMA warp
-constexpr int EMU = 4;                             // every EMU-th exponential runs on the FMA pipe
+constexpr int BWD_THREADS = 576;                   // 16 compute warps, MMA warp, TMA warp
+constexpr int EMU = 1;                             // of every 4 pairs of exponentials, this many run on the FMA pipe
 
 struct BwdParams {
     int B, T, H, KV;
@@ -78,15 +78,16 @@ attn_dprep_kernel(const __nv_bfloat16* __restrict__ o, long long o_stride, const
     if (lane == 0) dsum[((long long)b * H + head) * T + t] = acc;
 }
 
-// 64 scores -> 64 probabilities 2^(s*c - lse2), `keep(c)` false -> 0
-template <typename Keep>
-__device__ __forceinline__ void probs64(const float* s, float scale_log2, const float* lse2, bool per_column,
-                                        float lse2_row, Keep keep, float* pv) {
+// 32 scores -> 16 pairs of probabilities 2^(s*c - lse2).  `nl` holds -lse2: per column (shared
+// memory, PER_COLUMN) or one value for the row.
+template <bool PER_COLUMN>
+__device__ __forceinline__ void probs32(const float* s, float scale_log2, const float* nl_cols, float nl_row,
+                                        float2* pv) {
+    const float2 sc2 = make_float2(scale_log2, scale_log2);
 #pragma unroll
-    for (int c = 0; c < 64; ++c) {
-        const float x = fmaf(s[c], scale_log2, -(per_column ? lse2[c] : lse2_row));
-        const float e = (EMU > 0 && c % (EMU > 0 ? EMU : 1) == EMU - 1) ? exp2_poly(x) : exp2f(x);
-        pv[c] = keep(c) ? e : 0.f;
+    for (int c = 0; c < 32; c += 2) {
+        const float2 nl = PER_COLUMN ? *reinterpret_cast<const float2*>(nl_cols + c) : make_float2(nl_row, nl_row);
+        pv[c >> 1] = exp2_pair<EMU>(__ffma2_rn(make_float2(s[c], s[c + 1]), sc2, nl), c >> 1);
     }
 }
 
@@ -138,12 +139,12 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         tc::mbar_init(s_full + 0, 1);
         tc::mbar_init(s_full + 1, 1);
         tc::mbar_init(dp_full, 1);
-        tc::mbar_init(ds_ready, 8);
+        tc::mbar_init(ds_ready, 16);
         tc::mbar_init(dq_done, 1);
         *abort_flag = 0;
         tc::fence_barrier_init();
     }
-    if (warp == 8) {
+    if (warp == 16) {
         tc::tmem_alloc(tmem_slot, 512);
         tc::tmem_relinquish();
     }
@@ -153,7 +154,7 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     const uint32_t tmem0 = *tmem_slot;
     const uint32_t tm_dp = tmem0 + 256, tm_dq = tmem0 + 384;
 
-    if (warp == 9) {
+    if (warp == 17) {
         // ------------------------------------------------------------ TMA
         if (lane == 0) {
             tc::prefetch_tmap(&tmQ);
@@ -174,7 +175,7 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 load_tile<HD>(sV + vs * TB, &tmV, v_full + vs, vx, seq_row0 + j * BT);
             }
         }
-    } else if (warp == 8) {
+    } else if (warp == 16) {
         // ------------------------------------------------------------ MMA issue (one thread)
         if (lane == 0) {
             const uint32_t idesc_s = tc::instr_desc_f16(BT, BT, 1, 1, 0, 0);
@@ -209,7 +210,7 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                         tc::tc_commit(v_empty + vs);
                     }
                     const int ks = j % DQ_KST;
-                    mma_ts_tile<HD>(tm_dq, tmem0 + (j & 1) * 128, 64, k_addr + ks * TB, idesc_q, j != 0);
+                    mma_ts_tile<HD, true>(tm_dq, tmem0 + (j & 1) * 128, k_addr + ks * TB, idesc_q, j != 0);
                     tc::tc_commit(k_empty + ks);
                     if (j + 2 < n) {
                         const int k2 = (j + 2) % DQ_KST;
@@ -222,56 +223,77 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 if (ok) tc::tc_commit(dq_done);
             } while (false);
         }
-    } else {
-        // ------------------------------------------------------------ compute: thread = (query row, column half)
-        const int hf = warp >> 2;
+    } else if (warp < 16) {
+        // ------------------------------------------------------------ compute: thread = (query row, column quarter)
+        const int qd = warp >> 2;
         const int r = (warp & 3) * 32 + lane;
         const uint32_t lane_base = ((uint32_t)((warp & 3) * 32) << 16);
         const int qrow = qt * BT + r;
         const bool valid = qrow < p.T;
         const long long sidx = ((long long)b * p.H + head) * p.T + qrow;
-        const float lse2 = valid ? p.lse[sidx] * LOG2E : INFINITY;
-        const float dsum = valid ? p.dsum[sidx] : 0.f;
+        const float nl = valid ? -p.lse[sidx] * LOG2E : -INFINITY;
+        const float nds = valid ? -p.dsum[sidx] * p.scale : 0.f;      // -D * scale
+        const float2 scale2 = make_float2(p.scale, p.scale), nds2 = make_float2(nds, nds);
         bool ok = true;
-        for (int j = 0; j < n; ++j) {
-            const uint32_t tm_s = tmem0 + (j & 1) * 128 + hf * 64 + lane_base;
-            if (!tc::mbar_wait(s_full + (j & 1), (j >> 1) & 1, abort_flag) || !tc::mbar_wait(dp_full, j & 1, abort_flag)) {
+        float2 pv[16];                                                // probabilities of the tile in flight
+        // P(j) only needs the scores, so it is computed while the tensor pipe still works on dP(j)
+        auto compute_p = [&](int j) -> bool {
+            if (!tc::mbar_wait(s_full + (j & 1), (j >> 1) & 1, abort_flag)) return false;
+            tc::tc_fence_after();
+            float s[32];
+            tc::tmem_ld32(tmem0 + (j & 1) * 128 + qd * 32 + lane_base, reinterpret_cast<uint32_t*>(s));
+            tc::tmem_ld_wait();
+            probs32<false>(s, p.scale_log2, nullptr, nl, pv);
+            if (j == qt) {                                            // diagonal tile: keys after the query get 0
+                const int cmax = r - qd * 32;
+#pragma unroll
+                for (int c = 0; c < 32; c += 2) {
+                    pv[c >> 1].x = c <= cmax ? pv[c >> 1].x : 0.f;
+                    pv[c >> 1].y = c + 1 <= cmax ? pv[c >> 1].y : 0.f;
+                }
+            }
+            return true;
+        };
+        ok = compute_p(0);
+        if (!ok && lane == 0) atomicMax(p.status, (int)KB_TIMEOUT_EPI);
+        for (int j = 0; j < n && ok; ++j) {
+            if (!tc::mbar_wait(dp_full, j & 1, abort_flag)) {
                 if (lane == 0) atomicMax(p.status, (int)KB_TIMEOUT_EPI);
                 ok = false;
                 break;
             }
             tc::tc_fence_after();
-            float s[64], dp[64];
-            tc::tmem_ld32(tm_s, reinterpret_cast<uint32_t*>(s));
-            tc::tmem_ld32(tm_s + 32, reinterpret_cast<uint32_t*>(s + 32));
-            tc::tmem_ld32(tm_dp + hf * 64 + lane_base, reinterpret_cast<uint32_t*>(dp));
-            tc::tmem_ld32(tm_dp + hf * 64 + lane_base + 32, reinterpret_cast<uint32_t*>(dp + 32));
+            float dp[32];
+            tc::tmem_ld32(tm_dp + qd * 32 + lane_base, reinterpret_cast<uint32_t*>(dp));
             tc::tmem_ld_wait();
-            const int cmax = j == qt ? r - hf * 64 : 64;            // columns c <= cmax are at or below the diagonal
-            probs64(s, p.scale_log2, nullptr, false, lse2, [&](int c) { return c <= cmax; }, s);
-            uint32_t pk[32];
+            uint32_t pk[16];
 #pragma unroll
-            for (int c = 0; c < 64; c += 2)
-                pk[c >> 1] = pack_bf16(s[c] * (dp[c] - dsum) * p.scale, s[c + 1] * (dp[c + 1] - dsum) * p.scale);
-            tc::tmem_st32(tm_s, pk);
+            for (int c = 0; c < 32; c += 2) {
+                const float2 d = __fmul2_rn(pv[c >> 1], __ffma2_rn(make_float2(dp[c], dp[c + 1]), scale2, nds2));
+                pk[c >> 1] = pack_bf16(d.x, d.y);
+            }
+            tc::tmem_st16(tmem0 + (j & 1) * 128 + qd * 32 + lane_base, pk);
             tc::tmem_st_wait();
             tc::tc_fence_before();
             __syncwarp();
             if (lane == 0) tc::mbar_arrive(ds_ready);
+            if (j + 1 < n && !compute_p(j + 1)) {
+                if (lane == 0) atomicMax(p.status, (int)KB_TIMEOUT_EPI);
+                ok = false;
+            }
         }
         if (ok) {
             if (tc::mbar_wait(dq_done, 0, abort_flag)) {
                 tc::tc_fence_after();
-                __nv_bfloat16* dst = p.dq + (size_t)(seq_row0 + qrow) * p.dq_stride + head * HD + hf * (HD / 2);
+                constexpr int CW = HD / 4;                            // output columns per thread
+                __nv_bfloat16* dst = p.dq + (size_t)(seq_row0 + qrow) * p.dq_stride + head * HD + qd * CW;
+                uint32_t o[CW];
+                if constexpr (CW == 32) tc::tmem_ld32(tm_dq + qd * CW + lane_base, o);
+                else tc::tmem_ld16(tm_dq + qd * CW + lane_base, o);
+                tc::tmem_ld_wait();
+                if (valid) {
 #pragma unroll
-                for (int c = 0; c < HD / 2; c += 32) {
-                    uint32_t o[32];
-                    tc::tmem_ld32(tm_dq + hf * (HD / 2) + c + lane_base, o);
-                    tc::tmem_ld_wait();
-                    if (valid) {
-#pragma unroll
-                        for (int i = 0; i < 32; i += 8) st8(dst + c + i, pack8(reinterpret_cast<const float*>(o + i)));
-                    }
+                    for (int i = 0; i < CW; i += 8) st8(dst + i, pack8(reinterpret_cast<const float*>(o + i)));
                 }
             } else if (lane == 0) {
                 atomicMax(p.status, (int)KB_TIMEOUT_EPI);
@@ -280,18 +302,22 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     }
     tc::tc_fence_before();
     __syncthreads();
-    if (warp == 8) {
+    if (warp == 16) {
         tc::tc_fence_after();
         tc::tmem_dealloc(tmem0, 512);
     }
 }
 
 // ---------------------------------------------------------------------------------- dK, dV
-constexpr int KV_RING = 2;                         // ring depth of the query / output-gradient tiles
+// The query and output-gradient tiles of consecutive pairs share one ring of RING slots, filled
+// in the order Q(0), dO(0), Q(1), dO(1), ...: load number u goes to slot u % RING.  With five
+// slots a tile is requested more than a pair ahead of its first use, which keeps the TMA latency
+// off the per-pair critical path (a slot is held from the tile's first product to its last).
+constexpr int RING = 5, STAT_RING = 2;
 
 template <int HD>
 constexpr int dkdv_smem_bytes() {
-    return (2 + 2 * KV_RING) * Tile<HD>::BYTES + KV_RING * 2 * BT * 4 + 1024 + 256;
+    return (2 + RING) * Tile<HD>::BYTES + STAT_RING * 2 * BT * 4 + 256;
 }
 
 template <int HD>
@@ -299,22 +325,22 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
 attn_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO, const BwdParams p) {
     constexpr int TB = Tile<HD>::BYTES;
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    extern __shared__ __align__(1024) uint8_t smem[];
+    if (smem_u32(smem) & 1023) {                   // the swizzled tiles need 1024-byte aligned slots
+        if (threadIdx.x == 0) atomicMax(p.status, (int)KB_BAD_ARG);
+        return;
+    }
     uint8_t* sK = smem;
     uint8_t* sV = smem + TB;
-    uint8_t* sQ = smem + 2 * TB;                   // [KV_RING]
-    uint8_t* sDO = sQ + KV_RING * TB;              // [KV_RING]
-    float* sStat = reinterpret_cast<float*>(sDO + KV_RING * TB);   // [KV_RING][2][128]: lse * log2(e), D
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sStat + KV_RING * 2 * BT);
+    uint8_t* sRing = smem + 2 * TB;                // [RING]
+    float* sStat = reinterpret_cast<float*>(sRing + RING * TB);    // [STAT_RING][2][128]: -lse * log2(e), -D * scale
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sStat + STAT_RING * 2 * BT);
     uint64_t* kv_full = bars;
-    uint64_t* q_full = bars + 1;                   // [KV_RING]
-    uint64_t* q_empty = q_full + KV_RING;
-    uint64_t* do_full = q_empty + KV_RING;
-    uint64_t* do_empty = do_full + KV_RING;
-    uint64_t* stat_full = do_empty + KV_RING;
-    uint64_t* stat_empty = stat_full + KV_RING;
-    uint64_t* s_full = stat_empty + KV_RING;
+    uint64_t* full = bars + 1;                     // [RING]
+    uint64_t* empty = full + RING;                 // [RING]
+    uint64_t* stat_full = empty + RING;            // [STAT_RING]
+    uint64_t* stat_empty = stat_full + STAT_RING;
+    uint64_t* s_full = stat_empty + STAT_RING;
     uint64_t* dp_full = s_full + 1;
     uint64_t* p_ready = dp_full + 1;
     uint64_t* ds_ready = p_ready + 1;
@@ -334,23 +360,23 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 
     if (threadIdx.x == 0) {
         tc::mbar_init(kv_full, 1);
-        for (int i = 0; i < KV_RING; ++i) {
-            tc::mbar_init(q_full + i, 1);
-            tc::mbar_init(q_empty + i, 1);
-            tc::mbar_init(do_full + i, 1);
-            tc::mbar_init(do_empty + i, 1);
+        for (int i = 0; i < RING; ++i) {
+            tc::mbar_init(full + i, 1);
+            tc::mbar_init(empty + i, 1);
+        }
+        for (int i = 0; i < STAT_RING; ++i) {
             tc::mbar_init(stat_full + i, 1);
-            tc::mbar_init(stat_empty + i, 8);
+            tc::mbar_init(stat_empty + i, 16);
         }
         tc::mbar_init(s_full, 1);
         tc::mbar_init(dp_full, 1);
-        tc::mbar_init(p_ready, 8);
-        tc::mbar_init(ds_ready, 8);
+        tc::mbar_init(p_ready, 16);
+        tc::mbar_init(ds_ready, 16);
         tc::mbar_init(acc_done, 1);
         *abort_flag = 0;
         tc::fence_barrier_init();
     }
-    if (warp == 8) {
+    if (warp == 16) {
         tc::tmem_alloc(tmem_slot, 512);
         tc::tmem_relinquish();
     }
@@ -360,7 +386,7 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const uint32_t tmem0 = *tmem_slot;
     const uint32_t tm_dp = tmem0 + 128, tm_dv = tmem0 + 256, tm_dk = tmem0 + 384;
 
-    if (warp == 9) {
+    if (warp == 17) {
         // ------------------------------------------------------------ TMA (lane 0) + row statistics (all lanes)
         if (lane == 0) {
             tc::prefetch_tmap(&tmQ);
@@ -372,23 +398,20 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             load_tile<HD>(sV, &tmV, kv_full, p.v_col0 + g * HD, seq_row0 + jt * BT);
         }
         for (int t = 0; t < np; ++t) {
-            const int st = t % KV_RING;
-            const uint32_t eph = ((t / KV_RING) & 1) ^ 1;
             const int head = g * G + t / nqi, qt = jt + t % nqi;
             int ok = 1;
             if (lane == 0) {
-                if (!tc::mbar_wait(q_empty + st, eph, abort_flag)) ok = 0;
-                if (ok) {
-                    tc::mbar_expect_tx(q_full + st, TB);
-                    load_tile<HD>(sQ + st * TB, &tmQ, q_full + st, p.q_col0 + head * HD, seq_row0 + qt * BT);
-                    if (!tc::mbar_wait(do_empty + st, eph, abort_flag)) ok = 0;
-                }
-                if (ok) {
-                    tc::mbar_expect_tx(do_full + st, TB);
-                    load_tile<HD>(sDO + st * TB, &tmDO, do_full + st, p.do_col0 + head * HD, seq_row0 + qt * BT);
+#pragma unroll
+                for (int w = 0; w < 2 && ok; ++w) {                   // w = 0: Q(t), w = 1: dO(t)
+                    const int u = 2 * t + w, sl = u % RING;
+                    if (!tc::mbar_wait(empty + sl, ((u / RING) & 1) ^ 1, abort_flag)) { ok = 0; break; }
+                    tc::mbar_expect_tx(full + sl, TB);
+                    load_tile<HD>(sRing + sl * TB, w ? &tmDO : &tmQ, full + sl,
+                                  (w ? p.do_col0 : p.q_col0) + head * HD, seq_row0 + qt * BT);
                 }
             }
-            if (ok && !tc::mbar_wait(stat_empty + st, eph, abort_flag)) ok = 0;
+            const int st = t % STAT_RING;
+            if (ok && !tc::mbar_wait(stat_empty + st, ((t / STAT_RING) & 1) ^ 1, abort_flag)) ok = 0;
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) {
                 if (lane == 0) atomicMax(p.status, (int)KB_TIMEOUT_TMA);
@@ -400,86 +423,94 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             for (int e = 0; e < 4; ++e) {
                 const int c = lane + e * 32, qrow = qt * BT + c;
                 const bool valid = qrow < p.T;
-                dst[c] = valid ? p.lse[base + qrow] * LOG2E : INFINITY;
-                dst[BT + c] = valid ? p.dsum[base + qrow] : 0.f;
+                dst[c] = valid ? -p.lse[base + qrow] * LOG2E : -INFINITY;
+                dst[BT + c] = valid ? -p.dsum[base + qrow] * p.scale : 0.f;
             }
             __syncwarp();
             if (lane == 0) tc::mbar_arrive(stat_full + st);
         }
-    } else if (warp == 8) {
+    } else if (warp == 16) {
         // ------------------------------------------------------------ MMA issue (one thread)
         if (lane == 0) {
             const uint32_t idesc_s = tc::instr_desc_f16(BT, BT, 1, 1, 0, 0);
             const uint32_t idesc_a = tc::instr_desc_f16(BT, HD, 1, 1, 0, 1);
-            const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV), q_addr = smem_u32(sQ), do_addr = smem_u32(sDO);
+            const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV), ring = smem_u32(sRing);
+            auto slot_addr = [&](int u) { return ring + (u % RING) * TB; };
+            auto wait_full = [&](int u) { return tc::mbar_wait(full + u % RING, (u / RING) & 1, abort_flag); };
             do {
-                if (!tc::mbar_wait(kv_full, 0, abort_flag) || !tc::mbar_wait(q_full, 0, abort_flag)) KB_FAIL(KB_TIMEOUT_TMA)
+                if (!tc::mbar_wait(kv_full, 0, abort_flag) || !wait_full(0)) KB_FAIL(KB_TIMEOUT_TMA)
                 tc::tc_fence_after();
-                mma_nt_tiles<HD>(tmem0, k_addr, q_addr, idesc_s);
+                mma_nt_tiles<HD>(tmem0, k_addr, slot_addr(0), idesc_s);
                 tc::tc_commit(s_full);
-                if (!tc::mbar_wait(do_full, 0, abort_flag)) KB_FAIL(KB_TIMEOUT_TMA)
+                if (!wait_full(1)) KB_FAIL(KB_TIMEOUT_TMA)
                 tc::tc_fence_after();
-                mma_nt_tiles<HD>(tm_dp, v_addr, do_addr, idesc_s);
+                mma_nt_tiles<HD>(tm_dp, v_addr, slot_addr(1), idesc_s);
                 tc::tc_commit(dp_full);
                 bool ok = true;
                 for (int t = 0; t < np; ++t) {
-                    const int st = t % KV_RING, nst = (t + 1) % KV_RING;
-                    const uint32_t nph = ((t + 1) / KV_RING) & 1;
+                    const int uq = 2 * t, ud = 2 * t + 1;
                     if (!tc::mbar_wait(p_ready, t & 1, abort_flag)) { atomicMax(p.status, (int)KB_TIMEOUT_MMA); ok = false; break; }
                     tc::tc_fence_after();
-                    mma_ts_tile<HD>(tm_dv, tmem0, 64, do_addr + st * TB, idesc_a, t != 0);
-                    tc::tc_commit(do_empty + st);
+                    mma_ts_tile<HD, true>(tm_dv, tmem0, slot_addr(ud), idesc_a, t != 0);
+                    tc::tc_commit(empty + ud % RING);
                     if (t + 1 < np) {
-                        if (!tc::mbar_wait(q_full + nst, nph, abort_flag)) { atomicMax(p.status, (int)KB_TIMEOUT_TMA); ok = false; break; }
+                        if (!wait_full(uq + 2)) { atomicMax(p.status, (int)KB_TIMEOUT_TMA); ok = false; break; }
                         tc::tc_fence_after();
-                        mma_nt_tiles<HD>(tmem0, k_addr, q_addr + nst * TB, idesc_s);
+                        mma_nt_tiles<HD>(tmem0, k_addr, slot_addr(uq + 2), idesc_s);
                         tc::tc_commit(s_full);
                     }
                     if (!tc::mbar_wait(ds_ready, t & 1, abort_flag)) { atomicMax(p.status, (int)KB_TIMEOUT_MMA); ok = false; break; }
                     tc::tc_fence_after();
-                    mma_ts_tile<HD>(tm_dk, tm_dp, 64, q_addr + st * TB, idesc_a, t != 0);
-                    tc::tc_commit(q_empty + st);
+                    mma_ts_tile<HD, true>(tm_dk, tm_dp, slot_addr(uq), idesc_a, t != 0);
+                    tc::tc_commit(empty + uq % RING);
                     if (t + 1 < np) {
-                        if (!tc::mbar_wait(do_full + nst, nph, abort_flag)) { atomicMax(p.status, (int)KB_TIMEOUT_TMA); ok = false; break; }
+                        if (!wait_full(ud + 2)) { atomicMax(p.status, (int)KB_TIMEOUT_TMA); ok = false; break; }
                         tc::tc_fence_after();
-                        mma_nt_tiles<HD>(tm_dp, v_addr, do_addr + nst * TB, idesc_s);
+                        mma_nt_tiles<HD>(tm_dp, v_addr, slot_addr(ud + 2), idesc_s);
                         tc::tc_commit(dp_full);
                     }
                 }
                 if (ok) tc::tc_commit(acc_done);
             } while (false);
         }
-    } else {
-        // ------------------------------------------------------------ compute: thread = (key row, column half)
-        const int hf = warp >> 2;
+    } else if (warp < 16) {
+        // ------------------------------------------------------------ compute: thread = (key row, column quarter)
+        const int qd = warp >> 2;
         const int r = (warp & 3) * 32 + lane;
         const uint32_t lane_base = ((uint32_t)((warp & 3) * 32) << 16);
-        const uint32_t tm_s = tmem0 + hf * 64 + lane_base, tm_d = tm_dp + hf * 64 + lane_base;
+        const uint32_t tm_s = tmem0 + qd * 32 + lane_base, tm_d = tm_dp + qd * 32 + lane_base;
+        const float2 scale2 = make_float2(p.scale, p.scale);
         bool ok = true;
         for (int t = 0; t < np; ++t) {
-            const int st = t % KV_RING;
+            const int st = t % STAT_RING;
             const bool diag = t % nqi == 0;
-            const float* lse2 = sStat + st * 2 * BT + hf * 64;
-            const float* dsum = lse2 + BT;
-            if (!tc::mbar_wait(stat_full + st, (t / KV_RING) & 1, abort_flag) || !tc::mbar_wait(s_full, t & 1, abort_flag)) {
+            const float* nl = sStat + st * 2 * BT + qd * 32;          // -lse * log2(e) of this quarter's query positions
+            const float* nds = nl + BT;                               // -D * scale
+            if (!tc::mbar_wait(stat_full + st, (t / STAT_RING) & 1, abort_flag) || !tc::mbar_wait(s_full, t & 1, abort_flag)) {
                 if (lane == 0) atomicMax(p.status, (int)KB_TIMEOUT_EPI);
                 ok = false;
                 break;
             }
             tc::tc_fence_after();
-            uint32_t pk[32];
+            uint32_t pk[16];
             {
-                float s[64];
+                float s[32];
+                float2 pv[16];
                 tc::tmem_ld32(tm_s, reinterpret_cast<uint32_t*>(s));
-                tc::tmem_ld32(tm_s + 32, reinterpret_cast<uint32_t*>(s + 32));
                 tc::tmem_ld_wait();
-                // keep query positions at or after this key row (diagonal tile only)
-                const int cmin = diag ? r - hf * 64 : 0;
-                probs64(s, p.scale_log2, lse2, true, 0.f, [&](int c) { return c >= cmin; }, s);
+                probs32<true>(s, p.scale_log2, nl, 0.f, pv);
+                if (diag) {                                           // keep query positions at or after this key row
+                    const int cmin = r - qd * 32;
 #pragma unroll
-                for (int c = 0; c < 64; c += 2) pk[c >> 1] = pack_bf16(s[c], s[c + 1]);
+                    for (int c = 0; c < 32; c += 2) {
+                        pv[c >> 1].x = c >= cmin ? pv[c >> 1].x : 0.f;
+                        pv[c >> 1].y = c + 1 >= cmin ? pv[c >> 1].y : 0.f;
+                    }
+                }
+#pragma unroll
+                for (int c = 0; c < 16; ++c) pk[c] = pack_bf16(pv[c].x, pv[c].y);
             }
-            tc::tmem_st32(tm_s, pk);
+            tc::tmem_st16(tm_s, pk);
             tc::tmem_st_wait();
             tc::tc_fence_before();
             __syncwarp();
@@ -491,17 +522,18 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             }
             tc::tc_fence_after();
             {
-                float dp[64];
+                float dp[32];
                 tc::tmem_ld32(tm_d, reinterpret_cast<uint32_t*>(dp));
-                tc::tmem_ld32(tm_d + 32, reinterpret_cast<uint32_t*>(dp + 32));
                 tc::tmem_ld_wait();
 #pragma unroll
-                for (int c = 0; c < 64; c += 2) {
-                    const float2 pv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&pk[c >> 1]));
-                    pk[c >> 1] = pack_bf16(pv.x * (dp[c] - dsum[c]) * p.scale, pv.y * (dp[c + 1] - dsum[c + 1]) * p.scale);
+                for (int c = 0; c < 32; c += 2) {
+                    const float2 pv = make_float2(__uint_as_float(pk[c >> 1] << 16), __uint_as_float(pk[c >> 1] & 0xffff0000u));
+                    const float2 d = __fmul2_rn(pv, __ffma2_rn(make_float2(dp[c], dp[c + 1]), scale2,
+                                                               *reinterpret_cast<const float2*>(nds + c)));
+                    pk[c >> 1] = pack_bf16(d.x, d.y);
                 }
             }
-            tc::tmem_st32(tm_d, pk);
+            tc::tmem_st16(tm_d, pk);
             tc::tmem_st_wait();
             tc::tc_fence_before();
             __syncwarp();
@@ -513,24 +545,25 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (ok) {
             if (tc::mbar_wait(acc_done, 0, abort_flag)) {
                 tc::tc_fence_after();
+                constexpr int CW = HD / 4;                            // output columns per thread
                 const int krow = jt * BT + r;
                 const bool valid = krow < p.T;
-                __nv_bfloat16* dv = p.dv + (size_t)(seq_row0 + krow) * p.dv_stride + g * HD + hf * (HD / 2);
-                __nv_bfloat16* dk = p.dk + (size_t)(seq_row0 + krow) * p.dk_stride + g * HD + hf * (HD / 2);
+                __nv_bfloat16* dv = p.dv + (size_t)(seq_row0 + krow) * p.dv_stride + g * HD + qd * CW;
+                __nv_bfloat16* dk = p.dk + (size_t)(seq_row0 + krow) * p.dk_stride + g * HD + qd * CW;
+                uint32_t o[CW], o2[CW];
+                if constexpr (CW == 32) {
+                    tc::tmem_ld32(tm_dv + qd * CW + lane_base, o);
+                    tc::tmem_ld32(tm_dk + qd * CW + lane_base, o2);
+                } else {
+                    tc::tmem_ld16(tm_dv + qd * CW + lane_base, o);
+                    tc::tmem_ld16(tm_dk + qd * CW + lane_base, o2);
+                }
+                tc::tmem_ld_wait();
+                if (valid) {
 #pragma unroll
-                for (int c = 0; c < HD / 2; c += 32) {
-                    uint32_t o[32];
-                    tc::tmem_ld32(tm_dv + hf * (HD / 2) + c + lane_base, o);
-                    tc::tmem_ld_wait();
-                    if (valid) {
-#pragma unroll
-                        for (int i = 0; i < 32; i += 8) st8(dv + c + i, pack8(reinterpret_cast<const float*>(o + i)));
-                    }
-                    tc::tmem_ld32(tm_dk + hf * (HD / 2) + c + lane_base, o);
-                    tc::tmem_ld_wait();
-                    if (valid) {
-#pragma unroll
-                        for (int i = 0; i < 32; i += 8) st8(dk + c + i, pack8(reinterpret_cast<const float*>(o + i)));
+                    for (int i = 0; i < CW; i += 8) {
+                        st8(dv + i, pack8(reinterpret_cast<const float*>(o + i)));
+                        st8(dk + i, pack8(reinterpret_cast<const float*>(o2 + i)));
                     }
                 }
             } else if (lane == 0) {
@@ -540,7 +573,7 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
     tc::tc_fence_before();
     __syncthreads();
-    if (warp == 8) {
+    if (warp == 16) {
         tc::tc_fence_after();
         tc::tmem_dealloc(tmem0, 512);
     }

@@ -81,14 +81,16 @@ __device__ __forceinline__ void mma_nt_tiles(uint32_t d_tmem, uint32_t a_addr, u
 }
 
 // acc[128 x HD] (+)= A B with A = 128 x 128 bf16 in tensor memory and B a stored tile read as
-// [K = 128 tokens, N = HD] (MN-major).  The packed A operand lives in two runs of 32 columns:
-// contraction steps 0..3 at `a_tmem`, steps 4..7 at `a_tmem + a_hi`.
-template <int HD>
-__device__ __forceinline__ void mma_ts_tile(uint32_t d_tmem, uint32_t a_tmem, uint32_t a_hi, uint32_t b_addr,
-                                            uint32_t idesc, bool accumulate) {
+// [K = 128 tokens, N = HD] (MN-major).  The packed A operand (8 columns per 16-wide contraction
+// step) is either one run of 64 columns (QUARTERS false) or four runs of 16 columns, one at the
+// start of each 32-column quarter of the fp32 tile it overwrites (QUARTERS true: every thread of
+// a row writes its packed result inside the columns it read).
+template <int HD, bool QUARTERS>
+__device__ __forceinline__ void mma_ts_tile(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_addr, uint32_t idesc,
+                                            bool accumulate) {
 #pragma unroll
     for (int k = 0; k < BT / 16; ++k) {
-        const uint32_t a = a_tmem + (k < 4 ? k * 8 : a_hi + (k - 4) * 8);
+        const uint32_t a = a_tmem + (QUARTERS ? 32 * (k >> 1) + 8 * (k & 1) : 8 * k);
         tc::mma_f16_ts(d_tmem, a, tc::smem_desc_sw128(b_addr + k * 2048, HALF_BYTES, 1024), idesc,
                        accumulate || k != 0);
     }
@@ -99,17 +101,40 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
     return *reinterpret_cast<const uint32_t*>(&h);
 }
 
-// 2^x for x <= 0 on the FMA pipe (Cody-Waite split, degree-3 minimax on [0,1)); relative error
-// about 1e-4, below the bf16 rounding of the probabilities it feeds.  Used for a share of the
-// elements so that the special-function unit is not the only exponent source.
-__device__ __forceinline__ float exp2_poly(float x) {
-    x = fmaxf(x, -126.f);
-    const float fl = floorf(x);
-    const float f = x - fl;
-    float p = fmaf(f, 0.07802403f, 0.22606707f);
-    p = fmaf(p, f, 0.69583399f);
-    p = fmaf(p, f, 0.99992513f);
-    return __int_as_float(__float_as_int(p) + ((int)fl << 23));
+// max of three (one instruction on sm_100)
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
+// 2^x for a pair of x <= 0 on the FMA pipe with packed two-wide instructions: the integer part
+// comes from a round-down add of 1.5 * 2^23 (its low mantissa bits then hold floor(x)), the
+// fraction goes through a degree-3 minimax polynomial on [0, 1) (relative error 7.5e-5, below
+// the bf16 rounding of the probabilities it feeds), and the exponent is added with integer
+// arithmetic.  Used for a share of the elements so that the special-function unit is not the
+// only source of exponentials.
+__device__ __forceinline__ float2 exp2_poly2(float2 x) {
+    const float M = 12582912.f;
+    x.x = fmaxf(x.x, -126.f);
+    x.y = fmaxf(x.y, -126.f);
+    const float2 t = __fadd2_rd(x, make_float2(M, M));
+    const float2 fl = __fadd2_rn(t, make_float2(-M, -M));
+    const float2 f = __ffma2_rn(fl, make_float2(-1.f, -1.f), x);
+    float2 p = __ffma2_rn(f, make_float2(0.07802403f, 0.07802403f), make_float2(0.22606707f, 0.22606707f));
+    p = __ffma2_rn(p, f, make_float2(0.69583399f, 0.69583399f));
+    p = __ffma2_rn(p, f, make_float2(0.99992513f, 0.99992513f));
+    p.x = __int_as_float(__float_as_int(p.x) + (__float_as_int(t.x) << 23));
+    p.y = __int_as_float(__float_as_int(p.y) + (__float_as_int(t.y) << 23));
+    return p;
+}
+
+// 2^x for a pair: pair number `i` of a row decides between the special-function unit and the
+// polynomial (EMU of every 4 pairs are emulated).
+template <int EMU>
+__device__ __forceinline__ float2 exp2_pair(float2 x, int i) {
+    if ((i & 3) < EMU) return exp2_poly2(x);
+    return make_float2(exp2f(x.x), exp2f(x.y));
 }
 
 }  // namespace attn

@@ -2,13 +2,14 @@
 // batches or packed variable-length sequences (cu_seqlens).
 //
 // One CTA owns two consecutive 128-row query tiles of one head and walks the key/value tiles
-// they share.  Ten warps: two softmax warpgroups (one per query tile, thread = query row), one
-// MMA-issuing warp, one TMA warp.  Tensor memory holds both score tiles and both output
+// they share.  Eighteen warps: four softmax warpgroups (two per query tile: each of a row's two
+// threads takes 64 of the 128 key columns; the row maximum and sum cross between them through
+// shared memory), one MMA-issuing warp, one TMA warp.  Tensor memory holds both score tiles and both output
 // accumulators (512 columns), so the tensor pipe alternates between the two query tiles:
 //
 //   tensor pipe:   PV0(j)  S0(j+1)  PV1(j)  S1(j+1)  PV0(j+1) ...
-//   warpgroup 0:   ........softmax of S0(j+1)........
-//   warpgroup 1:   ...softmax of S1(j)....  ........softmax of S1(j+1)...
+//   tile 0 warps:  ........softmax of S0(j+1)........
+//   tile 1 warps:  ...softmax of S1(j)....  ........softmax of S1(j+1)...
 //
 //   S = Q K^T      tcgen05.mma, both operands K-major in shared memory (TMA, 128-byte swizzle)
 //   softmax        tcgen05.ld the row, online max / sum in base 2, P written back over the score
@@ -26,8 +27,8 @@ using namespace attn;
 
 constexpr int KST = 2, VST = 2;                    // ring depths
 constexpr float RESCALE_THRESHOLD = 8.0f;          // in log2 units
-constexpr int EMU = 4;                             // every EMU-th exponential runs on the FMA pipe
-constexpr int FWD_THREADS = 320;
+constexpr int EMU = 1;                             // of every 4 pairs of exponentials, this many run on the FMA pipe
+constexpr int FWD_THREADS = 576;                   // 16 softmax warps, MMA warp, TMA warp
 
 struct FlashParams {
     int B, T, H, KV;
@@ -42,9 +43,22 @@ struct FlashParams {
     int* status;
 };
 
+#ifdef KB_ATTN_PROFILE
+// Phase timing of CTA 0 (clock64 sums), for tuning builds only.
+__device__ long long g_attn_dbg[16];
+#define KB_TICK(i, t0)                                       \
+    if (prof) {                                              \
+        const long long t1_ = clock64();                     \
+        dbg[i] += t1_ - t0;                                  \
+        t0 = t1_;                                            \
+    }
+#else
+#define KB_TICK(i, t0)
+#endif
+
 template <int HD>
 constexpr int fwd_smem_bytes() {
-    return (2 + KST + VST) * Tile<HD>::BYTES + 1024 + 256;
+    return (2 + KST + VST) * Tile<HD>::BYTES + 1024 + 256 + 8 * BT * 4;
 }
 
 template <int HD>
@@ -68,6 +82,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     uint64_t* o_done = p_ready + 2;                // [2]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    // row maxima [parity][tile][half][row] and, at the end, row sums [2 + tile][half][row] of the two
+    // threads that share a query row
+    float* row_buf = reinterpret_cast<float*>(smem + (2 + KST + VST) * TB + 256);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // heavy pairs (late query tiles) first
@@ -97,13 +114,13 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         for (int i = 0; i < VST; ++i) { tc::mbar_init(v_full + i, 1); tc::mbar_init(v_empty + i, 1); }
         for (int i = 0; i < 2; ++i) {
             tc::mbar_init(s_full + i, 1);
-            tc::mbar_init(p_ready + i, 4);
+            tc::mbar_init(p_ready + i, 8);
             tc::mbar_init(o_done + i, 1);
         }
         *abort_flag = 0;
         tc::fence_barrier_init();
     }
-    if (warp == 8) {
+    if (warp == 16) {
         tc::tmem_alloc(tmem_slot, 512);
         tc::tmem_relinquish();
     }
@@ -115,7 +132,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 
     if (n == 0) {
         // nothing to do for this pair (sequence shorter than the grid was sized for)
-    } else if (warp == 9) {
+    } else if (warp == 17) {
         // ------------------------------------------------------------ TMA
         if (lane == 0) {
             tc::prefetch_tmap(&tmQ);
@@ -135,7 +152,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 load_tile<HD>(sV + vs * TB, &tmV, v_full + vs, vx, seq_row0 + j * BT);
             }
         }
-    } else if (warp == 8) {
+    } else if (warp == 16) {
         // ------------------------------------------------------------ MMA issue (one thread)
         if (lane == 0) {
             const uint32_t idesc_s = tc::instr_desc_f16(BT, BT, 1, 1, 0, 0);
@@ -158,14 +175,14 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 if (j < n0) {
                     if (!tc::mbar_wait(p_ready + 0, ph, abort_flag)) { atomicMax(p.status, (int)KB_TIMEOUT_MMA); break; }
                     tc::tc_fence_after();
-                    mma_ts_tile<HD>(tmem0 + 256, tmem0, 32, vj, idesc_o, j != 0);
+                    mma_ts_tile<HD, false>(tmem0 + 256, tmem0, vj, idesc_o, j != 0);
                     tc::tc_commit(o_done + 0);
                     if (j + 1 < n0) { mma_nt_tiles<HD>(tmem0, q_addr, k1, idesc_s); tc::tc_commit(s_full + 0); }
                 }
                 if (j < n1) {
                     if (!tc::mbar_wait(p_ready + 1, ph, abort_flag)) { atomicMax(p.status, (int)KB_TIMEOUT_MMA); break; }
                     tc::tc_fence_after();
-                    mma_ts_tile<HD>(tmem0 + 384, tmem0 + 128, 32, vj, idesc_o, j != 0);
+                    mma_ts_tile<HD, false>(tmem0 + 384, tmem0 + 128, vj, idesc_o, j != 0);
                     tc::tc_commit(o_done + 1);
                     tc::tc_commit(v_empty + vs);
                     if (j + 1 < n1) { mma_nt_tiles<HD>(tmem0 + 128, q_addr + TB, k1, idesc_s); tc::tc_commit(s_full + 1); }
@@ -175,44 +192,60 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 if (j + 1 < n) tc::tc_commit(k_empty + ks1);
             }
         }
-    } else {
-        // ------------------------------------------------------------ softmax: thread = query row
-        const int t = warp >> 2;                                   // which query tile
+    } else if (warp < 16) {
+        // ------------------------------------------------------------ softmax: two threads per query row
+        const int t = warp >> 3;                                   // which query tile
+        const int hf = (warp >> 2) & 1;                            // which 64 of the tile's 128 key columns
         const int qt = t ? qt1 : qt0, nt = t ? n1 : n0;
         const int r = (warp & 3) * 32 + lane;                      // row inside the tile
         const uint32_t lane_base = ((uint32_t)((warp & 3) * 32) << 16);
         const uint32_t tmem_s = tmem0 + t * 128 + lane_base, tmem_o = tmem0 + 256 + t * 128 + lane_base;
         float m_used = -INFINITY, l = 0.f;
         bool ok = true;
+#ifdef KB_ATTN_PROFILE
+        const bool prof = blockIdx.x == 0 && threadIdx.x == 256;     // first row of the second (longer) query tile
+        long long dbg[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        long long tk = clock64();
+#endif
         for (int j = 0; j < nt && ok; ++j) {
             const uint32_t ph = j & 1;
+            KB_TICK(0, tk)                                              // loop overhead / arrive
             if (!tc::mbar_wait(s_full + t, ph, abort_flag)) {
                 if (lane == 0) atomicMax(p.status, (int)KB_TIMEOUT_EPI);
                 ok = false;
                 break;
             }
             tc::tc_fence_after();
-            float s[BT];
-#pragma unroll
-            for (int c = 0; c < BT; c += 32) tc::tmem_ld32(tmem_s + c, reinterpret_cast<uint32_t*>(s + c));
+            float s[64];
+            tc::tmem_ld32(tmem_s + hf * 64, reinterpret_cast<uint32_t*>(s));
+            tc::tmem_ld32(tmem_s + hf * 64 + 32, reinterpret_cast<uint32_t*>(s + 32));
+            KB_TICK(1, tk)                                              // wait for the scores
             tc::tmem_ld_wait();
-            float mx = -INFINITY;
+            KB_TICK(2, tk)                                              // tensor-memory load
             if (j == qt) {                                          // diagonal tile: causal mask
+                const int cmax = r - hf * 64;
 #pragma unroll
-                for (int c = 0; c < BT; ++c) {
-                    s[c] = c <= r ? s[c] : -INFINITY;
-                    mx = fmaxf(mx, s[c]);
-                }
-            } else {
-#pragma unroll
-                for (int c = 0; c < BT; ++c) mx = fmaxf(mx, s[c]);
+                for (int c = 0; c < 64; ++c) s[c] = c <= cmax ? s[c] : -INFINITY;
             }
-            mx *= p.scale_log2;
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};      // four chains: latency, not count, matters here
+#pragma unroll
+            for (int c = 0; c < 64; c += 8) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) mx4[i] = fmax3(mx4[i], s[c + 2 * i], s[c + 2 * i + 1]);
+            }
+            float mx = fmaxf(fmax3(mx4[0], mx4[1], mx4[2]), mx4[3]);
+            // the row maximum spans both halves: exchange through shared memory.  The named barrier
+            // also orders "both halves have read their scores" before either writes P over them.
+            float* mine = row_buf + ((ph * 2 + t) * 2 + hf) * BT + r;
+            *mine = mx;
+            asm volatile("bar.sync %0, 256;" ::"r"(1 + t) : "memory");
+            mx = fmaxf(mx, row_buf[((ph * 2 + t) * 2 + (hf ^ 1)) * BT + r]) * p.scale_log2;
             const bool grow = mx > m_used + RESCALE_THRESHOLD;      // first tile: m_used = -inf -> true
             if (j == 0) {
                 m_used = mx;
             } else if (__any_sync(0xffffffffu, grow)) {
-                // O holds sums of p * v with p relative to m_used: move it to the new maximum
+                // O holds sums of p * v with p relative to m_used: move it to the new maximum.  Both
+                // halves see the same maxima and take the same branch; each rescales half of O's columns.
                 if (!tc::mbar_wait(o_done + t, (j - 1) & 1, abort_flag)) {
                     if (lane == 0) atomicMax(p.status, (int)KB_TIMEOUT_EPI);
                     ok = false;
@@ -222,39 +255,52 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 const float m_new = fmaxf(m_used, mx);
                 const float f = exp2f(m_used - m_new);
 #pragma unroll 1
-                for (int c = 0; c < HD; c += 32) {
+                for (int c = 0; c < HD / 2; c += 32) {
                     uint32_t o[32];
-                    tc::tmem_ld32(tmem_o + c, o);
+                    tc::tmem_ld32(tmem_o + hf * (HD / 2) + c, o);
                     tc::tmem_ld_wait();
 #pragma unroll
                     for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
-                    tc::tmem_st32(tmem_o + c, o);
+                    tc::tmem_st32(tmem_o + hf * (HD / 2) + c, o);
                 }
                 tc::tmem_st_wait();
                 l *= f;
                 m_used = m_new;
             }
-            float sum0 = 0.f, sum1 = 0.f;
+            KB_TICK(3, tk)                                              // max, exchange and rescale check
+            const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), nm2 = make_float2(-m_used, -m_used);
+            float2 sum2 = make_float2(0.f, 0.f);
 #pragma unroll
-            for (int q4 = 0; q4 < 4; ++q4) {                        // 32 scores -> 16 packed columns at a time
+            for (int q4 = 0; q4 < 2; ++q4) {                        // 32 scores -> 16 packed columns at a time
                 uint32_t pk[16];
 #pragma unroll
                 for (int c = 0; c < 32; c += 2) {
-                    const float x0 = fmaf(s[q4 * 32 + c], p.scale_log2, -m_used);
-                    const float x1 = fmaf(s[q4 * 32 + c + 1], p.scale_log2, -m_used);
-                    const float p0 = exp2f(x0);
-                    const float p1 = (EMU > 0 && (c + 1) % (EMU > 0 ? EMU : 1) == EMU - 1) ? exp2_poly(x1) : exp2f(x1);
-                    sum0 += p0;
-                    sum1 += p1;
-                    pk[c >> 1] = pack_bf16(p0, p1);
+                    const float2 x = __ffma2_rn(make_float2(s[q4 * 32 + c], s[q4 * 32 + c + 1]), sc2, nm2);
+                    const float2 e = exp2_pair<EMU>(x, c >> 1);
+                    sum2 = __fadd2_rn(sum2, e);
+                    pk[c >> 1] = pack_bf16(e.x, e.y);
                 }
-                tc::tmem_st16(tmem_s + q4 * 16, pk);
+                tc::tmem_st16(tmem_s + hf * 32 + q4 * 16, pk);
             }
-            l += sum0 + sum1;
+            l += sum2.x + sum2.y;
+            KB_TICK(4, tk)                                              // exponentials, packing, store issue
             tc::tmem_st_wait();
             tc::tc_fence_before();
             __syncwarp();
             if (lane == 0) tc::mbar_arrive(p_ready + t);
+            KB_TICK(5, tk)                                              // store wait, fence, arrive
+        }
+#ifdef KB_ATTN_PROFILE
+        if (prof) {
+            for (int i = 0; i < 6; ++i) g_attn_dbg[i] = dbg[i];
+            g_attn_dbg[6] = nt;
+        }
+#endif
+        if (nt > 0) {
+            // the row sum spans both halves too (every thread of the tile takes part in the barrier)
+            row_buf[((2 + t) * 2 + hf) * BT + r] = l;
+            asm volatile("bar.sync %0, 256;" ::"r"(1 + t) : "memory");
+            l += row_buf[((2 + t) * 2 + (hf ^ 1)) * BT + r];
         }
         if (ok && nt > 0) {
             if (tc::mbar_wait(o_done + t, (nt - 1) & 1, abort_flag)) {
@@ -264,11 +310,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 // sequence) are computed but never stored; for the valid rows the causal mask already
                 // excludes every key at or beyond the end.
                 const bool valid = qt * BT + r < Tb;
-                __nv_bfloat16* dst = p.out + (size_t)(seq_row0 + qt * BT + r) * p.out_stride + head * HD;
+                __nv_bfloat16* dst = p.out + (size_t)(seq_row0 + qt * BT + r) * p.out_stride + head * HD + hf * (HD / 2);
 #pragma unroll 1
-                for (int c = 0; c < HD; c += 32) {
+                for (int c = 0; c < HD / 2; c += 32) {
                     uint32_t o[32];
-                    tc::tmem_ld32(tmem_o + c, o);
+                    tc::tmem_ld32(tmem_o + hf * (HD / 2) + c, o);
                     tc::tmem_ld_wait();
                     if (valid) {
 #pragma unroll
@@ -280,7 +326,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                         }
                     }
                 }
-                if (valid) {
+                if (valid && hf == 0) {
                     const long long base = p.cu_seqlens ? (long long)seq_row0 : (long long)b * p.lse_bs;
                     p.lse[(long long)head * p.lse_hs + base + qt * BT + r] = (m_used + log2f(l)) * LN2;
                 }
@@ -291,7 +337,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
     tc::tc_fence_before();
     __syncthreads();
-    if (warp == 8) {
+    if (warp == 16) {
         tc::tc_fence_after();
         tc::tmem_dealloc(tmem0, 512);
     }
@@ -322,6 +368,12 @@ int launch_fwd(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap
 }
 
 }  // namespace
+
+#ifdef KB_ATTN_PROFILE
+KB_API int kb_attn_dbg_read(long long* host16) {
+    return cudaMemcpyFromSymbol(host16, g_attn_dbg, sizeof(long long) * 16) == cudaSuccess ? 0 : 1;
+}
+#endif
 
 // q/k/v: token-major matrices [total tokens, *] whose rows hold the heads side by side (row strides
 // in elements; *_col0 = column of head 0).  out: token-major with `out_stride` elements per token.

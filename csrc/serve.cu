@@ -585,9 +585,14 @@ paged_decode_bulk_kernel(const bf16* __restrict__ q, long long q_stride, const b
         part_ml[(pbase * G + g) * 2 + 1] = sum;
     }
 }
+// Reads the decode status word and clears it, so that one timeout is reported once.
 KB_API int kb_decode_status() {
     int v = 0;
-    cudaMemcpyFromSymbol(&v, g_decode_status, sizeof(int));
+    if (cudaMemcpyFromSymbol(&v, g_decode_status, sizeof(int)) != cudaSuccess) return -1;
+    if (v != 0) {
+        const int zero = 0;
+        cudaMemcpyToSymbol(g_decode_status, &zero, sizeof(int));
+    }
     return v;
 }
 

@@ -188,7 +188,11 @@ FLAG_TABLE: list[tuple[str, dict[str, Any]]] = [
     _f("backend", "auto", str, choices=["auto", "nccl", "gloo", "native"],
        help="'native' = in-kernel NVLink collectives; 'nccl'/'gloo' = library collectives"),
     _f("dtype", "bf16", str, choices=["bf16", "fp32"]),
-    _f("sequence_parallel", flag=True), _f("distributed_muon", flag=True),
+    _f("sequence_parallel", flag=True),
+    _f("distributed_muon", flag=True, help="each Muon matrix is orthogonalised by one owner rank (the default)"),
+    _f("no_distributed_muon", flag=True, help="repeat Newton-Schulz on every rank, as the reference does"),
+    _f("halt_on_nonfinite", flag=True, help="stop the run (all ranks) when the loss or gradient norm is not finite"),
+    _f("watchdog_s", 0.0, float, help="log which rank and phase stalled when a step phase exceeds this many seconds (0: off)"),
     _f("fp8_recipe", "block128", str, choices=["tensorwise", "block128"]),
     _f("reference_lr_order", flag=True,
        help="apply the schedule after the optimizer step (step 0 at full LR, step 1 at LR 0)"),

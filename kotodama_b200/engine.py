@@ -21,6 +21,8 @@ global-norm clip before both optimizers, Muon then AdamW) and the model
 """
 from __future__ import annotations
 
+import os
+
 import math
 from dataclasses import dataclass, field
 from typing import Any, Optional
@@ -245,6 +247,9 @@ class TrainEngine:
         self._wcache: dict[str, torch.Tensor] = {}
         self._gather_weights()
         self.refresh_fp8()
+        # AttnRes routing in blocked form for every block with at least this many committed sources
+        self.route_block_min = int(os.environ.get("KOTODAMA_ROUTE_BLOCK_MIN", "2"))
+        self._route_plan, self._route_groups = self._make_route_plan()
 
     @classmethod
     def from_meta(cls, model: KotodamaModel, cfg: ModelConfig, *, seed: int = 0, **kw: Any) -> "TrainEngine":
@@ -315,6 +320,111 @@ class TrainEngine:
         else:
             g.add_(val.view(g.shape).to(g.dtype))
 
+    # ------------------------------------------------------------ AttnRes routing schedule
+    def _route_names(self, j: int) -> tuple[str, str, str]:
+        """Parameter names (pseudo-query, key-norm weight, following RMSNorm weight) of routing call
+        ``j``: ``2i`` before the attention of layer ``i``, ``2i + 1`` before its MLP, ``2L`` at the output."""
+        if j == 2 * self.cfg.num_layers:
+            return "final_res_query", "final_res_norm.weight", "norm.weight"
+        p = f"layers.{j // 2}."
+        if j % 2 == 0:
+            return p + "attn_res_query", p + "attn_res_norm.weight", p + "attn_norm.weight"
+        return p + "mlp_res_query", p + "mlp_res_norm.weight", p + "ffn_norm.weight"
+
+    def _make_route_plan(self):
+        """Groups the routing calls by the set of committed sources they see.  A group starts at the
+        pre-attention call of a boundary layer (which sees the finished block as its last source,
+        i.e. exactly the committed set of the calls that follow) and runs to the call before the next
+        boundary.  Groups with at least ``route_block_min`` committed sources run in blocked form: one
+        phase-1 pass for all their queries, then one phase-2 merge per call
+        (reference: serve.py:113-164)."""
+        cfg = self.cfg
+        plan: dict[int, tuple[int, int]] = {}
+        groups: list[dict] = []
+        if not cfg.attn_res or self.route_block_min <= 0:
+            return plan, groups
+        bset = self.model._attn_res_boundary_set
+        committed, cur = 0, None
+        for j in range(2 * cfg.num_layers + 1):
+            if j % 2 == 0 and j // 2 in bset and j < 2 * cfg.num_layers:
+                committed += 1
+                cur = None
+                if committed >= self.route_block_min and self.ops.route_blocked_ok(committed, cfg.hidden_size):
+                    cur = dict(S=committed, members=[])
+                    groups.append(cur)
+            if cur is not None:
+                plan[j] = (len(groups) - 1, len(cur["members"]))
+                cur["members"].append(j)
+        return plan, groups
+
+    def _route_fwd(self, j: int, srcs: list, fw: dict):
+        """Routing call ``j`` over ``srcs`` (committed sources, then the partial sum) fused with the
+        RMSNorm that follows.  Returns the normalised activations and what the backward needs."""
+        ops, eps = self.ops, self.cfg.norm_eps
+        qn, rn, nn_ = self._route_names(j)
+        attn_res = self.cfg.attn_res
+        q = self._p(qn) if attn_res else None
+        rnw = self._p(rn) if attn_res else None
+        ent = self._route_plan.get(j)
+        if ent is None:
+            xn, stats = ops.route_norm_fwd(srcs, q, rnw, self._p(nn_), eps)
+            return xn, ("plain", stats)
+        gid, k = ent
+        grp = self._route_groups[gid]
+        if k == 0:
+            assert len(srcs) == grp["S"]
+            names = [self._route_names(m) for m in grp["members"]]
+            qs = torch.stack([self._p(n[0]) for n in names])
+            rns = torch.stack([self._p(n[1]) for n in names])
+            o, lse, st = ops.route_p1_fwd(srcs, qs, rns, eps)
+            fw[gid] = dict(o=o, lse=lse, stats=st, srcs=list(srcs), qs=qs, rns=rns, dw2={})
+            partial = None
+        else:
+            assert len(srcs) == grp["S"] + 1
+            partial = srcs[-1]
+        g = fw[gid]
+        xn, st2 = ops.route_p2_fwd(g["o"][k], g["lse"][k], partial, q, rnw, self._p(nn_), eps)
+        return xn, ("blocked", gid, k, partial, st2)
+
+    def _route_bwd(self, j: int, dxn: torch.Tensor, srcs: list, saved, fw: dict, dsrc_list) -> None:
+        """Backward of :meth:`_route_fwd`: source gradients are written or accumulated in place,
+        parameter gradients go to the arena."""
+        ops, eps = self.ops, self.cfg.norm_eps
+        qn, rn, nn_ = self._route_names(j)
+        attn_res = self.cfg.attn_res
+        q = self._p(qn) if attn_res else None
+        rnw = self._p(rn) if attn_res else None
+        if saved[0] == "plain":
+            ds, acc = dsrc_list(srcs)
+            dq, drn, dnw = ops.route_norm_bwd(dxn, srcs, q, rnw, self._p(nn_), eps, saved[1], ds, acc)
+            self._acc_small(nn_, dnw)
+            if attn_res:
+                self._acc_small(qn, dq)
+                self._acc_small(rn, drn)
+            return
+        _, gid, k, partial, st2 = saved
+        g = fw[gid]
+        if "do" not in g:
+            g["do"] = torch.empty_like(g["o"])
+            g["dlse"] = torch.empty_like(g["lse"])
+        dpart, pacc = None, False
+        if partial is not None:
+            (dpart,), (pacc,) = dsrc_list([partial])
+        dw2, dnw = ops.route_p2_bwd(dxn, g["o"][k], g["lse"][k], partial, q, rnw, self._p(nn_), eps, st2,
+                                    g["do"][k], g["dlse"][k], dpart, pacc)
+        self._acc_small(nn_, dnw)
+        g["dw2"][k] = dw2
+        if k != 0:
+            return
+        ds, acc = dsrc_list(g["srcs"])
+        dws = ops.route_p1_bwd(g["srcs"], g["qs"], g["rns"], g["do"], g["dlse"], g["lse"], g["stats"], ds, acc)
+        for mk, m in enumerate(self._route_groups[gid]["members"]):
+            dw = dws[mk] if g["dw2"].get(mk) is None else dws[mk] + g["dw2"][mk]
+            mq, mr, _ = self._route_names(m)
+            self._acc_small(mq, dw * self._p(mr).float())
+            self._acc_small(mr, dw * self._p(mq).float())
+        fw.pop(gid)
+
     # ------------------------------------------------------------ forward
     @torch.no_grad()
     def forward_backward(self, input_ids: torch.Tensor, loss_scale: float = 1.0, first_micro: bool = True,
@@ -339,7 +449,7 @@ class TrainEngine:
         cos, sin = self.model.rope_cos, self.model.rope_sin
         attn_res = cfg.attn_res
         bset = self.model._attn_res_boundary_set if attn_res else frozenset()
-        qw = lambda n: self._p(n) if attn_res else None
+        fw: dict = {}                                               # blocked routing groups in flight
 
         embed = ops.embedding_fwd(ids, wemb)
         committed: list[torch.Tensor] = []
@@ -350,8 +460,7 @@ class TrainEngine:
             p = f"layers.{i}."
             r = _LayerRec()
             r.srcs1 = committed + [partial]
-            r.xn1, r.stats1 = ops.route_norm_fwd(r.srcs1, qw(p + "attn_res_query"), qw(p + "attn_res_norm.weight"),
-                                                 self._p(p + "attn_norm.weight"), eps)
+            r.xn1, r.stats1 = self._route_fwd(2 * i, r.srcs1, fw)
             if i in bset:
                 committed = committed + [partial]
                 partial = None
@@ -368,8 +477,7 @@ class TrainEngine:
             partial = self.comm.row_linear(ops, r.attn_o.view(Nq, H * hd), lw["wo"], residual=partial)
             r.part_after_attn = partial
             r.srcs2 = committed + [partial]
-            r.xn2, r.stats2 = ops.route_norm_fwd(r.srcs2, qw(p + "mlp_res_query"), qw(p + "mlp_res_norm.weight"),
-                                                 self._p(p + "ffn_norm.weight"), eps)
+            r.xn2, r.stats2 = self._route_fwd(2 * i + 1, r.srcs2, fw)
             r.gu = self.comm.col_linear(ops, r.xn2, lw["wgu"])
             r.act = ops.swiglu_fwd(r.gu)
             partial = self.comm.row_linear(ops, r.act, lw["wd"], residual=partial)
@@ -378,8 +486,7 @@ class TrainEngine:
                 r = _LayerRec()
             recs.append(r)
         fsrcs = committed + [partial]
-        xf, fstats = ops.route_norm_fwd(fsrcs, qw("final_res_query"), qw("final_res_norm.weight"),
-                                        self._p("norm.weight"), eps)
+        xf, fstats = self._route_fwd(2 * cfg.num_layers, fsrcs, fw)
         wl = self.model.get_lm_head_weight()
         g_wl = self._g("embed_tokens.weight") if self.model.lm_head is None else self._g("lm_head.weight")
         ce, zl, dxf = ops.linear_ce(xf, wl, labels, cfg.z_loss_weight, loss_scale,
@@ -409,13 +516,7 @@ class TrainEngine:
                     out.append(g); acc.append(False)
             return out, acc
 
-        ds, acc = dsrc_list(fsrcs)
-        dq, drn, dnw = ops.route_norm_bwd(dxf, fsrcs, qw("final_res_query"), qw("final_res_norm.weight"),
-                                          self._p("norm.weight"), eps, fstats, ds, acc)
-        self._acc_small("norm.weight", dnw)
-        if attn_res:
-            self._acc_small("final_res_query", dq)
-            self._acc_small("final_res_norm.weight", drn)
+        self._route_bwd(2 * cfg.num_layers, dxf, fsrcs, fstats, fw, dsrc_list)
         del dxf, xf
         for i in reversed(range(cfg.num_layers)):
             lw, r, p = self.layer_w[i], recs[i], f"layers.{i}."
@@ -427,13 +528,7 @@ class TrainEngine:
             dxn2 = self.comm.col_linear_bwd(ops, dgu, lw["wgu"], r.xn2, lw["g_wgu"], not first_micro)
             del dgu
             grads[id(r.part_after_attn)] = dP                      # residual add: gradient passes through
-            ds, acc = dsrc_list(r.srcs2)
-            dq, drn, dnw = ops.route_norm_bwd(dxn2, r.srcs2, qw(p + "mlp_res_query"), qw(p + "mlp_res_norm.weight"),
-                                              self._p(p + "ffn_norm.weight"), eps, r.stats2, ds, acc)
-            self._acc_small(p + "ffn_norm.weight", dnw)
-            if attn_res:
-                self._acc_small(p + "mlp_res_query", dq)
-                self._acc_small(p + "mlp_res_norm.weight", drn)
+            self._route_bwd(2 * i + 1, dxn2, r.srcs2, r.stats2, fw, dsrc_list)
             del dxn2
             # ---- attention sub-layer
             dP = grads[id(r.part_after_attn)]
@@ -459,13 +554,7 @@ class TrainEngine:
             del dqkv
             if r.part_before_attn is not None:
                 grads[id(r.part_before_attn)] = dP
-            ds, acc = dsrc_list(r.srcs1)
-            dq, drn, dnw = ops.route_norm_bwd(dxn1, r.srcs1, qw(p + "attn_res_query"), qw(p + "attn_res_norm.weight"),
-                                              self._p(p + "attn_norm.weight"), eps, r.stats1, ds, acc)
-            self._acc_small(p + "attn_norm.weight", dnw)
-            if attn_res:
-                self._acc_small(p + "attn_res_query", dq)
-                self._acc_small(p + "attn_res_norm.weight", drn)
+            self._route_bwd(2 * i, dxn1, r.srcs1, r.stats1, fw, dsrc_list)
             del dxn1
             recs[i] = None  # free activations of this layer
             if last_micro:

@@ -54,7 +54,8 @@ class CudaOps(TorchOps):
         self._splitk_ws: dict = {}
         self.attention_library_calls = 0   # stays 0: attention runs on the native kernels in both directions
         self.gemm_2cta = os.environ.get("KOTODAMA_GEMM_2CTA", "1") == "1"   # CTA-pair kernel for large products
-        for name in ("kb_route_bwd_grid", "kb_qknorm_grid_warps", "kb_route_pipe_grid"):
+        for name in ("kb_route_bwd_grid", "kb_qknorm_grid_warps", "kb_route_pipe_grid", "kb_route_blocked_ok",
+                     "kb_route_blocked_grid"):
             getattr(self.lib, name).restype = _I
 
     # ------------------------------------------------------------------ utils
@@ -285,6 +286,80 @@ class CudaOps(TorchOps):
             return None, None, dn_w
         dw = self._colsum(dw_part)
         return dw * rn_w.float(), dw * q.float(), dn_w
+
+    # ------------------------------------------------------------------ AttnRes route, blocked form
+    def route_blocked_ok(self, S: int, D: int) -> bool:
+        return bool(self.lib.kb_route_blocked_ok(_I(S), _I(D)))
+
+    def _fold_w(self, q: torch.Tensor, rn_w: torch.Tensor) -> torch.Tensor:
+        w = torch.empty(q.shape, device=q.device, dtype=torch.float32)
+        self._call("kb_route_fold_w", _p(q.contiguous()), _p(rn_w.contiguous()), _p(w), _I(q.numel()), _st())
+        return w
+
+    @staticmethod
+    def _p1_chunk(S: int, D: int) -> int:
+        """Queries per phase-1 launch: 8, or 4 where two backward ring stages of 8 would not fit."""
+        return 8 if 2 * (S + 8) * (2 * D + 16) <= 220 * 1024 else 4
+
+    def route_p1_fwd(self, srcs, qs, rn_ws, eps):
+        S, Q = len(srcs), qs.shape[0]
+        N, D = srcs[0].shape
+        dev = srcs[0].device
+        wf = self._fold_w(qs, rn_ws)
+        o = torch.empty(Q, N, D, device=dev, dtype=torch.bfloat16)
+        lse = torch.empty(Q, N, device=dev, dtype=torch.float32)
+        r = torch.empty(N, S, device=dev, dtype=torch.float32)
+        logit = torch.empty(Q, N, S, device=dev, dtype=torch.float32)
+        arr = (_VP * S)(*[t.data_ptr() for t in srcs])
+        qc = self._p1_chunk(S, D)
+        for q0 in range(0, Q, qc):
+            n = min(qc, Q - q0)
+            self._call("kb_route_p1_fwd", arr, _I(S), _I(n), _p(wf[q0:]), _p(o[q0:]), _p(lse[q0:]), _p(r),
+                       _p(logit[q0:]), _I(N), _I(D), _F(eps), _p(self.status(dev)), _st())
+        return o, lse, (r, logit, wf)
+
+    def route_p2_fwd(self, o, lse, partial, q, rn_w, n_w, eps):
+        N, D = o.shape
+        xn = torch.empty(N, D, device=o.device, dtype=torch.bfloat16)
+        stats2 = torch.empty(N, 4, device=o.device, dtype=torch.float32)
+        w = self._fold_w(q, rn_w) if partial is not None else None
+        self._call("kb_route_p2_fwd", _p(o), _p(lse), _p(partial), _p(w), _p(n_w), _p(xn), _p(stats2), _I(N), _I(D),
+                   _F(eps), _st())
+        return xn, (stats2, w)
+
+    def route_p2_bwd(self, dxn, o, lse, partial, q, rn_w, n_w, eps, stats2, do_out, dlse_out, dpart, dpart_acc):
+        stats2, w = stats2
+        N, D = o.shape
+        dev = o.device
+        grid = self.lib.kb_route_blocked_grid(_I(N), _I(2))
+        dnw_part = torch.empty(grid, D, device=dev, dtype=torch.float32)
+        dw_part = torch.empty(grid, D, device=dev, dtype=torch.float32) if partial is not None else None
+        self._call("kb_route_p2_bwd", _p(dxn), _p(o), _p(partial), _p(w), _p(n_w), _p(stats2), _p(do_out), _p(dlse_out),
+                   _p(dpart), _I(1 if dpart_acc else 0), _p(dw_part), _p(dnw_part), _I(N), _I(D), _p(self.status(dev)),
+                   _st())
+        dn_w = self._colsum(dnw_part)
+        return (self._colsum(dw_part) if partial is not None else None), dn_w
+
+    def route_p1_bwd(self, srcs, qs, rn_ws, do, dlse, lse, stats, dsrcs, acc):
+        r, logit, wf = stats
+        S, Q = len(srcs), qs.shape[0]
+        N, D = srcs[0].shape
+        dev = srcs[0].device
+        grid = self.lib.kb_route_blocked_grid(_I(N), _I(1))
+        sa = (_VP * S)(*[t.data_ptr() for t in srcs])
+        da = (_VP * S)(*[t.data_ptr() for t in dsrcs])
+        mask = sum(1 << i for i, a in enumerate(acc) if a)
+        dws = torch.empty(Q, D, device=dev, dtype=torch.float32)
+        qc = self._p1_chunk(S, D)
+        for q0 in range(0, Q, qc):
+            n = min(qc, Q - q0)
+            part = torch.empty(grid, n * D, device=dev, dtype=torch.float32)
+            self._call("kb_route_p1_bwd", sa, da, ctypes.c_uint(mask), _I(S), _I(n), _p(wf[q0:]), _p(do[q0:]),
+                       _p(dlse[q0:]), _p(lse[q0:]), _p(r), _p(logit[q0:]), _p(part), _I(N), _I(D), _p(self.status(dev)),
+                       _st())
+            dws[q0:q0 + n] = self._colsum(part).view(n, D)
+            mask = (1 << S) - 1                     # later query chunks add to what the first one wrote
+        return dws
 
     def _colsum(self, part: torch.Tensor) -> torch.Tensor:
         out = torch.empty(part.shape[1], device=part.device, dtype=torch.float32)

@@ -220,6 +220,108 @@ class TorchOps:
                 dsrcs[j].copy_(du[:, j])
         return dq, drn, dn_w
 
+    # --------------------------------------------------- AttnRes route, blocked form
+    # One phase-1 pass over the committed sources serves every sub-layer query of a block; each
+    # sub-layer then merges its own partial sum with a phase-2 step fused with the RMSNorm that
+    # follows (reference: serve.py:113-164, kernels/phase_1.py:59-101, kernels/phase_2.py:9-57).
+    def route_blocked_ok(self, S: int, D: int) -> bool:
+        """Whether the blocked kernels cover ``S`` committed sources of width ``D`` (always, here)."""
+        return True
+
+    def route_p1_fwd(self, srcs: Sequence[torch.Tensor], qs: torch.Tensor, rn_ws: torch.Tensor, eps: float):
+        """Phase 1 for ``Q`` queries at once.  ``srcs``: S committed sources ``[N,D]``; ``qs``/``rn_ws``
+        ``[Q,D]`` pseudo-queries and key-norm weights.  Returns ``o[Q,N,D]`` (source dtype),
+        ``lse[Q,N]`` fp32 and ``stats = (r[N,S], logit[Q,N,S])``."""
+        u = torch.stack([_f(s) for s in srcs], 1)                       # [N,S,D]
+        w = _f(qs) * _f(rn_ws)                                          # [Q,D]
+        r = torch.rsqrt(u.pow(2).mean(-1) + eps)                        # [N,S]
+        logit = torch.einsum("nsd,qd->qns", u, w) * r
+        lse = torch.logsumexp(logit, -1)
+        o = torch.einsum("qns,nsd->qnd", torch.softmax(logit, -1), u)
+        return o.to(srcs[0].dtype), lse, (r, logit)
+
+    def route_p2_fwd(self, o: torch.Tensor, lse: torch.Tensor, partial: Optional[torch.Tensor], q: torch.Tensor,
+                     rn_w: torch.Tensor, n_w: torch.Tensor, eps: float):
+        """Phase 2 + RMSNorm: merges the partial sum into one query's phase-1 result
+        (``pi = sigmoid(l_p - lse)``, ``h = o + pi (p - o)``; ``partial`` None: ``h = o``) and normalises.
+        Returns ``xn[N,D]`` and ``stats2[N,4]`` = (pi, l_p, r_p, rstd) fp32."""
+        of = _f(o)
+        n, d = of.shape
+        if partial is None:
+            pi = lp = rp = torch.zeros(n, dtype=of.dtype, device=of.device)
+            h = of
+        else:
+            pf = _f(partial)
+            w = _f(q) * _f(rn_w)
+            rp = torch.rsqrt(pf.pow(2).mean(-1) + eps)
+            lp = (pf * w).sum(-1) * rp
+            pi = torch.sigmoid(lp - lse)
+            h = of + pi.unsqueeze(-1) * (pf - of)
+        rstd = torch.rsqrt(h.pow(2).mean(-1) + eps)
+        xn = (h * rstd.unsqueeze(-1) * _f(n_w)).to(o.dtype)
+        return xn, torch.stack([pi, lp, rp, rstd], 1)
+
+    def route_p2_bwd(self, dxn: torch.Tensor, o: torch.Tensor, lse: torch.Tensor, partial: Optional[torch.Tensor],
+                     q: torch.Tensor, rn_w: torch.Tensor, n_w: torch.Tensor, eps: float, stats2: torch.Tensor,
+                     do_out: torch.Tensor, dlse_out: torch.Tensor, dpart: Optional[torch.Tensor], dpart_acc: bool):
+        """Backward of :meth:`route_p2_fwd`: writes ``do_out[N,D]`` and ``dlse_out[N]``, writes or
+        accumulates the partial's gradient into ``dpart`` and returns fp32 ``(dw, dn_w)`` where ``dw``
+        is the gradient of ``q * rn_w`` (None without a partial)."""
+        of, g = _f(o), _f(dxn)
+        d = of.shape[1]
+        pi, lp, rp, rstd = stats2.unbind(1)
+        if partial is None:
+            h = of
+        else:
+            pf = _f(partial)
+            h = of + pi.unsqueeze(-1) * (pf - of)
+        hn = h * rstd.unsqueeze(-1)
+        dn_w = (g * hn).sum(0)
+        gw = g * _f(n_w)
+        dh = rstd.unsqueeze(-1) * (gw - hn * (gw * hn).mean(-1, keepdim=True))
+        if partial is None:
+            do_out.copy_(dh)
+            dlse_out.zero_()
+            return None, dn_w
+        w = _f(q) * _f(rn_w)
+        c = (dh * (of - pf)).sum(-1)
+        dlse = pi * (1 - pi) * c
+        dlp = -dlse
+        dp = pi.unsqueeze(-1) * dh + dlp.unsqueeze(-1) * (rp.unsqueeze(-1) * w - (lp * rp * rp / d).unsqueeze(-1) * pf)
+        dw = ((dlp * rp).unsqueeze(-1) * pf).sum(0)
+        do_out.copy_((1 - pi).unsqueeze(-1) * dh)
+        dlse_out.copy_(dlse)
+        if dpart_acc:
+            dpart.add_(dp.to(dpart.dtype))
+        else:
+            dpart.copy_(dp)
+        return dw, dn_w
+
+    def route_p1_bwd(self, srcs: Sequence[torch.Tensor], qs: torch.Tensor, rn_ws: torch.Tensor, do: torch.Tensor,
+                     dlse: torch.Tensor, lse: torch.Tensor, stats, dsrcs: Sequence[torch.Tensor],
+                     acc: Sequence[bool]) -> torch.Tensor:
+        """Backward of :meth:`route_p1_fwd` for all ``Q`` queries at once: writes or accumulates the
+        source gradients and returns ``dws[Q,D]`` fp32, the gradients of ``qs * rn_ws``
+        (reference: kernels/phase_1.py:204-274)."""
+        r, logit = stats
+        u = torch.stack([_f(s) for s in srcs], 1)                       # [N,S,D]
+        d = u.shape[-1]
+        w = _f(qs) * _f(rn_ws)
+        g = _f(do)                                                      # [Q,N,D]
+        pr = torch.exp(logit - lse.unsqueeze(-1))                       # [Q,N,S]
+        a = torch.einsum("qnd,nsd->qns", g, u)
+        abar = (pr * a).sum(-1, keepdim=True)
+        dl = pr * (dlse.unsqueeze(-1) + a - abar)
+        du = (torch.einsum("qns,qnd->nsd", pr, g) + torch.einsum("qns,qd->nsd", dl * r, w)
+              - ((dl * logit).sum(0) * r * r / d).unsqueeze(-1) * u)
+        dws = torch.einsum("qns,nsd->qd", dl * r, u)
+        for j in range(len(srcs)):
+            if acc[j]:
+                dsrcs[j].add_(du[:, j].to(dsrcs[j].dtype))
+            else:
+                dsrcs[j].copy_(du[:, j])
+        return dws
+
     # ------------------------------------------------------ QK-norm + RoPE
     def qknorm_rope_fwd(self, qkv: torch.Tensor, qw: Optional[torch.Tensor], kw: Optional[torch.Tensor],
                         cos: torch.Tensor, sin: torch.Tensor, seq_len: int, n_q: int, n_kv: int, hd: int,

@@ -1,9 +1,13 @@
 """Parallelism: communication strategies, process groups, tensor parallelism."""
 from __future__ import annotations
 
+import logging
+
 import torch.distributed as dist
 
 from .comm import LibraryComm, LocalComm
+
+logger = logging.getLogger(__name__)
 
 
 def make_comm(backend: str = "auto", world: int | None = None, distributed_muon: bool = True):
@@ -16,10 +20,14 @@ def make_comm(backend: str = "auto", world: int | None = None, distributed_muon:
     if backend in ("auto", "native"):
         try:
             from .native import NativeComm
-            return NativeComm(distributed_muon=distributed_muon)
-        except Exception:
+            comm = NativeComm(distributed_muon=distributed_muon)
+            logger.warning("communication: in-kernel NVLink collectives (NativeComm)")
+            return comm
+        except Exception as e:
             if backend == "native":
                 raise
+            logger.warning("communication: in-kernel collectives unavailable (%s: %s); "
+                           "falling back to library collectives (LibraryComm)", type(e).__name__, e)
     return LibraryComm(distributed_muon=distributed_muon)
 
 

@@ -155,7 +155,10 @@ def train(args: argparse.Namespace) -> dict[str, Any]:
         backend = args.backend
         if device_kind == "cpu" or backend in ("gloo", "nccl"):
             backend = "library"
-        comm = make_comm("nccl" if backend == "library" else backend, world, distributed_muon=True)
+        comm = make_comm("nccl" if backend == "library" else backend, world,
+                         distributed_muon=not args.no_distributed_muon)
+        if is_main:
+            logger.info("Data parallelism: %s", type(comm).__name__)
     kw = dict(device=device, dtype=dtype, comm=comm, muon_lr=args.muon_lr, muon_momentum=args.muon_momentum,
               muon_weight_decay=args.muon_weight_decay, muon_ns_iterations=args.muon_ns_iterations,
               muon_ns_coefficients=args.muon_ns_coefficients, adamw_lr=args.adamw_lr,
@@ -216,7 +219,9 @@ def train(args: argparse.Namespace) -> dict[str, Any]:
         from .monitor.geometric import GeometricMonitor, MonitorConfig
         monitor = GeometricMonitor(model, MonitorConfig(tier1_every=args.geo_monitor_tier1_every,
                                                         tier2_every=args.geo_monitor_tier2_every))
-        probe_ds = RandomTokenDataset(cfg.vocab_size, seq_len, seed=args.seed + 1, rank=0) if args.random_data else dataset
+        # a dataset instance of its own: drawing the probe batch must not advance the training stream
+        probe_ds = (RandomTokenDataset(cfg.vocab_size, seq_len, seed=args.seed + 1, rank=0) if args.random_data
+                    else TokenizedDataset(args.data_path, seq_len, rank=0, world_size=1, seed=args.seed + 1))
         it = iter(probe_ds)
         monitor.set_probe_batch(torch.stack([next(it) for _ in range(min(monitor.config.tier1_probe_size, 64))]))
     wb: Optional[WandbLogger] = None
@@ -233,7 +238,9 @@ def train(args: argparse.Namespace) -> dict[str, Any]:
                                  "parallelism": f"tp{tp_size}" if tp_size > 1 else "ddp", "tp_size": tp_size,
                                  "dp_size": dp_size})
     from .monitor.profiler import StepProfiler
+    from .monitor.watchdog import StepWatchdog
     profiler = StepProfiler(args, enabled=is_main and args.profile)
+    watchdog = StepWatchdog(args.watchdog_s, rank=rank)
 
     # -- loop --------------------------------------------------------------------
     if is_main:
@@ -249,20 +256,25 @@ def train(args: argparse.Namespace) -> dict[str, Any]:
         if not args.reference_lr_order:
             scheduler.step(step)
         ga = grad_accum_for_step(step, total_steps, grad_accum, args.batch_ramp_initial, args.batch_ramp_pct)
+        watchdog.phase(step, "data")
         micro = [next(batches) for _ in range(ga)]
         if device_kind == "cuda":
             ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             ev0.record()
+        watchdog.phase(step, "train_step")
         res = engine.train_step(micro, keep_grads=wb is not None and step % 50 == 0)
         if device_kind == "cuda":
             ev1.record()
-        step_loss = float(res["loss"].item())            # the one device->host sync of the step
-        step_z = float(res["z_loss"].item())
-        grad_norm = float(res["grad_norm"].item())
+        watchdog.phase(step, "loss_readback")
+        # the one device->host sync of the step: loss, z-loss and gradient norm in one read
+        step_loss, step_z, grad_norm = torch.stack([res["loss"].reshape(()).float(), res["z_loss"].reshape(()).float(),
+                                                    res["grad_norm"].reshape(()).float()]).tolist()
         if device_kind == "cuda":
             dev_ms_acc += ev0.elapsed_time(ev1)
-        if not math.isfinite(step_loss) or not math.isfinite(grad_norm):
+        finite = math.isfinite(step_loss) and math.isfinite(grad_norm)
+        if not finite:
             logger.error("Non-finite loss/grad-norm at step %d (loss=%s grad_norm=%s)", step, step_loss, grad_norm)
+        watchdog.phase(step, "bookkeeping")
         if wb is not None and step % 50 == 0:
             wb.log_custom(step, per_layer_grad_norms(model))
         if args.reference_lr_order:
@@ -307,11 +319,31 @@ def train(args: argparse.Namespace) -> dict[str, Any]:
             wb.commit(step)
         profiler.step_end(step)
         data_state = dataset.state_dict() if hasattr(dataset, "state_dict") else None
-        if step > 0 and args.save_every > 0 and step % args.save_every == 0:
+        want_save = step > 0 and args.save_every > 0 and step % args.save_every == 0
+        # Health of the step, agreed by all ranks in the one host collective the loop has anyway.  The
+        # bounded-wait status word (a kernel gave up on a peer flag or a copy and returned with partial
+        # output) is read at every log interval and before anything is written to a checkpoint.
+        fault = ""
+        if want_save or sigterm.received or step % args.log_every == 0 or step == total_steps - 1:
+            try:
+                engine.check()
+            except Exception as e:                                 # noqa: BLE001 - reported on every rank below
+                fault = f"{type(e).__name__}: {e}"
+        if args.halt_on_nonfinite and not finite:
+            fault = fault or f"non-finite loss/grad-norm at step {step}"
+        watchdog.phase(step, "health_allreduce")
+        code = comm.all_reduce_max(2.0 if fault else (1.0 if sigterm.received else 0.0))
+        if code > 1.5:
+            ckpt.shutdown()
+            watchdog.stop()
+            raise RuntimeError(f"rank {rank}: training stopped at step {step}: " + (fault or "a peer rank reported a fault"))
+        if want_save:
+            watchdog.phase(step, "checkpoint")
             ckpt.save(step, model, muon_opt, adamw_opt, scheduler, tokens_consumed, data_state)
-        if _sigterm_any(sigterm.received, comm):
+        if code > 0.5:
             if is_main:
                 logger.info("SIGTERM exit: saving checkpoint at step %d", step)
+            watchdog.phase(step, "checkpoint")
             ckpt.save_blocking(step, model, muon_opt, adamw_opt, scheduler, tokens_consumed, data_state)
             break
     else:
@@ -320,17 +352,13 @@ def train(args: argparse.Namespace) -> dict[str, Any]:
         if total_steps > start_step:
             data_state = dataset.state_dict() if hasattr(dataset, "state_dict") else None
             ckpt.save(total_steps - 1, model, muon_opt, adamw_opt, scheduler, tokens_consumed, data_state)
+    watchdog.stop()
     ckpt.shutdown()
     if wb is not None:
         wb.finish()
     sigterm.restore()
     engine.check()
     return {"losses": history, "last_step": last_step, "tokens_consumed": tokens_consumed, "engine": engine}
-
-
-def _sigterm_any(local_flag: bool, comm: Any) -> bool:
-    """All ranks must agree to leave the loop (the save contains a barrier)."""
-    return comm.all_reduce_max(1.0 if local_flag else 0.0) > 0.5
 
 
 def main(argv: Optional[list[str]] = None) -> None:

@@ -50,6 +50,35 @@ def test_engine_grads_match_autograd(attn_res, boundaries):
         assert torch.allclose(q.grad, g, rtol=1e-7, atol=1e-9), n
 
 
+@pytest.mark.parametrize("layers,boundaries", [(8, None), (28, [0, 3, 7, 12, 21, 25]), (6, [2, 4])])
+def test_blocked_routing_matches_stacked(layers, boundaries):
+    """The blocked AttnRes schedule (one phase-1 pass per block for all of its queries, a phase-2
+    merge per sub-layer) equals the stacked per-call form and autograd, fp64, uniform and explicit
+    boundaries."""
+    torch.manual_seed(1)
+    cfg = small_cfg(True, num_layers=layers, attn_res_n_blocks=4, attn_res_boundaries=boundaries, hidden_size=32,
+                    intermediate_size=48, num_attention_heads=2, num_kv_heads=1)
+    ref = KotodamaModel(cfg).double()
+    randomise(ref)
+    m_blocked, m_plain = copy.deepcopy(ref), copy.deepcopy(ref)
+    ids = torch.randint(0, cfg.vocab_size, (2, 12))
+    out = ref(ids, labels=ids)
+    out["loss"].backward()
+    eng = TrainEngine(m_blocked, device="cpu", dtype=torch.float64)
+    assert eng._route_groups and all(g["S"] >= 2 for g in eng._route_groups)
+    n_blocked = sum(len(g["members"]) for g in eng._route_groups)
+    assert n_blocked == len(eng._route_plan) >= 5
+    plain = TrainEngine(m_plain, device="cpu", dtype=torch.float64)
+    plain._route_plan, plain._route_groups = {}, []
+    l1, _ = eng.forward_backward(ids)
+    l2, _ = plain.forward_backward(ids)
+    assert torch.allclose(l1, out["loss"], rtol=1e-10) and torch.allclose(l2, out["loss"], rtol=1e-10)
+    assert torch.allclose(eng.arena.grads, plain.arena.grads, rtol=1e-7, atol=1e-10)
+    for (n, p), (_, q) in zip(ref.named_parameters(), m_blocked.named_parameters()):
+        g = p.grad if p.grad is not None else torch.zeros_like(p)
+        assert torch.allclose(q.grad, g, rtol=1e-7, atol=1e-9), n
+
+
 def test_engine_grad_accumulation_matches_big_batch():
     cfg = small_cfg()
     m1 = KotodamaModel(cfg).double(); randomise(m1)
