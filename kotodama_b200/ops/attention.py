@@ -8,10 +8,11 @@ import torch
 from .flash import flash_bwd, flash_fwd, supported
 
 
-def attention_fwd(ops, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, need_grad: bool = True):
+def attention_fwd(ops, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, need_grad: bool = True,
+                  cu_seqlens=None, max_seqlen: int = 0):
     if not supported(q):
         raise NotImplementedError(f"native attention covers bf16 with head_dim 64 or 128, got {q.dtype} {tuple(q.shape)}")
-    return flash_fwd(ops, q, k, v)
+    return flash_fwd(ops, q, k, v, cu_seqlens=cu_seqlens, max_seqlen=max_seqlen)
 
 
 def attention_bwd(ops, do, q, k, v, o, lse, dq_out, dk_out, dv_out) -> None:

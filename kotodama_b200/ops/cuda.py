@@ -391,9 +391,9 @@ class CudaOps(TorchOps):
         return dw[:hd], dw[hd:]
 
     # ------------------------------------------------------------------ attention
-    def attention_fwd(self, q, k, v, need_grad=True):
+    def attention_fwd(self, q, k, v, need_grad=True, cu_seqlens=None, max_seqlen=0):
         from .attention import attention_fwd
-        return attention_fwd(self, q, k, v, need_grad)
+        return attention_fwd(self, q, k, v, need_grad, cu_seqlens=cu_seqlens, max_seqlen=max_seqlen)
 
     def attention_bwd(self, do, q, k, v, o, lse, dq_out, dk_out, dv_out):
         from .attention import attention_bwd

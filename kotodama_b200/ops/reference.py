@@ -372,9 +372,15 @@ class TorchOps:
         return dqw, dkw
 
     # ------------------------------------------------------------ attention
-    def attention_fwd(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, need_grad: bool = True):
+    def attention_fwd(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, need_grad: bool = True,
+                      cu_seqlens: Optional[torch.Tensor] = None, max_seqlen: int = 0):
         """Causal GQA attention.  ``q[B,T,H,hd]``, ``k,v[B,T,KV,hd]`` (may be strided views);
-        returns ``o[B,T,H,hd]`` contiguous and ``lse[B,H,T]`` fp32 (natural log)."""
+        returns ``o[B,T,H,hd]`` contiguous and ``lse[B,H,T]`` fp32 (natural log).  With ``cu_seqlens``
+        the single batch row holds several sequences back to back (``lse`` is then ``[H, total]``)."""
+        if cu_seqlens is not None:
+            cu = cu_seqlens.tolist()
+            outs = [self.attention_fwd(q[:, a:e], k[:, a:e], v[:, a:e], need_grad) for a, e in zip(cu[:-1], cu[1:])]
+            return torch.cat([o for o, _ in outs], 1), torch.cat([l[0] for _, l in outs], 1)
         b, t, h, hd = q.shape
         kv = k.shape[2]
         g = h // kv

@@ -18,7 +18,7 @@ import json
 import queue
 import threading
 import time
-from typing import Any, Optional
+from typing import Any, Optional, Union
 
 from .engine import Request, SamplingParams, ServingEngine
 
@@ -50,7 +50,7 @@ class CompletionRequest(BaseModel):
     top_p: float = Field(0.0, ge=0.0, le=1.0)
     frequency_penalty: float = Field(0.0, ge=0.0, le=1.0)
     n: int = Field(1, ge=1, le=8)
-    stop: Optional[list[str]] = None
+    stop: Union[list[str], str, None] = None          # a single string or a list, as the OpenAI API allows
 
 
 class ByteTokenizer:
@@ -79,21 +79,53 @@ def load_tokenizer(name: Optional[str]) -> Any:
     return ByteTokenizer()
 
 
+class Ticket:
+    """Handle of one submitted request: the queue its tokens arrive on, and what a cancel needs."""
+
+    def __init__(self) -> None:
+        self.out: "queue.Queue" = queue.Queue()
+        self.rid: Optional[int] = None
+        self.cancelled = False
+
+
 class EngineWorker:
-    """Owns the engine on one thread; clients submit prompts and read tokens from per-request queues."""
+    """Owns the engine on one thread; clients submit prompts and read tokens from per-request queues.
+    A client that stops reading (stop string matched, connection closed) cancels its ticket, which
+    takes the request out of the engine and frees its KV pages.  An exception in a step is reported
+    to every open stream and the affected requests are retired; the thread keeps serving."""
 
     def __init__(self, engine: ServingEngine) -> None:
         self.engine = engine
-        self._inbox: "queue.Queue[tuple[list[int], SamplingParams, queue.Queue]]" = queue.Queue()
-        self._streams: dict[int, tuple[Request, "queue.Queue", int]] = {}
+        self._inbox: "queue.Queue[tuple]" = queue.Queue()
+        self._streams: dict[int, tuple[Request, Ticket, int]] = {}
         self._stop = False
+        self.errors = 0
         self._thread = threading.Thread(target=self._run, name="engine", daemon=True)
         self._thread.start()
 
-    def submit(self, prompt: list[int], params: SamplingParams) -> "queue.Queue":
-        out: "queue.Queue" = queue.Queue()
-        self._inbox.put((prompt, params, out))
-        return out
+    def submit(self, prompt: list[int], params: SamplingParams) -> Ticket:
+        t = Ticket()
+        self._inbox.put(("add", t, prompt, params))
+        return t
+
+    def cancel(self, ticket: Ticket) -> None:
+        ticket.cancelled = True
+        self._inbox.put(("cancel", ticket, None, None))
+
+    def _handle(self, item: tuple) -> None:
+        kind, ticket, prompt, params = item
+        if kind == "add":
+            if ticket.cancelled:
+                return
+            try:
+                r = self.engine.add_request(prompt, params)
+                ticket.rid = r.rid
+                self._streams[r.rid] = (r, ticket, 0)
+            except ValueError as e:
+                ticket.out.put(("error", str(e)))
+        elif ticket.rid is not None and ticket.rid in self._streams:
+            self.engine.cancel(ticket.rid)
+            del self._streams[ticket.rid]
 
     def _drain_inbox(self, block: bool) -> None:
         try:
@@ -101,29 +133,36 @@ class EngineWorker:
         except queue.Empty:
             return
         while True:
-            prompt, params, out = item
-            try:
-                r = self.engine.add_request(prompt, params)
-                self._streams[r.rid] = (r, out, 0)
-            except ValueError as e:
-                out.put(("error", str(e)))
+            self._handle(item)
             try:
                 item = self._inbox.get_nowait()
             except queue.Empty:
                 return
+
+    def _fail_all(self, msg: str) -> None:
+        """A step raised: every open stream gets the error, its request leaves the engine."""
+        self.errors += 1
+        for rid, (r, ticket, _) in list(self._streams.items()):
+            ticket.out.put(("error", msg))
+            self.engine.cancel(rid)
+        self._streams.clear()
 
     def _run(self) -> None:
         while not self._stop:
             self._drain_inbox(block=not self.engine.has_work())
             if not self.engine.has_work():
                 continue
-            self.engine.step()
-            for rid, (r, out, sent) in list(self._streams.items()):
+            try:
+                self.engine.step()
+            except Exception as e:                             # noqa: BLE001 - the worker must outlive a bad step
+                self._fail_all(f"{type(e).__name__}: {e}")
+                continue
+            for rid, (r, ticket, sent) in list(self._streams.items()):
                 for t in r.generated[sent:]:
-                    out.put(("token", t))
-                self._streams[rid] = (r, out, len(r.generated))
+                    ticket.out.put(("token", t))
+                self._streams[rid] = (r, ticket, len(r.generated))
                 if r.finished:
-                    out.put(("done", r.finish_reason))
+                    ticket.out.put(("done", r.finish_reason))
                     del self._streams[rid]
 
     def shutdown(self) -> None:
@@ -146,33 +185,44 @@ def create_app(engine: ServingEngine, tokenizer: Any = None, model_name: str = "
                               eos_token_id=getattr(tok, "eos_token_id", None))
 
     def encode(prompt: str) -> list[int]:
-        ids = tok.encode(prompt)
-        ids = [i for i in ids if i < engine.cfg.vocab_size] or [0]
+        ids = list(tok.encode(prompt)) or [0]
+        bad = [i for i in ids if not 0 <= i < engine.cfg.vocab_size]
+        if bad:
+            raise HTTPException(status_code=400, detail=f"tokenizer produced {len(bad)} ids outside the model's "
+                                                        f"vocabulary of {engine.cfg.vocab_size} (first: {bad[0]})")
         if len(ids) >= engine.max_ctx:
             raise HTTPException(status_code=400, detail=f"Prompt too long: {len(ids)} tokens >= {engine.max_ctx}")
         return ids
 
-    def collect(q: "queue.Queue", stop_strings: list[str]):
-        """Blocking generator of (kind, payload, text_so_far)."""
+    def collect(ticket: Ticket, stop_strings: list[str]):
+        """Blocking generator of (kind, payload, text_so_far).  Leaving it before the engine finished
+        the request (stop string, client gone) cancels the request in the engine."""
         ids: list[int] = []
         text = ""
-        while True:
-            kind, val = q.get()
-            if kind == "error":
-                raise HTTPException(status_code=400, detail=val)
-            if kind == "done":
-                yield "done", val, text
-                return
-            ids.append(val)
-            new_text = tok.decode(ids, skip_special_tokens=True)
-            delta, text = new_text[len(text):], new_text
-            hit = next((s for s in stop_strings if s and s in text), None)
-            if hit is not None:
-                cut = text.index(hit)
-                yield "token", delta[: max(0, len(delta) - (len(text) - cut))], text[:cut]
-                yield "done", "stop", text[:cut]
-                return
-            yield "token", delta, text
+        finished = False
+        try:
+            while True:
+                kind, val = ticket.out.get()
+                if kind == "error":
+                    finished = True
+                    raise HTTPException(status_code=400 if "KV pages" in val or "prompt" in val else 500, detail=val)
+                if kind == "done":
+                    finished = True
+                    yield "done", val, text
+                    return
+                ids.append(val)
+                new_text = tok.decode(ids, skip_special_tokens=True)
+                delta, text = new_text[len(text):], new_text
+                hit = next((s for s in stop_strings if s and s in text), None)
+                if hit is not None:
+                    cut = text.index(hit)
+                    yield "token", delta[: max(0, len(delta) - (len(text) - cut))], text[:cut]
+                    yield "done", "stop", text[:cut]
+                    return
+                yield "token", delta, text
+        finally:
+            if not finished:
+                worker.cancel(ticket)
 
     @app.get("/health")
     def health() -> dict[str, Any]:
@@ -204,15 +254,18 @@ def create_app(engine: ServingEngine, tokenizer: Any = None, model_name: str = "
             async def frames():
                 gen = collect(q, req.stop_strings)
                 n = 0
-                while True:
-                    kind, val, _ = await loop.run_in_executor(None, next, gen)
-                    if kind == "token":
-                        n += 1
-                        if val:
-                            yield f"data: {json.dumps({'token': val})}\n\n"
-                    else:
-                        yield f"data: {json.dumps({'done': True, 'prompt_tokens': len(ids), 'completion_tokens': n})}\n\n"
-                        return
+                try:
+                    while True:
+                        kind, val, _ = await loop.run_in_executor(None, next, gen)
+                        if kind == "token":
+                            n += 1
+                            if val:
+                                yield f"data: {json.dumps({'token': val})}\n\n"
+                        else:
+                            yield f"data: {json.dumps({'done': True, 'prompt_tokens': len(ids), 'completion_tokens': n})}\n\n"
+                            return
+                finally:
+                    gen.close()                               # a dropped connection cancels the request
             return StreamingResponse(frames(), media_type="text/event-stream")
 
         def run() -> tuple[str, int]:
@@ -239,7 +292,8 @@ def create_app(engine: ServingEngine, tokenizer: Any = None, model_name: str = "
 
         def run(q) -> tuple[str, int, str]:
             n, text, reason = 0, "", "length"
-            for kind, val, text in collect(q, req.stop or []):
+            stops = [req.stop] if isinstance(req.stop, str) else (req.stop or [])
+            for kind, val, text in collect(q, stops):
                 if kind == "token":
                     n += 1
                 else:

@@ -4,8 +4,8 @@ decoding on the device.
 The reference server (``serve.py:322-391``) handles one request at a time with a contiguous KV
 cache grown by ``torch.cat``.  Here any number of requests run concurrently: a request is
 prefilled in one pass over its prompt (writing post-norm, post-RoPE keys and values straight
-into its pages; requests admitted in the same step whose prompts have similar lengths share
-that pass as a padded batch), then joins the decode batch, where every step advances all running requests
+into its pages; requests admitted in the same step share that pass, packed back to back with
+the attention kernel taking the sequence boundaries), then joins the decode batch, where every step advances all running requests
 by one token with the split-KV paged attention kernel.  Pages return to the free list when a
 request finishes.
 
@@ -140,9 +140,9 @@ class ServingEngine:
         self.waiting: list[Request] = []
         self.running: list[Request] = []
         self._next_id = 0
-        self._dec_state = None
+        self._dec_states: dict[int, dict] = {}
         self.use_cuda_graphs = True          # decode steps are replayed from captured graphs on CUDA
-        self.prefill_batch_tokens = prefill_batch_tokens     # rows of one (padded) prefill pass over several prompts; 0: one prompt per pass
+        self.prefill_batch_tokens = prefill_batch_tokens     # tokens of one packed prefill pass over several prompts; 0: one prompt per pass
         self.stats = {"prefill_tokens": 0, "decode_tokens": 0, "prefill_s": 0.0, "decode_s": 0.0, "steps": 0,
                       "prefill_passes": 0}
         ar = self.arena
@@ -165,10 +165,27 @@ class ServingEngine:
             raise ValueError("empty prompt")
         if len(prompt) + 1 > self.max_ctx:
             raise ValueError(f"prompt of {len(prompt)} tokens does not fit the context of {self.max_ctx}")
+        need = self.cache.pages_for(min(len(prompt) + params.max_new_tokens, self.max_ctx))
+        if need > self.cache.num_pages:
+            raise ValueError(f"request needs {need} KV pages, the cache has {self.cache.num_pages}")
         r = Request(self._next_id, list(prompt), params)
         self._next_id += 1
         self.waiting.append(r)
         return r
+
+    def cancel(self, rid: int) -> bool:
+        """Ends request ``rid`` now (a client went away, a stop string matched): it leaves the waiting
+        queue or the decode batch and its KV pages return to the free list.  Call between steps."""
+        for lst in (self.waiting, self.running):
+            for r in lst:
+                if r.rid == rid:
+                    lst.remove(r)
+                    if r.pages:
+                        self.cache.release(r.pages)
+                        r.pages = []
+                    r.finished, r.finish_reason = True, "cancelled"
+                    return True
+        return False
 
     def has_work(self) -> bool:
         return bool(self.waiting or self.running)
@@ -176,7 +193,7 @@ class ServingEngine:
     # ------------------------------------------------------------------ model pass
     @torch.no_grad()
     def _forward(self, ids: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor, decode: Optional[dict],
-                 last_rows: torch.Tensor, prompts: int = 1) -> torch.Tensor:
+                 last_rows: torch.Tensor, seqs: Optional[dict] = None) -> torch.Tensor:
         """Runs all layers on ``ids[N]``; keys/values go to ``slots`` (negative = padding, dropped).
         ``decode`` holds the page table and context lengths for paged attention; ``None`` means a
         causal prefill of ``prompts`` requests, each padded to ``N / prompts`` rows.
@@ -200,9 +217,8 @@ class ServingEngine:
             v_rows = qkv[:, (H + KV) * hd:]
             ops.kv_append(k_rows, v_rows, self.cache.k[i], self.cache.v[i], slots)
             if decode is None:
-                T = N // prompts
-                o, _ = ops.attention_fwd(qk[:, : H * hd].view(prompts, T, H, hd), k_rows.view(prompts, T, KV, hd),
-                                         v_rows.view(prompts, T, KV, hd), need_grad=False)
+                o, _ = ops.attention_fwd(qk[:, : H * hd].view(1, N, H, hd), k_rows.view(1, N, KV, hd),
+                                         v_rows.view(1, N, KV, hd), need_grad=False, **seqs)
                 attn = o.reshape(N, H * hd)
             else:
                 attn = ops.paged_decode_attention(qk[:, : H * hd], self.cache.k[i], self.cache.v[i],
@@ -223,35 +239,37 @@ class ServingEngine:
 
     # ------------------------------------------------------------------ scheduling
     def _prefill(self, reqs: list[Request]) -> None:
-        """One pass over the prompts of ``reqs``: they are laid out as a ``[len(reqs), T]`` batch padded
-        at the end to the longest prompt (causal attention never looks at the padding, and padded rows
-        carry slot -1 so that they are not written to the cache)."""
-        B, ns = len(reqs), [len(r.prompt) for r in reqs]
-        T = max(ns)
-        ids = torch.zeros(B, T, dtype=torch.long)
-        slots = torch.full((B, T), -1, dtype=torch.long)
-        for b, r in enumerate(reqs):
-            n = ns[b]
-            ids[b, :n] = torch.tensor(r.prompt, dtype=torch.long)
+        """One pass over the prompts of ``reqs``, packed back to back (no padding): the attention kernel
+        takes the sequence boundaries (``cu_seqlens``), every other op is per token."""
+        ns = [len(r.prompt) for r in reqs]
+        total = sum(ns)
+        ids = torch.empty(total, dtype=torch.long)
+        slots = torch.empty(total, dtype=torch.long)
+        pos = torch.empty(total, dtype=torch.int32)
+        cu = [0]
+        for r, n in zip(reqs, ns):
+            at = cu[-1]
+            ids[at:at + n] = torch.tensor(r.prompt, dtype=torch.long)
             t = torch.arange(n)
-            slots[b, :n] = torch.tensor(r.pages, dtype=torch.long)[t // PAGE] * PAGE + t % PAGE
-        pos = torch.arange(T, dtype=torch.int32).repeat(B)
-        last = torch.tensor([b * T + n - 1 for b, n in enumerate(ns)])
+            slots[at:at + n] = torch.tensor(r.pages, dtype=torch.long)[t // PAGE] * PAGE + t % PAGE
+            pos[at:at + n] = t.to(torch.int32)
+            cu.append(at + n)
+        last = torch.tensor([c - 1 for c in cu[1:]])
         dev = self.device
-        logits = self._forward(ids.view(-1).to(dev), pos.to(dev), slots.view(-1).to(dev), None, last.to(dev), prompts=B)
+        seqs = {"cu_seqlens": torch.tensor(cu, dtype=torch.int32).to(dev), "max_seqlen": max(ns)}
+        logits = self._forward(ids.to(dev), pos.to(dev), slots.to(dev), None, last.to(dev), seqs=seqs)
         toks = sample_tokens(logits, reqs, self.ops).tolist()
         if self.tp is not None:
             toks = self.tp.sync_tokens(toks, self.device)
         for r, n, tok in zip(reqs, ns, toks):
             r.ctx_len = n
             self._accept(r, int(tok))
-        self.stats["prefill_tokens"] += sum(ns)
+        self.stats["prefill_tokens"] += total
         self.stats["prefill_passes"] += 1
 
     def _admit(self) -> list[list[Request]]:
         """Moves the waiting requests that fit (batch slots, pages) to ``running`` and groups them
-        into prefill passes: sorted by prompt length, neighbours share a pass while the padded batch
-        stays within ``prefill_batch_tokens`` rows and at most a quarter of it is padding."""
+        into prefill passes of at most ``prefill_batch_tokens`` packed tokens (0: one prompt per pass)."""
         admitted: list[Request] = []
         while self.waiting and len(self.running) < self.max_batch:
             r = self.waiting[0]
@@ -266,13 +284,10 @@ class ServingEngine:
             admitted.append(r)
         groups: list[list[Request]] = []
         cur: list[Request] = []
-        for r in sorted(admitted, key=lambda q: len(q.prompt)):
-            if cur:
-                total = sum(len(q.prompt) for q in cur) + len(r.prompt)
-                padded = len(r.prompt) * (len(cur) + 1)             # sorted: the newcomer is the longest
-                if padded > self.prefill_batch_tokens or 4 * (padded - total) > padded:
-                    groups.append(cur)
-                    cur = []
+        for r in admitted:
+            if cur and sum(len(q.prompt) for q in cur) + len(r.prompt) > self.prefill_batch_tokens:
+                groups.append(cur)
+                cur = []
             cur.append(r)
         if cur:
             groups.append(cur)
@@ -293,23 +308,25 @@ class ServingEngine:
         running requests changes (pages are assigned once, at admission)."""
         B = len(reqs)
         key = tuple(r.rid for r in reqs)
-        st = self._dec_state
-        if st is None or st["key"] != key:
+        # static buffers and captured graphs are kept per batch size: a batch size that comes back
+        # (requests of unequal length retire one by one) replays its old graphs
+        st = self._dec_states.get(B)
+        if st is None:
+            dev = self.device
+            st = {"B": B, "key": None, "ids": torch.zeros(B, dtype=torch.long, device=dev),
+                  "pos": torch.zeros(B, dtype=torch.int32, device=dev),
+                  "slots": torch.zeros(B, dtype=torch.long, device=dev),
+                  "ctx": torch.zeros(B, dtype=torch.int32, device=dev),
+                  "table": torch.zeros(B, self.max_pages_per_req, dtype=torch.int32, device=dev),
+                  "rows": torch.arange(B, device=dev), "graphs": {}}
+            self._dec_states[B] = st
+        if st["key"] != key:
             table = torch.zeros(B, self.max_pages_per_req, dtype=torch.int32)
             for i, r in enumerate(reqs):
                 table[i, : len(r.pages)] = torch.tensor(r.pages, dtype=torch.int32)
-            if st is None or st["B"] != B:
-                dev = self.device
-                st = {"B": B, "ids": torch.zeros(B, dtype=torch.long, device=dev),
-                      "pos": torch.zeros(B, dtype=torch.int32, device=dev),
-                      "slots": torch.zeros(B, dtype=torch.long, device=dev),
-                      "ctx": torch.zeros(B, dtype=torch.int32, device=dev),
-                      "table": torch.zeros(B, self.max_pages_per_req, dtype=torch.int32, device=dev),
-                      "rows": torch.arange(B, device=dev), "graphs": {}}
             st["table"].copy_(table, non_blocking=True)
             st["host_table"] = table
             st["key"] = key
-            self._dec_state = st
         lens = torch.tensor([r.ctx_len for r in reqs], dtype=torch.int32)
         last = torch.tensor([r.generated[-1] for r in reqs], dtype=torch.long)
         idx = torch.arange(B)

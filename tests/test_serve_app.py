@@ -62,3 +62,44 @@ def test_openai_completions(client):
     assert r.status_code == 200 and len(body["choices"]) == 2 and body["object"] == "text_completion"
     assert body["usage"]["prompt_tokens"] == 2 and body["usage"]["completion_tokens"] <= 6
     assert client.post("/v1/completions", json={"prompt": "hi", "n": 9}).status_code == 422
+
+
+def test_stop_as_string_cancels_the_request_in_the_engine(client):
+    """OpenAI clients may send ``stop`` as one string; a stop hit ends the request in the engine too
+    (its KV pages come back although max_tokens was not reached)."""
+    import time
+    full = client.post("/v1/completions", json={"prompt": "hi", "max_tokens": 40, "temperature": 0}).json()
+    text = full["choices"][0]["text"]
+    stop = next((ch for ch in text[1:] if ch.strip()), None)
+    if stop is None:
+        pytest.skip("model produced no printable character to stop on")
+    r = client.post("/v1/completions", json={"prompt": "hi", "max_tokens": 40, "temperature": 0, "stop": stop})
+    body = r.json()
+    assert r.status_code == 200 and stop not in body["choices"][0]["text"][1:] and body["choices"][0]["finish_reason"] == "stop"
+    for _ in range(100):                                      # the cancel travels through the worker's inbox
+        st = client.get("/stats").json()
+        if st["free_pages"] == st["num_pages"] and st["running"] == 0:
+            break
+        time.sleep(0.02)
+    assert st["free_pages"] == st["num_pages"] and st["running"] == 0
+
+
+def test_worker_survives_a_failing_step(client):
+    """An exception inside a step reaches the waiting client as an error and the worker keeps serving."""
+    worker = client.app.state.worker
+    eng = worker.engine
+    real = eng.step
+    calls = {"n": 0}
+
+    def boom():
+        calls["n"] += 1
+        raise RuntimeError("KV cache exhausted")
+    eng.step = boom
+    try:
+        r = client.post("/generate", json={"prompt": "hello", "max_new_tokens": 5, "temperature": 0})
+        assert r.status_code == 500 and "KV cache exhausted" in r.json()["detail"]
+    finally:
+        eng.step = real
+    assert calls["n"] == 1 and worker.errors == 1 and not eng.has_work()
+    ok = client.post("/generate", json={"prompt": "hello", "max_new_tokens": 3, "temperature": 0})
+    assert ok.status_code == 200 and ok.json()["completion_tokens"] >= 1

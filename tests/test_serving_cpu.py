@@ -1,4 +1,5 @@
 """Paged-KV continuous-batching engine against the plain model (contiguous KV cache, one request)."""
+import pytest
 import torch
 
 from kotodama_b200.config import MODEL_PRESETS, ModelConfig
@@ -45,7 +46,9 @@ def test_paged_engine_matches_contiguous_cache_greedy():
         assert eng.stats["prefill_tokens"] == sum(map(len, prompts))
 
 
-def test_prompts_of_similar_length_share_a_padded_prefill_pass():
+def test_prompts_share_a_packed_prefill_pass():
+    """Prompts admitted together run as one packed pass (sequence boundaries go to the attention
+    kernel, nothing is padded), however unequal their lengths; the token budget splits passes."""
     import copy
     cfg, model = _model()
     g = torch.Generator().manual_seed(2)
@@ -54,11 +57,31 @@ def test_prompts_of_similar_length_share_a_padded_prefill_pass():
     eng = ServingEngine(copy.deepcopy(model), device="cpu", dtype=torch.float32, max_batch=8, max_ctx=128)
     got = eng.generate(prompts, SamplingParams(max_new_tokens=6, temperature=0.0))
     assert got == ref
-    assert eng.stats["prefill_passes"] == 2                        # the short one alone, four padded to 33 rows
-    eng.prefill_batch_tokens = 64                                  # only 28 and 30 still fit one pass (60 rows)
+    assert eng.stats["prefill_passes"] == 1
+    eng.prefill_batch_tokens = 64                                  # 30+33 | 28+31 | 9
     eng.stats["prefill_passes"] = 0
     assert eng.generate(prompts, SamplingParams(max_new_tokens=6, temperature=0.0)) == ref
-    assert eng.stats["prefill_passes"] == 4
+    assert eng.stats["prefill_passes"] == 3
+
+
+def test_cancel_releases_pages_and_oversize_requests_are_refused():
+    cfg, model = _model()
+    eng = ServingEngine(model, device="cpu", dtype=torch.float32, max_batch=4, num_pages=8, max_ctx=256)
+    with pytest.raises(ValueError):                                 # 10 pages can never be had from a cache of 8
+        eng.add_request(list(range(1, 60)), SamplingParams(max_new_tokens=100, temperature=0.0))
+    a = eng.add_request([1, 2, 3], SamplingParams(max_new_tokens=30, temperature=0.0))
+    b = eng.add_request([4, 5, 6], SamplingParams(max_new_tokens=30, temperature=0.0))
+    eng.step()
+    eng.step()
+    free_before = len(eng.cache.free)
+    assert eng.cancel(a.rid) and a.finished and a.finish_reason == "cancelled"
+    assert len(eng.cache.free) == free_before + 3                   # 33 tokens = 3 pages came back
+    assert not eng.cancel(a.rid)
+    n = len(a.generated)
+    while eng.has_work():
+        eng.step()
+    assert len(a.generated) == n and len(b.generated) == 30
+    assert len(eng.cache.free) == eng.cache.num_pages
 
 
 def test_continuous_batching_admits_when_pages_free_up():
