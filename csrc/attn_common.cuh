@@ -69,14 +69,15 @@ __device__ __forceinline__ void load_tile(uint8_t* dst, const CUtensorMap* m, ui
 }
 
 // acc[128 x 128] (+)= A B^T with both tiles K-major over head_dim: A rows -> accumulator lanes,
-// B rows -> accumulator columns.
+// B rows -> accumulator columns.  One descriptor pair is built per call; each contraction step
+// only adds a constant to the low words, so the issuing thread stays ahead of the tensor pipe.
 template <int HD>
 __device__ __forceinline__ void mma_nt_tiles(uint32_t d_tmem, uint32_t a_addr, uint32_t b_addr, uint32_t idesc) {
+    const tc::DescHalves a = tc::smem_desc_halves(a_addr, 16, 1024), b = tc::smem_desc_halves(b_addr, 16, 1024);
 #pragma unroll
     for (int k = 0; k < HD / 16; ++k) {
-        const uint32_t off = (k >> 2) * HALF_BYTES + (k & 3) * 32;
-        tc::mma_f16(d_tmem, tc::smem_desc_sw128(a_addr + off, 16, 1024), tc::smem_desc_sw128(b_addr + off, 16, 1024),
-                    idesc, k != 0);
+        const uint32_t off = ((k >> 2) * HALF_BYTES + (k & 3) * 32) >> 4;
+        tc::mma_f16_h(d_tmem, a.lo + off, a.hi, b.lo + off, b.hi, idesc, k != 0);
     }
 }
 
@@ -88,11 +89,12 @@ __device__ __forceinline__ void mma_nt_tiles(uint32_t d_tmem, uint32_t a_addr, u
 template <int HD, bool QUARTERS>
 __device__ __forceinline__ void mma_ts_tile(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_addr, uint32_t idesc,
                                             bool accumulate) {
+    const tc::DescHalves b = tc::smem_desc_halves(b_addr, HALF_BYTES, 1024);
+    const uint32_t acc = accumulate ? 1u : 0u;
 #pragma unroll
     for (int k = 0; k < BT / 16; ++k) {
         const uint32_t a = a_tmem + (QUARTERS ? 32 * (k >> 1) + 8 * (k & 1) : 8 * k);
-        tc::mma_f16_ts(d_tmem, a, tc::smem_desc_sw128(b_addr + k * 2048, HALF_BYTES, 1024), idesc,
-                       accumulate || k != 0);
+        tc::mma_f16_ts_h(d_tmem, a, b.lo + k * (2048 >> 4), b.hi, idesc, k == 0 ? acc : 1u);
     }
 }
 

@@ -1,23 +1,26 @@
 // Causal GQA flash-attention forward for sm_100a (head_dim 64 or 128, bf16), fixed-length
 // batches or packed variable-length sequences (cu_seqlens).
 //
-// One CTA owns two consecutive 128-row query tiles of one head and walks the key/value tiles
-// they share.  Eighteen warps: four softmax warpgroups (two per query tile: each of a row's two
-// threads takes 64 of the 128 key columns; the row maximum and sum cross between them through
-// shared memory), one MMA-issuing warp, one TMA warp.  Tensor memory holds both score tiles and both output
-// accumulators (512 columns), so the tensor pipe alternates between the two query tiles:
+// One CTA owns one 128-row query tile of one head and walks its key/value tiles.  Six warps: four
+// softmax warps (thread = query row), one MMA-issuing warp, one TMA warp.  The score tile is
+// double-buffered in tensor memory, so the scores of the next key tile are already there when the
+// softmax of the current one ends: the softmax warps never wait for the tensor pipe, and the
+// tensor pipe only has the P V product of a tile on the path between two softmax passes.
 //
-//   tensor pipe:   PV0(j)  S0(j+1)  PV1(j)  S1(j+1)  PV0(j+1) ...
-//   tile 0 warps:  ........softmax of S0(j+1)........
-//   tile 1 warps:  ...softmax of S1(j)....  ........softmax of S1(j+1)...
+//   tensor pipe:   S(j+1) ........ PV(j) S(j+2) ........ PV(j+1) S(j+3)
+//   softmax:       softmax(j) ......... softmax(j+1) ......... softmax(j+2)
 //
 //   S = Q K^T      tcgen05.mma, both operands K-major in shared memory (TMA, 128-byte swizzle)
-//   softmax        tcgen05.ld the row, online max / sum in base 2, P written back over the score
-//                  columns as packed bf16 (tcgen05.st); a share of the exponentials is evaluated
-//                  on the FMA pipe so that the special-function unit is not the only source
+//   softmax        tcgen05.ld the row, online max / sum in base 2 with packed two-wide arithmetic,
+//                  P written back over the score columns as packed bf16 (tcgen05.st); a share of
+//                  the exponentials is evaluated on the FMA pipe so that the special-function unit
+//                  is not the only source
 //   O += P V       tcgen05.mma with A read from tensor memory and V as an MN-major shared operand
-// K and V tiles move through two-stage rings.  The running maximum is refreshed lazily: O and
-// the running sum are rescaled only when a row's maximum grows by more than 2^8.
+// The softmax can finish tile j+1 before the issuing thread has looked at tile j, so every
+// barrier that hands a score buffer over exists once per buffer (a single barrier would be two
+// phases ahead of its waiter).  K tiles move through a three-stage ring (a tile is requested two products ahead), V tiles
+// through a two-stage ring.  The running maximum is refreshed lazily: O and the running sum are
+// rescaled only when a row's maximum grows by more than 2^8.
 // Every wait is bounded (status word on timeout).
 #include "attn_common.cuh"
 
@@ -25,10 +28,16 @@ namespace {
 
 using namespace attn;
 
-constexpr int KST = 2, VST = 2;                    // ring depths
+#define KB_FAIL_FWD(code)                              \
+    {                                                  \
+        atomicMax(p.status, (int)(code));              \
+        break;                                         \
+    }
+
+constexpr int KST = 3, VST = 2;                    // ring depths
 constexpr float RESCALE_THRESHOLD = 8.0f;          // in log2 units
-constexpr int EMU = 1;                             // of every 4 pairs of exponentials, this many run on the FMA pipe
-constexpr int FWD_THREADS = 576;                   // 16 softmax warps, MMA warp, TMA warp
+constexpr int EMU = 2;                             // of every 4 pairs of exponentials, this many run on the FMA pipe
+constexpr int FWD_THREADS = 192;
 
 struct FlashParams {
     int B, T, H, KV;
@@ -39,7 +48,7 @@ struct FlashParams {
     float* lse;                                    // natural log; index head * lse_hs + (b * lse_bs | cu[b]) + t
     long long lse_hs, lse_bs;
     int q_col0, k_col0, v_col0;                    // first column of head 0 inside each operand's rows
-    int n_pairs;                                   // query-tile pairs per sequence (grid decode)
+    int n_tiles;                                   // query tiles per sequence (grid decode)
     int* status;
 };
 
@@ -58,7 +67,7 @@ __device__ long long g_attn_dbg[16];
 
 template <int HD>
 constexpr int fwd_smem_bytes() {
-    return (2 + KST + VST) * Tile<HD>::BYTES + 1024 + 256 + 8 * BT * 4;
+    return (1 + KST + VST) * Tile<HD>::BYTES + 1024 + 256;
 }
 
 template <int HD>
@@ -68,8 +77,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     constexpr int TB = Tile<HD>::BYTES;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t* sQ = smem;                            // two query tiles
-    uint8_t* sK = smem + 2 * TB;
+    uint8_t* sQ = smem;
+    uint8_t* sK = smem + TB;
     uint8_t* sV = sK + KST * TB;
     uint64_t* bars = reinterpret_cast<uint64_t*>(sV + VST * TB);
     uint64_t* q_full = bars + 0;
@@ -77,19 +86,16 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     uint64_t* k_empty = k_full + KST;
     uint64_t* v_full = k_empty + KST;              // [VST]
     uint64_t* v_empty = v_full + VST;
-    uint64_t* s_full = v_empty + VST;              // [2] one per query tile
-    uint64_t* p_ready = s_full + 2;                // [2]
-    uint64_t* o_done = p_ready + 2;                // [2]
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + 2);
+    uint64_t* s_full = v_empty + VST;              // [2] one per score buffer
+    uint64_t* p_ready = s_full + 2;                // [2] one per score buffer
+    uint64_t* o_done = p_ready + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    // row maxima [parity][tile][half][row] and, at the end, row sums [2 + tile][half][row] of the two
-    // threads that share a query row
-    float* row_buf = reinterpret_cast<float*>(smem + (2 + KST + VST) * TB + 256);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // heavy pairs (late query tiles) first
+    // heavy tiles (late queries) first
     const int HB = p.H * p.B;
-    const int pair = p.n_pairs - 1 - (int)(blockIdx.x / HB);
+    const int qt = p.n_tiles - 1 - (int)(blockIdx.x / HB);
     const int hb = blockIdx.x % HB;
     const int head = hb % p.H, b = hb / p.H;
     const int kvh = head / (p.H / p.KV);
@@ -101,152 +107,145 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         seq_row0 = b * p.T;
         Tb = p.T;
     }
-    const int nkv = (Tb + BT - 1) / BT;
-    // tile counts of the two query tiles; a tile that starts past the sequence end has none
-    const int qt0 = 2 * pair, qt1 = 2 * pair + 1;
-    const int n0 = qt0 < nkv ? qt0 + 1 : 0;
-    const int n1 = qt1 < nkv ? qt1 + 1 : 0;
-    const int n = n0 > n1 ? n0 : n1;
+    // key tiles of this query tile; a tile that starts past the sequence end has none
+    const int n = qt * BT < Tb ? qt + 1 : 0;
 
     if (threadIdx.x == 0) {
         tc::mbar_init(q_full, 1);
         for (int i = 0; i < KST; ++i) { tc::mbar_init(k_full + i, 1); tc::mbar_init(k_empty + i, 1); }
         for (int i = 0; i < VST; ++i) { tc::mbar_init(v_full + i, 1); tc::mbar_init(v_empty + i, 1); }
-        for (int i = 0; i < 2; ++i) {
-            tc::mbar_init(s_full + i, 1);
-            tc::mbar_init(p_ready + i, 8);
-            tc::mbar_init(o_done + i, 1);
-        }
+        tc::mbar_init(s_full + 0, 1);
+        tc::mbar_init(s_full + 1, 1);
+        tc::mbar_init(p_ready + 0, 4);
+        tc::mbar_init(p_ready + 1, 4);
+        tc::mbar_init(o_done, 1);
         *abort_flag = 0;
         tc::fence_barrier_init();
     }
-    if (warp == 16) {
+    if (warp == 4) {
         tc::tmem_alloc(tmem_slot, 512);
         tc::tmem_relinquish();
     }
     tc::tc_fence_before();
     __syncthreads();
     tc::tc_fence_after();
-    const uint32_t tmem0 = *tmem_slot;
-    // scores of tile t at columns t*128, output accumulator of tile t at 256 + t*128
+    const uint32_t tmem0 = *tmem_slot;             // score buffers at columns 0 and 128, output accumulator at 256
+    const uint32_t tmem_oacc = tmem0 + 256;
 
     if (n == 0) {
-        // nothing to do for this pair (sequence shorter than the grid was sized for)
-    } else if (warp == 17) {
+        // nothing to do (sequence shorter than the grid was sized for)
+    } else if (warp == 5) {
         // ------------------------------------------------------------ TMA
         if (lane == 0) {
             tc::prefetch_tmap(&tmQ);
             tc::prefetch_tmap(&tmK);
             tc::prefetch_tmap(&tmV);
             const int qx = p.q_col0 + head * HD, kx = p.k_col0 + kvh * HD, vx = p.v_col0 + kvh * HD;
-            tc::mbar_expect_tx(q_full, (n1 > 0 ? 2 : 1) * TB);
-            load_tile<HD>(sQ, &tmQ, q_full, qx, seq_row0 + qt0 * BT);
-            if (n1 > 0) load_tile<HD>(sQ + TB, &tmQ, q_full, qx, seq_row0 + qt1 * BT);
-            for (int j = 0; j < n; ++j) {
-                const int ks = j % KST, vs = j % VST;
-                if (!tc::mbar_wait(k_empty + ks, ((j / KST) & 1) ^ 1, abort_flag)) { atomicMax(p.status, (int)KB_TIMEOUT_TMA); break; }
+            tc::mbar_expect_tx(q_full, TB);
+            load_tile<HD>(sQ, &tmQ, q_full, qx, seq_row0 + qt * BT);
+            // order of need: K0 K1 V0 K2 V1 K3 V2 ...
+            auto load_k = [&](int j) -> bool {
+                const int ks = j % KST;
+                if (!tc::mbar_wait(k_empty + ks, ((j / KST) & 1) ^ 1, abort_flag)) return false;
                 tc::mbar_expect_tx(k_full + ks, TB);
                 load_tile<HD>(sK + ks * TB, &tmK, k_full + ks, kx, seq_row0 + j * BT);
-                if (!tc::mbar_wait(v_empty + vs, ((j / VST) & 1) ^ 1, abort_flag)) { atomicMax(p.status, (int)KB_TIMEOUT_TMA); break; }
+                return true;
+            };
+            bool ok = load_k(0) && (n < 2 || load_k(1));
+            for (int j = 0; j < n && ok; ++j) {
+                const int vs = j % VST;
+                if (!tc::mbar_wait(v_empty + vs, ((j / VST) & 1) ^ 1, abort_flag)) { ok = false; break; }
                 tc::mbar_expect_tx(v_full + vs, TB);
                 load_tile<HD>(sV + vs * TB, &tmV, v_full + vs, vx, seq_row0 + j * BT);
+                if (j + 2 < n) ok = load_k(j + 2);
             }
+            if (!ok) atomicMax(p.status, (int)KB_TIMEOUT_TMA);
         }
-    } else if (warp == 16) {
+    } else if (warp == 4) {
         // ------------------------------------------------------------ MMA issue (one thread)
         if (lane == 0) {
             const uint32_t idesc_s = tc::instr_desc_f16(BT, BT, 1, 1, 0, 0);
             const uint32_t idesc_o = tc::instr_desc_f16(BT, HD, 1, 1, 0, 1);
             const uint32_t q_addr = smem_u32(sQ), k_addr = smem_u32(sK), v_addr = smem_u32(sV);
-            bool ok = tc::mbar_wait(q_full, 0, abort_flag) && tc::mbar_wait(k_full, 0, abort_flag);
-            if (!ok) atomicMax(p.status, (int)KB_TIMEOUT_TMA);
-            if (ok) {
+            do {
+                if (!tc::mbar_wait(q_full, 0, abort_flag) || !tc::mbar_wait(k_full, 0, abort_flag)) KB_FAIL_FWD(KB_TIMEOUT_TMA)
                 tc::tc_fence_after();
-                if (n0 > 0) { mma_nt_tiles<HD>(tmem0, q_addr, k_addr, idesc_s); tc::tc_commit(s_full + 0); }
-                if (n1 > 0) { mma_nt_tiles<HD>(tmem0 + 128, q_addr + TB, k_addr, idesc_s); tc::tc_commit(s_full + 1); }
+                mma_nt_tiles<HD>(tmem0, q_addr, k_addr, idesc_s);
+                tc::tc_commit(s_full + 0);
                 tc::tc_commit(k_empty + 0);
-            }
-            for (int j = 0; j < n && ok; ++j) {
-                const uint32_t ph = j & 1;
-                const int vs = j % VST, ks1 = (j + 1) % KST;
-                const uint32_t vj = v_addr + vs * TB, k1 = k_addr + ks1 * TB;
-                if (!tc::mbar_wait(v_full + vs, (j / VST) & 1, abort_flag)) { atomicMax(p.status, (int)KB_TIMEOUT_TMA); break; }
-                if (j + 1 < n && !tc::mbar_wait(k_full + ks1, ((j + 1) / KST) & 1, abort_flag)) { atomicMax(p.status, (int)KB_TIMEOUT_TMA); break; }
-                if (j < n0) {
-                    if (!tc::mbar_wait(p_ready + 0, ph, abort_flag)) { atomicMax(p.status, (int)KB_TIMEOUT_MMA); break; }
+                if (n > 1) {
+                    if (!tc::mbar_wait(k_full + 1, 0, abort_flag)) KB_FAIL_FWD(KB_TIMEOUT_TMA)
                     tc::tc_fence_after();
-                    mma_ts_tile<HD, false>(tmem0 + 256, tmem0, vj, idesc_o, j != 0);
-                    tc::tc_commit(o_done + 0);
-                    if (j + 1 < n0) { mma_nt_tiles<HD>(tmem0, q_addr, k1, idesc_s); tc::tc_commit(s_full + 0); }
+                    mma_nt_tiles<HD>(tmem0 + 128, q_addr, k_addr + TB, idesc_s);
+                    tc::tc_commit(s_full + 1);
+                    tc::tc_commit(k_empty + 1);
                 }
-                if (j < n1) {
-                    if (!tc::mbar_wait(p_ready + 1, ph, abort_flag)) { atomicMax(p.status, (int)KB_TIMEOUT_MMA); break; }
+                for (int j = 0; j < n; ++j) {
+                    const int vs = j % VST;
+                    if (!tc::mbar_wait(v_full + vs, (j / VST) & 1, abort_flag)) KB_FAIL_FWD(KB_TIMEOUT_TMA)
+                    if (!tc::mbar_wait(p_ready + (j & 1), (j >> 1) & 1, abort_flag)) KB_FAIL_FWD(KB_TIMEOUT_MMA)
                     tc::tc_fence_after();
-                    mma_ts_tile<HD, false>(tmem0 + 384, tmem0 + 128, vj, idesc_o, j != 0);
-                    tc::tc_commit(o_done + 1);
+                    mma_ts_tile<HD, false>(tmem_oacc, tmem0 + (j & 1) * 128, v_addr + vs * TB, idesc_o, j != 0);
+                    tc::tc_commit(o_done);
                     tc::tc_commit(v_empty + vs);
-                    if (j + 1 < n1) { mma_nt_tiles<HD>(tmem0 + 128, q_addr + TB, k1, idesc_s); tc::tc_commit(s_full + 1); }
-                } else {
-                    tc::tc_commit(v_empty + vs);
+                    if (j + 2 < n) {
+                        const int ks = (j + 2) % KST;
+                        if (!tc::mbar_wait(k_full + ks, ((j + 2) / KST) & 1, abort_flag)) KB_FAIL_FWD(KB_TIMEOUT_TMA)
+                        tc::tc_fence_after();
+                        mma_nt_tiles<HD>(tmem0 + (j & 1) * 128, q_addr, k_addr + ks * TB, idesc_s);
+                        tc::tc_commit(s_full + (j & 1));
+                        tc::tc_commit(k_empty + ks);
+                    }
                 }
-                if (j + 1 < n) tc::tc_commit(k_empty + ks1);
-            }
+            } while (false);
         }
-    } else if (warp < 16) {
-        // ------------------------------------------------------------ softmax: two threads per query row
-        const int t = warp >> 3;                                   // which query tile
-        const int hf = (warp >> 2) & 1;                            // which 64 of the tile's 128 key columns
-        const int qt = t ? qt1 : qt0, nt = t ? n1 : n0;
-        const int r = (warp & 3) * 32 + lane;                      // row inside the tile
-        const uint32_t lane_base = ((uint32_t)((warp & 3) * 32) << 16);
-        const uint32_t tmem_s = tmem0 + t * 128 + lane_base, tmem_o = tmem0 + 256 + t * 128 + lane_base;
+    } else {
+        // ------------------------------------------------------------ softmax: thread = query row
+        const int r = warp * 32 + lane;                            // row inside the tile
+        const uint32_t lane_base = ((uint32_t)(warp * 32) << 16);
+        const uint32_t tmem_o = tmem_oacc + lane_base;
         float m_used = -INFINITY, l = 0.f;
         bool ok = true;
 #ifdef KB_ATTN_PROFILE
-        const bool prof = blockIdx.x == 0 && threadIdx.x == 256;     // first row of the second (longer) query tile
+        const bool prof = blockIdx.x == 0 && threadIdx.x == 0;
         long long dbg[8] = {0, 0, 0, 0, 0, 0, 0, 0};
         long long tk = clock64();
 #endif
-        for (int j = 0; j < nt && ok; ++j) {
-            const uint32_t ph = j & 1;
+        for (int j = 0; j < n && ok; ++j) {
+            const uint32_t tmem_s = tmem0 + (j & 1) * 128 + lane_base;
             KB_TICK(0, tk)                                              // loop overhead / arrive
-            if (!tc::mbar_wait(s_full + t, ph, abort_flag)) {
+            if (!tc::mbar_wait(s_full + (j & 1), (j >> 1) & 1, abort_flag)) {
                 if (lane == 0) atomicMax(p.status, (int)KB_TIMEOUT_EPI);
                 ok = false;
                 break;
             }
             tc::tc_fence_after();
-            float s[64];
-            tc::tmem_ld32(tmem_s + hf * 64, reinterpret_cast<uint32_t*>(s));
-            tc::tmem_ld32(tmem_s + hf * 64 + 32, reinterpret_cast<uint32_t*>(s + 32));
             KB_TICK(1, tk)                                              // wait for the scores
+            float s[BT];
+#pragma unroll
+            for (int c = 0; c < BT; c += 32) tc::tmem_ld32(tmem_s + c, reinterpret_cast<uint32_t*>(s + c));
             tc::tmem_ld_wait();
             KB_TICK(2, tk)                                              // tensor-memory load
             if (j == qt) {                                          // diagonal tile: causal mask
-                const int cmax = r - hf * 64;
 #pragma unroll
-                for (int c = 0; c < 64; ++c) s[c] = c <= cmax ? s[c] : -INFINITY;
+                for (int c = 0; c < BT; ++c) s[c] = c <= r ? s[c] : -INFINITY;
             }
-            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};      // four chains: latency, not count, matters here
+            float mx8[8];                                           // eight chains: latency, not count, matters here
 #pragma unroll
-            for (int c = 0; c < 64; c += 8) {
+            for (int i = 0; i < 8; ++i) mx8[i] = fmaxf(s[2 * i], s[2 * i + 1]);
 #pragma unroll
-                for (int i = 0; i < 4; ++i) mx4[i] = fmax3(mx4[i], s[c + 2 * i], s[c + 2 * i + 1]);
+            for (int c = 16; c < BT; c += 16) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) mx8[i] = fmax3(mx8[i], s[c + 2 * i], s[c + 2 * i + 1]);
             }
-            float mx = fmaxf(fmax3(mx4[0], mx4[1], mx4[2]), mx4[3]);
-            // the row maximum spans both halves: exchange through shared memory.  The named barrier
-            // also orders "both halves have read their scores" before either writes P over them.
-            float* mine = row_buf + ((ph * 2 + t) * 2 + hf) * BT + r;
-            *mine = mx;
-            asm volatile("bar.sync %0, 256;" ::"r"(1 + t) : "memory");
-            mx = fmaxf(mx, row_buf[((ph * 2 + t) * 2 + (hf ^ 1)) * BT + r]) * p.scale_log2;
+            const float mx = fmax3(fmax3(mx8[0], mx8[1], mx8[2]), fmax3(mx8[3], mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])) *
+                             p.scale_log2;
             const bool grow = mx > m_used + RESCALE_THRESHOLD;      // first tile: m_used = -inf -> true
             if (j == 0) {
                 m_used = mx;
             } else if (__any_sync(0xffffffffu, grow)) {
-                // O holds sums of p * v with p relative to m_used: move it to the new maximum.  Both
-                // halves see the same maxima and take the same branch; each rescales half of O's columns.
-                if (!tc::mbar_wait(o_done + t, (j - 1) & 1, abort_flag)) {
+                // O holds sums of p * v with p relative to m_used: move it to the new maximum
+                if (!tc::mbar_wait(o_done, (j - 1) & 1, abort_flag)) {
                     if (lane == 0) atomicMax(p.status, (int)KB_TIMEOUT_EPI);
                     ok = false;
                     break;
@@ -255,23 +254,23 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 const float m_new = fmaxf(m_used, mx);
                 const float f = exp2f(m_used - m_new);
 #pragma unroll 1
-                for (int c = 0; c < HD / 2; c += 32) {
+                for (int c = 0; c < HD; c += 32) {
                     uint32_t o[32];
-                    tc::tmem_ld32(tmem_o + hf * (HD / 2) + c, o);
+                    tc::tmem_ld32(tmem_o + c, o);
                     tc::tmem_ld_wait();
 #pragma unroll
                     for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
-                    tc::tmem_st32(tmem_o + hf * (HD / 2) + c, o);
+                    tc::tmem_st32(tmem_o + c, o);
                 }
                 tc::tmem_st_wait();
                 l *= f;
                 m_used = m_new;
             }
-            KB_TICK(3, tk)                                              // max, exchange and rescale check
+            KB_TICK(3, tk)                                              // max and rescale check
             const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), nm2 = make_float2(-m_used, -m_used);
             float2 sum2 = make_float2(0.f, 0.f);
 #pragma unroll
-            for (int q4 = 0; q4 < 2; ++q4) {                        // 32 scores -> 16 packed columns at a time
+            for (int q4 = 0; q4 < 4; ++q4) {                        // 32 scores -> 16 packed columns at a time
                 uint32_t pk[16];
 #pragma unroll
                 for (int c = 0; c < 32; c += 2) {
@@ -280,41 +279,35 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                     sum2 = __fadd2_rn(sum2, e);
                     pk[c >> 1] = pack_bf16(e.x, e.y);
                 }
-                tc::tmem_st16(tmem_s + hf * 32 + q4 * 16, pk);
+                tc::tmem_st16(tmem_s + q4 * 16, pk);
             }
             l += sum2.x + sum2.y;
             KB_TICK(4, tk)                                              // exponentials, packing, store issue
             tc::tmem_st_wait();
             tc::tc_fence_before();
             __syncwarp();
-            if (lane == 0) tc::mbar_arrive(p_ready + t);
+            if (lane == 0) tc::mbar_arrive(p_ready + (j & 1));
             KB_TICK(5, tk)                                              // store wait, fence, arrive
         }
 #ifdef KB_ATTN_PROFILE
         if (prof) {
             for (int i = 0; i < 6; ++i) g_attn_dbg[i] = dbg[i];
-            g_attn_dbg[6] = nt;
+            g_attn_dbg[6] = n;
         }
 #endif
-        if (nt > 0) {
-            // the row sum spans both halves too (every thread of the tile takes part in the barrier)
-            row_buf[((2 + t) * 2 + hf) * BT + r] = l;
-            asm volatile("bar.sync %0, 256;" ::"r"(1 + t) : "memory");
-            l += row_buf[((2 + t) * 2 + (hf ^ 1)) * BT + r];
-        }
-        if (ok && nt > 0) {
-            if (tc::mbar_wait(o_done + t, (nt - 1) & 1, abort_flag)) {
+        if (ok) {
+            if (tc::mbar_wait(o_done, (n - 1) & 1, abort_flag)) {
                 tc::tc_fence_after();
                 const float inv = 1.f / l;
                 // Rows past the end of the sequence (zero-filled by TMA, or the first rows of the next
                 // sequence) are computed but never stored; for the valid rows the causal mask already
                 // excludes every key at or beyond the end.
                 const bool valid = qt * BT + r < Tb;
-                __nv_bfloat16* dst = p.out + (size_t)(seq_row0 + qt * BT + r) * p.out_stride + head * HD + hf * (HD / 2);
+                __nv_bfloat16* dst = p.out + (size_t)(seq_row0 + qt * BT + r) * p.out_stride + head * HD;
 #pragma unroll 1
-                for (int c = 0; c < HD / 2; c += 32) {
+                for (int c = 0; c < HD; c += 32) {
                     uint32_t o[32];
-                    tc::tmem_ld32(tmem_o + hf * (HD / 2) + c, o);
+                    tc::tmem_ld32(tmem_o + c, o);
                     tc::tmem_ld_wait();
                     if (valid) {
 #pragma unroll
@@ -326,7 +319,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                         }
                     }
                 }
-                if (valid && hf == 0) {
+                if (valid) {
                     const long long base = p.cu_seqlens ? (long long)seq_row0 : (long long)b * p.lse_bs;
                     p.lse[(long long)head * p.lse_hs + base + qt * BT + r] = (m_used + log2f(l)) * LN2;
                 }
@@ -337,7 +330,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
     tc::tc_fence_before();
     __syncthreads();
-    if (warp == 16) {
+    if (warp == 4) {
         tc::tc_fence_after();
         tc::tmem_dealloc(tmem0, 512);
     }
@@ -362,7 +355,7 @@ int launch_fwd(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap
     static bool attr[64] = {};
     int r = ensure_smem(flash_fwd_kernel<HD>, fwd_smem_bytes<HD>(), attr);
     if (r) return r;
-    const int grid = p.n_pairs * p.H * p.B;
+    const int grid = p.n_tiles * p.H * p.B;
     flash_fwd_kernel<HD><<<grid, FWD_THREADS, fwd_smem_bytes<HD>(), st>>>(tmQ, tmK, tmV, p);
     return cudaGetLastError() == cudaSuccess ? 0 : 8;
 }
@@ -404,7 +397,7 @@ KB_API int kb_flash_fwd(const void* q, long long q_stride, int q_cols, int q_col
     p.lse_hs = cu_seqlens ? total : max_T;
     p.lse_bs = cu_seqlens ? 0 : (long long)H * max_T;
     p.q_col0 = q_col0; p.k_col0 = k_col0; p.v_col0 = v_col0;
-    p.n_pairs = (max_T + 2 * BT - 1) / (2 * BT);
+    p.n_tiles = (max_T + BT - 1) / BT;
     p.status = status;
     return hd == 128 ? launch_fwd<128>(tmQ, tmK, tmV, p, max_T, st) : launch_fwd<64>(tmQ, tmK, tmV, p, max_T, st);
 }

@@ -28,6 +28,13 @@ __device__ __forceinline__ bf16x8 ld8(const __nv_bfloat16* p) {
 __device__ __forceinline__ void st8(__nv_bfloat16* p, const bf16x8& x) {
     *reinterpret_cast<uint4*>(p) = *reinterpret_cast<const uint4*>(&x);
 }
+// p[0..8) += x, rounded to bf16 in the L2 (one 16-byte reduction: no read latency on the issuing
+// thread, unlike load-add-store).
+__device__ __forceinline__ void red_add8(__nv_bfloat16* p, const bf16x8& x) {
+    const uint4 v = *reinterpret_cast<const uint4*>(&x);
+    asm volatile("red.global.add.noftz.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+                 : "memory");
+}
 __device__ __forceinline__ void unpack8(const bf16x8& x, float* f) {
 #pragma unroll
     for (int i = 0; i < 4; ++i) {

@@ -156,7 +156,8 @@ __device__ __forceinline__ float3 block_sum3(float a, float b, float c, float4* 
 // ------------------------------------------------------------------------------------------------
 // phase 2 backward: persistent CTAs, thread = 8-column chunk(s), rows through a bulk-copy ring
 // ------------------------------------------------------------------------------------------------
-// stage rows: [dxn][o][partial][old dpartial]; the last two only when present
+// stage rows: [dxn][o][partial]; the last only when present.  An accumulated partial gradient is
+// added in the L2 (red), so its old value never travels to the SM.
 template <int CPT>
 __global__ void __launch_bounds__(512)
 route_p2_bwd_kernel(const bf16* __restrict__ dxn, const bf16* __restrict__ o, const bf16* __restrict__ part,
@@ -169,7 +170,7 @@ route_p2_bwd_kernel(const bf16* __restrict__ dxn, const bf16* __restrict__ o, co
     __shared__ int abort_flag;
     const bool has_p = part != nullptr;
     const bool acc = has_p && dpart_acc;
-    const int rows = 2 + (has_p ? 1 : 0) + (acc ? 1 : 0);
+    const int rows = 2 + (has_p ? 1 : 0);
     const uint32_t row_bytes = (uint32_t)D * 2;
     const int nchunks = D >> 3;
     const float invD = 1.f / (float)D;
@@ -188,7 +189,6 @@ route_p2_bwd_kernel(const bf16* __restrict__ dxn, const bf16* __restrict__ o, co
         bulk_g2s(base, dxn + tok * D, row_bytes, &full[st]);
         bulk_g2s(base + row_bytes, o + tok * D, row_bytes, &full[st]);
         if (has_p) bulk_g2s(base + 2 * row_bytes, part + tok * D, row_bytes, &full[st]);
-        if (acc) bulk_g2s(base + 3 * row_bytes, dpart + tok * D, row_bytes, &full[st]);
     };
     if (threadIdx.x == 0)
         for (int it = 0; it < stages && it < my_tokens; ++it) issue(it);
@@ -267,13 +267,8 @@ route_p2_bwd_kernel(const bf16* __restrict__ dxn, const bf16* __restrict__ o, co
                     dp[i] = pi * dh[i] + c_w * wv[k][i] - c_p * pf[i];
                     dw_acc[k][i] += c_w * pf[i];
                 }
-                if (acc) {
-                    float old[8];
-                    unpack8(ld8(base + 3 * D + c * 8), old);
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) dp[i] += old[i];
-                }
-                st8(dpart + tok * D + (size_t)c * 8, pack8(dp));
+                if (acc) red_add8(dpart + tok * D + (size_t)c * 8, pack8(dp));
+                else st8(dpart + tok * D + (size_t)c * 8, pack8(dp));
             }
         }
         if (threadIdx.x == 0) dlse[tok] = has_p ? dl : 0.f;
@@ -624,13 +619,8 @@ route_p1_bwd_kernel(P1Srcs srcs, P1Dsts dsts, int S, int Q, const float* __restr
                     }
                 }
                 bf16* dst = dsts.p[s] + tok * D + (size_t)c * 8;
-                if (dsts.acc_mask >> s & 1u) {
-                    float old[8];
-                    unpack8(ld8(dst), old);
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) du[i] += old[i];
-                }
-                st8(dst, pack8(du));
+                if (dsts.acc_mask >> s & 1u) red_add8(dst, pack8(du));
+                else st8(dst, pack8(du));
             }
         }
         __syncthreads();                     // every thread is done reading this stage and the tables
@@ -775,7 +765,7 @@ KB_API int kb_route_p2_bwd(const void* dxn, const void* o, const void* part, con
     const int nchunks = D / 8;
     const int cpt = (nchunks + 511) / 512;
     const int threads = ((nchunks + cpt - 1) / cpt + 31) / 32 * 32;
-    const int rows = 2 + (part ? 1 : 0) + (part && dpart_acc ? 1 : 0);
+    const int rows = 2 + (part ? 1 : 0);
     const size_t stage = (size_t)rows * D * 2;
     const int ctas_per_sm = 2;
     int stages = (int)((200 * 1024 / ctas_per_sm) / stage);

@@ -187,6 +187,43 @@ __host__ __device__ __forceinline__ uint32_t instr_desc_f16(int m, int n, int a_
     return d;
 }
 
+// Descriptor halves for issue loops that step through a tile: the low word carries the start
+// address (in 16-byte units) and the leading offset, the high word the stride offset, version and
+// swizzle mode.  Stepping the operand by `bytes` is one 32-bit add of (bytes >> 4) to the low
+// word (the 14-bit address field must not overflow: operands stay below 256 KB).
+struct DescHalves {
+    uint32_t lo, hi;
+};
+__device__ __forceinline__ DescHalves smem_desc_halves(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    DescHalves d;
+    d.lo = ((smem_addr & 0x3FFFF) >> 4) | (((lbo_bytes >> 4) & 0x3FFF) << 16);
+    d.hi = ((sbo_bytes >> 4) & 0x3FFF) | (1u << 14) | (2u << 29);
+    return d;
+}
+// D[tmem] (+)= A[smem] * B[smem] from descriptor halves; `acc` 0 overwrites the accumulator.
+__device__ __forceinline__ void mma_f16_h(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
+                                          uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "mov.b64 da, {%1, %2};\n\t"
+        "mov.b64 db, {%3, %4};\n\t"
+        "setp.ne.b32 p, %6, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(acc)
+        : "memory");
+}
+// A operand from tensor memory.
+__device__ __forceinline__ void mma_f16_ts_h(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t b_hi,
+                                             uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(acc)
+        : "memory");
+}
+
 __device__ __forceinline__ bool elect_one() {
     uint32_t pred;
     asm volatile(
