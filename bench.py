@@ -129,12 +129,30 @@ def run_native(args, rank, world, local):
     torch.manual_seed(1234)
     with torch.device("meta"):
         model = KotodamaModel(cfg)
-    comm = make_comm(args.backend, world)
+    tp = args.mode == "tp" and world > 1
+    if tp:
+        # tensor + sequence parallelism over all ranks: every rank sees the same global batch
+        from kotodama_b200.parallel.tp import TensorParallelComm, create_process_groups
+        tp_group, dp_group = create_process_groups(world, world)
+        comm = None
+        if args.backend in ("auto", "native"):
+            try:
+                from kotodama_b200.parallel.tp_native import FusedTensorParallelComm
+                comm = FusedTensorParallelComm(tp_group, dp_group)
+            except Exception as e:                         # noqa: BLE001 - reported in the JSON line
+                if args.backend == "native":
+                    raise
+                print(f"[bench] fused tensor-parallel kernels unavailable ({e}); library collectives", file=sys.stderr)
+        if comm is None:
+            comm = TensorParallelComm(tp_group, dp_group, sequence_parallel=True)
+    else:
+        comm = make_comm(args.backend, world)
     eng = TrainEngine.from_meta(model, cfg, device=f"cuda:{local}", dtype=torch.bfloat16, comm=comm, seed=1234,
-                                muon_lr=0.02, muon_ns_coefficients="gram_ns", gradient_clip=1.0)
+                                muon_lr=0.02, muon_ns_coefficients="gram_ns", gradient_clip=1.0, fp8=args.fp8)
     K, W = args.steps, args.warmup
-    dev_batches = [b.cuda() for b in token_batches(W + K, args.micro_batch, args.seq, cfg.vocab_size, 42 + rank, False)]
-    host_batches = token_batches(K, args.micro_batch, args.seq, cfg.vocab_size, 4242 + rank, True)
+    data_rank = 0 if tp else rank                          # TP ranks consume the same tokens
+    dev_batches = [b.cuda() for b in token_batches(W + K, args.micro_batch, args.seq, cfg.vocab_size, 42 + data_rank, False)]
+    host_batches = token_batches(K, args.micro_batch, args.seq, cfg.vocab_size, 4242 + data_rank, True)
     for i in range(W):
         eng.train_step([dev_batches[i]])
     eng.ops.check_status()
@@ -175,12 +193,24 @@ def run_native(args, rank, world, local):
     e2e_s = max_over_ranks(time.perf_counter() - t0, world)
     clocks = sampler.stop() if rank == 0 else {}
     eng.ops.check_status()
-    tokens = K * args.micro_batch * args.seq * world
+    tokens = K * args.micro_batch * args.seq * (1 if tp else world)
     mem = torch.cuda.max_memory_allocated() / 1e9
     return dict(dev_ms=dev_ms, e2e_s=e2e_s, tokens=tokens, launches=launches, clocks=clocks, loss=last,
                 mem_gb=mem, flops_per_token=cfg.flops_per_token(args.seq), extra={
                     "gemm": eng.ops.gemm_backend, "attention_library_calls": getattr(eng.ops, "attention_library_calls", 0),
-                    "comm": type(comm).__name__})
+                    "comm": type(comm).__name__, "fused_tp_fallback_calls": getattr(comm, "fallback_calls", None)})
+
+
+def run_serve(args, rank, world, local):
+    """BASELINE config 3: the paged-KV serving engine under 64 concurrent requests (prompts uniform in
+    [128, 2048], 256 new tokens each, greedy), tensor-parallel over all ranks when N > 1.  Wall-clock
+    with a device synchronize around every scheduler step: the host scheduling is part of serving."""
+    sys.path.insert(0, os.path.join(ROOT, "benchmarks"))
+    import serve_bench
+    a = argparse.Namespace(model=args.model, requests=64, min_prompt=128, max_prompt=2048, new_tokens=256, seed=0,
+                           device="cuda", passes=2, profile_decode_step=-1, op_times="", prefill_batch_tokens=8192,
+                           attn_res_blocks=args.attn_res_blocks)
+    return serve_bench.run(a, rank, world, local)
 
 
 def run_reference(args, rank, world, local):
@@ -209,6 +239,10 @@ def main() -> None:
     ap.add_argument("--attn-res-blocks", type=int, default=7)
     ap.add_argument("--backend", default="auto", choices=["auto", "native", "nccl"])
     ap.add_argument("--op-times", default="", help="write a per-op device-time table to this file")
+    ap.add_argument("--mode", default="dp", choices=["dp", "tp", "serve"],
+                    help="dp: data parallel (the headline); tp: tensor + sequence parallel over all ranks, one global "
+                         "batch of --micro-batch sequences; serve: 64-request paged-KV serving")
+    ap.add_argument("--fp8", action="store_true", help="block-scaled e4m3 projections (bf16 masters)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
@@ -218,6 +252,25 @@ def main() -> None:
             print(json.dumps({"impl": "reference", "unavailable": r["unavailable"]}))
         return
     rank, world, local = dist_setup(args.gpus)
+    if args.mode == "serve":
+        out = run_serve(args, rank, world, local)
+        if rank == 0:
+            print(json.dumps({
+                "metric": "serve_decode_tokens_per_sec", "value": out["decode_tok_s"], "unit": "tokens/s",
+                "n_gpus": world, "steps": out["new_tokens"], "warmup": 1, "higher_is_better": True, "scaling": "strong",
+                "ms_per_step": out["p50_token_latency_ms"], "vs_baseline": None, "dtype": "bf16",
+                "data": "synthetic uniform-random prompts, random-init weights",
+                "config": {"model": f"{args.model} AttnRes-Llama", "requests": out["requests"],
+                           "prompt_tokens": out["prompt_tokens"], "new_tokens": out["new_tokens"], "page": 16,
+                           "parallelism": f"tp{world}", "timing": "wall clock, device synchronize around every step, max over ranks"},
+                "prefill_tokens_per_sec": out["prefill_tok_s"], "p50_token_latency_ms": out["p50_token_latency_ms"],
+                "p95_token_latency_ms": out["p95_token_latency_ms"], "gpu_launches": out["kernel_launches"],
+                "e2e": {"value": out["decode_tok_s"], "unit": "tokens/s", "h2d_bytes_per_step": 64 * 28,
+                        "d2h_bytes_per_step": 64 * 8}, "impl": "native", "notes": out}))
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
     r = run_native(args, rank, world, local)
     if rank == 0:
         if "unavailable" in r:
@@ -230,13 +283,15 @@ def main() -> None:
             line = {
                 "metric": "train_tokens_per_sec", "value": round(value, 1), "unit": "tokens/s", "n_gpus": world,
                 "steps": K, "warmup": args.warmup, "ms_per_step": round(r["dev_ms"] / K, 3),
-                "higher_is_better": True, "scaling": "weak",
+                "higher_is_better": True, "scaling": "strong" if args.mode == "tp" else "weak",
                 "vs_baseline": round(value / (BASELINE_TOK_S_PER_GPU * world), 4),
-                "dtype": "bf16", "data": "synthetic uniform-random tokens, random-init weights",
+                "dtype": "fp8 e4m3 block-scaled projections, bf16 elsewhere" if args.fp8 else "bf16",
+                "data": "synthetic uniform-random tokens, random-init weights",
                 "config": {"model": f"{args.model} AttnRes-Llama ({args.attn_res_blocks} blocks)",
-                           "global_batch": args.micro_batch * world, "seq_len": args.seq,
+                           "global_batch": args.micro_batch * (1 if args.mode == "tp" else world), "seq_len": args.seq,
                            "micro_batch_per_gpu": args.micro_batch, "grad_accum": 1,
-                           "parallelism": f"dp{world}", "optimizer": "Muon+AdamW every step",
+                           "parallelism": (f"tp{world}+sp" if args.mode == "tp" else f"dp{world}"),
+                           "optimizer": "Muon+AdamW every step",
                            "l2": "per-step working set (tens of GB) exceeds the 126 MB L2; no explicit flush",
                            "baseline_note": "vs_baseline = value / (30 K tok/s per GPU x N), the reference's "
                                             "published 240 K tok/s on 8 GPUs (fp8, micro-batch 4)"},

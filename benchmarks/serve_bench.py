@@ -42,18 +42,31 @@ def main() -> None:
                     help="bracket this decode step of the last pass with cudaProfilerStart/Stop (ncu --profile-from-start off)")
     ap.add_argument("--op-times", default="", help="after the run: per-op device times of 8 eager decode steps, to this file")
     a = ap.parse_args()
-    cuda = a.device == "cuda"
     world, rank = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0"))
-    tp = None
     if world > 1:
         import torch.distributed as dist
-        from kotodama_b200.serve.tp import ServeTP
-        if cuda:
+        if a.device == "cuda":
             torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
-            a.device = f"cuda:{torch.cuda.current_device()}"
-            dist.init_process_group("nccl", device_id=torch.device(a.device))
+            dist.init_process_group("nccl", device_id=torch.device(f"cuda:{torch.cuda.current_device()}"))
         else:
             dist.init_process_group("gloo")
+    out = run(a, rank, world, int(os.environ.get("LOCAL_RANK", rank)))
+    if rank == 0:
+        print(json.dumps(out))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def run(a, rank: int, world: int, local: int) -> dict:
+    """The benchmark proper (process group already initialised when ``world > 1``); returns the result
+    dictionary on every rank (times are the slowest rank's)."""
+    cuda = a.device.startswith("cuda")
+    tp = None
+    if world > 1:
+        from kotodama_b200.serve.tp import ServeTP
+        if cuda:
+            a.device = f"cuda:{torch.cuda.current_device()}"
         tp = ServeTP()
     cfg = ModelConfig(**MODEL_PRESETS[a.model], attn_res=True, attn_res_n_blocks=7 if a.model != "tiny" else 2)
     with torch.device("meta"):
@@ -155,11 +168,7 @@ def main() -> None:
         out["prefill_plus_first_step_s"] = round(float(t[0]), 3)
         out["decode_tok_s"] = round(decode_tokens / max(float(t[1]), 1e-9), 1)
         out["p50_token_latency_ms"] = round(float(t[2]), 3)
-        dist.barrier()
-    if rank == 0:
-        print(json.dumps(out))
-    if tp is not None:
-        dist.destroy_process_group()
+    return out
 
 
 if __name__ == "__main__":

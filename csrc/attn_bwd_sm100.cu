@@ -232,8 +232,9 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         const bool valid = qrow < p.T;
         const long long sidx = ((long long)b * p.H + head) * p.T + qrow;
         const float nl = valid ? -p.lse[sidx] * LOG2E : -INFINITY;
-        const float nds = valid ? -p.dsum[sidx] * p.scale : 0.f;      // -D * scale
-        const float2 scale2 = make_float2(p.scale, p.scale), nds2 = make_float2(nds, nds);
+        // dS leaves as truncated bf16: its rounding bias rides on the scale constants (pack_bf16_trunc)
+        const float nds = valid ? -p.dsum[sidx] * p.scale * TRUNC_BIAS : 0.f;      // -D * scale
+        const float2 scale2 = make_float2(p.scale * TRUNC_BIAS, p.scale * TRUNC_BIAS), nds2 = make_float2(nds, nds);
         bool ok = true;
         float2 pv[16];                                                // probabilities of the tile in flight
         // P(j) only needs the scores, so it is computed while the tensor pipe still works on dP(j)
@@ -270,7 +271,7 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
 #pragma unroll
             for (int c = 0; c < 32; c += 2) {
                 const float2 d = __fmul2_rn(pv[c >> 1], __ffma2_rn(make_float2(dp[c], dp[c + 1]), scale2, nds2));
-                pk[c >> 1] = pack_bf16(d.x, d.y);
+                pk[c >> 1] = pack_bf16_trunc(d.x, d.y);
             }
             tc::tmem_st16(tmem0 + (j & 1) * 128 + qd * 32 + lane_base, pk);
             tc::tmem_st_wait();
@@ -423,8 +424,9 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             for (int e = 0; e < 4; ++e) {
                 const int c = lane + e * 32, qrow = qt * BT + c;
                 const bool valid = qrow < p.T;
-                dst[c] = valid ? -p.lse[base + qrow] * LOG2E : -INFINITY;
-                dst[BT + c] = valid ? -p.dsum[base + qrow] * p.scale : 0.f;
+                // both tables carry the truncation bias of the packed operands they feed (pack_bf16_trunc)
+                dst[c] = valid ? TRUNC_BIAS_LOG2 - p.lse[base + qrow] * LOG2E : -INFINITY;
+                dst[BT + c] = valid ? -p.dsum[base + qrow] * p.scale * TRUNC_BIAS : 0.f;
             }
             __syncwarp();
             if (lane == 0) tc::mbar_arrive(stat_full + st);
@@ -479,7 +481,7 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const int r = (warp & 3) * 32 + lane;
         const uint32_t lane_base = ((uint32_t)((warp & 3) * 32) << 16);
         const uint32_t tm_s = tmem0 + qd * 32 + lane_base, tm_d = tm_dp + qd * 32 + lane_base;
-        const float2 scale2 = make_float2(p.scale, p.scale);
+        const float2 scale2 = make_float2(p.scale * TRUNC_BIAS, p.scale * TRUNC_BIAS);
         bool ok = true;
         for (int t = 0; t < np; ++t) {
             const int st = t % STAT_RING;
@@ -508,7 +510,7 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                     }
                 }
 #pragma unroll
-                for (int c = 0; c < 16; ++c) pk[c] = pack_bf16(pv[c].x, pv[c].y);
+                for (int c = 0; c < 16; ++c) pk[c] = pack_bf16_trunc(pv[c].x, pv[c].y);
             }
             tc::tmem_st16(tm_s, pk);
             tc::tmem_st_wait();
@@ -530,7 +532,7 @@ attn_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                     const float2 pv = make_float2(__uint_as_float(pk[c >> 1] << 16), __uint_as_float(pk[c >> 1] & 0xffff0000u));
                     const float2 d = __fmul2_rn(pv, __ffma2_rn(make_float2(dp[c], dp[c + 1]), scale2,
                                                                *reinterpret_cast<const float2*>(nds + c)));
-                    pk[c >> 1] = pack_bf16(d.x, d.y);
+                    pk[c >> 1] = pack_bf16_trunc(d.x, d.y);
                 }
             }
             tc::tmem_st16(tm_d, pk);

@@ -103,6 +103,17 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
     return *reinterpret_cast<const uint32_t*>(&h);
 }
 
+// Two floats -> packed bf16 by keeping the upper halves (one byte-permute on the integer pipe).
+// The fp32 -> bf16 conversion instruction shares the special-function pipe with the exponentials,
+// which is the busiest pipe of these kernels.  Callers pre-multiply the values by TRUNC_BIAS
+// (folded into a constant they apply anyway), which turns truncation into rounding to within a
+// quarter of a bf16 step on average.
+constexpr float TRUNC_BIAS = 1.001953125f;         // 1 + 2^-9
+constexpr float TRUNC_BIAS_LOG2 = 0.0028150156f;   // log2(1 + 2^-9)
+__device__ __forceinline__ uint32_t pack_bf16_trunc(float a, float b) {
+    return __byte_perm(__float_as_uint(a), __float_as_uint(b), 0x7632);
+}
+
 // max of three (one instruction on sm_100)
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
     float d;

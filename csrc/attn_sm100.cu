@@ -1,8 +1,9 @@
 // Causal GQA flash-attention forward for sm_100a (head_dim 64 or 128, bf16), fixed-length
 // batches or packed variable-length sequences (cu_seqlens).
 //
-// One CTA owns one 128-row query tile of one head and walks its key/value tiles.  Six warps: four
-// softmax warps (thread = query row), one MMA-issuing warp, one TMA warp.  The score tile is
+// One CTA owns one 128-row query tile of one head and walks its key/value tiles.  Ten warps: eight
+// softmax warps (two threads per query row, 64 key columns each; the row maximum and sum cross
+// between them through shared memory), one MMA-issuing warp, one TMA warp.  The score tile is
 // double-buffered in tensor memory, so the scores of the next key tile are already there when the
 // softmax of the current one ends: the softmax warps never wait for the tensor pipe, and the
 // tensor pipe only has the P V product of a tile on the path between two softmax passes.
@@ -37,7 +38,7 @@ using namespace attn;
 constexpr int KST = 3, VST = 2;                    // ring depths
 constexpr float RESCALE_THRESHOLD = 8.0f;          // in log2 units
 constexpr int EMU = 2;                             // of every 4 pairs of exponentials, this many run on the FMA pipe
-constexpr int FWD_THREADS = 192;
+constexpr int FWD_THREADS = 320;                   // 8 softmax warps, MMA warp, TMA warp
 
 struct FlashParams {
     int B, T, H, KV;
@@ -67,7 +68,7 @@ __device__ long long g_attn_dbg[16];
 
 template <int HD>
 constexpr int fwd_smem_bytes() {
-    return (1 + KST + VST) * Tile<HD>::BYTES + 1024 + 256;
+    return (1 + KST + VST) * Tile<HD>::BYTES + 1024 + 256 + 6 * BT * 4;
 }
 
 template <int HD>
@@ -89,8 +90,12 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     uint64_t* s_full = v_empty + VST;              // [2] one per score buffer
     uint64_t* p_ready = s_full + 2;                // [2] one per score buffer
     uint64_t* o_done = p_ready + 2;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + 1);
+    uint64_t* xch = o_done + 1;                    // the two halves of a row exchange their maximum / sum
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(xch + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    // row maxima [tile parity][half][row] and, at the end, row sums [4 + half][row] of the two threads
+    // that share a query row
+    float* row_buf = reinterpret_cast<float*>(smem + (1 + KST + VST) * TB + 256);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // heavy tiles (late queries) first
@@ -116,13 +121,14 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         for (int i = 0; i < VST; ++i) { tc::mbar_init(v_full + i, 1); tc::mbar_init(v_empty + i, 1); }
         tc::mbar_init(s_full + 0, 1);
         tc::mbar_init(s_full + 1, 1);
-        tc::mbar_init(p_ready + 0, 4);
-        tc::mbar_init(p_ready + 1, 4);
+        tc::mbar_init(p_ready + 0, 8);
+        tc::mbar_init(p_ready + 1, 8);
         tc::mbar_init(o_done, 1);
+        tc::mbar_init(xch, 8);
         *abort_flag = 0;
         tc::fence_barrier_init();
     }
-    if (warp == 4) {
+    if (warp == 8) {
         tc::tmem_alloc(tmem_slot, 512);
         tc::tmem_relinquish();
     }
@@ -134,7 +140,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 
     if (n == 0) {
         // nothing to do (sequence shorter than the grid was sized for)
-    } else if (warp == 5) {
+    } else if (warp == 9) {
         // ------------------------------------------------------------ TMA
         if (lane == 0) {
             tc::prefetch_tmap(&tmQ);
@@ -161,7 +167,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             }
             if (!ok) atomicMax(p.status, (int)KB_TIMEOUT_TMA);
         }
-    } else if (warp == 4) {
+    } else if (warp == 8) {
         // ------------------------------------------------------------ MMA issue (one thread)
         if (lane == 0) {
             const uint32_t idesc_s = tc::instr_desc_f16(BT, BT, 1, 1, 0, 0);
@@ -199,10 +205,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 }
             } while (false);
         }
-    } else {
-        // ------------------------------------------------------------ softmax: thread = query row
-        const int r = warp * 32 + lane;                            // row inside the tile
-        const uint32_t lane_base = ((uint32_t)(warp * 32) << 16);
+    } else if (warp < 8) {
+        // ------------------------------------------------------------ softmax: two threads per query row
+        const int hf = warp >> 2;                                  // which 64 of the tile's 128 key columns
+        const int r = (warp & 3) * 32 + lane;                      // row inside the tile
+        const uint32_t lane_base = ((uint32_t)((warp & 3) * 32) << 16);
         const uint32_t tmem_o = tmem_oacc + lane_base;
         float m_used = -INFINITY, l = 0.f;
         bool ok = true;
@@ -221,30 +228,42 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             }
             tc::tc_fence_after();
             KB_TICK(1, tk)                                              // wait for the scores
-            float s[BT];
-#pragma unroll
-            for (int c = 0; c < BT; c += 32) tc::tmem_ld32(tmem_s + c, reinterpret_cast<uint32_t*>(s + c));
+            float s[64];
+            tc::tmem_ld32(tmem_s + hf * 64, reinterpret_cast<uint32_t*>(s));
+            tc::tmem_ld32(tmem_s + hf * 64 + 32, reinterpret_cast<uint32_t*>(s + 32));
             tc::tmem_ld_wait();
             KB_TICK(2, tk)                                              // tensor-memory load
             if (j == qt) {                                          // diagonal tile: causal mask
+                const int cmax = r - hf * 64;
 #pragma unroll
-                for (int c = 0; c < BT; ++c) s[c] = c <= r ? s[c] : -INFINITY;
+                for (int c = 0; c < 64; ++c) s[c] = c <= cmax ? s[c] : -INFINITY;
             }
             float mx8[8];                                           // eight chains: latency, not count, matters here
 #pragma unroll
             for (int i = 0; i < 8; ++i) mx8[i] = fmaxf(s[2 * i], s[2 * i + 1]);
 #pragma unroll
-            for (int c = 16; c < BT; c += 16) {
+            for (int c = 16; c < 64; c += 16) {
 #pragma unroll
                 for (int i = 0; i < 8; ++i) mx8[i] = fmax3(mx8[i], s[c + 2 * i], s[c + 2 * i + 1]);
             }
-            const float mx = fmax3(fmax3(mx8[0], mx8[1], mx8[2]), fmax3(mx8[3], mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])) *
-                             p.scale_log2;
+            float mx = fmax3(fmax3(mx8[0], mx8[1], mx8[2]), fmax3(mx8[3], mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7]));
+            // The row maximum spans both halves: exchange through shared memory.  The barrier also
+            // orders "both halves have read their scores" before either writes P over them.
+            row_buf[((j & 1) * 2 + hf) * BT + r] = mx;
+            __syncwarp();
+            if (lane == 0) tc::mbar_arrive(xch);
+            if (!tc::mbar_wait(xch, j & 1, abort_flag)) {           // bounded, like every other wait
+                if (lane == 0) atomicMax(p.status, (int)KB_TIMEOUT_EPI);
+                ok = false;
+                break;
+            }
+            mx = fmaxf(mx, row_buf[((j & 1) * 2 + (hf ^ 1)) * BT + r]) * p.scale_log2;
             const bool grow = mx > m_used + RESCALE_THRESHOLD;      // first tile: m_used = -inf -> true
             if (j == 0) {
                 m_used = mx;
             } else if (__any_sync(0xffffffffu, grow)) {
-                // O holds sums of p * v with p relative to m_used: move it to the new maximum
+                // O holds sums of p * v with p relative to m_used: move it to the new maximum.  Both
+                // halves see the same maxima and take the same branch; each rescales half of O's columns.
                 if (!tc::mbar_wait(o_done, (j - 1) & 1, abort_flag)) {
                     if (lane == 0) atomicMax(p.status, (int)KB_TIMEOUT_EPI);
                     ok = false;
@@ -254,34 +273,37 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 const float m_new = fmaxf(m_used, mx);
                 const float f = exp2f(m_used - m_new);
 #pragma unroll 1
-                for (int c = 0; c < HD; c += 32) {
+                for (int c = 0; c < HD / 2; c += 32) {
                     uint32_t o[32];
-                    tc::tmem_ld32(tmem_o + c, o);
+                    tc::tmem_ld32(tmem_o + hf * (HD / 2) + c, o);
                     tc::tmem_ld_wait();
 #pragma unroll
                     for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
-                    tc::tmem_st32(tmem_o + c, o);
+                    tc::tmem_st32(tmem_o + hf * (HD / 2) + c, o);
                 }
                 tc::tmem_st_wait();
                 l *= f;
                 m_used = m_new;
             }
-            KB_TICK(3, tk)                                              // max and rescale check
-            const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), nm2 = make_float2(-m_used, -m_used);
-            float2 sum2 = make_float2(0.f, 0.f);
+            KB_TICK(3, tk)                                              // max, exchange and rescale check
+            // P carries the truncation bias (see pack_bf16_trunc); so does the running sum, which the
+            // epilogue divides out
+            const float2 sc2 = make_float2(p.scale_log2, p.scale_log2);
+            const float2 nm2 = make_float2(TRUNC_BIAS_LOG2 - m_used, TRUNC_BIAS_LOG2 - m_used);
+            float2 sum2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll
-            for (int q4 = 0; q4 < 4; ++q4) {                        // 32 scores -> 16 packed columns at a time
+            for (int q4 = 0; q4 < 2; ++q4) {                        // 32 scores -> 16 packed columns at a time
                 uint32_t pk[16];
 #pragma unroll
                 for (int c = 0; c < 32; c += 2) {
                     const float2 x = __ffma2_rn(make_float2(s[q4 * 32 + c], s[q4 * 32 + c + 1]), sc2, nm2);
                     const float2 e = exp2_pair<EMU>(x, c >> 1);
-                    sum2 = __fadd2_rn(sum2, e);
-                    pk[c >> 1] = pack_bf16(e.x, e.y);
+                    sum2[(c >> 1) & 1] = __fadd2_rn(sum2[(c >> 1) & 1], e);
+                    pk[c >> 1] = pack_bf16_trunc(e.x, e.y);
                 }
-                tc::tmem_st16(tmem_s + q4 * 16, pk);
+                tc::tmem_st16(tmem_s + hf * 32 + q4 * 16, pk);
             }
-            l += sum2.x + sum2.y;
+            l += (sum2[0].x + sum2[0].y) + (sum2[1].x + sum2[1].y);
             KB_TICK(4, tk)                                              // exponentials, packing, store issue
             tc::tmem_st_wait();
             tc::tc_fence_before();
@@ -295,19 +317,31 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             g_attn_dbg[6] = n;
         }
 #endif
+        // the row sum spans both halves too
+        if (ok) {
+            row_buf[(4 + hf) * BT + r] = l;
+            __syncwarp();
+            if (lane == 0) tc::mbar_arrive(xch);
+            if (tc::mbar_wait(xch, n & 1, abort_flag)) {
+                l += row_buf[(4 + (hf ^ 1)) * BT + r];
+            } else {
+                if (lane == 0) atomicMax(p.status, (int)KB_TIMEOUT_EPI);
+                ok = false;
+            }
+        }
         if (ok) {
             if (tc::mbar_wait(o_done, (n - 1) & 1, abort_flag)) {
                 tc::tc_fence_after();
-                const float inv = 1.f / l;
+                const float inv = TRUNC_BIAS / l;
                 // Rows past the end of the sequence (zero-filled by TMA, or the first rows of the next
                 // sequence) are computed but never stored; for the valid rows the causal mask already
                 // excludes every key at or beyond the end.
                 const bool valid = qt * BT + r < Tb;
-                __nv_bfloat16* dst = p.out + (size_t)(seq_row0 + qt * BT + r) * p.out_stride + head * HD;
+                __nv_bfloat16* dst = p.out + (size_t)(seq_row0 + qt * BT + r) * p.out_stride + head * HD + hf * (HD / 2);
 #pragma unroll 1
-                for (int c = 0; c < HD; c += 32) {
+                for (int c = 0; c < HD / 2; c += 32) {
                     uint32_t o[32];
-                    tc::tmem_ld32(tmem_o + c, o);
+                    tc::tmem_ld32(tmem_o + hf * (HD / 2) + c, o);
                     tc::tmem_ld_wait();
                     if (valid) {
 #pragma unroll
@@ -319,9 +353,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                         }
                     }
                 }
-                if (valid) {
+                if (valid && hf == 0) {
                     const long long base = p.cu_seqlens ? (long long)seq_row0 : (long long)b * p.lse_bs;
-                    p.lse[(long long)head * p.lse_hs + base + qt * BT + r] = (m_used + log2f(l)) * LN2;
+                    p.lse[(long long)head * p.lse_hs + base + qt * BT + r] = (m_used + log2f(l) - TRUNC_BIAS_LOG2) * LN2;
                 }
             } else if (lane == 0) {
                 atomicMax(p.status, (int)KB_TIMEOUT_EPI);
@@ -330,7 +364,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
     tc::tc_fence_before();
     __syncthreads();
-    if (warp == 4) {
+    if (warp == 8) {
         tc::tc_fence_after();
         tc::tmem_dealloc(tmem0, 512);
     }

@@ -74,13 +74,13 @@ KB_API int kb_flag_signal(void* const* peer_flags, int world, int rank, int slot
     PeerPtrs pp;
     for (int i = 0; i < 8; ++i) pp.p[i] = i < world ? peer_flags[i] : nullptr;
     flag_signal_kernel<<<1, 32, 0, st>>>(pp, world, rank, slot, epoch);
-    return 0;
+    return kb_launch_status();
 }
 KB_API int kb_flag_wait(const int* flags, int world, int slot, int epoch, double limit_s, int* status,
                         cudaStream_t st) {
     if (world < 1 || world > 8) return 5;
     flag_wait_kernel<<<1, 32, 0, st>>>(flags, world, slot, epoch, (unsigned long long)(limit_s * 1e9), status);
-    return 0;
+    return kb_launch_status();
 }
 
 // out[i] = scale * sum_r peer[r][offset + i]  for i in [0, n); out is this rank's own buffer range.
@@ -144,7 +144,7 @@ KB_API int kb_reduce_to_owner(void* const* peer_bufs, int world, long long offse
     if (blocks < 1) blocks = 1;
     if (blocks > max_ctas) blocks = max_ctas;
     reduce_to_owner_kernel<<<(int)blocks, 256, 0, st>>>(pp, world, offset, n, scale, (bf16*)out);
-    return 0;
+    return kb_launch_status();
 }
 
 // Two-shot all-reduce of [offset, offset+n): rank r owns the r-th of `world` equal slices
@@ -182,7 +182,7 @@ KB_API int kb_allreduce_slices(void* const* peer_bufs, int world, int rank, long
     if (blocks < 1) blocks = 1;
     if (blocks > max_ctas) blocks = max_ctas;
     allreduce_slices_kernel<<<(int)blocks, 256, 0, st>>>(pp, world, rank, offset, n, scale);
-    return 0;
+    return kb_launch_status();
 }
 
 // Sum of one float per rank; doubles as a barrier.  vals layout on every rank: float vals[2][8]
@@ -224,7 +224,7 @@ KB_API int kb_scalar_allreduce(void* const* peer_vals, void* const* peer_flags, 
     }
     scalar_allreduce_kernel<<<1, 32, 0, st>>>(pv, pf, world, rank, slot, epoch, in, out,
                                               (unsigned long long)(limit_s * 1e9), status);
-    return 0;
+    return kb_launch_status();
 }
 
 // Owner's Muon parameter write, broadcast: every rank's arena gets p*decay - alpha*orth.
@@ -287,7 +287,7 @@ KB_API int kb_muon_apply_bcast(void* const* peer_params, int world, int rank, lo
     dim3 grid((C + 63) / 64, (R + 63) / 64), block(8, 32);
     muon_apply_bcast_kernel<<<grid, block, 0, st>>>(pp, world, rank, offset, (const __half*)orth, R, C,
                                                     wd > 0 ? 1.f - lr * wd : 1.f, lr * scale, transposed);
-    return 0;
+    return kb_launch_status();
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -359,7 +359,7 @@ KB_API int kb_ag_push(const void* src, long long n_elems, void* const* peer_stag
     if (blocks > max_ctas) blocks = max_ctas;
     ag_push_kernel<<<(int)blocks, 256, 0, st>>>((const uint4*)src, nvec, ps, pr, world, first, count, epoch, done,
                                                 need, counter, (unsigned long long)(limit_s * 1e9), status);
-    return 0;
+    return kb_launch_status();
 }
 
 // out[i] = sum_s slab[s][i] (+ residual[i]) once cnt[s] >= expected (arrivals of this call) for
@@ -424,7 +424,7 @@ KB_API int kb_rs_reduce(const void* slabs, long long slab_elems, int* cnt, int e
     rs_reduce_kernel<<<(int)blocks, 256, 0, st>>>((const bf16*)slabs, slab_elems, cnt, expected, world,
                                                   (const bf16*)residual, (bf16*)out, pd, done_epoch, counter,
                                                   (unsigned long long)(limit_s * 1e9), status);
-    return 0;
+    return kb_launch_status();
 }
 
 // One-shot all-reduce of a small bf16 vector (decode-time row-parallel outputs): every rank's
@@ -489,7 +489,7 @@ KB_API int kb_allreduce_oneshot(void* const* peer_parts, void* const* peer_flags
     if (blocks > max_ctas) blocks = max_ctas;
     allreduce_oneshot_kernel<<<(int)blocks, 256, 0, st>>>(pp, pf, world, rank, slot, epoch, n, (const bf16*)residual,
                                                           (bf16*)out, (unsigned long long)(limit_s * 1e9), status);
-    return 0;
+    return kb_launch_status();
 }
 
 // Graph-replayable all-reduce for decode-sized activations (row-parallel projections under tensor
@@ -574,5 +574,5 @@ KB_API int kb_allreduce_push(const void* x, long long n, long long slot_elems, v
     allreduce_push_kernel<<<(int)blocks, 256, 0, st>>>((const uint4*)x, n >> 3, slot_elems >> 3, pr, pf, world, rank,
                                                        (const bf16*)residual, (bf16*)out, epoch_ptr, counters,
                                                        (unsigned long long)(limit_s * 1e9), status);
-    return 0;
+    return kb_launch_status();
 }

@@ -13,6 +13,18 @@
 enum KbStatus : int { KB_OK = 0, KB_TIMEOUT_TMA = 1, KB_TIMEOUT_MMA = 2, KB_TIMEOUT_EPI = 3, KB_TIMEOUT_PEER = 4,
                       KB_BAD_ARG = 5 };
 
+// Launcher return code for "the launch itself was refused" (bad grid, shared-memory attribute, ...).
+#define KB_LAUNCH_FAILED 9
+// After a <<<>>>: 0, or KB_LAUNCH_FAILED when the runtime rejected the launch.
+static inline int kb_launch_status() { return cudaGetLastError() == cudaSuccess ? 0 : KB_LAUNCH_FAILED; }
+// Function attributes (dynamic shared memory opt-in) belong to one device: `flags[64]` remembers
+// which devices have been set up.  Returns the flag of the current device, or null.
+static inline bool* kb_device_flag(bool* flags) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    return flags + dev;
+}
+
 struct __align__(16) bf16x8 {
     __nv_bfloat162 v[4];
 };

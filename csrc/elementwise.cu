@@ -349,7 +349,7 @@ KB_API int kb_route_norm_fwd(const void* const* srcs, int S, const void* q, cons
     const int grid = N < kb_num_sms() * 8 ? N : kb_num_sms() * 8;
     ROUTE_DISPATCH((route_norm_fwd_kernel<MAXS, CPT><<<grid, threads, 0, st>>>(
         rs, S, (const bf16*)q, (const bf16*)rn_w, (const bf16*)n_w, (bf16*)xn, alpha, r, logit, rstd, N, D, eps)))
-    return 0;
+    return kb_launch_status();
 }
 
 KB_API int kb_route_norm_bwd(const void* const* srcs, void* const* dsts, unsigned acc_mask, int S, const void* dxn,
@@ -370,7 +370,7 @@ KB_API int kb_route_norm_bwd(const void* const* srcs, void* const* dsts, unsigne
     ROUTE_DISPATCH((route_norm_bwd_kernel<MAXS, CPT><<<grid, threads, 0, st>>>(
         rs, ds, S, (const bf16*)dxn, (const bf16*)q, (const bf16*)rn_w, (const bf16*)n_w, alpha, r, logit, rstd,
         dw_part, dnw_part, N, D)))
-    return 0;
+    return kb_launch_status();
 }
 
 // out[c] = sum_r part[r, c] ; block (128, 8): 8 row groups reduced through shared memory.
@@ -391,7 +391,7 @@ __global__ void colsum_kernel(const float* __restrict__ part, float* __restrict_
 }
 KB_API int kb_colsum(const float* part, float* out, int R, int C, cudaStream_t st) {
     colsum_kernel<<<(C + 127) / 128, dim3(128, 8), 0, st>>>(part, out, R, C);
-    return 0;
+    return kb_launch_status();
 }
 
 // ============================================================================ QK-norm + RoPE
@@ -529,7 +529,7 @@ KB_API int kb_qknorm_rope_fwd(const void* qkv, const void* qw, const void* kw, c
     if (hd == 128) { if (norm) QK_FWD(2, true); else QK_FWD(2, false); }
     else if (hd == 64) { if (norm) QK_FWD(1, true); else QK_FWD(1, false); }
     else return 5;
-    return 0;
+    return kb_launch_status();
 }
 
 KB_API int kb_qknorm_rope_bwd(const void* dqk, const void* qkv, const void* qw, const void* kw, const float* cosT,
@@ -543,7 +543,7 @@ KB_API int kb_qknorm_rope_bwd(const void* dqk, const void* qkv, const void* qw, 
     if (hd == 128) { if (norm) QK_BWD(2, true); else QK_BWD(2, false); }
     else if (hd == 64) { if (norm) QK_BWD(1, true); else QK_BWD(1, false); }
     else return 5;
-    return 0;
+    return kb_launch_status();
 }
 
 // ============================================================================ SwiGLU
@@ -592,12 +592,12 @@ static inline int ew_grid(long long work, int threads) {
 KB_API int kb_swiglu_fwd(const void* gu, void* act, long long N, int F, cudaStream_t st) {
     if (F % 8) return 5;
     swiglu_fwd_kernel<<<ew_grid(N * (F / 8), 256), 256, 0, st>>>((const bf16*)gu, (bf16*)act, N, F);
-    return 0;
+    return kb_launch_status();
 }
 KB_API int kb_swiglu_bwd(const void* gu, const void* dact, void* dgu, long long N, int F, cudaStream_t st) {
     if (F % 8) return 5;
     swiglu_bwd_kernel<<<ew_grid(N * (F / 8), 256), 256, 0, st>>>((const bf16*)gu, (const bf16*)dact, (bf16*)dgu, N, F);
-    return 0;
+    return kb_launch_status();
 }
 
 // ============================================================================ CE + z-loss
@@ -671,7 +671,7 @@ KB_API int kb_ce_zloss(void* logits, const long long* labels, float* row_ce, flo
                        float z_w, float scale, int rows, int V, int write_grad, cudaStream_t st) {
     if (V % 8) return 5;
     ce_zloss_kernel<<<rows, 512, 0, st>>>((bf16*)logits, labels, row_ce, row_z, inv_count, z_w, scale, V, write_grad);
-    return 0;
+    return kb_launch_status();
 }
 
 // ============================================================================ embedding
@@ -701,12 +701,12 @@ __global__ void embedding_bwd_kernel(const long long* __restrict__ ids, const bf
 KB_API int kb_embedding_fwd(const long long* ids, const void* w, void* out, int N, int D, cudaStream_t st) {
     if (D % 8) return 5;
     embedding_fwd_kernel<<<ew_grid((long long)N * (D / 8), 256), 256, 0, st>>>(ids, (const bf16*)w, (bf16*)out, N, D);
-    return 0;
+    return kb_launch_status();
 }
 KB_API int kb_embedding_bwd(const long long* ids, const void* dout, void* dw, int N, int D, cudaStream_t st) {
     if (D % 2) return 5;
     embedding_bwd_kernel<<<ew_grid((long long)N * (D / 2), 256), 256, 0, st>>>(ids, (const bf16*)dout, (bf16*)dw, N, D);
-    return 0;
+    return kb_launch_status();
 }
 
 // ============================================================================ reductions
@@ -743,11 +743,11 @@ KB_API int kb_sumsq(const void* x, long long n, int dtype, float* partial, float
     else if (dtype == 1) sumsq_partial_kernel<__half><<<grid, 256, 0, st>>>((const __half*)x, n, partial);
     else sumsq_partial_kernel<float><<<grid, 256, 0, st>>>((const float*)x, n, partial);
     sum_final_kernel<<<1, 256, 0, st>>>(partial, grid, out, accumulate);
-    return 0;
+    return kb_launch_status();
 }
 KB_API int kb_sum_f32(const float* x, int n, float* out, cudaStream_t st) {
     sum_final_kernel<<<1, 256, 0, st>>>(x, n, out, 0);
-    return 0;
+    return kb_launch_status();
 }
 
 // ============================================================================ optimizers
@@ -772,7 +772,7 @@ KB_API int kb_adamw(void* p, const void* g, float* m, float* v, long long n, con
     const float bc1 = 1.f - powf(b1, (float)step), bc2 = 1.f - powf(b2, (float)step);
     adamw_kernel<<<ew_grid(n, 256), 256, 0, st>>>((bf16*)p, (const bf16*)g, m, v, n, gscale, lr, b1, b2, eps, wd, bc1,
                                                  sqrtf(bc2));
-    return 0;
+    return kb_launch_status();
 }
 
 // Muon momentum: buf = mom*buf + g*gs (bf16), x = (nesterov ? mom*buf + g*gs : buf) as fp16,
@@ -800,7 +800,7 @@ KB_API int kb_muon_momentum(const void* g, void* buf, void* x, long long n, cons
                             int nesterov, float* partial, float* sumsq_out, cudaStream_t st) {
     muon_momentum_kernel<<<1024, 256, 0, st>>>((const bf16*)g, (bf16*)buf, (__half*)x, n, gscale, mom, nesterov, partial);
     sum_final_kernel<<<1, 256, 0, st>>>(partial, 1024, sumsq_out, 0);
-    return 0;
+    return kb_launch_status();
 }
 
 // x *= 1/(sqrt(sumsq)+1e-7)   (fp16, in place)
@@ -811,7 +811,7 @@ __global__ void ns_normalize_kernel(__half* __restrict__ x, long long n, const f
 }
 KB_API int kb_ns_normalize(void* x, long long n, const float* sumsq, cudaStream_t st) {
     ns_normalize_kernel<<<ew_grid(n, 256), 256, 0, st>>>((__half*)x, n, sumsq);
-    return 0;
+    return kb_launch_status();
 }
 
 // p = p*(1-lr*wd) - lr*scale*orth   (p bf16 [R,C]; orth fp16 [R,C] or [C,R] when transposed)
@@ -848,7 +848,7 @@ KB_API int kb_muon_apply(void* p, const void* orth, int R, int C, float lr, floa
     dim3 grid((C + 31) / 32, (R + 31) / 32), block(32, 8);
     muon_apply_kernel<<<grid, block, 0, st>>>((bf16*)p, (const __half*)orth, R, C, wd > 0 ? 1.f - lr * wd : 1.f,
                                               lr * scale, transposed);
-    return 0;
+    return kb_launch_status();
 }
 
 // out[C,R] = in[R,C]^T for 16-bit elements.
@@ -874,7 +874,7 @@ __global__ void transpose16_kernel(const uint16_t* __restrict__ in, uint16_t* __
 KB_API int kb_transpose16(const void* in, void* out, int R, int C, cudaStream_t st) {
     dim3 grid((C + 63) / 64, (R + 63) / 64), block(32, 8);
     transpose16_kernel<<<grid, block, 0, st>>>((const uint16_t*)in, (uint16_t*)out, R, C);
-    return 0;
+    return kb_launch_status();
 }
 
 // y = a*x + y_scale*y style helpers for Newton-Schulz epilogues done outside the GEMM (fp16).
@@ -884,7 +884,7 @@ __global__ void axpby_half_kernel(__half* __restrict__ y, const __half* __restri
 }
 KB_API int kb_axpby_half(void* y, const void* x, long long n, float a, float b, cudaStream_t st) {
     axpby_half_kernel<<<ew_grid(n, 256), 256, 0, st>>>((__half*)y, (const __half*)x, n, a, b);
-    return 0;
+    return kb_launch_status();
 }
 
 // Mirror the upper triangle of square 16-bit matrices into the lower one: A[i][j] = A[j][i], i > j.
@@ -914,7 +914,7 @@ __global__ void mirror_upper16_kernel(uint16_t* __restrict__ a, int R, long long
 KB_API int kb_mirror_upper16(void* a, int R, long long ld, int batch, long long batch_stride, cudaStream_t st) {
     dim3 grid((R + 63) / 64, (R + 63) / 64, batch), block(32, 8);
     mirror_upper16_kernel<<<grid, block, 0, st>>>((uint16_t*)a, R, ld, batch_stride);
-    return 0;
+    return kb_launch_status();
 }
 
 // dst = bf16(src + beta * addend)  (addend optional): finishes a split-K GEMM.  With `rezero` the
@@ -932,7 +932,7 @@ __global__ void f32_to_bf16_add_kernel(float* __restrict__ src, const bf16* __re
 KB_API int kb_f32_to_bf16_add(float* src, const void* addend, float beta, void* dst, long long n, int rezero,
                               cudaStream_t st) {
     f32_to_bf16_add_kernel<<<ew_grid(n, 256), 256, 0, st>>>(src, (const bf16*)addend, beta, (bf16*)dst, n, rezero);
-    return 0;
+    return kb_launch_status();
 }
 
 KB_API int kb_last_error() { return (int)cudaGetLastError(); }

@@ -661,14 +661,16 @@ static int launch_gemm2(const void* A, const void* B, void* C, const void* Cin, 
     if (sym_upper && M != N) return 5;
     if ((lda & 7) || (ldb & 7) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15)) return 6;
     if (batch > 1 && ((a_bs & 7) || (b_bs & 7))) return 6;
-    static bool attr_set = false;
-    if (!attr_set) {
+    static bool attr_flags[64] = {};
+    bool* attr_set_p = kb_device_flag(attr_flags);
+    if (!attr_set_p) return 7;
+    if (!*attr_set_p) {
         if (cudaFuncSetAttribute(gemm_tcgen05_2cta_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  Cfg<1>::SMEM) != cudaSuccess ||
             cudaFuncSetAttribute(gemm_tcgen05_2cta_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  Cfg<2>::SMEM) != cudaSuccess)
             return 7;
-        attr_set = true;
+        *attr_set_p = true;
     }
     CUtensorMap tmA, tmB;
     int r;
@@ -736,7 +738,7 @@ static int launch_gemm2(const void* A, const void* B, void* C, const void* Cin, 
     if (tiles < pairs) pairs = (int)tiles;
     if (wide) gemm_tcgen05_2cta_kernel<2><<<2 * pairs, 192, Cfg<2>::SMEM, st>>>(tmA, tmB, p);
     else gemm_tcgen05_2cta_kernel<1><<<2 * pairs, 192, Cfg<1>::SMEM, st>>>(tmA, tmB, p);
-    return 0;
+    return kb_launch_status();
 }
 
 // Same contract as kb_gemm (no split-K); launched as clusters of two CTAs.

@@ -339,11 +339,13 @@ KB_API int kb_gemm_fp8(const void* A, const void* B, const float* sa, const floa
     if (b_gran != 1 && b_gran != 128) return 5;
     if (out_type != 1 && out_type != 2) return 5;
     if ((lda & 15) || (ldb & 15) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15)) return 6;
-    static bool attr_set = false;
-    if (!attr_set) {
+    static bool attr_flags[64] = {};
+    bool* attr_set_p = kb_device_flag(attr_flags);
+    if (!attr_set_p) return 7;
+    if (!*attr_set_p) {
         if (cudaFuncSetAttribute(gemm_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
             return 7;
-        attr_set = true;
+        *attr_set_p = true;
     }
     CUtensorMap tmA, tmB;
     int r = make_tmap8(&tmA, A, K, M, lda, BK, BM);

@@ -525,14 +525,16 @@ static int launch_gemm(const void* A, const void* B, void* C, const void* Cin, i
     if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return 5;
     if ((lda & 7) || (ldb & 7) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15)) return 6;
     if (batch > 1 && ((a_bs & 7) || (b_bs & 7))) return 6;
-    static bool attr_set = false;
-    if (!attr_set) {
+    static bool attr_flags[64] = {};
+    bool* attr_set_p = kb_device_flag(attr_flags);
+    if (!attr_set_p) return 7;
+    if (!*attr_set_p) {
         if (cudaFuncSetAttribute(gemm_tcgen05_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  SMEM_BYTES) != cudaSuccess ||
             cudaFuncSetAttribute(gemm_tcgen05_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  SMEM_BYTES) != cudaSuccess)
             return 7;
-        attr_set = true;
+        *attr_set_p = true;
     }
     CUtensorMap tmA, tmB;
     int r;
@@ -562,7 +564,7 @@ static int launch_gemm(const void* A, const void* B, void* C, const void* Cin, i
         memset(&none, 0, sizeof(none));
         gemm_tcgen05_kernel<false><<<grid, 192, SMEM_BYTES, st>>>(tmA, tmB, p, none);
     }
-    return 0;
+    return kb_launch_status();
 }
 
 }  // namespace

@@ -171,18 +171,18 @@ KB_API int kb_quant_rows(const void* x, long long ldx, void* q, long long ldq, f
     long long blocks = (warps + 7) / 8;
     if (blocks > 148 * 16) blocks = 148 * 16;
     quant_rows_kernel<<<(int)blocks, 256, 0, st>>>((const __nv_bfloat16*)x, ldx, (uint8_t*)q, ldq, s, M, K / 128);
-    return 0;
+    return kb_launch_status();
 }
 KB_API int kb_quant_blocks(const void* w, long long ldw, void* q, float* s, void* qt, float* st_, int N, int K,
                            cudaStream_t st) {
     if (N <= 0 || K <= 0 || (K & 127) || (N & 15) || (ldw & 7)) return 5;
     dim3 grid(K / 128, (N + 127) / 128);
     quant_blocks_kernel<<<grid, 256, 0, st>>>((const __nv_bfloat16*)w, ldw, (uint8_t*)q, s, (uint8_t*)qt, st_, N, K);
-    return 0;
+    return kb_launch_status();
 }
 KB_API int kb_quant_cols_t(const void* x, long long ldx, void* qt, float* s, int M, int N, cudaStream_t st) {
     if (M <= 0 || N <= 0 || (M & 127) || (N & 7) || (ldx & 7)) return 5;
     dim3 grid(M / 128, (N + 127) / 128);
     quant_cols_t_kernel<<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, ldx, (uint8_t*)qt, s, M, N);
-    return 0;
+    return kb_launch_status();
 }

@@ -28,6 +28,7 @@ constexpr int MAXQ = 8;          // queries per phase-1 launch
 constexpr int MAXS = 8;          // committed sources per phase-1 launch
 constexpr int KSW = 16;          // 16-column contraction steps per warp (warp slice = 256 columns)
 constexpr int RB_STAGES = 4;
+constexpr int RB_DYN_SMEM = 200 * 1024;   // dynamic shared memory of the ring kernels (their static tables take another 23 KB)
 
 __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
     asm volatile("cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
@@ -332,139 +333,192 @@ __device__ __forceinline__ uint32_t frag_addr(uint32_t rows, uint32_t pitch, int
 // ldmatrix on different banks.
 __host__ __device__ __forceinline__ uint32_t p1_pitch(int D) { return (uint32_t)D * 2 + 16; }
 
+// Shared skeleton of the two phase-1 kernels.  The last warp of the CTA is the producer: it
+// streams one token's rows per ring stage and recycles a stage when every compute warp has
+// released it (mbarrier, no CTA-wide barrier).  The compute warps meet once per token, after
+// writing their partial dot products; each of them then finishes the token's small softmax
+// algebra redundantly in registers, so nothing else has to be synchronised.
+struct P1Smem {
+    float scr[2][16][80];                      // [token parity][warp]: 64 partial dots [q][s], 8 partial squared norms
+    __align__(16) float tab[16][3][64];        // per warp: coefficient tables [s][q] for the per-element pass
+    uint64_t full[RB_STAGES], empty[RB_STAGES], meet;
+    int abort_flag;
+};
+
+// Meeting point of the compute warps for token `it` (bounded wait; false = give up).
+__device__ __forceinline__ bool p1_meet(P1Smem& sm, int it, int lane) {
+    __syncwarp();
+    if (lane == 0) tc::mbar_arrive(&sm.meet);
+    return tc::mbar_wait(&sm.meet, it & 1, &sm.abort_flag);
+}
+
+// Sum over the compute warps of the partials this lane owns: dots (q = g, s = 2t, 2t+1) and the
+// squared norms of the same two sources.
+__device__ __forceinline__ void p1_gather(const P1Smem& sm, int par, int ncw, int g, int t, float2& dots, float2& ss) {
+    dots = make_float2(0.f, 0.f);
+    ss = make_float2(0.f, 0.f);
+    for (int w = 0; w < ncw; ++w) {
+        const float2 d = *reinterpret_cast<const float2*>(&sm.scr[par][w][g * 8 + 2 * t]);
+        const float2 q = *reinterpret_cast<const float2*>(&sm.scr[par][w][64 + 2 * t]);
+        dots.x += d.x; dots.y += d.y;
+        ss.x += q.x; ss.y += q.y;
+    }
+}
+__device__ __forceinline__ float quad_max(float v) {
+    v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 1));
+    return fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 2));
+}
+__device__ __forceinline__ float quad_sum(float v) {
+    v += __shfl_xor_sync(0xffffffffu, v, 1);
+    return v + __shfl_xor_sync(0xffffffffu, v, 2);
+}
+
 template <int THREADS>
 __global__ void __launch_bounds__(THREADS, 1)
 route_p1_fwd_kernel(P1Srcs srcs, int S, int Q, const float* __restrict__ wf, bf16* __restrict__ o,
                     float* __restrict__ lse, float* __restrict__ r_g, float* __restrict__ logit_g, int N, int D,
                     float eps, int stages, int* status) {
     extern __shared__ __align__(128) uint8_t smem[];
-    __shared__ float scr[16][80];              // per warp: 64 dots [q][s] and 8 squared norms
-    __shared__ float fin[80];
-    __shared__ __align__(16) float pt[MAXS][MAXQ];   // probabilities, one row of 8 queries per source
-    __shared__ uint64_t full[RB_STAGES];
-    __shared__ int abort_flag;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    __shared__ P1Smem sm;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int ncw = (blockDim.x >> 5) - 1;                        // compute warps; the last warp is the producer
     const int g = lane >> 2, t = lane & 3;
     const uint32_t pitch = p1_pitch(D);
     const uint32_t row_bytes = (uint32_t)D * 2;
     const int nchunks = D >> 3, nks = D >> 4;
     const float invD = 1.f / (float)D;
     if (threadIdx.x == 0) {
-        for (int s = 0; s < stages; ++s) tc::mbar_init(&full[s], 1);
-        abort_flag = 0;
+        for (int i = 0; i < stages; ++i) {
+            tc::mbar_init(&sm.full[i], 1);
+            tc::mbar_init(&sm.empty[i], ncw);
+        }
+        tc::mbar_init(&sm.meet, ncw);
+        sm.abort_flag = 0;
         tc::fence_barrier_init();
     }
     __syncthreads();
     const int my_tokens = blockIdx.x < N ? (N - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-    auto issue = [&](int it) {
-        const int st = it % stages;
-        const size_t tok = (size_t)blockIdx.x + (size_t)it * gridDim.x;
-        uint8_t* base = smem + (size_t)st * S * pitch;
-        tc::mbar_expect_tx(&full[st], S * row_bytes);
-        for (int s = 0; s < S; ++s) bulk_g2s(base + (size_t)s * pitch, srcs.p[s] + tok * D, row_bytes, &full[st]);
-    };
-    if (threadIdx.x == 0)
-        for (int it = 0; it < stages && it < my_tokens; ++it) issue(it);
 
-    // the queries' A fragments for this warp's column slice stay in registers for the whole kernel
-    uint32_t wa0[KSW], wa2[KSW];
-#pragma unroll
-    for (int i = 0; i < KSW; ++i) {
-        const int ks = warp * KSW + i;
-        wa0[i] = wa2[i] = 0;
-        if (ks < nks && g < Q) {
-            const float* wr = wf + (size_t)g * D + ks * 16 + 2 * t;
-            const __nv_bfloat162 lo = __floats2bfloat162_rn(wr[0], wr[1]), hi = __floats2bfloat162_rn(wr[8], wr[9]);
-            wa0[i] = *reinterpret_cast<const uint32_t*>(&lo);
-            wa2[i] = *reinterpret_cast<const uint32_t*>(&hi);
+    if (warp == ncw) {
+        // ------------------------------------------------------------ producer
+        if (lane == 0) {
+            for (int it = 0; it < my_tokens; ++it) {
+                const int st = it % stages;
+                if (!tc::mbar_wait(&sm.empty[st], ((it / stages) & 1) ^ 1, &sm.abort_flag)) {
+                    atomicMax(status, (int)KB_TIMEOUT_TMA);
+                    break;
+                }
+                const size_t tok = (size_t)blockIdx.x + (size_t)it * gridDim.x;
+                uint8_t* base = smem + (size_t)st * S * pitch;
+                tc::mbar_expect_tx(&sm.full[st], S * row_bytes);
+                for (int q = 0; q < S; ++q) bulk_g2s(base + (size_t)q * pitch, srcs.p[q] + tok * D, row_bytes, &sm.full[st]);
+            }
         }
-    }
-
-    for (int it = 0; it < my_tokens; ++it) {
-        const int st = it % stages;
-        const size_t tok = (size_t)blockIdx.x + (size_t)it * gridDim.x;
-        if (!tc::mbar_wait(&full[st], (it / stages) & 1, &abort_flag)) {
-            if (threadIdx.x == 0) atomicMax(status, (int)KB_TIMEOUT_TMA);
-            break;
-        }
-        const uint8_t* stage = smem + (size_t)st * S * pitch;
-        const uint32_t rows = smem_u32(stage);
-        float cd[4] = {0.f, 0.f, 0.f, 0.f}, cg[4] = {0.f, 0.f, 0.f, 0.f};
+    } else {
+        // ------------------------------------------------------------ compute
+        // the queries' A fragments for this warp's column slice stay in registers for the whole kernel
+        uint32_t wa0[KSW], wa2[KSW];
 #pragma unroll
         for (int i = 0; i < KSW; ++i) {
             const int ks = warp * KSW + i;
-            if (ks < nks) {
-                uint32_t v0, v1;
-                ldsm_x2(v0, v1, frag_addr(rows, pitch, S, ks * 16, lane));
-                mma_16816(cd, wa0[i], wa2[i], v0, v1);        // dots[q = g][s = 2t, 2t + 1]
-                mma_16816(cg, v0, v1, v0, v1);                // gram[s = g][s' = 2t, 2t + 1]
+            wa0[i] = wa2[i] = 0;
+            if (ks < nks && g < Q) {
+                const float* wr = wf + (size_t)g * D + ks * 16 + 2 * t;
+                const __nv_bfloat162 lo = __floats2bfloat162_rn(wr[0], wr[1]), hi = __floats2bfloat162_rn(wr[8], wr[9]);
+                wa0[i] = *reinterpret_cast<const uint32_t*>(&lo);
+                wa2[i] = *reinterpret_cast<const uint32_t*>(&hi);
             }
         }
-        *reinterpret_cast<float2*>(&scr[warp][g * 8 + 2 * t]) = make_float2(cd[0], cd[1]);
-        if ((g >> 1) == t) scr[warp][64 + g] = (g & 1) ? cg[1] : cg[0];
-        __syncthreads();
-        for (int i = threadIdx.x; i < 72; i += blockDim.x) {
-            float a = 0.f;
-            for (int w = 0; w < nwarp; ++w) a += scr[w][i];
-            fin[i] = a;
-        }
-        __syncthreads();
-        if (threadIdx.x < Q) {
-            const int q = threadIdx.x;
-            float lg[MAXS], mx = -INFINITY;
+        const int c = threadIdx.x;                                  // this thread's 8-column chunk
+        const bool active = c < nchunks;
+        float* tab = &sm.tab[warp][0][0];                           // probabilities [s][q]
+        for (int it = 0; it < my_tokens; ++it) {
+            const int st = it % stages, par = it & 1;
+            const size_t tok = (size_t)blockIdx.x + (size_t)it * gridDim.x;
+            if (!tc::mbar_wait(&sm.full[st], (it / stages) & 1, &sm.abort_flag)) {
+                if (lane == 0) atomicMax(status, (int)KB_TIMEOUT_TMA);
+                break;
+            }
+            const uint8_t* stage = smem + (size_t)st * S * pitch;
+            const uint32_t rows = smem_u32(stage);
+            float cd[4] = {0.f, 0.f, 0.f, 0.f}, cg[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int s = 0; s < MAXS; ++s) {
-                if (s < S) {
-                    const float rr = rsqrtf(fin[64 + s] * invD + eps);
-                    lg[s] = fin[q * 8 + s] * rr;
-                    mx = fmaxf(mx, lg[s]);
-                    logit_g[((size_t)q * N + tok) * S + s] = lg[s];
-                    if (q == 0) r_g[tok * S + s] = rr;
+            for (int i = 0; i < KSW; ++i) {
+                const int ks = warp * KSW + i;
+                if (ks < nks) {
+                    uint32_t v0, v1;
+                    ldsm_x2(v0, v1, frag_addr(rows, pitch, S, ks * 16, lane));
+                    mma_16816(cd, wa0[i], wa2[i], v0, v1);        // dots[q = g][s = 2t, 2t + 1]
+                    mma_16816(cg, v0, v1, v0, v1);                // gram[s = g][s' = 2t, 2t + 1]
                 }
             }
-            float den = 0.f;
-#pragma unroll
-            for (int s = 0; s < MAXS; ++s) {
-                lg[s] = s < S ? __expf(lg[s] - mx) : 0.f;
-                den += lg[s];
+            *reinterpret_cast<float2*>(&sm.scr[par][warp][g * 8 + 2 * t]) = make_float2(cd[0], cd[1]);
+            if ((g >> 1) == t) sm.scr[par][warp][64 + g] = (g & 1) ? cg[1] : cg[0];
+            if (!p1_meet(sm, it, lane)) {
+                if (lane == 0) atomicMax(status, (int)KB_TIMEOUT_EPI);
+                break;
             }
+            // every warp finishes the token's softmax itself: lane (g, t) owns query g, sources 2t and 2t+1
+            float2 dots, ss;
+            p1_gather(sm, par, ncw, g, t, dots, ss);
+            const int s0 = 2 * t, s1 = 2 * t + 1;
+            const float r0 = rsqrtf(ss.x * invD + eps), r1 = rsqrtf(ss.y * invD + eps);
+            const float l0 = s0 < S ? dots.x * r0 : -INFINITY, l1 = s1 < S ? dots.y * r1 : -INFINITY;
+            const float mx = quad_max(fmaxf(l0, l1));
+            const float e0 = __expf(l0 - mx), e1 = __expf(l1 - mx);
+            const float den = quad_sum(e0 + e1);
             const float inv = 1.f / den;
-#pragma unroll
-            for (int s = 0; s < MAXS; ++s) pt[s][q] = lg[s] * inv;
-            lse[(size_t)q * N + tok] = mx + __logf(den);
-        }
-        __syncthreads();
-        for (int c = threadIdx.x; c < nchunks; c += blockDim.x) {
-            float acc[MAXQ][8];
-#pragma unroll
-            for (int q = 0; q < MAXQ; ++q)
-#pragma unroll
-                for (int i = 0; i < 8; ++i) acc[q][i] = 0.f;
-#pragma unroll
-            for (int s = 0; s < MAXS; ++s) {
-                if (s < S) {
-                    float v[8];
-                    unpack8(ld8(reinterpret_cast<const bf16*>(stage + (size_t)s * pitch) + c * 8), v);
-                    const float4 p0 = *reinterpret_cast<const float4*>(&pt[s][0]);
-                    const float4 p1 = *reinterpret_cast<const float4*>(&pt[s][4]);
-                    const float pq[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
-#pragma unroll
-                    for (int q = 0; q < MAXQ; ++q)
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) acc[q][i] += pq[q] * v[i];
+            tab[s0 * 8 + g] = e0 * inv;
+            tab[s1 * 8 + g] = e1 * inv;
+            if (warp == 0 && g < Q) {                                 // one warp records the statistics
+                if (s0 < S) logit_g[((size_t)g * N + tok) * S + s0] = l0;
+                if (s1 < S) logit_g[((size_t)g * N + tok) * S + s1] = l1;
+                if (t == 0) lse[(size_t)g * N + tok] = mx + __logf(den);
+                if (g == 0) {
+                    if (s0 < S) r_g[tok * S + s0] = r0;
+                    if (s1 < S) r_g[tok * S + s1] = r1;
                 }
             }
+            __syncwarp();
+            if (active) {
+                float2 acc[MAXQ][4];
 #pragma unroll
-            for (int q = 0; q < MAXQ; ++q)
-                if (q < Q) st8(o + ((size_t)q * N + tok) * D + (size_t)c * 8, pack8(acc[q]));
+                for (int q = 0; q < MAXQ; ++q)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) acc[q][i] = make_float2(0.f, 0.f);
+#pragma unroll
+                for (int q = 0; q < MAXS; ++q) {                    // q runs over sources here
+                    if (q < S) {
+                        float v[8];
+                        unpack8(ld8(reinterpret_cast<const bf16*>(stage + (size_t)q * pitch) + c * 8), v);
+                        const float4 p0 = *reinterpret_cast<const float4*>(tab + q * 8);
+                        const float4 p1 = *reinterpret_cast<const float4*>(tab + q * 8 + 4);
+                        const float pq[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+#pragma unroll
+                        for (int k = 0; k < MAXQ; ++k)
+#pragma unroll
+                            for (int i = 0; i < 4; ++i)
+                                acc[k][i] = __ffma2_rn(make_float2(pq[k], pq[k]), make_float2(v[2 * i], v[2 * i + 1]), acc[k][i]);
+                    }
+                }
+#pragma unroll
+                for (int k = 0; k < MAXQ; ++k)
+                    if (k < Q) {
+                        bf16x8 ov;
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) ov.v[i] = __floats2bfloat162_rn(acc[k][i].x, acc[k][i].y);
+                        st8(o + ((size_t)k * N + tok) * D + (size_t)c * 8, ov);
+                    }
+            }
+            __syncwarp();
+            if (lane == 0) tc::mbar_arrive(&sm.empty[st]);          // this warp is done with the stage
         }
-        __syncthreads();                     // every thread is done reading this stage (and pt)
-        if (threadIdx.x == 0 && it + stages < my_tokens) issue(it + stages);
     }
-    if (threadIdx.x == 0 && abort_flag) {
-        for (int s = 0; s < stages; ++s) {
+    __syncthreads();
+    if (threadIdx.x == 0 && sm.abort_flag) {     // copies still in flight must land before shared memory is released
+        for (int i = 0; i < stages; ++i) {
             const uint64_t t0 = global_timer_ns();
-            while (!tc::mbar_try_wait(&full[s], 0) && !tc::mbar_try_wait(&full[s], 1) &&
+            while (!tc::mbar_try_wait(&sm.full[i], 0) && !tc::mbar_try_wait(&sm.full[i], 1) &&
                    global_timer_ns() - t0 < 2000000ull) {}
         }
     }
@@ -473,23 +527,18 @@ route_p1_fwd_kernel(P1Srcs srcs, int S, int Q, const float* __restrict__ wf, bf1
 // phase 1 backward (reference: kernels/phase_1.py:204-274), all Q queries of the block at once:
 //   P_qs = e^{l_qs - lse_q}, a_qs = do_q . u_s, dl_qs = P_qs (dlse_q + a_qs - sum_s P_qs a_qs)
 //   du_s += sum_q [P_qs do_q + dl_qs r_s w_q] - (sum_q dl_qs l_qs) r_s^2 u_s / D
-//   dw_q += sum_s dl_qs r_s u_s            (per-CTA partial rows, reduced by a column sum)
+// and cw[s][tok][q] = dl_qs r_s, from which route_dw_kernel forms dw_q = sum_tok sum_s cw u_s.
 // stage rows: S sources, then Q gradient rows.
 template <int THREADS>
 __global__ void __launch_bounds__(THREADS, 1)
 route_p1_bwd_kernel(P1Srcs srcs, P1Dsts dsts, int S, int Q, const float* __restrict__ wf,
                     const bf16* __restrict__ dout, const float* __restrict__ dlse, const float* __restrict__ lse,
-                    const float* __restrict__ r_g, const float* __restrict__ logit_g, float* __restrict__ dw_part,
+                    const float* __restrict__ r_g, const float* __restrict__ logit_g, float* __restrict__ cw_g,
                     int N, int D, int stages, int* status) {
     extern __shared__ __align__(128) uint8_t smem[];
-    __shared__ float scr[16][64];              // per warp: a[q][s]
-    __shared__ float fin[64];
-    __shared__ __align__(16) float tP[MAXS][MAXQ], tW[MAXS][MAXQ];   // P_qs and dl_qs r_s, one row per source
-    __shared__ float tV[MAXS];                 // (sum_q dl_qs l_qs) r_s^2 / D
-    __shared__ float tL[MAXQ][MAXS];
-    __shared__ uint64_t full[2];
-    __shared__ int abort_flag;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    __shared__ P1Smem sm;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int ncw = (blockDim.x >> 5) - 1;
     const int g = lane >> 2, t = lane & 3;
     const uint32_t pitch = p1_pitch(D);
     const uint32_t row_bytes = (uint32_t)D * 2;
@@ -497,150 +546,190 @@ route_p1_bwd_kernel(P1Srcs srcs, P1Dsts dsts, int S, int Q, const float* __restr
     const float invD = 1.f / (float)D;
     const int rows_per_stage = S + Q;
     if (threadIdx.x == 0) {
-        for (int s = 0; s < stages; ++s) tc::mbar_init(&full[s], 1);
-        abort_flag = 0;
+        for (int i = 0; i < stages; ++i) {
+            tc::mbar_init(&sm.full[i], 1);
+            tc::mbar_init(&sm.empty[i], ncw);
+        }
+        tc::mbar_init(&sm.meet, ncw);
+        sm.abort_flag = 0;
         tc::fence_barrier_init();
     }
     __syncthreads();
     const int my_tokens = blockIdx.x < N ? (N - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-    auto issue = [&](int it) {
-        const int st = it % stages;
-        const size_t tok = (size_t)blockIdx.x + (size_t)it * gridDim.x;
-        uint8_t* base = smem + (size_t)st * rows_per_stage * pitch;
-        tc::mbar_expect_tx(&full[st], rows_per_stage * row_bytes);
-        for (int s = 0; s < S; ++s) bulk_g2s(base + (size_t)s * pitch, srcs.p[s] + tok * D, row_bytes, &full[st]);
-        for (int q = 0; q < Q; ++q)
-            bulk_g2s(base + (size_t)(S + q) * pitch, dout + ((size_t)q * N + tok) * D, row_bytes, &full[st]);
-    };
-    if (threadIdx.x == 0)
-        for (int it = 0; it < stages && it < my_tokens; ++it) issue(it);
 
-    const int c = threadIdx.x;                 // this thread's 8-column chunk (one per thread: D <= 8 * THREADS)
-    const bool active = c < nchunks;
-    float dw_acc[MAXQ][8];
-#pragma unroll
-    for (int q = 0; q < MAXQ; ++q)
-#pragma unroll
-        for (int i = 0; i < 8; ++i) dw_acc[q][i] = 0.f;
-
-    for (int it = 0; it < my_tokens; ++it) {
-        const int st = it % stages;
-        const size_t tok = (size_t)blockIdx.x + (size_t)it * gridDim.x;
-        if (!tc::mbar_wait(&full[st], (it / stages) & 1, &abort_flag)) {
-            if (threadIdx.x == 0) atomicMax(status, (int)KB_TIMEOUT_TMA);
-            break;
-        }
-        const uint8_t* stage = smem + (size_t)st * rows_per_stage * pitch;
-        const uint32_t rows = smem_u32(stage);
-        float ca[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-        for (int i = 0; i < KSW; ++i) {
-            const int ks = warp * KSW + i;
-            if (ks < nks) {
-                uint32_t a0, a2, v0, v1;
-                ldsm_x2(a0, a2, frag_addr(rows + S * pitch, pitch, Q, ks * 16, lane));
-                ldsm_x2(v0, v1, frag_addr(rows, pitch, S, ks * 16, lane));
-                mma_16816(ca, a0, a2, v0, v1);                // a[q = g][s = 2t, 2t + 1]
+    if (warp == ncw) {
+        if (lane == 0) {
+            for (int it = 0; it < my_tokens; ++it) {
+                const int st = it % stages;
+                if (!tc::mbar_wait(&sm.empty[st], ((it / stages) & 1) ^ 1, &sm.abort_flag)) {
+                    atomicMax(status, (int)KB_TIMEOUT_TMA);
+                    break;
+                }
+                const size_t tok = (size_t)blockIdx.x + (size_t)it * gridDim.x;
+                uint8_t* base = smem + (size_t)st * rows_per_stage * pitch;
+                tc::mbar_expect_tx(&sm.full[st], rows_per_stage * row_bytes);
+                for (int q = 0; q < S; ++q) bulk_g2s(base + (size_t)q * pitch, srcs.p[q] + tok * D, row_bytes, &sm.full[st]);
+                for (int q = 0; q < Q; ++q)
+                    bulk_g2s(base + (size_t)(S + q) * pitch, dout + ((size_t)q * N + tok) * D, row_bytes, &sm.full[st]);
             }
         }
-        *reinterpret_cast<float2*>(&scr[warp][g * 8 + 2 * t]) = make_float2(ca[0], ca[1]);
-        __syncthreads();
-        for (int i = threadIdx.x; i < 64; i += blockDim.x) {
-            float a = 0.f;
-            for (int w = 0; w < nwarp; ++w) a += scr[w][i];
-            fin[i] = a;
-        }
-        __syncthreads();
-        if (threadIdx.x < Q) {
-            const int q = threadIdx.x;
-            const float ls = lse[(size_t)q * N + tok], dls = dlse[(size_t)q * N + tok];
-            float pr[MAXS], lg[MAXS], abar = 0.f;
-#pragma unroll
-            for (int s = 0; s < MAXS; ++s) {
-                lg[s] = s < S ? logit_g[((size_t)q * N + tok) * S + s] : 0.f;
-                pr[s] = s < S ? __expf(lg[s] - ls) : 0.f;
-                abar += pr[s] * fin[q * 8 + s];
+    } else {
+        const int c = threadIdx.x;
+        const bool active = c < nchunks;
+        float* tP = &sm.tab[warp][0][0];                            // [q][s]: P_qs
+        float* tW = &sm.tab[warp][1][0];                            // [q][s]: dl_qs r_s
+        float* tV = &sm.tab[warp][2][0];                            // [s]: (sum_q dl_qs l_qs) r_s^2 / D
+        const int s0 = 2 * t, s1 = 2 * t + 1;
+        const bool qv = g < Q;
+        for (int it = 0; it < my_tokens; ++it) {
+            const int st = it % stages, par = it & 1;
+            const size_t tok = (size_t)blockIdx.x + (size_t)it * gridDim.x;
+            // statistics of this lane's (query, two sources): requested before the wait, used after the dots
+            const float ls = qv ? lse[(size_t)g * N + tok] : 0.f, dls = qv ? dlse[(size_t)g * N + tok] : 0.f;
+            const float lg0 = qv && s0 < S ? logit_g[((size_t)g * N + tok) * S + s0] : -INFINITY;
+            const float lg1 = qv && s1 < S ? logit_g[((size_t)g * N + tok) * S + s1] : -INFINITY;
+            const float rr0 = s0 < S ? r_g[tok * S + s0] : 0.f, rr1 = s1 < S ? r_g[tok * S + s1] : 0.f;
+            if (!tc::mbar_wait(&sm.full[st], (it / stages) & 1, &sm.abort_flag)) {
+                if (lane == 0) atomicMax(status, (int)KB_TIMEOUT_TMA);
+                break;
             }
+            const uint8_t* stage = smem + (size_t)st * rows_per_stage * pitch;
+            const uint32_t rows = smem_u32(stage);
+            float ca[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int s = 0; s < MAXS; ++s) {
-                const float dl = pr[s] * (dls + fin[q * 8 + s] - abar);
-                const float rr = s < S ? r_g[tok * S + s] : 0.f;
-                tP[s][q] = pr[s];
-                tW[s][q] = dl * rr;
-                tL[q][s] = dl * lg[s] * rr * rr * invD;
-            }
-        } else if (threadIdx.x < MAXQ) {       // unused queries contribute nothing
-            const int q = threadIdx.x;
-#pragma unroll
-            for (int s = 0; s < MAXS; ++s) tP[s][q] = tW[s][q] = tL[q][s] = 0.f;
-        }
-        __syncthreads();
-        if (threadIdx.x < MAXS) {
-            float a = 0.f;
-#pragma unroll
-            for (int q = 0; q < MAXQ; ++q) a += tL[q][threadIdx.x];
-            tV[threadIdx.x] = a;
-        }
-        __syncthreads();
-        if (active) {
-            // gradient rows and query rows of this chunk, unpacked once
-            float gq[MAXQ][8];
-#pragma unroll
-            for (int q = 0; q < MAXQ; ++q) {
-                if (q < Q) unpack8(ld8(reinterpret_cast<const bf16*>(stage + (size_t)(S + q) * pitch) + c * 8), gq[q]);
-                else {
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) gq[q][i] = 0.f;
+            for (int i = 0; i < KSW; ++i) {
+                const int ks = warp * KSW + i;
+                if (ks < nks) {
+                    uint32_t a0, a2, v0, v1;
+                    ldsm_x2(a0, a2, frag_addr(rows + S * pitch, pitch, Q, ks * 16, lane));
+                    ldsm_x2(v0, v1, frag_addr(rows, pitch, S, ks * 16, lane));
+                    mma_16816(ca, a0, a2, v0, v1);                // a[q = g][s = 2t, 2t + 1]
                 }
             }
+            *reinterpret_cast<float2*>(&sm.scr[par][warp][g * 8 + 2 * t]) = make_float2(ca[0], ca[1]);
+            if (!p1_meet(sm, it, lane)) {
+                if (lane == 0) atomicMax(status, (int)KB_TIMEOUT_EPI);
+                break;
+            }
+            float2 a = make_float2(0.f, 0.f);
+            for (int w = 0; w < ncw; ++w) {
+                const float2 d = *reinterpret_cast<const float2*>(&sm.scr[par][w][g * 8 + 2 * t]);
+                a.x += d.x; a.y += d.y;
+            }
+            const float p0 = __expf(lg0 - ls), p1 = __expf(lg1 - ls);           // 0 for unused (query, source) pairs
+            const float abar = quad_sum(p0 * a.x + p1 * a.y);
+            const float dl0 = p0 * (dls + a.x - abar), dl1 = p1 * (dls + a.y - abar);
+            *reinterpret_cast<float2*>(&tP[g * 8 + s0]) = make_float2(p0, p1);
+            *reinterpret_cast<float2*>(&tW[g * 8 + s0]) = make_float2(dl0 * rr0, dl1 * rr1);
+            // sum over the queries (lanes with the same t) of dl * l, scaled per source
+            float v0 = s0 < S && qv ? dl0 * lg0 : 0.f, v1 = s1 < S && qv ? dl1 * lg1 : 0.f;
 #pragma unroll
-            for (int s = 0; s < MAXS; ++s) {
-                if (s >= S) continue;
-                float v[8], du[8];
-                unpack8(ld8(reinterpret_cast<const bf16*>(stage + (size_t)s * pitch) + c * 8), v);
-                const float4 p0 = *reinterpret_cast<const float4*>(&tP[s][0]), p1 = *reinterpret_cast<const float4*>(&tP[s][4]);
-                const float4 w0 = *reinterpret_cast<const float4*>(&tW[s][0]), w1 = *reinterpret_cast<const float4*>(&tW[s][4]);
-                const float pq[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
-                const float wq[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
-                const float cv = tV[s];
+            for (int off = 4; off < 32; off <<= 1) {
+                v0 += __shfl_xor_sync(0xffffffffu, v0, off);
+                v1 += __shfl_xor_sync(0xffffffffu, v1, off);
+            }
+            if (g == 0) *reinterpret_cast<float2*>(&tV[s0]) = make_float2(v0 * rr0 * rr0 * invD, v1 * rr1 * rr1 * invD);
+            if (warp == 0 && qv) {                                    // coefficients of the query gradients
+                if (s0 < S) cw_g[((size_t)s0 * N + tok) * MAXQ + g] = dl0 * rr0;
+                if (s1 < S) cw_g[((size_t)s1 * N + tok) * MAXQ + g] = dl1 * rr1;
+            }
+            __syncwarp();
+            if (active) {
+                float2 du[MAXS][4];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) du[i] = -cv * v[i];
+                for (int q = 0; q < MAXS; ++q)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) du[q][i] = make_float2(0.f, 0.f);
 #pragma unroll
                 for (int q = 0; q < MAXQ; ++q) {
                     if (q < Q) {
+                        float gq[8];
+                        unpack8(ld8(reinterpret_cast<const bf16*>(stage + (size_t)(S + q) * pitch) + c * 8), gq);
                         const float4 x0 = *reinterpret_cast<const float4*>(wf + (size_t)q * D + c * 8);
                         const float4 x1 = *reinterpret_cast<const float4*>(wf + (size_t)q * D + c * 8 + 4);
-                        const float wv[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+                        const float2 w2[4] = {make_float2(x0.x, x0.y), make_float2(x0.z, x0.w), make_float2(x1.x, x1.y),
+                                              make_float2(x1.z, x1.w)};
+                        const float4 pa = *reinterpret_cast<const float4*>(tP + q * 8), pb = *reinterpret_cast<const float4*>(tP + q * 8 + 4);
+                        const float4 wa = *reinterpret_cast<const float4*>(tW + q * 8), wb = *reinterpret_cast<const float4*>(tW + q * 8 + 4);
+                        const float ps[8] = {pa.x, pa.y, pa.z, pa.w, pb.x, pb.y, pb.z, pb.w};
+                        const float ws[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
 #pragma unroll
-                        for (int i = 0; i < 8; ++i) {
-                            du[i] += pq[q] * gq[q][i] + wq[q] * wv[i];
-                            dw_acc[q][i] += wq[q] * v[i];
+                        for (int k = 0; k < MAXS; ++k) {
+                            if (k < S) {
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) {
+                                    du[k][i] = __ffma2_rn(make_float2(ps[k], ps[k]), make_float2(gq[2 * i], gq[2 * i + 1]), du[k][i]);
+                                    du[k][i] = __ffma2_rn(make_float2(ws[k], ws[k]), w2[i], du[k][i]);
+                                }
+                            }
                         }
                     }
                 }
-                bf16* dst = dsts.p[s] + tok * D + (size_t)c * 8;
-                if (dsts.acc_mask >> s & 1u) red_add8(dst, pack8(du));
-                else st8(dst, pack8(du));
-            }
-        }
-        __syncthreads();                     // every thread is done reading this stage and the tables
-        if (threadIdx.x == 0 && it + stages < my_tokens) issue(it + stages);
-    }
-    if (active) {
 #pragma unroll
-        for (int q = 0; q < MAXQ; ++q) {
-            if (q < Q) {
-                float* b = dw_part + ((size_t)blockIdx.x * Q + q) * D + (size_t)c * 8;
+                for (int k = 0; k < MAXS; ++k) {
+                    if (k >= S) continue;
+                    float v[8];
+                    unpack8(ld8(reinterpret_cast<const bf16*>(stage + (size_t)k * pitch) + c * 8), v);
+                    const float cv = -tV[k];
+                    bf16x8 ov;
 #pragma unroll
-                for (int i = 0; i < 8; ++i) b[i] = dw_acc[q][i];
+                    for (int i = 0; i < 4; ++i) {
+                        const float2 d = __ffma2_rn(make_float2(cv, cv), make_float2(v[2 * i], v[2 * i + 1]), du[k][i]);
+                        ov.v[i] = __floats2bfloat162_rn(d.x, d.y);
+                    }
+                    bf16* dst = dsts.p[k] + tok * D + (size_t)c * 8;
+                    if (dsts.acc_mask >> k & 1u) red_add8(dst, ov);
+                    else st8(dst, ov);
+                }
             }
+            __syncwarp();
+            if (lane == 0) tc::mbar_arrive(&sm.empty[st]);
         }
     }
-    if (threadIdx.x == 0 && abort_flag) {
-        for (int s = 0; s < stages; ++s) {
+    __syncthreads();
+    if (threadIdx.x == 0 && sm.abort_flag) {
+        for (int i = 0; i < stages; ++i) {
             const uint64_t t0 = global_timer_ns();
-            while (!tc::mbar_try_wait(&full[s], 0) && !tc::mbar_try_wait(&full[s], 1) &&
+            while (!tc::mbar_try_wait(&sm.full[i], 0) && !tc::mbar_try_wait(&sm.full[i], 1) &&
                    global_timer_ns() - t0 < 2000000ull) {}
+        }
+    }
+}
+
+// dw_part[cta][q][D] = sum over this CTA's tokens and all sources of cw[s][tok][q] * u_s[tok][:]
+// (the query gradients of phase 1; a column sum over the CTAs finishes them).  Pure streaming: a
+// thread owns 8 columns and reads its 16 bytes of every source row.
+__global__ void __launch_bounds__(512)
+route_dw_kernel(P1Srcs srcs, int S, int Q, const float* __restrict__ cw_g, float* __restrict__ dw_part, int N, int D) {
+    const int c = threadIdx.x;
+    const int nchunks = D >> 3;
+    if (c >= nchunks) return;
+    float2 acc[MAXQ][4];
+#pragma unroll
+    for (int q = 0; q < MAXQ; ++q)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[q][i] = make_float2(0.f, 0.f);
+    for (size_t tok = blockIdx.x; tok < (size_t)N; tok += gridDim.x) {
+#pragma unroll 2
+        for (int s = 0; s < S; ++s) {
+            float v[8];
+            unpack8(ld8(srcs.p[s] + tok * D + (size_t)c * 8), v);
+            const float4 c0 = *reinterpret_cast<const float4*>(cw_g + ((size_t)s * N + tok) * MAXQ);
+            const float4 c1 = *reinterpret_cast<const float4*>(cw_g + ((size_t)s * N + tok) * MAXQ + 4);
+            const float cq[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+#pragma unroll
+            for (int q = 0; q < MAXQ; ++q)
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    acc[q][i] = __ffma2_rn(make_float2(cq[q], cq[q]), make_float2(v[2 * i], v[2 * i + 1]), acc[q][i]);
+        }
+    }
+    for (int q = 0; q < Q; ++q) {
+        float* b = dw_part + ((size_t)blockIdx.x * Q + q) * D + (size_t)c * 8;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            b[2 * i] = acc[q][i].x;
+            b[2 * i + 1] = acc[q][i].y;
         }
     }
 }
@@ -650,10 +739,10 @@ int rb_ensure_smem(K kernel, size_t bytes, bool* done_for_device) {
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 7;
     if (!done_for_device[dev]) {
-        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024) != cudaSuccess) return 7;
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, RB_DYN_SMEM) != cudaSuccess) return 7;
         done_for_device[dev] = true;
     }
-    return bytes <= 220 * 1024 ? 0 : 8;
+    return bytes <= (size_t)RB_DYN_SMEM ? 0 : 8;
 }
 
 }  // namespace
@@ -671,12 +760,12 @@ KB_API int kb_route_fold_w(const void* q, const void* rn, float* w, int n, cudaS
 // 1 when the blocked kernels cover this shape (else the caller uses the per-call kernels).
 KB_API int kb_route_blocked_ok(int S, int D) {
     return S >= 1 && S <= MAXS && D % 16 == 0 && D >= 16 && D <= 4096 &&
-           (size_t)(S + MAXQ) * p1_pitch(D) <= 220 * 1024;
+           (size_t)(S + MAXQ) * p1_pitch(D) <= (size_t)RB_DYN_SMEM;
 }
 
 // Number of CTAs (= rows of the partial weight-gradient buffers) of the two backward kernels.
 KB_API int kb_route_blocked_grid(int N, int which) {
-    const int g = rb_num_sms() * (which == 2 ? 2 : 1);
+    const int g = rb_num_sms() * (which == 2 ? 2 : 4);
     return N < g ? N : g;
 }
 
@@ -686,29 +775,30 @@ KB_API int kb_route_p1_fwd(const void* const* srcs, int S, int Q, const float* w
     P1Srcs ps;
     for (int s = 0; s < MAXS; ++s) ps.p[s] = s < S ? (const bf16*)srcs[s] : nullptr;
     const size_t stage = (size_t)S * p1_pitch(D);
-    int stages = (int)((200 * 1024) / stage);
+    int stages = (int)(RB_DYN_SMEM / stage);
     if (stages > RB_STAGES) stages = RB_STAGES;
     if (stages < 1) return 8;
     const size_t smem = stage * stages;
     const int grid = N < rb_num_sms() ? N : rb_num_sms();
-    if (D <= 3072) {
+    const int threads = ((D / 8 + 31) / 32) * 32 + 32;           // compute warps + the producer warp
+    if (threads <= 416) {
         static bool attr[64] = {};
-        int r_ = rb_ensure_smem(route_p1_fwd_kernel<384>, smem, attr);
+        int r_ = rb_ensure_smem(route_p1_fwd_kernel<416>, smem, attr);
         if (r_) return r_;
-        const int threads = ((D / 8 + 31) / 32) * 32;
-        route_p1_fwd_kernel<384><<<grid, threads, smem, st>>>(ps, S, Q, wf, (bf16*)o, lse, r, logit, N, D, eps, stages, status);
+        route_p1_fwd_kernel<416><<<grid, threads, smem, st>>>(ps, S, Q, wf, (bf16*)o, lse, r, logit, N, D, eps, stages, status);
     } else {
         static bool attr[64] = {};
-        int r_ = rb_ensure_smem(route_p1_fwd_kernel<512>, smem, attr);
+        int r_ = rb_ensure_smem(route_p1_fwd_kernel<544>, smem, attr);
         if (r_) return r_;
-        route_p1_fwd_kernel<512><<<grid, 512, smem, st>>>(ps, S, Q, wf, (bf16*)o, lse, r, logit, N, D, eps, stages, status);
+        route_p1_fwd_kernel<544><<<grid, threads, smem, st>>>(ps, S, Q, wf, (bf16*)o, lse, r, logit, N, D, eps, stages, status);
     }
     return cudaGetLastError() == cudaSuccess ? 0 : 8;
 }
 
+// cw[S][N][8] fp32 workspace: coefficients of the query gradients, consumed by kb_route_dw.
 KB_API int kb_route_p1_bwd(const void* const* srcs, void* const* dsts, unsigned acc_mask, int S, int Q, const float* wf,
                            const void* dout, const float* dlse, const float* lse, const float* r, const float* logit,
-                           float* dw_part, int N, int D, int* status, cudaStream_t st) {
+                           float* cw, int N, int D, int* status, cudaStream_t st) {
     if (!kb_route_blocked_ok(S, D) || Q < 1 || Q > MAXQ || N < 1) return 5;
     P1Srcs ps;
     P1Dsts pd;
@@ -718,23 +808,36 @@ KB_API int kb_route_p1_bwd(const void* const* srcs, void* const* dsts, unsigned 
     }
     pd.acc_mask = acc_mask;
     const size_t stage = (size_t)(S + Q) * p1_pitch(D);
-    const int stages = 2 * stage <= 220 * 1024 ? 2 : 1;
+    int stages = (int)(RB_DYN_SMEM / stage);
+    if (stages > RB_STAGES) stages = RB_STAGES;
+    if (stages < 1) return 8;
     const size_t smem = stage * stages;
-    const int grid = kb_route_blocked_grid(N, 1);
-    if (D <= 3072) {
+    const int grid = N < rb_num_sms() ? N : rb_num_sms();
+    const int threads = ((D / 8 + 31) / 32) * 32 + 32;
+    if (threads <= 416) {
         static bool attr[64] = {};
-        int r_ = rb_ensure_smem(route_p1_bwd_kernel<384>, smem, attr);
+        int r_ = rb_ensure_smem(route_p1_bwd_kernel<416>, smem, attr);
         if (r_) return r_;
-        const int threads = ((D / 8 + 31) / 32) * 32;
-        route_p1_bwd_kernel<384><<<grid, threads, smem, st>>>(ps, pd, S, Q, wf, (const bf16*)dout, dlse, lse, r, logit,
-                                                              dw_part, N, D, stages, status);
+        route_p1_bwd_kernel<416><<<grid, threads, smem, st>>>(ps, pd, S, Q, wf, (const bf16*)dout, dlse, lse, r, logit, cw,
+                                                              N, D, stages, status);
     } else {
         static bool attr[64] = {};
-        int r_ = rb_ensure_smem(route_p1_bwd_kernel<512>, smem, attr);
+        int r_ = rb_ensure_smem(route_p1_bwd_kernel<544>, smem, attr);
         if (r_) return r_;
-        route_p1_bwd_kernel<512><<<grid, 512, smem, st>>>(ps, pd, S, Q, wf, (const bf16*)dout, dlse, lse, r, logit,
-                                                          dw_part, N, D, stages, status);
+        route_p1_bwd_kernel<544><<<grid, threads, smem, st>>>(ps, pd, S, Q, wf, (const bf16*)dout, dlse, lse, r, logit, cw,
+                                                              N, D, stages, status);
     }
+    return cudaGetLastError() == cudaSuccess ? 0 : 8;
+}
+
+// dw_part[grid][Q][D] (grid = kb_route_blocked_grid(N, 1) rows) from cw and the sources.
+KB_API int kb_route_dw(const void* const* srcs, int S, int Q, const float* cw, float* dw_part, int N, int D,
+                       cudaStream_t st) {
+    if (S < 1 || S > MAXS || Q < 1 || Q > MAXQ || D % 8 != 0 || D > 4096 || N < 1) return 5;
+    P1Srcs ps;
+    for (int s = 0; s < MAXS; ++s) ps.p[s] = s < S ? (const bf16*)srcs[s] : nullptr;
+    const int threads = ((D / 8 + 31) / 32) * 32;
+    route_dw_kernel<<<kb_route_blocked_grid(N, 1), threads, 0, st>>>(ps, S, Q, cw, dw_part, N, D);
     return cudaGetLastError() == cudaSuccess ? 0 : 8;
 }
 

@@ -402,18 +402,20 @@ PipeCfg pipe_cfg(int S, int D, bool bwd) {
 #define PIPE_CASE(MAXS_, CPT_)                                                                              \
     {                                                                                                       \
         auto kern = route_pipe_kernel<MAXS_, CPT_, BWD>;                                                    \
-        static size_t attr_smem = 0; /* per instantiation: raise the limit only when it grows */           \
-        if (cfg.smem > attr_smem) {                                                                         \
+        static bool attr_flags[64] = {}; /* per instantiation and device */                                \
+        bool* attr = kb_device_flag(attr_flags);                                                            \
+        if (!attr) return 7;                                                                                \
+        if (!*attr) {                                                                                       \
             if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) !=      \
                 cudaSuccess)                                                                                \
                 return 7;                                                                                   \
-            attr_smem = 200 * 1024;                                                                         \
+            *attr = true;                                                                                   \
         }                                                                                                   \
         kern<<<grid, cfg.threads, cfg.smem, st>>>(rs, ds, S, (const bf16*)dxn, (const bf16*)q,              \
                                                    (const bf16*)rn_w, (const bf16*)n_w, (bf16*)xn, alpha, r, \
                                                    logit, rstd, dw_part, dnw_part, N, D, eps, cfg.stages,  \
                                                    status);                                                 \
-        return 0;                                                                                           \
+        return kb_launch_status();                                                                          \
     }
 #define PIPE_CPT(MAXS_)                   \
     switch (cfg.cpt) {                    \

@@ -37,7 +37,7 @@ KB_API int kb_kv_append(const void* k, const void* v, long long k_stride, long l
     if (blocks > 4096) blocks = 4096;
     kv_append_kernel<<<(int)blocks, 256, 0, st>>>((const bf16*)k, (const bf16*)v, k_stride, v_stride, (bf16*)k_pages,
                                                   (bf16*)v_pages, slot, N, row_elems, hd);
-    return 0;
+    return kb_launch_status();
 }
 
 // One CTA per (request, kv head, split of SPLIT tokens).  G = query heads per kv head.
@@ -620,11 +620,13 @@ KB_API int kb_paged_decode(const void* q, long long q_stride, const void* k_page
     }
 #define DEC(HD_, G_)                                                                                          \
     if (streaming == 2 && (HD_) == 128 && (G_) <= 4) {                                                         \
-        static bool attr = false;                                                                              \
-        if (!attr) {                                                                                           \
+        static bool attr_flags[64] = {};                                                                       \
+        bool* attr = kb_device_flag(attr_flags);                                                               \
+        if (!attr) return 7;                                                                                   \
+        if (!*attr) {                                                                                          \
             if (cudaFuncSetAttribute(paged_decode_bulk_kernel<HD_, G_>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
                                      4 * 4 * PAGE * (HD_) * 2) != cudaSuccess) return 7;                       \
-            attr = true;                                                                                       \
+            *attr = true;                                                                                      \
         }                                                                                                      \
         paged_decode_bulk_kernel<HD_, G_><<<grid, 128, 4 * 4 * PAGE * (HD_) * 2, st>>>(                        \
             (const bf16*)q, q_stride, (const bf16*)k_pages, (const bf16*)v_pages, page_table, max_pages, ctx_lens, \
@@ -664,7 +666,7 @@ KB_API int kb_paged_decode(const void* q, long long q_stride, const void* k_page
     } else {
         return 5;
     }
-    return 0;
+    return kb_launch_status();
 }
 
 // Greedy sampling: out[row] = argmax_j logits[row][j] (first index on ties).
@@ -701,7 +703,7 @@ __global__ void argmax_kernel(const bf16* __restrict__ logits, long long stride,
 }
 KB_API int kb_argmax(const void* logits, long long stride, int rows, int V, long long* out, cudaStream_t st) {
     argmax_kernel<<<rows, 512, 0, st>>>((const bf16*)logits, stride, V, out);
-    return 0;
+    return kb_launch_status();
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -98,12 +98,23 @@ class CudaOps(TorchOps):
         if out is None:
             out = torch.empty(*lead, M, N, device=a.device, dtype=out_dtype)
         if self.gemm_backend == "cublas":
+            # library arm for A/B runs: one cuBLAS call with alpha/beta where the dtypes allow it (no
+            # fp32 round trip, no extra passes over the result), so that the comparison is fair
             am = a.transpose(-1, -2) if a_mn else a
             bm = b if b_mn else b.transpose(-1, -2)
-            r = torch.matmul(am, bm).float() * alpha
-            if cin is not None:
-                r = r + beta * cin.float()
-            out.copy_(r)
+            same = out.dtype == a.dtype == b.dtype and (cin is None or cin.dtype == out.dtype)
+            if same and cin is None and alpha == 1.0:
+                torch.matmul(am, bm, out=out)
+            elif same and batch == 1:
+                torch.addmm(cin if cin is not None else out, am, bm, beta=beta if cin is not None else 0.0, alpha=alpha, out=out)
+            elif same:
+                torch.baddbmm(cin if cin is not None else out, am, bm, beta=beta if cin is not None else 0.0, alpha=alpha, out=out)
+            else:                                  # mixed dtypes (fp32 accumulation targets): library product, then one fused pass
+                r = torch.matmul(am, bm)
+                if cin is not None:
+                    torch.add(cin.to(out.dtype) * beta, r.to(out.dtype), alpha=alpha, out=out)
+                else:
+                    out.copy_(r if alpha == 1.0 else r * alpha)
             if diag:
                 out.diagonal(dim1=-2, dim2=-1).add_(diag)
             return out
@@ -299,7 +310,7 @@ class CudaOps(TorchOps):
     @staticmethod
     def _p1_chunk(S: int, D: int) -> int:
         """Queries per phase-1 launch: 8, or 4 where two backward ring stages of 8 would not fit."""
-        return 8 if 2 * (S + 8) * (2 * D + 16) <= 220 * 1024 else 4
+        return 8 if 2 * (S + 8) * (2 * D + 16) <= 200 * 1024 else 4
 
     def route_p1_fwd(self, srcs, qs, rn_ws, eps):
         S, Q = len(srcs), qs.shape[0]
@@ -351,12 +362,15 @@ class CudaOps(TorchOps):
         mask = sum(1 << i for i, a in enumerate(acc) if a)
         dws = torch.empty(Q, D, device=dev, dtype=torch.float32)
         qc = self._p1_chunk(S, D)
+        cw = torch.empty(S, N, 8, device=dev, dtype=torch.float32)
         for q0 in range(0, Q, qc):
             n = min(qc, Q - q0)
-            part = torch.empty(grid, n * D, device=dev, dtype=torch.float32)
             self._call("kb_route_p1_bwd", sa, da, ctypes.c_uint(mask), _I(S), _I(n), _p(wf[q0:]), _p(do[q0:]),
-                       _p(dlse[q0:]), _p(lse[q0:]), _p(r), _p(logit[q0:]), _p(part), _I(N), _I(D), _p(self.status(dev)),
+                       _p(dlse[q0:]), _p(lse[q0:]), _p(r), _p(logit[q0:]), _p(cw), _I(N), _I(D), _p(self.status(dev)),
                        _st())
+            # query gradients: dw_q = sum over tokens and sources of cw * source (streaming pass + column sum)
+            part = torch.empty(grid, n * D, device=dev, dtype=torch.float32)
+            self._call("kb_route_dw", sa, _I(S), _I(n), _p(cw), _p(part), _I(N), _I(D), _st())
             dws[q0:q0 + n] = self._colsum(part).view(n, D)
             mask = (1 << S) - 1                     # later query chunks add to what the first one wrote
         return dws
