@@ -134,41 +134,30 @@ route_p2_fwd_kernel(const bf16* __restrict__ o, const float* __restrict__ lse, c
     }
 }
 
-// Sum three values over the block; every thread gets the totals.  `scr` holds 2 x 32 float4 and is
-// used alternately by consecutive calls, so one __syncthreads per call is enough.
-__device__ __forceinline__ float3 block_sum3(float a, float b, float c, float4* scr, int parity) {
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = (blockDim.x + 31) >> 5;
-    a = warp_sum(a);
-    b = warp_sum(b);
-    c = warp_sum(c);
-    float4* s = scr + parity * 32;
-    if (lane == 0) s[warp] = make_float4(a, b, c, 0.f);
-    __syncthreads();
-    float3 r = make_float3(0.f, 0.f, 0.f);
-    for (int i = 0; i < nwarp; ++i) {
-        const float4 v = s[i];
-        r.x += v.x;
-        r.y += v.y;
-        r.z += v.z;
-    }
-    return r;
-}
-
 // ------------------------------------------------------------------------------------------------
 // phase 2 backward: persistent CTAs, thread = 8-column chunk(s), rows through a bulk-copy ring
 // ------------------------------------------------------------------------------------------------
 // stage rows: [dxn][o][partial]; the last only when present.  An accumulated partial gradient is
-// added in the L2 (red), so its old value never travels to the SM.
+// added in the L2 (red), so its old value never travels to the SM.  The last warp is the producer
+// (it refills a stage when every compute warp has released it); the compute warps meet once per
+// token to combine three partial sums.
+struct P2Smem {
+    float4 scr[2][16];                         // [token parity][warp]: partial sums A, B, C
+    uint64_t full[RB_STAGES], empty[RB_STAGES], meet;
+    int abort_flag;
+};
+
 template <int CPT>
-__global__ void __launch_bounds__(512)
+__global__ void __launch_bounds__(416, CPT == 1 ? 2 : 1)
 route_p2_bwd_kernel(const bf16* __restrict__ dxn, const bf16* __restrict__ o, const bf16* __restrict__ part,
                     const float* __restrict__ w, const bf16* __restrict__ n_w, const float* __restrict__ stats2,
                     bf16* __restrict__ dout, float* __restrict__ dlse, bf16* __restrict__ dpart, int dpart_acc,
                     float* __restrict__ dw_part, float* __restrict__ dnw_part, int N, int D, int stages, int* status) {
     extern __shared__ __align__(128) uint8_t smem[];
-    __shared__ float4 scr[64];
-    __shared__ uint64_t full[RB_STAGES];
-    __shared__ int abort_flag;
+    __shared__ P2Smem sm;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int ncw = (blockDim.x >> 5) - 1;                        // compute warps; the last warp is the producer
+    const int nct = ncw * 32;                                     // compute threads
     const bool has_p = part != nullptr;
     const bool acc = has_p && dpart_acc;
     const int rows = 2 + (has_p ? 1 : 0);
@@ -176,123 +165,151 @@ route_p2_bwd_kernel(const bf16* __restrict__ dxn, const bf16* __restrict__ o, co
     const int nchunks = D >> 3;
     const float invD = 1.f / (float)D;
     if (threadIdx.x == 0) {
-        for (int s = 0; s < stages; ++s) tc::mbar_init(&full[s], 1);
-        abort_flag = 0;
+        for (int i = 0; i < stages; ++i) {
+            tc::mbar_init(&sm.full[i], 1);
+            tc::mbar_init(&sm.empty[i], ncw);
+        }
+        tc::mbar_init(&sm.meet, ncw);
+        sm.abort_flag = 0;
         tc::fence_barrier_init();
     }
     __syncthreads();
     const int my_tokens = blockIdx.x < N ? (N - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-    auto issue = [&](int it) {
-        const int st = it % stages;
-        const size_t tok = (size_t)blockIdx.x + (size_t)it * gridDim.x;
-        uint8_t* base = smem + (size_t)st * rows * row_bytes;
-        tc::mbar_expect_tx(&full[st], rows * row_bytes);
-        bulk_g2s(base, dxn + tok * D, row_bytes, &full[st]);
-        bulk_g2s(base + row_bytes, o + tok * D, row_bytes, &full[st]);
-        if (has_p) bulk_g2s(base + 2 * row_bytes, part + tok * D, row_bytes, &full[st]);
-    };
-    if (threadIdx.x == 0)
-        for (int it = 0; it < stages && it < my_tokens; ++it) issue(it);
 
-    float nw[CPT][8], wv[CPT][8], dw_acc[CPT][8], dnw_acc[CPT][8];
-#pragma unroll
-    for (int k = 0; k < CPT; ++k) {
-        const int c = threadIdx.x + k * blockDim.x;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) nw[k][i] = wv[k][i] = dw_acc[k][i] = dnw_acc[k][i] = 0.f;
-        if (c < nchunks) {
-            unpack8(ld8(n_w + c * 8), nw[k]);
-            if (has_p) {
-#pragma unroll
-                for (int i = 0; i < 8; ++i) wv[k][i] = w[c * 8 + i];
+    if (warp == ncw) {
+        if (lane == 0) {
+            for (int it = 0; it < my_tokens; ++it) {
+                const int st = it % stages;
+                if (!tc::mbar_wait(&sm.empty[st], ((it / stages) & 1) ^ 1, &sm.abort_flag)) {
+                    atomicMax(status, (int)KB_TIMEOUT_TMA);
+                    break;
+                }
+                const size_t tok = (size_t)blockIdx.x + (size_t)it * gridDim.x;
+                uint8_t* base = smem + (size_t)st * rows * row_bytes;
+                tc::mbar_expect_tx(&sm.full[st], rows * row_bytes);
+                bulk_g2s(base, dxn + tok * D, row_bytes, &sm.full[st]);
+                bulk_g2s(base + row_bytes, o + tok * D, row_bytes, &sm.full[st]);
+                if (has_p) bulk_g2s(base + 2 * row_bytes, part + tok * D, row_bytes, &sm.full[st]);
             }
         }
-    }
-
-    for (int it = 0; it < my_tokens; ++it) {
-        const int st = it % stages;
-        const size_t tok = (size_t)blockIdx.x + (size_t)it * gridDim.x;
-        if (!tc::mbar_wait(&full[st], (it / stages) & 1, &abort_flag)) {
-            if (threadIdx.x == 0) atomicMax(status, (int)KB_TIMEOUT_TMA);
-            break;
-        }
-        const bf16* base = reinterpret_cast<const bf16*>(smem + (size_t)st * rows * row_bytes);
-        const float4 sv = *reinterpret_cast<const float4*>(stats2 + tok * 4);   // pi, l_p, r_p, rstd
-        const float pi = sv.x, lp = sv.y, rp = sv.z, rstd = sv.w;
-        float gw[CPT][8], hn[CPT][8], dif[CPT][8];                              // g * n_w, h * rstd, o - p
-        float A = 0.f, Bv = 0.f, Cv = 0.f;
+    } else {
+        float nw[CPT][8], wv[CPT][8], dw_acc[CPT][8], dnw_acc[CPT][8];
 #pragma unroll
         for (int k = 0; k < CPT; ++k) {
-            const int c = threadIdx.x + k * blockDim.x;
+            const int c = threadIdx.x + k * nct;
 #pragma unroll
-            for (int i = 0; i < 8; ++i) gw[k][i] = hn[k][i] = dif[k][i] = 0.f;
+            for (int i = 0; i < 8; ++i) nw[k][i] = wv[k][i] = dw_acc[k][i] = dnw_acc[k][i] = 0.f;
             if (c < nchunks) {
-                float g[8], of[8], pf[8];
-                unpack8(ld8(base + c * 8), g);
-                unpack8(ld8(base + D + c * 8), of);
-                if (has_p) unpack8(ld8(base + 2 * D + c * 8), pf);
+                unpack8(ld8(n_w + c * 8), nw[k]);
+                if (has_p) {
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    dif[k][i] = has_p ? of[i] - pf[i] : 0.f;
-                    hn[k][i] = (of[i] - pi * dif[k][i]) * rstd;
-                    gw[k][i] = g[i] * nw[k][i];
-                    dnw_acc[k][i] += g[i] * hn[k][i];
-                    A += gw[k][i] * hn[k][i];
-                    Bv += gw[k][i] * dif[k][i];
-                    Cv += hn[k][i] * dif[k][i];
+                    for (int i = 0; i < 8; ++i) wv[k][i] = w[c * 8 + i];
                 }
             }
         }
-        const float3 red = block_sum3(A, Bv, Cv, scr, it & 1);
-        const float m = red.x * invD;
-        const float cdot = rstd * (red.y - m * red.z);                          // sum dh (o - p)
-        const float dl = pi * (1.f - pi) * cdot;                                // dlse; dl_p = -dl
-        const float c_w = -dl * rp;
-        const float c_p = -dl * lp * rp * rp * invD;
+        for (int it = 0; it < my_tokens; ++it) {
+            const int st = it % stages, par = it & 1;
+            const size_t tok = (size_t)blockIdx.x + (size_t)it * gridDim.x;
+            const float4 sv = *reinterpret_cast<const float4*>(stats2 + tok * 4);   // pi, l_p, r_p, rstd
+            if (!tc::mbar_wait(&sm.full[st], (it / stages) & 1, &sm.abort_flag)) {
+                if (lane == 0) atomicMax(status, (int)KB_TIMEOUT_TMA);
+                break;
+            }
+            const bf16* base = reinterpret_cast<const bf16*>(smem + (size_t)st * rows * row_bytes);
+            const float pi = sv.x, lp = sv.y, rp = sv.z, rstd = sv.w;
+            float gw[CPT][8], hn[CPT][8], dif[CPT][8];                              // g * n_w, h * rstd, o - p
+            float A = 0.f, Bv = 0.f, Cv = 0.f;
+#pragma unroll
+            for (int k = 0; k < CPT; ++k) {
+                const int c = threadIdx.x + k * nct;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) gw[k][i] = hn[k][i] = dif[k][i] = 0.f;
+                if (c < nchunks) {
+                    float g[8], of[8], pf[8];
+                    unpack8(ld8(base + c * 8), g);
+                    unpack8(ld8(base + D + c * 8), of);
+                    if (has_p) unpack8(ld8(base + 2 * D + c * 8), pf);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        dif[k][i] = has_p ? of[i] - pf[i] : 0.f;
+                        hn[k][i] = (of[i] - pi * dif[k][i]) * rstd;
+                        gw[k][i] = g[i] * nw[k][i];
+                        dnw_acc[k][i] += g[i] * hn[k][i];
+                        A += gw[k][i] * hn[k][i];
+                        Bv += gw[k][i] * dif[k][i];
+                        Cv += hn[k][i] * dif[k][i];
+                    }
+                }
+            }
+            A = warp_sum(A);
+            Bv = warp_sum(Bv);
+            Cv = warp_sum(Cv);
+            if (lane == 0) sm.scr[par][warp] = make_float4(A, Bv, Cv, 0.f);
+            __syncwarp();
+            if (lane == 0) tc::mbar_arrive(&sm.meet);
+            if (!tc::mbar_wait(&sm.meet, it & 1, &sm.abort_flag)) {
+                if (lane == 0) atomicMax(status, (int)KB_TIMEOUT_EPI);
+                break;
+            }
+            float3 red = make_float3(0.f, 0.f, 0.f);
+            for (int i = 0; i < ncw; ++i) {
+                const float4 v = sm.scr[par][i];
+                red.x += v.x;
+                red.y += v.y;
+                red.z += v.z;
+            }
+            const float m = red.x * invD;
+            const float cdot = rstd * (red.y - m * red.z);                          // sum dh (o - p)
+            const float dl = pi * (1.f - pi) * cdot;                                // dlse; dl_p = -dl
+            const float c_w = -dl * rp;
+            const float c_p = -dl * lp * rp * rp * invD;
+#pragma unroll
+            for (int k = 0; k < CPT; ++k) {
+                const int c = threadIdx.x + k * nct;
+                if (c >= nchunks) continue;
+                float dh[8], dov[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    dh[i] = rstd * (gw[k][i] - hn[k][i] * m);
+                    dov[i] = (1.f - pi) * dh[i];
+                }
+                st8(dout + tok * D + (size_t)c * 8, pack8(dov));
+                if (has_p) {
+                    // o - p = dif and h = hn / rstd give p back without another shared-memory read
+                    float dp[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const float pf = hn[k][i] / rstd - (1.f - pi) * dif[k][i];
+                        dp[i] = pi * dh[i] + c_w * wv[k][i] - c_p * pf;
+                        dw_acc[k][i] += c_w * pf;
+                    }
+                    if (acc) red_add8(dpart + tok * D + (size_t)c * 8, pack8(dp));
+                    else st8(dpart + tok * D + (size_t)c * 8, pack8(dp));
+                }
+            }
+            if (threadIdx.x == 0) dlse[tok] = has_p ? dl : 0.f;
+            __syncwarp();
+            if (lane == 0) tc::mbar_arrive(&sm.empty[st]);
+        }
 #pragma unroll
         for (int k = 0; k < CPT; ++k) {
-            const int c = threadIdx.x + k * blockDim.x;
-            if (c >= nchunks) continue;
-            float dh[8], dov[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                dh[i] = rstd * (gw[k][i] - hn[k][i] * m);
-                dov[i] = (1.f - pi) * dh[i];
-            }
-            st8(dout + tok * D + (size_t)c * 8, pack8(dov));
-            if (has_p) {
-                float pf[8], dp[8];
-                unpack8(ld8(base + 2 * D + c * 8), pf);
+            const int c = threadIdx.x + k * nct;
+            if (c < nchunks) {
+                float* a = dnw_part + (size_t)blockIdx.x * D + (size_t)c * 8;
+                float* b = dw_part + (size_t)blockIdx.x * D + (size_t)c * 8;
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
-                    dp[i] = pi * dh[i] + c_w * wv[k][i] - c_p * pf[i];
-                    dw_acc[k][i] += c_w * pf[i];
+                    a[i] = dnw_acc[k][i];
+                    if (has_p) b[i] = dw_acc[k][i];
                 }
-                if (acc) red_add8(dpart + tok * D + (size_t)c * 8, pack8(dp));
-                else st8(dpart + tok * D + (size_t)c * 8, pack8(dp));
-            }
-        }
-        if (threadIdx.x == 0) dlse[tok] = has_p ? dl : 0.f;
-        __syncthreads();                     // every thread is done reading this stage
-        if (threadIdx.x == 0 && it + stages < my_tokens) issue(it + stages);
-    }
-#pragma unroll
-    for (int k = 0; k < CPT; ++k) {
-        const int c = threadIdx.x + k * blockDim.x;
-        if (c < nchunks) {
-            float* a = dnw_part + (size_t)blockIdx.x * D + (size_t)c * 8;
-            float* b = dw_part + (size_t)blockIdx.x * D + (size_t)c * 8;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                a[i] = dnw_acc[k][i];
-                if (has_p) b[i] = dw_acc[k][i];
             }
         }
     }
-    if (threadIdx.x == 0 && abort_flag) {    // copies still in flight must land before shared memory is released
-        for (int s = 0; s < stages; ++s) {
+    __syncthreads();
+    if (threadIdx.x == 0 && sm.abort_flag) {    // copies still in flight must land before shared memory is released
+        for (int i = 0; i < stages; ++i) {
             const uint64_t t0 = global_timer_ns();
-            while (!tc::mbar_try_wait(&full[s], 0) && !tc::mbar_try_wait(&full[s], 1) &&
+            while (!tc::mbar_try_wait(&sm.full[i], 0) && !tc::mbar_try_wait(&sm.full[i], 1) &&
                    global_timer_ns() - t0 < 2000000ull) {}
         }
     }
@@ -866,8 +883,8 @@ KB_API int kb_route_p2_bwd(const void* dxn, const void* o, const void* part, con
                            float* dnw_part, int N, int D, int* status, cudaStream_t st) {
     if (D % 8 != 0 || D < 8 || D > 8192 || N < 1) return 5;
     const int nchunks = D / 8;
-    const int cpt = (nchunks + 511) / 512;
-    const int threads = ((nchunks + cpt - 1) / cpt + 31) / 32 * 32;
+    const int cpt = (nchunks + 383) / 384;                                   // one chunk per thread up to D = 3072
+    const int threads = ((nchunks + cpt - 1) / cpt + 31) / 32 * 32 + 32;     // compute warps + the producer warp
     const int rows = 2 + (part ? 1 : 0);
     const size_t stage = (size_t)rows * D * 2;
     const int ctas_per_sm = 2;
@@ -888,6 +905,7 @@ KB_API int kb_route_p2_bwd(const void* dxn, const void* o, const void* part, con
     }
     if (cpt == 1) P2B(1)
     else if (cpt == 2) P2B(2)
+    else if (cpt == 3) P2B(3)
     else return 5;
 #undef P2B
     return cudaGetLastError() == cudaSuccess ? 0 : 8;
