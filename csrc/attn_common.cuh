@@ -81,6 +81,20 @@ __device__ __forceinline__ void mma_nt_tiles(uint32_t d_tmem, uint32_t a_addr, u
     }
 }
 
+// acc[128 x 128] = A B^T with A = 128 x HD bf16 held in tensor memory (8 columns per 16-wide
+// contraction step) and B a stored tile, K-major over head_dim.  Reading only B from shared
+// memory halves the shared-memory traffic of the product, which is what bounds the all-shared
+// form of a 128 x 128 tile.
+template <int HD>
+__device__ __forceinline__ void mma_tn_tile(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_addr, uint32_t idesc) {
+    const tc::DescHalves b = tc::smem_desc_halves(b_addr, 16, 1024);
+#pragma unroll
+    for (int k = 0; k < HD / 16; ++k) {
+        const uint32_t off = ((k >> 2) * HALF_BYTES + (k & 3) * 32) >> 4;
+        tc::mma_f16_ts_h(d_tmem, a_tmem + 8 * k, b.lo + off, b.hi, idesc, k != 0);
+    }
+}
+
 // acc[128 x HD] (+)= A B with A = 128 x 128 bf16 in tensor memory and B a stored tile read as
 // [K = 128 tokens, N = HD] (MN-major).  The packed A operand (8 columns per 16-wide contraction
 // step) is either one run of 64 columns (QUARTERS false) or four runs of 16 columns, one at the

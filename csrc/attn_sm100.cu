@@ -11,7 +11,9 @@
 //   tensor pipe:   S(j+1) ........ PV(j) S(j+2) ........ PV(j+1) S(j+3)
 //   softmax:       softmax(j) ......... softmax(j+1) ......... softmax(j+2)
 //
-//   S = Q K^T      tcgen05.mma, both operands K-major in shared memory (TMA, 128-byte swizzle)
+//   S = Q K^T      tcgen05.mma with Q read from tensor memory (written there once per CTA) and K
+//                  K-major in shared memory (TMA, 128-byte swizzle): half the shared-memory traffic
+//                  of the all-shared form, which is what bounds a 128 x 128 tile
 //   softmax        tcgen05.ld the row, online max / sum in base 2 with packed two-wide arithmetic,
 //                  P written back over the score columns as packed bf16 (tcgen05.st); a share of
 //                  the exponentials is evaluated on the FMA pipe so that the special-function unit
@@ -35,7 +37,7 @@ using namespace attn;
         break;                                         \
     }
 
-constexpr int KST = 3, VST = 2;                    // ring depths
+constexpr int KST = 4, VST = 2;                    // ring depths
 constexpr float RESCALE_THRESHOLD = 8.0f;          // in log2 units
 constexpr int EMU = 2;                             // of every 4 pairs of exponentials, this many run on the FMA pipe
 constexpr int FWD_THREADS = 320;                   // 8 softmax warps, MMA warp, TMA warp
@@ -49,6 +51,8 @@ struct FlashParams {
     float* lse;                                    // natural log; index head * lse_hs + (b * lse_bs | cu[b]) + t
     long long lse_hs, lse_bs;
     int q_col0, k_col0, v_col0;                    // first column of head 0 inside each operand's rows
+    const __nv_bfloat16* q_ptr;                    // the query matrix itself (rows are read directly, once per CTA)
+    long long q_stride, q_rows;
     int n_tiles;                                   // query tiles per sequence (grid decode)
     int* status;
 };
@@ -68,7 +72,7 @@ __device__ long long g_attn_dbg[16];
 
 template <int HD>
 constexpr int fwd_smem_bytes() {
-    return (1 + KST + VST) * Tile<HD>::BYTES + 1024 + 256 + 6 * BT * 4;
+    return (KST + VST) * Tile<HD>::BYTES + 1024 + 256 + 6 * BT * 4;
 }
 
 template <int HD>
@@ -78,11 +82,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     constexpr int TB = Tile<HD>::BYTES;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t* sQ = smem;
-    uint8_t* sK = smem + TB;
+    uint8_t* sK = smem;
     uint8_t* sV = sK + KST * TB;
     uint64_t* bars = reinterpret_cast<uint64_t*>(sV + VST * TB);
-    uint64_t* q_full = bars + 0;
+    uint64_t* q_ready = bars + 0;                  // the query tile sits in tensor memory
     uint64_t* k_full = bars + 1;                   // [KST]
     uint64_t* k_empty = k_full + KST;
     uint64_t* v_full = k_empty + KST;              // [VST]
@@ -95,7 +98,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     // row maxima [tile parity][half][row] and, at the end, row sums [4 + half][row] of the two threads
     // that share a query row
-    float* row_buf = reinterpret_cast<float*>(smem + (1 + KST + VST) * TB + 256);
+    float* row_buf = reinterpret_cast<float*>(smem + (KST + VST) * TB + 256);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // heavy tiles (late queries) first
@@ -116,7 +119,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const int n = qt * BT < Tb ? qt + 1 : 0;
 
     if (threadIdx.x == 0) {
-        tc::mbar_init(q_full, 1);
+        tc::mbar_init(q_ready, 8);
         for (int i = 0; i < KST; ++i) { tc::mbar_init(k_full + i, 1); tc::mbar_init(k_empty + i, 1); }
         for (int i = 0; i < VST; ++i) { tc::mbar_init(v_full + i, 1); tc::mbar_init(v_empty + i, 1); }
         tc::mbar_init(s_full + 0, 1);
@@ -135,20 +138,18 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     tc::tc_fence_before();
     __syncthreads();
     tc::tc_fence_after();
-    const uint32_t tmem0 = *tmem_slot;             // score buffers at columns 0 and 128, output accumulator at 256
-    const uint32_t tmem_oacc = tmem0 + 256;
+    // score buffers at columns 0 and 128, output accumulator at 256, the query tile (packed bf16) at 384
+    const uint32_t tmem0 = *tmem_slot;
+    const uint32_t tmem_oacc = tmem0 + 256, tmem_q = tmem0 + 384;
 
     if (n == 0) {
         // nothing to do (sequence shorter than the grid was sized for)
     } else if (warp == 9) {
         // ------------------------------------------------------------ TMA
         if (lane == 0) {
-            tc::prefetch_tmap(&tmQ);
             tc::prefetch_tmap(&tmK);
             tc::prefetch_tmap(&tmV);
-            const int qx = p.q_col0 + head * HD, kx = p.k_col0 + kvh * HD, vx = p.v_col0 + kvh * HD;
-            tc::mbar_expect_tx(q_full, TB);
-            load_tile<HD>(sQ, &tmQ, q_full, qx, seq_row0 + qt * BT);
+            const int kx = p.k_col0 + kvh * HD, vx = p.v_col0 + kvh * HD;
             // order of need: K0 K1 V0 K2 V1 K3 V2 ...
             auto load_k = [&](int j) -> bool {
                 const int ks = j % KST;
@@ -172,17 +173,17 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (lane == 0) {
             const uint32_t idesc_s = tc::instr_desc_f16(BT, BT, 1, 1, 0, 0);
             const uint32_t idesc_o = tc::instr_desc_f16(BT, HD, 1, 1, 0, 1);
-            const uint32_t q_addr = smem_u32(sQ), k_addr = smem_u32(sK), v_addr = smem_u32(sV);
+            const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV);
             do {
-                if (!tc::mbar_wait(q_full, 0, abort_flag) || !tc::mbar_wait(k_full, 0, abort_flag)) KB_FAIL_FWD(KB_TIMEOUT_TMA)
+                if (!tc::mbar_wait(q_ready, 0, abort_flag) || !tc::mbar_wait(k_full, 0, abort_flag)) KB_FAIL_FWD(KB_TIMEOUT_TMA)
                 tc::tc_fence_after();
-                mma_nt_tiles<HD>(tmem0, q_addr, k_addr, idesc_s);
+                mma_tn_tile<HD>(tmem0, tmem_q, k_addr, idesc_s);
                 tc::tc_commit(s_full + 0);
                 tc::tc_commit(k_empty + 0);
                 if (n > 1) {
                     if (!tc::mbar_wait(k_full + 1, 0, abort_flag)) KB_FAIL_FWD(KB_TIMEOUT_TMA)
                     tc::tc_fence_after();
-                    mma_nt_tiles<HD>(tmem0 + 128, q_addr, k_addr + TB, idesc_s);
+                    mma_tn_tile<HD>(tmem0 + 128, tmem_q, k_addr + TB, idesc_s);
                     tc::tc_commit(s_full + 1);
                     tc::tc_commit(k_empty + 1);
                 }
@@ -198,7 +199,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                         const int ks = (j + 2) % KST;
                         if (!tc::mbar_wait(k_full + ks, ((j + 2) / KST) & 1, abort_flag)) KB_FAIL_FWD(KB_TIMEOUT_TMA)
                         tc::tc_fence_after();
-                        mma_nt_tiles<HD>(tmem0 + (j & 1) * 128, q_addr, k_addr + ks * TB, idesc_s);
+                        mma_tn_tile<HD>(tmem0 + (j & 1) * 128, tmem_q, k_addr + ks * TB, idesc_s);
                         tc::tc_commit(s_full + (j & 1));
                         tc::tc_commit(k_empty + ks);
                     }
@@ -213,6 +214,25 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const uint32_t tmem_o = tmem_oacc + lane_base;
         float m_used = -INFINITY, l = 0.f;
         bool ok = true;
+        {
+            // this thread's half of its query row goes to tensor memory as the A operand of every S = Q K^T
+            constexpr int QW = HD / 2;                              // elements per thread
+            const long long grow = (long long)seq_row0 + qt * BT + r;
+            const __nv_bfloat16* src = p.q_ptr + grow * p.q_stride + p.q_col0 + head * HD + hf * QW;
+            uint32_t qp[QW / 2];
+#pragma unroll
+            for (int i = 0; i < QW / 8; ++i) {
+                uint4 v = make_uint4(0u, 0u, 0u, 0u);
+                if (grow < p.q_rows) v = *reinterpret_cast<const uint4*>(src + i * 8);
+                qp[4 * i] = v.x; qp[4 * i + 1] = v.y; qp[4 * i + 2] = v.z; qp[4 * i + 3] = v.w;
+            }
+            if constexpr (QW == 64) tc::tmem_st32(tmem_q + hf * 32 + lane_base, qp);
+            else tc::tmem_st16(tmem_q + hf * 16 + lane_base, qp);
+            tc::tmem_st_wait();
+            tc::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) tc::mbar_arrive(q_ready);
+        }
 #ifdef KB_ATTN_PROFILE
         const bool prof = blockIdx.x == 0 && threadIdx.x == 0;
         long long dbg[8] = {0, 0, 0, 0, 0, 0, 0, 0};
@@ -431,6 +451,9 @@ KB_API int kb_flash_fwd(const void* q, long long q_stride, int q_cols, int q_col
     p.lse_hs = cu_seqlens ? total : max_T;
     p.lse_bs = cu_seqlens ? 0 : (long long)H * max_T;
     p.q_col0 = q_col0; p.k_col0 = k_col0; p.v_col0 = v_col0;
+    p.q_ptr = (const __nv_bfloat16*)q;
+    p.q_stride = q_stride;
+    p.q_rows = rows;
     p.n_tiles = (max_T + BT - 1) / BT;
     p.status = status;
     return hd == 128 ? launch_fwd<128>(tmQ, tmK, tmV, p, max_T, st) : launch_fwd<64>(tmQ, tmK, tmV, p, max_T, st);
