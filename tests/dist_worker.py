@@ -21,6 +21,16 @@ def build(cfg, device, dtype, comm, seed=0):
     return TrainEngine(model, device=device, dtype=dtype, comm=comm, muon_lr=0.02, adamw_lr=1e-3)
 
 
+def tp_cfg(world: int) -> ModelConfig:
+    """Model for the tensor-parallel modes: the smoke preset up to two ranks, a wider one (8 query and
+    8 key/value heads, every projection a multiple of 64 columns per rank) for four and eight."""
+    if world <= 2:
+        return ModelConfig(**MODEL_PRESETS["smoke"], attn_res=True, attn_res_n_blocks=2)
+    return ModelConfig(hidden_size=512, num_layers=4, num_attention_heads=8, num_kv_heads=8, head_dim=64,
+                       intermediate_size=1024, vocab_size=1024, max_position_embeddings=2048, attn_res=True,
+                       attn_res_n_blocks=2)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--mode", required=True)
@@ -79,7 +89,7 @@ def main():
             comm = FusedTensorParallelComm(tp_group, None)
         else:
             comm = TensorParallelComm(tp_group, None, sequence_parallel=True)
-        cfg = ModelConfig(**MODEL_PRESETS["smoke"], attn_res=True, attn_res_n_blocks=2)
+        cfg = tp_cfg(world)
         shared = torch.randint(0, cfg.vocab_size, (2, 128 * world), generator=torch.Generator().manual_seed(7))
         eng = build(cfg, device, dtype, comm)
         losses = [float(eng.train_step([shared])["loss"]) for _ in range(a.steps)]
@@ -94,7 +104,7 @@ def main():
         import copy
         from kotodama_b200.serve.engine import SamplingParams, ServingEngine
         from kotodama_b200.serve.tp import ServeTP, TPLeader, run_follower
-        cfg = ModelConfig(**MODEL_PRESETS["smoke"], attn_res=True, attn_res_n_blocks=2)
+        cfg = tp_cfg(world) if cuda else ModelConfig(**MODEL_PRESETS["smoke"], attn_res=True, attn_res_n_blocks=2)
         torch.manual_seed(0)
         full = KotodamaModel(cfg)
         prompts = [[(7 * i + 3 * j) % cfg.vocab_size for j in range(5 + 3 * i)] for i in range(5)]

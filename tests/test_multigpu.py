@@ -1,4 +1,5 @@
-"""Two GPU ranks: in-kernel NVLink collectives against the NCCL strategy."""
+"""Several GPU ranks (2 and, where the box has them, 4 or 8): in-kernel NVLink collectives against
+the NCCL strategy, for data parallelism, fused tensor parallelism and tensor-parallel serving."""
 import os
 
 import pytest
@@ -8,14 +9,18 @@ from test_distributed_cpu import _launch
 
 pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
 
+_N = torch.cuda.device_count() if torch.cuda.is_available() else 0
+RANKS = sorted({2, max([n for n in (2, 4, 8) if n <= _N] or [2])})
 
-def test_native_comm_matches_library_comm(tmp_path):
+
+@pytest.mark.parametrize("nproc", RANKS)
+def test_native_comm_matches_library_comm(tmp_path, nproc):
     out = str(tmp_path / "r")
     env_backup = dict(os.environ)
     os.environ["NCCL_NVLS_ENABLE"] = "0"
     try:
-        lib = _launch("gpu_library", out, steps=3)
-        nat = _launch("gpu_native", out, steps=3)
+        lib = _launch("gpu_library", out, nproc=nproc, steps=3)
+        nat = _launch("gpu_native", out, nproc=nproc, steps=3)
     finally:
         os.environ.clear(); os.environ.update(env_backup)
     assert all(r["ranks_match"] for r in lib) and all(r["ranks_match"] for r in nat)
@@ -26,14 +31,15 @@ def test_native_comm_matches_library_comm(tmp_path):
     assert float((pl - pn).norm() / pl.norm()) < 2e-2
 
 
-def test_fused_tp_kernels_match_library_tp(tmp_path):
+@pytest.mark.parametrize("nproc", RANKS)
+def test_fused_tp_kernels_match_library_tp(tmp_path, nproc):
     """all-gather->GEMM and GEMM->reduce-scatter kernels against NCCL collectives around plain GEMMs."""
     out = str(tmp_path / "t")
     env_backup = dict(os.environ)
     os.environ["NCCL_NVLS_ENABLE"] = "0"
     try:
-        lib = _launch("gpu_tp_library", out, steps=3)
-        fused = _launch("gpu_tp_fused", out, steps=3)
+        lib = _launch("gpu_tp_library", out, nproc=nproc, steps=3)
+        fused = _launch("gpu_tp_fused", out, nproc=nproc, steps=3)
     finally:
         os.environ.clear(); os.environ.update(env_backup)
     assert fused[0]["fused_calls"] > 0 and fused[0]["fallback_calls"] == 0, fused[0]
@@ -44,13 +50,14 @@ def test_fused_tp_kernels_match_library_tp(tmp_path):
     assert float((pl - pf).norm() / pl.norm()) < 2e-2
 
 
-def test_tensor_parallel_serving_native_allreduce(tmp_path):
-    """TP=2 serving on two GPUs: decode steps run from CUDA graphs that contain the push all-reduce
+@pytest.mark.parametrize("nproc", RANKS)
+def test_tensor_parallel_serving_native_allreduce(tmp_path, nproc):
+    """Tensor-parallel serving over all ranks: decode steps run from CUDA graphs that contain the push all-reduce
     kernel; ranks stay in lock-step; the kernel matches an exact fp32 sum."""
     env_backup = dict(os.environ)
     os.environ["NCCL_NVLS_ENABLE"] = "0"
     try:
-        res = _launch("gpu_tp_serve", str(tmp_path / "s"))
+        res = _launch("gpu_tp_serve", str(tmp_path / "s"), nproc=nproc)
     finally:
         os.environ.clear(); os.environ.update(env_backup)
     for r in res:
