@@ -298,6 +298,25 @@ class CudaOps(TorchOps):
         dw = self._colsum(dw_part)
         return dw * rn_w.float(), dw * q.float(), dn_w
 
+    # ------------------------------------------------------------------ sampling
+    def sample(self, logits, temperature, top_k, top_p, rep_penalty, seeds, counters, seen, slots):
+        """Batched device sampler (``csrc/sampler.cu``); per-row parameter sequences go to the device in
+        one small copy each."""
+        B, V = logits.shape
+        dev = logits.device
+        f = lambda x: torch.as_tensor(list(x), dtype=torch.float32).to(dev, non_blocking=True)
+        i32 = lambda x: torch.as_tensor(list(x), dtype=torch.int32).to(dev, non_blocking=True)
+        m = (1 << 63) - 1
+        sd = torch.as_tensor([int(x) & m for x in seeds], dtype=torch.int64).to(dev, non_blocking=True)
+        out = torch.empty(B, device=dev, dtype=torch.long)
+        t, k, p, r, c, sl = f(temperature), i32(top_k), f(top_p), f(rep_penalty), i32(counters), i32(slots)
+        if logits.dtype not in (torch.bfloat16, torch.float32) or logits.stride(1) != 1:
+            raise KernelError(f"sampler takes bf16/fp32 row-major logits, got {logits.dtype} {logits.stride()}")
+        self._call("kb_sample", _p(logits), _I(0 if logits.dtype == torch.bfloat16 else 1), _LL(logits.stride(0)), _I(B),
+                   _I(V), _p(t), _p(k), _p(p), _p(r), _p(sd), _p(c), _p(seen), _I(seen.shape[1] if seen is not None else 0),
+                   _p(sl), _p(out), _st())
+        return out
+
     # ------------------------------------------------------------------ AttnRes route, blocked form
     def route_blocked_ok(self, S: int, D: int) -> bool:
         return bool(self.lib.kb_route_blocked_ok(_I(S), _I(D)))

@@ -371,6 +371,63 @@ class TorchOps:
         dqkv_out[:, : nh * hd] = dx.reshape(n, nh * hd)
         return dqw, dkw
 
+    # ------------------------------------------------------------ sampling
+    @staticmethod
+    def sample_uniform(seed: int, counter: int) -> float:
+        """The sampler's random draw: splitmix64 of (seed, counter), top 24 bits, in [0, 1)."""
+        m = (1 << 64) - 1
+        z = (seed + 0x9E3779B97F4A7C15 * (counter + 1)) & m
+        z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & m
+        z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & m
+        z ^= z >> 31
+        return (z >> 40) / 16777216.0
+
+    def sample(self, logits: torch.Tensor, temperature, top_k, top_p, rep_penalty, seeds, counters,
+               seen: Optional[torch.Tensor], slots) -> torch.Tensor:
+        """Next token per row of ``logits[B,V]`` in the reference's order (``serve.py:266-304``):
+        repetition penalty (tokens whose bit is set in the request's ``seen`` bitmap row) ->
+        temperature -> top-k (ties at the k-th value kept) -> top-p -> multinomial by inverse CDF in
+        vocabulary order with ``u = sample_uniform(seed, counter)``; greedy at temperature 0.  The
+        chosen token's bit is set in ``seen``.  Parameters are per-row sequences."""
+        B, V = logits.shape
+        out = torch.empty(B, dtype=torch.long)
+        for b in range(B):
+            v = logits[b].detach().float().cpu()
+            row = seen[int(slots[b])] if seen is not None else None
+            if row is not None and float(rep_penalty[b]) != 1.0:
+                words = row.cpu().to(torch.int64) & 0xFFFFFFFF
+                bits = ((words.unsqueeze(1) >> torch.arange(32)) & 1).flatten()[:V].bool()
+                rp = float(rep_penalty[b])
+                v = torch.where(bits, torch.where(v > 0, v / rp, v * rp), v)
+            T = float(temperature[b])
+            if T <= 0:
+                tok = int(v.argmax())
+            else:
+                v = v / T
+                k = int(top_k[b])
+                keep = torch.ones(V, dtype=torch.bool)
+                if 0 < k < V:
+                    keep &= v >= torch.topk(v, k).values[-1]
+                w = torch.where(keep, torch.exp(v - v.max()), torch.zeros_like(v))
+                p = float(top_p[b])
+                if 0.0 < p < 1.0:
+                    srt, idx = torch.sort(torch.where(keep, v, torch.full_like(v, float("-inf"))), descending=True)
+                    ws = w[idx]
+                    before = ws.cumsum(0) - ws                     # mass of strictly earlier items
+                    ok = (before <= p * float(w.sum())) & (ws > 0)
+                    cut = srt[ok][-1] if bool(ok.any()) else srt[0]
+                    w = torch.where(v >= cut, w, torch.zeros_like(w))    # ties at the threshold stay
+                target = self.sample_uniform(int(seeds[b]), int(counters[b])) * float(w.sum())
+                cdf = w.cumsum(0)
+                hit = ((cdf > target) & (w > 0)).nonzero()
+                tok = int(hit[0]) if hit.numel() else int((w > 0).nonzero()[-1])
+            out[b] = tok
+            if row is not None:
+                word = int(row[tok >> 5].item()) & 0xFFFFFFFF
+                word |= 1 << (tok & 31)
+                row[tok >> 5] = word - (1 << 32) if word >= (1 << 31) else word
+        return out.to(logits.device)
+
     # ------------------------------------------------------------ attention
     def attention_fwd(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, need_grad: bool = True,
                       cu_seqlens: Optional[torch.Tensor] = None, max_seqlen: int = 0):

@@ -41,6 +41,7 @@ class SamplingParams:
     top_p: float = 0.0
     repetition_penalty: float = 1.0
     eos_token_id: Optional[int] = None
+    seed: Optional[int] = None           # of the sampler's random draws; None: derived from the request id
 
 
 @dataclass
@@ -53,6 +54,7 @@ class Request:
     ctx_len: int = 0
     finished: bool = False
     finish_reason: str = ""
+    slot: int = -1                       # row of the engine's seen-token bitmap (repetition penalty)
 
 
 class PagedKVCache:
@@ -84,34 +86,31 @@ class PagedKVCache:
         self.free.extend(reversed(pages))
 
 
-def sample_tokens(logits: torch.Tensor, reqs: list[Request], ops: Any) -> torch.Tensor:
-    """Next token per row of ``logits[B,V]``.  All-greedy batches use the argmax kernel."""
+def request_seed(r: Request) -> int:
+    return r.params.seed if r.params.seed is not None else (0x9E3779B1 * (r.rid + 1) + 12345) & 0x7FFFFFFF
+
+
+def sample_tokens(logits: torch.Tensor, reqs: list[Request], ops: Any, seen: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Next token per row of ``logits[B,V]``.  All-greedy batches use the argmax kernel; anything else
+    goes to the batched sampler of the ops backend (on CUDA one kernel for the whole batch, with
+    per-request parameters, seeds and seen-token bitmaps): repetition penalty -> temperature -> top-k
+    -> top-p -> multinomial, the reference's order (``serve.py:266-304``)."""
     if all(r.params.temperature == 0 and r.params.repetition_penalty == 1.0 for r in reqs):
         return ops.argmax(logits)
-    out = torch.empty(len(reqs), dtype=torch.long, device=logits.device)
-    for i, r in enumerate(reqs):
-        lg = logits[i].float()
-        p = r.params
-        if p.repetition_penalty != 1.0:
-            seen = torch.tensor(sorted(set(r.prompt + r.generated)), device=lg.device, dtype=torch.long)
-            if seen.numel():
-                vals = lg[seen]
-                lg[seen] = torch.where(vals > 0, vals / p.repetition_penalty, vals * p.repetition_penalty)
-        if p.temperature == 0:
-            out[i] = lg.argmax()
-            continue
-        lg = lg / p.temperature
-        if p.top_k > 0:
-            kth = torch.topk(lg, min(p.top_k, lg.numel())).values[-1]
-            lg = torch.where(lg < kth, torch.full_like(lg, float("-inf")), lg)
-        if 0.0 < p.top_p < 1.0:
-            srt, idx = torch.sort(lg, descending=True)
-            cum = torch.softmax(srt, -1).cumsum(-1)
-            remove = cum - torch.softmax(srt, -1) > p.top_p
-            srt = srt.masked_fill(remove, float("-inf"))
-            lg = torch.full_like(lg, float("-inf")).scatter(0, idx, srt)
-        out[i] = torch.multinomial(torch.softmax(lg, -1), 1)[0]
-    return out
+    ps = [r.params for r in reqs]
+    slots = [max(r.slot, 0) for r in reqs]
+    if seen is None and any(p.repetition_penalty != 1.0 for p in ps):
+        # no engine-owned bitmaps (direct use): build them from the requests' token lists
+        import numpy as np
+        words = np.zeros((len(reqs), (logits.shape[1] + 31) // 32), dtype=np.uint32)
+        for b, r in enumerate(reqs):
+            ids = np.unique(np.asarray(r.prompt + r.generated, dtype=np.int64))
+            np.bitwise_or.at(words[b], ids >> 5, (np.uint32(1) << (ids & 31).astype(np.uint32)))
+        seen = torch.from_numpy(words.view(np.int32)).to(logits.device)
+        slots = list(range(len(reqs)))
+    return ops.sample(logits, [p.temperature for p in ps], [p.top_k for p in ps], [p.top_p for p in ps],
+                      [p.repetition_penalty for p in ps], [request_seed(r) for r in reqs],
+                      [len(r.generated) for r in reqs], seen, slots)
 
 
 class ServingEngine:
@@ -140,6 +139,11 @@ class ServingEngine:
         self.waiting: list[Request] = []
         self.running: list[Request] = []
         self._next_id = 0
+        # one bitmap row per batch slot: the tokens a request has seen (prompt + generated), for the
+        # repetition penalty of the device sampler
+        self.seen_words = (cfg.vocab_size + 31) // 32
+        self.seen = torch.zeros(max_batch, self.seen_words, dtype=torch.int32, device=self.device)
+        self._free_slots = list(range(max_batch - 1, -1, -1))
         self._dec_states: dict[int, dict] = {}
         self.use_cuda_graphs = True          # decode steps are replayed from captured graphs on CUDA
         self.prefill_batch_tokens = prefill_batch_tokens     # tokens of one packed prefill pass over several prompts; 0: one prompt per pass
@@ -180,9 +184,7 @@ class ServingEngine:
             for r in lst:
                 if r.rid == rid:
                     lst.remove(r)
-                    if r.pages:
-                        self.cache.release(r.pages)
-                        r.pages = []
+                    self._release(r)
                     r.finished, r.finish_reason = True, "cancelled"
                     return True
         return False
@@ -258,7 +260,7 @@ class ServingEngine:
         dev = self.device
         seqs = {"cu_seqlens": torch.tensor(cu, dtype=torch.int32).to(dev), "max_seqlen": max(ns)}
         logits = self._forward(ids.to(dev), pos.to(dev), slots.to(dev), None, last.to(dev), seqs=seqs)
-        toks = sample_tokens(logits, reqs, self.ops).tolist()
+        toks = sample_tokens(logits, reqs, self.ops, self.seen).tolist()
         if self.tp is not None:
             toks = self.tp.sync_tokens(toks, self.device)
         for r, n, tok in zip(reqs, ns, toks):
@@ -279,6 +281,9 @@ class ServingEngine:
             # pages are handed out in admission order, which is also the order of the decode batch:
             # neighbouring requests of a decode step then read neighbouring pages
             r.pages = self.cache.allocate(need)
+            r.slot = self._free_slots.pop()
+            if r.params.repetition_penalty != 1.0:
+                self._init_seen(r)
             self.waiting.pop(0)
             self.running.append(r)
             admitted.append(r)
@@ -292,6 +297,22 @@ class ServingEngine:
         if cur:
             groups.append(cur)
         return groups
+
+    def _init_seen(self, r: Request) -> None:
+        """Bitmap of the prompt's tokens, built on the host and copied into the request's slot."""
+        import numpy as np
+        words = np.zeros(self.seen_words, dtype=np.uint32)
+        ids = np.unique(np.asarray(r.prompt, dtype=np.int64))
+        np.bitwise_or.at(words, ids >> 5, (np.uint32(1) << (ids & 31).astype(np.uint32)))
+        self.seen[r.slot].copy_(torch.from_numpy(words.view(np.int32)), non_blocking=True)
+
+    def _release(self, r: Request) -> None:
+        if r.pages:
+            self.cache.release(r.pages)
+            r.pages = []
+        if r.slot >= 0:
+            self._free_slots.append(r.slot)
+            r.slot = -1
 
     def _accept(self, r: Request, tok: int) -> None:
         r.generated.append(tok)
@@ -358,10 +379,10 @@ class ServingEngine:
                 g = st["graphs"][bucket] = (graph, logits, toks)
             g[0].replay()
             logits, toks = g[1], g[2]
-            toks = toks.tolist() if greedy else sample_tokens(logits, reqs, self.ops).tolist()
+            toks = toks.tolist() if greedy else sample_tokens(logits, reqs, self.ops, self.seen).tolist()
         else:
             logits = self._forward(st["ids"], st["pos"], st["slots"], decode, st["rows"])
-            toks = sample_tokens(logits, reqs, self.ops).tolist()
+            toks = sample_tokens(logits, reqs, self.ops, self.seen).tolist()
         if self.tp is not None:
             toks = self.tp.sync_tokens(toks, self.device)
         for r, t in zip(reqs, toks):
@@ -385,8 +406,7 @@ class ServingEngine:
         done += [r for r in self.running if r.finished]
         self.running = [r for r in self.running if not r.finished]
         for r in done:
-            self.cache.release(r.pages)
-            r.pages = []
+            self._release(r)
         self.stats["prefill_s"] += t1 - t0
         self.stats["decode_s"] += time.perf_counter() - t1
         self.stats["steps"] += 1

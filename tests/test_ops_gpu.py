@@ -413,3 +413,37 @@ def test_bounded_wait_reports_status_and_context_survives(ops):
     flags[:2] = 1                                                          # both "ranks" have signalled epoch 1
     assert ops.lib.kb_flag_wait(VP(flags.data_ptr()), I(2), I(0), I(1), D(0.2), VP(st.data_ptr()), stream) == 0
     ops.check_status()
+
+
+# ----------------------------------------------------------------------------- device sampler
+@pytest.mark.parametrize("V,dtype", [(49152, torch.bfloat16), (1000, torch.float32), (50257, torch.float32)])
+def test_device_sampler_matches_host_sampler(ops, V, dtype):
+    """A mixed batch (greedy, top-k, nucleus, repetition penalty, plain multinomial) in one launch equals
+    the per-request host sampler for the same seeds and draw counters, and records the sampled tokens
+    in the seen-token bitmaps."""
+    B = 12
+    g = torch.Generator(device="cuda").manual_seed(3)
+    logits = (torch.randn(B, V, device="cuda", generator=g) * 4).to(dtype)
+    temp = [0.0, 0.7, 1.0, 1.3, 0.0, 0.9, 1.0, 0.5, 1.0, 2.0, 0.8, 1.0]
+    top_k = [50, 50, 0, 5, 0, 1, 200, 0, 0, 40, 50, 3]
+    top_p = [0.0, 0.0, 0.9, 0.0, 0.0, 0.0, 0.5, 0.3, 0.0, 0.95, 0.8, 0.0]
+    rep = [1.0, 1.0, 1.0, 1.5, 2.0, 1.0, 1.2, 1.0, 1.0, 1.0, 1.3, 1.0]
+    seeds = [11 * i + 5 for i in range(B)]
+    counters = [i % 5 for i in range(B)]
+    slots = list(range(B - 1, -1, -1))
+    words = (V + 31) // 32
+    seen = torch.randint(-2**31, 2**31 - 1, (B, words), device="cuda", generator=g, dtype=torch.int64).to(torch.int32)
+    seen &= torch.randint(-2**31, 2**31 - 1, (B, words), device="cuda", generator=g, dtype=torch.int64).to(torch.int32)
+    seen_host = seen.cpu().clone()
+    got = ops.sample(logits, temp, top_k, top_p, rep, seeds, counters, seen, slots).cpu()
+    ref = TORCH_OPS.sample(logits.float().cpu(), temp, top_k, top_p, rep, seeds, counters, seen_host, slots)
+    same = int((got == ref).sum())
+    assert same >= B - 1, (got.tolist(), ref.tolist())             # a draw on a CDF boundary may round the other way
+    for b in (0, 4, 5):                                             # greedy and top-1 rows are exact
+        assert int(got[b]) == int(ref[b])
+    for b in range(B):                                              # the sampled token is now marked as seen
+        t = int(got[b])
+        assert (int(seen[slots[b], t >> 5].item()) >> (t & 31)) & 1
+    if same == B:
+        assert torch.equal(seen.cpu(), seen_host)
+    ops.check_status()

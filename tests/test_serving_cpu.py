@@ -105,10 +105,22 @@ def test_sampler_order_and_limits():
     assert int(sample_tokens(logits.clone(), [r], ops)[0]) == 2      # token 3 penalised: 3/2 < 2
     r2 = Request(1, [0], SamplingParams(temperature=1.0, top_k=1))
     assert int(sample_tokens(logits.clone(), [r2], ops)[0]) == 3
-    torch.manual_seed(0)
-    r3 = Request(2, [0], SamplingParams(temperature=1.0, top_k=0, top_p=0.5))
-    draws = {int(sample_tokens(logits.clone(), [r3], ops)[0]) for _ in range(50)}
+    draws = set()
+    for seed in range(50):
+        r3 = Request(2, [0], SamplingParams(temperature=1.0, top_k=0, top_p=0.5, seed=seed))
+        draws.add(int(sample_tokens(logits.clone(), [r3], ops)[0]))
     assert draws <= {3}                                              # p(3)=0.64 alone exceeds 0.5
+    # the multinomial draw follows the softmax: 4000 seeded draws of a 3-way distribution
+    lg = torch.log(torch.tensor([[0.2, 0.5, 0.3]]))
+    counts = [0, 0, 0]
+    for seed in range(4000):
+        counts[int(sample_tokens(lg, [Request(3, [0], SamplingParams(temperature=1.0, top_k=0, seed=seed))], ops)[0])] += 1
+    assert abs(counts[0] / 4000 - 0.2) < 0.03 and abs(counts[1] / 4000 - 0.5) < 0.03
+    # same seed and draw counter -> same token; the counter is the number of tokens generated so far
+    a = Request(4, [0], SamplingParams(temperature=1.0, top_k=0, seed=7))
+    b = Request(5, [0], SamplingParams(temperature=1.0, top_k=0, seed=7))
+    big = torch.randn(1, 500, generator=torch.Generator().manual_seed(1)) * 3
+    assert int(sample_tokens(big, [a], ops)[0]) == int(sample_tokens(big, [b], ops)[0])
 
 
 def test_page_allocator():
