@@ -241,6 +241,10 @@ def train(args: argparse.Namespace) -> dict[str, Any]:
     from .monitor.watchdog import StepWatchdog
     profiler = StepProfiler(args, enabled=is_main and args.profile)
     watchdog = StepWatchdog(args.watchdog_s, rank=rank)
+    health = None
+    if world > 1:
+        from .parallel.health import PeerHealth
+        health = PeerHealth()
 
     # -- loop --------------------------------------------------------------------
     if is_main:
@@ -252,6 +256,11 @@ def train(args: argparse.Namespace) -> dict[str, Any]:
     history: list[float] = []
     last_step = start_step - 1
     for step in range(start_step, total_steps):
+        if health is not None:
+            # a peer that left between steps is noticed here, on the host, before this rank enters
+            # kernels and collectives that could no longer complete
+            health.raise_if_peer_left()
+            health.beat(step)
         profiler.step_begin(step)
         if not args.reference_lr_order:
             scheduler.step(step)
@@ -365,11 +374,23 @@ def main(argv: Optional[list[str]] = None) -> None:
     args = parse_args(argv)
     try:
         train(args)
-    except Exception:
+    except Exception as e:
         logger.exception("Training failed")
+        _announce_leave(f"{type(e).__name__}: {e}")
         raise
     finally:
         cleanup_distributed()
+
+
+def _announce_leave(reason: str) -> None:
+    """Tell the peers (through the rendezvous store) that this rank is on its way out."""
+    import torch.distributed as dist
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+        from .parallel.health import PeerHealth
+        try:
+            PeerHealth().announce_leave(reason)
+        except Exception:                          # noqa: BLE001
+            pass
 
 
 if __name__ == "__main__":

@@ -41,7 +41,9 @@ def main():
     cuda = a.mode.startswith("gpu")
     if cuda:
         torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
-    dist.init_process_group("nccl" if cuda else "gloo")
+    import datetime
+    dist.init_process_group("nccl" if cuda else "gloo",
+                            timeout=datetime.timedelta(seconds=20 if a.mode.startswith("cpu_rank_leaves") else 600))
     device = torch.device("cuda", torch.cuda.current_device()) if cuda else torch.device("cpu")
     dtype = torch.bfloat16 if cuda else torch.float32
     preset = "smoke" if cuda else "tiny"
@@ -139,6 +141,43 @@ def main():
                 errs.append(float((got.float() - exact.float()).abs().max()))
             eng.ops.check_status()
             result.update(allreduce_max_err=max(errs))
+    if a.mode in ("cpu_rank_leaves", "cpu_rank_leaves_silent"):
+        # the last rank leaves the job between steps: with a notice in the store (the others raise on
+        # the host before their next step) or silently (their next collective ends with an error
+        # within the process group's timeout)
+        import time
+        from kotodama_b200.parallel.health import PeerHealth, PeerLeft
+        comm = LibraryComm(distributed_muon=True)
+        eng = build(cfg, device, dtype, comm)
+        health = PeerHealth()
+        outcome, steps_done, t_detect = "completed", 0, None
+        for step in range(4):
+            try:
+                if a.mode == "cpu_rank_leaves":
+                    health.raise_if_peer_left()
+                health.beat(step)
+                if rank == world - 1 and step == 2:
+                    if a.mode == "cpu_rank_leaves":
+                        health.announce_leave("test: leaving between steps")
+                    outcome = "left"
+                    break
+                if rank != world - 1 and step == 2:
+                    time.sleep(1.0)                 # let the notice (or the exit) happen first
+                    if a.mode == "cpu_rank_leaves":
+                        health.raise_if_peer_left()
+                t0 = time.time()
+                eng.train_step([batch])
+                steps_done += 1
+            except PeerLeft as e:
+                outcome, t_detect = "peer_left:" + str(e), 0.0
+                break
+            except Exception as e:                  # noqa: BLE001 - the collective failed
+                outcome, t_detect = "collective_error:" + type(e).__name__, time.time() - t0
+                break
+        result.update(outcome=outcome, steps_done=steps_done, detect_s=t_detect)
+        with open(f"{a.out}.{a.mode}.{rank}.json", "w") as fh:
+            json.dump(result, fh)
+        os._exit(0)                                 # no barrier: the group is incomplete by design
     if a.mode == "cpu_tp_autograd":
         from kotodama_b200.optim.muon import build_hybrid_optimizer
         from kotodama_b200.parallel.tp import (apply_tensor_parallelism, create_process_groups, gather_full_state_dict,

@@ -219,3 +219,49 @@ def test_geometric_monitor_tiers():
     hidden, _ = mon._probe_forward(ids, set())
     ref, _ = model.hidden_states(ids)
     assert torch.allclose(hidden[cfg.num_layers - 1], ref, atol=1e-5)
+
+
+def test_watchdog_names_rank_and_phase():
+    import time
+    from kotodama_b200.monitor.watchdog import StepWatchdog
+    seen = []
+    wd = StepWatchdog(0.15, rank=3, on_stall=lambda r, s, p, dt: seen.append((r, s, p)), poll_s=0.02)
+    wd.phase(7, "data")
+    time.sleep(0.05)
+    wd.phase(7, "train_step")
+    time.sleep(0.4)                                   # stalls in train_step
+    wd.phase(8, "data")                               # heartbeat: the report is not repeated for the new phase
+    time.sleep(0.05)
+    wd.stop()
+    assert seen == [(3, 7, "train_step")]
+    assert wd.stalls[0][:2] == (7, "train_step") and wd.stalls[0][2] > 0.15
+    off = StepWatchdog(0.0)
+    off.phase(0, "x")
+    off.stop()
+    assert off._thread is None
+
+
+def test_halt_on_nonfinite_stops_the_run(tmp_path, monkeypatch):
+    from kotodama_b200 import train as train_mod
+    from kotodama_b200.config import default_args
+    from kotodama_b200.engine import TrainEngine
+    real = TrainEngine.train_step
+    calls = {"n": 0}
+
+    def poisoned(self, micro, **kw):
+        res = real(self, micro, **kw)
+        calls["n"] += 1
+        if calls["n"] == 3:
+            res["loss"] = res["loss"] * float("nan")
+        return res
+    monkeypatch.setattr(TrainEngine, "train_step", poisoned)
+    args = default_args(model_size="tiny", device="cpu", dtype="fp32", random_data=True, total_steps=6, sequence_length=32,
+                        micro_batch_size=2, global_batch_tokens=64, checkpoint_dir=str(tmp_path), save_every=0,
+                        log_every=100, warmup_steps=2, attn_res=True, attn_res_n_blocks=2, halt_on_nonfinite=True)
+    with pytest.raises(RuntimeError, match="non-finite"):
+        train_mod.train(args)
+    assert calls["n"] == 3
+    calls["n"] = 0
+    args.halt_on_nonfinite = False                     # the reference's behaviour: log and continue
+    out = train_mod.train(args)
+    assert out["last_step"] == 5

@@ -87,3 +87,21 @@ def test_tensor_parallel_serving_matches_single_process(tmp_path):
         assert r["tp"] == r["ref"], (r["tp"], r["ref"])
         assert r["local_heads"] == 2 and r["local_kv"] == 1
         assert r["library_calls"] > 0 and r["native_calls"] == 0
+
+
+def test_rank_leaves_between_steps_is_noticed_on_the_host(tmp_path):
+    """One rank announces its departure between steps; the survivor raises PeerLeft before entering
+    the next step (no collective is attempted, nothing waits for a timeout)."""
+    res = _launch("cpu_rank_leaves", str(tmp_path / "h"), timeout=300)
+    assert res[1]["outcome"] == "left" and res[1]["steps_done"] == 2
+    assert res[0]["outcome"].startswith("peer_left") and "[1]" in res[0]["outcome"]
+    assert res[0]["steps_done"] == 2
+
+
+def test_rank_leaves_silently_ends_the_next_collective_with_an_error(tmp_path):
+    """Without a notice the survivor's next collective fails within the process group's (short)
+    timeout instead of hanging."""
+    res = _launch("cpu_rank_leaves_silent", str(tmp_path / "s"), timeout=300)
+    assert res[1]["outcome"] == "left"
+    assert res[0]["outcome"].startswith("collective_error"), res[0]
+    assert res[0]["detect_s"] < 60
