@@ -609,6 +609,39 @@ class TrainEngine:
                 for s, x, transposed, rows, cols in prepared:
                     comm.muon_apply(ops, s, x, g["lr"], g["weight_decay"], max(1.0, (rows / cols) ** 0.5), transposed)
                 owned = []
+            if comm.tp_size > 1 and hasattr(comm, "muon_exchange_group"):
+                # Tensor parallelism: matrices of one shape and shard dimension travel together.  Two
+                # all-to-alls per group bring whole matrices to their owners and the results back, and
+                # every owner orthogonalises its share as one batch.
+                tgroups: dict[tuple, list] = {}
+                for s in owned:
+                    tgroups.setdefault((tuple(comm.full_shape(s)), tuple(s.shape)), []).append(s)
+                for (full_shape, _), slots in tgroups.items():
+                    rows, cols = full_shape
+                    transposed = rows > cols
+                    shards = [ops.muon_momentum(ar.view(s.name, grads=True), self.momentum[s.name], g["momentum"],
+                                                g["nesterov"], coef)[0] for s in slots]
+
+                    def orthogonalise(batch: torch.Tensor) -> torch.Tensor:
+                        xs = []
+                        for m in batch:                          # per-matrix Frobenius normalisation
+                            xm = ops.transpose(m) if transposed else m
+                            xs.append(ops.ns_normalize(xm, ops.sumsq(m)))
+                        out = []
+                        for c0 in range(0, len(xs), self.ns_batch):
+                            chunk = xs[c0:c0 + self.ns_batch]
+                            xb = torch.stack(chunk) if len(chunk) > 1 else chunk[0]
+                            for (a, b, c) in coeffs:
+                                xb = ops.ns_iteration(xb, a, b, c)
+                            out += list(xb) if len(chunk) > 1 else [xb]
+                        # back to the parameter's orientation and dtype
+                        return torch.stack([(ops.transpose(o) if transposed else o).to(batch.dtype) for o in out])
+
+                    res = comm.muon_exchange_group(slots, shards, orthogonalise)
+                    scale = max(1.0, (rows / cols) ** 0.5)
+                    for s, x in zip(slots, res):
+                        comm.muon_apply(ops, s, x.contiguous(), g["lr"], g["weight_decay"], scale, False)
+                owned = []
             for s in owned:
                 grad = ar.view(s.name, grads=True)
                 x, sq = ops.muon_momentum(grad, self.momentum[s.name], g["momentum"], g["nesterov"], coef)

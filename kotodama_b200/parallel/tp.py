@@ -291,6 +291,46 @@ class TensorParallelComm(LocalComm):
         n = slot.shape[d]
         return full.narrow(d, self.tp_rank * n, n).contiguous()
 
+    def muon_exchange_group(self, slots, shards, orthogonalise):
+        """Owner-computes Newton-Schulz for a group of same-shape, same-shard-dimension matrices with two
+        collectives in total: an all-to-all that brings every shard of matrix ``i`` to rank ``i % tp`` (so
+        each owner holds whole matrices and can orthogonalise them as one batch), and an all-to-all that
+        returns to every rank its own shard of every result.  ``shards``: this rank's shard of each
+        matrix, in ``slots`` order; ``orthogonalise(batch[n, rows, cols]) -> batch``.  Returns the
+        orthogonalised shards in ``slots`` order.  (The reference gathers every matrix on every rank,
+        one call per matrix, and repeats the iteration everywhere: ``muon.py:286-296``.)"""
+        W, me = self.tp_size, self.tp_rank
+        n = len(slots)
+        d = shard_dim_of(slots[0].name)
+        sr, sc = shards[0].shape
+        numel = sr * sc
+        owned_by = [[i for i in range(n) if i % W == o] for o in range(W)]
+        n_me = len(owned_by[me])
+        send = torch.cat([torch.stack([shards[i] for i in owned_by[o]]).reshape(-1) if owned_by[o]
+                          else shards[0].new_empty(0) for o in range(W)])
+        recv = send.new_empty(W * n_me * numel)
+        dist.all_to_all_single(recv, send, output_split_sizes=[n_me * numel] * W,
+                               input_split_sizes=[len(owned_by[o]) * numel for o in range(W)], group=self.tp_group)
+        back_send = send.new_empty(W * n_me * numel)
+        if n_me:
+            parts = recv.view(W, n_me, sr, sc)
+            full = (parts.permute(1, 0, 2, 3).reshape(n_me, W * sr, sc) if d == 0
+                    else parts.permute(1, 2, 0, 3).reshape(n_me, sr, W * sc)).contiguous()
+            orth = orthogonalise(full)
+            out = (orth.reshape(n_me, W, sr, sc).permute(1, 0, 2, 3) if d == 0
+                   else orth.reshape(n_me, sr, W, sc).permute(2, 0, 1, 3))
+            back_send.view(W, n_me, sr, sc).copy_(out)
+        back = send.new_empty(n * numel)
+        dist.all_to_all_single(back, back_send, output_split_sizes=[len(owned_by[o]) * numel for o in range(W)],
+                               input_split_sizes=[n_me * numel] * W, group=self.tp_group)
+        res = [None] * n
+        at = 0
+        for o in range(W):
+            for i in owned_by[o]:
+                res[i] = back[at:at + numel].view(sr, sc)
+                at += numel
+        return res
+
     def gather_momentum(self, slot, buf):
         return all_gather_along_dim(buf, shard_dim_of(slot.name), self.tp_group)
 
