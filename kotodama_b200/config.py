@@ -150,6 +150,7 @@ FLAG_TABLE: list[tuple[str, dict[str, Any]]] = [
     _f("z_loss_weight", 1e-5), _f("activation_checkpointing", flag=True),
     # AttnRes
     _f("attn_res", flag=True, help="Block Attention Residuals"),
+    _f("no_attn_res", flag=True, help="turn Block Attention Residuals off (overrides a config file that enables them)"),
     _f("attn_res_n_blocks", 7), _f("attn_res_boundaries", None, str, help="e.g. '0,3,7,12,21,25'"),
     # scale
     _f("total_tokens", 6_000_000_000), _f("total_steps", None, int),
@@ -230,6 +231,8 @@ def parse_args(argv: Optional[Sequence[str]] = None) -> argparse.Namespace:
         parser.set_defaults(**{k: v for k, v in cfg.items() if k in known})
         args = parser.parse_args(argv)
         args._config_file = args.config
+    if getattr(args, "no_attn_res", False):
+        args.attn_res = False
     return args
 
 

@@ -7,7 +7,7 @@ declare -A RUNS=(
   [native]=""
   [nccl]="--backend nccl"
   [mb8]="--micro_batch_size 8"
-  [no_attnres]="--attn_res_n_blocks 7 --model_size 3b"
+  [no_attnres]="--no_attn_res"
   [original_ns]="--muon_ns_coefficients original"
   [adamw_only]="--adamw_only"
   [fp8]="--fp8"
