@@ -232,7 +232,10 @@ def main() -> None:
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=4)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    ap.add_argument("--impl", default="native", choices=["native", "reference", "library"],
+                    help="native: this framework; reference: the unmodified reference (baseline/_ref); library: this "
+                         "framework's engine with cuBLAS GEMMs and NCCL collectives instead of its own kernels - a same-box "
+                         "yardstick for context, never the reference arm")
     ap.add_argument("--model", default="3b")
     ap.add_argument("--micro-batch", type=int, default=8)
     ap.add_argument("--seq", type=int, default=4096)
@@ -251,6 +254,9 @@ def main() -> None:
         if int(os.environ.get("RANK", 0)) == 0:
             print(json.dumps({"impl": "reference", "unavailable": r["unavailable"]}))
         return
+    if args.impl == "library":
+        os.environ["KOTODAMA_GEMM"] = "cublas"
+        args.backend = "nccl"
     rank, world, local = dist_setup(args.gpus)
     if args.mode == "serve":
         out = run_serve(args, rank, world, local)
@@ -304,6 +310,11 @@ def main() -> None:
             if r.get("flops_per_token"):
                 line["tflops_per_gpu"] = round(value / world * r["flops_per_token"] / 1e12, 1)
             line["notes"] = r["extra"]
+            if args.impl == "library":
+                line["impl"] = "library_arm"
+                line["library_arm"] = ("this framework's executor with torch.addmm/baddbmm (cuBLAS) for every GEMM and NCCL "
+                                       "for every collective; attention, routing, loss and optimizer kernels are the "
+                                       "framework's own (it has no library attention path). Context only: not the reference.")
             print(json.dumps(line))
     if world > 1:
         dist.barrier()

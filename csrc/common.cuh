@@ -11,7 +11,7 @@
 
 // Status codes written to a status word by kernels whose waits are bounded.
 enum KbStatus : int { KB_OK = 0, KB_TIMEOUT_TMA = 1, KB_TIMEOUT_MMA = 2, KB_TIMEOUT_EPI = 3, KB_TIMEOUT_PEER = 4,
-                      KB_BAD_ARG = 5 };
+                      KB_BAD_ARG = 5, KB_BAD_INDEX = 6 };   // 6: an index read from data (token id, label, cache slot) was out of range; the access was skipped
 
 // Launcher return code for "the launch itself was refused" (bad grid, shared-memory attribute, ...).
 #define KB_LAUNCH_FAILED 9

@@ -607,11 +607,16 @@ KB_API int kb_swiglu_bwd(const void* gu, const void* dact, void* dgu, long long 
 __global__ void __launch_bounds__(512)
 ce_zloss_kernel(bf16* __restrict__ logits, const long long* __restrict__ labels, float* __restrict__ row_ce,
                 float* __restrict__ row_z, const float* __restrict__ inv_count, float z_w, float scale, int V,
-                int write_grad) {
+                int write_grad, int* __restrict__ status) {
     __shared__ float scratch[2 * 32];
     const int row = blockIdx.x;
     bf16* lg = logits + (size_t)row * V;
-    const long long y = labels[row];
+    long long y = labels[row];
+    if (y >= V) {
+        // a label outside the vocabulary: recorded, and the row is treated as ignored (negative labels are the ignore index)
+        if (threadIdx.x == 0 && status) atomicMax(status, (int)KB_BAD_INDEX);
+        y = -1;
+    }
     const int nchunks = V >> 3;
     float mx = -INFINITY, se = 0.f;
     for (int c = threadIdx.x; c < nchunks; c += blockDim.x) {
@@ -668,44 +673,62 @@ ce_zloss_kernel(bf16* __restrict__ logits, const long long* __restrict__ labels,
     }
 }
 KB_API int kb_ce_zloss(void* logits, const long long* labels, float* row_ce, float* row_z, const float* inv_count,
-                       float z_w, float scale, int rows, int V, int write_grad, cudaStream_t st) {
+                       float z_w, float scale, int rows, int V, int write_grad, int* status, cudaStream_t st) {
     if (V % 8) return 5;
-    ce_zloss_kernel<<<rows, 512, 0, st>>>((bf16*)logits, labels, row_ce, row_z, inv_count, z_w, scale, V, write_grad);
+    ce_zloss_kernel<<<rows, 512, 0, st>>>((bf16*)logits, labels, row_ce, row_z, inv_count, z_w, scale, V, write_grad,
+                                          status);
     return kb_launch_status();
 }
 
 // ============================================================================ embedding
+// Token ids come from data: an id outside [0, V) is recorded in the status word (KB_BAD_INDEX) and
+// its row is written as zeros (forward) or skipped (backward) instead of being dereferenced.
 __global__ void embedding_fwd_kernel(const long long* __restrict__ ids, const bf16* __restrict__ w,
-                                     bf16* __restrict__ out, int N, int D) {
+                                     bf16* __restrict__ out, int N, int D, int V, int* __restrict__ status) {
     const int dc = D >> 3;
     const long long total = (long long)N * dc;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
          i += (long long)gridDim.x * blockDim.x) {
         const long long row = i / dc;
         const int c = (int)(i % dc);
-        st8(out + row * D + (size_t)c * 8, ld8(w + ids[row] * D + (size_t)c * 8));
+        const long long id = ids[row];
+        if (id < 0 || id >= V) {
+            if (c == 0 && status) atomicMax(status, (int)KB_BAD_INDEX);
+            *reinterpret_cast<uint4*>(out + row * D + (size_t)c * 8) = make_uint4(0, 0, 0, 0);
+            continue;
+        }
+        st8(out + row * D + (size_t)c * 8, ld8(w + id * D + (size_t)c * 8));
     }
 }
 __global__ void embedding_bwd_kernel(const long long* __restrict__ ids, const bf16* __restrict__ dout,
-                                     bf16* __restrict__ dw, int N, int D) {
+                                     bf16* __restrict__ dw, int N, int D, int V, int* __restrict__ status) {
     const int dc = D >> 1;
     const long long total = (long long)N * dc;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
          i += (long long)gridDim.x * blockDim.x) {
         const long long row = i / dc;
         const int c = (int)(i % dc);
+        const long long id = ids[row];
+        if (id < 0 || id >= V) {
+            if (c == 0 && status) atomicMax(status, (int)KB_BAD_INDEX);
+            continue;
+        }
         const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(dout + row * D + (size_t)c * 2);
-        atomicAdd(reinterpret_cast<__nv_bfloat162*>(dw + ids[row] * D + (size_t)c * 2), v);
+        atomicAdd(reinterpret_cast<__nv_bfloat162*>(dw + id * D + (size_t)c * 2), v);
     }
 }
-KB_API int kb_embedding_fwd(const long long* ids, const void* w, void* out, int N, int D, cudaStream_t st) {
-    if (D % 8) return 5;
-    embedding_fwd_kernel<<<ew_grid((long long)N * (D / 8), 256), 256, 0, st>>>(ids, (const bf16*)w, (bf16*)out, N, D);
+KB_API int kb_embedding_fwd(const long long* ids, const void* w, void* out, int N, int D, int V, int* status,
+                            cudaStream_t st) {
+    if (D % 8 || V < 1) return 5;
+    embedding_fwd_kernel<<<ew_grid((long long)N * (D / 8), 256), 256, 0, st>>>(ids, (const bf16*)w, (bf16*)out, N, D, V,
+                                                                              status);
     return kb_launch_status();
 }
-KB_API int kb_embedding_bwd(const long long* ids, const void* dout, void* dw, int N, int D, cudaStream_t st) {
-    if (D % 2) return 5;
-    embedding_bwd_kernel<<<ew_grid((long long)N * (D / 2), 256), 256, 0, st>>>(ids, (const bf16*)dout, (bf16*)dw, N, D);
+KB_API int kb_embedding_bwd(const long long* ids, const void* dout, void* dw, int N, int D, int V, int* status,
+                            cudaStream_t st) {
+    if (D % 2 || V < 1) return 5;
+    embedding_bwd_kernel<<<ew_grid((long long)N * (D / 2), 256), 256, 0, st>>>(ids, (const bf16*)dout, (bf16*)dw, N, D, V,
+                                                                              status);
     return kb_launch_status();
 }
 

@@ -12,9 +12,11 @@ typedef __nv_bfloat16 bf16;
 constexpr int PAGE = 16;
 
 // k, v: [N, n_kv*hd] rows with the given strides; slot[n] = page * PAGE + offset in page, or < 0 to skip.
+// A slot at or past `num_slots` (pages * PAGE) is recorded as KB_BAD_INDEX and skipped.
 __global__ void kv_append_kernel(const bf16* __restrict__ k, const bf16* __restrict__ v, long long k_stride,
                                  long long v_stride, bf16* __restrict__ k_pages, bf16* __restrict__ v_pages,
-                                 const long long* __restrict__ slot, int N, int row_elems, int hd) {
+                                 const long long* __restrict__ slot, int N, int row_elems, int hd, long long num_slots,
+                                 int* __restrict__ status) {
     const int chunks = row_elems >> 3;
     const int n_kv = row_elems / hd;
     const long long total = (long long)N * chunks;
@@ -23,6 +25,10 @@ __global__ void kv_append_kernel(const bf16* __restrict__ k, const bf16* __restr
         const int n = (int)(i / chunks), c = (int)(i % chunks);
         const long long s = slot[n];
         if (s < 0) continue;
+        if (s >= num_slots) {
+            if (c == 0 && status) atomicMax(status, (int)KB_BAD_INDEX);
+            continue;
+        }
         const int kvh = (c * 8) / hd, d = (c * 8) % hd;
         const size_t dst = (((size_t)(s / PAGE) * n_kv + kvh) * PAGE + (size_t)(s % PAGE)) * hd + d;
         st8(k_pages + dst, ld8(k + (size_t)n * k_stride + (size_t)c * 8));
@@ -30,13 +36,14 @@ __global__ void kv_append_kernel(const bf16* __restrict__ k, const bf16* __restr
     }
 }
 KB_API int kb_kv_append(const void* k, const void* v, long long k_stride, long long v_stride, void* k_pages,
-                        void* v_pages, const long long* slot, int N, int row_elems, int hd, cudaStream_t st) {
+                        void* v_pages, const long long* slot, int N, int row_elems, int hd, long long num_slots,
+                        int* status, cudaStream_t st) {
     if (row_elems % 8 || k_stride % 8 || v_stride % 8 || hd % 8 || row_elems % hd) return 5;
     long long blocks = ((long long)N * (row_elems / 8) + 255) / 256;
     if (blocks < 1) blocks = 1;
     if (blocks > 4096) blocks = 4096;
     kv_append_kernel<<<(int)blocks, 256, 0, st>>>((const bf16*)k, (const bf16*)v, k_stride, v_stride, (bf16*)k_pages,
-                                                  (bf16*)v_pages, slot, N, row_elems, hd);
+                                                  (bf16*)v_pages, slot, N, row_elems, hd, num_slots, status);
     return kb_launch_status();
 }
 

@@ -79,7 +79,9 @@ class CudaOps(TorchOps):
             v = int(t.item())
             if v != 0:
                 t.zero_()
-                raise KernelError(f"device {idx}: a kernel wait timed out (status {v})")
+                what = {5: "a kernel refused its arguments", 6: "an index read from data (token id, label or cache slot) "
+                        "was out of range; the access was skipped"}.get(v, "a kernel wait timed out")
+                raise KernelError(f"device {idx}: {what} (status {v})")
         if self._status:        # the decode kernels keep their own status word (no status argument)
             torch.cuda.synchronize()
             v = int(self.lib.kb_decode_status())
@@ -463,7 +465,8 @@ class CudaOps(TorchOps):
             lg = logits[: e - s]
             self.gemm_nt(h[s:e], w, out=lg)
             rc = self.lib.kb_ce_zloss(_p(lg), _p(labels[s:e]), _p(row_ce[s:e]), _p(row_z[s:e]), _p(inv),
-                                      _F(z_weight), _F(grad_scale), _I(e - s), _I(V), _I(int(need_grad)), _st())
+                                      _F(z_weight), _F(grad_scale), _I(e - s), _I(V), _I(int(need_grad)),
+                                      _p(self.status(dev)), _st())
             self._rc(rc, "kb_ce_zloss")
             if need_grad:
                 self.gemm_nn(lg, w, out=dh[s:e])
@@ -479,12 +482,13 @@ class CudaOps(TorchOps):
     def embedding_fwd(self, ids, w):
         N, D = ids.numel(), w.shape[1]
         out = torch.empty(N, D, device=w.device, dtype=w.dtype)
-        self._rc(self.lib.kb_embedding_fwd(_p(ids), _p(w), _p(out), _I(N), _I(D), _st()), "kb_embedding_fwd")
+        self._rc(self.lib.kb_embedding_fwd(_p(ids), _p(w), _p(out), _I(N), _I(D), _I(w.shape[0]),
+                                           _p(self.status(w.device)), _st()), "kb_embedding_fwd")
         return out
 
     def embedding_bwd(self, dout, ids, dw):
-        self._rc(self.lib.kb_embedding_bwd(_p(ids), _p(dout), _p(dw), _I(ids.numel()), _I(dw.shape[1]), _st()),
-                 "kb_embedding_bwd")
+        self._rc(self.lib.kb_embedding_bwd(_p(ids), _p(dout), _p(dw), _I(ids.numel()), _I(dw.shape[1]), _I(dw.shape[0]),
+                                           _p(self.status(dw.device)), _st()), "kb_embedding_bwd")
 
     # ------------------------------------------------------------------ optimizer math
     def sumsq(self, x, out: Optional[torch.Tensor] = None, accumulate: bool = False):
@@ -549,7 +553,9 @@ class CudaOps(TorchOps):
         """Copy rows ``k[n], v[n]`` (``[N, n_kv*hd]`` views) into cache slot ``slots[n]`` (page*16 + offset)."""
         N, row = k.shape
         self._rc(self.lib.kb_kv_append(_p(k), _p(v), _LL(k.stride(0)), _LL(v.stride(0)), _p(k_pages), _p(v_pages),
-                                       _p(slots), _I(N), _I(row), _I(k_pages.shape[-1]), _st()), "kb_kv_append")
+                                       _p(slots), _I(N), _I(row), _I(k_pages.shape[-1]),
+                                       _LL(k_pages.shape[0] * k_pages.shape[-2]), _p(self.status(k.device)), _st()),
+                 "kb_kv_append")
 
     def paged_decode_attention(self, q, k_pages, v_pages, page_table, ctx_lens, max_ctx, n_q, n_kv, hd, split=512):
         """``q[B, n_q*hd]`` (one new token per request) against the paged cache; returns ``[B, n_q*hd]``."""

@@ -146,6 +146,9 @@ class ServingEngine:
         self._free_slots = list(range(max_batch - 1, -1, -1))
         self._dec_states: dict[int, dict] = {}
         self.use_cuda_graphs = True          # decode steps are replayed from captured graphs on CUDA
+        # when a list: every pass appends ([request ids], fp32 logits on the host) - for tests that compare
+        # two engines by logits rather than by sampled tokens
+        self.logit_trace: Optional[list] = None
         self.prefill_batch_tokens = prefill_batch_tokens     # tokens of one packed prefill pass over several prompts; 0: one prompt per pass
         self.stats = {"prefill_tokens": 0, "decode_tokens": 0, "prefill_s": 0.0, "decode_s": 0.0, "steps": 0,
                       "prefill_passes": 0}
@@ -260,6 +263,8 @@ class ServingEngine:
         dev = self.device
         seqs = {"cu_seqlens": torch.tensor(cu, dtype=torch.int32).to(dev), "max_seqlen": max(ns)}
         logits = self._forward(ids.to(dev), pos.to(dev), slots.to(dev), None, last.to(dev), seqs=seqs)
+        if self.logit_trace is not None:
+            self.logit_trace.append(([r.rid for r in reqs], logits.float().cpu()))
         toks = sample_tokens(logits, reqs, self.ops, self.seen).tolist()
         if self.tp is not None:
             toks = self.tp.sync_tokens(toks, self.device)
@@ -383,6 +388,8 @@ class ServingEngine:
         else:
             logits = self._forward(st["ids"], st["pos"], st["slots"], decode, st["rows"])
             toks = sample_tokens(logits, reqs, self.ops, self.seen).tolist()
+        if self.logit_trace is not None:
+            self.logit_trace.append(([r.rid for r in reqs], logits[:B].float().cpu()))
         if self.tp is not None:
             toks = self.tp.sync_tokens(toks, self.device)
         for r, t in zip(reqs, toks):

@@ -111,9 +111,12 @@ def main():
         full = KotodamaModel(cfg)
         prompts = [[(7 * i + 3 * j) % cfg.vocab_size for j in range(5 + 3 * i)] for i in range(5)]
         params = SamplingParams(max_new_tokens=6, temperature=0.0)
-        ref = ServingEngine(copy.deepcopy(full), device=device, dtype=dtype, max_batch=8, max_ctx=256).generate(prompts, params)
+        ref_eng = ServingEngine(copy.deepcopy(full), device=device, dtype=dtype, max_batch=8, max_ctx=256)
+        ref_eng.logit_trace = []
+        ref = ref_eng.generate(prompts, params)
         tp = ServeTP()
         eng = ServingEngine(full, device=device, dtype=dtype, max_batch=8, max_ctx=256, tp=tp)
+        eng.logit_trace = []
         if rank == 0:
             lead = TPLeader(eng, tp)
             gen = lead.generate(prompts, params)
@@ -126,6 +129,26 @@ def main():
         result.update(ref=ref, tp=gathered[0], ranks_equal=all(g == gathered[0] for g in gathered),
                       native_calls=tp.native_calls, library_calls=tp.library_calls,
                       local_heads=eng.H, local_kv=eng.KV)
+        # by logits: while a request's token history is shared, every pass must agree within rounding;
+        # where the greedy tokens part, the unsharded margin between the two candidates must be within it
+
+        def per_request(trace):
+            out = {}
+            for rids, lg in trace:
+                for i, rid in enumerate(rids):
+                    out.setdefault(rid, []).append(lg[i])
+            return [out[k] for k in sorted(out)]
+        worst, flips_ok, compared = 0.0, True, 0
+        for rt, tt, rl, tl in zip(ref, gen, per_request(ref_eng.logit_trace), per_request(eng.logit_trace)):
+            for i in range(min(len(rl), len(tl))):
+                err = float((tl[i] - rl[i]).abs().max())
+                worst = max(worst, float((tl[i] - rl[i]).norm() / (rl[i].norm() + 1e-12)))
+                compared += 1
+                if rt[i] != tt[i]:
+                    margin = float(rl[i][rt[i]] - rl[i][tt[i]])
+                    flips_ok = flips_ok and 0 <= margin <= 2 * err + 1e-6
+                    break
+        result.update(logit_rel_err_max=worst, flips_ok=flips_ok, logits_compared=compared)
         if cuda:
             eng.ops.check_status()
             # the all-reduce kernel alone, against an exact fp32 sum of the gathered partials

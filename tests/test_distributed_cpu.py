@@ -85,6 +85,7 @@ def test_tensor_parallel_serving_matches_single_process(tmp_path):
     for r in res:
         assert r["ranks_equal"]
         assert r["tp"] == r["ref"], (r["tp"], r["ref"])
+        assert r["logit_rel_err_max"] < 1e-4 and r["logits_compared"] == 30
         assert r["local_heads"] == 2 and r["local_kv"] == 1
         assert r["library_calls"] > 0 and r["native_calls"] == 0
 

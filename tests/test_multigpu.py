@@ -65,5 +65,5 @@ def test_tensor_parallel_serving_native_allreduce(tmp_path, nproc):
         assert r["native_calls"] > 0
         assert r["allreduce_max_err"] == 0.0
         assert all(len(t) == 6 for t in r["tp"])
-    same = sum(a == b for ta, tb in zip(res[0]["tp"], res[0]["ref"]) for a, b in zip(ta, tb))
-    assert same >= 0.6 * 30, (res[0]["tp"], res[0]["ref"])     # bf16: sharded sums round differently
+    # bf16: sharded sums round differently, so tokens may part at a near-tie; the logits may not
+    assert res[0]["logit_rel_err_max"] < 4e-2 and res[0]["flips_ok"] and res[0]["logits_compared"] >= 10, res[0]
