@@ -76,9 +76,17 @@ def fp8_table(ops, args, flush) -> None:
         shapes = [tuple(map(int, args.single[:3]))]
     for (M, N, K) in shapes:
         a, b = operands(M, N, K, "nt")
+        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        # the other back end first (for the record), then the selected one
+        chosen = ops.fp8_backend
+        other = "promote" if chosen == "mx" else "mx"
+        ops.fp8_backend, ops.fp8_pow2 = other, other == "mx"
         qa, sa = ops.quant_rows(a)
         qb, sb = ops.quant_blocks(b)
-        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        t_other = time_fn(lambda: ops.gemm_fp8(qa, sa, qb, sb, 128, out=out), args.iters, flush)
+        ops.fp8_backend, ops.fp8_pow2 = chosen, chosen == "mx"
+        qa, sa = ops.quant_rows(a)
+        qb, sb = ops.quant_blocks(b)
         t_g = time_fn(lambda: ops.gemm_fp8(qa, sa, qb, sb, 128, out=out), args.iters, flush)
         t_q = time_fn(lambda: ops.quant_rows(a), args.iters, flush)
         qat, sat = ops.quant_cols_t(a)
@@ -86,7 +94,8 @@ def fp8_table(ops, args, flush) -> None:
         t_b = time_fn(lambda: ops.gemm_nt(a, b, out=out), args.iters, flush)
         t_l = time_fn(lambda: torch.matmul(a, b.t(), out=out), args.iters, flush)
         fl = 2.0 * M * N * K
-        print(json.dumps(dict(M=M, N=N, K=K, fp8_ms=round(t_g, 4), fp8_tflops=round(fl / t_g / 1e9, 1),
+        print(json.dumps(dict(M=M, N=N, K=K, backend=chosen, fp8_ms=round(t_g, 4), fp8_tflops=round(fl / t_g / 1e9, 1),
+                              **{f"{other}_ms": round(t_other, 4)},
                               quant_rows_ms=round(t_q, 4), quant_gbs=round(M * K * 3 / t_q / 1e6, 1),
                               bf16_ms=round(t_b, 4), cublas_bf16_ms=round(t_l, 4),
                               fp8_vs_bf16=round(t_b / t_g, 3), fp8_plus_quant_vs_bf16=round(t_b / (t_g + t_q), 3))))

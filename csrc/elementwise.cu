@@ -395,121 +395,193 @@ KB_API int kb_colsum(const float* part, float* out, int R, int C, cudaStream_t s
 }
 
 // ============================================================================ QK-norm + RoPE
-// One warp per (token, head).  Lane l owns elements [l*E, l*E+E) of each half, E = hd/64.
-template <int E, bool NORM>
-__global__ void qknorm_rope_fwd_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ qw,
-                                       const bf16* __restrict__ kw, const float* __restrict__ cosT,
-                                       const float* __restrict__ sinT, bf16* __restrict__ out,
-                                       float* __restrict__ rstd_o, int N, int T, int nq, int nkv, int pos_offset,
-                                       float eps, const int* __restrict__ positions) {
-    constexpr int HD = 64 * E;
+// One warp per token.  A head is covered by HD/16 lanes (lane `sub` owns elements [8*sub, 8*sub+8) of
+// each half, one 16-byte access per half), so a warp takes 32/(HD/16) heads per pass; the token's
+// cos/sin row and the norm weights stay in registers across all heads of the token.
+template <int HD, bool NORM>
+__global__ void __launch_bounds__(256)
+qknorm_rope_fwd_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ qw, const bf16* __restrict__ kw,
+                       const float* __restrict__ cosT, const float* __restrict__ sinT, bf16* __restrict__ out,
+                       float* __restrict__ rstd_o, int N, int T, int nq, int nkv, int pos_offset, float eps,
+                       const int* __restrict__ positions) {
+    constexpr int LPH = HD / 16, HPW = 32 / LPH;
     const int nh = nq + nkv;
-    const int lane = threadIdx.x & 31;
-    const long long total = (long long)N * nh;
+    const int lane = threadIdx.x & 31, sub = lane % LPH, hsel = lane / LPH, e0 = sub * 8;
     const int in_stride = (nq + 2 * nkv) * HD, out_stride = nh * HD;
-    for (long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); w < total;
-         w += (long long)gridDim.x * (blockDim.x >> 5)) {
-        const int tok = (int)(w / nh), head = (int)(w % nh);
-        const bf16* src = qkv + (size_t)tok * in_stride + head * HD;
-        float x1[E], x2[E];
+    float wq1[8], wq2[8], wk1[8], wk2[8];
+    if (NORM) {
+        unpack8(ld8(qw + e0), wq1);
+        unpack8(ld8(qw + HD / 2 + e0), wq2);
+        unpack8(ld8(kw + e0), wk1);
+        unpack8(ld8(kw + HD / 2 + e0), wk2);
+    }
+    const long long nwarps = (long long)gridDim.x * (blockDim.x >> 5);
+    for (long long tok = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); tok < N; tok += nwarps) {
+        const int pos = positions ? positions[tok] : (int)(tok % T) + pos_offset;
+        float c[8], sn[8];
+        *reinterpret_cast<float4*>(c) = *reinterpret_cast<const float4*>(cosT + (size_t)pos * HD + e0);
+        *reinterpret_cast<float4*>(c + 4) = *reinterpret_cast<const float4*>(cosT + (size_t)pos * HD + e0 + 4);
+        *reinterpret_cast<float4*>(sn) = *reinterpret_cast<const float4*>(sinT + (size_t)pos * HD + e0);
+        *reinterpret_cast<float4*>(sn + 4) = *reinterpret_cast<const float4*>(sinT + (size_t)pos * HD + e0 + 4);
+        const bf16* src = qkv + (size_t)tok * in_stride;
+        bf16* dst = out + (size_t)tok * out_stride;
+#pragma unroll 2
+        for (int h0 = 0; h0 < nh; h0 += HPW) {
+            const int head = h0 + hsel;
+            const bool ok = head < nh;
+            const bool isq = head < nq;
+            float x1[8], x2[8];
+            if (ok) {
+                unpack8(ld8(src + head * HD + e0), x1);
+                unpack8(ld8(src + head * HD + HD / 2 + e0), x2);
+            } else {
 #pragma unroll
-        for (int i = 0; i < E; ++i) {
-            x1[i] = __bfloat162float(src[lane * E + i]);
-            x2[i] = __bfloat162float(src[HD / 2 + lane * E + i]);
-        }
-        float rs = 1.f;
-        if (NORM) {
-            float ss = 0.f;
-#pragma unroll
-            for (int i = 0; i < E; ++i) ss += x1[i] * x1[i] + x2[i] * x2[i];
-            ss = warp_sum(ss);
-            rs = rsqrtf(ss / HD + eps);
-            if (lane == 0) rstd_o[w] = rs;
-            const bf16* wt = head < nq ? qw : kw;
-#pragma unroll
-            for (int i = 0; i < E; ++i) {
-                x1[i] *= rs * __bfloat162float(wt[lane * E + i]);
-                x2[i] *= rs * __bfloat162float(wt[HD / 2 + lane * E + i]);
+                for (int i = 0; i < 8; ++i) x1[i] = x2[i] = 0.f;
             }
-        } else if (lane == 0) {
-            rstd_o[w] = 1.f;
-        }
-        const int pos = positions ? positions[tok] : tok % T + pos_offset;
-        bf16* dst = out + (size_t)tok * out_stride + head * HD;
+            if (NORM) {
+                float ss = 0.f;
 #pragma unroll
-        for (int i = 0; i < E; ++i) {
-            const float c = cosT[(size_t)pos * HD + lane * E + i], s = sinT[(size_t)pos * HD + lane * E + i];
-            dst[lane * E + i] = __float2bfloat16(x1[i] * c - x2[i] * s);
-            dst[HD / 2 + lane * E + i] = __float2bfloat16(x2[i] * c + x1[i] * s);
+                for (int i = 0; i < 8; ++i) ss += x1[i] * x1[i] + x2[i] * x2[i];
+#pragma unroll
+                for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+                const float rs = rsqrtf(ss / HD + eps);
+                if (ok && sub == 0) rstd_o[tok * nh + head] = rs;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    x1[i] *= rs * (isq ? wq1[i] : wk1[i]);
+                    x2[i] *= rs * (isq ? wq2[i] : wk2[i]);
+                }
+            } else if (ok && sub == 0) {
+                rstd_o[tok * nh + head] = 1.f;
+            }
+            float o1[8], o2[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                o1[i] = x1[i] * c[i] - x2[i] * sn[i];
+                o2[i] = x2[i] * c[i] + x1[i] * sn[i];
+            }
+            if (ok) {
+                st8(dst + head * HD + e0, pack8(o1));
+                st8(dst + head * HD + HD / 2 + e0, pack8(o2));
+            }
         }
     }
 }
 
 // Backward; per-warp weight-gradient partials go to dw_part[warp_global][2][HD] (q then k).
-template <int E, bool NORM>
-__global__ void qknorm_rope_bwd_kernel(const bf16* __restrict__ dqk, const bf16* __restrict__ qkv,
-                                       const bf16* __restrict__ qw, const bf16* __restrict__ kw,
-                                       const float* __restrict__ cosT, const float* __restrict__ sinT,
-                                       const float* __restrict__ rstd_i, bf16* __restrict__ dqkv,
-                                       float* __restrict__ dw_part, int N, int T, int nq, int nkv, int pos_offset) {
-    constexpr int HD = 64 * E;
+template <int HD, bool NORM>
+__global__ void __launch_bounds__(256, 2)
+qknorm_rope_bwd_kernel(const bf16* __restrict__ dqk, const bf16* __restrict__ qkv, const bf16* __restrict__ qw,
+                       const bf16* __restrict__ kw, const float* __restrict__ cosT, const float* __restrict__ sinT,
+                       const float* __restrict__ rstd_i, bf16* __restrict__ dqkv, float* __restrict__ dw_part, int N,
+                       int T, int nq, int nkv, int pos_offset) {
+    constexpr int LPH = HD / 16, HPW = 32 / LPH;
     const int nh = nq + nkv;
-    const int lane = threadIdx.x & 31;
-    const long long total = (long long)N * nh;
+    const int lane = threadIdx.x & 31, sub = lane % LPH, hsel = lane / LPH, e0 = sub * 8;
     const int full_stride = (nq + 2 * nkv) * HD, qk_stride = nh * HD;
-    float aq1[E], aq2[E], ak1[E], ak2[E];
+    float wq1[8], wq2[8], wk1[8], wk2[8];
+    float aq1[8], aq2[8], ak1[8], ak2[8];
 #pragma unroll
-    for (int i = 0; i < E; ++i) aq1[i] = aq2[i] = ak1[i] = ak2[i] = 0.f;
+    for (int i = 0; i < 8; ++i) aq1[i] = aq2[i] = ak1[i] = ak2[i] = 0.f;
+    if (NORM) {
+        unpack8(ld8(qw + e0), wq1);
+        unpack8(ld8(qw + HD / 2 + e0), wq2);
+        unpack8(ld8(kw + e0), wk1);
+        unpack8(ld8(kw + HD / 2 + e0), wk2);
+    }
     const long long wid = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    for (long long w = wid; w < total; w += (long long)gridDim.x * (blockDim.x >> 5)) {
-        const int tok = (int)(w / nh), head = (int)(w % nh);
-        const bf16* g = dqk + (size_t)tok * qk_stride + head * HD;
-        const int pos = tok % T + pos_offset;
-        float d1[E], d2[E];
+    const long long nwarps = (long long)gridDim.x * (blockDim.x >> 5);
+    for (long long tok = wid; tok < N; tok += nwarps) {
+        const int pos = (int)(tok % T) + pos_offset;
+        float c[8], sn[8];
+        *reinterpret_cast<float4*>(c) = *reinterpret_cast<const float4*>(cosT + (size_t)pos * HD + e0);
+        *reinterpret_cast<float4*>(c + 4) = *reinterpret_cast<const float4*>(cosT + (size_t)pos * HD + e0 + 4);
+        *reinterpret_cast<float4*>(sn) = *reinterpret_cast<const float4*>(sinT + (size_t)pos * HD + e0);
+        *reinterpret_cast<float4*>(sn + 4) = *reinterpret_cast<const float4*>(sinT + (size_t)pos * HD + e0 + 4);
+        const bf16* gsrc = dqk + (size_t)tok * qk_stride;
+        const bf16* xsrc = qkv + (size_t)tok * full_stride;
+        bf16* dst = dqkv + (size_t)tok * full_stride;
+#pragma unroll 2
+        for (int h0 = 0; h0 < nh; h0 += HPW) {
+            const int head = h0 + hsel;
+            const bool ok = head < nh;
+            const bool isq = head < nq;
+            float d1[8], d2[8];
+            {
+                float g1[8], g2[8];
+                if (ok) {
+                    unpack8(ld8(gsrc + head * HD + e0), g1);
+                    unpack8(ld8(gsrc + head * HD + HD / 2 + e0), g2);
+                } else {
 #pragma unroll
-        for (int i = 0; i < E; ++i) {
-            const float c = cosT[(size_t)pos * HD + lane * E + i], s = sinT[(size_t)pos * HD + lane * E + i];
-            const float g1 = __bfloat162float(g[lane * E + i]), g2 = __bfloat162float(g[HD / 2 + lane * E + i]);
-            d1[i] = g1 * c + g2 * s;
-            d2[i] = g2 * c - g1 * s;
-        }
-        bf16* dst = dqkv + (size_t)tok * full_stride + head * HD;
-        if (NORM) {
-            const bf16* src = qkv + (size_t)tok * full_stride + head * HD;
-            const bf16* wt = head < nq ? qw : kw;
-            const float rs = rstd_i[w];
-            float xh1[E], xh2[E], m = 0.f;
+                    for (int i = 0; i < 8; ++i) g1[i] = g2[i] = 0.f;
+                }
 #pragma unroll
-            for (int i = 0; i < E; ++i) {
-                xh1[i] = __bfloat162float(src[lane * E + i]) * rs;
-                xh2[i] = __bfloat162float(src[HD / 2 + lane * E + i]) * rs;
-                if (head < nq) { aq1[i] += d1[i] * xh1[i]; aq2[i] += d2[i] * xh2[i]; }
-                else { ak1[i] += d1[i] * xh1[i]; ak2[i] += d2[i] * xh2[i]; }
-                d1[i] *= __bfloat162float(wt[lane * E + i]);
-                d2[i] *= __bfloat162float(wt[HD / 2 + lane * E + i]);
-                m += d1[i] * xh1[i] + d2[i] * xh2[i];
+                for (int i = 0; i < 8; ++i) {
+                    d1[i] = g1[i] * c[i] + g2[i] * sn[i];
+                    d2[i] = g2[i] * c[i] - g1[i] * sn[i];
+                }
             }
-            m = warp_sum(m) / HD;
+            if (NORM) {
+                float xh1[8], xh2[8];
+                float rs = 0.f;
+                if (ok) {
+                    unpack8(ld8(xsrc + head * HD + e0), xh1);
+                    unpack8(ld8(xsrc + head * HD + HD / 2 + e0), xh2);
+                    rs = rstd_i[tok * nh + head];
+                } else {
 #pragma unroll
-            for (int i = 0; i < E; ++i) {
-                d1[i] = rs * (d1[i] - xh1[i] * m);
-                d2[i] = rs * (d2[i] - xh2[i] * m);
+                    for (int i = 0; i < 8; ++i) xh1[i] = xh2[i] = 0.f;
+                }
+                const float fq = isq ? 1.f : 0.f, fk = 1.f - fq;       // rows past the last head carry zeros
+                float m = 0.f;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    xh1[i] *= rs;
+                    xh2[i] *= rs;
+                    const float t1 = d1[i] * xh1[i], t2 = d2[i] * xh2[i];
+                    aq1[i] += fq * t1; aq2[i] += fq * t2;
+                    ak1[i] += fk * t1; ak2[i] += fk * t2;
+                    d1[i] *= isq ? wq1[i] : wk1[i];
+                    d2[i] *= isq ? wq2[i] : wk2[i];
+                    m += d1[i] * xh1[i] + d2[i] * xh2[i];
+                }
+#pragma unroll
+                for (int o = LPH / 2; o > 0; o >>= 1) m += __shfl_xor_sync(0xffffffffu, m, o);
+                m *= 1.f / HD;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    d1[i] = rs * (d1[i] - xh1[i] * m);
+                    d2[i] = rs * (d2[i] - xh2[i] * m);
+                }
             }
-        }
-#pragma unroll
-        for (int i = 0; i < E; ++i) {
-            dst[lane * E + i] = __float2bfloat16(d1[i]);
-            dst[HD / 2 + lane * E + i] = __float2bfloat16(d2[i]);
+            if (ok) {
+                st8(dst + head * HD + e0, pack8(d1));
+                st8(dst + head * HD + HD / 2 + e0, pack8(d2));
+            }
         }
     }
     if (NORM) {
-        float* p = dw_part + (size_t)wid * 2 * HD;
+        // sum the head slots of the warp, then the lanes of slot 0 write this warp's partial row
 #pragma unroll
-        for (int i = 0; i < E; ++i) {
-            p[lane * E + i] = aq1[i];
-            p[HD / 2 + lane * E + i] = aq2[i];
-            p[HD + lane * E + i] = ak1[i];
-            p[HD + HD / 2 + lane * E + i] = ak2[i];
+        for (int i = 0; i < 8; ++i) {
+#pragma unroll
+            for (int o = LPH; o < 32; o <<= 1) {
+                aq1[i] += __shfl_xor_sync(0xffffffffu, aq1[i], o);
+                aq2[i] += __shfl_xor_sync(0xffffffffu, aq2[i], o);
+                ak1[i] += __shfl_xor_sync(0xffffffffu, ak1[i], o);
+                ak2[i] += __shfl_xor_sync(0xffffffffu, ak2[i], o);
+            }
+        }
+        if (hsel == 0) {
+            float* p = dw_part + (size_t)wid * 2 * HD;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                p[e0 + i] = aq1[i];
+                p[HD / 2 + e0 + i] = aq2[i];
+                p[HD + e0 + i] = ak1[i];
+                p[HD + HD / 2 + e0 + i] = ak2[i];
+            }
         }
     }
 }
@@ -519,15 +591,15 @@ KB_API int kb_qknorm_grid_warps() { return kb_num_sms() * 8 * 8; }
 KB_API int kb_qknorm_rope_fwd(const void* qkv, const void* qw, const void* kw, const float* cosT, const float* sinT,
                               void* out, float* rstd, int N, int T, int nq, int nkv, int hd, int pos_offset,
                               float eps, const int* positions, cudaStream_t st) {
-    const long long total = (long long)N * (nq + nkv);
-    long long blocks = (total + 7) / 8;
-    if (blocks > kb_num_sms() * 16) blocks = kb_num_sms() * 16;
+    long long blocks = ((long long)N + 7) / 8;                  // one warp per token
+    if (blocks > kb_num_sms() * 8) blocks = kb_num_sms() * 8;
+    if (blocks < 1) blocks = 1;
     const bool norm = qw != nullptr;
 #define QK_FWD(E, NORM) qknorm_rope_fwd_kernel<E, NORM><<<(int)blocks, 256, 0, st>>>( \
         (const bf16*)qkv, (const bf16*)qw, (const bf16*)kw, cosT, sinT, (bf16*)out, rstd, N, T, nq, nkv, pos_offset, eps, \
         positions)
-    if (hd == 128) { if (norm) QK_FWD(2, true); else QK_FWD(2, false); }
-    else if (hd == 64) { if (norm) QK_FWD(1, true); else QK_FWD(1, false); }
+    if (hd == 128) { if (norm) QK_FWD(128, true); else QK_FWD(128, false); }
+    else if (hd == 64) { if (norm) QK_FWD(64, true); else QK_FWD(64, false); }
     else return 5;
     return kb_launch_status();
 }
@@ -540,8 +612,8 @@ KB_API int kb_qknorm_rope_bwd(const void* dqk, const void* qkv, const void* qw, 
 #define QK_BWD(E, NORM) qknorm_rope_bwd_kernel<E, NORM><<<blocks, 256, 0, st>>>( \
         (const bf16*)dqk, (const bf16*)qkv, (const bf16*)qw, (const bf16*)kw, cosT, sinT, rstd, (bf16*)dqkv, dw_part, \
         N, T, nq, nkv, pos_offset)
-    if (hd == 128) { if (norm) QK_BWD(2, true); else QK_BWD(2, false); }
-    else if (hd == 64) { if (norm) QK_BWD(1, true); else QK_BWD(1, false); }
+    if (hd == 128) { if (norm) QK_BWD(128, true); else QK_BWD(128, false); }
+    else if (hd == 64) { if (norm) QK_BWD(64, true); else QK_BWD(64, false); }
     else return 5;
     return kb_launch_status();
 }

@@ -1,4 +1,5 @@
-// Quantisers for the block-scaled fp8 path (e4m3, scale = amax / 448 per tile, fp32 scales).
+// Quantisers for the block-scaled fp8 path (e4m3, fp32 scales; scale = amax / 448 per tile, or the
+// next power of two above it in `pow2` mode, which the hardware block-scaled GEMM requires).
 //
 //   kb_quant_rows     x [M,K] bf16 -> q [M,K],  s[K/128][M]      1x128 tiles along K (activations; the
 //                                                                 scale array is stored K-block-major so
@@ -17,36 +18,78 @@ namespace {
 
 constexpr float FP8_MAX = 448.f;
 
+// Scale of a tile: amax / 448, or with `pow2` the next power of two at or above it (an exact
+// 8-bit exponent, which the hardware block-scaled MMA takes as the scale factor; values then use
+// at least half of the e4m3 range instead of all of it).
+__device__ __forceinline__ float tile_scale(float amax, int pow2) {
+    float s = fmaxf(amax, 1e-12f) / FP8_MAX;
+    if (pow2) {
+        uint32_t b = __float_as_uint(s);
+        if (b & 0x007FFFFFu) b = (b & 0x7F800000u) + 0x00800000u;
+        s = __uint_as_float(b);
+    }
+    return s;
+}
+
 __device__ __forceinline__ uint32_t pack4_e4m3(float a, float b, float c, float d) {
     const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
     const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
     return lo | (hi << 16);
 }
 
-// one warp per (row, K block): lane l holds elements [4l, 4l+4)
+__device__ __forceinline__ uint2 pack8_e4m3(const float* v, float inv) {
+    return make_uint2(pack4_e4m3(v[0] * inv, v[1] * inv, v[2] * inv, v[3] * inv),
+                      pack4_e4m3(v[4] * inv, v[5] * inv, v[6] * inv, v[7] * inv));
+}
+
+// Sixteen lanes per (row, K block): a lane holds 8 consecutive elements (one 16-byte load, one 8-byte
+// store), so a warp covers two K blocks per step; U steps are in flight per thread.
+template <int U>
 __global__ void __launch_bounds__(256)
 quant_rows_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, uint8_t* __restrict__ q, long long ldq,
-                  float* __restrict__ s, int M, int kblocks) {
-    const int lane = threadIdx.x & 31;
-    const long long warp_global = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+                  float* __restrict__ s, int M, int kblocks, int pow2) {
+    const int sub = threadIdx.x & 15;
+    const long long half_global = ((long long)blockIdx.x * 256 + threadIdx.x) >> 4;     // which 16-lane group
+    const long long groups = (long long)gridDim.x * 16;
     const long long total = (long long)M * kblocks;
-    for (long long w = warp_global; w < total; w += (long long)gridDim.x * 8) {
-        const int row = (int)(w / kblocks), kb = (int)(w % kblocks);
-        const uint2 raw = *reinterpret_cast<const uint2*>(x + row * ldx + kb * 128 + lane * 4);
-        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
-        const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
-        float amax = fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(b.x), fabsf(b.y)));
-        amax = warp_max(amax);
-        const float scale = fmaxf(amax, 1e-12f) / FP8_MAX, inv = 1.f / scale;
-        *reinterpret_cast<uint32_t*>(q + row * ldq + kb * 128 + lane * 4) = pack4_e4m3(a.x * inv, a.y * inv, b.x * inv, b.y * inv);
-        if (lane == 0) s[(long long)kb * M + row] = scale;
+    for (long long w0 = half_global; (w0 & ~1LL) < total; w0 += groups * U) {      // both groups of a warp iterate together (shuffles)
+        uint4 raw[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const long long w = w0 + (long long)u * groups;
+            if (w < total) {
+                const long long row = w / kblocks;
+                const int kb = (int)(w - row * kblocks);
+                raw[u] = *reinterpret_cast<const uint4*>(x + row * ldx + kb * 128 + sub * 8);
+            } else {
+                raw[u] = make_uint4(0, 0, 0, 0);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const long long w = w0 + (long long)u * groups;
+            float v[8];
+            unpack8(*reinterpret_cast<const bf16x8*>(&raw[u]), v);
+            float amax = 0.f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+            if (w < total) {
+                const long long row = w / kblocks;
+                const int kb = (int)(w - row * kblocks);
+                const float scale = tile_scale(amax, pow2), inv = 1.f / scale;
+                *reinterpret_cast<uint2*>(q + row * ldq + kb * 128 + sub * 8) = pack8_e4m3(v, inv);
+                if (sub == 0) s[(long long)kb * M + row] = scale;
+            }
+        }
     }
 }
 
 // one CTA (256 threads) per 128x128 block; thread t: row t/2, columns (t%2)*64 .. +64
 __global__ void __launch_bounds__(256)
 quant_blocks_kernel(const __nv_bfloat16* __restrict__ w, long long ldw, uint8_t* __restrict__ q, float* __restrict__ s,
-                    uint8_t* __restrict__ qt, float* __restrict__ st, int N, int K) {
+                    uint8_t* __restrict__ qt, float* __restrict__ st, int N, int K, int pow2) {
     __shared__ float red[8];
     __shared__ __align__(16) uint8_t tile[128][128 + 16];
     const int nb = blockIdx.y, kb = blockIdx.x;
@@ -74,7 +117,7 @@ quant_blocks_kernel(const __nv_bfloat16* __restrict__ w, long long ldw, uint8_t*
     amax = red[0];
 #pragma unroll
     for (int i = 1; i < 8; ++i) amax = fmaxf(amax, red[i]);
-    const float scale = fmaxf(amax, 1e-12f) / FP8_MAX, inv = 1.f / scale;
+    const float scale = tile_scale(amax, pow2), inv = 1.f / scale;
     if (threadIdx.x == 0) {
         s[(long long)kb * gridDim.y + nb] = scale;
         if (st) st[(long long)nb * gridDim.x + kb] = scale;
@@ -109,7 +152,7 @@ quant_blocks_kernel(const __nv_bfloat16* __restrict__ w, long long ldw, uint8_t*
 // one CTA (256 threads) per 128 (rows of x, the M / token dim) x 128 (columns of x) tile.
 __global__ void __launch_bounds__(256)
 quant_cols_t_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, uint8_t* __restrict__ qt, float* __restrict__ s,
-                    int M, int N) {
+                    int M, int N, int pow2) {
     __shared__ __nv_bfloat16 tile[128][128 + 8];
     __shared__ float cmax[2][128];
     const int mb = blockIdx.x, nb = blockIdx.y;
@@ -143,7 +186,7 @@ quant_cols_t_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, uint8_t*
     {
         const int c = threadIdx.x >> 1, m0 = (threadIdx.x & 1) * 64;
         const int col = nb * 128 + c;
-        const float scale = fmaxf(fmaxf(cmax[0][c], cmax[1][c]), 1e-12f) / FP8_MAX, inv = 1.f / scale;
+        const float scale = tile_scale(fmaxf(cmax[0][c], cmax[1][c]), pow2), inv = 1.f / scale;
         if (col < N) {
             if (m0 == 0) s[(long long)mb * N + col] = scale;
 #pragma unroll
@@ -164,25 +207,26 @@ quant_cols_t_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, uint8_t*
 
 }  // namespace
 
-KB_API int kb_quant_rows(const void* x, long long ldx, void* q, long long ldq, float* s, int M, int K,
+KB_API int kb_quant_rows(const void* x, long long ldx, void* q, long long ldq, float* s, int M, int K, int pow2,
                          cudaStream_t st) {
-    if (M <= 0 || K <= 0 || (K & 127) || (ldx & 3) || (ldq & 3)) return 5;
-    const long long warps = (long long)M * (K / 128);
-    long long blocks = (warps + 7) / 8;
-    if (blocks > 148 * 16) blocks = 148 * 16;
-    quant_rows_kernel<<<(int)blocks, 256, 0, st>>>((const __nv_bfloat16*)x, ldx, (uint8_t*)q, ldq, s, M, K / 128);
+    if (M <= 0 || K <= 0 || (K & 127) || (ldx & 7) || (ldq & 7) || ((uintptr_t)x & 15) || ((uintptr_t)q & 7)) return 5;
+    const long long groups = (long long)M * (K / 128);
+    long long blocks = (groups + 16 * 4 - 1) / (16 * 4);          // 16 groups per block, 4 steps each
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    if (blocks < 1) blocks = 1;
+    quant_rows_kernel<4><<<(int)blocks, 256, 0, st>>>((const __nv_bfloat16*)x, ldx, (uint8_t*)q, ldq, s, M, K / 128, pow2);
     return kb_launch_status();
 }
 KB_API int kb_quant_blocks(const void* w, long long ldw, void* q, float* s, void* qt, float* st_, int N, int K,
-                           cudaStream_t st) {
+                           int pow2, cudaStream_t st) {
     if (N <= 0 || K <= 0 || (K & 127) || (N & 15) || (ldw & 7)) return 5;
     dim3 grid(K / 128, (N + 127) / 128);
-    quant_blocks_kernel<<<grid, 256, 0, st>>>((const __nv_bfloat16*)w, ldw, (uint8_t*)q, s, (uint8_t*)qt, st_, N, K);
+    quant_blocks_kernel<<<grid, 256, 0, st>>>((const __nv_bfloat16*)w, ldw, (uint8_t*)q, s, (uint8_t*)qt, st_, N, K, pow2);
     return kb_launch_status();
 }
-KB_API int kb_quant_cols_t(const void* x, long long ldx, void* qt, float* s, int M, int N, cudaStream_t st) {
+KB_API int kb_quant_cols_t(const void* x, long long ldx, void* qt, float* s, int M, int N, int pow2, cudaStream_t st) {
     if (M <= 0 || N <= 0 || (M & 127) || (N & 7) || (ldx & 7)) return 5;
     dim3 grid(M / 128, (N + 127) / 128);
-    quant_cols_t_kernel<<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, ldx, (uint8_t*)qt, s, M, N);
+    quant_cols_t_kernel<<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, ldx, (uint8_t*)qt, s, M, N, pow2);
     return kb_launch_status();
 }

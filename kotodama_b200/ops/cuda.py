@@ -54,6 +54,11 @@ class CudaOps(TorchOps):
         self._splitk_ws: dict = {}
         self.attention_library_calls = 0   # stays 0: attention runs on the native kernels in both directions
         self.gemm_2cta = os.environ.get("KOTODAMA_GEMM_2CTA", "1") == "1"   # CTA-pair kernel for large products
+        # fp8 products: "mx" = hardware block-scaled MMA (power-of-two scales, accumulation stays in tensor
+        # memory); "promote" = fp32 scales applied per K block in registers
+        self.fp8_backend = os.environ.get("KOTODAMA_FP8", "mx")
+        self.fp8_pow2 = self.fp8_backend == "mx"
+        self.fp8_pair = int(os.environ.get("KOTODAMA_FP8_PAIR", "0"))       # mx kernel: 1 = SM-pair tiles, 0 = one CTA per tile (faster, default)
         for name in ("kb_route_bwd_grid", "kb_qknorm_grid_warps", "kb_route_pipe_grid", "kb_route_blocked_ok",
                      "kb_route_blocked_grid"):
             getattr(self.lib, name).restype = _I
@@ -184,7 +189,7 @@ class CudaOps(TorchOps):
         x = x.contiguous()
         q = torch.empty(M, K, device=x.device, dtype=torch.float8_e4m3fn)
         s = torch.empty(K // 128, M, device=x.device, dtype=torch.float32)
-        self._call("kb_quant_rows", _p(x), _LL(K), _p(q), _LL(K), _p(s), _I(M), _I(K), _st())
+        self._call("kb_quant_rows", _p(x), _LL(K), _p(q), _LL(K), _p(s), _I(M), _I(K), _I(int(self.fp8_pow2)), _st())
         return q, s
 
     def quant_blocks(self, w, transposed=False):
@@ -195,7 +200,7 @@ class CudaOps(TorchOps):
         s = torch.empty(K // 128, N // 128, device=dev, dtype=torch.float32)
         qt = torch.empty(K, N, device=dev, dtype=torch.float8_e4m3fn) if transposed else None
         st = torch.empty(N // 128, K // 128, device=dev, dtype=torch.float32) if transposed else None
-        self._call("kb_quant_blocks", _p(w), _LL(K), _p(q), _p(s), _p(qt), _p(st), _I(N), _I(K), _st())
+        self._call("kb_quant_blocks", _p(w), _LL(K), _p(q), _p(s), _p(qt), _p(st), _I(N), _I(K), _I(int(self.fp8_pow2)), _st())
         return (q, s, qt, st) if transposed else (q, s)
 
     def quant_cols_t(self, x):
@@ -203,7 +208,7 @@ class CudaOps(TorchOps):
         x = x.contiguous()
         qt = torch.empty(N, M, device=x.device, dtype=torch.float8_e4m3fn)
         s = torch.empty(M // 128, N, device=x.device, dtype=torch.float32)
-        self._call("kb_quant_cols_t", _p(x), _LL(N), _p(qt), _p(s), _I(M), _I(N), _st())
+        self._call("kb_quant_cols_t", _p(x), _LL(N), _p(qt), _p(s), _I(M), _I(N), _I(int(self.fp8_pow2)), _st())
         return qt, s
 
     def gemm_fp8(self, qa, sa, qb, sb, b_gran, out=None, accumulate=False, out_dtype=torch.bfloat16, residual=None):
@@ -213,9 +218,9 @@ class CudaOps(TorchOps):
             out = torch.empty(M, N, device=qa.device, dtype=out_dtype)
         cin = residual if residual is not None else (out if accumulate else None)
         otype = {torch.bfloat16: 1, torch.float32: 2}[out.dtype]
-        self._call("kb_gemm_fp8", _p(qa), _p(qb), _p(sa), _p(sb), _p(out), _p(cin), _I(M), _I(N), _I(K), _LL(K), _LL(K),
+        self._call("kb_gemm_mxfp8" if self.fp8_backend == "mx" else "kb_gemm_fp8", _p(qa), _p(qb), _p(sa), _p(sb), _p(out), _p(cin), _I(M), _I(N), _I(K), _LL(K), _LL(K),
                    _LL(out.stride(0)), _I(b_gran), _I(sb.shape[1]), _I(otype), _F(1.0), _F(1.0 if cin is not None else 0.0),
-                   _p(self.status(qa.device)), _I(0), _st())
+                   _p(self.status(qa.device)), _I(self.fp8_pair if self.fp8_backend == "mx" else 0), _st())
         return out
 
     def gemm_nt(self, a, b, out=None, residual=None, accumulate=False):

@@ -54,11 +54,17 @@ class TorchOps:
     name = "torch"
 
     # ------------------------------------------------------------------ block-scaled fp8
+    fp8_pow2 = False      # scales rounded up to powers of two (what the hardware block-scaled GEMM takes)
+
+    def _scale(self, amax: torch.Tensor) -> torch.Tensor:
+        s = amax.clamp_min(1e-12) / FP8_MAX
+        return torch.exp2(torch.ceil(torch.log2(s.double()))).float() if self.fp8_pow2 else s
+
     def quant_rows(self, x: torch.Tensor):
         """``x[M,K]`` -> e4m3 ``q[M,K]`` and scales ``s[K/128, M]`` (one per row and 128 columns)."""
         M, K = x.shape
         xb = x.float().view(M, K // 128, 128)
-        s = xb.abs().amax(-1).clamp_min(1e-12) / FP8_MAX
+        s = self._scale(xb.abs().amax(-1))
         q = _to_e4m3(xb / s[..., None]).view(M, K)
         return q, s.t().contiguous()
 
@@ -67,7 +73,7 @@ class TorchOps:
         also ``qt[K,N]`` and ``st[N/128, K/128]``."""
         N, K = w.shape
         wb = w.float().view(N // 128, 128, K // 128, 128)
-        s = wb.abs().amax((1, 3)).clamp_min(1e-12) / FP8_MAX            # [N/128, K/128]
+        s = self._scale(wb.abs().amax((1, 3)))                          # [N/128, K/128]
         q = _to_e4m3(wb / s[:, None, :, None]).view(N, K)
         if not transposed:
             return q, s.t().contiguous()
@@ -77,7 +83,7 @@ class TorchOps:
         """``x[M,N]`` -> e4m3 ``qt[N,M]`` and scales ``s[M/128, N]`` (one per column and 128 rows)."""
         M, N = x.shape
         xb = x.float().view(M // 128, 128, N)
-        s = xb.abs().amax(1).clamp_min(1e-12) / FP8_MAX                 # [M/128, N]
+        s = self._scale(xb.abs().amax(1))                               # [M/128, N]
         q = _to_e4m3(xb / s[:, None, :]).view(M, N)
         return q.t().contiguous(), s.contiguous()
 

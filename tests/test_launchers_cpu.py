@@ -67,6 +67,6 @@ def test_arrival_counts(lib):
 
 
 def test_quantisers_refuse_ragged_shapes(lib):
-    assert lib.kb_quant_rows(VP(PTR), LL(200), VP(PTR), LL(200), VP(PTR), I(4), I(200), VP(None)) == 5      # K % 128
-    assert lib.kb_quant_blocks(VP(PTR), LL(256), VP(PTR), VP(PTR), VP(None), VP(None), I(100), I(256), VP(None)) == 5
-    assert lib.kb_quant_cols_t(VP(PTR), LL(256), VP(PTR), VP(PTR), I(100), I(256), VP(None)) == 5           # M % 128
+    assert lib.kb_quant_rows(VP(PTR), LL(200), VP(PTR), LL(200), VP(PTR), I(4), I(200), I(0), VP(None)) == 5      # K % 128
+    assert lib.kb_quant_blocks(VP(PTR), LL(256), VP(PTR), VP(PTR), VP(None), VP(None), I(100), I(256), I(0), VP(None)) == 5
+    assert lib.kb_quant_cols_t(VP(PTR), LL(256), VP(PTR), VP(PTR), I(100), I(256), I(0), VP(None)) == 5           # M % 128

@@ -378,7 +378,19 @@ def _fp8_inputs(M, N, K, seed=0):
     return x, w
 
 
-def test_fp8_quantisers_match_reference(ops):
+@pytest.fixture(params=["mx", "mx_pair", "promote"])
+def fp8_backend(ops, request):
+    """The fp8 GEMM back ends: the hardware block-scaled MMA (power-of-two scales) as one CTA per tile
+    and as SM pairs, and the kernel that applies fp32 scales per K block in registers."""
+    old = (ops.fp8_backend, ops.fp8_pow2, ops.fp8_pair, TORCH_OPS.fp8_pow2)
+    mx = request.param.startswith("mx")
+    ops.fp8_backend, ops.fp8_pow2, ops.fp8_pair = ("mx" if mx else "promote"), mx, int(request.param == "mx_pair")
+    TORCH_OPS.fp8_pow2 = mx
+    yield request.param
+    ops.fp8_backend, ops.fp8_pow2, ops.fp8_pair, TORCH_OPS.fp8_pow2 = old
+
+
+def test_fp8_quantisers_match_reference(ops, fp8_backend):
     x, w = _fp8_inputs(256, 384, 512)
     q, s = ops.quant_rows(x)
     qr, sr = TORCH_OPS.quant_rows(x)
@@ -393,9 +405,10 @@ def test_fp8_quantisers_match_reference(ops):
     ops.check_status()
 
 
-@pytest.mark.parametrize("M,N,K", [(256, 384, 512), (1024, 5120, 3072), (384, 128, 128)])
-def test_fp8_gemm_matches_dequantised_fp32(ops, M, N, K):
-    """The kernel's promotion (per-K-block scale * partial sum, fp32) against the same sum in PyTorch fp32."""
+@pytest.mark.parametrize("M,N,K", [(256, 384, 512), (1024, 5120, 3072), (384, 128, 128), (200, 640, 1024)])
+def test_fp8_gemm_matches_dequantised_fp32(ops, fp8_backend, M, N, K):
+    """The kernel's block scaling (in the tensor core, or per-K-block scale * partial sum in registers)
+    against the same sum in PyTorch fp32, and the power-of-two recipe's error against the exact product."""
     x, w = _fp8_inputs(M, N, K, seed=1)
     qa, sa = ops.quant_rows(x)
     qb, sb = ops.quant_blocks(w)
@@ -416,7 +429,7 @@ def test_fp8_gemm_matches_dequantised_fp32(ops, M, N, K):
     ops.check_status()
 
 
-def test_fp8_weight_paths_in_gemm_ops(ops):
+def test_fp8_weight_paths_in_gemm_ops(ops, fp8_backend):
     from kotodama_b200.ops.reference import Fp8Weight
     x, w = _fp8_inputs(512, 768, 1024, seed=2)
     W8 = Fp8Weight(w)
