@@ -8,7 +8,8 @@ attention heads), and the two row-parallel projections of each layer are all-red
   memory, so decode steps that contain it can be captured in a CUDA graph and replayed; activations
   larger than the receive slots (long prefills) and the CPU path use the library all-reduce.
 * ranks stay in lock-step by construction: rank 0 owns the request queue, ``TPLeader.step``
-  broadcasts the requests admitted since the last step and then every rank executes the same
+  broadcasts a fixed-size header tensor (and, only when something was admitted or cancelled since
+  the last step, a byte tensor describing it) and then every rank executes the same
   ``engine.step()``; sampling is a function of the all-reduced (bitwise identical) logits and of
   per-request seeds, so all ranks pick the same tokens.  ``run_follower`` is the loop of ranks > 0.
 
@@ -17,6 +18,8 @@ The reference serves one request at a time on one GPU (``serve.py:322-391``).
 from __future__ import annotations
 
 import ctypes
+import dataclasses
+import json
 from typing import Any, Optional
 
 import torch
@@ -101,13 +104,62 @@ class ServeTP:
 
 
 # ---------------------------------------------------------------------------- lock-step driving
+class _Control:
+    """Rank 0 -> followers, once per step: a fixed-size header tensor ``[stop, body bytes, step,
+    0]`` on the group's device, followed - only when requests were admitted or cancelled since
+    the last step - by a byte tensor with their JSON.  A decode step without admissions costs one
+    32-byte broadcast; nothing is pickled."""
+
+    def __init__(self, tp: ServeTP, device: torch.device) -> None:
+        self.group = tp.group
+        self.src = dist.get_global_rank(tp.group, 0)
+        # NCCL moves device tensors, gloo host tensors
+        self.device = device if dist.get_backend(tp.group) == "nccl" else torch.device("cpu")
+        self.step_no = 0
+        self.header_bytes = 0
+        self.body_bytes = 0
+
+    def send(self, stop: bool, new: list, cancel: list) -> None:
+        body = b""
+        if new or cancel:
+            body = json.dumps({"new": [[p, dataclasses.asdict(sp) if sp is not None else None] for p, sp in new],
+                               "cancel": cancel}).encode()
+        self.step_no += 1
+        hdr = torch.tensor([int(stop), len(body), self.step_no, 0], dtype=torch.int64).to(self.device)
+        dist.broadcast(hdr, src=self.src, group=self.group)
+        self.header_bytes += 32
+        if body:
+            t = torch.frombuffer(bytearray(body), dtype=torch.uint8).to(self.device)
+            dist.broadcast(t, src=self.src, group=self.group)
+            self.body_bytes += len(body)
+
+    def recv(self) -> tuple[bool, list, list]:
+        hdr = torch.zeros(4, dtype=torch.int64, device=self.device)
+        dist.broadcast(hdr, src=self.src, group=self.group)
+        stop, n, step_no, _ = hdr.tolist()
+        self.step_no += 1
+        if step_no != self.step_no:
+            raise RuntimeError(f"tensor-parallel serving: follower at step {self.step_no}, leader at {step_no}")
+        if n == 0:
+            return bool(stop), [], []
+        t = torch.empty(n, dtype=torch.uint8, device=self.device)
+        dist.broadcast(t, src=self.src, group=self.group)
+        msg = json.loads(bytes(t.cpu().numpy()))
+        from .engine import SamplingParams
+        new = [(p, SamplingParams(**sp) if sp is not None else None) for p, sp in msg["new"]]
+        return bool(stop), new, msg["cancel"]
+
+
 class TPLeader:
-    """Rank 0's view of a tensor-parallel engine: requests are queued here and shipped to the
-    followers at the start of the next step."""
+    """Rank 0's view of a tensor-parallel engine: admissions and cancellations are queued here and
+    shipped to the followers at the start of the next step, so every rank applies them at the same
+    point of the schedule."""
 
     def __init__(self, engine: Any, tp: ServeTP) -> None:
         self.engine, self.tp = engine, tp
+        self.control = _Control(tp, engine.device)
         self._pending: list = []
+        self._cancels: list = []
 
     def __getattr__(self, name: str) -> Any:        # everything else (cache, stats, ...) is the engine's
         return getattr(self.engine, name)
@@ -117,18 +169,24 @@ class TPLeader:
         self._pending.append((list(prompt), params))
         return r
 
+    def cancel(self, rid: int) -> bool:
+        """Takes effect at the next step boundary on every rank (request ids are assigned in admission
+        order, so they agree across ranks)."""
+        self._cancels.append(int(rid))
+        return True
+
     def step(self):
-        msg = [{"stop": False, "new": self._pending}]
-        dist.broadcast_object_list(msg, src=dist.get_global_rank(self.tp.group, 0), group=self.tp.group)
-        self._pending = []
+        self.control.send(False, self._pending, self._cancels)
+        for rid in self._cancels:
+            self.engine.cancel(rid)
+        self._pending, self._cancels = [], []
         return self.engine.step()
 
     def has_work(self) -> bool:
         return self.engine.has_work()
 
     def shutdown(self) -> None:
-        dist.broadcast_object_list([{"stop": True, "new": []}], src=dist.get_global_rank(self.tp.group, 0),
-                                   group=self.tp.group)
+        self.control.send(True, [], [])
 
     def generate(self, prompts: list[list[int]], params: Any = None) -> list[list[int]]:
         reqs = [self.add_request(p, params) for p in prompts]
@@ -138,14 +196,16 @@ class TPLeader:
 
 
 def run_follower(engine: Any, tp: ServeTP) -> list:
-    """Loop of the ranks other than 0: mirror the leader's admissions, run the same steps.
-    Returns the mirrored requests in admission order."""
+    """Loop of the ranks other than 0: mirror the leader's admissions and cancellations, run the
+    same steps.  Returns the mirrored requests in admission order."""
+    control = _Control(tp, engine.device)
     reqs = []
     while True:
-        msg = [None]
-        dist.broadcast_object_list(msg, src=dist.get_global_rank(tp.group, 0), group=tp.group)
-        if msg[0]["stop"]:
+        stop, new, cancel = control.recv()
+        if stop:
             return reqs
-        for prompt, params in msg[0]["new"]:
+        for prompt, params in new:
             reqs.append(engine.add_request(prompt, params))
+        for rid in cancel:
+            engine.cancel(rid)
         engine.step()

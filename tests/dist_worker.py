@@ -120,9 +120,26 @@ def main():
         if rank == 0:
             lead = TPLeader(eng, tp)
             gen = lead.generate(prompts, params)
+            # second phase: a request is cancelled while it decodes; every rank must drop it at the same step
+            extra = [lead.add_request(p, SamplingParams(max_new_tokens=5, temperature=0.0)) for p in prompts[:3]]
+            lead.step()
+            lead.step()
+            lead.cancel(extra[1].rid)
+            while lead.has_work():
+                lead.step()
             lead.shutdown()
+            extra_out = [(list(r.generated), r.finish_reason) for r in extra]
+            control = lead.control
         else:
-            gen = [r.generated for r in run_follower(eng, tp)]
+            mirrored = run_follower(eng, tp)
+            gen = [r.generated for r in mirrored[:len(prompts)]]
+            extra_out = [(list(r.generated), r.finish_reason) for r in mirrored[len(prompts):]]
+            control = None
+        extras = [None] * world
+        dist.all_gather_object(extras, extra_out)
+        result.update(extra_equal=all(e == extras[0] for e in extras), extra=extras[0])
+        if control is not None:
+            result.update(control_steps=control.step_no, control_body_bytes=control.body_bytes)
         # every rank ran the same requests: compare what each rank generated
         gathered = [None] * world
         dist.all_gather_object(gathered, [list(g) for g in gen])

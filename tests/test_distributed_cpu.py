@@ -86,8 +86,13 @@ def test_tensor_parallel_serving_matches_single_process(tmp_path):
         assert r["ranks_equal"]
         assert r["tp"] == r["ref"], (r["tp"], r["ref"])
         assert r["logit_rel_err_max"] < 1e-4 and r["logits_compared"] == 30
+        # a request cancelled on the leader leaves every rank at the same step
+        assert r["extra_equal"] and r["extra"][1][1] == "cancelled" and len(r["extra"][1][0]) < 5
+        assert len(r["extra"][0][0]) == 5 and len(r["extra"][2][0]) == 5
         assert r["local_heads"] == 2 and r["local_kv"] == 1
         assert r["library_calls"] > 0 and r["native_calls"] == 0
+    # steady-state steps carry a 32-byte header only: bodies were sent for the two admission steps and the cancel
+    assert res[0]["control_steps"] > 8 and 0 < res[0]["control_body_bytes"] < 4000
 
 
 def test_rank_leaves_between_steps_is_noticed_on_the_host(tmp_path):
