@@ -83,6 +83,32 @@ def main():
                       q_shape=list(full["layers.0.attn.q_proj.weight"].shape),
                       local_q_shape=list(eng.model.layers[0].attn.q_proj.weight.shape),
                       momentum_shape=list(eng.muon_state_dict()["state"][0]["momentum_buffer"].shape))
+    if a.mode in ("cpu_tp2_dp2", "gpu_tp2_dp2"):
+        # tensor parallel groups of two ranks, replicated data-parallel: every replica gets its own batch
+        from kotodama_b200.parallel.tp import TensorParallelComm, create_process_groups, gather_full_state_dict
+        tp_group, dp_group = create_process_groups(world, 2)
+        comm = TensorParallelComm(tp_group, dp_group, sequence_parallel=True)
+        cfg = ModelConfig(**MODEL_PRESETS["smoke"], attn_res=True, attn_res_n_blocks=2)
+        batches = [torch.randint(0, cfg.vocab_size, (2, 128 if cuda else 64), generator=torch.Generator().manual_seed(7 + d))
+                   for d in range(world // 2)]
+        eng = build(cfg, device, dtype, comm)
+        losses = [float(eng.train_step([batches[comm.dp_rank]])["loss"]) for _ in range(a.steps)]
+        if cuda:
+            eng.check()
+        full = gather_full_state_dict(eng.model, tp_group)
+        flat = torch.cat([v.float().flatten() for _, v in sorted(full.items())])
+        everyone = [torch.empty_like(flat) for _ in range(world)]
+        dist.all_gather(everyone, flat)
+        result.update(losses=losses, dp_rank=comm.dp_rank, tp_rank=comm.tp_rank,
+                      replicas_match=all(torch.equal(everyone[0], t) for t in everyone),
+                      checksum=float(flat.double().abs().sum()))
+        if rank == 0:
+            # the same job in one process: both replicas' batches as two micro-batches of one step
+            ref = build(cfg, device, dtype, None)
+            ref_losses = [float(ref.train_step(batches)["loss"]) for _ in range(a.steps)]
+            ref_flat = torch.cat([v.float().flatten() for _, v in sorted(ref.model.state_dict().items())])
+            result.update(ref_losses=ref_losses, ref_checksum=float(ref_flat.double().abs().sum()),
+                          rel_param_diff=float((flat - ref_flat.to(flat.device)).norm() / ref_flat.norm()))
     if a.mode in ("gpu_tp_library", "gpu_tp_fused"):
         from kotodama_b200.parallel.tp import TensorParallelComm, create_process_groups, gather_full_state_dict
         tp_group, _ = create_process_groups(world, world)

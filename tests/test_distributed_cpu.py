@@ -111,3 +111,18 @@ def test_rank_leaves_silently_ends_the_next_collective_with_an_error(tmp_path):
     assert res[1]["outcome"] == "left"
     assert res[0]["outcome"].startswith("collective_error"), res[0]
     assert res[0]["detect_s"] < 60
+
+
+def test_tensor_parallel_groups_replicated_data_parallel(tmp_path):
+    """Four CPU ranks as two tensor-parallel groups of two, each group a data-parallel replica with its
+    own batch: every rank ends with the same full parameters, equal to one process that takes both
+    batches as micro-batches of one step."""
+    res = _launch("cpu_tp2_dp2", str(tmp_path / "h"), nproc=4, steps=2)
+    assert sorted((r["dp_rank"], r["tp_rank"]) for r in res) == [(0, 0), (0, 1), (1, 0), (1, 1)]
+    assert all(r["replicas_match"] for r in res)
+    r0 = res[0]
+    assert r0["rel_param_diff"] < 5e-4, r0
+    # a replica's loss is over its own batch; the mean over replicas is the one-process loss
+    by_dp = {r["dp_rank"]: r["losses"] for r in res if r["tp_rank"] == 0}
+    for i, ref in enumerate(r0["ref_losses"]):
+        assert abs((by_dp[0][i] + by_dp[1][i]) / 2 - ref) < 2e-3, (by_dp, r0["ref_losses"])

@@ -67,3 +67,22 @@ def test_tensor_parallel_serving_native_allreduce(tmp_path, nproc):
         assert all(len(t) == 6 for t in r["tp"])
     # bf16: sharded sums round differently, so tokens may part at a near-tie; the logits may not
     assert res[0]["logit_rel_err_max"] < 4e-2 and res[0]["flips_ok"] and res[0]["logits_compared"] >= 10, res[0]
+
+
+@pytest.mark.skipif(_N < 4, reason="needs four GPUs")
+def test_tensor_parallel_groups_replicated_data_parallel_gpu(tmp_path):
+    """Two tensor-parallel groups of two GPUs, each a data-parallel replica with its own batch (library
+    collectives inside the groups and across them): replicas end identical and track one GPU that takes
+    both batches as micro-batches."""
+    env_backup = dict(os.environ)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    try:
+        res = _launch("gpu_tp2_dp2", str(tmp_path / "h"), nproc=4, steps=3)
+    finally:
+        os.environ.clear(); os.environ.update(env_backup)
+    assert all(r["replicas_match"] for r in res)
+    r0 = res[0]
+    assert r0["rel_param_diff"] < 2e-2, r0
+    by_dp = {r["dp_rank"]: r["losses"] for r in res if r["tp_rank"] == 0}
+    for i, ref in enumerate(r0["ref_losses"]):
+        assert abs((by_dp[0][i] + by_dp[1][i]) / 2 - ref) < 5e-2, (by_dp, r0["ref_losses"])
