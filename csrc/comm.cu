@@ -15,6 +15,7 @@
 //   kb_rs_reduce        reduce-scatter consumer: waits for the arrival counters that kb_gemm_rs's
 //                       epilogue raises, sums the per-source slabs (+ residual), frees the slabs
 //   kb_allreduce_oneshot small all-reduce for decode: every rank reads every peer's partial
+//   kb_allreduce_multimem the same small all-reduce with the sum done in NVSwitch (multimem.ld_reduce)
 //   kb_muon_apply_bcast p_new = p*decay - alpha*orth written into every rank's parameter arena
 //                       (the all-gather of the updated matrix is the parameter write itself)
 #include "common.cuh"
@@ -551,6 +552,85 @@ allreduce_push_kernel(const uint4* __restrict__ x, long long nvec, long long slo
     }
     if (last_block_done(counters + 1) && threadIdx.x == 0) *epoch_ptr = epoch;
 }
+// The same all-reduce with the reduction done inside NVSwitch (`multimem.ld_reduce`).  Every rank
+// keeps its partial in its OWN symmetric buffer (slot [parity]); `mc_base` is the multicast address
+// of that buffer: one 16-byte `multimem.ld_reduce.add` at offset i returns the sum over all ranks'
+// buffers at offset i, accumulated in fp32 by the switch.  Per call a rank sends nothing and
+// receives n elements, where the push form receives (world - 1) * n.  Flags and the device-side
+// call number are as above.  The multicast object covers symmetric buffers of this job's own ranks only.
+__device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(const void* mc_addr) {
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(mc_addr)
+                 : "memory");
+    return v;
+}
+__global__ void __launch_bounds__(256)
+allreduce_multimem_kernel(const uint4* __restrict__ x, long long nvec, long long slot_vecs, uint4* sym_local,
+                          const uint4* mc_base, PeerPtrs flags, int world, int rank,
+                          const bf16* __restrict__ residual, bf16* __restrict__ out, int* epoch_ptr, unsigned* counters,
+                          unsigned long long limit_ns, int* status) {
+    __shared__ int ok;
+    const int epoch = *reinterpret_cast<volatile int*>(epoch_ptr) + 1;
+    const int par = epoch & 1;
+    if (threadIdx.x == 0) ok = 1;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    uint4* mine = sym_local + (long long)par * slot_vecs;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += stride) mine[i] = x[i];
+    if (last_block_done(counters) && threadIdx.x < world) {
+        __threadfence_system();
+        st_release_sys(reinterpret_cast<int*>(flags.p[threadIdx.x]) + par * 8 + rank, epoch);
+    }
+    if (threadIdx.x < world) {
+        if (!wait_flag(reinterpret_cast<const int*>(flags.p[rank]) + par * 8 + threadIdx.x, epoch, limit_ns)) {
+            atomicMax(status, (int)KB_TIMEOUT_PEER);
+            ok = 0;
+        }
+    }
+    __syncthreads();
+    if (ok) {
+        const uint4* mc = mc_base + (long long)par * slot_vecs;
+        for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+            const uint4 raw = multimem_ld_reduce_bf16x8(mc + i);
+            if (residual) {
+                float acc[8], t[8];
+                unpack8(ld8(residual + i * 8), acc);
+                unpack8(*reinterpret_cast<const bf16x8*>(&raw), t);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[j] += t[j];
+                st8(out + i * 8, pack8(acc));
+            } else {
+                *reinterpret_cast<uint4*>(out + i * 8) = raw;
+            }
+        }
+    }
+    if (last_block_done(counters + 1) && threadIdx.x == 0) *epoch_ptr = epoch;
+}
+// sym_local: this rank's symmetric buffer of 2 * slot_elems bf16; mc_base: the multicast address of the
+// same buffer; the rest as kb_allreduce_push.
+KB_API int kb_allreduce_multimem(const void* x, long long n, long long slot_elems, void* sym_local, const void* mc_base,
+                                 void* const* peer_flags, int world, int rank, const void* residual, void* out,
+                                 int* epoch_ptr, unsigned* counters, double limit_s, int* status, int max_ctas,
+                                 cudaStream_t st) {
+    if (world < 1 || world > 8 || (n & 7) || (slot_elems & 7) || n > slot_elems || ((uintptr_t)x & 15)) return 5;
+    if (!sym_local || !mc_base || ((uintptr_t)sym_local & 15) || ((uintptr_t)mc_base & 15)) return 6;
+    PeerPtrs pf;
+    for (int i = 0; i < 8; ++i) pf.p[i] = i < world ? peer_flags[i] : nullptr;
+    int sms = 0, dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (max_ctas < 1 || max_ctas > sms) max_ctas = sms;
+    long long blocks = ((n >> 3) + 255) / 256;
+    if (blocks < 1) blocks = 1;
+    if (blocks > max_ctas) blocks = max_ctas;
+    allreduce_multimem_kernel<<<(int)blocks, 256, 0, st>>>((const uint4*)x, n >> 3, slot_elems >> 3, (uint4*)sym_local,
+                                                           (const uint4*)mc_base, pf, world, rank, (const bf16*)residual,
+                                                           (bf16*)out, epoch_ptr, counters,
+                                                           (unsigned long long)(limit_s * 1e9), status);
+    return kb_launch_status();
+}
+
 // x: this rank's partial (n bf16 elements, 16-byte aligned, n % 8 == 0); peer_recv[q]: rank q's
 // receive buffer of 2 * world * slot_elems elements; peer_flags[q]: rank q's 16 flag ints;
 // epoch_ptr / counters (2 unsigned, zero-initialised): local device memory.

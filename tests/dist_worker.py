@@ -140,6 +140,7 @@ def main():
         ref_eng = ServingEngine(copy.deepcopy(full), device=device, dtype=dtype, max_batch=8, max_ctx=256)
         ref_eng.logit_trace = []
         ref = ref_eng.generate(prompts, params)
+        os.environ["KOTODAMA_SERVE_MULTIMEM"] = "1"     # exercise the in-switch all-reduce where the box offers it
         tp = ServeTP()
         eng = ServingEngine(full, device=device, dtype=dtype, max_batch=8, max_ctx=256, tp=tp)
         eng.logit_trace = []
@@ -201,12 +202,23 @@ def main():
             parts = [torch.empty_like(y) for _ in range(world)]
             dist.all_gather(parts, y)
             exact = (sum(p.float() for p in parts) + res.float()).to(torch.bfloat16)
-            errs = []
-            for _ in range(5):                      # repeated calls walk through both parities
-                got = tp.all_reduce(eng.ops, y, res)
-                errs.append(float((got.float() - exact.float()).abs().max()))
-            eng.ops.check_status()
-            result.update(allreduce_max_err=max(errs))
+            def worst():
+                errs = []
+                for _ in range(5):                  # repeated calls walk through both parities
+                    got = tp.all_reduce(eng.ops, y, res)
+                    errs.append(float((got.float() - exact.float()).abs().max()))
+                eng.ops.check_status()
+                return max(errs)
+            # in-switch reduction (when the buffers have a multicast mapping): the switch rounds the sum to
+            # bf16 before the residual is added, so it may differ from the once-rounded sum by one ulp
+            mm_calls0 = tp.multimem_calls
+            mm_err = worst()
+            used_mm = tp.multimem_calls - mm_calls0
+            saved, tp.mc_ptr = tp.mc_ptr, 0         # plain peer stores: exact
+            push_err = worst()
+            tp.mc_ptr = saved
+            result.update(allreduce_max_err=push_err, multimem_calls=used_mm, has_multicast=bool(saved),
+                          multimem_rel_err=mm_err / float(exact.float().abs().max()))
     if a.mode in ("cpu_rank_leaves", "cpu_rank_leaves_silent"):
         # the last rank leaves the job between steps: with a notice in the store (the others raise on
         # the host before their next step) or silently (their next collective ends with an error
