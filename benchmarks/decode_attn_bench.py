@@ -27,6 +27,7 @@ def main() -> None:
     ap.add_argument("--hi", type=int, default=2304)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--splits", default="128,256,512,1024")
+    ap.add_argument("--kernels", default="mma,bulk", help="of mma, bulk, stream, phases")
     a = ap.parse_args()
     ops = get_ops("cuda")
     hd, B = 128, a.batch
@@ -48,7 +49,9 @@ def main() -> None:
     kv_bytes = float(ctx.sum()) * a.kv * hd * 2 * 2
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
     max_ctx = ((int(ctx.max()) + 511) // 512) * 512
-    for split in [int(s) for s in a.splits.split(",")]:
+    import ctypes
+    for kernel, split in [(k, int(s)) for k in a.kernels.split(",") for s in a.splits.split(",")]:
+        ops.lib.kb_set_decode_kernel(ctypes.c_int({"phases": 0, "stream": 1, "bulk": 2, "mma": 3}[kernel]))
         fn = lambda: ops.paged_decode_attention(q, k_pages, v_pages, table, ctx, max_ctx, a.heads, a.kv, hd, split=split)
         for _ in range(3):
             fn()
@@ -62,7 +65,7 @@ def main() -> None:
             ts.append(e0.elapsed_time(e1))
         ts.sort()
         ms = ts[len(ts) // 2]
-        print(json.dumps({"batch": B, "mean_ctx": round(float(ctx.float().mean()), 1), "split": split, "ms": round(ms, 4),
+        print(json.dumps({"kernel": kernel, "batch": B, "mean_ctx": round(float(ctx.float().mean()), 1), "split": split, "ms": round(ms, 4),
                           "kv_mb": round(kv_bytes / 1e6, 1), "gb_s": round(kv_bytes / ms / 1e6, 1)}))
     ops.check_status()
 

@@ -416,7 +416,13 @@ qknorm_rope_fwd_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ qw
         unpack8(ld8(kw + HD / 2 + e0), wk2);
     }
     const long long nwarps = (long long)gridDim.x * (blockDim.x >> 5);
-    for (long long tok = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); tok < N; tok += nwarps) {
+    // few tokens (decode): a warp takes one pass of HPW heads of one token instead of the whole token
+    const int ngroups = (nh + HPW - 1) / HPW;
+    const int gsplit = N >= nwarps ? 1 : ngroups;
+    for (long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); item < (long long)N * gsplit;
+         item += nwarps) {
+        const long long tok = item / gsplit;
+        const int h_lo = gsplit == 1 ? 0 : (int)(item % gsplit) * HPW, h_hi = gsplit == 1 ? nh : min(nh, h_lo + HPW);
         const int pos = positions ? positions[tok] : (int)(tok % T) + pos_offset;
         float c[8], sn[8];
         *reinterpret_cast<float4*>(c) = *reinterpret_cast<const float4*>(cosT + (size_t)pos * HD + e0);
@@ -426,7 +432,7 @@ qknorm_rope_fwd_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ qw
         const bf16* src = qkv + (size_t)tok * in_stride;
         bf16* dst = out + (size_t)tok * out_stride;
 #pragma unroll 2
-        for (int h0 = 0; h0 < nh; h0 += HPW) {
+        for (int h0 = h_lo; h0 < h_hi; h0 += HPW) {
             const int head = h0 + hsel;
             const bool ok = head < nh;
             const bool isq = head < nq;
@@ -591,7 +597,7 @@ KB_API int kb_qknorm_grid_warps() { return kb_num_sms() * 8 * 8; }
 KB_API int kb_qknorm_rope_fwd(const void* qkv, const void* qw, const void* kw, const float* cosT, const float* sinT,
                               void* out, float* rstd, int N, int T, int nq, int nkv, int hd, int pos_offset,
                               float eps, const int* positions, cudaStream_t st) {
-    long long blocks = ((long long)N + 7) / 8;                  // one warp per token
+    long long blocks = ((long long)N * ((nq + nkv + 3) / 4) + 7) / 8;    // at most one warp per (token, head group)
     if (blocks > kb_num_sms() * 8) blocks = kb_num_sms() * 8;
     if (blocks < 1) blocks = 1;
     const bool norm = qw != nullptr;

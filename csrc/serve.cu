@@ -592,6 +592,203 @@ paged_decode_bulk_kernel(const bf16* __restrict__ q, long long q_stride, const b
         part_ml[(pbase * G + g) * 2 + 1] = sum;
     }
 }
+// Tensor-core variant (head_dim 128): the G query heads of a KV head are the first G rows of a
+// 16-row `mma.sync.m16n8k16` A operand, so one page (16 tokens) costs 16 MMAs for Q K^T and 16 for
+// P V instead of ~400 scalar FMAs and bf16 unpacks per lane - the scalar kernels are bound by
+// instruction issue at 0.46 of the copy bandwidth, not by memory.  Every warp owns its own ring of
+// pages (page w, w + 4, ... of the split): its 32 lanes each issue one 256-byte cp.async.bulk per
+// K / V row into rows of 272 bytes (the 16-byte pad makes the ldmatrix reads conflict-free), so
+// there is no block-wide barrier in the loop.  Waits are bounded as in the bulk kernel.
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+// d += a * b, m16n8k16, bf16 inputs; rows 8..15 of A are zero here (a1 = a3 = 0)
+__device__ __forceinline__ void mma_16816(float* d, uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+    const uint32_t z = 0;
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+                 "{%0, %1, %2, %3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(z), "r"(a2), "r"(z), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack2_bf16(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+constexpr int MMA_PITCH = 272;                       // bytes per staged K / V row (256 + 16)
+constexpr int MMA_PAGE = PAGE * MMA_PITCH;           // one staged (page, head) block of K or V
+constexpr int MMA_NST = 2;                           // pages in flight per warp
+constexpr int MMA_SMEM = 4 * MMA_NST * 2 * MMA_PAGE;
+
+template <int G>
+__global__ void __launch_bounds__(128, 3)
+paged_decode_mma_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* __restrict__ k_pages,
+                        const bf16* __restrict__ v_pages, const int* __restrict__ page_table, int max_pages,
+                        const int* __restrict__ ctx_lens, int n_kv, int split_tokens, float scale,
+                        float* __restrict__ part_o, float* __restrict__ part_ml, int nsplit) {
+    constexpr int HD = 128, PG = PAGE * HD;
+    extern __shared__ __align__(128) uint8_t ring_raw[];
+    __shared__ __align__(16) bf16 qs[G][HD];
+    __shared__ int spage[2048 / PAGE];
+    __shared__ float wml[4][G][2];
+    __shared__ uint64_t full[4][MMA_NST];
+    __shared__ int abort_flag;
+    const int kvh = blockIdx.x, req = blockIdx.y, sp = blockIdx.z;
+    const int ctx = ctx_lens[req];
+    const int t0 = sp * split_tokens;
+    const int nt = min(split_tokens, ctx - t0);
+    const size_t pbase = ((size_t)(req * n_kv + kvh) * nsplit + sp);
+    if (nt <= 0) {
+        if (threadIdx.x < G) {
+            part_ml[(pbase * G + threadIdx.x) * 2] = -INFINITY;
+            part_ml[(pbase * G + threadIdx.x) * 2 + 1] = 0.f;
+        }
+        return;
+    }
+    const int npages = (nt + PAGE - 1) / PAGE;
+    const float qscale = scale * 1.4426950408889634f;
+    for (int i = threadIdx.x; i < G * HD; i += blockDim.x) {
+        const int g = i / HD, d = i % HD;
+        qs[g][d] = __float2bfloat16(__bfloat162float(q[(size_t)req * q_stride + (size_t)(kvh * G + g) * HD + d]) * qscale);
+    }
+    for (int i = threadIdx.x; i < npages; i += blockDim.x)
+        spage[i] = page_table[(size_t)req * max_pages + t0 / PAGE + i];
+    if (threadIdx.x == 0) {
+        for (int w = 0; w < 4; ++w)
+            for (int s = 0; s < MMA_NST; ++s) tc::mbar_init(&full[w][s], 1);
+        abort_flag = 0;
+        tc::fence_barrier_init();
+    }
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    uint8_t* ring = ring_raw + (size_t)warp * MMA_NST * 2 * MMA_PAGE;
+    const int my_pages = warp < npages ? (npages - warp + 3) / 4 : 0;       // pages warp, warp + 4, ...
+    auto issue = [&](int i) {                                               // i-th page of this warp
+        const int st = i % MMA_NST;
+        if (lane == 0) tc::mbar_expect_tx(&full[warp][st], 2 * PG * 2);
+        __syncwarp();
+        const int row = lane & 15, is_v = lane >> 4;
+        const size_t src = ((size_t)spage[warp + 4 * i] * n_kv + kvh) * PG + (size_t)row * HD;
+        bulk_g2s_dec(ring + (size_t)(st * 2 + is_v) * MMA_PAGE + row * MMA_PITCH, (is_v ? v_pages : k_pages) + src, HD * 2,
+                     &full[warp][st]);
+    };
+    for (int i = 0; i < MMA_NST && i < my_pages; ++i) issue(i);
+
+    // Q fragments: row g = lane / 4 of the A operand (zero for g >= G), k = 16 ks + 2 (lane % 4) [+ 8]
+    const int g_row = lane >> 2, qd = lane & 3;
+    uint32_t qa0[8], qa2[8];
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {
+        qa0[ks] = g_row < G ? *reinterpret_cast<const uint32_t*>(&qs[g_row < G ? g_row : 0][ks * 16 + 2 * qd]) : 0u;
+        qa2[ks] = g_row < G ? *reinterpret_cast<const uint32_t*>(&qs[g_row < G ? g_row : 0][ks * 16 + 8 + 2 * qd]) : 0u;
+    }
+    float o[16][4];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+    float m = -INFINITY, l = 0.f;
+    bool ok = true;
+    // ldmatrix lane addressing (byte offsets inside a staged page)
+    const uint32_t k_off = (uint32_t)(((lane & 7) + (lane >> 4) * 8) * MMA_PITCH + ((lane >> 3) & 1) * 16);
+    const uint32_t v_off = (uint32_t)(((lane & 7) + ((lane >> 3) & 1) * 8) * MMA_PITCH + (lane >> 4) * 16);
+    for (int i = 0; i < my_pages; ++i) {
+        const int st = i % MMA_NST;
+        if (!tc::mbar_wait(&full[warp][st], (uint32_t)(i / MMA_NST) & 1u, &abort_flag)) {
+            ok = false;
+            break;
+        }
+        const uint32_t kb = smem_u32(ring + (size_t)(st * 2) * MMA_PAGE), vb = kb + MMA_PAGE;
+        float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+            uint32_t b00, b01, b10, b11;
+            ldsm_x4(kb + k_off + ks * 32, b00, b01, b10, b11);
+            mma_16816(s0, qa0[ks], qa2[ks], b00, b01);
+            mma_16816(s1, qa0[ks], qa2[ks], b10, b11);
+        }
+        // online softmax on row g_row: this lane holds tokens 2 qd, 2 qd + 1, 8 + 2 qd, 9 + 2 qd of the page
+        const int tok0 = (warp + 4 * i) * PAGE + 2 * qd;
+        const float v00 = tok0 < nt ? s0[0] : -INFINITY, v01 = tok0 + 1 < nt ? s0[1] : -INFINITY;
+        const float v10 = tok0 + 8 < nt ? s1[0] : -INFINITY, v11 = tok0 + 9 < nt ? s1[1] : -INFINITY;
+        float mx = fmaxf(fmaxf(v00, v01), fmaxf(v10, v11));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float mn = fmaxf(m, mx);                   // finite: the first token of a staged page is always valid
+        const float f = exp2f(m - mn);
+        m = mn;
+        const float p00 = exp2f(v00 - mn), p01 = exp2f(v01 - mn), p10 = exp2f(v10 - mn), p11 = exp2f(v11 - mn);
+        l = l * f + (p00 + p01) + (p10 + p11);
+        const uint32_t pa0 = pack2_bf16(p00, p01), pa2 = pack2_bf16(p10, p11);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) { o[j][0] *= f; o[j][1] *= f; }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            uint32_t b0, b1, b2, b3;
+            ldsm_x4_trans(vb + v_off + j * 32, b0, b1, b2, b3);
+            mma_16816(o[2 * j], pa0, pa2, b0, b1);
+            mma_16816(o[2 * j + 1], pa0, pa2, b2, b3);
+        }
+        __syncwarp();                                    // every lane has read this stage
+        if (i + MMA_NST < my_pages) {
+            tc::fence_proxy_async();
+            issue(i + MMA_NST);
+        }
+    }
+    if (!ok) {
+        // a copy did not arrive in time: report, contribute nothing, and let copies in flight land
+        if (lane == 0) {
+            atomicMax(&g_decode_status, (int)KB_TIMEOUT_TMA);
+            const uint64_t t_0 = global_timer_ns();
+            while (global_timer_ns() - t_0 < 2000000ull) {}
+        }
+        __syncwarp();
+        m = -INFINITY;
+        l = 0.f;
+    }
+    l += __shfl_xor_sync(0xffffffffu, l, 1);
+    l += __shfl_xor_sync(0xffffffffu, l, 2);
+    // the warp's partial output goes to the start of its own (now idle) ring: [G][HD] floats
+    __syncwarp();
+    float* wo_w = reinterpret_cast<float*>(ring);
+    if (g_row < G) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            wo_w[g_row * HD + 8 * j + 2 * qd] = m == -INFINITY ? 0.f : o[j][0];
+            wo_w[g_row * HD + 8 * j + 2 * qd + 1] = m == -INFINITY ? 0.f : o[j][1];
+        }
+        if (qd == 0) {
+            wml[warp][g_row][0] = m;
+            wml[warp][g_row][1] = l;
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < G * HD; i += blockDim.x) {
+        const int g = i / HD, d = i % HD;
+        const float mxx = fmaxf(fmaxf(wml[0][g][0], wml[1][g][0]), fmaxf(wml[2][g][0], wml[3][g][0]));
+        float acc = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w)
+            if (wml[w][g][0] != -INFINITY)
+                acc += reinterpret_cast<const float*>(ring_raw + (size_t)w * MMA_NST * 2 * MMA_PAGE)[g * HD + d] *
+                       exp2f(wml[w][g][0] - mxx);
+        part_o[(pbase * G + g) * HD + d] = acc;
+    }
+    if (threadIdx.x < G) {
+        const int g = threadIdx.x;
+        const float mxx = fmaxf(fmaxf(wml[0][g][0], wml[1][g][0]), fmaxf(wml[2][g][0], wml[3][g][0]));
+        float sum = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w)
+            if (wml[w][g][0] != -INFINITY) sum += wml[w][g][1] * exp2f(wml[w][g][0] - mxx);
+        part_ml[(pbase * G + g) * 2] = mxx == -INFINITY ? -INFINITY : mxx * 0.6931471805599453f;
+        part_ml[(pbase * G + g) * 2 + 1] = sum;
+    }
+}
+
 // Reads the decode status word and clears it, so that one timeout is reported once.
 KB_API int kb_decode_status() {
     int v = 0;
@@ -603,6 +800,11 @@ KB_API int kb_decode_status() {
     return v;
 }
 
+// Which decode attention kernel kb_paged_decode launches: -1 = read KB_DECODE_KERNEL on the first call,
+// 0 phases, 1 stream, 2 bulk, 3 mma.  kb_set_decode_kernel lets one process compare them.
+static int g_decode_kernel = -1;
+KB_API void kb_set_decode_kernel(int which) { g_decode_kernel = which; }
+
 // Workspace sizes (floats) for B requests: part_o = B*n_kv*nsplit*G*hd, part_ml = B*n_kv*nsplit*G*2.
 KB_API int kb_paged_decode(const void* q, long long q_stride, const void* k_pages, const void* v_pages,
                            const int* page_table, int max_pages, const int* ctx_lens, int B, int n_q, int n_kv, int hd,
@@ -613,20 +815,33 @@ KB_API int kb_paged_decode(const void* q, long long q_stride, const void* k_page
     const int nsplit = (max_ctx + split_tokens - 1) / split_tokens;
     dim3 grid(n_kv, B, nsplit);
     const size_t smem = (size_t)G * split_tokens * sizeof(float);
-    // KB_DECODE_KERNEL: "bulk" (default for head_dim 128: pages streamed into a shared-memory ring by
-    // cp.async.bulk, measured 0.114 ms against 0.136 ms), "stream" (online softmax from registers) or
-    // "phases" (three-phase kernel with the scores in shared memory)
-    static int streaming = -1, unroll = 2;
+    // KB_DECODE_KERNEL: "mma" (default for head_dim 128: tensor-core tiles, per-warp page rings), "bulk"
+    // (scalar FMA from a block-wide cp.async.bulk ring; the default for other head sizes), "stream" (online
+    // softmax from registers) or "phases" (three-phase kernel with the scores in shared memory)
+    int& streaming = g_decode_kernel;
+    static int unroll = 2;
     if (streaming < 0) {
         const char* e = getenv("KB_DECODE_KERNEL");
-        streaming = (e && e[0] == 'p') ? 0 : (e && e[0] == 's') ? 1 : 2;     // phases | stream | bulk (default)
+        streaming = (e && e[0] == 'p') ? 0 : (e && e[0] == 's') ? 1 : (e && e[0] == 'b') ? 2 : 3;   // phases | stream | bulk | mma (default)
         // tokens per lane group and iteration: 2 (default: 168 registers, three CTAs per SM; measured
         // 0.136 ms against 0.155 ms for 4, which needs 237 registers and leaves two CTAs per SM)
         const char* u = getenv("KB_DECODE_UNROLL");
         if (u && atoi(u) == 4) unroll = 4;
     }
 #define DEC(HD_, G_)                                                                                          \
-    if (streaming == 2 && (HD_) == 128 && (G_) <= 4) {                                                         \
+    if (streaming == 3 && (HD_) == 128) {                                                                      \
+        static bool mma_flags[64] = {};                                                                        \
+        bool* attr = kb_device_flag(mma_flags);                                                                \
+        if (!attr) return 7;                                                                                   \
+        if (!*attr) {                                                                                          \
+            if (cudaFuncSetAttribute(paged_decode_mma_kernel<G_>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                     MMA_SMEM) != cudaSuccess) return 7;                                       \
+            *attr = true;                                                                                      \
+        }                                                                                                      \
+        paged_decode_mma_kernel<G_><<<grid, 128, MMA_SMEM, st>>>(                                              \
+            (const bf16*)q, q_stride, (const bf16*)k_pages, (const bf16*)v_pages, page_table, max_pages, ctx_lens, \
+            n_kv, split_tokens, scale, part_o, part_ml, nsplit);                                               \
+    } else if (streaming >= 2 && (HD_) == 128 && (G_) <= 4) {                                                         \
         static bool attr_flags[64] = {};                                                                       \
         bool* attr = kb_device_flag(attr_flags);                                                               \
         if (!attr) return 7;                                                                                   \

@@ -237,10 +237,15 @@ def test_newton_schulz_matches_reference(ops):
     assert 0.5 < float(s.min()) and float(s.max()) < 1.5
 
 
-def test_paged_decode_and_kv_append(ops):
-    B, n_q, n_kv, hd, P = 5, 6, 2, 128, 64
-    ctx = torch.tensor([1, 16, 17, 300, 513], dtype=torch.int32, device="cuda")
-    maxp = 40
+@pytest.mark.parametrize("kernel", ["mma", "bulk", "stream", "phases"])
+@pytest.mark.parametrize("n_q,n_kv", [(6, 2), (8, 2), (4, 4)])
+def test_paged_decode_and_kv_append(ops, kernel, n_q, n_kv):
+    """Every decode attention kernel (tensor-core tiles, bulk-copy ring, streaming, three-phase) against
+    the PyTorch restatement: contexts that end inside a page, exactly on one, in the second split."""
+    import ctypes
+    B, hd, P = 6, 128, 64
+    ctx = torch.tensor([1, 16, 17, 300, 513, 1100], dtype=torch.int32, device="cuda")
+    maxp = 80
     k_pages = torch.zeros(P + 200, n_kv, 16, hd, device="cuda", dtype=torch.bfloat16)
     v_pages = torch.zeros_like(k_pages)
     table = torch.zeros(B, maxp, dtype=torch.int32, device="cuda")
@@ -258,10 +263,16 @@ def test_paged_decode_and_kv_append(ops):
         slots = pages[pos // 16] * 16 + pos % 16
         ops.kv_append(k, v, k_pages, v_pages, slots)
     q = bf(B, n_q * hd, seed=9)
-    out = ops.paged_decode_attention(q, k_pages, v_pages, table, ctx, int(ctx.max()), n_q, n_kv, hd)
+    ops.lib.kb_set_decode_kernel(ctypes.c_int({"phases": 0, "stream": 1, "bulk": 2, "mma": 3}[kernel]))
+    try:
+        out = ops.paged_decode_attention(q, k_pages, v_pages, table, ctx, int(ctx.max()), n_q, n_kv, hd)
+        torch.cuda.synchronize()
+    finally:
+        ops.lib.kb_set_decode_kernel(ctypes.c_int(3))
     ref = TORCH_OPS.paged_decode_attention(q.float(), k_pages.float(), v_pages.float(), table, ctx, int(ctx.max()),
                                            n_q, n_kv, hd)
     assert rel_err(out, ref) < 1e-2
+    ops.check_status()
     lg = bf(7, 49152, seed=3)
     assert torch.equal(ops.argmax(lg), lg.float().argmax(-1))
 
