@@ -1,0 +1,345 @@
+// Skinny GEMM for decode-size activations (M <= 128 rows): C = alpha * A x B^T + beta * Cin, bf16,
+// both operands K-major.  Such a product is a weight stream: the N x K weight must cross HBM once,
+// and an M x N output has far too few 128 x 256 tiles to put every SM on that stream.  The K range
+// of each output tile is therefore split over the CTAs of a thread-block cluster (up to 8), and the
+// partial sums meet in distributed shared memory instead of in global memory:
+//
+//   TMA (128-byte swizzle) -> shared-memory ring -> tcgen05.mma (128 x BN x 16) over this CTA's
+//   K range -> the fp32 partial tile goes from tensor memory to this CTA's shared memory (the ring,
+//   now idle) -> cluster barrier -> every CTA sums its share of the rows over all CTAs of the
+//   cluster with `ld.shared::cluster`, applies alpha / beta * Cin and stores bf16 -> cluster barrier.
+//
+// One launch, no fp32 workspace, no atomics, no finishing kernel (the split-K path of the general
+// kernel needs all three).  BN is 256 or 128 and the cluster size is chosen per shape so that
+// tiles x cluster size comes close to the number of SMs.
+// Roles (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer and TMEM owner, warps 2-5 =
+// tensor memory -> shared memory, then the cluster reduction.  All waits are bounded; a CTA whose
+// wait ran out still takes part in both cluster barriers, so its peers are never left waiting.
+#include <cuda.h>
+#include <string.h>
+
+#include "tc.cuh"
+
+namespace {
+
+constexpr int BM = 128, BK = 64;
+constexpr int A_STAGE = BM * BK * 2;
+template <int BN> struct Cfg {
+    static constexpr int STAGES = BN == 256 ? 4 : 6;
+    static constexpr int B_STAGE = BN * BK * 2;
+    static constexpr int RING = STAGES * (A_STAGE + B_STAGE);
+    static constexpr int PITCH = BN * 4 + 16;            // bytes per staged fp32 row (+16: conflict-free row-per-lane stores)
+    static constexpr int SMEM = RING + 1024 + 256;
+    static_assert(BM * PITCH <= RING, "the partial tile is staged in the ring");
+};
+
+struct SkinnyParams {
+    int M, N, K;
+    float alpha, beta;
+    __nv_bfloat16* C;
+    const __nv_bfloat16* Cin;      // may be null, may alias C
+    long long ldc, ldcin;
+    int* status;
+    int a_rows;                    // rows of A that TMA fetches per K block (M rounded up to 8): the rest of the 128-row
+                                   // operand tile is left as it is - its products land in rows that nobody reads
+};
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t cluster_nctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t mapa(uint32_t smem_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ float4 ld_dsmem_f4(uint32_t cluster_addr) {
+    float4 v;
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                 : "r"(cluster_addr));
+    return v;
+}
+
+template <int BN>
+__global__ void __launch_bounds__(192, 1)
+gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const SkinnyParams p) {
+    constexpr int STAGES = Cfg<BN>::STAGES, B_STAGE = Cfg<BN>::B_STAGE, PITCH = Cfg<BN>::PITCH;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* sA = smem;
+    uint8_t* sB = smem + STAGES * A_STAGE;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg<BN>::RING);
+    uint64_t* full = bars;                 // [STAGES] TMA -> MMA
+    uint64_t* empty = bars + STAGES;       // [STAGES] MMA -> TMA
+    uint64_t* acc_full = bars + 2 * STAGES;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 1);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int S = (int)cluster_nctarank(), r = (int)cluster_ctarank();
+    const int tn = blockIdx.y;
+    const int kblocks_total = (p.K + BK - 1) / BK;
+    const int kb_per = (kblocks_total + S - 1) / S;
+    const int kb0 = min(kblocks_total, r * kb_per), kb1 = min(kblocks_total, kb0 + kb_per);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            tc::mbar_init(&full[s], 1);
+            tc::mbar_init(&empty[s], 1);
+        }
+        tc::mbar_init(acc_full, 1);
+        *abort_flag = 0;
+        tc::fence_barrier_init();
+    }
+    if (warp == 1) {
+        tc::tmem_alloc(tmem_slot, BN);
+        tc::tmem_relinquish();
+    }
+    tc::tc_fence_before();
+    __syncthreads();
+    tc::tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    bool have_partial = kb1 > kb0;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            tc::prefetch_tmap(&tmA);
+            tc::prefetch_tmap(&tmB);
+            int stage = 0;
+            uint32_t phase = 0;
+            for (int kb = kb0; kb < kb1; ++kb) {
+                if (!tc::mbar_wait(&empty[stage], phase ^ 1, abort_flag)) {
+                    atomicMax(p.status, (int)KB_TIMEOUT_TMA);
+                    break;
+                }
+                tc::mbar_expect_tx(&full[stage], p.a_rows * BK * 2 + B_STAGE);
+                tc::tma_load_3d(sB + stage * B_STAGE, &tmB, &full[stage], kb * BK, tn * BN, 0);
+                tc::tma_load_3d(sA + stage * A_STAGE, &tmA, &full[stage], kb * BK, 0, 0);
+                if (++stage == STAGES) { stage = 0; phase ^= 1; }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && have_partial) {
+            const uint32_t idesc = tc::instr_desc_f16(BM, BN, 1, 1, 0, 0);
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int kb = kb0; kb < kb1; ++kb) {
+                if (!tc::mbar_wait(&full[stage], phase, abort_flag)) {
+                    atomicMax(p.status, (int)KB_TIMEOUT_MMA);
+                    ok = false;
+                    break;
+                }
+                tc::tc_fence_after();
+                const uint32_t a_addr = smem_u32(sA + stage * A_STAGE), b_addr = smem_u32(sB + stage * B_STAGE);
+#pragma unroll
+                for (int k = 0; k < BK / 16; ++k)
+                    tc::mma_f16(tmem_base, tc::smem_desc_sw128(a_addr + k * 32, 16, 1024),
+                                tc::smem_desc_sw128(b_addr + k * 32, 16, 1024), idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+                tc::tc_commit(&empty[stage]);
+                if (++stage == STAGES) { stage = 0; phase ^= 1; }
+            }
+            if (ok) tc::tc_commit(acc_full);
+        }
+    } else {
+        // ---- tensor memory -> this CTA's shared memory (rows below M only), fp32, padded rows
+        const int quarter = warp & 3;
+        const int row = quarter * 32 + lane;
+        if (have_partial) {
+            if (!tc::mbar_wait(acc_full, 0, abort_flag)) {
+                if (lane == 0) atomicMax(p.status, (int)KB_TIMEOUT_EPI);
+                have_partial = false;
+            }
+        }
+        tc::tc_fence_after();
+        if (quarter * 32 < p.M) {                                    // warp-uniform
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t acc[32];
+                if (have_partial) {
+                    tc::tmem_ld32(taddr + c0, acc);
+                    tc::tmem_ld_wait();
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) acc[j] = 0u;
+                }
+                if (row < p.M) {
+                    float4* dst = reinterpret_cast<float4*>(smem + (size_t)row * PITCH + c0 * 4);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        dst[j] = make_float4(__uint_as_float(acc[4 * j]), __uint_as_float(acc[4 * j + 1]),
+                                             __uint_as_float(acc[4 * j + 2]), __uint_as_float(acc[4 * j + 3]));
+                }
+            }
+        }
+        tc::tc_fence_before();
+    }
+    // every CTA's partial tile is in its shared memory
+    __syncthreads();
+    cluster_sync_all();
+    if (warp >= 2) {
+        // ---- reduction over the cluster: this CTA owns rows r, r + S, ...; a row is BN / 4 float4
+        constexpr int V4 = BN / 4;                                   // float4 per row
+        constexpr int ROWS_PER_PASS = 128 / V4;                      // 2 (BN 256) or 4 (BN 128)
+        const int t = threadIdx.x - 64;
+        const int c4 = t % V4, sub = t / V4;
+        const int col = tn * BN + c4 * 4;
+        const uint32_t base = smem_u32(smem);
+        for (int i = sub; ; i += ROWS_PER_PASS) {
+            const int row = r + i * S;
+            if (row >= p.M) break;
+            if (col >= p.N) continue;
+            const uint32_t off = base + (uint32_t)row * PITCH + (uint32_t)c4 * 16;
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int q = 0; q < S; ++q) {
+                const float4 v = ld_dsmem_f4(mapa(off, (uint32_t)q));
+                acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+            }
+            float o[4] = {p.alpha * acc.x, p.alpha * acc.y, p.alpha * acc.z, p.alpha * acc.w};
+            const int ncols = min(4, p.N - col);
+            __nv_bfloat16* dst = p.C + (long long)row * p.ldc + col;
+            const __nv_bfloat16* cin = p.Cin ? p.Cin + (long long)row * p.ldcin + col : nullptr;
+            if (ncols == 4 && ((p.ldc | p.ldcin | col) & 3) == 0) {
+                if (cin) {
+                    const uint2 raw = *reinterpret_cast<const uint2*>(cin);
+                    const __nv_bfloat162* c2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+                    const float2 c01 = __bfloat1622float2(c2[0]), c23 = __bfloat1622float2(c2[1]);
+                    o[0] += p.beta * c01.x; o[1] += p.beta * c01.y; o[2] += p.beta * c23.x; o[3] += p.beta * c23.y;
+                }
+                uint2 out;
+                __nv_bfloat162 lo = __floats2bfloat162_rn(o[0], o[1]), hi = __floats2bfloat162_rn(o[2], o[3]);
+                out.x = *reinterpret_cast<uint32_t*>(&lo);
+                out.y = *reinterpret_cast<uint32_t*>(&hi);
+                *reinterpret_cast<uint2*>(dst) = out;
+            } else {
+                for (int j = 0; j < ncols; ++j)
+                    dst[j] = __float2bfloat16(o[j] + (cin ? p.beta * __bfloat162float(cin[j]) : 0.f));
+            }
+        }
+    }
+    // nobody leaves while a peer may still read its shared memory
+    cluster_sync_all();
+    if (warp == 1) {
+        tc::tc_fence_after();
+        tc::tmem_dealloc(tmem_base, BN);
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn get_encode_sk() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+    return fn;
+}
+// bf16 matrix [rows, cols], cols contiguous, row stride ld elements
+int make_tmap_sk(CUtensorMap* m, const void* base, long long cols, long long rows, long long ld, int box_cols, int box_rows) {
+    EncodeTiledFn enc = get_encode_sk();
+    if (!enc) return 100;
+    cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, 1};
+    cuuint64_t strides[2] = {(cuuint64_t)ld * 2, (cuuint64_t)(rows * ld) * 2};
+    cuuint32_t box[3] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    const CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : 200 + (int)r;
+}
+
+template <int BN>
+int launch_skinny(const CUtensorMap& tmA, const CUtensorMap& tmB, const SkinnyParams& p, int tiles, int S, cudaStream_t st) {
+    static bool attr_flags[64] = {};
+    bool* attr = kb_device_flag(attr_flags);
+    if (!attr) return 7;
+    if (!*attr) {
+        if (cudaFuncSetAttribute(gemm_skinny_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN>::SMEM) != cudaSuccess)
+            return 7;
+        *attr = true;
+    }
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(S, tiles, 1);
+    cfg.blockDim = dim3(192, 1, 1);
+    cfg.dynamicSmemBytes = Cfg<BN>::SMEM;
+    cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = S;
+    at[0].val.clusterDim.y = 1;
+    at[0].val.clusterDim.z = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_skinny_kernel<BN>, tmA, tmB, p);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return KB_LAUNCH_FAILED;
+    }
+    return 0;
+}
+
+}  // namespace
+
+// C[M,N] = alpha * A[M,K] x B[N,K]^T + beta * Cin, all bf16, K contiguous in A and B (lda/ldb in
+// elements, multiples of 8; 16-byte aligned bases), M <= 128.  `split` <= 0: chosen here (BN and the
+// cluster size that put the most CTAs on the weight stream); otherwise the cluster size to use (1..8).
+// Returns 0, a refusal code, or KB_LAUNCH_FAILED when the runtime cannot place the cluster.
+KB_API int kb_gemm_skinny(const void* A, const void* B, void* C, const void* Cin, int M, int N, int K, long long lda,
+                          long long ldb, long long ldc, long long ldcin, float alpha, float beta, int split, int bn,
+                          int* status, cudaStream_t st) {
+    if (M <= 0 || M > BM || N <= 0 || K <= 0) return 5;
+    if ((lda & 7) || (ldb & 7) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15)) return 6;
+    if (bn != 0 && bn != 128 && bn != 256) return 5;
+    int sms = 0, dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int kt = (K + BK - 1) / BK;
+    int best_bn = 256, best_s = 1, best_ctas = 0;
+    // Cluster sizes 1, 2, 3, 4 and 8 place well; 5 to 7 were measured to run in more than one wave
+    // (3072 x 3072: 19.0 us with 6 CTAs per cluster against 11.0 us with 4).  Among the candidates the
+    // one with the most CTAs wins, the narrower tile on a tie.
+    for (int cand : {128, 256}) {
+        if (bn && cand != bn) continue;
+        const int tiles = (N + cand - 1) / cand;
+        int s = split > 0 ? split : sms / tiles;
+        if (s > 8) s = 8;
+        if (s > kt / 2) s = kt / 2;
+        if (s < 1) s = 1;
+        if (split <= 0 && s > 4 && s < 8) s = 4;
+        const int per = (kt + s - 1) / s;
+        s = (kt + per - 1) / per;                         // no empty K parts
+        if (split <= 0 && s > 4 && s < 8) s = 4;
+        if (tiles * s > best_ctas) { best_ctas = tiles * s; best_bn = cand; best_s = s; }
+    }
+    const int tiles = (N + best_bn - 1) / best_bn;
+    CUtensorMap tmA, tmB;
+    const int a_rows = ((M + 7) / 8) * 8;
+    int r = make_tmap_sk(&tmA, A, K, M, lda, BK, a_rows);
+    if (r) return r;
+    r = make_tmap_sk(&tmB, B, K, N, ldb, BK, best_bn);
+    if (r) return r;
+    SkinnyParams p;
+    memset(&p, 0, sizeof(p));
+    p.M = M; p.N = N; p.K = K; p.alpha = alpha; p.beta = beta;
+    p.C = (__nv_bfloat16*)C; p.Cin = (const __nv_bfloat16*)Cin; p.ldc = ldc; p.ldcin = ldcin; p.status = status;
+    p.a_rows = a_rows;
+    return best_bn == 256 ? launch_skinny<256>(tmA, tmB, p, tiles, best_s, st)
+                          : launch_skinny<128>(tmA, tmB, p, tiles, best_s, st);
+}

@@ -56,6 +56,7 @@ class CudaOps(TorchOps):
         self.gemm_2cta = os.environ.get("KOTODAMA_GEMM_2CTA", "1") == "1"   # CTA-pair kernel for large products
         # fp8 products: "mx" = hardware block-scaled MMA (power-of-two scales, accumulation stays in tensor
         # memory); "promote" = fp32 scales applied per K block in registers
+        self.skinny_cluster = os.environ.get("KOTODAMA_SKINNY", "cluster") != "splitk"   # decode-size GEMMs: cluster split-K through DSMEM
         self.fp8_backend = os.environ.get("KOTODAMA_FP8", "mx")
         self.fp8_pow2 = self.fp8_backend == "mx"
         self.fp8_pair = int(os.environ.get("KOTODAMA_FP8_PAIR", "0"))       # mx kernel: 1 = SM-pair tiles, 0 = one CTA per tile (faster, default)
@@ -135,8 +136,21 @@ class CudaOps(TorchOps):
         kblocks = (K + 63) // 64
         if (batch == 1 and M <= 128 and tiles <= 74 and kblocks >= 8 and out.dtype == torch.bfloat16
                 and out.is_contiguous() and (cin is None or cin.is_contiguous()) and self.split_k_small_m):
-            # skinny (decode-size) products: too few output tiles to fill the GPU, so the K range is
-            # split over CTAs with fp32 atomic accumulation and a small finishing kernel
+            # skinny (decode-size) products: too few output tiles to fill the GPU.  bf16 K-major operands: the K
+            # range is split over the CTAs of a thread-block cluster and the partial tiles are summed through
+            # distributed shared memory (one launch); otherwise split-K with fp32 atomics and a finishing kernel
+            if (self.skinny_cluster and not a_mn and not b_mn and a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
+                    and not diag):
+                rc = self.lib.kb_gemm_skinny(_p(a), _p(b), _p(out), _p(cin), _I(M), _I(N), _I(K), _LL(a.stride(-2)),
+                                             _LL(b.stride(-2)), _LL(out.stride(-2)),
+                                             _LL(cin.stride(-2) if cin is not None else 0), _F(alpha), _F(beta), _I(0),
+                                             _I(0), _p(self.status(a.device)), _st())
+                if rc == 0:
+                    self.launches += 1
+                    return out
+                if rc != 9:                          # 9: the runtime could not place the cluster - use the atomics path
+                    self._rc(rc, "kb_gemm_skinny")
+                self.skinny_cluster = False
             split = max(2, min(148 // tiles, kblocks // 2, 16))
             # one fp32 workspace per output size, zeroed once: the finishing kernel clears it again
             key = (M * N, a.device.index)

@@ -321,12 +321,27 @@ def test_serving_engine_gpu_matches_cpu_logits():
     assert compared >= 12
 
 
-@pytest.mark.parametrize("M,N,K", [(64, 3072, 3072), (64, 5120, 3072), (17, 3072, 8192), (128, 512, 1024)])
-def test_gemm_split_k_small_m(ops, M, N, K):
+@pytest.mark.parametrize("path", ["cluster", "splitk"])
+@pytest.mark.parametrize("M,N,K", [(64, 3072, 3072), (64, 5120, 3072), (17, 3072, 8192), (128, 512, 1024), (64, 16384, 3072),
+                                   (33, 1000, 1536), (1, 3072, 3072)])
+def test_gemm_skinny_small_m(ops, path, M, N, K):
+    """Decode-size products on both paths: K split over a thread-block cluster with the partial tiles
+    summed through distributed shared memory, and K split over CTAs with fp32 atomics + finishing kernel."""
     a, b, r = bf(M, K, seed=1), bf(N, K, scale=0.05, seed=2), bf(M, N, seed=3)
     ref = a.float() @ b.float().t()
-    assert rel_err(ops.gemm_nt(a, b), ref) < 1e-2
-    assert rel_err(ops.gemm_nt(a, b, residual=r), ref + r.float()) < 1e-2
+    prev = ops.skinny_cluster
+    ops.skinny_cluster = path == "cluster"
+    try:
+        n0 = ops.launches
+        assert rel_err(ops.gemm_nt(a, b), ref) < 1e-2
+        if path == "cluster":
+            assert ops.launches - n0 == 1 and ops.skinny_cluster        # one launch, and the cluster was placed
+        assert rel_err(ops.gemm_nt(a, b, residual=r), ref + r.float()) < 1e-2
+        out = r.clone()
+        ops.gemm_nt(a, b, out=out, accumulate=True)                      # addend aliases the output
+        assert rel_err(out, ref + r.float()) < 1e-2
+    finally:
+        ops.skinny_cluster = prev
     ops.check_status()
 
 
