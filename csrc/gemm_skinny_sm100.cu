@@ -23,14 +23,19 @@
 namespace {
 
 constexpr int BM = 128, BK = 64;
-constexpr int A_STAGE = BM * BK * 2;
-template <int BN> struct Cfg {
-    static constexpr int STAGES = BN == 256 ? 4 : 6;
+// AM: rows of A that get a slot in the ring (64 when M <= 64, else 128).  The MMA always reads a
+// 128-row operand tile; with AM = 64 its upper half is whatever follows the slot in shared memory,
+// and the products of those rows land in accumulator rows that nobody reads.  A smaller A slot
+// means more stages, i.e. more weight bytes in flight per SM, which is what bounds this kernel.
+template <int BN, int AM> struct Cfg {
+    static constexpr int A_STAGE = AM * BK * 2;
     static constexpr int B_STAGE = BN * BK * 2;
+    static constexpr int STAGES = (200 * 1024) / (A_STAGE + B_STAGE);
     static constexpr int RING = STAGES * (A_STAGE + B_STAGE);
     static constexpr int PITCH = BN * 4 + 16;            // bytes per staged fp32 row (+16: conflict-free row-per-lane stores)
-    static constexpr int SMEM = RING + 1024 + 256;
-    static_assert(BM * PITCH <= RING, "the partial tile is staged in the ring");
+    static constexpr int SMEM = RING + BM * BK * 2 /* slack: the 128-row read of the last A slot */ + 1024 + 256;
+    static_assert(AM * PITCH <= RING, "the partial tile is staged in the ring");
+    static_assert(SMEM <= 227 * 1024, "shared memory");
 };
 
 struct SkinnyParams {
@@ -40,6 +45,7 @@ struct SkinnyParams {
     const __nv_bfloat16* Cin;      // may be null, may alias C
     long long ldc, ldcin;
     int* status;
+    int b_packed;                  // B is stored tile-major: [N / 128][K / 64][128 rows][64 columns], 16 KB contiguous per tile
     int a_rows;                    // rows of A that TMA fetches per K block (M rounded up to 8): the rest of the 128-row
                                    // operand tile is left as it is - its products land in rows that nobody reads
 };
@@ -70,15 +76,25 @@ __device__ __forceinline__ float4 ld_dsmem_f4(uint32_t cluster_addr) {
     return v;
 }
 
-template <int BN>
+__device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* m, uint64_t* bar, int x, int y, int z, int w) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cta.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z), "r"(w)
+        : "memory");
+}
+
+template <int BN, int AM>
 __global__ void __launch_bounds__(192, 1)
 gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const SkinnyParams p) {
-    constexpr int STAGES = Cfg<BN>::STAGES, B_STAGE = Cfg<BN>::B_STAGE, PITCH = Cfg<BN>::PITCH;
+    using C_ = Cfg<BN, AM>;
+    constexpr int STAGES = C_::STAGES, A_STAGE = C_::A_STAGE, B_STAGE = C_::B_STAGE, PITCH = C_::PITCH;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t* sA = smem;
-    uint8_t* sB = smem + STAGES * A_STAGE;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg<BN>::RING);
+    // B slots first, A slots behind them: the 128-row read of an A slot may run into the next slot or
+    // into the slack after the last one, never outside the allocation
+    uint8_t* sB = smem;
+    uint8_t* sA = smem + STAGES * B_STAGE;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C_::RING + BM * BK * 2);
     uint64_t* full = bars;                 // [STAGES] TMA -> MMA
     uint64_t* empty = bars + STAGES;       // [STAGES] MMA -> TMA
     uint64_t* acc_full = bars + 2 * STAGES;
@@ -123,7 +139,8 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                     break;
                 }
                 tc::mbar_expect_tx(&full[stage], p.a_rows * BK * 2 + B_STAGE);
-                tc::tma_load_3d(sB + stage * B_STAGE, &tmB, &full[stage], kb * BK, tn * BN, 0);
+                if (p.b_packed) tma_load_4d(sB + stage * B_STAGE, &tmB, &full[stage], 0, 0, kb, tn * (BN / 128));
+                else tc::tma_load_3d(sB + stage * B_STAGE, &tmB, &full[stage], kb * BK, tn * BN, 0);
                 tc::tma_load_3d(sA + stage * A_STAGE, &tmA, &full[stage], kb * BK, 0, 0);
                 if (++stage == STAGES) { stage = 0; phase ^= 1; }
             }
@@ -264,13 +281,28 @@ int make_tmap_sk(CUtensorMap* m, const void* base, long long cols, long long row
     return r == CUDA_SUCCESS ? 0 : 200 + (int)r;
 }
 
-template <int BN>
+// the tile-major copy of a weight: dims {64, 128, K / 64, N / 128}, a box takes whole 16 KB tiles
+int make_tmap_packed(CUtensorMap* m, const void* base, long long n_tiles, long long k_tiles, int box_n_tiles) {
+    EncodeTiledFn enc = get_encode_sk();
+    if (!enc) return 100;
+    cuuint64_t dims[4] = {64, 128, (cuuint64_t)k_tiles, (cuuint64_t)n_tiles};
+    cuuint64_t strides[3] = {128, 16384, (cuuint64_t)k_tiles * 16384};
+    cuuint32_t box[4] = {64, 128, 1, (cuuint32_t)box_n_tiles};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    const CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : 200 + (int)r;
+}
+
+template <int BN, int AM>
 int launch_skinny(const CUtensorMap& tmA, const CUtensorMap& tmB, const SkinnyParams& p, int tiles, int S, cudaStream_t st) {
     static bool attr_flags[64] = {};
     bool* attr = kb_device_flag(attr_flags);
     if (!attr) return 7;
     if (!*attr) {
-        if (cudaFuncSetAttribute(gemm_skinny_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN>::SMEM) != cudaSuccess)
+        if (cudaFuncSetAttribute(gemm_skinny_kernel<BN, AM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 Cfg<BN, AM>::SMEM) != cudaSuccess)
             return 7;
         *attr = true;
     }
@@ -278,7 +310,7 @@ int launch_skinny(const CUtensorMap& tmA, const CUtensorMap& tmB, const SkinnyPa
     memset(&cfg, 0, sizeof(cfg));
     cfg.gridDim = dim3(S, tiles, 1);
     cfg.blockDim = dim3(192, 1, 1);
-    cfg.dynamicSmemBytes = Cfg<BN>::SMEM;
+    cfg.dynamicSmemBytes = Cfg<BN, AM>::SMEM;
     cfg.stream = st;
     cudaLaunchAttribute at[1];
     at[0].id = cudaLaunchAttributeClusterDimension;
@@ -287,7 +319,7 @@ int launch_skinny(const CUtensorMap& tmA, const CUtensorMap& tmB, const SkinnyPa
     at[0].val.clusterDim.z = 1;
     cfg.attrs = at;
     cfg.numAttrs = 1;
-    const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_skinny_kernel<BN>, tmA, tmB, p);
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_skinny_kernel<BN, AM>, tmA, tmB, p);
     if (e != cudaSuccess) {
         cudaGetLastError();
         return KB_LAUNCH_FAILED;
@@ -301,11 +333,17 @@ int launch_skinny(const CUtensorMap& tmA, const CUtensorMap& tmB, const SkinnyPa
 // elements, multiples of 8; 16-byte aligned bases), M <= 128.  `split` <= 0: chosen here (BN and the
 // cluster size that put the most CTAs on the weight stream); otherwise the cluster size to use (1..8).
 // Returns 0, a refusal code, or KB_LAUNCH_FAILED when the runtime cannot place the cluster.
+// `b_packed` != 0: B points at the tile-major copy made by kb_pack_weight_tiles ([ceil(N/128)][K/64][128][64],
+// K a multiple of 64); every TMA box is then whole contiguous 16 KB tiles instead of 128-byte pieces 2K
+// bytes apart.  Measured on the 3B decode shapes this is worth 3 % (the kernel is bound by the ~70 GB/s
+// one SM can take in and by its fixed ~6 us of launch, prologue and cluster reduction, not by DRAM
+// locality), so the serving engine does not make the copies unless asked to.
 KB_API int kb_gemm_skinny(const void* A, const void* B, void* C, const void* Cin, int M, int N, int K, long long lda,
                           long long ldb, long long ldc, long long ldcin, float alpha, float beta, int split, int bn,
-                          int* status, cudaStream_t st) {
+                          int b_packed, int* status, cudaStream_t st) {
     if (M <= 0 || M > BM || N <= 0 || K <= 0) return 5;
-    if ((lda & 7) || (ldb & 7) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15)) return 6;
+    if ((lda & 7) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15)) return 6;
+    if (b_packed ? (K % BK) != 0 : (ldb & 7) != 0) return 6;
     if (bn != 0 && bn != 128 && bn != 256) return 5;
     int sms = 0, dev = 0;
     cudaGetDevice(&dev);
@@ -333,13 +371,41 @@ KB_API int kb_gemm_skinny(const void* A, const void* B, void* C, const void* Cin
     const int a_rows = ((M + 7) / 8) * 8;
     int r = make_tmap_sk(&tmA, A, K, M, lda, BK, a_rows);
     if (r) return r;
-    r = make_tmap_sk(&tmB, B, K, N, ldb, BK, best_bn);
+    if (b_packed) r = make_tmap_packed(&tmB, B, (N + 127) / 128, K / BK, best_bn / 128);
+    else r = make_tmap_sk(&tmB, B, K, N, ldb, BK, best_bn);
     if (r) return r;
     SkinnyParams p;
     memset(&p, 0, sizeof(p));
     p.M = M; p.N = N; p.K = K; p.alpha = alpha; p.beta = beta;
     p.C = (__nv_bfloat16*)C; p.Cin = (const __nv_bfloat16*)Cin; p.ldc = ldc; p.ldcin = ldcin; p.status = status;
     p.a_rows = a_rows;
-    return best_bn == 256 ? launch_skinny<256>(tmA, tmB, p, tiles, best_s, st)
-                          : launch_skinny<128>(tmA, tmB, p, tiles, best_s, st);
+    p.b_packed = b_packed;
+    if (M <= 64)
+        return best_bn == 256 ? launch_skinny<256, 64>(tmA, tmB, p, tiles, best_s, st)
+                              : launch_skinny<128, 64>(tmA, tmB, p, tiles, best_s, st);
+    return best_bn == 256 ? launch_skinny<256, 128>(tmA, tmB, p, tiles, best_s, st)
+                          : launch_skinny<128, 128>(tmA, tmB, p, tiles, best_s, st);
+}
+
+// Tile-major copy of a K-major bf16 weight for kb_gemm_skinny: dst[nt][kt][r][c] = w[nt * 128 + r][kt * 64 + c]
+// (zero for rows past N).  One-off, at load time.
+namespace {
+__global__ void pack_weight_tiles_kernel(const __nv_bfloat16* __restrict__ w, long long ldw, __nv_bfloat16* __restrict__ dst,
+                                         int N, int k_tiles) {
+    const int nt = blockIdx.y, kt = blockIdx.x;
+    uint4* out = reinterpret_cast<uint4*>(dst + ((long long)nt * k_tiles + kt) * 8192);
+    for (int i = threadIdx.x; i < 1024; i += blockDim.x) {            // 128 rows x 8 chunks of 8 elements
+        const int r = i >> 3, c8 = i & 7;
+        const int row = nt * 128 + r;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (row < N) v = *reinterpret_cast<const uint4*>(w + (long long)row * ldw + kt * 64 + c8 * 8);
+        out[i] = v;
+    }
+}
+}  // namespace
+KB_API int kb_pack_weight_tiles(const void* w, long long ldw, void* dst, int N, int K, cudaStream_t st) {
+    if (N <= 0 || K <= 0 || (K % BK) || (ldw & 7) || ((uintptr_t)w & 15) || ((uintptr_t)dst & 15)) return 5;
+    dim3 grid(K / BK, (N + 127) / 128);
+    pack_weight_tiles_kernel<<<grid, 256, 0, st>>>((const __nv_bfloat16*)w, ldw, (__nv_bfloat16*)dst, N, K / BK);
+    return kb_launch_status();
 }

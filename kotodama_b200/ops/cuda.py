@@ -15,7 +15,7 @@ from typing import Optional, Sequence
 import torch
 
 from . import _build
-from .reference import Fp8Weight, TorchOps
+from .reference import DecodeWeight, Fp8Weight, TorchOps
 
 _VP = ctypes.c_void_p
 _I = ctypes.c_int
@@ -57,6 +57,7 @@ class CudaOps(TorchOps):
         # fp8 products: "mx" = hardware block-scaled MMA (power-of-two scales, accumulation stays in tensor
         # memory); "promote" = fp32 scales applied per K block in registers
         self.skinny_cluster = os.environ.get("KOTODAMA_SKINNY", "cluster") != "splitk"   # decode-size GEMMs: cluster split-K through DSMEM
+        self.pack_decode_weights = os.environ.get("KOTODAMA_PACK_DECODE", "0") == "1"   # serving: tile-major weight copies for decode (measured +3 %, costs a second copy of the weights: off)
         self.fp8_backend = os.environ.get("KOTODAMA_FP8", "mx")
         self.fp8_pow2 = self.fp8_backend == "mx"
         self.fp8_pair = int(os.environ.get("KOTODAMA_FP8_PAIR", "0"))       # mx kernel: 1 = SM-pair tiles, 0 = one CTA per tile (faster, default)
@@ -144,7 +145,7 @@ class CudaOps(TorchOps):
                 rc = self.lib.kb_gemm_skinny(_p(a), _p(b), _p(out), _p(cin), _I(M), _I(N), _I(K), _LL(a.stride(-2)),
                                              _LL(b.stride(-2)), _LL(out.stride(-2)),
                                              _LL(cin.stride(-2) if cin is not None else 0), _F(alpha), _F(beta), _I(0),
-                                             _I(0), _p(self.status(a.device)), _st())
+                                             _I(0), _I(0), _p(self.status(a.device)), _st())
                 if rc == 0:
                     self.launches += 1
                     return out
@@ -237,7 +238,36 @@ class CudaOps(TorchOps):
                    _p(self.status(qa.device)), _I(self.fp8_pair if self.fp8_backend == "mx" else 0), _st())
         return out
 
+    def decode_weight(self, w: torch.Tensor) -> DecodeWeight:
+        N, K = w.shape
+        if not (self.skinny_cluster and self.pack_decode_weights and w.is_cuda and w.dtype == torch.bfloat16
+                and w.is_contiguous() and K % 64 == 0):
+            return DecodeWeight(w)
+        packed = torch.empty(((N + 127) // 128) * (K // 64) * 8192, device=w.device, dtype=torch.bfloat16)
+        self._call("kb_pack_weight_tiles", _p(w), _LL(K), _p(packed), _I(N), _I(K), _st())
+        return DecodeWeight(w, packed)
+
     def gemm_nt(self, a, b, out=None, residual=None, accumulate=False):
+        if isinstance(b, DecodeWeight):
+            M, K = a.shape
+            N = b.w.shape[0]
+            if (b.packed is not None and self.skinny_cluster and M <= 128 and a.dtype == torch.bfloat16
+                    and a.stride(-1) == 1 and a.stride(-2) % 8 == 0 and a.data_ptr() % 16 == 0
+                    and (N + 255) // 256 <= 74 and K >= 512):
+                if out is None:
+                    out = torch.empty(M, N, device=a.device, dtype=torch.bfloat16)
+                cin = residual if residual is not None else (out if accumulate else None)
+                if out.stride(-1) == 1 and (cin is None or (cin.stride(-1) == 1 and cin.dtype == out.dtype)):
+                    rc = self.lib.kb_gemm_skinny(_p(a), _p(b.packed), _p(out), _p(cin), _I(M), _I(N), _I(K), _LL(a.stride(-2)),
+                                                 _LL(K), _LL(out.stride(-2)), _LL(cin.stride(-2) if cin is not None else 0),
+                                                 _F(1.0), _F(1.0), _I(0), _I(0), _I(1), _p(self.status(a.device)), _st())
+                    if rc == 0:
+                        self.launches += 1
+                        return out
+                    if rc != 9:
+                        self._rc(rc, "kb_gemm_skinny(packed)")
+                    self.skinny_cluster = False
+            b = b.w
         if isinstance(b, Fp8Weight):
             if self.fp8_ok(a.shape[0], a.shape[1], b.shape[0]) and a.dtype == torch.bfloat16 and not (
                     accumulate and residual is not None):

@@ -44,6 +44,19 @@ class Fp8Weight:
         self.q, self.s, self.qt, self.st = ops.quant_blocks(self.w, transposed=True)
 
 
+class DecodeWeight:
+    """A projection weight of the serving engine: the K-major matrix ``w`` plus, on CUDA, a tile-major
+    copy (``packed``: [N/128][K/64][128][64], 16 KB contiguous per tile) that the decode-size GEMM
+    streams at DRAM page granularity.  Products with more than 128 rows (prefill) use ``w``."""
+
+    def __init__(self, w: torch.Tensor, packed: Optional[torch.Tensor] = None) -> None:
+        self.w, self.packed = w, packed
+
+    @property
+    def shape(self):
+        return self.w.shape
+
+
 def _to_e4m3(x: torch.Tensor) -> torch.Tensor:
     return x.clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn)
 
@@ -52,6 +65,10 @@ class TorchOps:
     """Backend object; ``CudaOps`` derives from it and overrides methods with kernels."""
 
     name = "torch"
+
+    def decode_weight(self, w: torch.Tensor) -> "DecodeWeight":
+        """Wrap a serving projection weight; the CUDA backend adds the tile-major copy."""
+        return DecodeWeight(w)
 
     # ------------------------------------------------------------------ block-scaled fp8
     fp8_pow2 = False      # scales rounded up to powers of two (what the hardware block-scaled GEMM takes)
@@ -112,6 +129,8 @@ class TorchOps:
                 residual: Optional[torch.Tensor] = None, accumulate: bool = False) -> torch.Tensor:
         """``a[M,K] @ b[N,K]^T (+ residual) -> [M,N]``; ``accumulate`` adds into ``out``.  ``b`` may be
         an ``Fp8Weight``: the product then runs in block-scaled fp8."""
+        if isinstance(b, DecodeWeight):
+            b = b.w
         if isinstance(b, Fp8Weight):
             if self.fp8_ok(a.shape[0], a.shape[1], b.shape[0]) and not accumulate:
                 r = self.gemm_fp8(*self.quant_rows(a), b.q, b.s, 128, out_dtype=a.dtype)

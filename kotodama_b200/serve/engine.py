@@ -157,9 +157,10 @@ class ServingEngine:
         for i in range(cfg.num_layers):
             p = f"layers.{i}."
             g = lambda n: ar.view(p + n) if (p + n) in ar.by_name else None
+            dw = self.ops.decode_weight          # on CUDA: adds the tile-major copy that decode-size products stream
             self.layers.append(dict(
-                wqkv=ar.fused(p + "attn.q_proj.weight", p + "attn.v_proj.weight"), wo=ar.view(p + "attn.o_proj.weight"),
-                wgu=ar.fused(p + "ffn.gate_proj.weight", p + "ffn.up_proj.weight"), wd=ar.view(p + "ffn.down_proj.weight"),
+                wqkv=dw(ar.fused(p + "attn.q_proj.weight", p + "attn.v_proj.weight")), wo=dw(ar.view(p + "attn.o_proj.weight")),
+                wgu=dw(ar.fused(p + "ffn.gate_proj.weight", p + "ffn.up_proj.weight")), wd=dw(ar.view(p + "ffn.down_proj.weight")),
                 attn_norm=g("attn_norm.weight"), ffn_norm=g("ffn_norm.weight"), qn=g("attn.q_norm.weight"),
                 kn=g("attn.k_norm.weight"), aq=g("attn_res_query"), an=g("attn_res_norm.weight"),
                 mq=g("mlp_res_query"), mn=g("mlp_res_norm.weight")))

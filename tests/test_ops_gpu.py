@@ -340,6 +340,14 @@ def test_gemm_skinny_small_m(ops, path, M, N, K):
         out = r.clone()
         ops.gemm_nt(a, b, out=out, accumulate=True)                      # addend aliases the output
         assert rel_err(out, ref + r.float()) < 1e-2
+        if path == "cluster" and K % 64 == 0:
+            ops.pack_decode_weights = True
+            dw = ops.decode_weight(b)                                    # tile-major copy of the weight
+            ops.pack_decode_weights = False
+            assert dw.packed is not None
+            n1 = ops.launches
+            assert rel_err(ops.gemm_nt(a, dw, residual=r), ref + r.float()) < 1e-2
+            assert ops.launches - n1 == 1
     finally:
         ops.skinny_cluster = prev
     ops.check_status()
