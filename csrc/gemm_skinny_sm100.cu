@@ -108,6 +108,13 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     const int kb_per = (kblocks_total + S - 1) / S;
     const int kb0 = min(kblocks_total, r * kb_per), kb1 = min(kblocks_total, kb0 + kb_per);
 
+    auto load_stage = [&](int kb, int stage) {
+        tc::mbar_expect_tx(&full[stage], p.a_rows * BK * 2 + B_STAGE);
+        if (p.b_packed) tma_load_4d(sB + stage * B_STAGE, &tmB, &full[stage], 0, 0, kb, tn * (BN / 128));
+        else tc::tma_load_3d(sB + stage * B_STAGE, &tmB, &full[stage], kb * BK, tn * BN, 0);
+        tc::tma_load_3d(sA + stage * A_STAGE, &tmA, &full[stage], kb * BK, 0, 0);
+    };
+    const int first = min(STAGES, kb1 - kb0);                    // loads that need no free-slot wait
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             tc::mbar_init(&full[s], 1);
@@ -116,6 +123,11 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         tc::mbar_init(acc_full, 1);
         *abort_flag = 0;
         tc::fence_barrier_init();
+        // the first ring-full of loads goes out before the block-wide barrier below (which waits for
+        // the tensor-memory allocation): their latency overlaps the rest of the prologue
+        tc::prefetch_tmap(&tmA);
+        tc::prefetch_tmap(&tmB);
+        for (int i = 0; i < first; ++i) load_stage(kb0 + i, i);
     }
     if (warp == 1) {
         tc::tmem_alloc(tmem_slot, BN);
@@ -129,19 +141,14 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
 
     if (warp == 0) {
         if (lane == 0) {
-            tc::prefetch_tmap(&tmA);
-            tc::prefetch_tmap(&tmB);
-            int stage = 0;
-            uint32_t phase = 0;
-            for (int kb = kb0; kb < kb1; ++kb) {
+            int stage = first == STAGES ? 0 : first;
+            uint32_t phase = first == STAGES ? 1 : 0;
+            for (int kb = kb0 + first; kb < kb1; ++kb) {
                 if (!tc::mbar_wait(&empty[stage], phase ^ 1, abort_flag)) {
                     atomicMax(p.status, (int)KB_TIMEOUT_TMA);
                     break;
                 }
-                tc::mbar_expect_tx(&full[stage], p.a_rows * BK * 2 + B_STAGE);
-                if (p.b_packed) tma_load_4d(sB + stage * B_STAGE, &tmB, &full[stage], 0, 0, kb, tn * (BN / 128));
-                else tc::tma_load_3d(sB + stage * B_STAGE, &tmB, &full[stage], kb * BK, tn * BN, 0);
-                tc::tma_load_3d(sA + stage * A_STAGE, &tmA, &full[stage], kb * BK, 0, 0);
+                load_stage(kb, stage);
                 if (++stage == STAGES) { stage = 0; phase ^= 1; }
             }
         }
