@@ -10,6 +10,7 @@
 //   kb_reduce_to_owner  owner sums a gradient range over all ranks (fp32), scales, stores bf16
 //   kb_allreduce_slices two-shot all-reduce: each rank reduces its slice, stores it to every peer
 //   kb_scalar_allreduce sum of one float per rank (also a full barrier)
+//   kb_packed_allreduce sum of up to 8 floats per rank in one launch (tensor-parallel loss and norm terms)
 //   kb_ag_push          all-gather producer: this rank's shard into every peer's staging slot, then
 //                       the shard's ready flag (consumed by kb_gemm_ag's TMA producer)
 //   kb_rs_reduce        reduce-scatter consumer: waits for the arrival counters that kb_gemm_rs's
@@ -224,6 +225,52 @@ KB_API int kb_scalar_allreduce(void* const* peer_vals, void* const* peer_flags, 
         pf.p[i] = i < world ? peer_flags[i] : nullptr;
     }
     scalar_allreduce_kernel<<<1, 32, 0, st>>>(pv, pf, world, rank, slot, epoch, in, out,
+                                              (unsigned long long)(limit_s * 1e9), status);
+    return kb_launch_status();
+}
+
+// Packed small all-reduce: up to 8 floats per rank summed in one launch (loss terms, squared gradient
+// norms: the reductions a tensor-parallel step needs besides its activation collectives).  Every rank
+// stores its `count` values into slot [parity][rank] of every peer, raises its flag there, waits for
+// all flags and sums in rank order - bitwise identical on every rank.  vals layout on every rank:
+// float vals[2][8][8]; flags as above.
+__global__ void packed_allreduce_kernel(PeerPtrs vals, PeerPtrs flags, int world, int rank, int slot, int epoch,
+                                        const float* __restrict__ in, float* __restrict__ out, int count,
+                                        unsigned long long limit_ns, int* status) {
+    __shared__ int ok;
+    if (threadIdx.x == 0) ok = 1;
+    __syncthreads();
+    const int par = epoch & 1;
+    if (threadIdx.x < world) {
+        float* dst = reinterpret_cast<float*>(vals.p[threadIdx.x]) + (par * 8 + rank) * 8;
+        for (int j = 0; j < count; ++j) dst[j] = in[j];
+        __threadfence_system();
+        st_release_sys(reinterpret_cast<int*>(flags.p[threadIdx.x]) + slot * 8 + rank, epoch);
+        if (!wait_flag(reinterpret_cast<const int*>(flags.p[rank]) + slot * 8 + threadIdx.x, epoch, limit_ns)) {
+            atomicMax(status, (int)KB_TIMEOUT_PEER);
+            ok = 0;
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x < count) {
+        float s = 0.f;
+        if (ok) {
+            const volatile float* mine = reinterpret_cast<const volatile float*>(vals.p[rank]) + par * 64;
+            for (int r = 0; r < world; ++r) s += mine[r * 8 + threadIdx.x];
+        }
+        out[threadIdx.x] = s;
+    }
+}
+KB_API int kb_packed_allreduce(void* const* peer_vals, void* const* peer_flags, int world, int rank, int slot,
+                               int epoch, const float* in, float* out, int count, double limit_s, int* status,
+                               cudaStream_t st) {
+    if (world < 1 || world > 8 || count < 1 || count > 8 || !in || !out) return 5;
+    PeerPtrs pv, pf;
+    for (int i = 0; i < 8; ++i) {
+        pv.p[i] = i < world ? peer_vals[i] : nullptr;
+        pf.p[i] = i < world ? peer_flags[i] : nullptr;
+    }
+    packed_allreduce_kernel<<<1, 32, 0, st>>>(pv, pf, world, rank, slot, epoch, in, out, count,
                                               (unsigned long long)(limit_s * 1e9), status);
     return kb_launch_status();
 }

@@ -37,7 +37,7 @@ from .tp import TensorParallelComm
 _VP, _I, _LL, _F, _D = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float, ctypes.c_double
 
 # slots of the per-rank sync array (8 ints each, indexed by source rank)
-_AG_READY, _AG_DONE, _RS_CNT, _RS_DONE = 0, 2, 3, 5      # AG_READY and RS_CNT take two slots (parity)
+_AG_READY, _AG_DONE, _RS_CNT, _RS_DONE, _SMALL = 0, 2, 3, 5, 6      # AG_READY and RS_CNT take two slots (parity)
 _N_SLOTS = 8
 _BM, _BK = 128, 64
 
@@ -78,9 +78,40 @@ class FusedTensorParallelComm(TensorParallelComm):
         self._h = [h]
         self.sync_ptrs = [int(p) for p in h.buffer_ptrs]
         self.counters = torch.zeros(4, device=dev, dtype=torch.int32)     # last-block elections
+        # packed small all-reduce (loss terms, squared gradient norm): values [2 parities][8 ranks][8 floats]
+        self.small_vals = self.symm_mem.empty(2 * 8 * 8, dtype=torch.float32, device=dev)
+        self.small_vals.zero_()
+        h_s = self.symm_mem.rendezvous(self.small_vals, self.tp_group)
+        self._h.append(h_s)
+        self.small_ptrs = [int(p) for p in h_s.buffer_ptrs]
+        self.small_calls = 0
         self.side = torch.cuda.Stream(device=dev)
         torch.cuda.synchronize()
         dist.barrier(group=self.tp_group)
+
+    def _small_allreduce(self, t: torch.Tensor) -> torch.Tensor:
+        """Sum of a few floats over the TP group inside one kernel (no library collective)."""
+        n = t.numel()
+        if not (hasattr(self, "small_ptrs") and t.is_cuda and n <= 8):
+            dist.all_reduce(t, group=self.tp_group)
+            return t
+        src = t.reshape(-1).float().contiguous()
+        out = torch.empty_like(src)
+        self.small_calls += 1
+        rc = self.lib.kb_packed_allreduce(self._arr(self.small_ptrs), self._arr(self.sync_ptrs), _I(self.tp_size),
+                                          _I(self.tp_rank), _I(_SMALL), _I(self.small_calls), _VP(src.data_ptr()),
+                                          _VP(out.data_ptr()), _I(n), _D(self.WAIT_LIMIT_S), self._status(), self._st())
+        self._ck(rc, "kb_packed_allreduce")
+        return out.reshape(t.shape).to(t.dtype)
+
+    def loss_reduce(self, t: torch.Tensor) -> torch.Tensor:
+        return self._small_allreduce(t)
+
+    def grad_sumsq(self, ops) -> torch.Tensor:
+        ar = self.engine.arena
+        sharded = self._small_allreduce(ops.sumsq(ar.grads[:ar.muon_end]).reshape(1).clone())
+        lo, hi = ar.adamw_range()
+        return (sharded + ops.sumsq(ar.grads[lo:hi]).reshape(1))[0]
 
     def _buffer(self, kind: str, elems: int) -> tuple[torch.Tensor, list[int]]:
         """Symmetric buffer of at least ``elems`` bf16 elements per parity (2 parities).  Grows by
