@@ -620,19 +620,34 @@ __device__ __forceinline__ uint32_t pack2_bf16(float lo, float hi) {
     return *reinterpret_cast<const uint32_t*>(&v);
 }
 
-constexpr int MMA_PITCH = 272;                       // bytes per staged K / V row (256 + 16)
-constexpr int MMA_PAGE = PAGE * MMA_PITCH;           // one staged (page, head) block of K or V
+// A staged (page, head) block of K or V is two 128-byte-swizzled half tiles [16 rows][64 elements]
+// (2 KB each), written by one TMA tensor copy each: four copies per page instead of 32 row copies -
+// the per-copy cost of the copy engine was what bounded the first version of this kernel.
+constexpr int MMA_HALF = PAGE * 128;                 // bytes of one half tile
+constexpr int MMA_PAGE = 2 * MMA_HALF;               // one staged (page, head) block of K or V
 constexpr int MMA_NST = 2;                           // pages in flight per warp
-constexpr int MMA_SMEM = 4 * MMA_NST * 2 * MMA_PAGE;
+constexpr int MMA_SMEM = 4 * MMA_NST * 2 * MMA_PAGE + 1024;
+
+__device__ __forceinline__ void tma_load_2d_dec(void* dst, const CUtensorMap* m, uint64_t* bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cta.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(x), "r"(y)
+        : "memory");
+}
+// byte offset of 16-byte chunk `chunk` (0..15 over the 256-byte row) of row `row` inside a staged block
+__device__ __forceinline__ uint32_t swz_off(int row, int chunk) {
+    return (uint32_t)((chunk >> 3) * MMA_HALF + row * 128 + (((chunk & 7) ^ (row & 7)) << 4));
+}
 
 template <int G>
 __global__ void __launch_bounds__(128, 3)
-paged_decode_mma_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* __restrict__ k_pages,
-                        const bf16* __restrict__ v_pages, const int* __restrict__ page_table, int max_pages,
+paged_decode_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                        const bf16* __restrict__ q, long long q_stride, const int* __restrict__ page_table, int max_pages,
                         const int* __restrict__ ctx_lens, int n_kv, int split_tokens, float scale,
                         float* __restrict__ part_o, float* __restrict__ part_ml, int nsplit) {
-    constexpr int HD = 128, PG = PAGE * HD;
-    extern __shared__ __align__(128) uint8_t ring_raw[];
+    constexpr int HD = 128;
+    extern __shared__ uint8_t ring_unaligned[];
+    uint8_t* ring_raw = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(ring_unaligned) + 1023) & ~uintptr_t(1023));
     __shared__ __align__(16) bf16 qs[G][HD];
     __shared__ int spage[2048 / PAGE];
     __shared__ float wml[4][G][2];
@@ -669,13 +684,16 @@ paged_decode_mma_kernel(const bf16* __restrict__ q, long long q_stride, const bf
     uint8_t* ring = ring_raw + (size_t)warp * MMA_NST * 2 * MMA_PAGE;
     const int my_pages = warp < npages ? (npages - warp + 3) / 4 : 0;       // pages warp, warp + 4, ...
     auto issue = [&](int i) {                                               // i-th page of this warp
-        const int st = i % MMA_NST;
-        if (lane == 0) tc::mbar_expect_tx(&full[warp][st], 2 * PG * 2);
-        __syncwarp();
-        const int row = lane & 15, is_v = lane >> 4;
-        const size_t src = ((size_t)spage[warp + 4 * i] * n_kv + kvh) * PG + (size_t)row * HD;
-        bulk_g2s_dec(ring + (size_t)(st * 2 + is_v) * MMA_PAGE + row * MMA_PITCH, (is_v ? v_pages : k_pages) + src, HD * 2,
-                     &full[warp][st]);
+        if (lane == 0) {
+            const int st = i % MMA_NST;
+            uint8_t* dst = ring + (size_t)(st * 2) * MMA_PAGE;
+            const int row0 = (spage[warp + 4 * i] * n_kv + kvh) * PAGE;     // row of the [pages * heads * 16, 128] view
+            tc::mbar_expect_tx(&full[warp][st], 2 * MMA_PAGE);
+            tma_load_2d_dec(dst, &tmK, &full[warp][st], 0, row0);
+            tma_load_2d_dec(dst + MMA_HALF, &tmK, &full[warp][st], 64, row0);
+            tma_load_2d_dec(dst + MMA_PAGE, &tmV, &full[warp][st], 0, row0);
+            tma_load_2d_dec(dst + MMA_PAGE + MMA_HALF, &tmV, &full[warp][st], 64, row0);
+        }
     };
     for (int i = 0; i < MMA_NST && i < my_pages; ++i) issue(i);
 
@@ -692,9 +710,10 @@ paged_decode_mma_kernel(const bf16* __restrict__ q, long long q_stride, const bf
     for (int j = 0; j < 16; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
     float m = -INFINITY, l = 0.f;
     bool ok = true;
-    // ldmatrix lane addressing (byte offsets inside a staged page)
-    const uint32_t k_off = (uint32_t)(((lane & 7) + (lane >> 4) * 8) * MMA_PITCH + ((lane >> 3) & 1) * 16);
-    const uint32_t v_off = (uint32_t)(((lane & 7) + ((lane >> 3) & 1) * 8) * MMA_PITCH + (lane >> 4) * 16);
+    // ldmatrix lane addressing: K matrices are (tokens 0-7 | 8-15) x (k 0-7 | 8-15) of a 16-wide k step, V
+    // matrices (tokens 0-7 | 8-15) x (head dims 0-7 | 8-15) of a 16-wide column step
+    const int k_row = (lane & 7) + (lane >> 4) * 8, k_sub = (lane >> 3) & 1;
+    const int v_row = (lane & 7) + ((lane >> 3) & 1) * 8, v_sub = lane >> 4;
     for (int i = 0; i < my_pages; ++i) {
         const int st = i % MMA_NST;
         if (!tc::mbar_wait(&full[warp][st], (uint32_t)(i / MMA_NST) & 1u, &abort_flag)) {
@@ -706,7 +725,7 @@ paged_decode_mma_kernel(const bf16* __restrict__ q, long long q_stride, const bf
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
             uint32_t b00, b01, b10, b11;
-            ldsm_x4(kb + k_off + ks * 32, b00, b01, b10, b11);
+            ldsm_x4(kb + swz_off(k_row, ks * 2 + k_sub), b00, b01, b10, b11);
             mma_16816(s0, qa0[ks], qa2[ks], b00, b01);
             mma_16816(s1, qa0[ks], qa2[ks], b10, b11);
         }
@@ -728,7 +747,7 @@ paged_decode_mma_kernel(const bf16* __restrict__ q, long long q_stride, const bf
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             uint32_t b0, b1, b2, b3;
-            ldsm_x4_trans(vb + v_off + j * 32, b0, b1, b2, b3);
+            ldsm_x4_trans(vb + swz_off(v_row, j * 2 + v_sub), b0, b1, b2, b3);
             mma_16816(o[2 * j], pa0, pa2, b0, b1);
             mma_16816(o[2 * j + 1], pa0, pa2, b2, b3);
         }
@@ -800,16 +819,41 @@ KB_API int kb_decode_status() {
     return v;
 }
 
+typedef CUresult (*EncodeTiledFnDec)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                     const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                     CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+// pages [num_pages][n_kv][16][128] bf16 seen as rows of 128 elements; a box is half a (page, head) block
+static int make_page_tmap(CUtensorMap* m, const void* base, long long rows) {
+    static EncodeTiledFnDec enc = nullptr;
+    if (!enc) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            return 100;
+        enc = reinterpret_cast<EncodeTiledFnDec>(ptr);
+    }
+    cuuint64_t dims[2] = {128, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {256};
+    cuuint32_t box[2] = {64, PAGE};
+    cuuint32_t estr[2] = {1, 1};
+    const CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : 200 + (int)r;
+}
+
 // Which decode attention kernel kb_paged_decode launches: -1 = read KB_DECODE_KERNEL on the first call,
 // 0 phases, 1 stream, 2 bulk, 3 mma.  kb_set_decode_kernel lets one process compare them.
 static int g_decode_kernel = -1;
 KB_API void kb_set_decode_kernel(int which) { g_decode_kernel = which; }
 
 // Workspace sizes (floats) for B requests: part_o = B*n_kv*nsplit*G*hd, part_ml = B*n_kv*nsplit*G*2.
+// `num_pages`: pages in k_pages / v_pages (the tensor-core kernel addresses them through a tensor map).
 KB_API int kb_paged_decode(const void* q, long long q_stride, const void* k_pages, const void* v_pages,
                            const int* page_table, int max_pages, const int* ctx_lens, int B, int n_q, int n_kv, int hd,
                            int max_ctx, int split_tokens, float scale, float* part_o, float* part_ml, void* out,
-                           long long out_stride, cudaStream_t st) {
+                           long long out_stride, int num_pages, cudaStream_t st) {
     const int G = n_q / n_kv;
     if (n_q % n_kv || split_tokens % PAGE || split_tokens > 2048) return 5;
     const int nsplit = (max_ctx + split_tokens - 1) / split_tokens;
@@ -829,7 +873,7 @@ KB_API int kb_paged_decode(const void* q, long long q_stride, const void* k_page
         if (u && atoi(u) == 4) unroll = 4;
     }
 #define DEC(HD_, G_)                                                                                          \
-    if (streaming == 3 && (HD_) == 128) {                                                                      \
+    if (streaming == 3 && (HD_) == 128 && num_pages > 0) {                                                     \
         static bool mma_flags[64] = {};                                                                        \
         bool* attr = kb_device_flag(mma_flags);                                                                \
         if (!attr) return 7;                                                                                   \
@@ -838,8 +882,13 @@ KB_API int kb_paged_decode(const void* q, long long q_stride, const void* k_page
                                      MMA_SMEM) != cudaSuccess) return 7;                                       \
             *attr = true;                                                                                      \
         }                                                                                                      \
+        CUtensorMap tmK, tmV;                                                                                  \
+        const long long page_rows = (long long)num_pages * n_kv * PAGE;                                        \
+        int tr = make_page_tmap(&tmK, k_pages, page_rows);                                                     \
+        if (!tr) tr = make_page_tmap(&tmV, v_pages, page_rows);                                                \
+        if (tr) return tr;                                                                                     \
         paged_decode_mma_kernel<G_><<<grid, 128, MMA_SMEM, st>>>(                                              \
-            (const bf16*)q, q_stride, (const bf16*)k_pages, (const bf16*)v_pages, page_table, max_pages, ctx_lens, \
+            tmK, tmV, (const bf16*)q, q_stride, page_table, max_pages, ctx_lens,                               \
             n_kv, split_tokens, scale, part_o, part_ml, nsplit);                                               \
     } else if (streaming >= 2 && (HD_) == 128 && (G_) <= 4) {                                                         \
         static bool attr_flags[64] = {};                                                                       \
@@ -990,5 +1039,5 @@ KB_API int kb_paged_decode_noalloc(const void* q, long long q_stride, const void
         return KB_NOALLOC_TOO_LARGE;
     }
     return kb_paged_decode(q, q_stride, k_pages, v_pages, page_table, max_pages, ctx_lens, B, n_q, n_kv, hd, max_ctx,
-                           split_tokens, scale, scratch, scratch + ml_off, out, out_stride, stream);
+                           split_tokens, scale, scratch, scratch + ml_off, out, out_stride, /*num_pages=*/0, stream);
 }

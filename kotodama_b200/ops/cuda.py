@@ -617,7 +617,7 @@ class CudaOps(TorchOps):
         rc = self.lib.kb_paged_decode(_p(q), _LL(q.stride(0)), _p(k_pages), _p(v_pages), _p(page_table),
                                       _I(page_table.shape[1]), _p(ctx_lens), _I(B), _I(n_q), _I(n_kv), _I(hd),
                                       _I(max_ctx), _I(split), _F(1.0 / math.sqrt(hd)), _p(part_o), _p(part_ml),
-                                      _p(out), _LL(out.stride(0)), _st())
+                                      _p(out), _LL(out.stride(0)), _I(k_pages.shape[0]), _st())
         self._rc(rc, "kb_paged_decode")
         self.launches += 1
         return out

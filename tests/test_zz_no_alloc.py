@@ -60,7 +60,13 @@ def test_no_alloc_paged_decode_matches_regular_entry_point_twice():
     for seed, B, n_q, n_kv, hd, ctx_list in cases:
         q, k_pages, v_pages, table, ctx = _case(seed, B, n_q, n_kv, hd, ctx_list)
         max_ctx = max(ctx_list)
-        ref = ops.paged_decode_attention(q, k_pages, v_pages, table, ctx, max_ctx, n_q, n_kv, hd, split=256)
+        # the allocation-free entry point runs the bulk-copy kernel (it has no page count for a tensor map):
+        # take the reference from the same kernel, so that the comparison can be bit for bit
+        lib.kb_set_decode_kernel(ctypes.c_int(2))
+        try:
+            ref = ops.paged_decode_attention(q, k_pages, v_pages, table, ctx, max_ctx, n_q, n_kv, hd, split=256)
+        finally:
+            lib.kb_set_decode_kernel(ctypes.c_int(3))
         rc, out, allocs = _call_noalloc(lib, q, k_pages, v_pages, table, ctx, n_q, n_kv, hd, max_ctx, 256)
         torch.cuda.synchronize()
         assert rc == 0
