@@ -158,7 +158,7 @@ def run(a, rank: int, world: int, local: int) -> dict:
            "prefill_passes": eng.stats["prefill_passes"], "prefill_batch_tokens": a.prefill_batch_tokens}
     if tp is not None:
         out.update(native_allreduce_calls=tp.native_calls, library_allreduce_calls=tp.library_calls,
-                   multimem_allreduce_calls=tp.multimem_calls)
+                   multimem_allreduce_calls=tp.multimem_calls, fused_gemm_allreduce_calls=tp.fused_calls)
     if hasattr(eng.ops, "check_status"):
         eng.ops.check_status()
     if tp is not None:

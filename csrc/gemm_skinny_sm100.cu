@@ -45,6 +45,16 @@ struct SkinnyParams {
     const __nv_bfloat16* Cin;      // may be null, may alias C
     long long ldc, ldcin;
     int* status;
+    // all-reduce over tensor-parallel ranks fused into the epilogue (AR kernels only): every rank's summed
+    // tile rows are pushed into slot [parity][rank] of every rank's receive buffer, the last CTA raises this
+    // rank's flag on every peer, and every CTA then sums its rows over the ranks' slots (+ Cin) into C
+    void* ar_recv[8];              // peer receive buffers: [2 parities][world][ar_slot_elems] bf16
+    void* ar_flags[8];             // peer flag arrays: int [2 parities][8]
+    int ar_world, ar_rank;
+    long long ar_slot_elems;
+    int* ar_epoch;                 // device-side call counter (graph replay needs no host update)
+    unsigned* ar_counters;         // two zero-initialised counters: last-CTA elections
+    unsigned long long ar_limit_ns;
     int b_packed;                  // B is stored tile-major: [N / 128][K / 64][128 rows][64 columns], 16 KB contiguous per tile
     int a_rows;                    // rows of A that TMA fetches per K block (M rounded up to 8): the rest of the 128-row
                                    // operand tile is left as it is - its products land in rows that nobody reads
@@ -83,7 +93,28 @@ __device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* m, uin
         : "memory");
 }
 
-template <int BN, int AM>
+__device__ __forceinline__ void st_release_sys_i32(int* p, int v) {
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_sys_i32(const int* p) {
+    int v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+// bounded wait for flag >= epoch (false on timeout)
+__device__ __forceinline__ bool wait_flag_sk(const int* flag, int epoch, unsigned long long limit_ns) {
+    if (ld_acquire_sys_i32(flag) >= epoch) return true;
+    const uint64_t t0 = global_timer_ns();
+    unsigned sleep_ns = 64;
+    while (ld_acquire_sys_i32(flag) < epoch) {
+        if (global_timer_ns() - t0 > limit_ns) return false;
+        __nanosleep(sleep_ns);
+        if (sleep_ns < 1024) sleep_ns <<= 1;
+    }
+    return true;
+}
+
+template <int BN, int AM, bool AR>
 __global__ void __launch_bounds__(192, 1)
 gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const SkinnyParams p) {
     using C_ = Cfg<BN, AM>;
@@ -212,43 +243,129 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     // every CTA's partial tile is in its shared memory
     __syncthreads();
     cluster_sync_all();
-    if (warp >= 2) {
-        // ---- reduction over the cluster: this CTA owns rows r, r + S, ...; a row is BN / 4 float4
-        constexpr int V4 = BN / 4;                                   // float4 per row
-        constexpr int ROWS_PER_PASS = 128 / V4;                      // 2 (BN 256) or 4 (BN 128)
-        const int t = threadIdx.x - 64;
-        const int c4 = t % V4, sub = t / V4;
-        const int col = tn * BN + c4 * 4;
-        const uint32_t base = smem_u32(smem);
-        for (int i = sub; ; i += ROWS_PER_PASS) {
-            const int row = r + i * S;
-            if (row >= p.M) break;
-            if (col >= p.N) continue;
-            const uint32_t off = base + (uint32_t)row * PITCH + (uint32_t)c4 * 16;
-            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-            for (int q = 0; q < S; ++q) {
-                const float4 v = ld_dsmem_f4(mapa(off, (uint32_t)q));
-                acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
-            }
-            float o[4] = {p.alpha * acc.x, p.alpha * acc.y, p.alpha * acc.z, p.alpha * acc.w};
-            const int ncols = min(4, p.N - col);
-            __nv_bfloat16* dst = p.C + (long long)row * p.ldc + col;
-            const __nv_bfloat16* cin = p.Cin ? p.Cin + (long long)row * p.ldcin + col : nullptr;
-            if (ncols == 4 && ((p.ldc | p.ldcin | col) & 3) == 0) {
-                if (cin) {
-                    const uint2 raw = *reinterpret_cast<const uint2*>(cin);
-                    const __nv_bfloat162* c2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
-                    const float2 c01 = __bfloat1622float2(c2[0]), c23 = __bfloat1622float2(c2[1]);
-                    o[0] += p.beta * c01.x; o[1] += p.beta * c01.y; o[2] += p.beta * c23.x; o[3] += p.beta * c23.y;
+    // ---- reduction over the cluster: this CTA owns rows r, r + S, ...; a thread takes 8 columns of a row
+    constexpr int V8 = BN / 8;                                   // threads per row
+    constexpr int ROWS_PER_PASS = 128 / V8;                      // 4 (BN 256) or 8 (BN 128)
+    const int t = threadIdx.x - 64;
+    const int c8 = t % V8, sub = t / V8;
+    const int col = tn * BN + c8 * 8;
+    const uint32_t sbase = smem_u32(smem);
+    auto cluster_sum8 = [&](int row, float* acc) {
+        const uint32_t off = sbase + (uint32_t)row * PITCH + (uint32_t)c8 * 32;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+        for (int q = 0; q < S; ++q) {
+            const uint32_t a = mapa(off, (uint32_t)q);
+            const float4 v0 = ld_dsmem_f4(a), v1 = ld_dsmem_f4(a + 16);
+            acc[0] += v0.x; acc[1] += v0.y; acc[2] += v0.z; acc[3] += v0.w;
+            acc[4] += v1.x; acc[5] += v1.y; acc[6] += v1.z; acc[7] += v1.w;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] *= p.alpha;
+    };
+    const bool vec_ok = ((p.ldc | p.ldcin) & 7) == 0 && col + 8 <= p.N;
+    if (!AR) {
+        if (warp >= 2) {
+            for (int i = sub;; i += ROWS_PER_PASS) {
+                const int row = r + i * S;
+                if (row >= p.M) break;
+                if (col >= p.N) continue;
+                float o[8];
+                cluster_sum8(row, o);
+                __nv_bfloat16* dst = p.C + (long long)row * p.ldc + col;
+                const __nv_bfloat16* cin = p.Cin ? p.Cin + (long long)row * p.ldcin + col : nullptr;
+                if (vec_ok) {
+                    if (cin) {
+                        float ci[8];
+                        unpack8(ld8(cin), ci);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) o[j] += p.beta * ci[j];
+                    }
+                    st8(dst, pack8(o));
+                } else {
+                    const int ncols = min(8, p.N - col);
+                    for (int j = 0; j < ncols; ++j)
+                        dst[j] = __float2bfloat16(o[j] + (cin ? p.beta * __bfloat162float(cin[j]) : 0.f));
                 }
-                uint2 out;
-                __nv_bfloat162 lo = __floats2bfloat162_rn(o[0], o[1]), hi = __floats2bfloat162_rn(o[2], o[3]);
-                out.x = *reinterpret_cast<uint32_t*>(&lo);
-                out.y = *reinterpret_cast<uint32_t*>(&hi);
-                *reinterpret_cast<uint2*>(dst) = out;
-            } else {
-                for (int j = 0; j < ncols; ++j)
-                    dst[j] = __float2bfloat16(o[j] + (cin ? p.beta * __bfloat162float(cin[j]) : 0.f));
+            }
+        }
+    } else {
+        // ---- fused all-reduce (N is a multiple of 8 and C / Cin are dense [M, N]: checked by the launcher)
+        __shared__ int s_last, s_ok;
+        const int epoch = *reinterpret_cast<volatile int*>(p.ar_epoch) + 1;
+        const int par = epoch & 1;
+        const int W = p.ar_world;
+        const long long my_slot = ((long long)par * W + p.ar_rank) * p.ar_slot_elems;
+        if (threadIdx.x == 0) s_ok = 1;
+        if (warp >= 2) {
+            for (int i = sub;; i += ROWS_PER_PASS) {
+                const int row = r + i * S;
+                if (row >= p.M) break;
+                if (col >= p.N) continue;
+                float o[8];
+                cluster_sum8(row, o);
+                const bf16x8 v = pack8(o);
+                const long long at = my_slot + (long long)row * p.N + col;
+#pragma unroll
+                for (int q = 0; q < 8; ++q)
+                    if (q < W) st8(reinterpret_cast<__nv_bfloat16*>(p.ar_recv[q]) + at, v);
+            }
+        }
+        // this rank's flag goes up on every peer once all of its CTAs have pushed
+        __threadfence_system();
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            const unsigned total = gridDim.x * gridDim.y;
+            const unsigned prev = atomicAdd(p.ar_counters, 1u);
+            s_last = prev == total - 1;
+            if (s_last) *p.ar_counters = 0;
+        }
+        __syncthreads();
+        if (s_last && threadIdx.x < W) {
+            __threadfence_system();
+            st_release_sys_i32(reinterpret_cast<int*>(p.ar_flags[threadIdx.x]) + par * 8 + p.ar_rank, epoch);
+        }
+        if (threadIdx.x < W) {
+            if (!wait_flag_sk(reinterpret_cast<const int*>(p.ar_flags[p.ar_rank]) + par * 8 + threadIdx.x, epoch, p.ar_limit_ns)) {
+                atomicMax(p.status, (int)KB_TIMEOUT_PEER);
+                s_ok = 0;
+            }
+        }
+        __syncthreads();
+        if (warp >= 2 && s_ok) {
+            const __nv_bfloat16* mine = reinterpret_cast<const __nv_bfloat16*>(p.ar_recv[p.ar_rank]) + (long long)par * W * p.ar_slot_elems;
+            for (int i = sub;; i += ROWS_PER_PASS) {
+                const int row = r + i * S;
+                if (row >= p.M) break;
+                if (col >= p.N) continue;
+                const long long at = (long long)row * p.N + col;
+                float acc[8];
+                if (p.Cin) {
+                    unpack8(ld8(p.Cin + at), acc);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) acc[j] *= p.beta;
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+                }
+                for (int q = 0; q < W; ++q) {                      // rank order: bitwise identical on every rank
+                    float tq[8];
+                    const uint4 raw = __ldcg(reinterpret_cast<const uint4*>(mine + q * p.ar_slot_elems + at));
+                    unpack8(*reinterpret_cast<const bf16x8*>(&raw), tq);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) acc[j] += tq[j];
+                }
+                st8(p.C + at, pack8(acc));
+            }
+        }
+        // the last CTA to get here advances the call counter
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            const unsigned total = gridDim.x * gridDim.y;
+            const unsigned prev = atomicAdd(p.ar_counters + 1, 1u);
+            if (prev == total - 1) {
+                p.ar_counters[1] = 0;
+                *p.ar_epoch = epoch;
             }
         }
     }
@@ -302,13 +419,13 @@ int make_tmap_packed(CUtensorMap* m, const void* base, long long n_tiles, long l
     return r == CUDA_SUCCESS ? 0 : 200 + (int)r;
 }
 
-template <int BN, int AM>
+template <int BN, int AM, bool AR>
 int launch_skinny(const CUtensorMap& tmA, const CUtensorMap& tmB, const SkinnyParams& p, int tiles, int S, cudaStream_t st) {
     static bool attr_flags[64] = {};
     bool* attr = kb_device_flag(attr_flags);
     if (!attr) return 7;
     if (!*attr) {
-        if (cudaFuncSetAttribute(gemm_skinny_kernel<BN, AM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        if (cudaFuncSetAttribute(gemm_skinny_kernel<BN, AM, AR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  Cfg<BN, AM>::SMEM) != cudaSuccess)
             return 7;
         *attr = true;
@@ -326,7 +443,16 @@ int launch_skinny(const CUtensorMap& tmA, const CUtensorMap& tmB, const SkinnyPa
     at[0].val.clusterDim.z = 1;
     cfg.attrs = at;
     cfg.numAttrs = 1;
-    const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_skinny_kernel<BN, AM>, tmA, tmB, p);
+    if (AR) {
+        // every CTA waits for flags that go up only after all CTAs of every rank have pushed: the whole
+        // grid must be resident at once
+        int clusters = 0;
+        if (cudaOccupancyMaxActiveClusters(&clusters, gemm_skinny_kernel<BN, AM, AR>, &cfg) != cudaSuccess || clusters < tiles) {
+            cudaGetLastError();
+            return KB_LAUNCH_FAILED;
+        }
+    }
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_skinny_kernel<BN, AM, AR>, tmA, tmB, p);
     if (e != cudaSuccess) {
         cudaGetLastError();
         return KB_LAUNCH_FAILED;
@@ -334,20 +460,21 @@ int launch_skinny(const CUtensorMap& tmA, const CUtensorMap& tmB, const SkinnyPa
     return 0;
 }
 
-}  // namespace
 
-// C[M,N] = alpha * A[M,K] x B[N,K]^T + beta * Cin, all bf16, K contiguous in A and B (lda/ldb in
-// elements, multiples of 8; 16-byte aligned bases), M <= 128.  `split` <= 0: chosen here (BN and the
-// cluster size that put the most CTAs on the weight stream); otherwise the cluster size to use (1..8).
-// Returns 0, a refusal code, or KB_LAUNCH_FAILED when the runtime cannot place the cluster.
-// `b_packed` != 0: B points at the tile-major copy made by kb_pack_weight_tiles ([ceil(N/128)][K/64][128][64],
-// K a multiple of 64); every TMA box is then whole contiguous 16 KB tiles instead of 128-byte pieces 2K
-// bytes apart.  Measured on the 3B decode shapes this is worth 3 % (the kernel is bound by the ~70 GB/s
-// one SM can take in and by its fixed ~6 us of launch, prologue and cluster reduction, not by DRAM
-// locality), so the serving engine does not make the copies unless asked to.
-KB_API int kb_gemm_skinny(const void* A, const void* B, void* C, const void* Cin, int M, int N, int K, long long lda,
-                          long long ldb, long long ldc, long long ldcin, float alpha, float beta, int split, int bn,
-                          int b_packed, int* status, cudaStream_t st) {
+
+struct ArArgs {
+    void* const* recv;
+    void* const* flags;
+    int world, rank;
+    long long slot_elems;
+    int* epoch;
+    unsigned* counters;
+    double limit_s;
+};
+
+static int skinny_dispatch(const void* A, const void* B, void* C, const void* Cin, int M, int N, int K, long long lda,
+                           long long ldb, long long ldc, long long ldcin, float alpha, float beta, int split, int bn,
+                           int b_packed, int* status, const ArArgs* ar, cudaStream_t st) {
     if (M <= 0 || M > BM || N <= 0 || K <= 0) return 5;
     if ((lda & 7) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15)) return 6;
     if (b_packed ? (K % BK) != 0 : (ldb & 7) != 0) return 6;
@@ -374,6 +501,7 @@ KB_API int kb_gemm_skinny(const void* A, const void* B, void* C, const void* Cin
         if (tiles * s > best_ctas) { best_ctas = tiles * s; best_bn = cand; best_s = s; }
     }
     const int tiles = (N + best_bn - 1) / best_bn;
+    if (ar && tiles * best_s > sms) return KB_LAUNCH_FAILED;      // the fused all-reduce needs the whole grid resident
     CUtensorMap tmA, tmB;
     const int a_rows = ((M + 7) / 8) * 8;
     int r = make_tmap_sk(&tmA, A, K, M, lda, BK, a_rows);
@@ -387,11 +515,63 @@ KB_API int kb_gemm_skinny(const void* A, const void* B, void* C, const void* Cin
     p.C = (__nv_bfloat16*)C; p.Cin = (const __nv_bfloat16*)Cin; p.ldc = ldc; p.ldcin = ldcin; p.status = status;
     p.a_rows = a_rows;
     p.b_packed = b_packed;
+    if (ar) {
+        for (int i = 0; i < 8; ++i) {
+            p.ar_recv[i] = i < ar->world ? ar->recv[i] : nullptr;
+            p.ar_flags[i] = i < ar->world ? ar->flags[i] : nullptr;
+        }
+        p.ar_world = ar->world; p.ar_rank = ar->rank; p.ar_slot_elems = ar->slot_elems;
+        p.ar_epoch = ar->epoch; p.ar_counters = ar->counters;
+        p.ar_limit_ns = (unsigned long long)(ar->limit_s * 1e9);
+        if (M <= 64)
+            return best_bn == 256 ? launch_skinny<256, 64, true>(tmA, tmB, p, tiles, best_s, st)
+                                  : launch_skinny<128, 64, true>(tmA, tmB, p, tiles, best_s, st);
+        return best_bn == 256 ? launch_skinny<256, 128, true>(tmA, tmB, p, tiles, best_s, st)
+                              : launch_skinny<128, 128, true>(tmA, tmB, p, tiles, best_s, st);
+    }
     if (M <= 64)
-        return best_bn == 256 ? launch_skinny<256, 64>(tmA, tmB, p, tiles, best_s, st)
-                              : launch_skinny<128, 64>(tmA, tmB, p, tiles, best_s, st);
-    return best_bn == 256 ? launch_skinny<256, 128>(tmA, tmB, p, tiles, best_s, st)
-                          : launch_skinny<128, 128>(tmA, tmB, p, tiles, best_s, st);
+        return best_bn == 256 ? launch_skinny<256, 64, false>(tmA, tmB, p, tiles, best_s, st)
+                              : launch_skinny<128, 64, false>(tmA, tmB, p, tiles, best_s, st);
+    return best_bn == 256 ? launch_skinny<256, 128, false>(tmA, tmB, p, tiles, best_s, st)
+                          : launch_skinny<128, 128, false>(tmA, tmB, p, tiles, best_s, st);
+}
+
+}  // namespace
+
+// C[M,N] = alpha * A[M,K] x B[N,K]^T + beta * Cin, all bf16, K contiguous in A and B (lda/ldb in
+// elements, multiples of 8; 16-byte aligned bases), M <= 128.  `split` <= 0: chosen here (BN and the
+// cluster size that put the most CTAs on the weight stream); otherwise the cluster size to use (1..8).
+// Returns 0, a refusal code, or KB_LAUNCH_FAILED when the runtime cannot place the cluster.
+// `b_packed` != 0: B points at the tile-major copy made by kb_pack_weight_tiles ([ceil(N/128)][K/64][128][64],
+// K a multiple of 64); every TMA box is then whole contiguous 16 KB tiles instead of 128-byte pieces 2K
+// bytes apart.  Measured on the 3B decode shapes this is worth 3 % (the kernel is bound by the ~70 GB/s
+// one SM can take in and by its fixed ~6 us of launch, prologue and cluster reduction, not by DRAM
+// locality), so the serving engine does not make the copies unless asked to.
+KB_API int kb_gemm_skinny(const void* A, const void* B, void* C, const void* Cin, int M, int N, int K, long long lda,
+                          long long ldb, long long ldc, long long ldcin, float alpha, float beta, int split, int bn,
+                          int b_packed, int* status, cudaStream_t st) {
+    return skinny_dispatch(A, B, C, Cin, M, N, K, lda, ldb, ldc, ldcin, alpha, beta, split, bn, b_packed, status, nullptr, st);
+}
+
+// Row-parallel projection of tensor-parallel decode in ONE launch: out = sum over ranks of (A_r x B_r^T) + residual.
+// The product is the cluster split-K above; its epilogue pushes the summed tile rows into every rank's
+// receive buffer (plain peer stores), raises this rank's epoch flag on every peer and sums all ranks' slots.
+// Buffers, flags, the device-side call counter and the two election counters are those of
+// kb_allreduce_push (same layout, same protocol), so both entry points can share them.  out and residual
+// are dense [M, N] bf16, N a multiple of 8, M * N <= slot_elems.  KB_LAUNCH_FAILED: the grid cannot be fully
+// resident (the caller then runs the product and the all-reduce as two launches).
+KB_API int kb_gemm_skinny_allreduce(const void* A, const void* B, void* out, const void* residual, int M, int N, int K,
+                                    long long lda, long long ldb, int b_packed, void* const* peer_recv,
+                                    void* const* peer_flags, int world, int rank, long long slot_elems, int* epoch_ptr,
+                                    unsigned* counters, double limit_s, int* status, cudaStream_t st) {
+    if (world < 1 || world > 8 || rank < 0 || rank >= world || (N & 7) || (slot_elems & 7) ||
+        (long long)M * N > slot_elems || !epoch_ptr || !counters)
+        return 5;
+    for (int i = 0; i < world; ++i)
+        if (!peer_recv[i] || !peer_flags[i] || ((uintptr_t)peer_recv[i] & 15)) return 6;
+    if (((uintptr_t)out & 15) || ((uintptr_t)residual & 15)) return 6;
+    ArArgs ar{peer_recv, peer_flags, world, rank, slot_elems, epoch_ptr, counters, limit_s};
+    return skinny_dispatch(A, B, out, residual, M, N, K, lda, ldb, N, N, 1.0f, 1.0f, 0, 0, b_packed, status, &ar, st);
 }
 
 // Tile-major copy of a K-major bf16 weight for kb_gemm_skinny: dst[nt][kt][r][c] = w[nt * 128 + r][kt * 64 + c]

@@ -49,6 +49,8 @@ class ServeTP:
         if multimem is None and os.environ.get("KOTODAMA_SERVE_MULTIMEM", "0") != "1":
             multimem = False
         self.multimem = multimem
+        self.fused_gemm = os.environ.get("KOTODAMA_SERVE_FUSED_AR", "1") == "1"   # GEMM + all-reduce in one launch (decode)
+        self.fused_calls = 0
         self.native_calls = 0
         self.multimem_calls = 0
         self.library_calls = 0
@@ -143,8 +145,42 @@ class ServeTP:
         dist.broadcast(t, src=dist.get_global_rank(self.group, 0), group=self.group)
         return t.tolist()
 
-    def row_linear(self, ops: Any, x: torch.Tensor, w: torch.Tensor, residual: Optional[torch.Tensor]) -> torch.Tensor:
+    def row_linear(self, ops: Any, x: torch.Tensor, w: Any, residual: Optional[torch.Tensor]) -> torch.Tensor:
+        """Row-parallel projection + all-reduce (+ residual).  Decode-size inputs on CUDA take one launch: the
+        cluster split-K product whose epilogue pushes the tile rows to every rank and sums all ranks' slots
+        (``kb_gemm_skinny_allreduce``); everything else is the product followed by ``all_reduce``."""
+        wt = getattr(w, "w", w)
+        use_native = self.native if self.native is not None else x.is_cuda
+        if (self.fused_gemm and use_native and x.is_cuda and isinstance(wt, torch.Tensor) and x.dtype == torch.bfloat16
+                and wt.dtype == torch.bfloat16 and x.dim() == 2 and x.shape[0] <= 128 and wt.shape[0] % 8 == 0
+                and wt.shape[1] >= 512 and x.stride(-1) == 1 and x.stride(0) % 8 == 0 and wt.is_contiguous()
+                and getattr(ops, "skinny_cluster", False) and not self.mc_ptr_requested()
+                and (residual is None or residual.is_contiguous())):
+            if not self._ready:
+                self._setup(x.device, wt.shape[0], ops)
+            M, K = x.shape
+            N = wt.shape[0]
+            if M * N <= self.slot_elems and not self.mc_ptr:
+                out = torch.empty(M, N, device=x.device, dtype=torch.bfloat16)
+                packed = getattr(w, "packed", None)
+                rc = self.lib.kb_gemm_skinny_allreduce(
+                    _VP(x.data_ptr()), _VP((packed if packed is not None else wt).data_ptr()), _VP(out.data_ptr()),
+                    _VP(residual.data_ptr() if residual is not None else None), _I(M), _I(N), _I(K), _LL(x.stride(0)),
+                    _LL(K), _I(int(packed is not None)), self.recv_ptrs, self.flag_ptrs, _I(self.size), _I(self.rank),
+                    _LL(self.slot_elems), _VP(self.epoch.data_ptr()), _VP(self.counters.data_ptr()), _D(self.WAIT_LIMIT_S),
+                    _VP(ops.status(x.device).data_ptr()), _VP(torch.cuda.current_stream().cuda_stream))
+                if rc == 0:
+                    ops.launches += 1
+                    self.native_calls += 1
+                    self.fused_calls += 1
+                    return out
+                if rc != 9:
+                    raise RuntimeError(f"kb_gemm_skinny_allreduce: launcher returned {rc}")
+                self.fused_gemm = False              # the grid cannot be resident at once on this device: two launches
         return self.all_reduce(ops, ops.gemm_nt(x, w), residual)
+
+    def mc_ptr_requested(self) -> bool:
+        return self.multimem is True
 
 
 # ---------------------------------------------------------------------------- lock-step driving

@@ -66,6 +66,7 @@ def test_tensor_parallel_serving_native_allreduce(tmp_path, nproc):
         assert r["allreduce_max_err"] == 0.0                     # push kernel: one rounding, exact
         assert r["multimem_rel_err"] <= 2.0 ** -7                # in-switch sum (if used): at most one bf16 ulp apart
         assert (r["multimem_calls"] == 5) == r["has_multicast"]  # used exactly when the buffers have a multicast mapping
+        assert r["fused_gemm_calls"] == 4 and r["fused_gemm_rel_err"] < 1e-2     # product + all-reduce in one launch
         assert all(len(t) == 6 for t in r["tp"])
     # bf16: sharded sums round differently, so tokens may part at a near-tie; the logits may not
     assert res[0]["logit_rel_err_max"] < 4e-2 and res[0]["flips_ok"] and res[0]["logits_compared"] >= 10, res[0]
