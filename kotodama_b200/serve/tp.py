@@ -153,7 +153,7 @@ class ServeTP:
         use_native = self.native if self.native is not None else x.is_cuda
         if (self.fused_gemm and use_native and x.is_cuda and isinstance(wt, torch.Tensor) and x.dtype == torch.bfloat16
                 and wt.dtype == torch.bfloat16 and x.dim() == 2 and x.shape[0] <= 128 and wt.shape[0] % 8 == 0
-                and wt.shape[1] >= 512 and x.stride(-1) == 1 and x.stride(0) % 8 == 0 and wt.is_contiguous()
+                and wt.shape[1] >= 256 and x.stride(-1) == 1 and x.stride(0) % 8 == 0 and wt.is_contiguous()
                 and getattr(ops, "skinny_cluster", False) and not self.mc_ptr_requested()
                 and (residual is None or residual.is_contiguous())):
             if not self._ready:

@@ -218,21 +218,22 @@ def main():
             push_err = worst()
             tp.mc_ptr = saved
             # the row-parallel projection in one launch (cluster split-K product with the all-reduce in its epilogue)
-            gk = torch.Generator(device="cuda").manual_seed(20 + rank)
-            xk = (torch.randn(48, 1024, device="cuda", generator=gk) * 0.1).to(torch.bfloat16)
-            wk = (torch.randn(1536, 1024, device="cuda", generator=gk) * 0.1).to(torch.bfloat16)
-            rk = torch.randn(48, 1536, device="cuda", generator=torch.Generator(device="cuda").manual_seed(6)).to(torch.bfloat16)
-            part = (xk.float() @ wk.float().t()).to(torch.bfloat16)
-            parts_k = [torch.empty_like(part) for _ in range(world)]
-            dist.all_gather(parts_k, part)
-            want = sum(t.float() for t in parts_k) + rk.float()
             saved_mc, tp.mc_ptr = tp.mc_ptr, 0
             f0 = tp.fused_calls
             errs_k = []
-            for _ in range(4):                       # both parities, interleaved with the plain all-reduce
-                got = tp.row_linear(eng.ops, xk, wk, rk)
-                errs_k.append(float((got.float() - want).norm() / want.norm()))
-                tp.all_reduce(eng.ops, y, res)
+            for (Kk, Nk) in ((1024, 1536), (384, 3072)):          # the second: a shard as thin as 3072 / 8
+                gk = torch.Generator(device="cuda").manual_seed(20 + rank)
+                xk = (torch.randn(48, Kk, device="cuda", generator=gk) * 0.1).to(torch.bfloat16)
+                wk = (torch.randn(Nk, Kk, device="cuda", generator=gk) * 0.1).to(torch.bfloat16)
+                rk = torch.randn(48, Nk, device="cuda", generator=torch.Generator(device="cuda").manual_seed(6)).to(torch.bfloat16)
+                part = (xk.float() @ wk.float().t()).to(torch.bfloat16)
+                parts_k = [torch.empty_like(part) for _ in range(world)]
+                dist.all_gather(parts_k, part)
+                want = sum(t.float() for t in parts_k) + rk.float()
+                for _ in range(2):                   # both parities, interleaved with the plain all-reduce
+                    got = tp.row_linear(eng.ops, xk, wk, rk)
+                    errs_k.append(float((got.float() - want).norm() / want.norm()))
+                    tp.all_reduce(eng.ops, y, res)
             tp.mc_ptr = saved_mc
             eng.ops.check_status()
             result.update(fused_gemm_calls=tp.fused_calls - f0, fused_gemm_rel_err=max(errs_k))
