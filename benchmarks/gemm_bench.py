@@ -102,6 +102,63 @@ def fp8_table(ops, args, flush) -> None:
     ops.check_status()
 
 
+def decode_table(ops, args) -> None:
+    """The four projections of a decode step (M = --decode-rows) for every layer of the preset, timed inside a
+    CUDA graph (distinct weights per layer, so every product streams its weight from memory): the cluster
+    split-K kernel, split-K with fp32 atomics + finishing kernel, and cuBLAS (torch.addmm)."""
+    from kotodama_b200.config import MODEL_PRESETS
+    c = MODEL_PRESETS[args.model]
+    D, F, L = c["hidden_size"], c["intermediate_size"], c["num_layers"]
+    QKV = (c["num_attention_heads"] + 2 * c["num_kv_heads"]) * c["head_dim"]
+    shapes = [(QKV, D), (D, c["num_attention_heads"] * c["head_dim"]), (2 * F, D), (D, F)]
+    M = args.decode_rows
+    g = torch.Generator(device="cuda").manual_seed(0)
+    r = lambda *s_: (torch.randn(*s_, device="cuda", generator=g) * 0.05).to(torch.bfloat16)
+    ws = [[r(N, K) for (N, K) in shapes] for _ in range(L)]
+    acts = {K: r(M, K) for (_, K) in shapes}
+    res = {N: r(M, N) for (N, _) in shapes}
+
+    def mine():
+        for l in range(L):
+            for i, (N, K) in enumerate(shapes):
+                ops.gemm_nt(acts[K], ws[l][i], residual=res[N])
+
+    def lib():
+        for l in range(L):
+            for i, (N, K) in enumerate(shapes):
+                torch.addmm(res[N], acts[K], ws[l][i].t())
+
+    def graph_ms(fn):
+        fn()
+        torch.cuda.synchronize()
+        gr = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gr):
+            fn()
+        for _ in range(3):
+            gr.replay()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(max(args.iters, 1)):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            gr.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        ts.sort()
+        return ts[len(ts) // 2]
+    by = sum(N * K * 2 for N, K in shapes) * L
+    arms = [("cluster split-K (DSMEM)", True, mine), ("split-K atomics + finish", False, mine), ("cuBLAS addmm", None, lib)]
+    for name, cluster, fn in arms:
+        if cluster is not None:
+            ops.skinny_cluster = cluster
+        ms = graph_ms(fn)
+        print(json.dumps({"arm": name, "rows": M, "products": 4 * L, "ms_per_step": round(ms, 3),
+                          "weight_TBs": round(by / ms / 1e9, 2), "ideal_ms": round(by / 6451.8e6, 3)}))
+    ops.skinny_cluster = True
+    ops.check_status()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--single", nargs=4, default=None, metavar=("M", "N", "K", "MODE"))
@@ -111,6 +168,8 @@ def main() -> None:
     ap.add_argument("--out", default="")
     ap.add_argument("--two-cta", type=int, default=-1, help="force the CTA-pair kernel on (1) or off (0)")
     ap.add_argument("--fp8", action="store_true", help="block-scaled e4m3 GEMM (quantisation timed separately)")
+    ap.add_argument("--decode", action="store_true", help="decode-size products of every layer inside a CUDA graph")
+    ap.add_argument("--decode-rows", type=int, default=64)
     args = ap.parse_args()
     ops = get_ops("cuda")
     if args.two_cta >= 0:
@@ -118,6 +177,9 @@ def main() -> None:
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
     if args.fp8:
         fp8_table(ops, args, flush)
+        return
+    if args.decode:
+        decode_table(ops, args)
         return
     if args.single:
         M, N, K = map(int, args.single[:3])
