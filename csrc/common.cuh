@@ -6,6 +6,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <string.h>
 
 #define KB_API extern "C" __attribute__((visibility("default")))
 
@@ -23,6 +24,37 @@ static inline bool* kb_device_flag(bool* flags) {
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
     return flags + dev;
+}
+
+// ---- programmatic dependent launch (overlap of a kernel's launch and prologue with its predecessor's tail)
+// A kernel launched through kb_launch_dep() may start as soon as every CTA of the kernel before it on the
+// stream has executed kb_dep_trigger() (or exited); it must execute kb_dep_wait() before it reads anything
+// an earlier kernel wrote and before it writes anything an earlier kernel may still read.  The wait returns
+// once the predecessor has completed and its writes are visible; in a kernel launched the ordinary way both
+// instructions do nothing.  Every thread of such a kernel executes the wait (before any early return), so
+// that "this grid has completed" keeps implying "everything before it has completed".
+__device__ __forceinline__ void kb_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void kb_dep_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+// Process-wide switch (kb_set_dependent_launch; defined in elementwise.cu): 0 = ordinary launches everywhere.
+extern int g_kb_dependent_launch;
+template <typename... KArgs, typename... Args>
+static inline int kb_launch_dep(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = g_kb_dependent_launch ? 1 : 0;
+    if (cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...) != cudaSuccess) {
+        cudaGetLastError();
+        return KB_LAUNCH_FAILED;
+    }
+    return 0;
 }
 
 struct __align__(16) bf16x8 {

@@ -11,6 +11,15 @@
 
 typedef __nv_bfloat16 bf16;
 
+// Switch of the dependent launches (common.cuh: kb_launch_dep).  The serving engine turns it on around its
+// decode steps, whose ~320 launches of a few microseconds each otherwise pay a launch gap apiece.
+int g_kb_dependent_launch = 0;
+KB_API int kb_set_dependent_launch(int on) {
+    const int was = g_kb_dependent_launch;
+    g_kb_dependent_launch = on ? 1 : 0;
+    return was;
+}
+
 static inline int kb_num_sms() {
     static int n = 0;
     if (n == 0) {
@@ -405,6 +414,8 @@ qknorm_rope_fwd_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ qw
                        float* __restrict__ rstd_o, int N, int T, int nq, int nkv, int pos_offset, float eps,
                        const int* __restrict__ positions) {
     constexpr int LPH = HD / 16, HPW = 32 / LPH;
+    kb_dep_trigger();
+    kb_dep_wait();
     const int nh = nq + nkv;
     const int lane = threadIdx.x & 31, sub = lane % LPH, hsel = lane / LPH, e0 = sub * 8;
     const int in_stride = (nq + 2 * nkv) * HD, out_stride = nh * HD;
@@ -601,13 +612,12 @@ KB_API int kb_qknorm_rope_fwd(const void* qkv, const void* qw, const void* kw, c
     if (blocks > kb_num_sms() * 8) blocks = kb_num_sms() * 8;
     if (blocks < 1) blocks = 1;
     const bool norm = qw != nullptr;
-#define QK_FWD(E, NORM) qknorm_rope_fwd_kernel<E, NORM><<<(int)blocks, 256, 0, st>>>( \
+#define QK_FWD(E, NORM) kb_launch_dep(qknorm_rope_fwd_kernel<E, NORM>, dim3((unsigned)blocks), dim3(256), 0, st, \
         (const bf16*)qkv, (const bf16*)qw, (const bf16*)kw, cosT, sinT, (bf16*)out, rstd, N, T, nq, nkv, pos_offset, eps, \
         positions)
-    if (hd == 128) { if (norm) QK_FWD(128, true); else QK_FWD(128, false); }
-    else if (hd == 64) { if (norm) QK_FWD(64, true); else QK_FWD(64, false); }
-    else return 5;
-    return kb_launch_status();
+    if (hd == 128) return norm ? QK_FWD(128, true) : QK_FWD(128, false);
+    if (hd == 64) return norm ? QK_FWD(64, true) : QK_FWD(64, false);
+    return 5;
 }
 
 KB_API int kb_qknorm_rope_bwd(const void* dqk, const void* qkv, const void* qw, const void* kw, const float* cosT,
@@ -626,6 +636,8 @@ KB_API int kb_qknorm_rope_bwd(const void* dqk, const void* qkv, const void* qw, 
 
 // ============================================================================ SwiGLU
 __global__ void swiglu_fwd_kernel(const bf16* __restrict__ gu, bf16* __restrict__ act, long long N, int F) {
+    kb_dep_trigger();
+    kb_dep_wait();
     const int fc = F >> 3;
     const long long total = N * fc;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
@@ -669,8 +681,7 @@ static inline int ew_grid(long long work, int threads) {
 }
 KB_API int kb_swiglu_fwd(const void* gu, void* act, long long N, int F, cudaStream_t st) {
     if (F % 8) return 5;
-    swiglu_fwd_kernel<<<ew_grid(N * (F / 8), 256), 256, 0, st>>>((const bf16*)gu, (bf16*)act, N, F);
-    return kb_launch_status();
+    return kb_launch_dep(swiglu_fwd_kernel, dim3(ew_grid(N * (F / 8), 256)), dim3(256), 0, st, (const bf16*)gu, (bf16*)act, N, F);
 }
 KB_API int kb_swiglu_bwd(const void* gu, const void* dact, void* dgu, long long N, int F, cudaStream_t st) {
     if (F % 8) return 5;

@@ -55,6 +55,8 @@ struct SkinnyParams {
     int* ar_epoch;                 // device-side call counter (graph replay needs no host update)
     unsigned* ar_counters;         // two zero-initialised counters: last-CTA elections
     unsigned long long ar_limit_ns;
+    int b_const;                   // B is never written while this process launches kernels (a served weight): its first
+                                   // ring-full of tiles may be fetched before the kernels ahead on the stream have finished
     int b_packed;                  // B is stored tile-major: [N / 128][K / 64][128 rows][64 columns], 16 KB contiguous per tile
     int a_rows;                    // rows of A that TMA fetches per K block (M rounded up to 8): the rest of the 128-row
                                    // operand tile is left as it is - its products land in rows that nobody reads
@@ -139,11 +141,15 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     const int kb_per = (kblocks_total + S - 1) / S;
     const int kb0 = min(kblocks_total, r * kb_per), kb1 = min(kblocks_total, kb0 + kb_per);
 
-    auto load_stage = [&](int kb, int stage) {
+    auto load_b = [&](int kb, int stage) {                       // announces the bytes of both operands
         tc::mbar_expect_tx(&full[stage], p.a_rows * BK * 2 + B_STAGE);
         if (p.b_packed) tma_load_4d(sB + stage * B_STAGE, &tmB, &full[stage], 0, 0, kb, tn * (BN / 128));
         else tc::tma_load_3d(sB + stage * B_STAGE, &tmB, &full[stage], kb * BK, tn * BN, 0);
-        tc::tma_load_3d(sA + stage * A_STAGE, &tmA, &full[stage], kb * BK, 0, 0);
+    };
+    auto load_a = [&](int kb, int stage) { tc::tma_load_3d(sA + stage * A_STAGE, &tmA, &full[stage], kb * BK, 0, 0); };
+    auto load_stage = [&](int kb, int stage) {
+        load_b(kb, stage);
+        load_a(kb, stage);
     };
     const int first = min(STAGES, kb1 - kb0);                    // loads that need no free-slot wait
     if (threadIdx.x == 0) {
@@ -158,7 +164,17 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         // the tensor-memory allocation): their latency overlaps the rest of the prologue
         tc::prefetch_tmap(&tmA);
         tc::prefetch_tmap(&tmB);
-        for (int i = 0; i < first; ++i) load_stage(kb0 + i, i);
+        // Launched as a dependent of the kernel before it, this CTA may be running while that kernel still
+        // is: the weight tiles of the first ring-full (up to 200 KB per CTA, most of a 3B projection over
+        // the grid) stream in meanwhile; the activations are fetched after the wait.
+        if (p.b_const) {
+            for (int i = 0; i < first; ++i) load_b(kb0 + i, i);
+            kb_dep_wait();
+            for (int i = 0; i < first; ++i) load_a(kb0 + i, i);
+        } else {
+            kb_dep_wait();
+            for (int i = 0; i < first; ++i) load_stage(kb0 + i, i);
+        }
     }
     if (warp == 1) {
         tc::tmem_alloc(tmem_slot, BN);
@@ -167,6 +183,8 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     tc::tc_fence_before();
     __syncthreads();
     tc::tc_fence_after();
+    kb_dep_wait();                       // every thread: returns at once after thread 0's wait above
+    kb_dep_trigger();
     const uint32_t tmem_base = *tmem_slot;
     bool have_partial = kb1 > kb0;
 
@@ -436,11 +454,13 @@ int launch_skinny(const CUtensorMap& tmA, const CUtensorMap& tmB, const SkinnyPa
     cfg.blockDim = dim3(192, 1, 1);
     cfg.dynamicSmemBytes = Cfg<BN, AM>::SMEM;
     cfg.stream = st;
-    cudaLaunchAttribute at[1];
+    cudaLaunchAttribute at[2];
     at[0].id = cudaLaunchAttributeClusterDimension;
     at[0].val.clusterDim.x = S;
     at[0].val.clusterDim.y = 1;
     at[0].val.clusterDim.z = 1;
+    at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at;
     cfg.numAttrs = 1;
     if (AR) {
@@ -452,6 +472,7 @@ int launch_skinny(const CUtensorMap& tmA, const CUtensorMap& tmB, const SkinnyPa
             return KB_LAUNCH_FAILED;
         }
     }
+    cfg.numAttrs = g_kb_dependent_launch ? 2 : 1;
     const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_skinny_kernel<BN, AM, AR>, tmA, tmB, p);
     if (e != cudaSuccess) {
         cudaGetLastError();
@@ -477,7 +498,7 @@ static int skinny_dispatch(const void* A, const void* B, void* C, const void* Ci
                            int b_packed, int* status, const ArArgs* ar, cudaStream_t st) {
     if (M <= 0 || M > BM || N <= 0 || K <= 0) return 5;
     if ((lda & 7) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15)) return 6;
-    if (b_packed ? (K % BK) != 0 : (ldb & 7) != 0) return 6;
+    if ((b_packed & 1) ? (K % BK) != 0 : (ldb & 7) != 0) return 6;
     if (bn != 0 && bn != 128 && bn != 256) return 5;
     int sms = 0, dev = 0;
     cudaGetDevice(&dev);
@@ -506,7 +527,7 @@ static int skinny_dispatch(const void* A, const void* B, void* C, const void* Ci
     const int a_rows = ((M + 7) / 8) * 8;
     int r = make_tmap_sk(&tmA, A, K, M, lda, BK, a_rows);
     if (r) return r;
-    if (b_packed) r = make_tmap_packed(&tmB, B, (N + 127) / 128, K / BK, best_bn / 128);
+    if (b_packed & 1) r = make_tmap_packed(&tmB, B, (N + 127) / 128, K / BK, best_bn / 128);
     else r = make_tmap_sk(&tmB, B, K, N, ldb, BK, best_bn);
     if (r) return r;
     SkinnyParams p;
@@ -514,7 +535,8 @@ static int skinny_dispatch(const void* A, const void* B, void* C, const void* Ci
     p.M = M; p.N = N; p.K = K; p.alpha = alpha; p.beta = beta;
     p.C = (__nv_bfloat16*)C; p.Cin = (const __nv_bfloat16*)Cin; p.ldc = ldc; p.ldcin = ldcin; p.status = status;
     p.a_rows = a_rows;
-    p.b_packed = b_packed;
+    p.b_packed = b_packed & 1;
+    p.b_const = (b_packed >> 1) & 1;
     if (ar) {
         for (int i = 0; i < 8; ++i) {
             p.ar_recv[i] = i < ar->world ? ar->recv[i] : nullptr;
@@ -542,7 +564,9 @@ static int skinny_dispatch(const void* A, const void* B, void* C, const void* Ci
 // elements, multiples of 8; 16-byte aligned bases), M <= 128.  `split` <= 0: chosen here (BN and the
 // cluster size that put the most CTAs on the weight stream); otherwise the cluster size to use (1..8).
 // Returns 0, a refusal code, or KB_LAUNCH_FAILED when the runtime cannot place the cluster.
-// `b_packed` != 0: B points at the tile-major copy made by kb_pack_weight_tiles ([ceil(N/128)][K/64][128][64],
+// `b_packed` bit 1: B is a constant of the process (a served weight), so a dependent launch may fetch its tiles
+// before the kernels ahead of it have finished.
+// `b_packed` bit 0: B points at the tile-major copy made by kb_pack_weight_tiles ([ceil(N/128)][K/64][128][64],
 // K a multiple of 64); every TMA box is then whole contiguous 16 KB tiles instead of 128-byte pieces 2K
 // bytes apart.  Measured on the 3B decode shapes this is worth 3 % (the kernel is bound by the ~70 GB/s
 // one SM can take in and by its fixed ~6 us of launch, prologue and cluster reduction, not by DRAM

@@ -59,6 +59,8 @@ route_pipe_kernel(RouteSrcs srcs, RouteDsts dsts, int S, const bf16* __restrict_
         tc::fence_barrier_init();
     }
     __syncthreads();
+    kb_dep_trigger();
+    kb_dep_wait();                      // the sources are what the kernels before this one wrote
     const int my_tokens = blockIdx.x < N ? (N - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
 
     auto issue = [&](int it) {
@@ -411,6 +413,11 @@ PipeCfg pipe_cfg(int S, int D, bool bwd) {
                 return 7;                                                                                   \
             *attr = true;                                                                                   \
         }                                                                                                   \
+        if (!BWD) /* the forward also runs in decode steps, where launch gaps matter */                     \
+            return kb_launch_dep(kern, dim3(grid), dim3(cfg.threads), cfg.smem, st, rs, ds, S,              \
+                                 (const bf16*)dxn, (const bf16*)q, (const bf16*)rn_w, (const bf16*)n_w,     \
+                                 (bf16*)xn, alpha, r, logit, rstd, dw_part, dnw_part, N, D, eps,            \
+                                 cfg.stages, status);                                                       \
         kern<<<grid, cfg.threads, cfg.smem, st>>>(rs, ds, S, (const bf16*)dxn, (const bf16*)q,              \
                                                    (const bf16*)rn_w, (const bf16*)n_w, (bf16*)xn, alpha, r, \
                                                    logit, rstd, dw_part, dnw_part, N, D, eps, cfg.stages,  \

@@ -17,6 +17,8 @@ __global__ void kv_append_kernel(const bf16* __restrict__ k, const bf16* __restr
                                  long long v_stride, bf16* __restrict__ k_pages, bf16* __restrict__ v_pages,
                                  const long long* __restrict__ slot, int N, int row_elems, int hd, long long num_slots,
                                  int* __restrict__ status) {
+    kb_dep_trigger();
+    kb_dep_wait();
     const int chunks = row_elems >> 3;
     const int n_kv = row_elems / hd;
     const long long total = (long long)N * chunks;
@@ -42,9 +44,8 @@ KB_API int kb_kv_append(const void* k, const void* v, long long k_stride, long l
     long long blocks = ((long long)N * (row_elems / 8) + 255) / 256;
     if (blocks < 1) blocks = 1;
     if (blocks > 4096) blocks = 4096;
-    kv_append_kernel<<<(int)blocks, 256, 0, st>>>((const bf16*)k, (const bf16*)v, k_stride, v_stride, (bf16*)k_pages,
-                                                  (bf16*)v_pages, slot, N, row_elems, hd, num_slots, status);
-    return kb_launch_status();
+    return kb_launch_dep(kv_append_kernel, dim3((unsigned)blocks), dim3(256), 0, st, (const bf16*)k, (const bf16*)v, k_stride,
+                         v_stride, (bf16*)k_pages, (bf16*)v_pages, slot, N, row_elems, hd, num_slots, status);
 }
 
 // One CTA per (request, kv head, split of SPLIT tokens).  G = query heads per kv head.
@@ -374,6 +375,8 @@ paged_decode_stream_kernel(const bf16* __restrict__ q, long long q_stride, const
 template <int HD>
 __global__ void paged_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                    bf16* __restrict__ out, long long out_stride, int n_kv, int G, int nsplit) {
+    kb_dep_trigger();
+    kb_dep_wait();
     const int req = blockIdx.x, head = blockIdx.y;
     const int kvh = head / G, g = head % G;
     const int d = threadIdx.x;
@@ -654,6 +657,8 @@ paged_decode_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
     __shared__ uint64_t full[4][MMA_NST];
     __shared__ int abort_flag;
     const int kvh = blockIdx.x, req = blockIdx.y, sp = blockIdx.z;
+    kb_dep_trigger();
+    kb_dep_wait();                      // the rows appended to the pages and the queries come from the kernels before
     const int ctx = ctx_lens[req];
     const int t0 = sp * split_tokens;
     const int nt = min(split_tokens, ctx - t0);
@@ -887,9 +892,10 @@ KB_API int kb_paged_decode(const void* q, long long q_stride, const void* k_page
         int tr = make_page_tmap(&tmK, k_pages, page_rows);                                                     \
         if (!tr) tr = make_page_tmap(&tmV, v_pages, page_rows);                                                \
         if (tr) return tr;                                                                                     \
-        paged_decode_mma_kernel<G_><<<grid, 128, MMA_SMEM, st>>>(                                              \
+        const int lr = kb_launch_dep(paged_decode_mma_kernel<G_>, grid, dim3(128), MMA_SMEM, st,               \
             tmK, tmV, (const bf16*)q, q_stride, page_table, max_pages, ctx_lens,                               \
             n_kv, split_tokens, scale, part_o, part_ml, nsplit);                                               \
+        if (lr) return lr;                                                                                     \
     } else if (streaming >= 2 && (HD_) == 128 && (G_) <= 4) {                                                         \
         static bool attr_flags[64] = {};                                                                       \
         bool* attr = kb_device_flag(attr_flags);                                                               \
@@ -923,7 +929,9 @@ KB_API int kb_paged_decode(const void* q, long long q_stride, const void* k_page
             case 8: DEC(128, 8); break;
             default: return 5;
         }
-        paged_merge_kernel<128><<<dim3(B, n_q), 128, 0, st>>>(part_o, part_ml, (bf16*)out, out_stride, n_kv, G, nsplit);
+        if (kb_launch_status()) return KB_LAUNCH_FAILED;
+        return kb_launch_dep(paged_merge_kernel<128>, dim3(B, n_q), dim3(128), 0, st, (const float*)part_o, (const float*)part_ml,
+                             (bf16*)out, out_stride, n_kv, G, nsplit);
     } else if (hd == 64) {
         switch (G) {
             case 1: DEC(64, 1); break;
@@ -933,7 +941,9 @@ KB_API int kb_paged_decode(const void* q, long long q_stride, const void* k_page
             case 8: DEC(64, 8); break;
             default: return 5;
         }
-        paged_merge_kernel<64><<<dim3(B, n_q), 64, 0, st>>>(part_o, part_ml, (bf16*)out, out_stride, n_kv, G, nsplit);
+        if (kb_launch_status()) return KB_LAUNCH_FAILED;
+        return kb_launch_dep(paged_merge_kernel<64>, dim3(B, n_q), dim3(64), 0, st, (const float*)part_o, (const float*)part_ml,
+                             (bf16*)out, out_stride, n_kv, G, nsplit);
     } else {
         return 5;
     }

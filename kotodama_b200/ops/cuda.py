@@ -8,6 +8,7 @@ their waits and report through a device status word, read by :meth:`CudaOps.chec
 """
 from __future__ import annotations
 
+import contextlib
 import ctypes
 import math
 from typing import Optional, Sequence
@@ -99,8 +100,10 @@ class CudaOps(TorchOps):
     def _gemm(self, a: torch.Tensor, b: torch.Tensor, M: int, N: int, K: int, a_mn: bool, b_mn: bool,
               out: Optional[torch.Tensor] = None, cin: Optional[torch.Tensor] = None, alpha: float = 1.0,
               beta: float = 0.0, out_dtype: Optional[torch.dtype] = None, batch: int = 1,
-              sym_upper: bool = False, diag: float = 0.0) -> torch.Tensor:
-        """``diag`` is added to the diagonal of the result (fused into the CTA-pair kernel's epilogue when
+              sym_upper: bool = False, diag: float = 0.0, b_const: bool = False) -> torch.Tensor:
+        """``b_const``: ``b`` is a weight that nothing writes while kernels are in flight (serving), so a
+        decode-size product launched as a dependent may fetch it before the kernels ahead have finished.
+        ``diag`` is added to the diagonal of the result (fused into the CTA-pair kernel's epilogue when
         there is an addend, a separate in-place add otherwise)."""
         out_dtype = out_dtype or (out.dtype if out is not None else a.dtype)
         lead = (batch,) if batch > 1 else ()
@@ -145,7 +148,7 @@ class CudaOps(TorchOps):
                 rc = self.lib.kb_gemm_skinny(_p(a), _p(b), _p(out), _p(cin), _I(M), _I(N), _I(K), _LL(a.stride(-2)),
                                              _LL(b.stride(-2)), _LL(out.stride(-2)),
                                              _LL(cin.stride(-2) if cin is not None else 0), _F(alpha), _F(beta), _I(0),
-                                             _I(0), _I(0), _p(self.status(a.device)), _st())
+                                             _I(0), _I(2 if b_const else 0), _p(self.status(a.device)), _st())
                 if rc == 0:
                     self.launches += 1
                     return out
@@ -238,6 +241,18 @@ class CudaOps(TorchOps):
                    _p(self.status(qa.device)), _I(self.fp8_pair if self.fp8_backend == "mx" else 0), _st())
         return out
 
+    @contextlib.contextmanager
+    def dependent_launch(self, on: bool = True):
+        """Inside the block the decode-path kernels (routing + norm forward, QK-norm + RoPE, cache append, decode
+        attention and its merge, SwiGLU, the decode-size product) are launched as programmatic dependents of
+        the kernel before them: their launch and prologue - for the product also the first ring-full of weight
+        tiles - overlap that kernel's tail.  A CUDA graph captured inside the block keeps the edges."""
+        was = self.lib.kb_set_dependent_launch(_I(1 if on else 0))
+        try:
+            yield
+        finally:
+            self.lib.kb_set_dependent_launch(_I(was))
+
     def decode_weight(self, w: torch.Tensor) -> DecodeWeight:
         N, K = w.shape
         if not (self.skinny_cluster and self.pack_decode_weights and w.is_cuda and w.dtype == torch.bfloat16
@@ -248,7 +263,8 @@ class CudaOps(TorchOps):
         return DecodeWeight(w, packed)
 
     def gemm_nt(self, a, b, out=None, residual=None, accumulate=False):
-        if isinstance(b, DecodeWeight):
+        b_const = isinstance(b, DecodeWeight)
+        if b_const:
             M, K = a.shape
             N = b.w.shape[0]
             if (b.packed is not None and self.skinny_cluster and M <= 128 and a.dtype == torch.bfloat16
@@ -260,7 +276,7 @@ class CudaOps(TorchOps):
                 if out.stride(-1) == 1 and (cin is None or (cin.stride(-1) == 1 and cin.dtype == out.dtype)):
                     rc = self.lib.kb_gemm_skinny(_p(a), _p(b.packed), _p(out), _p(cin), _I(M), _I(N), _I(K), _LL(a.stride(-2)),
                                                  _LL(K), _LL(out.stride(-2)), _LL(cin.stride(-2) if cin is not None else 0),
-                                                 _F(1.0), _F(1.0), _I(0), _I(0), _I(1), _p(self.status(a.device)), _st())
+                                                 _F(1.0), _F(1.0), _I(0), _I(0), _I(3), _p(self.status(a.device)), _st())
                     if rc == 0:
                         self.launches += 1
                         return out
@@ -275,7 +291,7 @@ class CudaOps(TorchOps):
                 return self.gemm_fp8(qa, sa, b.q, b.s, 128, out=out, accumulate=accumulate, residual=residual)
             b = b.w
         cin = residual if residual is not None else (out if accumulate else None)
-        return self._gemm(a, b, a.shape[0], b.shape[0], a.shape[1], False, False, out, cin, 1.0, 1.0)
+        return self._gemm(a, b, a.shape[0], b.shape[0], a.shape[1], False, False, out, cin, 1.0, 1.0, b_const=b_const)
 
     def gemm_nn(self, a, b, out=None):
         if isinstance(b, Fp8Weight):

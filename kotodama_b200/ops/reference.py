@@ -10,6 +10,8 @@ Triton backward ``src/model/flash_attn_res/kernels/phase_1.py:204-249``; RMSNorm
 """
 from __future__ import annotations
 
+import contextlib
+
 import math
 from typing import Optional, Sequence
 
@@ -65,6 +67,11 @@ class TorchOps:
     """Backend object; ``CudaOps`` derives from it and overrides methods with kernels."""
 
     name = "torch"
+
+    @contextlib.contextmanager
+    def dependent_launch(self, on: bool = True):
+        """Only the CUDA back end has launches to overlap."""
+        yield
 
     def decode_weight(self, w: torch.Tensor) -> "DecodeWeight":
         """Wrap a serving projection weight; the CUDA backend adds the tile-major copy."""

@@ -20,6 +20,7 @@ temperature -> top-k -> top-p -> multinomial, greedy at temperature 0 (``serve.p
 from __future__ import annotations
 
 import math
+import os
 from dataclasses import dataclass, field
 from typing import Any, Optional
 
@@ -146,6 +147,8 @@ class ServingEngine:
         self._free_slots = list(range(max_batch - 1, -1, -1))
         self._dec_states: dict[int, dict] = {}
         self.use_cuda_graphs = True          # decode steps are replayed from captured graphs on CUDA
+        # captured decode kernels start while the kernel before them drains (KOTODAMA_DEPENDENT_LAUNCH=0: plain order)
+        self.dependent_launch = os.environ.get("KOTODAMA_DEPENDENT_LAUNCH", "1") != "0"
         # when a list: every pass appends ([request ids], fp32 logits on the host) - for tests that compare
         # two engines by logits rather than by sampled tokens
         self.logit_trace: Optional[list] = None
@@ -379,7 +382,8 @@ class ServingEngine:
                 self._forward(st["ids"], st["pos"], st["slots"], decode, st["rows"])
                 torch.cuda.synchronize()
                 graph = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(graph):
+                # the captured launches are programmatic dependents of one another (the graph keeps the edges)
+                with torch.cuda.graph(graph), self.ops.dependent_launch(self.dependent_launch):
                     logits = self._forward(st["ids"], st["pos"], st["slots"], decode, st["rows"])
                     toks = self.ops.argmax(logits)
                 g = st["graphs"][bucket] = (graph, logits, toks)

@@ -166,7 +166,7 @@ class ServeTP:
                 rc = self.lib.kb_gemm_skinny_allreduce(
                     _VP(x.data_ptr()), _VP((packed if packed is not None else wt).data_ptr()), _VP(out.data_ptr()),
                     _VP(residual.data_ptr() if residual is not None else None), _I(M), _I(N), _I(K), _LL(x.stride(0)),
-                    _LL(K), _I(int(packed is not None)), self.recv_ptrs, self.flag_ptrs, _I(self.size), _I(self.rank),
+                    _LL(K), _I(int(packed is not None) | (2 if hasattr(w, "w") else 0)), self.recv_ptrs, self.flag_ptrs, _I(self.size), _I(self.rank),
                     _LL(self.slot_elems), _VP(self.epoch.data_ptr()), _VP(self.counters.data_ptr()), _D(self.WAIT_LIMIT_S),
                     _VP(ops.status(x.device).data_ptr()), _VP(torch.cuda.current_stream().cuda_stream))
                 if rc == 0:
