@@ -40,6 +40,8 @@ def main() -> None:
     ap.add_argument("--passes", type=int, default=2, help="2: report the second (warm) pass, the first one separately")
     ap.add_argument("--profile-decode-step", type=int, default=-1,
                     help="bracket this decode step of the last pass with cudaProfilerStart/Stop (ncu --profile-from-start off)")
+    ap.add_argument("--graph-times", action="store_true",
+                    help="also report the device time of the decode graph replays alone (p50), i.e. the step without the host's share")
     ap.add_argument("--op-times", default="", help="after the run: per-op device times of 8 eager decode steps, to this file")
     a = ap.parse_args()
     world, rank = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0"))
@@ -109,6 +111,8 @@ def run(a, rank: int, world: int, local: int) -> dict:
         return dict(t_first=t_first, step_ms=step_ms, decode_tokens=decode_tokens,
                     prefill_s=eng.stats["prefill_s"] - before["prefill_s"])
 
+    if cuda and a.graph_times:
+        eng.graph_ms = []
     cold = one_pass()                    # first pass: allocator growth, graph capture, first-use set-up
     res = one_pass(a.profile_decode_step) if a.passes > 1 else cold
     t_first, step_ms, decode_tokens = res["t_first"], res["step_ms"], res["decode_tokens"]
@@ -153,6 +157,8 @@ def run(a, rank: int, world: int, local: int) -> dict:
            "decode_tok_s": round(decode_tokens / max(total_decode_s, 1e-9), 1),
            "p50_token_latency_ms": round(statistics.median(step_ms), 3) if step_ms else None,
            "p95_token_latency_ms": round(sorted(step_ms)[int(0.95 * (len(step_ms) - 1))], 3) if step_ms else None,
+           "decode_graph_ms_p50": (round(statistics.median(eng.graph_ms[-len(step_ms):]), 3)
+                                   if eng.graph_ms and step_ms else None),
            "kernel_launches": getattr(eng.ops, "launches", None),
            "attention_library_calls": getattr(eng.ops, "attention_library_calls", 0), "tp": world,
            "prefill_passes": eng.stats["prefill_passes"], "prefill_batch_tokens": a.prefill_batch_tokens}

@@ -24,6 +24,7 @@ import os
 from dataclasses import dataclass, field
 from typing import Any, Optional
 
+import numpy as np
 import torch
 
 from ..config import ModelConfig
@@ -149,6 +150,8 @@ class ServingEngine:
         self.use_cuda_graphs = True          # decode steps are replayed from captured graphs on CUDA
         # captured decode kernels start while the kernel before them drains (KOTODAMA_DEPENDENT_LAUNCH=0: plain order)
         self.dependent_launch = os.environ.get("KOTODAMA_DEPENDENT_LAUNCH", "1") != "0"
+        self.graph_ms: Optional[list[float]] = None      # set to a list to collect the device time of every decode replay
+        self._graph_events: list = []
         # when a list: every pass appends ([request ids], fp32 logits on the host) - for tests that compare
         # two engines by logits rather than by sampled tokens
         self.logit_trace: Optional[list] = None
@@ -342,29 +345,33 @@ class ServingEngine:
         # (requests of unequal length retire one by one) replays its old graphs
         st = self._dec_states.get(B)
         if st is None:
+            # ids | slots (int64), pos | ctx (int32) live in ONE device buffer with a pinned host twin: a decode
+            # step costs one host -> device copy of 24 bytes per request
             dev = self.device
-            st = {"B": B, "key": None, "ids": torch.zeros(B, dtype=torch.long, device=dev),
-                  "pos": torch.zeros(B, dtype=torch.int32, device=dev),
-                  "slots": torch.zeros(B, dtype=torch.long, device=dev),
-                  "ctx": torch.zeros(B, dtype=torch.int32, device=dev),
+            packed = torch.zeros(24 * B, dtype=torch.uint8, device=dev)
+            host = torch.zeros(24 * B, dtype=torch.uint8, pin_memory=dev.type == "cuda")
+            cut = lambda t, lo, hi, dt: t[lo * B: hi * B].view(dt)
+            st = {"B": B, "key": None, "packed": packed, "host": host,
+                  "ids": cut(packed, 0, 8, torch.long), "slots": cut(packed, 8, 16, torch.long),
+                  "pos": cut(packed, 16, 20, torch.int32), "ctx": cut(packed, 20, 24, torch.int32),
+                  "h_ids": cut(host, 0, 8, torch.long).numpy(), "h_slots": cut(host, 8, 16, torch.long).numpy(),
+                  "h_pos": cut(host, 16, 20, torch.int32).numpy(), "h_ctx": cut(host, 20, 24, torch.int32).numpy(),
                   "table": torch.zeros(B, self.max_pages_per_req, dtype=torch.int32, device=dev),
-                  "rows": torch.arange(B, device=dev), "graphs": {}}
+                  "rows": torch.arange(B, device=dev), "idx": np.arange(B), "graphs": {}}
             self._dec_states[B] = st
         if st["key"] != key:
-            table = torch.zeros(B, self.max_pages_per_req, dtype=torch.int32)
+            table = np.zeros((B, self.max_pages_per_req), dtype=np.int32)
             for i, r in enumerate(reqs):
-                table[i, : len(r.pages)] = torch.tensor(r.pages, dtype=torch.int32)
-            st["table"].copy_(table, non_blocking=True)
+                table[i, : len(r.pages)] = r.pages
+            st["table"].copy_(torch.from_numpy(table), non_blocking=True)
             st["host_table"] = table
             st["key"] = key
-        lens = torch.tensor([r.ctx_len for r in reqs], dtype=torch.int32)
-        last = torch.tensor([r.generated[-1] for r in reqs], dtype=torch.long)
-        idx = torch.arange(B)
-        slots = st["host_table"][idx, (lens // PAGE).long()].long() * PAGE + (lens % PAGE).long()
-        st["ids"].copy_(last, non_blocking=True)
-        st["pos"].copy_(lens, non_blocking=True)
-        st["ctx"].copy_(lens + 1, non_blocking=True)
-        st["slots"].copy_(slots, non_blocking=True)
+        lens = np.fromiter((r.ctx_len for r in reqs), dtype=np.int64, count=B)
+        st["h_ids"][:] = np.fromiter((r.generated[-1] for r in reqs), dtype=np.int64, count=B)
+        st["h_slots"][:] = st["host_table"][st["idx"], lens // PAGE].astype(np.int64) * PAGE + lens % PAGE
+        st["h_pos"][:] = lens
+        st["h_ctx"][:] = lens + 1
+        st["packed"].copy_(st["host"], non_blocking=True)
         return st
 
     def _decode(self) -> None:
@@ -387,16 +394,26 @@ class ServingEngine:
                     logits = self._forward(st["ids"], st["pos"], st["slots"], decode, st["rows"])
                     toks = self.ops.argmax(logits)
                 g = st["graphs"][bucket] = (graph, logits, toks)
-            g[0].replay()
+            if self.graph_ms is not None:            # device time of the replay alone (what the host adds is wall - this)
+                ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+                ev[0].record()
+                g[0].replay()
+                ev[1].record()
+                self._graph_events.append(ev)
+            else:
+                g[0].replay()
             logits, toks = g[1], g[2]
-            toks = toks.tolist() if greedy else sample_tokens(logits, reqs, self.ops, self.seen).tolist()
+            toks = toks if greedy else sample_tokens(logits, reqs, self.ops, self.seen)
         else:
             logits = self._forward(st["ids"], st["pos"], st["slots"], decode, st["rows"])
-            toks = sample_tokens(logits, reqs, self.ops, self.seen).tolist()
+            toks = sample_tokens(logits, reqs, self.ops, self.seen)
         if self.logit_trace is not None:
             self.logit_trace.append(([r.rid for r in reqs], logits[:B].float().cpu()))
-        if self.tp is not None:
-            toks = self.tp.sync_tokens(toks, self.device)
+        # one device -> host read per step (under tensor parallelism: of rank 0's tokens, broadcast on the device)
+        toks = self.tp.sync_tokens(toks, self.device) if self.tp is not None else toks.tolist()
+        if self.graph_ms is not None and self._graph_events:
+            self.graph_ms += [a.elapsed_time(b) for a, b in self._graph_events]     # the token read above synchronised
+            self._graph_events.clear()
         for r, t in zip(reqs, toks):
             r.ctx_len += 1
             self._accept(r, int(t))
