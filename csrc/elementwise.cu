@@ -407,16 +407,21 @@ KB_API int kb_colsum(const float* part, float* out, int R, int C, cudaStream_t s
 // One warp per token.  A head is covered by HD/16 lanes (lane `sub` owns elements [8*sub, 8*sub+8) of
 // each half, one 16-byte access per half), so a warp takes 32/(HD/16) heads per pass; the token's
 // cos/sin row and the norm weights stay in registers across all heads of the token.
-template <int HD, bool NORM>
+// APPEND (serving): the rotated keys and the untouched values of token n also go to slot[n] of the paged cache
+// ([pages][nkv][16][HD]; slot = page * 16 + offset, negative = skip, at or past num_slots = skipped and recorded
+// as KB_BAD_INDEX) - the value heads are walked as nkv more heads that are only copied.
+template <int HD, bool NORM, bool APPEND>
 __global__ void __launch_bounds__(256)
 qknorm_rope_fwd_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ qw, const bf16* __restrict__ kw,
                        const float* __restrict__ cosT, const float* __restrict__ sinT, bf16* __restrict__ out,
                        float* __restrict__ rstd_o, int N, int T, int nq, int nkv, int pos_offset, float eps,
-                       const int* __restrict__ positions) {
+                       const int* __restrict__ positions, bf16* __restrict__ k_pages, bf16* __restrict__ v_pages,
+                       const long long* __restrict__ slot, long long num_slots, int* __restrict__ status) {
     constexpr int LPH = HD / 16, HPW = 32 / LPH;
     kb_dep_trigger();
     kb_dep_wait();
     const int nh = nq + nkv;
+    const int nwalk = APPEND ? nh + nkv : nh;            // heads this kernel walks
     const int lane = threadIdx.x & 31, sub = lane % LPH, hsel = lane / LPH, e0 = sub * 8;
     const int in_stride = (nq + 2 * nkv) * HD, out_stride = nh * HD;
     float wq1[8], wq2[8], wk1[8], wk2[8];
@@ -428,13 +433,21 @@ qknorm_rope_fwd_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ qw
     }
     const long long nwarps = (long long)gridDim.x * (blockDim.x >> 5);
     // few tokens (decode): a warp takes one pass of HPW heads of one token instead of the whole token
-    const int ngroups = (nh + HPW - 1) / HPW;
+    const int ngroups = (nwalk + HPW - 1) / HPW;
     const int gsplit = N >= nwarps ? 1 : ngroups;
     for (long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); item < (long long)N * gsplit;
          item += nwarps) {
         const long long tok = item / gsplit;
-        const int h_lo = gsplit == 1 ? 0 : (int)(item % gsplit) * HPW, h_hi = gsplit == 1 ? nh : min(nh, h_lo + HPW);
+        const int h_lo = gsplit == 1 ? 0 : (int)(item % gsplit) * HPW, h_hi = gsplit == 1 ? nwalk : min(nwalk, h_lo + HPW);
         const int pos = positions ? positions[tok] : (int)(tok % T) + pos_offset;
+        long long cslot = -1;
+        if (APPEND) {
+            cslot = slot[tok];
+            if (cslot >= num_slots) {
+                if (lane == 0 && h_lo == 0 && status) atomicMax(status, (int)KB_BAD_INDEX);
+                cslot = -1;
+            }
+        }
         float c[8], sn[8];
         *reinterpret_cast<float4*>(c) = *reinterpret_cast<const float4*>(cosT + (size_t)pos * HD + e0);
         *reinterpret_cast<float4*>(c + 4) = *reinterpret_cast<const float4*>(cosT + (size_t)pos * HD + e0 + 4);
@@ -445,10 +458,11 @@ qknorm_rope_fwd_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ qw
 #pragma unroll 2
         for (int h0 = h_lo; h0 < h_hi; h0 += HPW) {
             const int head = h0 + hsel;
+            const bool isv = APPEND && head >= nh && head < nwalk;       // a value head: copied to its page only
             const bool ok = head < nh;
             const bool isq = head < nq;
             float x1[8], x2[8];
-            if (ok) {
+            if (ok || isv) {
                 unpack8(ld8(src + head * HD + e0), x1);
                 unpack8(ld8(src + head * HD + HD / 2 + e0), x2);
             } else {
@@ -463,10 +477,12 @@ qknorm_rope_fwd_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ qw
                 for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
                 const float rs = rsqrtf(ss / HD + eps);
                 if (ok && sub == 0) rstd_o[tok * nh + head] = rs;
+                if (!isv) {
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    x1[i] *= rs * (isq ? wq1[i] : wk1[i]);
-                    x2[i] *= rs * (isq ? wq2[i] : wk2[i]);
+                    for (int i = 0; i < 8; ++i) {
+                        x1[i] *= rs * (isq ? wq1[i] : wk1[i]);
+                        x2[i] *= rs * (isq ? wq2[i] : wk2[i]);
+                    }
                 }
             } else if (ok && sub == 0) {
                 rstd_o[tok * nh + head] = 1.f;
@@ -480,6 +496,13 @@ qknorm_rope_fwd_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ qw
             if (ok) {
                 st8(dst + head * HD + e0, pack8(o1));
                 st8(dst + head * HD + HD / 2 + e0, pack8(o2));
+            }
+            if (APPEND && cslot >= 0 && (isv || (ok && !isq))) {
+                const int kvh = isv ? head - nh : head - nq;
+                const size_t at = (((size_t)(cslot / 16) * nkv + kvh) * 16 + (size_t)(cslot % 16)) * HD + e0;
+                bf16* page = isv ? v_pages : k_pages;
+                st8(page + at, pack8(isv ? x1 : o1));
+                st8(page + at + HD / 2, pack8(isv ? x2 : o2));
             }
         }
     }
@@ -605,19 +628,45 @@ qknorm_rope_bwd_kernel(const bf16* __restrict__ dqk, const bf16* __restrict__ qk
 
 KB_API int kb_qknorm_grid_warps() { return kb_num_sms() * 8 * 8; }
 
-KB_API int kb_qknorm_rope_fwd(const void* qkv, const void* qw, const void* kw, const float* cosT, const float* sinT,
-                              void* out, float* rstd, int N, int T, int nq, int nkv, int hd, int pos_offset,
-                              float eps, const int* positions, cudaStream_t st) {
-    long long blocks = ((long long)N * ((nq + nkv + 3) / 4) + 7) / 8;    // at most one warp per (token, head group)
+// `k_pages` non-null: also append to the paged cache (see the kernel); `slot`, `num_slots`, `status` as kb_kv_append.
+static int qknorm_rope_fwd_launch(const void* qkv, const void* qw, const void* kw, const float* cosT, const float* sinT,
+                                  void* out, float* rstd, int N, int T, int nq, int nkv, int hd, int pos_offset,
+                                  float eps, const int* positions, void* k_pages, void* v_pages, const long long* slot,
+                                  long long num_slots, int* status, cudaStream_t st) {
+    const bool append = k_pages != nullptr;
+    if (append && (!v_pages || !slot)) return 5;
+    const int nwalk = nq + nkv + (append ? nkv : 0);
+    long long blocks = ((long long)N * ((nwalk + 3) / 4) + 7) / 8;       // at most one warp per (token, head group)
     if (blocks > kb_num_sms() * 8) blocks = kb_num_sms() * 8;
     if (blocks < 1) blocks = 1;
     const bool norm = qw != nullptr;
-#define QK_FWD(E, NORM) kb_launch_dep(qknorm_rope_fwd_kernel<E, NORM>, dim3((unsigned)blocks), dim3(256), 0, st, \
+#define QK_FWD(E, NORM, APP) kb_launch_dep(qknorm_rope_fwd_kernel<E, NORM, APP>, dim3((unsigned)blocks), dim3(256), 0, st, \
         (const bf16*)qkv, (const bf16*)qw, (const bf16*)kw, cosT, sinT, (bf16*)out, rstd, N, T, nq, nkv, pos_offset, eps, \
-        positions)
-    if (hd == 128) return norm ? QK_FWD(128, true) : QK_FWD(128, false);
-    if (hd == 64) return norm ? QK_FWD(64, true) : QK_FWD(64, false);
+        positions, (bf16*)k_pages, (bf16*)v_pages, slot, num_slots, status)
+    if (hd == 128) {
+        if (append) return norm ? QK_FWD(128, true, true) : QK_FWD(128, false, true);
+        return norm ? QK_FWD(128, true, false) : QK_FWD(128, false, false);
+    }
+    if (hd == 64) {
+        if (append) return norm ? QK_FWD(64, true, true) : QK_FWD(64, false, true);
+        return norm ? QK_FWD(64, true, false) : QK_FWD(64, false, false);
+    }
     return 5;
+}
+KB_API int kb_qknorm_rope_fwd(const void* qkv, const void* qw, const void* kw, const float* cosT, const float* sinT,
+                              void* out, float* rstd, int N, int T, int nq, int nkv, int hd, int pos_offset,
+                              float eps, const int* positions, cudaStream_t st) {
+    return qknorm_rope_fwd_launch(qkv, qw, kw, cosT, sinT, out, rstd, N, T, nq, nkv, hd, pos_offset, eps, positions,
+                                  nullptr, nullptr, nullptr, 0, nullptr, st);
+}
+// QK-norm + RoPE and the cache append of the new tokens in one launch (serving).
+KB_API int kb_qknorm_rope_append(const void* qkv, const void* qw, const void* kw, const float* cosT, const float* sinT,
+                                 void* out, float* rstd, int N, int T, int nq, int nkv, int hd, int pos_offset,
+                                 float eps, const int* positions, void* k_pages, void* v_pages, const long long* slot,
+                                 long long num_slots, int* status, cudaStream_t st) {
+    if (!k_pages) return 5;
+    return qknorm_rope_fwd_launch(qkv, qw, kw, cosT, sinT, out, rstd, N, T, nq, nkv, hd, pos_offset, eps, positions,
+                                  k_pages, v_pages, slot, num_slots, status, st);
 }
 
 KB_API int kb_qknorm_rope_bwd(const void* dqk, const void* qkv, const void* qw, const void* kw, const float* cosT,

@@ -642,12 +642,52 @@ __device__ __forceinline__ uint32_t swz_off(int row, int chunk) {
     return (uint32_t)((chunk >> 3) * MMA_HALF + row * 128 + (((chunk & 7) ^ (row & 7)) << 4));
 }
 
+// Merge of the splits inside the decode kernel: the CTA that finishes last for a (request, kv head) pair -
+// elected through a counter that it leaves at zero for the next call - combines the pair's partial results
+// exactly as paged_merge_kernel does (thread d = head dimension d, HD = blockDim.x = 128).  Every CTA of the
+// pair calls this, also the ones whose split is empty.
+template <int G>
+__device__ __forceinline__ void merge_by_last_cta(const float* part_o, const float* part_ml, bf16* __restrict__ out,
+                                                  long long out_stride, unsigned* counters, int req, int kvh, int n_kv,
+                                                  int nsplit) {
+    constexpr int HD = 128;
+    __shared__ int s_last;
+    __threadfence();                                     // this thread's partial results, device-wide
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned prev = atomicAdd(&counters[req * n_kv + kvh], 1u);
+        s_last = prev == (unsigned)nsplit - 1u;
+        if (s_last) counters[req * n_kv + kvh] = 0u;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    const int d = threadIdx.x;
+    const size_t pb0 = (size_t)(req * n_kv + kvh) * nsplit;
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        float M = -INFINITY;
+        for (int sidx = 0; sidx < nsplit; ++sidx) M = fmaxf(M, __ldcg(part_ml + ((pb0 + sidx) * G + g) * 2));
+        float num = 0.f, den = 0.f;
+        for (int sidx = 0; sidx < nsplit; ++sidx) {
+            const size_t pb = pb0 + sidx;
+            const float m = __ldcg(part_ml + (pb * G + g) * 2), l = __ldcg(part_ml + (pb * G + g) * 2 + 1);
+            if (l <= 0.f) continue;
+            const float w = __expf(m - M);
+            den += w * l;
+            num += w * __ldcg(part_o + (pb * G + g) * HD + d);
+        }
+        out[(size_t)req * out_stride + (size_t)(kvh * G + g) * HD + d] = __float2bfloat16(den > 0.f ? num / den : 0.f);
+    }
+}
+
 template <int G>
 __global__ void __launch_bounds__(128, 3)
 paged_decode_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                         const bf16* __restrict__ q, long long q_stride, const int* __restrict__ page_table, int max_pages,
                         const int* __restrict__ ctx_lens, int n_kv, int split_tokens, float scale,
-                        float* __restrict__ part_o, float* __restrict__ part_ml, int nsplit) {
+                        float* part_o, float* part_ml, int nsplit, bf16* __restrict__ out, long long out_stride,
+                        unsigned* merge_counters) {
     constexpr int HD = 128;
     extern __shared__ uint8_t ring_unaligned[];
     uint8_t* ring_raw = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(ring_unaligned) + 1023) & ~uintptr_t(1023));
@@ -668,6 +708,7 @@ paged_decode_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
             part_ml[(pbase * G + threadIdx.x) * 2] = -INFINITY;
             part_ml[(pbase * G + threadIdx.x) * 2 + 1] = 0.f;
         }
+        if (merge_counters) merge_by_last_cta<G>(part_o, part_ml, out, out_stride, merge_counters, req, kvh, n_kv, nsplit);
         return;
     }
     const int npages = (nt + PAGE - 1) / PAGE;
@@ -811,6 +852,7 @@ paged_decode_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
         part_ml[(pbase * G + g) * 2] = mxx == -INFINITY ? -INFINITY : mxx * 0.6931471805599453f;
         part_ml[(pbase * G + g) * 2 + 1] = sum;
     }
+    if (merge_counters) merge_by_last_cta<G>(part_o, part_ml, out, out_stride, merge_counters, req, kvh, n_kv, nsplit);
 }
 
 // Reads the decode status word and clears it, so that one timeout is reported once.
@@ -855,11 +897,12 @@ KB_API void kb_set_decode_kernel(int which) { g_decode_kernel = which; }
 
 // Workspace sizes (floats) for B requests: part_o = B*n_kv*nsplit*G*hd, part_ml = B*n_kv*nsplit*G*2.
 // `num_pages`: pages in k_pages / v_pages (the tensor-core kernel addresses them through a tensor map).
-KB_API int kb_paged_decode(const void* q, long long q_stride, const void* k_pages, const void* v_pages,
-                           const int* page_table, int max_pages, const int* ctx_lens, int B, int n_q, int n_kv, int hd,
-                           int max_ctx, int split_tokens, float scale, float* part_o, float* part_ml, void* out,
-                           long long out_stride, int num_pages, cudaStream_t st) {
+static int paged_decode_impl(const void* q, long long q_stride, const void* k_pages, const void* v_pages,
+                             const int* page_table, int max_pages, const int* ctx_lens, int B, int n_q, int n_kv, int hd,
+                             int max_ctx, int split_tokens, float scale, float* part_o, float* part_ml, void* out,
+                             long long out_stride, int num_pages, unsigned* merge_counters, cudaStream_t st) {
     const int G = n_q / n_kv;
+    bool merged = false;                 // the decode kernel merged the splits itself
     if (n_q % n_kv || split_tokens % PAGE || split_tokens > 2048) return 5;
     const int nsplit = (max_ctx + split_tokens - 1) / split_tokens;
     dim3 grid(n_kv, B, nsplit);
@@ -894,8 +937,9 @@ KB_API int kb_paged_decode(const void* q, long long q_stride, const void* k_page
         if (tr) return tr;                                                                                     \
         const int lr = kb_launch_dep(paged_decode_mma_kernel<G_>, grid, dim3(128), MMA_SMEM, st,               \
             tmK, tmV, (const bf16*)q, q_stride, page_table, max_pages, ctx_lens,                               \
-            n_kv, split_tokens, scale, part_o, part_ml, nsplit);                                               \
+            n_kv, split_tokens, scale, part_o, part_ml, nsplit, (bf16*)out, out_stride, merge_counters);       \
         if (lr) return lr;                                                                                     \
+        merged = merge_counters != nullptr;                                                                    \
     } else if (streaming >= 2 && (HD_) == 128 && (G_) <= 4) {                                                         \
         static bool attr_flags[64] = {};                                                                       \
         bool* attr = kb_device_flag(attr_flags);                                                               \
@@ -930,6 +974,7 @@ KB_API int kb_paged_decode(const void* q, long long q_stride, const void* k_page
             default: return 5;
         }
         if (kb_launch_status()) return KB_LAUNCH_FAILED;
+        if (merged) return 0;
         return kb_launch_dep(paged_merge_kernel<128>, dim3(B, n_q), dim3(128), 0, st, (const float*)part_o, (const float*)part_ml,
                              (bf16*)out, out_stride, n_kv, G, nsplit);
     } else if (hd == 64) {
@@ -948,6 +993,24 @@ KB_API int kb_paged_decode(const void* q, long long q_stride, const void* k_page
         return 5;
     }
     return kb_launch_status();
+}
+KB_API int kb_paged_decode(const void* q, long long q_stride, const void* k_pages, const void* v_pages,
+                           const int* page_table, int max_pages, const int* ctx_lens, int B, int n_q, int n_kv, int hd,
+                           int max_ctx, int split_tokens, float scale, float* part_o, float* part_ml, void* out,
+                           long long out_stride, int num_pages, cudaStream_t st) {
+    return paged_decode_impl(q, q_stride, k_pages, v_pages, page_table, max_pages, ctx_lens, B, n_q, n_kv, hd, max_ctx,
+                             split_tokens, scale, part_o, part_ml, out, out_stride, num_pages, nullptr, st);
+}
+// The same in one launch where the tensor-core kernel runs (head_dim 128, `num_pages` > 0): the last CTA of a
+// (request, kv head) pair merges the pair's splits.  `merge_counters`: B * n_kv zero-initialised words owned by
+// the caller; the kernel leaves them at zero.  Calls that share the counters must not overlap in time.
+KB_API int kb_paged_decode_merged(const void* q, long long q_stride, const void* k_pages, const void* v_pages,
+                                  const int* page_table, int max_pages, const int* ctx_lens, int B, int n_q, int n_kv,
+                                  int hd, int max_ctx, int split_tokens, float scale, float* part_o, float* part_ml,
+                                  void* out, long long out_stride, int num_pages, unsigned* merge_counters,
+                                  cudaStream_t st) {
+    return paged_decode_impl(q, q_stride, k_pages, v_pages, page_table, max_pages, ctx_lens, B, n_q, n_kv, hd, max_ctx,
+                             split_tokens, scale, part_o, part_ml, out, out_stride, num_pages, merge_counters, st);
 }
 
 // Greedy sampling: out[row] = argmax_j logits[row][j] (first index on ties).

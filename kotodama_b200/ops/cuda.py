@@ -58,6 +58,11 @@ class CudaOps(TorchOps):
         # fp8 products: "mx" = hardware block-scaled MMA (power-of-two scales, accumulation stays in tensor
         # memory); "promote" = fp32 scales applied per K block in registers
         self.skinny_cluster = os.environ.get("KOTODAMA_SKINNY", "cluster") != "splitk"   # decode-size GEMMs: cluster split-K through DSMEM
+        self._merge_counters: dict = {}
+        # split merge of the decode attention: its own (dependent) launch, or inside the decode kernel by the last CTA
+        # of a (request, kv head) pair.  Measured on the 3B decode step: 4.18 ms with the launch, 4.37 ms fused (the
+        # device-wide fence and the election at the end of 2560 CTAs cost more than 28 short launches), so: launch
+        self.decode_merge_fused = os.environ.get("KOTODAMA_DECODE_MERGE", "kernel") == "fused"
         self.pack_decode_weights = os.environ.get("KOTODAMA_PACK_DECODE", "0") == "1"   # serving: tile-major weight copies for decode (measured +3 %, costs a second copy of the weights: off)
         self.fp8_backend = os.environ.get("KOTODAMA_FP8", "mx")
         self.fp8_pow2 = self.fp8_backend == "mx"
@@ -467,10 +472,22 @@ class CudaOps(TorchOps):
         return out
 
     # ------------------------------------------------------------------ QK-norm + RoPE
-    def qknorm_rope_fwd(self, qkv, qw, kw, cos, sin, seq_len, n_q, n_kv, hd, eps, pos_offset=0, positions=None):
+    def qknorm_rope_fwd(self, qkv, qw, kw, cos, sin, seq_len, n_q, n_kv, hd, eps, pos_offset=0, positions=None,
+                        append=None):
+        """``append=(k_pages, v_pages, slots)``: the same launch also writes the rotated keys and the values of
+        every token into its cache slot (what ``kv_append`` does as a launch of its own)."""
         N = qkv.shape[0]
         out = torch.empty(N, (n_q + n_kv) * hd, device=qkv.device, dtype=qkv.dtype)
         rstd = torch.empty(N, n_q + n_kv, device=qkv.device, dtype=torch.float32)
+        if append is not None:
+            k_pages, v_pages, slots = append
+            rc = self.lib.kb_qknorm_rope_append(_p(qkv), _p(qw), _p(kw), _p(cos), _p(sin), _p(out), _p(rstd), _I(N),
+                                                _I(seq_len), _I(n_q), _I(n_kv), _I(hd), _I(pos_offset), _F(eps),
+                                                _p(positions), _p(k_pages), _p(v_pages), _p(slots),
+                                                _LL(k_pages.shape[0] * k_pages.shape[-2]), _p(self.status(qkv.device)),
+                                                _st())
+            self._rc(rc, "kb_qknorm_rope_append")
+            return out, rstd
         rc = self.lib.kb_qknorm_rope_fwd(_p(qkv), _p(qw), _p(kw), _p(cos), _p(sin), _p(out), _p(rstd), _I(N),
                                          _I(seq_len), _I(n_q), _I(n_kv), _I(hd), _I(pos_offset), _F(eps), _p(positions),
                                          _st())
@@ -630,10 +647,16 @@ class CudaOps(TorchOps):
         part_o = torch.empty(B * n_kv * nsplit * G * hd, device=q.device, dtype=torch.float32)
         part_ml = torch.empty(B * n_kv * nsplit * G * 2, device=q.device, dtype=torch.float32)
         out = torch.empty(B, n_q * hd, device=q.device, dtype=q.dtype)
-        rc = self.lib.kb_paged_decode(_p(q), _LL(q.stride(0)), _p(k_pages), _p(v_pages), _p(page_table),
-                                      _I(page_table.shape[1]), _p(ctx_lens), _I(B), _I(n_q), _I(n_kv), _I(hd),
-                                      _I(max_ctx), _I(split), _F(1.0 / math.sqrt(hd)), _p(part_o), _p(part_ml),
-                                      _p(out), _LL(out.stride(0)), _I(k_pages.shape[0]), _st())
+        # election counters of the in-kernel merge: zero once, left at zero by every call
+        key = (q.device.index, B * n_kv)
+        counters = self._merge_counters.get(key)
+        if counters is None:
+            counters = self._merge_counters[key] = torch.zeros(B * n_kv, device=q.device, dtype=torch.int32)
+        rc = self.lib.kb_paged_decode_merged(_p(q), _LL(q.stride(0)), _p(k_pages), _p(v_pages), _p(page_table),
+                                             _I(page_table.shape[1]), _p(ctx_lens), _I(B), _I(n_q), _I(n_kv), _I(hd),
+                                             _I(max_ctx), _I(split), _F(1.0 / math.sqrt(hd)), _p(part_o), _p(part_ml),
+                                             _p(out), _LL(out.stride(0)), _I(k_pages.shape[0]),
+                                             _p(counters if self.decode_merge_fused else None), _st())
         self._rc(rc, "kb_paged_decode")
         self.launches += 1
         return out

@@ -357,7 +357,7 @@ class TorchOps:
     # ------------------------------------------------------ QK-norm + RoPE
     def qknorm_rope_fwd(self, qkv: torch.Tensor, qw: Optional[torch.Tensor], kw: Optional[torch.Tensor],
                         cos: torch.Tensor, sin: torch.Tensor, seq_len: int, n_q: int, n_kv: int, hd: int,
-                        eps: float, pos_offset: int = 0, positions: Optional[torch.Tensor] = None):
+                        eps: float, pos_offset: int = 0, positions: Optional[torch.Tensor] = None, append=None):
         """Per-head RMSNorm (weight shared by heads) then rotate-half RoPE on the q and k parts of a
         fused ``qkv[N,(n_q+2*n_kv)*hd]`` projection.  Token ``n`` sits at position
         ``pos_offset + n % seq_len``.  Returns ``qk[N,(n_q+n_kv)*hd]`` and ``rstd[N,n_q+n_kv]`` (fp32)."""
@@ -376,6 +376,9 @@ class TorchOps:
         h2 = hd // 2
         rot = torch.cat([-y[..., h2:], y[..., :h2]], -1)
         out = (y * c + rot * s).to(qkv.dtype).reshape(n, nh * hd)
+        if append is not None:                           # serving: keys and values of the new tokens go to their cache slots
+            k_pages, v_pages, slots = append
+            self.kv_append(out[:, n_q * hd:], qkv[:, nh * hd:], k_pages, v_pages, slots)
         return out, rstd
 
     def qknorm_rope_bwd(self, dqk: torch.Tensor, qkv: torch.Tensor, qw, kw, cos, sin, rstd, seq_len: int,

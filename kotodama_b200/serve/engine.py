@@ -224,10 +224,11 @@ class ServingEngine:
                 committed = committed + [partial]
                 partial = None
             qkv = ops.gemm_nt(xn, lw["wqkv"])
-            qk, _ = ops.qknorm_rope_fwd(qkv, lw["qn"], lw["kn"], cos, sin, N, H, KV, hd, eps, positions=positions)
+            # QK-norm + RoPE; the same launch puts the new keys and values into their cache slots
+            qk, _ = ops.qknorm_rope_fwd(qkv, lw["qn"], lw["kn"], cos, sin, N, H, KV, hd, eps, positions=positions,
+                                        append=(self.cache.k[i], self.cache.v[i], slots))
             k_rows = qk[:, H * hd:]
             v_rows = qkv[:, (H + KV) * hd:]
-            ops.kv_append(k_rows, v_rows, self.cache.k[i], self.cache.v[i], slots)
             if decode is None:
                 o, _ = ops.attention_fwd(qk[:, : H * hd].view(1, N, H, hd), k_rows.view(1, N, KV, hd),
                                          v_rows.view(1, N, KV, hd), need_grad=False, **seqs)

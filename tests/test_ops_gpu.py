@@ -273,8 +273,51 @@ def test_paged_decode_and_kv_append(ops, kernel, n_q, n_kv):
                                            n_q, n_kv, hd)
     assert rel_err(out, ref) < 1e-2
     ops.check_status()
+    if kernel == "mma":
+        # the merge of the splits by the last CTA of a (request, kv head) pair equals the merge kernel bit for bit,
+        # call after call (the election counters go back to zero)
+        was = ops.decode_merge_fused
+        try:
+            ops.decode_merge_fused = True
+            fused = [ops.paged_decode_attention(q, k_pages, v_pages, table, ctx, int(ctx.max()), n_q, n_kv, hd) for _ in range(3)]
+            ops.decode_merge_fused = False
+            plain = ops.paged_decode_attention(q, k_pages, v_pages, table, ctx, int(ctx.max()), n_q, n_kv, hd)
+        finally:
+            ops.decode_merge_fused = was
+        for f in fused:
+            assert torch.equal(f, plain)
+        assert all(int(c.abs().sum()) == 0 for c in ops._merge_counters.values())
     lg = bf(7, 49152, seed=3)
     assert torch.equal(ops.argmax(lg), lg.float().argmax(-1))
+
+
+@pytest.mark.parametrize("n_tok", [5, 64, 3000])
+def test_qknorm_rope_with_cache_append_equals_two_launches(ops, n_tok):
+    """QK-norm + RoPE with the cache append in the same launch (few tokens: one warp per head group;
+    many: one warp per token) against the two kernels it replaces; padding rows (slot < 0) are skipped and a
+    slot past the cache is refused with status 6."""
+    nq, nkv, hd, P = 24, 8, 128, 256
+    qkv = bf(n_tok, (nq + 2 * nkv) * hd, seed=1)
+    qw, kw = bf(hd, seed=2) + 1, bf(hd, seed=3) + 1
+    cos, sin = (torch.randn(4096, hd, device="cuda") for _ in range(2))
+    pos = torch.randint(0, 4096, (n_tok,), device="cuda", dtype=torch.int32)
+    slots = torch.randperm(P * 16, device="cuda")[:n_tok].long()
+    slots[::7] = -1
+    kp, vp = (torch.zeros(P, nkv, 16, hd, device="cuda", dtype=torch.bfloat16) for _ in range(2))
+    kp2, vp2 = torch.zeros_like(kp), torch.zeros_like(vp)
+    out1, r1 = ops.qknorm_rope_fwd(qkv, qw, kw, cos, sin, n_tok, nq, nkv, hd, 1e-5, positions=pos)
+    ops.kv_append(out1[:, nq * hd:], qkv[:, (nq + nkv) * hd:], kp, vp, slots)
+    out2, r2 = ops.qknorm_rope_fwd(qkv, qw, kw, cos, sin, n_tok, nq, nkv, hd, 1e-5, positions=pos, append=(kp2, vp2, slots))
+    torch.cuda.synchronize()
+    assert torch.equal(out1, out2) and torch.equal(r1, r2)
+    assert torch.equal(kp, kp2) and torch.equal(vp, vp2)
+    ops.check_status()
+    bad = slots.clone()
+    bad[1] = P * 16 + 3
+    ops.qknorm_rope_fwd(qkv, qw, kw, cos, sin, n_tok, nq, nkv, hd, 1e-5, positions=pos, append=(kp2, vp2, bad))
+    with pytest.raises(Exception, match="index|6"):
+        ops.check_status()
+    ops.check_status()
 
 
 def test_serving_engine_gpu_matches_cpu_logits():
