@@ -111,6 +111,7 @@ class ForwardResult:
     states: list[torch.Tensor]                    # states[0] = embeddings, states[i+1] = after layer i
     attention: dict[int, torch.Tensor] = field(default_factory=dict)
     route_weights: dict[str, torch.Tensor] = field(default_factory=dict)
+    attention_outputs: list[torch.Tensor] = field(default_factory=list)   # attention branch of layer i, before the residual add
 
 
 @torch.no_grad()
@@ -126,18 +127,34 @@ def compute_attention_weights(layer: Any, x_normed: torch.Tensor, rope_cos: torc
 
 
 @torch.no_grad()
-def forward_with_states(model: KotodamaModel, input_ids: torch.Tensor, attention_layers: Optional[list[int]] = None
-                        ) -> ForwardResult:
+def forward_with_states(model: KotodamaModel, input_ids: torch.Tensor, attention_layers: Optional[list[int]] = None,
+                        capture_attention_outputs: bool = False,
+                        attention_fn: Optional[Any] = None) -> ForwardResult:
+    """One forward pass that keeps what the analysis tracks look at: the residual state after every layer,
+    the attention probabilities of ``attention_layers``, the depth-routing weights and - on request - every
+    layer's attention-branch output.  ``attention_fn(layer, probs)``: called with each wanted layer's
+    probabilities instead of keeping them (all layers of a long batch do not fit in memory at once)."""
     m, cfg = model, model.config
     want = set(attention_layers or [])
     x = m.embed_tokens(input_ids)
     states, attn, routes = [x], {}, {}
+    branch: list[torch.Tensor] = []
+
+    def see(i: int, layer: Any, h: torch.Tensor) -> None:
+        if i in want:
+            w = compute_attention_weights(layer, h, m.rope_cos, m.rope_sin)
+            if attention_fn is not None:
+                attention_fn(i, w)
+            else:
+                attn[i] = w
     if not cfg.attn_res:
         for i, layer in enumerate(m.layers):
             h = layer.attn_norm(x)
-            if i in want:
-                attn[i] = compute_attention_weights(layer, h, m.rope_cos, m.rope_sin)
-            x = x + layer.attn(h, m.rope_cos, m.rope_sin)
+            see(i, layer, h)
+            a = layer.attn(h, m.rope_cos, m.rope_sin)
+            if capture_attention_outputs:
+                branch.append(a)
+            x = x + a
             x = x + layer.ffn(layer.ffn_norm(x))
             states.append(x)
         xf = m.norm(x)
@@ -156,9 +173,10 @@ def forward_with_states(model: KotodamaModel, input_ids: torch.Tensor, attention
                 committed.append(partial)
                 partial = None
             hn = layer.attn_norm(h)
-            if i in want:
-                attn[i] = compute_attention_weights(layer, hn, m.rope_cos, m.rope_sin)
+            see(i, layer, hn)
             a = layer.attn(hn, m.rope_cos, m.rope_sin)
+            if capture_attention_outputs:
+                branch.append(a)
             partial = a if partial is None else partial + a
             srcs = committed + [partial]
             routes[f"mlp_{i}"] = weights(srcs, layer.mlp_res_query, layer.mlp_res_norm).mean(dim=(1, 2))
@@ -169,7 +187,7 @@ def forward_with_states(model: KotodamaModel, input_ids: torch.Tensor, attention
         routes["final"] = weights(srcs, m.final_res_query, m.final_res_norm).mean(dim=(1, 2))
         xf = m.norm(route_sources(srcs, m.final_res_query, m.final_res_norm.weight, m.final_res_norm.eps))
         states[-1] = xf
-    return ForwardResult(F.linear(xf, m.get_lm_head_weight()), states, attn, routes)
+    return ForwardResult(F.linear(xf, m.get_lm_head_weight()), states, attn, routes, branch)
 
 
 # ------------------------------------------------------------------------------ generation

@@ -4,6 +4,7 @@ import subprocess
 import sys
 from pathlib import Path
 
+import numpy as np
 import torch
 
 from kotodama_b200.config import MODEL_PRESETS, ModelConfig
@@ -49,11 +50,32 @@ def test_analysis_pipeline(tmp_path):
         assert key in tq[fam]
 
     # track 5
-    run("extract_activation_geometry.py", *common, "--prompt-set", "standard",
-        "--components", "point_clouds,eigenspectra,trajectories,attention,effective_rank")
-    geo = json.loads((out / "t" / "activation_geometry" / "geometry.json").read_text())
-    assert len(geo["eigenspectra"]) == cfg.num_layers + 1 and geo["effective_rank"]
-    run("visualize_activation_geometry.py", "--run", "t", "--output-dir", out)
+    run("extract_activation_geometry.py", *common, "--prompt-set", "standard", "--components", "all", "--topo-subsample", 200)
+    ag = out / "t" / "activation_geometry"
+    geo = json.loads((ag / "geometry.json").read_text())
+    L, H = cfg.num_layers, cfg.num_attention_heads
+    assert len(geo["eigenspectra"]) == L + 1 and len(geo["effective_rank"]["q_proj"]["participation_ratio"]) == L
+    assert len(geo["head_entropy"]["mean_per_layer"]) == L and 0 < geo["trajectories"]["straightness"] <= 1.0
+    assert all(v > 0 for v in geo["topo_clouds"]["twonn_dimension"].values())
+    for f in ("point_clouds", "topo_clouds", "trajectories", "attention_weights", "attention_outputs", "head_entropy", "weight_spectra"):
+        assert (ag / f"{f}.npz").exists(), f
+    with np.load(ag / "head_entropy.npz") as z:
+        assert z["entropy"].shape == (L, H) and (z["entropy"] >= 0).all()
+    with np.load(ag / "point_clouds.npz") as z:
+        assert set(z.files) == {f"layer_{i}" for i in range(-1, L)} and z["layer_0"].shape[1] == cfg.hidden_size
+    # a second run from token data, then the cross-run alignment from the files of both
+    torch.manual_seed(1)
+    ckpt2 = tmp_path / "other.pt"
+    torch.save({"step": 10, "tokens_consumed": 1000, "model": KotodamaModel(cfg).state_dict()}, ckpt2)
+    np.random.RandomState(0).randint(0, 260, size=8 * 48).astype("<u2").tofile(tmp_path / "eval.bin")
+    for name, ck in (("t", ckpt), ("u", ckpt2)):
+        run("extract_activation_geometry.py", "--checkpoint", ck, "--name", name, "--output-dir", out, "--tokenizer", "bytes",
+            "--section", "tiny", "--components", "point_clouds", "--eval-data", tmp_path / "eval.bin", "--n-seqs", 8, "--seq-len", 48)
+    run("extract_activation_geometry.py", "--components", "procrustes", "--runs", "t,u", "--output-dir", out)
+    dist = json.loads((out / "_pairs" / "procrustes.json").read_text())["t|u"]
+    assert len(dist) == L + 1 and all(0.0 <= d <= 1.0 for d in dist)
+    run("extract_activation_geometry.py", *common, "--prompt-set", "standard", "--components", "all", "--topo-subsample", 200)
+    run("visualize_activation_geometry.py", "--runs", "t,u", "--output-dir", out)
 
     # track 6
     run("extract_concept_geometry.py", *common, "--concept-sets", "weekdays,digits")

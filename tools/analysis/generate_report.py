@@ -303,6 +303,18 @@ def build(run: str, rd: Path, theme: str, metrics: Optional[Path] = None) -> str
             body += "<h4>Mean state norm per layer</h4>" + spark(geo["trajectories"]["mean_norm_per_layer"], ac)
         for l, a in geo.get("attention", {}).items():
             body += f"<h4>Head entropy, layer {l}</h4>" + spark(a["head_entropy"], ac)
+        if "head_entropy" in geo:
+            body += "<h4>Mean head entropy per layer (all layers)</h4>" + spark(geo["head_entropy"]["mean_per_layer"], ac)
+        if "attention_outputs" in geo:
+            body += "<h4>Attention branch norm / state norm per layer</h4>" + spark(geo["attention_outputs"]["branch_to_state_norm_ratio"], ac)
+        twonn = geo.get("topo_clouds", {}).get("twonn_dimension")
+        if twonn:
+            body += "<h4>TwoNN intrinsic dimension of the token clouds</h4>" + table([(f"layer {k}", float(v)) for k, v in twonn.items()])
+        for wtype, m in geo.get("effective_rank", {}).items():
+            if isinstance(m, dict) and "participation_ratio" in m:
+                body += f"<h4>Effective rank of {html.escape(wtype)} per layer</h4>" + spark(m["participation_ratio"], ac)
+        if "trajectories" in geo and "straightness" in geo["trajectories"]:
+            hero.append(("trajectory straightness", f"{geo['trajectories']['straightness']:.2f}", "net / path length through depth"))
         body += images(rd / "activation_geometry")
         sec.append(("Activation geometry", body))
     cg = load(rd / "concept_geometry" / "analysis.json")

@@ -1,10 +1,18 @@
 #!/usr/bin/env python
 """Plots for the activation-geometry track (5b) from the files written by
-``extract_activation_geometry.py``: per-layer RankMe / participation ratio, trajectory norms,
-head entropy, PCA point clouds.  Needs matplotlib; without it the script writes the same
-series as CSV so they can be plotted elsewhere.
+``extract_activation_geometry.py``.
+
+Per run (``--run``): per-layer RankMe / participation ratio of the states, trajectory norms, step
+cosines and step lengths, head entropy (selected layers as curves, all layers as a layer x head map),
+effective rank of every weight type over depth, TwoNN dimension of the token clouds, the share of the
+attention branch in the state, PCA point clouds, and the saved attention matrices.  With ``--runs a,b``
+the same series are overlaid for several runs and the Procrustes distances between them are drawn.
+
+Needs matplotlib; without it the script writes the same series as CSV (``series.csv``, one row per
+series; ``head_entropy_map.csv``) so they can be plotted elsewhere.
 
     python tools/analysis/visualize_activation_geometry.py --run my-run [--output-dir analysis]
+    python tools/analysis/visualize_activation_geometry.py --runs a,b [--output-dir analysis]
 
 Counterpart of the reference's ``scripts/analysis/visualize_activation_geometry.py``.
 """
@@ -19,57 +27,167 @@ import numpy as np
 
 
 def series(geo: dict) -> dict[str, list[float]]:
+    """Every 1-D series of a run's ``geometry.json``, keyed by what it shows."""
     s: dict[str, list[float]] = {}
     if "eigenspectra" in geo:
         s["rankme"] = [e["rankme"] for e in geo["eigenspectra"]]
         s["participation_ratio"] = [e["participation_ratio"] for e in geo["eigenspectra"]]
-    if "trajectories" in geo:
-        s["mean_norm"] = geo["trajectories"]["mean_norm_per_layer"]
-        s["step_cosine"] = geo["trajectories"]["mean_step_cosine"]
+    tr = geo.get("trajectories")
+    if tr:
+        s["mean_norm"] = tr["mean_norm_per_layer"]
+        s["step_cosine"] = tr["mean_step_cosine"]
+        if "mean_step_length" in tr:
+            s["step_length"] = tr["mean_step_length"]
     for l, a in geo.get("attention", {}).items():
         s[f"head_entropy_layer{l}"] = a["head_entropy"]
+        s[f"attention_distance_layer{l}"] = a["mean_attention_distance"]
+    he = geo.get("head_entropy")
+    if he:
+        s["head_entropy_mean"] = he["mean_per_layer"]
+        s["head_entropy_min"] = he["min_per_layer"]
+    er = geo.get("effective_rank", {})
+    for wtype, measures in er.items():
+        if isinstance(measures, dict) and "participation_ratio" in measures:
+            s[f"effective_rank_{wtype}"] = measures["participation_ratio"]
+            s[f"stable_rank_{wtype}"] = measures["stable_rank"]
+    for wtype, top in geo.get("weight_spectra", {}).items():
+        s[f"top_singular_value_{wtype}"] = top
+    ao = geo.get("attention_outputs")
+    if ao:
+        s["attention_branch_share"] = ao["branch_to_state_norm_ratio"]
+        s["attention_branch_rankme"] = [e["rankme"] for e in ao["spectrum"]]
+    tc = geo.get("topo_clouds", {}).get("twonn_dimension")
+    if tc:
+        s["twonn_dimension"] = [tc[k] for k in sorted(tc, key=int)]
+    pc = geo.get("point_clouds", {}).get("spread_per_layer")
+    if pc:
+        s["point_cloud_spread"] = pc
     return s
 
 
-def main() -> None:
-    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("--run", required=True)
-    ap.add_argument("--output-dir", default="analysis")
-    a = ap.parse_args()
-    d = Path(a.output_dir) / a.run / "activation_geometry"
-    geo = json.loads((d / "geometry.json").read_text())
-    s = series(geo)
-    try:
-        import matplotlib
-        matplotlib.use("Agg")
-        import matplotlib.pyplot as plt
-    except ImportError:
-        with open(d / "series.csv", "w", newline="") as fh:
-            w = csv.writer(fh)
-            for k, v in s.items():
-                w.writerow([k] + list(v))
-        print(f"matplotlib is not installed: wrote {d / 'series.csv'}")
-        return
+def write_csv(path: Path, rows: dict[str, list[float]]) -> None:
+    with open(path, "w", newline="") as fh:
+        w = csv.writer(fh)
+        for k, v in rows.items():
+            w.writerow([k] + list(v))
+
+
+def load_run(output_dir: str, run: str) -> tuple[Path, dict]:
+    d = Path(output_dir) / run / "activation_geometry"
+    return d, json.loads((d / "geometry.json").read_text())
+
+
+def plot_run(plt, d: Path, run: str, s: dict[str, list[float]]) -> None:
     for k, v in s.items():
         fig, ax = plt.subplots(figsize=(5, 3))
         ax.plot(v, marker="o", ms=3)
-        ax.set_title(f"{a.run}: {k}")
-        ax.set_xlabel("head" if k.startswith("head_entropy") else "layer")
+        ax.set_title(f"{run}: {k}")
+        ax.set_xlabel("head" if k.startswith(("head_entropy_layer", "attention_distance_layer")) else "layer")
         fig.tight_layout()
         fig.savefig(d / f"{k}.png", dpi=120)
         plt.close(fig)
     npz = d / "arrays.npz"
     if npz.exists():
-        pc = np.load(npz).get("point_clouds")
+        with np.load(npz) as z:
+            pc = z["point_clouds"] if "point_clouds" in z.files else None
         if pc is not None:
             for l in sorted({0, len(pc) // 2, len(pc) - 1}):
                 fig = plt.figure(figsize=(4, 4))
                 ax = fig.add_subplot(projection="3d")
                 ax.scatter(pc[l][:, 0], pc[l][:, 1], pc[l][:, 2], s=12)
-                ax.set_title(f"{a.run}: PCA-3, layer {l}")
+                ax.set_title(f"{run}: PCA-3, layer {l}")
                 fig.savefig(d / f"point_cloud_layer{l}.png", dpi=120)
                 plt.close(fig)
-    print(f"plots -> {d}")
+    he = d / "head_entropy.npz"
+    if he.exists():
+        with np.load(he) as z:
+            m = z["entropy"]
+        fig, ax = plt.subplots(figsize=(6, 4))
+        im = ax.imshow(m, aspect="auto", cmap="viridis")
+        ax.set_xlabel("head")
+        ax.set_ylabel("layer")
+        ax.set_title(f"{run}: attention entropy (nats)")
+        fig.colorbar(im)
+        fig.tight_layout()
+        fig.savefig(d / "head_entropy_map.png", dpi=120)
+        plt.close(fig)
+    aw = d / "attention_weights.npz"
+    if aw.exists():
+        with np.load(aw) as z:
+            for key in z.files[:6]:                      # a handful: one image per (prompt, layer), heads side by side
+                w = z[key].astype(np.float32)
+                n = min(len(w), 8)
+                fig, axes = plt.subplots(1, n, figsize=(2 * n, 2.2))
+                for h, ax in enumerate(np.atleast_1d(axes)):
+                    ax.imshow(w[h], cmap="magma")
+                    ax.set_xticks([])
+                    ax.set_yticks([])
+                    ax.set_title(f"h{h}", fontsize=7)
+                fig.suptitle(f"{run}: {key}", fontsize=8)
+                fig.savefig(d / f"attention_{key}.png", dpi=110)
+                plt.close(fig)
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--run", default=None)
+    ap.add_argument("--runs", default=None, help="comma-separated runs to overlay (comparison plots go to <output-dir>/_pairs)")
+    ap.add_argument("--output-dir", default="analysis")
+    a = ap.parse_args()
+    runs = [r.strip() for r in a.runs.split(",")] if a.runs else ([a.run] if a.run else [])
+    if not runs:
+        raise SystemExit("give --run or --runs")
+    loaded = {r: load_run(a.output_dir, r) for r in runs}
+    all_series = {r: series(geo) for r, (_, geo) in loaded.items()}
+    try:
+        import matplotlib
+        matplotlib.use("Agg")
+        import matplotlib.pyplot as plt
+    except ImportError:
+        plt = None
+    for r, (d, _) in loaded.items():
+        if plt is None:
+            write_csv(d / "series.csv", all_series[r])
+            he = d / "head_entropy.npz"
+            if he.exists():
+                with np.load(he) as z:
+                    np.savetxt(d / "head_entropy_map.csv", z["entropy"], delimiter=",", fmt="%.5f")
+            print(f"matplotlib is not installed: wrote {d / 'series.csv'}")
+        else:
+            plot_run(plt, d, r, all_series[r])
+            print(f"plots -> {d}")
+    if len(runs) > 1:
+        pd = Path(a.output_dir) / "_pairs"
+        pd.mkdir(parents=True, exist_ok=True)
+        shared = sorted(set.intersection(*[set(s) for s in all_series.values()]))
+        pj = pd / "procrustes.json"
+        dist = json.loads(pj.read_text()) if pj.exists() else {}
+        if plt is None:
+            rows = {f"{k}|{r}": all_series[r][k] for k in shared for r in runs}
+            rows.update({f"procrustes|{pair}": v for pair, v in dist.items()})
+            write_csv(pd / "comparison.csv", rows)
+            print(f"matplotlib is not installed: wrote {pd / 'comparison.csv'}")
+            return
+        for k in shared:
+            fig, ax = plt.subplots(figsize=(5.5, 3.2))
+            for r in runs:
+                ax.plot(all_series[r][k], marker="o", ms=3, label=r)
+            ax.set_title(k)
+            ax.legend(fontsize=7)
+            fig.tight_layout()
+            fig.savefig(pd / f"compare_{k}.png", dpi=120)
+            plt.close(fig)
+        if dist:
+            fig, ax = plt.subplots(figsize=(5.5, 3.2))
+            for pair, v in dist.items():
+                ax.plot(range(-1, len(v) - 1), v, marker="o", ms=3, label=pair)
+            ax.set_xlabel("layer (-1 = embeddings)")
+            ax.set_ylabel("Procrustes distance")
+            ax.legend(fontsize=7)
+            fig.tight_layout()
+            fig.savefig(pd / "procrustes.png", dpi=120)
+            plt.close(fig)
+        print(f"comparison plots -> {pd}")
 
 
 if __name__ == "__main__":
