@@ -114,3 +114,51 @@ def test_text_quality_metrics_on_known_text(tmp_path):
     assert set(cmp_["profiles"]) == {"a", "b"} and cmp_["profiles"]["b"]["loop_rate"] == 1.0
     assert cmp_["most_distinctive"]["a"] and (tmp_path / "cmp" / "text_quality_profiles.csv").exists()
     assert "loop_rate" in out
+
+
+def test_concept_geometry_statistics_on_planted_structure(tmp_path):
+    """Activations with a known shape: a circle, a line, a map, a shared pair direction - and noise as control."""
+    import math
+    rng = np.random.default_rng(0)
+    D, L, T = 32, 3, 2
+    basis = np.linalg.qr(rng.normal(size=(D, D)))[0]
+
+    def embed(low):                                      # [items, k] -> [T, items, L, D]: layer 0 is noise, the others carry it
+        n, k = low.shape
+        x = np.zeros((T, n, L, D), dtype=np.float32)
+        for t in range(T):
+            x[t, :, 0] = rng.normal(size=(n, D))
+            for l in (1, 2):
+                x[t, :, l] = low @ basis[:k] * 5 + rng.normal(size=(n, D)) * 0.05
+        return x
+    ang = np.arange(12) / 12 * 2 * math.pi
+    coords = np.stack([rng.uniform(25, 49, 20), rng.uniform(-124, -70, 20)], 1)
+    pair_base = rng.normal(size=(6, 4))
+    pairs = np.zeros((12, 5))
+    pairs[0::2, :4], pairs[1::2, :4], pairs[1::2, 4] = pair_base, pair_base, 3.0      # b = a + one shared direction
+    sets = {"ring": ("cyclic", embed(np.stack([np.cos(ang), np.sin(ang)], 1)), {}),
+            "line": ("ordinal", embed(np.arange(10, dtype=float)[:, None] / 3), {}),
+            "map": ("geographic", embed(np.stack([coords[:, 1], coords[:, 0]], 1) / 10), {"coordinates": coords.tolist()}),
+            "pairs": ("paired", embed(pairs), {}),
+            "noise": ("cyclic", rng.normal(size=(T, 9, L, D)).astype(np.float32), {})}
+    d = tmp_path / "cg"
+    d.mkdir()
+    meta = {"run": "planted", "sets": {}}
+    for name, (kind, acts, extra) in sets.items():
+        np.savez_compressed(d / f"{name}.npz", acts=acts, pooled=acts, last_tok=acts, token_counts=np.ones(acts.shape[:2], dtype=np.int32))
+        meta["sets"][name] = {"kind": kind, "tier": 1, "items": [str(i) for i in range(acts.shape[1])], **extra}
+    (d / "meta.json").write_text(json.dumps(meta))
+    run("analyze_concept_geometry.py", "--input", d, "--n-perm", 99)
+    ana = json.loads((d / "analysis.json").read_text())["sets"]
+    ring, line, geo, pr, noise = (ana[k] for k in ("ring", "line", "map", "pairs", "noise"))
+    assert ring["best_layer"]["r"] > 0.9 and ring["best_layer"]["p"] <= 0.02 and ring["best_layer"]["layer"] in (1, 2)
+    assert abs(abs(ring["per_layer"][1]["cyclic"]["winding"]) - 1.0) < 0.05 and ring["per_layer"][1]["cyclic"]["knn_overlap"] == 1.0
+    assert ring["first_significant_layer"] == 1                              # layer 0 is noise
+    assert line["best_layer"]["r"] > 0.95 and line["per_layer"][2]["ordinal"]["pc1_rank_correlation"] > 0.99
+    assert line["per_layer"][2]["direction"]["mean_cosine"] > 0.9 and line["per_layer"][2]["direction"]["z"] > 5
+    assert geo["best_layer"]["r"] > 0.9 and geo["per_layer"][1]["geographic"]["map_fit"] > 0.9
+    assert pr["per_layer"][1]["paired"]["completion_accuracy"] == 1.0 and pr["per_layer"][1]["paired"]["mean_cosine"] > 0.9
+    assert pr["per_layer"][0]["paired"]["completion_accuracy"] < 0.5
+    assert noise["best_layer"]["r"] < 0.5 and noise["significant_layers"] <= 1
+    assert ring["per_layer"][1]["smoothness_to_next"] > 0.9 > ring["per_layer"][0]["smoothness_to_next"]
+    assert ring["per_layer"][1]["subspace"]["top2_variance"] > 0.95 and ring["per_layer"][1]["template"]["distance_agreement"] > 0.9

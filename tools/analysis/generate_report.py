@@ -324,9 +324,16 @@ def build(run: str, rd: Path, theme: str, metrics: Optional[Path] = None) -> str
             body += f"<h4>{html.escape(name)} ({s['kind']})</h4>"
             if "best_layer" in s:
                 body += table(flat(s["best_layer"]))
-            key = s["kind"] if s["kind"] in ("cyclic", "ordinal") else None
+            key = s["kind"] if s["kind"] in ("cyclic", "ordinal", "geographic") else None
             if key and s["per_layer"] and key in s["per_layer"][0]:
                 body += spark([r[key]["r"] for r in s["per_layer"]], ac)
+            if s["kind"] == "paired" and s["per_layer"] and "paired" in s["per_layer"][0]:
+                body += spark([r["paired"]["completion_accuracy"] for r in s["per_layer"]], ac)
+            if s.get("first_significant_layer") is not None:
+                body += f"<p>structure significant (p &lt; 0.05) from layer {s['first_significant_layer']} on, in {s['significant_layers']} layers</p>"
+        if cg.get("summary"):
+            found = [n for n, v in cg["summary"].items() if v.get("p", 1.0) < 0.05]
+            hero.append(("concept sets with structure", f"{len(found)} / {len(cg['summary'])}", "Mantel p < 0.05 at the best layer"))
         body += images(rd / "concept_geometry")
         sec.append(("Concept geometry", body))
     if not sec:
