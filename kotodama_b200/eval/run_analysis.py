@@ -1,5 +1,7 @@
-"""Run-level analysis over JSONL metrics: endpoint summaries, training dynamics, geometric
-health, run comparison, 2x2 factorial interaction and comparison against a reference run.
+"""Run-level analysis over JSONL metrics: endpoint summaries, training dynamics (multi-window slopes,
+inflection points, rolling statistics, plateaus, jumps), geometric health (per-layer records, landmark
+profiles, depth gradient), run comparison with direction-aware deltas, 2x2 factorial interaction with its
+classification, and comparison against a reference run.  Pure functions over step-indexed dicts.
 
 Function set and result keys follow ``src/eval/run_analysis.py`` of the reference
 (``endpoint_summary :47``, ``training_dynamics :123``, ``geometric_health :410``,
@@ -118,29 +120,87 @@ def _jumps(series: list[tuple[int, float]], z: float = 4.0) -> list[dict[str, An
     return [{"step": series[i + 1][0], "delta": d, "z": (d - m) / sd} for i, d in enumerate(diffs) if abs(d - m) > z * sd]
 
 
+def _slope_at(series: list[tuple[int, float]], step: int, window: int) -> Optional[float]:
+    """Least-squares slope over the points within ``window`` steps before ``step``."""
+    return _slope([p for p in series if step - window <= p[0] <= step])
+
+
+def _windowed_slopes(series: list[tuple[int, float]], window: int) -> list[tuple[int, float]]:
+    """Slope of every consecutive stretch of ``window`` steps: [(stretch end, slope)]."""
+    if len(series) < 3:
+        return []
+    out, lo = [], series[0][0]
+    while lo < series[-1][0]:
+        seg = [p for p in series if lo <= p[0] <= lo + window]
+        sl = _slope(seg) if len(seg) >= 3 else None
+        if sl is not None:
+            out.append((seg[-1][0], sl))
+        lo += window
+    return out
+
+
+def _sign_changes(series: list[tuple[int, float]], floor: float = 0.0) -> list[dict[str, Any]]:
+    """Steps at which the series crosses zero; values within ``floor`` of zero (rounding noise) do not count."""
+    big = [(st, v) for st, v in series if abs(v) > floor]
+    return [{"step": s1, "from": a, "to": b} for (_, a), (s1, b) in zip(big, big[1:]) if a * b < 0]
+
+
+def _percentile(v: list[float], q: float) -> float:
+    w = sorted(v)
+    at = q * (len(w) - 1)
+    lo = int(at)
+    return w[lo] + (w[min(lo + 1, len(w) - 1)] - w[lo]) * (at - lo)
+
+
+def _rolling_stats(series: list[tuple[int, float]], window: int) -> list[dict[str, float]]:
+    """Mean, spread and quartiles over consecutive stretches of ``window`` steps."""
+    out, lo = [], series[0][0] if series else 0
+    while series and lo <= series[-1][0]:
+        w = [v for st, v in series if lo <= st < lo + window]
+        if len(w) >= 2:
+            out.append({"step": lo + window, "mean": sum(w) / len(w), "std": _std(w), "p25": _percentile(w, 0.25),
+                        "p75": _percentile(w, 0.75)})
+        lo += window
+    return out
+
+
 def training_dynamics(data: StepData, metric_keys: Optional[list[str]] = None) -> dict[str, Any]:
-    """Per metric: values at landmark fractions of the run, slopes over trailing windows, plateaus,
-    jumps and slope sign changes."""
+    """Per metric: values and multi-window slopes at landmark fractions of the run, slopes over trailing
+    windows, the second derivative's sign changes (inflection points), rolling statistics with a stability
+    score (late spread / early spread), plateaus, jumps and slope sign changes."""
     out: dict[str, Any] = {}
     max_step = max(data) if data else 0
     for key in metric_keys or DEFAULT_DYNAMICS_METRICS:
         series = extract_series(data, key)
         if len(series) < 3:
             continue
-        m: dict[str, Any] = {"n_points": len(series)}
+        m: dict[str, Any] = {"n_points": len(series), "max_step": max_step}
         m["landmarks"] = {f"{int(p * 100)}%": _at(data, int(max_step * p), key, tolerance=max(500, max_step // 20))
                           for p in LANDMARK_PCTS}
+        m["slopes_at_landmarks"] = {f"{int(p * 100)}%": {f"w{w}": _slope_at(series, int(max_step * p), w) for w in SLOPE_WINDOWS}
+                                    for p in LANDMARK_PCTS}
         m["slopes"] = {}
         for w in SLOPE_WINDOWS:
             tail = [p for p in series if p[0] >= max_step - w]
             sl = _slope(tail)
             if sl is not None:
                 m["slopes"][f"last_{w}"] = sl
+        span = max(series[-1][0] - series[0][0], 1)
+        coarse = _windowed_slopes(series, max(span // 20, 1))
+        curv_floor = 1e-6 * max((abs(v) for _, v in coarse), default=0.0) / span
+        m["inflection_points"] = _sign_changes(_windowed_slopes(coarse, max(span // 5, 1)), curv_floor) if len(coarse) >= 5 else []
+        roll_w = _rolling_stats(series, max(span // 20, 1))
+        if roll_w:
+            m["rolling_stats"] = roll_w
+            q = len(roll_w) // 4
+            early, late = [r["std"] for r in roll_w[:max(q, 1)] if r["std"] > 0], [r["std"] for r in roll_w[-max(q, 1):] if r["std"] > 0]
+            if early and late:
+                m["stability_score"] = (sum(late) / len(late)) / max(sum(early) / len(early), 1e-10)
         m["plateaus"] = _plateaus(series)
         m["jumps"] = _jumps(series)
         win = max(3, len(series) // 20)
         local = [(_slope(series[i - win: i + 1]) or 0.0, series[i][0]) for i in range(win, len(series))]
-        m["slope_sign_changes"] = [s for (a, _), (b, s) in zip(local, local[1:]) if a * b < 0]
+        m["slope_sign_changes"] = [st for (a, _), (b, st) in zip(local, local[1:]) if a * b < 0]
         roll = _rolling(series, win)
         m["final_rolling_mean"], m["final_rolling_std"] = roll[-1][1], roll[-1][2]
         out[key] = m
@@ -157,9 +217,18 @@ def _discover_layers(data: StepData) -> list[int]:
     return sorted(layers)
 
 
+GEO_LANDMARKS = {"early": 0.10, "quarter": 0.25, "mid": 0.50, "three_quarter": 0.75, "late": 0.90, "final": 1.0}
+LAYER_METRICS = [f"stable_rank_{p}" for p in STABLE_RANK_PROJECTIONS] + ["attn_entropy_mean", "attn_entropy_std", "anisotropy", "dead_units"]
+
+
 def geometric_health(data: StepData) -> dict[str, Any]:
+    """Per-layer geometric record (initial / final / minimum of every per-layer metric), the same metrics as
+    per-layer profiles at landmark fractions of the run (snapped to steps that carry geometric data), the
+    depth gradient (first / middle / last sampled layer at the end of the run), the stability of RankMe
+    (late spread / early spread), the routing weights of the final AttnRes call, and warning flags."""
     out: dict[str, Any] = {"layers": {}}
-    for layer in _discover_layers(data):
+    layers = _discover_layers(data)
+    for layer in layers:
         rec: dict[str, Any] = {}
         for proj in STABLE_RANK_PROJECTIONS:
             s = extract_series(data, f"geo/layer_{layer}/stable_rank_{proj}")
@@ -170,49 +239,107 @@ def geometric_health(data: StepData) -> dict[str, Any]:
             if s:
                 rec[name] = {"initial": s[0][1], "final": s[-1][1]}
         out["layers"][layer] = rec
+    geo_steps = sorted(st for st in data if any(k.startswith("geo/layer_") for k in data[st]))
+    if layers and geo_steps:
+        max_step = max(data)
+        marks = {n: min(geo_steps, key=lambda st: abs(st - int(max_step * p))) for n, p in GEO_LANDMARKS.items()}
+        out["landmarks"] = marks
+        out["profiles"] = {n: {"step": st, **{f"layer_{l}": {m: data[st].get(f"geo/layer_{l}/{m}") for m in LAYER_METRICS}
+                                              for l in layers}} for n, st in marks.items()}
+        if len(layers) >= 3:
+            pick = {"first": layers[0], "mid": layers[len(layers) // 2], "last": layers[-1]}
+            final = marks["final"]
+            out["depth_gradient"] = {"layers": pick, **{m: {w: data[final].get(f"geo/layer_{l}/{m}") for w, l in pick.items()}
+                                                        for m in ("attn_entropy_mean", "anisotropy", "stable_rank_q_proj")}}
     alphas = {k.rsplit("_", 1)[1]: extract_series(data, k)[-1][1] for k in extract_keys_matching(data, "attnres/final_alpha/")
               if extract_series(data, k)}
     if alphas:
         out["attnres_final_alpha"] = alphas
     flags = []
     rk = extract_series(data, "geo/rankme_last")
+    if len(rk) >= 8:
+        q = len(rk) // 4
+        out["rankme_stability"] = _std([v for _, v in rk[-q:]]) / max(_std([v for _, v in rk[:q]]), 1e-10)
     if rk and rk[-1][1] < 0.5 * max(v for _, v in rk):
         flags.append("rankme_collapse")
     for layer, rec in out["layers"].items():
         if rec.get("dead_units", {}).get("final", 0) > 0.1:
             flags.append(f"dead_units_layer_{layer}")
+        ent = rec.get("attn_entropy_mean", {})
+        if ent and ent.get("initial") and ent["final"] < 0.25 * ent["initial"]:
+            flags.append(f"attention_collapse_layer_{layer}")
     out["flags"] = flags
     return out
 
 
+LOWER_IS_BETTER = {"loss_final", "loss_min", "ppl_final", "ww_alpha_final"}
+COMPARISON_KEYS = ["loss_final", "loss_min", "ppl_final", "rankme_final", "rankme_min", "rankme_rebound_ratio", "ww_alpha_final",
+                   "ww_healthy_frac_final", "twonn_id_final", "avg_tokens_per_sec", "tokens_B"]
+
+
 def compare_runs(runs: dict[str, StepData], metric: str = "train/loss", at_steps: Optional[list[int]] = None
                  ) -> dict[str, Any]:
+    """Endpoint summaries side by side, ``metric`` at matched steps, a ranking by its last matched value, and
+    for every run after the first the deltas of the endpoint figures against the first run, each marked
+    better / worse according to the figure's direction (loss down, RankMe up, ...)."""
     summaries = {n: endpoint_summary(d) for n, d in runs.items()}
     common = min((s["max_step"] for s in summaries.values()), default=0)
     steps = at_steps or [int(common * p) for p in (0.25, 0.5, 0.75, 1.0)]
     table = {n: {s: _at(d, s, metric, tolerance=max(500, common // 20)) for s in steps} for n, d in runs.items()}
     final = {n: t[steps[-1]] for n, t in table.items() if t.get(steps[-1]) is not None}
     ranking = sorted(final, key=final.get)
+    names = list(runs)
+    deltas: dict[str, dict[str, Any]] = {}
+    for n in names[1:]:
+        row = {}
+        for k in COMPARISON_KEYS:
+            a, b = summaries[names[0]].get(k), summaries[n].get(k)
+            if isinstance(a, (int, float)) and isinstance(b, (int, float)):
+                d = b - a
+                better = d < 0 if k in LOWER_IS_BETTER else d > 0
+                row[k] = {"delta": d, "relative": d / abs(a) if a else None,
+                          "verdict": "same" if d == 0 else ("better" if better else "worse")}
+        deltas[n] = row
     return {"summaries": summaries, "metric": metric, "steps": steps, "table": table, "ranking": ranking,
-            "best": ranking[0] if ranking else None}
+            "best": ranking[0] if ranking else None, "baseline": names[0] if names else None, "deltas": deltas}
 
 
-def factorial_analysis(runs: dict[tuple[int, int], StepData], metric: str = "train/loss", step: Optional[int] = None
-                       ) -> dict[str, Any]:
+def _factorial_cell(y: dict[tuple[int, int], float]) -> dict[str, Any]:
+    a = ((y[(1, 0)] + y[(1, 1)]) - (y[(0, 0)] + y[(0, 1)])) / 2
+    b = ((y[(0, 1)] + y[(1, 1)]) - (y[(0, 0)] + y[(1, 0)])) / 2
+    inter = (y[(1, 1)] - y[(1, 0)]) - (y[(0, 1)] - y[(0, 0)])
+    additive = y[(0, 0)] + (y[(1, 0)] - y[(0, 0)]) + (y[(0, 1)] - y[(0, 0)])         # what "no interaction" predicts for both
+    scale = max(abs(y[(1, 0)] - y[(0, 0)]), abs(y[(0, 1)] - y[(0, 0)]), 1e-12)
+    rel = inter / scale
+    kind = "additive" if abs(rel) < 0.1 else ("reinforcing" if (inter < 0) == (a + b < 0) else "offsetting")
+    return {"values": {f"{k[0]}{k[1]}": v for k, v in y.items()}, "main_effect_a": a, "main_effect_b": b, "interaction": inter,
+            "additive_prediction": additive, "relative_interaction": rel, "classification": kind}
+
+
+def factorial_analysis(runs: dict[tuple[int, int], StepData], metric: str = "train/loss", step: Optional[int] = None,
+                       extra_metrics: Optional[list[str]] = None) -> dict[str, Any]:
     """2x2 design ``{(a, b): run}`` with a, b in {0, 1}: main effects and the interaction
-    ``(y11 - y10) - (y01 - y00)`` of ``metric`` at ``step`` (default: last common step)."""
+    ``(y11 - y10) - (y01 - y00)`` of ``metric`` at ``step`` (default: last common step), what a purely
+    additive model predicts for the cell with both factors, the interaction relative to the larger
+    single-factor effect and its classification (additive below 10 %; reinforcing when it pushes the same
+    way as the main effects, offsetting otherwise).  ``extra_metrics``: the same for further metrics."""
     need = [(0, 0), (0, 1), (1, 0), (1, 1)]
     if any(k not in runs for k in need):
         raise ValueError("factorial_analysis needs runs for (0,0), (0,1), (1,0), (1,1)")
     step = step if step is not None else min(max(d) for d in runs.values())
-    y = {k: _at(runs[k], step, metric, tolerance=max(500, step // 20)) for k in need}
+    tol = max(500, step // 20)
+    y = {k: _at(runs[k], step, metric, tolerance=tol) for k in need}
     if any(v is None for v in y.values()):
         return {"step": step, "values": y, "error": "metric missing for some cell"}
-    a = ((y[(1, 0)] + y[(1, 1)]) - (y[(0, 0)] + y[(0, 1)])) / 2
-    b = ((y[(0, 1)] + y[(1, 1)]) - (y[(0, 0)] + y[(1, 0)])) / 2
-    inter = (y[(1, 1)] - y[(1, 0)]) - (y[(0, 1)] - y[(0, 0)])
-    return {"step": step, "values": {f"{k[0]}{k[1]}": v for k, v in y.items()}, "main_effect_a": a,
-            "main_effect_b": b, "interaction": inter}
+    out = {"step": step, "metric": metric, **_factorial_cell(y)}
+    others = {}
+    for key in extra_metrics or []:
+        ys = {k: _at(runs[k], step, key, tolerance=tol) for k in need}
+        if all(v is not None for v in ys.values()):
+            others[key] = _factorial_cell(ys)
+    if others:
+        out["other_metrics"] = others
+    return out
 
 
 def reference_comparison(run: StepData, reference: StepData, metrics: Optional[list[str]] = None) -> dict[str, Any]:
@@ -225,6 +352,16 @@ def reference_comparison(run: StepData, reference: StepData, metrics: Optional[l
         a, b = _at(run, common, key, tolerance=max(500, common // 20)), _at(reference, common, key, tolerance=max(500, common // 20))
         if a is not None and b is not None:
             out["metrics"][key] = {"run": a, "reference": b, "delta": a - b, "ratio": a / b if b else None}
+    # the same deltas along the run: does the gap open early or late?
+    out["landmarks"] = {}
+    for p in LANDMARK_PCTS:
+        st = int(common * p)
+        row = {}
+        for key in metrics:
+            a, b = _at(run, st, key, tolerance=max(500, common // 20)), _at(reference, st, key, tolerance=max(500, common // 20))
+            if a is not None and b is not None:
+                row[key] = a - b
+        out["landmarks"][f"{int(p * 100)}%"] = {"step": st, "delta": row}
     ref_loss = extract_series(reference, "train/loss")
     if ref_loss:
         target = ref_loss[-1][1]

@@ -69,12 +69,27 @@ def test_perplexity_and_metrics_analysis(tmp_path):
     assert summ["max_step"] == 1990 and abs(summ["loss_final"] - 3.01) < 1e-9 and summ["rankme_final"] == 65.0
     dyn = run_analysis.training_dynamics(data)
     assert abs(dyn["train/loss"]["slopes"]["last_500"] + 0.001) < 1e-9 and dyn["train/loss"]["jumps"] == []
+    lm = dyn["train/loss"]["slopes_at_landmarks"]["50%"]
+    assert abs(lm["w100"] + 0.001) < 1e-9 and abs(lm["w500"] + 0.001) < 1e-9          # a straight line: same slope at every scale
+    assert dyn["train/loss"]["inflection_points"] == [] and dyn["train/loss"]["rolling_stats"][0]["p25"] < dyn["train/loss"]["rolling_stats"][0]["p75"]
+    assert 0.5 < dyn["train/loss"]["stability_score"] < 2.0
     gh = run_analysis.geometric_health(data)
     assert 0 in gh["layers"] and gh["flags"] == []
+    assert gh["landmarks"]["final"] == 1500 and gh["profiles"]["mid"]["layer_0"]["stable_rank_q_proj"] == 10.0
     worse = {s: {"train/loss": v["train/loss"] + 0.5} for s, v in data.items() if "train/loss" in v}
     cmp_ = run_analysis.compare_runs({"a": data, "b": worse})
-    assert cmp_["best"] == "a"
+    assert cmp_["best"] == "a" and cmp_["baseline"] == "a"
+    assert cmp_["deltas"]["b"]["loss_final"]["verdict"] == "worse" and abs(cmp_["deltas"]["b"]["loss_final"]["delta"] - 0.5) < 1e-9
     fa = run_analysis.factorial_analysis({(0, 0): worse, (0, 1): data, (1, 0): data, (1, 1): data})
     assert abs(fa["interaction"] - 0.5) < 1e-9
+    # either factor alone gains 0.5, both together gain 0.5 too: the second factor adds nothing on top of the first
+    assert fa["classification"] == "offsetting" and abs(fa["additive_prediction"] - (fa["values"]["00"] - 1.0)) < 1e-9
+    better2 = {s: {"train/loss": v["train/loss"] - 0.5} for s, v in data.items() if "train/loss" in v}
+    assert run_analysis.factorial_analysis({(0, 0): worse, (0, 1): data, (1, 0): data, (1, 1): better2})["classification"] == "additive"
     rc = run_analysis.reference_comparison(data, worse)
     assert rc["metrics"]["train/loss"]["delta"] < 0 and rc["steps_to_reference_final_loss"] < 1990
+    assert abs(rc["landmarks"]["50%"]["delta"]["train/loss"] + 0.5) < 1e-9
+    # a curve that bends: fast early, flat late -> one inflection-free decay but a plateau and a stability score below 1
+    bend = {s: {"train/loss": 2.0 + 3.0 * 0.995 ** s + (0.05 if s < 500 and s % 20 == 0 else 0.0)} for s in range(0, 4000, 10)}
+    d2 = run_analysis.training_dynamics(bend, ["train/loss"])["train/loss"]
+    assert d2["stability_score"] < 0.5 and d2["plateaus"] and abs(d2["slopes"]["last_1000"]) < 1e-4
