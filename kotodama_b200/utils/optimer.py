@@ -1,8 +1,10 @@
-"""Per-op device timing: wraps an ops backend so that every call is bracketed by CUDA events
-and aggregated by op name.  Used by ``bench.py --op-times`` and the kernel benchmarks; adds two
-event records per call, so totals are slightly above an untimed run."""
+"""Per-op timing: wraps an ops backend so that every call is bracketed by CUDA events (host clock
+where there is no GPU: the CPU back end runs its ops synchronously) and aggregated by op name.  Used by
+``bench.py --op-times``, ``tools/profile_step.py`` and the kernel benchmarks; adds two event records per
+call, so totals are slightly above an untimed run."""
 from __future__ import annotations
 
+import time
 from collections import defaultdict
 from typing import Any
 
@@ -13,8 +15,9 @@ class TimedOps:
     def __init__(self, inner: Any, prefix: str = "") -> None:
         self._inner = inner
         self._prefix = prefix
-        self._events: list[tuple[str, torch.cuda.Event, torch.cuda.Event]] = []
+        self._events: list[tuple[str, Any, Any]] = []      # (label, start, end): CUDA events, or host seconds
         self.enabled = True
+        self._cuda = torch.cuda.is_available()
 
     def __getattr__(self, name: str) -> Any:
         attr = getattr(self._inner, name)
@@ -24,10 +27,15 @@ class TimedOps:
         def wrapped(*a: Any, **k: Any) -> Any:
             if not self.enabled:
                 return attr(*a, **k)
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            out = attr(*a, **k)
-            e1.record()
+            if self._cuda:
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                out = attr(*a, **k)
+                e1.record()
+            else:
+                e0 = time.perf_counter()
+                out = attr(*a, **k)
+                e1 = time.perf_counter()
             label = self._prefix + name
             if name.startswith("gemm") and a:
                 label = f"{name}[{'x'.join(map(str, a[0].shape))}|{'x'.join(map(str, a[1].shape))}]"
@@ -40,11 +48,12 @@ class TimedOps:
         self._events.clear()
 
     def summary(self) -> list[tuple[str, float, int]]:
-        torch.cuda.synchronize()
+        if self._cuda:
+            torch.cuda.synchronize()
         tot: dict[str, float] = defaultdict(float)
         cnt: dict[str, int] = defaultdict(int)
         for name, e0, e1 in self._events:
-            tot[name] += e0.elapsed_time(e1)
+            tot[name] += e0.elapsed_time(e1) if self._cuda else (e1 - e0) * 1e3
             cnt[name] += 1
         return sorted(((n, t, cnt[n]) for n, t in tot.items()), key=lambda x: -x[1])
 

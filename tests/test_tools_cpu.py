@@ -1,0 +1,82 @@
+"""The command-line tools under tools/ on small inputs, CPU only."""
+import json
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parents[1]
+sys.path.insert(0, str(ROOT / "tools"))
+
+
+def tool(name, *args, timeout=600):
+    r = subprocess.run([sys.executable, str(ROOT / "tools" / name), *map(str, args)], capture_output=True, text=True, cwd=ROOT,
+                       timeout=timeout)
+    assert r.returncode == 0, r.stderr[-2000:]
+    return r.stdout
+
+
+def write_metrics(path: Path, offset: float) -> None:
+    path.parent.mkdir(parents=True, exist_ok=True)
+    with open(path, "w") as fh:
+        for s in range(0, 1000, 10):
+            fh.write(json.dumps({"step": s, "train/loss": 5.0 - 0.002 * s + offset, "perf/tokens_per_sec": 1000.0}) + "\n")
+
+
+def test_pull_metrics_local_runs_and_remote_copy(tmp_path):
+    write_metrics(tmp_path / "run-a" / "metrics.jsonl", 0.0)
+    write_metrics(tmp_path / "run-b" / "metrics.jsonl", 0.3)
+    out = tool("pull_metrics.py", tmp_path / "run-a", tmp_path / "run-b", "--dynamics")
+    lines = [json.loads(l) for l in out.splitlines() if l.startswith("{")]
+    summ = {l["run"]: l for l in lines if "loss_final" in l}
+    assert abs(summ["run-a"]["loss_final"] - 3.02) < 1e-9 and abs(summ["run-b"]["loss_final"] - 3.32) < 1e-9
+    assert any("dynamics" in l for l in lines)
+    rank = next(l for l in lines if "ranking" in l)
+    assert rank["ranking"] == ["run-a", "run-b"] and abs(rank["loss_final_delta"]["run-b"] - 0.3) < 1e-9
+    # the remote copy, with a stand-in for scp that serves one of the two files
+    import pull_metrics
+
+    class Done:
+        def __init__(self, rc, err=""):
+            self.returncode, self.stderr = rc, err
+    calls = []
+
+    def fake_scp(argv, **kw):
+        calls.append(argv)
+        src, dst = argv[-2], argv[-1]
+        if src.endswith("/metrics.jsonl"):
+            Path(dst).write_text((tmp_path / "run-a" / "metrics.jsonl").read_text())
+            return Done(0)
+        return Done(1, "scp: geo_metrics.jsonl: No such file or directory")
+    got = pull_metrics.pull_remote("node7:~/ckpt/run-a/", tmp_path / "pulled", "scp", runner=fake_scp)
+    assert [p.name for p in got] == ["metrics.jsonl"] and len(calls) == 2 and calls[0][0] == "scp"
+    assert calls[0][-2] == "node7:~/ckpt/run-a/metrics.jsonl"
+    assert pull_metrics.human(3 * 1024 * 1024) == "3.0 MB" and pull_metrics.metrics_path(str(tmp_path / "pulled")).name == "metrics.jsonl"
+
+
+def test_log_and_trace_summaries(tmp_path):
+    log = tmp_path / "train.log"
+    with open(log, "w") as fh:
+        for s in range(20):
+            fh.write(f"step={s} | loss={5 - 0.1 * s:.4f} | lr=1e-3 | tok/s={30000 + 100 * s} | tokens=1 | gpu_mem=41.5GB\n")
+            fh.write(f"device-timed: 800.0 ms/step, {40000 + s} tok/s\n")
+    rec = json.loads(tool("extract_benchmark_results.py", log).splitlines()[-1])
+    assert rec["lines"] == 20 and rec["gpu_mem_gb_max"] == 41.5 and abs(rec["loss_last"] - 3.1) < 1e-9
+    assert rec["tok_s_median"] == 31100.0 and rec["device_tok_s_median"] == 40011.0
+    trace = tmp_path / "trace.json"
+    trace.write_text(json.dumps({"traceEvents": [
+        {"cat": "kernel", "name": "gemm_kernel", "dur": 3000}, {"cat": "kernel", "name": "gemm_kernel", "dur": 1000},
+        {"cat": "kernel", "name": "attn_kernel", "dur": 2000}, {"cat": "cpu_op", "name": "aten::mm", "dur": 9999}]}))
+    out = tool("parse_profile.py", trace)
+    rows = [l.split() for l in out.splitlines()[1:]]
+    assert rows[0][0] == "gemm_kernel" and rows[0][1] == "4.00" and rows[0][2] == "2" and rows[1][0] == "attn_kernel"
+
+
+@pytest.mark.parametrize("optimizer", ["muon", "adamw"])
+def test_profile_step_runs_on_cpu(tmp_path, optimizer):
+    out = tool("profile_step.py", "--model", "tiny", "--device", "cpu", "--seq", 48, "--micro_batch", 2, "--steps", 1,
+               "--warmup_steps", 1, "--optimizer", optimizer, "--trace", tmp_path / "t.json")
+    assert "FORWARD_BACKWARD" in out and "OPTIMIZER_STEP" in out and "== ops" in out and "attention_fwd" in out
+    assert ("ns_iteration" in out or "newton" in out.lower()) == (optimizer == "muon")
+    assert (tmp_path / "t.json").stat().st_size > 1000
