@@ -80,3 +80,54 @@ def test_profile_step_runs_on_cpu(tmp_path, optimizer):
     assert "FORWARD_BACKWARD" in out and "OPTIMIZER_STEP" in out and "== ops" in out and "attention_fwd" in out
     assert ("ns_iteration" in out or "newton" in out.lower()) == (optimizer == "muon")
     assert (tmp_path / "t.json").stat().st_size > 1000
+
+
+def test_eval_via_server_against_a_live_server(tmp_path):
+    """The client of track 3 against the real HTTP server (uvicorn in a thread, tiny CPU engine)."""
+    import socket
+    import threading
+    import time
+
+    import torch
+    uvicorn = pytest.importorskip("uvicorn")
+    from kotodama_b200.config import ModelConfig
+    from kotodama_b200.models.llama import KotodamaModel
+    from kotodama_b200.serve.app import ByteTokenizer, create_app
+    from kotodama_b200.serve.engine import ServingEngine
+    torch.manual_seed(0)
+    cfg = ModelConfig(hidden_size=64, num_layers=2, num_attention_heads=2, num_kv_heads=1, head_dim=32, intermediate_size=96,
+                      vocab_size=300, max_position_embeddings=128, attn_res=True, attn_res_n_blocks=2)
+    eng = ServingEngine(KotodamaModel(cfg), device="cpu", dtype=torch.float32, max_batch=8, max_ctx=128)
+    app = create_app(eng, ByteTokenizer(), model_name="tiny")
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    server = uvicorn.Server(uvicorn.Config(app, host="127.0.0.1", port=port, log_level="error"))
+    th = threading.Thread(target=server.run, daemon=True)
+    th.start()
+    try:
+        prompts = tmp_path / "prompts.yaml"
+        prompts.write_text("mini:\n  - \"Once upon\"\n  - \"The river\"\n  - \"In 1987\"\n")
+        r = subprocess.run([sys.executable, str(ROOT / "tools" / "analysis" / "eval_via_server.py"), "--url", f"http://127.0.0.1:{port}",
+                            "--name", "live", "--prompt-set", "mini", "--prompts-file", str(prompts), "--n-samples", "2",
+                            "--max-tokens", "6", "--temperature", "0", "--concurrency", "4", "--wait", "30",
+                            "--output-dir", str(tmp_path / "analysis")], capture_output=True, text=True, cwd=ROOT, timeout=300)
+        assert r.returncode == 0, r.stderr[-2000:]
+        out = json.loads((tmp_path / "analysis" / "live" / "generations.json").read_text())
+        assert out["server_info"]["attn_res"] is True and out["server_stats"]["failed"] == 0 and out["server_stats"]["requests"] == 6
+        assert len(out["generations"]) == 3 and all(len(g["samples"]) == 2 for g in out["generations"])
+        for g in out["generations"]:
+            assert g["samples"][0] == g["samples"][1]                              # greedy
+            assert all(1 <= q["completion_tokens"] <= 6 for q in g["requests"])    # max_new_tokens reached the server
+        # a request the server refuses (prompt longer than the context) is reported, not retried forever
+        prompts.write_text("mini:\n  - \"" + "x" * 300 + "\"\n")
+        r = subprocess.run([sys.executable, str(ROOT / "tools" / "analysis" / "eval_via_server.py"), "--url", f"http://127.0.0.1:{port}",
+                            "--name", "bad", "--prompt-set", "mini", "--prompts-file", str(prompts), "--n-samples", "1",
+                            "--output-dir", str(tmp_path / "analysis")], capture_output=True, text=True, cwd=ROOT, timeout=120)
+        assert r.returncode == 0 and "HTTP 400" in r.stdout
+        bad = json.loads((tmp_path / "analysis" / "bad" / "generations.json").read_text())
+        assert bad["server_stats"]["failed"] == 1 and bad["generations"][0]["requests"][0]["attempts"] == 1
+    finally:
+        server.should_exit = True
+        th.join(timeout=20)
+        app.state.worker.shutdown()
