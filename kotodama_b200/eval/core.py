@@ -233,11 +233,25 @@ def generate(model: KotodamaModel, input_ids: torch.Tensor, max_new_tokens: int 
     return ids
 
 
-def generate_text(model: KotodamaModel, tokenizer: Any, prompt: str, **kw: Any) -> str:
+def generate_text(model: KotodamaModel, tokenizer: Any, prompt: str, details: bool = False, **kw: Any) -> Any:
+    """The continuation of ``prompt`` as text.  ``details=True``: a record with the continuation, the number of
+    new tokens and what ended the sample (``eos``, ``max_tokens`` or ``context``), as the reference's
+    ``generate_text`` returns (``src/eval/generate.py:105-186``)."""
     dev = next(model.parameters()).device
     ids = torch.tensor([tokenizer.encode(prompt)], device=dev)
-    out = generate(model, ids, eos_token_id=getattr(tokenizer, "eos_token_id", None), **kw)
-    return tokenizer.decode(out[0, ids.shape[1]:].tolist(), skip_special_tokens=True)
+    eos = getattr(tokenizer, "eos_token_id", None)
+    out = generate(model, ids, eos_token_id=eos, **kw)
+    new = out[0, ids.shape[1]:].tolist()
+    text = tokenizer.decode(new, skip_special_tokens=True)
+    if not details:
+        return text
+    if new and eos is not None and new[-1] == eos:
+        why = "eos"
+    elif out.shape[1] >= model.config.max_position_embeddings:
+        why = "context"
+    else:
+        why = "max_tokens"
+    return {"prompt": prompt, "continuation": text, "n_tokens": len(new), "stopped_by": why}
 
 
 # ------------------------------------------------------------------------------ perplexity
