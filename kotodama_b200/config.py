@@ -15,7 +15,7 @@ from __future__ import annotations
 import argparse
 import logging
 import math
-from dataclasses import asdict, dataclass, field
+from dataclasses import asdict, dataclass
 from typing import Any, Optional, Sequence
 
 logger = logging.getLogger(__name__)

@@ -11,7 +11,7 @@ from __future__ import annotations
 
 from typing import Any, Optional
 
-from .core import extract_keys_matching, extract_series, get_nearest_step
+from .core import extract_keys_matching, extract_series
 
 StepData = dict[int, dict[str, float]]
 DEFAULT_DYNAMICS_METRICS = ["train/loss", "geo/rankme_last"]

@@ -19,7 +19,6 @@ temperature -> top-k -> top-p -> multinomial, greedy at temperature 0 (``serve.p
 """
 from __future__ import annotations
 
-import math
 import os
 from dataclasses import dataclass, field
 from typing import Any, Optional

@@ -19,7 +19,6 @@ import logging
 import math
 import os
 import time
-from pathlib import Path
 from typing import Any, Optional
 
 import torch
