@@ -131,3 +131,35 @@ def test_eval_via_server_against_a_live_server(tmp_path):
         server.should_exit = True
         th.join(timeout=20)
         app.state.worker.shutdown()
+
+
+def test_visualize_nca_pictures_and_round_trip(tmp_path):
+    """Rule pictures (grid, strip, space-time), the complexity histogram, and decoding a generated token file."""
+    import struct
+    out = tool("visualize_nca.py", "--n-rules", 2, "--grid", 16, "--steps", 12, "--complexity-batch", 6, "--output-dir", tmp_path / "viz")
+    assert "complexity of 6 sampled rules" in out
+    for name in ("rule00_grid.png", "rule00_strip.png", "rule00_spacetime.png", "rule01_grid.png", "complexity_histogram.png", "summary.txt"):
+        assert (tmp_path / "viz" / name).exists(), name
+    png = (tmp_path / "viz" / "rule00_spacetime.png").read_bytes()
+    assert png[:8] == b"\x89PNG\r\n\x1a\n" and png[12:16] == b"IHDR"
+    w, h = struct.unpack(">II", png[16:24])
+    assert w > 12 * 2 and h > 16 * 2                                     # 12 time steps wide, groups x 16 cells high
+    # tokens written by the generator decode back into the grids they came from
+    import numpy as np
+    import torch
+    import visualize_nca as vn
+    from kotodama_b200.nca.generator import NCAConfig, NCARule, simulate_trajectory, tokenize_trajectory
+    cfg = NCAConfig(grid_size=16, num_steps=6)
+    torch.manual_seed(0)
+    rule = NCARule(cfg.d_state, cfg.n_groups, 3, 16, 2)
+    traj = simulate_trajectory(rule, cfg.grid_size, cfg.d_state, cfg.n_groups, cfg.num_steps, cfg.burn_in, 1.0, 0.5, device="cpu",
+                               generator=torch.Generator().manual_seed(0))
+    toks = np.asarray(tokenize_trajectory(traj, cfg.d_state, cfg.patch_size), dtype=np.int64)
+    grids = vn.decode_tokens(toks, cfg)
+    assert grids.shape == (cfg.num_steps * cfg.n_groups, 16, 16)
+    assert np.array_equal(grids.reshape(cfg.num_steps, cfg.n_groups, 16, 16), traj[0].cpu().numpy())
+
+
+def test_smoke_test_tool_passes_on_cpu():
+    out = tool("smoke_test.py", "--device", "cpu", "--steps", 12, timeout=900)
+    assert "FAIL" not in out and ("ok" in out.lower() or "pass" in out.lower())

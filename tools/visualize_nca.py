@@ -5,10 +5,14 @@
     python tools/visualize_nca.py --from-data data/nca.bin --output-dir outputs/nca_viz   # decode a token file
 
 For every sampled rule: a grid image (time steps left to right, one row per channel group), a
-strip of evenly spaced frames of channel 0, the rule's hyper-parameters and its gzip complexity
-(the Class-IV filter keeps ratios in [0.4, 0.7]); a summary text file lists them all.  With
-``--from-data`` the uint16 tokens are decoded back into grids (patch codes -> cells, frames
-delimited by START/END) and the first trajectories are drawn the same way.
+strip of evenly spaced frames of channel 0, a space-time image (one spatial row of every group
+followed through ALL time steps: time runs left to right, space top to bottom - gliders show as
+diagonals, frozen rules as horizontal stripes, noise as static), the rule's hyper-parameters and
+its gzip complexity (the Class-IV filter keeps ratios in [0.4, 0.7]); a summary text file lists
+them all.  ``--complexity-batch N`` also samples N more rules (short runs), and writes the
+distribution of their gzip ratios as a histogram image and as numbers: how many rules the filter
+would keep.  With ``--from-data`` the uint16 tokens are decoded back into grids (patch codes ->
+cells, frames delimited by START/END) and the first trajectories are drawn the same way.
 
 Images are written as PNG by a small encoder in this file (zlib only), so the tool has no
 plotting dependency; states are coloured with an evenly spaced hue wheel, one colour per state
@@ -64,14 +68,44 @@ def tile(frames: np.ndarray, pal: np.ndarray, cell: int, gap: int = 2) -> np.nda
     return out
 
 
+def space_time(traj: np.ndarray, pal: np.ndarray, cell: int = 4, gap: int = 2) -> np.ndarray:
+    """``traj[T, G, H, W]`` -> one image with a band per group: the middle row of the grid at every time step
+    (x = time, y = position in the row)."""
+    T, G, H, W = traj.shape
+    out = np.full((G * (W * cell + gap) + gap, T * cell + 2 * gap, 3), 40, dtype=np.uint8)
+    for g in range(G):
+        band = pal[traj[:, g, H // 2, :].T % len(pal)].repeat(cell, 0).repeat(cell, 1)      # [W, T] -> pixels
+        y = gap + g * (W * cell + gap)
+        out[y:y + W * cell, gap:gap + T * cell] = band
+    return out
+
+
+def histogram(values: list[float], lo: float, hi: float, keep: tuple[float, float], bins: int = 30, w: int = 14, h: int = 160) -> np.ndarray:
+    """Bar chart of ``values`` over [lo, hi]; bars inside ``keep`` are drawn in the kept colour."""
+    counts, edges = np.histogram(np.clip(values, lo, hi), bins=bins, range=(lo, hi))
+    top = max(int(counts.max()), 1)
+    img = np.full((h + 12, bins * w + 8, 3), 24, dtype=np.uint8)
+    for i, c in enumerate(counts):
+        mid = (edges[i] + edges[i + 1]) / 2
+        colour = (90, 200, 120) if keep[0] <= mid <= keep[1] else (200, 110, 90)
+        bar = int(round(c / top * h))
+        if bar:
+            img[6 + h - bar:6 + h, 4 + i * w + 1:4 + (i + 1) * w - 1] = colour
+    for edge in keep:                                     # thin lines at the filter's limits
+        x = 4 + int((edge - lo) / (hi - lo) * bins * w)
+        img[4:8 + h, x:x + 1] = (230, 230, 230)
+    return img
+
+
 def draw_trajectory(traj: np.ndarray, d_state: int, prefix: str, n_frames: int = 8) -> None:
-    """``traj[T, G, H, W]``: grid image (groups x sampled time steps) and a strip of channel 0."""
+    """``traj[T, G, H, W]``: grid image (groups x sampled time steps), a strip of channel 0, a space-time image."""
     T, G, H, W = traj.shape
     pal = palette(d_state)
     steps = np.unique(np.linspace(0, T - 1, min(n_frames, T)).astype(int))
     cell = max(2, 128 // H)
     write_png(prefix + "_grid.png", tile(traj[steps].transpose(1, 0, 2, 3), pal, cell))
     write_png(prefix + "_strip.png", tile(traj[steps, 0][None], pal, cell * 2))
+    write_png(prefix + "_spacetime.png", space_time(traj, pal, max(2, 96 // W)))
 
 
 def from_generator(a: argparse.Namespace) -> None:
@@ -96,6 +130,24 @@ def from_generator(a: argparse.Namespace) -> None:
         line = (f"rule {r:02d}: kernel {p['kernel_size']} hidden {p['hidden_dim']}x{p['num_hidden_layers']} "
                 f"identity_bias {p['identity_bias']:.2f} temperature {p['temperature']:.2f} | gzip {ratio:.3f} ({verdict}) "
                 f"| cells changing per step {change:.3f} | {len(toks)} tokens")
+        print(line)
+        lines.append(line)
+    if a.complexity_batch > 0:
+        short = NCAConfig(grid_size=a.grid, num_steps=min(a.steps, 32))
+        ratios = []
+        for r in range(a.complexity_batch):
+            p = sample_rule_config(short, rng)
+            torch.manual_seed(a.seed + 1000 + r)
+            rule = NCARule(short.d_state, short.n_groups, p["kernel_size"], p["hidden_dim"], p["num_hidden_layers"]).to(a.device)
+            traj = simulate_trajectory(rule, short.grid_size, short.d_state, short.n_groups, short.num_steps, short.burn_in,
+                                       p["identity_bias"], p["temperature"], device=a.device,
+                                       generator=gen if a.device == "cpu" else None)
+            ratios.append(compute_gzip_complexity(tokenize_trajectory(traj, short.d_state, short.patch_size)))
+        kept = sum(cfg.gzip_lower <= x <= cfg.gzip_upper for x in ratios)
+        write_png(os.path.join(a.output_dir, "complexity_histogram.png"),
+                  histogram(ratios, 0.0, 1.0, (cfg.gzip_lower, cfg.gzip_upper)))
+        line = (f"complexity of {len(ratios)} sampled rules: min {min(ratios):.3f} median {float(np.median(ratios)):.3f} "
+                f"max {max(ratios):.3f}; the filter [{cfg.gzip_lower}, {cfg.gzip_upper}] keeps {kept} ({100 * kept / len(ratios):.0f} %)")
         print(line)
         lines.append(line)
     with open(os.path.join(a.output_dir, "summary.txt"), "w") as fh:
@@ -142,6 +194,7 @@ def main() -> None:
     ap.add_argument("--grid", type=int, default=32)
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--frames", type=int, default=8, help="time steps shown per image")
+    ap.add_argument("--complexity-batch", type=int, default=0, help="also sample this many rules and draw the distribution of their gzip ratios")
     a = ap.parse_args()
     os.makedirs(a.output_dir, exist_ok=True)
     if a.from_data:
