@@ -163,3 +163,20 @@ def test_visualize_nca_pictures_and_round_trip(tmp_path):
 def test_smoke_test_tool_passes_on_cpu():
     out = tool("smoke_test.py", "--device", "cpu", "--steps", 12, timeout=900)
     assert "FAIL" not in out and ("ok" in out.lower() or "pass" in out.lower())
+
+
+def test_benchmark_matrix_on_the_tiny_cpu_configuration(tmp_path):
+    out = tool("benchmark_matrix.py", "matrix", "--config", "configs/tiny-cpu.yaml", "--gpus", 1, "--only", "native,adamw_only",
+               "--steps", 6, "--skip-lines", 1, "--out", tmp_path / "bm", "--", "--log_every", 1, timeout=900)
+    recs = [json.loads(l) for l in (tmp_path / "bm" / "results_summary.jsonl").read_text().splitlines()]
+    assert [r["name"] for r in recs] == ["native", "adamw_only"] and all(r["exit_code"] == 0 for r in recs)
+    assert all(r["tok_s_median"] > 0 and r["lines"] == 6 for r in recs) and "--adamw_only" in recs[1]["flags"]
+    assert "--log_every 1" in recs[0]["flags"] and "vs first" in out and "1.00x" in out
+    meta = json.loads((tmp_path / "bm" / "metadata.json").read_text())
+    assert meta["mode"] == "matrix" and set(meta["runs"]) == {"native", "adamw_only"} and "torch_version" in meta
+    # the canary mode, commands only
+    dry = tool("benchmark_matrix.py", "canary", "--models", "3b,8b", "--gpus", 8, "--dry-run", "--out", tmp_path / "c", "--", "--fp8")
+    assert "--nproc-per-node 8 --master-addr 127.0.0.1" in dry and "canary-3b.yaml" in dry and "canary-8b.yaml" in dry and "--fp8" in dry
+    import benchmark_matrix as bm
+    text = bm.estimates([{"name": "3b", "tok_s_median": 360000.0, "gpu_mem_gb_max": 120.0}])
+    assert "50 B tokens ->   1.6 days" in text and "250 B tokens" in text
