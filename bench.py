@@ -271,8 +271,10 @@ def main() -> None:
                            "parallelism": f"tp{world}", "timing": "wall clock, device synchronize around every step, max over ranks"},
                 "prefill_tokens_per_sec": out["prefill_tok_s"], "p50_token_latency_ms": out["p50_token_latency_ms"],
                 "p95_token_latency_ms": out["p95_token_latency_ms"], "gpu_launches": out["kernel_launches"],
-                "e2e": {"value": out["decode_tok_s"], "unit": "tokens/s", "h2d_bytes_per_step": 64 * 28,
-                        "d2h_bytes_per_step": 64 * 8}, "impl": "native", "notes": out}))
+                # per decode step: ids and cache slots (int64) + positions and context lengths (int32) go to the device as
+                # one pinned copy of 24 bytes per request, the sampled token ids (int64) come back
+                "e2e": {"value": out["decode_tok_s"], "unit": "tokens/s", "h2d_bytes_per_step": out["requests"] * 24,
+                        "d2h_bytes_per_step": out["requests"] * 8}, "impl": "native", "notes": out}))
         if world > 1:
             dist.barrier()
             dist.destroy_process_group()
