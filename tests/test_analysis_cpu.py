@@ -1,4 +1,5 @@
 """The analysis tracks (tools/analysis) end to end on a tiny random checkpoint, CPU only."""
+import importlib.util
 import json
 import subprocess
 import sys
@@ -76,6 +77,11 @@ def test_analysis_pipeline(tmp_path):
     assert len(dist) == L + 1 and all(0.0 <= d <= 1.0 for d in dist)
     run("extract_activation_geometry.py", *common, "--prompt-set", "standard", "--components", "all", "--topo-subsample", 200)
     run("visualize_activation_geometry.py", "--runs", "t,u", "--output-dir", out)
+    have_mpl = importlib.util.find_spec("matplotlib") is not None
+    ext = "png" if have_mpl else "svg"
+    for fig in ("rankme", "head_entropy_mean", "effective_rank_q_proj", "point_cloud_layer0", "head_entropy_map"):
+        assert (ag / f"{fig}.{ext}").exists(), fig
+    assert (out / "_pairs" / f"compare_point_cloud_spread.{ext}").exists() and (out / "_pairs" / f"procrustes.{ext}").exists()
 
     # track 6
     run("extract_concept_geometry.py", *common, "--concept-sets", "weekdays,digits")
@@ -83,6 +89,8 @@ def test_analysis_pipeline(tmp_path):
     ana = json.loads((out / "t" / "concept_geometry" / "analysis.json").read_text())
     assert ana["sets"]["weekdays"]["kind"] == "cyclic" and "best_layer" in ana["sets"]["weekdays"]
     run("visualize_concept_geometry.py", "--input", out / "t" / "concept_geometry")
+    for fig in ("weekdays_pca2", "weekdays_depth", "digits_pca2", "overview"):
+        assert (out / "t" / "concept_geometry" / f"{fig}.{ext}").exists(), fig
 
     # report
     run("generate_report.py", "t", "--output-dir", out, "--metrics", mj)
@@ -162,3 +170,49 @@ def test_concept_geometry_statistics_on_planted_structure(tmp_path):
     assert noise["best_layer"]["r"] < 0.5 and noise["significant_layers"] <= 1
     assert ring["per_layer"][1]["smoothness_to_next"] > 0.9 > ring["per_layer"][0]["smoothness_to_next"]
     assert ring["per_layer"][1]["subspace"]["top2_variance"] > 0.95 and ring["per_layer"][1]["template"]["distance_agreement"] > 0.9
+
+
+def test_builtin_plotting_layer_draws_well_formed_figures():
+    """kotodama_b200/eval/plot_utils.py: SVG figures without matplotlib - well-formed, everything inside the canvas,
+    gaps where data is missing, stable run colours."""
+    import math
+    import re
+    import xml.etree.ElementTree as ET
+
+    from kotodama_b200.eval import plot_utils as pu
+    ns = "{http://www.w3.org/2000/svg}"
+
+    def inside(svg):
+        root = ET.fromstring(svg)
+        w, h = float(root.get("width")), float(root.get("height"))
+        for el in root.iter():
+            for k in ("x", "x1", "x2", "cx"):
+                if el.get(k) is not None:
+                    assert -1 <= float(el.get(k)) <= w + 1, (el.tag, k, el.get(k))
+            for k in ("y", "y1", "y2", "cy"):
+                if el.get(k) is not None:
+                    assert -1 <= float(el.get(k)) <= h + 1, (el.tag, k, el.get(k))
+            if el.get("points"):
+                for pt in el.get("points").split():
+                    x, y = map(float, pt.split(","))
+                    assert 0 <= x <= w and 0 <= y <= h
+        return root
+    line = pu.line_chart({"proxy-muon": [5, 4, 3.5, None, 3.2, 3.1], "other <run>": [5, 4.5, 4.2, 4.0, float("nan"), 3.9]},
+                         title="loss & <tags>", xlabel="step", ylabel="loss", x=[0, 10, 20, 30, 40, 50], dashed=["other <run>"])
+    root = inside(line)
+    polys = root.findall(f"{ns}polyline")
+    assert len(polys) == 3                                   # the first series breaks at the missing value, the second ends before its NaN
+    assert "&lt;tags&gt;" in line and "stroke-dasharray" in line and pu.run_color("proxy-muon") in line
+    first = [tuple(map(float, p.split(","))) for p in polys[0].get("points").split()]
+    assert [x for x, _ in first] == sorted(x for x, _ in first) and first[0][1] < first[-1][1]     # falling values go down the page
+    ring = [(math.cos(i), math.sin(i)) for i in range(7)]
+    inside(pu.scatter(ring, labels=list("MTWTFSS"), connect="loop", title="weekdays"))
+    sc = pu.scatter([(0, 0), (1, 1), (2, 0), (3, 1)], arrows=[(0, 1), (2, 3)], ghosts=[(0.1, 0.2), (1.2, 0.9), (2, 0.3), (3.1, 1.1)])
+    assert inside(sc) is not None and sc.count("marker-end") == 2
+    hm = inside(pu.heatmap([[i * j for j in range(12)] for i in range(6)], title="entropy", xlabel="head", ylabel="layer"))
+    assert len([r for r in hm.findall(f"{ns}rect")]) >= 6 * 12 + 40
+    inside(pu.bar_chart({"a": 1.0, "b": -0.5, "c": 2.0}, title="bars"))
+    inside(pu.line_chart({"flat": [1.0, 1.0, 1.0]}))                      # degenerate ranges do not divide by zero
+    inside(pu.line_chart({"empty": []}))
+    assert pu.run_color("some-run") == pu.run_color("some-run") and re.fullmatch(r"#[0-9a-f]{6}", pu.sequential_color(0.37))
+    assert pu.run_label("a-very-long-run-name-indeed").endswith("…") and pu.run_label("proxy-nca") == "NCA"

@@ -248,10 +248,14 @@ def flat(d: Any, prefix: str = "") -> list[tuple[str, Any]]:
 
 
 def images(d: Path) -> str:
+    """The figures the visualisers left in ``d``: PNG (matplotlib) as data URIs, SVG (built-in plotting layer) inline."""
     out = []
     for p in sorted(d.glob("*.png")):
         out.append(f'<figure><img src="data:image/png;base64,{base64.b64encode(p.read_bytes()).decode()}"/>'
                    f"<figcaption>{html.escape(p.stem)}</figcaption></figure>")
+    for p in sorted(d.glob("*.svg")):
+        if not (d / (p.stem + ".png")).exists():
+            out.append(f"<figure>{p.read_text()}<figcaption>{html.escape(p.stem)}</figcaption></figure>")
     return "".join(out)
 
 

@@ -8,8 +8,9 @@ effective rank of every weight type over depth, TwoNN dimension of the token clo
 attention branch in the state, PCA point clouds, and the saved attention matrices.  With ``--runs a,b``
 the same series are overlaid for several runs and the Procrustes distances between them are drawn.
 
-Needs matplotlib; without it the script writes the same series as CSV (``series.csv``, one row per
-series; ``head_entropy_map.csv``) so they can be plotted elsewhere.
+With matplotlib the figures are PNG files; without it the same figures are drawn as SVG by the built-in
+plotting layer (``kotodama_b200/eval/plot_utils.py``) and the series are also written as CSV (``series.csv``,
+``head_entropy_map.csv``), so the track produces pictures on a bare Python install.
 
     python tools/analysis/visualize_activation_geometry.py --run my-run [--output-dir analysis]
     python tools/analysis/visualize_activation_geometry.py --runs a,b [--output-dir analysis]
@@ -21,9 +22,13 @@ from __future__ import annotations
 import argparse
 import csv
 import json
+import sys
 from pathlib import Path
 
 import numpy as np
+
+sys.path.insert(0, str(Path(__file__).resolve().parents[2]))
+from kotodama_b200.eval import plot_utils as pu  # noqa: E402
 
 
 def series(geo: dict) -> dict[str, list[float]]:
@@ -70,6 +75,31 @@ def write_csv(path: Path, rows: dict[str, list[float]]) -> None:
         w = csv.writer(fh)
         for k, v in rows.items():
             w.writerow([k] + list(v))
+
+
+def svg_run(d: Path, run: str, s: dict[str, list[float]]) -> int:
+    """The per-run figures without matplotlib: one SVG per series, the PCA clouds, the head-entropy map."""
+    n = 0
+    for k, v in s.items():
+        per_head = k.startswith(("head_entropy_layer", "attention_distance_layer"))
+        (d / f"{k}.svg").write_text(pu.line_chart({run: v}, title=f"{run}: {k}", xlabel="head" if per_head else "layer"))
+        n += 1
+    npz = d / "arrays.npz"
+    if npz.exists():
+        with np.load(npz) as z:
+            pc = z["point_clouds"] if "point_clouds" in z.files else None
+        if pc is not None:
+            for l in sorted({0, len(pc) // 2, len(pc) - 1}):
+                (d / f"point_cloud_layer{l}.svg").write_text(
+                    pu.scatter(pc[l][:, :2], title=f"{run}: PCA, layer {l}", xlabel="PC 1", ylabel="PC 2"))
+                n += 1
+    he = d / "head_entropy.npz"
+    if he.exists():
+        with np.load(he) as z:
+            (d / "head_entropy_map.svg").write_text(
+                pu.heatmap(z["entropy"].tolist(), title=f"{run}: attention entropy (nats)", xlabel="head", ylabel="layer"))
+        n += 1
+    return n
 
 
 def load_run(output_dir: str, run: str) -> tuple[Path, dict]:
@@ -152,7 +182,8 @@ def main() -> None:
             if he.exists():
                 with np.load(he) as z:
                     np.savetxt(d / "head_entropy_map.csv", z["entropy"], delimiter=",", fmt="%.5f")
-            print(f"matplotlib is not installed: wrote {d / 'series.csv'}")
+            n = svg_run(d, r, all_series[r])
+            print(f"matplotlib is not installed: {n} SVG figures and series.csv -> {d}")
         else:
             plot_run(plt, d, r, all_series[r])
             print(f"plots -> {d}")
@@ -166,7 +197,13 @@ def main() -> None:
             rows = {f"{k}|{r}": all_series[r][k] for k in shared for r in runs}
             rows.update({f"procrustes|{pair}": v for pair, v in dist.items()})
             write_csv(pd / "comparison.csv", rows)
-            print(f"matplotlib is not installed: wrote {pd / 'comparison.csv'}")
+            for k in shared:
+                (pd / f"compare_{k}.svg").write_text(pu.line_chart({r: all_series[r][k] for r in runs}, title=k, xlabel="layer"))
+            if dist:
+                n = max(len(v) for v in dist.values())
+                (pd / "procrustes.svg").write_text(pu.line_chart(dist, title="Procrustes distance between runs", x=list(range(-1, n - 1)),
+                                                                 xlabel="layer (-1 = embeddings)"))
+            print(f"matplotlib is not installed: {len(shared) + bool(dist)} SVG figures and comparison.csv -> {pd}")
             return
         for k in shared:
             fig, ax = plt.subplots(figsize=(5.5, 3.2))

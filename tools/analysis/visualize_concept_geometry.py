@@ -9,8 +9,9 @@ statistics of ``analyze_concept_geometry.py``:
     accuracy for paired sets) and the layer-to-layer smoothness
   * all sets: a layer x set heat map of the headline statistic and a table of best layers
 
-Needs matplotlib; without it the script writes the coordinates (``<set>_pca2.csv``) and the per-layer
-curves (``curves.csv``) so that they can be plotted elsewhere.
+With matplotlib the figures are PNG files; without it the same figures are drawn as SVG by the built-in plotting
+layer (``kotodama_b200/eval/plot_utils.py``), and the coordinates (``<set>_pca2.csv``) and per-layer curves
+(``curves.csv``) are written as well.
 
     python tools/analysis/visualize_concept_geometry.py --input analysis/run/concept_geometry [--view pooled]
 
@@ -21,9 +22,13 @@ from __future__ import annotations
 import argparse
 import csv
 import json
+import sys
 from pathlib import Path
 
 import numpy as np
+
+sys.path.insert(0, str(Path(__file__).resolve().parents[2]))
+from kotodama_b200.eval import plot_utils as pu  # noqa: E402
 
 HEADLINE = {"cyclic": ("cyclic", "r"), "ordinal": ("ordinal", "r"), "geographic": ("geographic", "r"),
             "paired": ("paired", "completion_accuracy")}
@@ -95,6 +100,18 @@ def main() -> None:
                 w.writerow(["item", "pc1", "pc2", "layer"])
                 for it, p in zip(info["items"], xy):
                     w.writerow([it, float(p[0]), float(p[1]), layer])
+            (d / f"{name}_pca2.svg").write_text(pu.scatter(
+                xy, labels=info["items"], title=f"{name} ({kind}): layer {layer}",
+                connect="loop" if kind == "cyclic" else "path" if kind == "ordinal" else "",
+                arrows=[(i, i + 1) for i in range(0, len(xy) - 1, 2)] if kind == "paired" else None,
+                ghosts=[(c[1], c[0]) for c in coords] if coords is not None else None))
+            if name in curves:
+                lines = {HEADLINE[kind][1]: curves[name], "null": curves[f"{name}|null"]}
+                if f"{name}|smoothness" in curves:
+                    lines["smoothness to next layer"] = curves[f"{name}|smoothness"]
+                (d / f"{name}_depth.svg").write_text(pu.line_chart(lines, title=name, xlabel="layer (0 = embeddings)", dashed=["null"],
+                                                                   colors={HEADLINE[kind][1]: "#1f77b4", "null": "#888888",
+                                                                           "smoothness to next layer": "#2ca02c"}))
             continue
         fig, ax = plt.subplots(figsize=(4.8, 4.8))
         if kind in ("cyclic", "ordinal"):
@@ -133,6 +150,10 @@ def main() -> None:
             w = csv.writer(fh)
             for k, v in curves.items():
                 w.writerow([k] + list(v))
+        if main_curves:
+            names = list(main_curves)
+            (d / "overview.svg").write_text(pu.heatmap([main_curves[n] for n in names], title="headline statistic over depth",
+                                                       xlabel="layer", row_labels=names, vmax=1.0))
     elif main_curves:
         names = list(main_curves)
         m = np.array([main_curves[n] for n in names])
@@ -146,7 +167,7 @@ def main() -> None:
         fig.tight_layout()
         fig.savefig(d / "overview.png", dpi=120)
         plt.close(fig)
-    print(f"{'plots' if plt else 'CSV (matplotlib missing)'} -> {d}")
+    print(f"{'plots' if plt else 'SVG figures and CSV (matplotlib is not installed)'} -> {d}")
 
 
 if __name__ == "__main__":
