@@ -320,5 +320,10 @@ def extract_keys_matching(data: dict[int, dict[str, float]], prefix: str) -> lis
     return sorted({k for r in data.values() for k in r if k.startswith(prefix)})
 
 
+def get_value(data: dict[int, dict[str, float]], step: int, key: str) -> Optional[float]:
+    """The metric at exactly this step, or None (``src/eval/metrics_io.py:170`` of the reference)."""
+    return data.get(step, {}).get(key)
+
+
 def load_multiple(paths: dict[str, str | Path]) -> dict[str, dict[int, dict[str, float]]]:
     return {name: load_metrics(p) for name, p in paths.items() if Path(p).exists()}
