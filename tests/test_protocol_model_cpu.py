@@ -204,3 +204,44 @@ def test_a_rank_that_never_arrives_is_a_deadlock_in_the_model_and_a_timeout_in_t
     progs[1] = []                                    # rank 1 never runs
     out = explore(progs, {})
     assert out is not None and "deadlock" in out
+
+
+# ----------------------------------------------------------------------------- programmatic dependent launches
+def dependent_launch_programs(k2_waits: bool = True, k3_reads_early: bool = False, k3_prefetches_weight: bool = True):
+    """Three kernels on one stream, each launched as a programmatic dependent of the one before it (csrc/common.cuh:
+    kb_launch_dep / kb_dep_trigger / kb_dep_wait; the decode graphs of serve/engine.py).  A kernel may START once its
+    predecessor has triggered, and its wait returns once the predecessor has COMPLETED.  K1 produces x, K2 turns x into
+    y, K3 reads y and x (x only through K2's completion: K3 waits for K2 alone) and may fetch a constant weight early.
+    Each kernel is one program here; "every thread waits" is modelled by the wait being a step of the kernel itself."""
+    k1: list[Step] = [("do", lambda m: m.__setitem__("trig1", 1)),
+                      ("do", lambda m: m.__setitem__("x", 1)),                 # the value K1 is there to produce
+                      ("do", lambda m: m.__setitem__("done1", 1))]
+    k2: list[Step] = [("wait", lambda m: g(m, "trig1") == 1),                 # launch condition
+                      ("do", lambda m: m.__setitem__("trig2", 1))]            # trigger first: K3 may start at once
+    if k2_waits:
+        k2.append(("wait", lambda m: g(m, "done1") == 1))
+        k2.append(("do", lambda m: None if g(m, "x") == 1 else "K2 read x before K1 wrote it"))
+    k2 += [("do", lambda m: m.__setitem__("y", 1)), ("do", lambda m: m.__setitem__("done2", 1))]
+    k3: list[Step] = [("wait", lambda m: g(m, "trig2") == 1)]
+    if k3_prefetches_weight:
+        k3.append(("do", lambda m: None if g(m, "w", 7) == 7 else "the weight changed under the prefetch"))   # nothing ever writes w
+    if k3_reads_early:
+        k3.append(("do", lambda m: None if g(m, "y") == 1 else "K3 read y before K2 wrote it"))
+    k3 += [("wait", lambda m: g(m, "done2") == 1),
+           ("do", lambda m: None if g(m, "y") == 1 else "K3 read y before K2 wrote it"),
+           ("do", lambda m: None if g(m, "x") == 1 else "K3 read x before K1 wrote it")]
+    return [k1, k2, k3]
+
+
+def test_dependent_launches_are_safe_when_every_kernel_waits():
+    assert explore(dependent_launch_programs(), {}) is None
+
+
+def test_dependent_launch_model_shows_what_each_rule_is_for():
+    # data of the predecessor read before the wait: stale
+    out = explore(dependent_launch_programs(k3_reads_early=True), {})
+    assert out is not None and "K3 read y before" in out
+    # a kernel in the middle that does not wait (it happens not to need its predecessor's data) breaks the chain for
+    # the kernel after it, which waits for the middle one only
+    out = explore(dependent_launch_programs(k2_waits=False), {})
+    assert out is not None and "K3 read x before" in out
