@@ -294,3 +294,50 @@ def test_analysis_forward_and_perplexity_match(ref, tmp_path):
         pb = compute_perplexity(ours, tmp_path / "eval.bin", seq_len=32, batch_size=4, max_tokens=40 * 32)
     assert pb["loss"] == pytest.approx(pa["loss"], rel=1e-5) and pb["perplexity"] == pytest.approx(pa["perplexity"], rel=1e-4)
     assert int(pb["tokens"]) == int(pa["n_tokens"])
+
+
+def test_sampler_distribution_matches_the_reference_server(ref, monkeypatch):
+    """The serving sampler (repetition penalty -> temperature -> top-k -> top-p -> multinomial) against the reference
+    server's ``sample_next_token``: the reference's filtered probabilities are captured at its ``torch.multinomial``
+    call; ours are measured by sweeping the sampler's uniform draw over a fine grid (inverse-CDF sampling cuts [0, 1)
+    into intervals whose lengths are the probabilities)."""
+    import importlib.util
+    serve_py = os.path.join(os.environ.get("KOTODAMA_REFERENCE", os.path.join(os.path.dirname(ROOT), "reference")), "serve.py")
+    if not os.path.isfile(serve_py):
+        pytest.skip("the reference's serve.py is not on this machine")
+    spec = importlib.util.spec_from_file_location("reference_serve", serve_py)
+    theirs = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(theirs)
+    from kotodama_b200.ops.reference import TorchOps
+    ours = TorchOps()
+    V, N = 40, 4000
+    g = torch.Generator().manual_seed(0)
+    seen_ids = [3, 7, 7, 11, 30]
+    for temperature, top_k, top_p, rp in [(0.7, 0, 0.0, 1.0), (1.3, 8, 0.0, 1.0), (0.9, 0, 0.8, 1.0), (1.0, 12, 0.6, 1.3), (0.5, 5, 0.95, 1.8)]:
+        logits = torch.randn(V, generator=g) * 2.5
+        captured = {}
+
+        def fake_multinomial(probs, num_samples=1, **kw):
+            captured["p"] = probs.detach().clone()
+            return probs.argmax().reshape(1)
+        monkeypatch.setattr(torch, "multinomial", fake_multinomial)
+        theirs.sample_next_token(logits.clone(), temperature, top_k, top_p, rp, list(seen_ids))
+        monkeypatch.undo()
+        want = captured["p"].double()
+        words = torch.zeros(1, (V + 31) // 32, dtype=torch.int32)
+        for t in set(seen_ids):
+            words[0, t >> 5] |= 1 << (t & 31)
+        counts = torch.zeros(V, dtype=torch.double)
+        for i in range(N):
+            ours.sample_uniform = lambda seed, counter, u=(i + 0.5) / N: u
+            tok = ours.sample(logits.clone()[None], [temperature], [top_k], [top_p], [rp], [0], [0], words.clone(), [0])
+            counts[int(tok)] += 1
+        got = counts / N
+        assert not bool(((got > 0) & (want == 0)).any())               # nothing outside the reference's support
+        assert bool((got[want > 2.0 / N] > 0).all())                   # everything inside it that the grid can resolve
+        assert float((got - want).abs().max()) < 2.5 / N, (temperature, top_k, top_p, rp)
+    # greedy: same token, penalty included
+    logits = torch.randn(V, generator=g)
+    a = theirs.sample_next_token(logits.clone(), 0.0, 0, 0.0, 1.5, list(seen_ids))
+    b = ours.sample(logits.clone()[None], [0.0], [0], [0.0], [1.5], [0], [0], words.clone(), [0])
+    assert a == int(b)
