@@ -104,8 +104,8 @@ def sample_tokens(logits: torch.Tensor, reqs: list[Request], ops: Any, seen: Opt
         # no engine-owned bitmaps (direct use): build them from the requests' token lists
         import numpy as np
         words = np.zeros((len(reqs), (logits.shape[1] + 31) // 32), dtype=np.uint32)
-        for b, r in enumerate(reqs):
-            ids = np.unique(np.asarray(r.prompt + r.generated, dtype=np.int64))
+        for b, r in enumerate(reqs):                     # generated tokens only, as the reference's server counts them
+            ids = np.unique(np.asarray(r.generated, dtype=np.int64))
             np.bitwise_or.at(words[b], ids >> 5, (np.uint32(1) << (ids & 31).astype(np.uint32)))
         seen = torch.from_numpy(words.view(np.int32)).to(logits.device)
         slots = list(range(len(reqs)))
@@ -140,8 +140,10 @@ class ServingEngine:
         self.waiting: list[Request] = []
         self.running: list[Request] = []
         self._next_id = 0
-        # one bitmap row per batch slot: the tokens a request has seen (prompt + generated), for the
-        # repetition penalty of the device sampler
+        # one bitmap row per batch slot: the tokens a request has generated so far, for the repetition penalty of
+        # the device sampler (the reference's server penalises generated tokens only, ``serve.py:266-283,345-373``;
+        # ``penalise_prompt`` adds the prompt's tokens, the convention of other serving stacks)
+        self.penalise_prompt = False
         self.seen_words = (cfg.vocab_size + 31) // 32
         self.seen = torch.zeros(max_batch, self.seen_words, dtype=torch.int32, device=self.device)
         self._free_slots = list(range(max_batch - 1, -1, -1))
@@ -311,11 +313,12 @@ class ServingEngine:
         return groups
 
     def _init_seen(self, r: Request) -> None:
-        """Bitmap of the prompt's tokens, built on the host and copied into the request's slot."""
-        import numpy as np
+        """A fresh bitmap row for the request's slot: empty (the sampler sets a bit per generated token), or the
+        prompt's tokens when ``penalise_prompt`` is on."""
         words = np.zeros(self.seen_words, dtype=np.uint32)
-        ids = np.unique(np.asarray(r.prompt, dtype=np.int64))
-        np.bitwise_or.at(words, ids >> 5, (np.uint32(1) << (ids & 31).astype(np.uint32)))
+        if self.penalise_prompt:
+            ids = np.unique(np.asarray(r.prompt, dtype=np.int64))
+            np.bitwise_or.at(words, ids >> 5, (np.uint32(1) << (ids & 31).astype(np.uint32)))
         self.seen[r.slot].copy_(torch.from_numpy(words.view(np.int32)), non_blocking=True)
 
     def _release(self, r: Request) -> None:

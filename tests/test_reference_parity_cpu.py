@@ -341,3 +341,42 @@ def test_sampler_distribution_matches_the_reference_server(ref, monkeypatch):
     a = theirs.sample_next_token(logits.clone(), 0.0, 0, 0.0, 1.5, list(seen_ids))
     b = ours.sample(logits.clone()[None], [0.0], [0], [0.0], [1.5], [0], [0], words.clone(), [0])
     assert a == int(b)
+
+
+def test_paged_serving_engine_generates_what_the_reference_server_generates(ref):
+    """End to end on the same weights (fp32, CPU): the reference server's ``generate`` (contiguous KV cache, one request)
+    against this package's engine (paged cache, continuous batching, several requests at once), greedy with and without
+    a repetition penalty, AttnRes with explicit boundaries."""
+    import importlib.util
+    serve_py = os.path.join(os.environ.get("KOTODAMA_REFERENCE", os.path.join(os.path.dirname(ROOT), "reference")), "serve.py")
+    if not os.path.isfile(serve_py):
+        pytest.skip("the reference's serve.py is not on this machine")
+    spec = importlib.util.spec_from_file_location("reference_serve", serve_py)
+    theirs_srv = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(theirs_srv)
+    from kotodama_b200.serve.engine import SamplingParams, ServingEngine
+    theirs, ours = _pair(ref, dtype=torch.float32, boundaries=[0, 1, 3])
+    ours.load_state_dict(theirs.state_dict())
+    theirs.eval(), ours.eval()
+
+    class Tok:                                   # ids in, ids out: the text is the id list
+        eos_token_id = -1
+
+        def encode(self, prompt, return_tensors=None):
+            return torch.tensor([[int(t) for t in prompt.split()]])
+
+        def decode(self, ids, skip_special_tokens=True):
+            return " ".join(str(int(i)) for i in ids)
+    prompts = [[5, 17, 3, 99, 42], [7] * 11, [200, 1, 2, 3, 4, 5, 6, 7, 8, 9, 10, 11, 12, 13, 14, 15, 16, 17]]
+    eng = ServingEngine(ours, device="cpu", dtype=torch.float32, max_batch=4, max_ctx=64)
+    seen = {}
+    for rp in (1.0, 2.0):
+        want = []
+        for p in prompts:
+            req = theirs_srv.GenerateRequest(prompt=" ".join(map(str, p)), max_new_tokens=14, temperature=0.0, top_k=0, top_p=0.0,
+                                             repetition_penalty=rp)
+            want.append([int(t) for t in theirs_srv.generate(theirs, Tok(), req).text.split()])
+        got = eng.generate(prompts, SamplingParams(max_new_tokens=14, temperature=0.0, repetition_penalty=rp))
+        assert got == want, rp
+        seen[rp] = want
+    assert seen[1.0] != seen[2.0]                # the penalty changes at least one continuation, so the second case means something

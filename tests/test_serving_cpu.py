@@ -102,7 +102,9 @@ def test_sampler_order_and_limits():
     r = Request(0, [3], SamplingParams(temperature=0.0, repetition_penalty=2.0))
     from kotodama_b200.ops import get_ops
     ops = get_ops("cpu")
-    assert int(sample_tokens(logits.clone(), [r], ops)[0]) == 2      # token 3 penalised: 3/2 < 2
+    assert int(sample_tokens(logits.clone(), [r], ops)[0]) == 3      # token 3 is in the prompt only: not penalised
+    r.generated.append(3)
+    assert int(sample_tokens(logits.clone(), [r], ops)[0]) == 2      # once generated it is: 3/2 < 2
     r2 = Request(1, [0], SamplingParams(temperature=1.0, top_k=1))
     assert int(sample_tokens(logits.clone(), [r2], ops)[0]) == 3
     draws = set()
