@@ -48,7 +48,9 @@ class CompletionRequest(BaseModel):
     max_tokens: int = Field(256, ge=1, le=2048)
     temperature: float = Field(0.7, ge=0.0, le=2.0)
     top_p: float = Field(0.0, ge=0.0, le=1.0)
-    frequency_penalty: float = Field(0.0, ge=0.0, le=1.0)
+    frequency_penalty: float = Field(0.0, ge=0.0, le=1.0)     # becomes repetition_penalty = 1 + this (at most 2, the sampler's limit)
+    presence_penalty: float = Field(0.0, ge=0.0, le=2.0)      # accepted for client compatibility, not used (as in the reference)
+    best_of: Optional[int] = None                             # accepted, not used
     n: int = Field(1, ge=1, le=8)
     stop: Union[list[str], str, None] = None          # a single string or a list, as the OpenAI API allows
 

@@ -380,3 +380,42 @@ def test_paged_serving_engine_generates_what_the_reference_server_generates(ref)
         assert got == want, rp
         seen[rp] = want
     assert seen[1.0] != seen[2.0]                # the penalty changes at least one continuation, so the second case means something
+
+
+def test_executor_training_steps_track_the_reference_loop(ref):
+    """Several optimizer steps of the hand-scheduled executor (own backward schedule, fused clip + Muon + AdamW) against
+    the reference's loop (autograd, ``clip_grad_norm_``, its Muon and AdamW, its scheduler stepped after the
+    optimizers) on the same weights and the same fixed batch, fp32 on the CPU.  Both sides run Newton-Schulz in half
+    precision with different batching, so the trajectories agree closely, not bit for bit."""
+    from kotodama_b200.engine import TrainEngine
+    from kotodama_b200.optim.muon import HybridScheduler
+    theirs, ours = _pair(ref, dtype=torch.float32, boundaries=[0, 1, 3])
+    ours.load_state_dict(theirs.state_dict())
+    tm, ta = ref.muon.build_hybrid_optimizer(theirs, muon_lr=0.02, adamw_lr=3e-3)
+    ts = ref.muon.HybridScheduler(tm, ta, warmup_steps=2, total_steps=8)
+    eng = TrainEngine(ours, device="cpu", dtype=torch.float32, muon_lr=0.02, adamw_lr=3e-3, gradient_clip=1.0)
+    os_ = HybridScheduler(eng.muon_opt, eng.adamw_opt, warmup_steps=2, total_steps=8)
+    ids = torch.randint(0, 211, (3, 32), generator=torch.Generator().manual_seed(9))
+    la, lb, na, nb = [], [], [], []
+    for step in range(8):
+        out = theirs(ids, labels=ids)
+        out["loss"].backward()
+        na.append(float(torch.nn.utils.clip_grad_norm_(theirs.parameters(), 1.0)))
+        tm.step(); ta.step()
+        tm.zero_grad(set_to_none=True); ta.zero_grad(set_to_none=True)
+        ts.step(step)
+        la.append(float(out["loss"].detach()))
+        if step == 0:
+            za = float(out["z_loss"].detach())
+        r = eng.train_step([ids])
+        os_.step(step)
+        if step == 0:
+            zb = float(r["z_loss"])
+        lb.append(float(r["loss"]))
+        nb.append(float(r["grad_norm"]))
+    # step 0: identical weights -> the same loss (z-loss included on both sides), z-loss and gradient norm
+    assert lb[0] == pytest.approx(la[0], rel=1e-5) and zb == pytest.approx(za, rel=1e-4)
+    assert nb[0] == pytest.approx(na[0], rel=1e-3)
+    for a, b in zip(la, lb):
+        assert abs(a - b) < 0.03 * max(abs(a), 1.0), (la, lb)
+    assert la[-1] < la[0] - 0.3 and lb[-1] < lb[0] - 0.3
