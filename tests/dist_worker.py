@@ -297,6 +297,59 @@ def main():
             losses.append(float(out["loss"]))
         full = gather_full_state_dict(model, tp_group)
         result.update(losses=losses, checksum=float(sum(v.double().abs().sum() for v in full.values())))
+    if a.mode == "cpu_tp_reference_parity":
+        # the reference's own tensor-parallel code (unmodified, from the baseline install) next to this package's
+        # autograd API, same weights, same batch, same process group: shards, loss and local gradients
+        import importlib
+        import types
+        ref_root = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "baseline", "_ref")
+        if not os.path.isdir(os.path.join(ref_root, "training")):
+            result["skipped"] = "reference not installed"
+        else:
+            pkg = types.ModuleType("src")
+            pkg.__path__ = [ref_root]
+            sys.modules.setdefault("src", pkg)
+            r_llama = importlib.import_module("src.model.llama")
+            r_tp = importlib.import_module("src.training.tensor_parallel")
+            from kotodama_b200.parallel import tp as o_tp
+            kw = dict(hidden_size=64, num_layers=4, num_attention_heads=4, num_kv_heads=2, head_dim=16, intermediate_size=96,
+                      vocab_size=211, max_position_embeddings=64, z_loss_weight=1e-3, attn_res=True, attn_res_n_blocks=2)
+            torch.manual_seed(0)
+            theirs = r_llama.LuxiaBaseModel(r_llama.LuxiaModelConfig(attn_impl="sdpa", **kw))
+            gq = torch.Generator().manual_seed(3)
+            with torch.no_grad():
+                for n, p_ in theirs.named_parameters():
+                    if "query" in n:
+                        p_.copy_(torch.randn(p_.shape, generator=gq) * 0.3)
+            ours = KotodamaModel(ModelConfig(**kw))
+            ours.load_state_dict(theirs.state_dict())
+            tp_group, _ = o_tp.create_process_groups(world, world)
+            r_tp.apply_tensor_parallelism(theirs, tp_group)
+            o_tp.apply_tensor_parallelism(ours, tp_group)
+            shards_equal = all(torch.equal(p1, p2) for (_, p1), (_, p2) in zip(theirs.named_parameters(), ours.named_parameters()))
+            shared = torch.randint(0, 211, (2, 24), generator=torch.Generator().manual_seed(7))
+            la = theirs(shared, labels=shared)["loss"]
+            lb = ours(shared, labels=shared)["loss"]
+            la.backward()
+            lb.backward()
+            r_tp.sync_tp_replicated_grads(theirs, tp_group)
+            o_tp.sync_tp_replicated_grads(ours, tp_group)
+            worst = 0.0
+            for (n, p1), (_, p2) in zip(theirs.named_parameters(), ours.named_parameters()):
+                if p1.grad is None or p2.grad is None:
+                    worst = max(worst, 0.0 if (p1.grad is None) == (p2.grad is None) else 1.0)
+                    continue
+                worst = max(worst, float((p1.grad - p2.grad).norm() / (p1.grad.norm() + 1e-12)))
+            # the reference's tp_clip_grad_norm allocates on "cuda" unconditionally; on CPU ranks its rule is restated:
+            # squared norms of the sharded gradients summed over the group, those of the replicated ones counted once
+            sharded = sum(float(p_.grad.pow(2).sum()) for p_ in theirs.parameters() if p_.grad is not None and hasattr(p_, "_tp_shard_dim"))
+            repl = sum(float(p_.grad.pow(2).sum()) for p_ in theirs.parameters() if p_.grad is not None and not hasattr(p_, "_tp_shard_dim"))
+            t = torch.tensor([sharded], dtype=torch.float64)
+            dist.all_reduce(t, group=tp_group)
+            na = float((t[0] + repl) ** 0.5)
+            nb = float(o_tp.tp_clip_grad_norm(ours, 1.0, tp_group))
+            result.update(shards_equal=shards_equal, loss_theirs=float(la), loss_ours=float(lb), grad_rel_err_max=worst,
+                          norm_theirs=na, norm_ours=nb, local_q_rows=int(ours.layers[0].attn.q_proj.weight.shape[0]))
     with open(f"{a.out}.{a.mode}.{rank}.json", "w") as fh:
         json.dump(result, fh)
     dist.barrier()

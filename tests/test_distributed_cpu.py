@@ -78,6 +78,21 @@ def test_tensor_parallel_allreduce_mode_and_autograd_api(tmp_path):
         assert abs(res[0]["checksum"] - checksum) / checksum < 5e-4, mode
 
 
+def test_autograd_tp_api_matches_the_reference_tensor_parallel_code(tmp_path):
+    """Two gloo ranks run the reference's unmodified tensor_parallel.py and this package's API side by side on the
+    same weights: identical shards, the same loss, the same local gradients and the same clipped norm."""
+    import pytest
+    res = _launch("cpu_tp_reference_parity", str(tmp_path / "p"))
+    if "skipped" in res[0]:
+        pytest.skip(res[0]["skipped"])
+    for r in res:
+        assert r["shards_equal"] and r["local_q_rows"] == 32
+        assert abs(r["loss_theirs"] - r["loss_ours"]) < 1e-5
+        assert r["grad_rel_err_max"] < 1e-4, r
+        assert abs(r["norm_theirs"] - r["norm_ours"]) / r["norm_theirs"] < 1e-4
+    assert abs(res[0]["loss_ours"] - res[1]["loss_ours"]) < 1e-6
+
+
 def test_tensor_parallel_serving_matches_single_process(tmp_path):
     """TP=2 serving over gloo: sharded heads / KV cache / MLP, all-reduced row projections, leader and
     follower in lock-step - same greedy tokens as the unsharded engine (fp32)."""
