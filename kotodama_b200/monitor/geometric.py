@@ -33,7 +33,7 @@ logger = logging.getLogger(__name__)
 class MonitorConfig:
     tier1_every: int = 500
     tier1_probe_size: int = 1024
-    tier1_sample_layers: list[int] = field(default_factory=list)     # empty: first / middle / last
+    tier1_sample_layers: list[int] = field(default_factory=list)     # empty: 0, L/4, L/2, 3L/4, last
     tier2_every: int = 5000
     tier2_twonn_samples: int = 3000
     tier2_twonn_layers: list[int] = field(default_factory=list)      # empty: five evenly spaced
@@ -136,10 +136,13 @@ class GeometricMonitor:
         self.model = model.module if hasattr(model, "module") else model
         self.config = config or MonitorConfig()
         L = len(self.model.layers)
+        # default layer samples as in the reference (``src/monitoring/geometric.py:108-124``): the metric keys carry the
+        # layer index, so runs monitored by either code base line up
         if not self.config.tier1_sample_layers:
-            self.config.tier1_sample_layers = sorted({0, L // 2, L - 1})
+            step = max(1, L // 4)
+            self.config.tier1_sample_layers = sorted({0, step, 2 * step, 3 * step, L - 1})
         if not self.config.tier2_twonn_layers:
-            self.config.tier2_twonn_layers = sorted({round(i * (L - 1) / 4) for i in range(5)})
+            self.config.tier2_twonn_layers = [0, L // 4, L // 2, 3 * L // 4, L - 1]
         self._probe: Optional[torch.Tensor] = None
         self._attnres: dict[str, float] = {}
 
@@ -150,9 +153,12 @@ class GeometricMonitor:
     # ---- probe forward -------------------------------------------------------
     @torch.no_grad()
     def _probe_forward(self, ids: torch.Tensor, want_attn: set[int]) -> tuple[dict[int, torch.Tensor], dict[int, torch.Tensor]]:
-        """Hidden state after every layer (the partial sum plus committed blocks' contribution is
-        what the next layer routes over; the recorded state is the MLP sub-layer's routed input for
-        AttnRes and the residual stream otherwise) and attention probabilities of ``want_attn``."""
+        """One state per layer and the attention probabilities of ``want_attn`` (first four sequences).
+        Without AttnRes the state is the residual stream after the layer; with AttnRes it is the routed
+        state the layer's attention reads, and for the last layer the final aggregation (before the
+        output norm) - the captures of the reference's monitor, so that both produce the same series.
+        The attention probabilities are always those the layer really used (the reference's plain path
+        feeds the layer's output back into the same layer's attention instead)."""
         m = self.model
         cfg = m.config
         x = m.embed_tokens(ids)
@@ -168,7 +174,7 @@ class GeometricMonitor:
             sc = (q.float() @ k2.float().transpose(-1, -2)) / math.sqrt(q.shape[-1])
             p = torch.softmax(sc.masked_fill(~causal, float("-inf")), -1)
             if idx in want_attn:
-                attn[idx] = p
+                attn[idx] = p[:4]                    # the first sequences only, as the reference does, to bound memory
             o = (p @ v2.float()).to(h.dtype).transpose(1, 2).reshape(h.shape[0], T, -1)
             return layer.attn.o_proj(o)
 
@@ -187,12 +193,12 @@ class GeometricMonitor:
             if i in bset:
                 committed.append(partial)
                 partial = None                       # the new block starts from zero
+            hidden[i] = h                            # the routed state the attention sub-layer reads (``geometric.py:463-476`` there)
             a = attention(layer, layer.attn_norm(h), i)
             partial = a if partial is None else partial + a
-            h = route_sources(committed + [partial], layer.mlp_res_query, layer.mlp_res_norm.weight,
-                              layer.mlp_res_norm.eps)
-            partial = partial + layer.ffn(layer.ffn_norm(h))
-            hidden[i] = h
+            h2 = route_sources(committed + [partial], layer.mlp_res_query, layer.mlp_res_norm.weight,
+                               layer.mlp_res_norm.eps)
+            partial = partial + layer.ffn(layer.ffn_norm(h2))
         srcs = committed + [partial]
         w = (m.final_res_query * m.final_res_norm.weight).float()
         u = torch.stack(srcs, 0).float()
@@ -202,7 +208,8 @@ class GeometricMonitor:
         for b in range(len(srcs)):
             self._attnres[f"attnres/final_alpha/block_{b}"] = float(alpha[b])
             self._attnres[f"attnres/block_norm/{b}"] = float(u[b].norm(dim=-1).mean())
-        hidden[len(m.layers) - 1] = m.norm((torch.softmax((u * w).sum(-1) * r, 0).unsqueeze(-1) * u).sum(0).to(x.dtype))
+        # the last entry is the final aggregation itself (before the output norm), as in the reference's monitor
+        hidden[len(m.layers) - 1] = (torch.softmax((u * w).sum(-1) * r, 0).unsqueeze(-1) * u).sum(0).to(x.dtype)
         return hidden, attn
 
     def _batch(self, probe: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
@@ -262,7 +269,7 @@ class GeometricMonitor:
             out["geo/ww_alpha_mean"] = sum(alphas) / len(alphas)
             out["geo/ww_alpha_std"] = _std(alphas)
             out["geo/ww_alpha_min"], out["geo/ww_alpha_max"] = min(alphas), max(alphas)
-            out["geo/ww_alpha_healthy_frac"] = sum(2.0 <= a <= 6.0 for a in alphas) / len(alphas)
+            out["geo/ww_alpha_healthy_frac"] = sum(2.0 < a < 4.0 for a in alphas) / len(alphas)      # the reference's band
             for k, v in by_type.items():
                 out[f"geo/ww_alpha_by_type/{k}"] = sum(v) / len(v)
         batch = self._batch(probe_batch)

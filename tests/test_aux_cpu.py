@@ -214,11 +214,11 @@ def test_geometric_monitor_tiers():
     assert "geo/ww_alpha_mean" in t2 and any(k.startswith("geo/twonn_id/") for k in t2)
     assert abs(rankme(torch.eye(8)) - 8) < 1e-3 and abs(stable_rank(torch.eye(8)) - 8) < 1e-3
     assert 1.0 < twonn_id(torch.randn(500, 3)) < 6.0
-    # the probe forward is the model: last hidden state equals the model's
+    # the probe forward is the model: its last entry (the final aggregation) under the output norm equals the model's
     ids = torch.randint(0, cfg.vocab_size, (2, 16))
     hidden, _ = mon._probe_forward(ids, set())
     ref, _ = model.hidden_states(ids)
-    assert torch.allclose(hidden[cfg.num_layers - 1], ref, atol=1e-5)
+    assert torch.allclose(model.norm(hidden[cfg.num_layers - 1]), ref, atol=1e-5)
 
 
 def test_watchdog_names_rank_and_phase():

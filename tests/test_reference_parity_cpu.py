@@ -419,3 +419,43 @@ def test_executor_training_steps_track_the_reference_loop(ref):
     for a, b in zip(la, lb):
         assert abs(a - b) < 0.03 * max(abs(a), 1.0), (la, lb)
     assert la[-1] < la[0] - 0.3 and lb[-1] < lb[0] - 0.3
+
+
+@pytest.mark.parametrize("attn_res", [True, False])
+def test_geometric_monitor_series_match(ref, attn_res):
+    """Both monitors on the same weights and probe batch: the same metric keys (layer samples included) and, with
+    AttnRes, the same values for every tier-1 series and the TwoNN dimensions.  Without AttnRes the attention entropy is
+    left out of the value comparison: the reference's plain path feeds a layer's output back into that layer's attention,
+    this package records the probabilities the layer really used."""
+    import warnings
+    theirs_geo = importlib.import_module("src.monitoring.geometric")
+    from kotodama_b200.monitor import geometric as ours_geo
+    theirs, ours = _pair(ref, dtype=torch.float32, attn_res=attn_res, boundaries=[0, 1, 3] if attn_res else None)
+    ours.load_state_dict(theirs.state_dict())
+    theirs.eval(), ours.eval()
+    ids = torch.randint(0, 211, (6, 32), generator=torch.Generator().manual_seed(1))
+    mt = theirs_geo.GeometricMonitor(theirs, theirs_geo.MonitorConfig(device="cpu"))
+    mo = ours_geo.GeometricMonitor(ours, ours_geo.MonitorConfig(device="cpu"))
+    assert mt.config.tier1_sample_layers == mo.config.tier1_sample_layers
+    assert mt.config.tier2_twonn_layers == mo.config.tier2_twonn_layers
+    mt.set_probe_batch(ids)
+    mo.set_probe_batch(ids)
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        torch.manual_seed(0)
+        a1 = mt.tier1(100)
+        torch.manual_seed(0)
+        b1 = mo.tier1(100)
+        torch.manual_seed(0)
+        a2 = mt.tier2(100)
+        torch.manual_seed(0)
+        b2 = mo.tier2(100)
+    assert set(a1) == set(b1)
+    assert set(a2) <= set(b2)                       # this package also reports k / v / up and the by-type means
+    for k, v in a1.items():
+        if "time" in k or (not attn_res and "attn_entropy" in k):
+            continue
+        assert b1[k] == pytest.approx(v, rel=1e-3, abs=1e-5), k
+    for k, v in a2.items():
+        if k.startswith("geo/twonn_id/"):
+            assert b2[k] == pytest.approx(v, rel=1e-3), k
