@@ -459,3 +459,40 @@ def test_geometric_monitor_series_match(ref, attn_res):
     for k, v in a2.items():
         if k.startswith("geo/twonn_id/"):
             assert b2[k] == pytest.approx(v, rel=1e-3), k
+
+
+def test_metric_files_written_by_both_loggers_are_interchangeable(ref, tmp_path):
+    """Twelve training steps and two geometric records through the reference's logger and this package's: the same
+    JSONL records (keys and values; the loss slope appears from the tenth step on both sides), so either analysis stack
+    reads either run."""
+    import json
+    theirs_log = importlib.import_module("src.monitoring.wandb_callback")
+    from kotodama_b200.eval import load_metrics
+    from kotodama_b200.monitor.logger import WandbLogger
+    a = theirs_log.WandbLogger(project="p", run_name="r", config={"x": 1}, log_dir=str(tmp_path / "theirs"), enabled=True)
+    b = WandbLogger(project="p", run_name="r", config={"x": 1}, log_dir=str(tmp_path / "ours"), enabled=True, use_wandb=False)
+    for lg in (a, b):
+        for step in range(12):
+            lg.log_step(step, loss=5.0 - 0.1 * step, z_loss=1e-3, grad_norm=1.5, muon_lr=0.02, adamw_lr=6e-4, tokens_per_sec=1000.0 + step,
+                        tokens_consumed=4096 * (step + 1), gpu_mem_gb=12.5, step_time_s=0.5, iters_per_sec=2.0)
+            if step in (5, 10):
+                lg.log_geo(step, {"geo/rankme_last": 40.0 + step, "geo/layer_0/anisotropy": 0.1})
+            lg.commit(step)
+        lg.finish()
+
+    def records(d, name):
+        out = []
+        for line in open(d / name):
+            r = json.loads(line)
+            r.pop("timestamp", None)
+            r.pop("_timestamp", None)
+            out.append(r)
+        return out
+    for name in ("metrics.jsonl", "geo_metrics.jsonl"):
+        ra, rb = records(tmp_path / "theirs", name), records(tmp_path / "ours", name)
+        assert len(ra) == len(rb) and len(ra) > 0, name
+        for x, y in zip(ra, rb):
+            assert set(x) == set(y), (name, set(x) ^ set(y))
+            for k in x:
+                assert y[k] == pytest.approx(x[k], rel=1e-9, abs=1e-12) if isinstance(x[k], float) else y[k] == x[k], (name, k)
+    assert load_metrics(tmp_path / "theirs" / "metrics.jsonl") == load_metrics(tmp_path / "ours" / "metrics.jsonl")
