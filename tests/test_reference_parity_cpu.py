@@ -496,3 +496,26 @@ def test_metric_files_written_by_both_loggers_are_interchangeable(ref, tmp_path)
             for k in x:
                 assert y[k] == pytest.approx(x[k], rel=1e-9, abs=1e-12) if isinstance(x[k], float) else y[k] == x[k], (name, k)
     assert load_metrics(tmp_path / "theirs" / "metrics.jsonl") == load_metrics(tmp_path / "ours" / "metrics.jsonl")
+
+
+def test_nca_rule_network_and_update_match(ref):
+    """The cellular-automaton rule network with the reference's weights: perception convolution with wrap-around
+    padding, 1 x 1 hidden layers, output logits per group - the same logits for the same grid."""
+    theirs = importlib.import_module("src.nca.generator")
+    from kotodama_b200.nca import generator as ours
+    d, G, K, Hd, nh, S = 10, 4, 3, 32, 2, 12
+    torch.manual_seed(0)
+    a = theirs.NCARule(d, G, K, Hd, nh)
+    b = ours.NCARule(d, G, K, Hd, nh)
+    sd = a.state_dict()
+    names = ["perception"] + [k.rsplit(".", 1)[0] for k in sd if k.startswith("hidden.") and k.endswith(".weight")] + ["output"]
+    with torch.no_grad():
+        for i, n in enumerate(names):
+            b.weights[i].copy_(sd[f"{n}.weight"])
+            b.biases[i].copy_(sd[f"{n}.bias"])
+    state = torch.randint(0, d, (2, G, S, S), generator=torch.Generator().manual_seed(1))
+    onehot = torch.nn.functional.one_hot(state, d).permute(0, 1, 4, 2, 3).reshape(2, G * d, S, S).float()
+    la, lb = a(onehot), b(onehot)
+    assert la.shape == lb.shape and torch.allclose(la, lb, atol=1e-5)
+    # the borders matter: a cell on the edge sees the opposite edge
+    assert not torch.allclose(la[..., 0, :], la[..., S // 2, :])
