@@ -519,3 +519,30 @@ def test_nca_rule_network_and_update_match(ref):
     assert la.shape == lb.shape and torch.allclose(la, lb, atol=1e-5)
     # the borders matter: a cell on the edge sees the opposite edge
     assert not torch.allclose(la[..., 0, :], la[..., S // 2, :])
+
+
+@pytest.mark.parametrize("kw", [dict(), dict(attn_res=False), dict(boundaries=[0, 1, 3])])
+def test_initialisation_and_reinitialisation_draw_the_same_weights(ref, kw):
+    """Under one seed both models are initialised to the same tensors (scheme, standard deviations and the order in
+    which parameters are drawn), and ``reinit_mlps`` / ``reinit_embeddings`` (the NCA -> language transition) redraw
+    the same ones."""
+    from kotodama_b200.config import ModelConfig
+    from kotodama_b200.models.llama import KotodamaModel
+    torch.manual_seed(11)
+    theirs = ref.llama.LuxiaBaseModel(ref.llama.LuxiaModelConfig(attn_impl="sdpa", **_cfg_kwargs(**kw)))
+    torch.manual_seed(11)
+    ours = KotodamaModel(ModelConfig(**_cfg_kwargs(**kw)))
+    sa, sb = theirs.state_dict(), ours.state_dict()
+    assert list(sa) == list(sb)
+    for k in sa:
+        assert torch.equal(sa[k], sb[k]), k
+    torch.manual_seed(12)
+    theirs.reinit_mlps()
+    theirs.reinit_embeddings(new_vocab_size=300)
+    torch.manual_seed(12)
+    ours.reinit_mlps()
+    ours.reinit_embeddings(new_vocab_size=300)
+    sa, sb = theirs.state_dict(), ours.state_dict()
+    assert sb["embed_tokens.weight"].shape == (300, 64) and ours.config.vocab_size == 300
+    for k in sa:
+        assert torch.equal(sa[k], sb[k]), k
