@@ -546,3 +546,53 @@ def test_initialisation_and_reinitialisation_draw_the_same_weights(ref, kw):
     assert sb["embed_tokens.weight"].shape == (300, 64) and ours.config.vocab_size == 300
     for k in sa:
         assert torch.equal(sa[k], sb[k]), k
+
+
+def test_asynchronous_checkpoints_cross_load(ref, tmp_path):
+    """The background-writer managers of both code bases (host clone, staging directory, persist, rotation): a file
+    written by either loads into the other with the same step, token count, parameters and optimizer moments, and both
+    keep the same number of files."""
+    from kotodama_b200.ckpt.manager import AsyncCheckpointManager
+    from kotodama_b200.optim.muon import HybridScheduler, build_hybrid_optimizer
+    theirs, ours = _pair(ref, dtype=torch.float32)
+    ours.load_state_dict(theirs.state_dict())
+    tm, ta = ref.muon.build_hybrid_optimizer(theirs)
+    om, oa = build_hybrid_optimizer(ours)
+    ids = torch.randint(0, 211, (2, 16), generator=torch.Generator().manual_seed(6))
+    for model, opts in ((theirs, (tm, ta)), (ours, (om, oa))):
+        model(ids, labels=ids)["loss"].backward()
+        for o in opts:
+            o.step()
+    ts = ref.muon.HybridScheduler(tm, ta, warmup_steps=3, total_steps=50)
+    so = HybridScheduler(om, oa, warmup_steps=3, total_steps=50)
+    a = ref.ckpt.AsyncCheckpointManager(str(tmp_path / "theirs"), rank=0, keep_last_n=2, shm_dir=str(tmp_path / "shm_a"), compress=False)
+    b = AsyncCheckpointManager(str(tmp_path / "ours"), rank=0, keep_last_n=2, shm_dir=str(tmp_path / "shm_b"), compress=False)
+    for step in (10, 20, 30):
+        ts.step(step)
+        so.step(step)
+        a.save(step, theirs, tm, ta, ts, tokens_consumed=1000 * step)
+        b.save(step, ours, om, oa, so, tokens_consumed=1000 * step)
+    a.shutdown()
+    b.shutdown()
+    fa = sorted(p.name for p in (tmp_path / "theirs").glob("step_*.pt*"))
+    fb = sorted(p.name for p in (tmp_path / "ours").glob("step_*.pt*"))
+    assert fa == fb == ["step_00000020.pt", "step_00000030.pt"]
+    # theirs -> ours
+    fresh = _pair(ref, dtype=torch.float32)[1]
+    fm, fa_ = build_hybrid_optimizer(fresh)
+    state = AsyncCheckpointManager(str(tmp_path / "theirs"), rank=0, shm_dir=str(tmp_path / "shm_c"), compress=False).load_latest(
+        fresh, fm, fa_, torch.device("cpu"))
+    assert state["step"] == 30 and state["tokens_consumed"] == 30000
+    for (n, p), (_, q) in zip(theirs.named_parameters(), fresh.named_parameters()):
+        assert torch.equal(p, q), n
+    mom_a = [s["momentum_buffer"] for s in tm.state.values() if "momentum_buffer" in s]
+    mom_b = [s["momentum_buffer"] for s in fm.state.values() if "momentum_buffer" in s]
+    assert len(mom_a) == len(mom_b) > 0 and all(torch.equal(x, y) for x, y in zip(mom_a, mom_b))
+    # ours -> theirs
+    fresh_t = _pair(ref, dtype=torch.float32)[0]
+    gm, ga = ref.muon.build_hybrid_optimizer(fresh_t)
+    state = ref.ckpt.AsyncCheckpointManager(str(tmp_path / "ours"), rank=0, shm_dir=str(tmp_path / "shm_d"), compress=False).load_latest(
+        fresh_t, gm, ga, torch.device("cpu"))
+    assert state["step"] == 30 and state["tokens_consumed"] == 30000
+    for (n, p), (_, q) in zip(ours.named_parameters(), fresh_t.named_parameters()):
+        assert torch.equal(p, q), n
