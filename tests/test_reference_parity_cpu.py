@@ -596,3 +596,40 @@ def test_asynchronous_checkpoints_cross_load(ref, tmp_path):
     assert state["step"] == 30 and state["tokens_consumed"] == 30000
     for (n, p), (_, q) in zip(ours.named_parameters(), fresh_t.named_parameters()):
         assert torch.equal(p, q), n
+
+
+def _reference_trainer():
+    """The reference's train.py as a module (for its parser and pure helpers).  It imports ``src.data.dataset``, a
+    module the upstream repository does not contain; the dataset classes of this package stand in for it."""
+    import types as _types
+    if "src.data.dataset" not in sys.modules:
+        data = _types.ModuleType("src.data")
+        data.__path__ = []
+        ds = _types.ModuleType("src.data.dataset")
+        from kotodama_b200.data.dataset import RandomTokenDataset, TokenizedDataset
+        ds.RandomTokenDataset, ds.TokenizedDataset = RandomTokenDataset, TokenizedDataset
+        sys.modules["src.data"], sys.modules["src.data.dataset"] = data, ds
+    return importlib.import_module("src.training.train")
+
+
+def test_training_flags_defaults_and_batch_ramp_match(ref, monkeypatch, tmp_path):
+    """Every flag of the reference's trainer exists here with the same default; a YAML file plus command-line overrides
+    resolve to the same values; the batch-size ramp gives the same accumulation count at every step."""
+    from kotodama_b200.config import grad_accum_for_step, parse_args
+    theirs = _reference_trainer()
+    monkeypatch.setattr(sys, "argv", ["train.py"])
+    a, b = vars(theirs.parse_args()), vars(parse_args([]))
+    assert set(a) <= set(b), sorted(set(a) - set(b))
+    assert {k: (a[k], b[k]) for k in a if a[k] != b[k]} == {}
+    cfg = tmp_path / "run.yaml"
+    cfg.write_text("model_size: 3b\nmicro_batch_size: 4\nmuon_lr: 0.015\nattn_res: true\nattn_res_boundaries: \"0,3,7\"\n"
+                   "decay_type: cosine\nsave_every: 123\nwandb: false\nfp8: true\n")
+    argv = ["--config", str(cfg), "--micro_batch_size", "2", "--warmup_steps", "77", "--async_checkpoint"]
+    monkeypatch.setattr(sys, "argv", ["train.py", *argv])
+    a, b = vars(theirs.parse_args()), vars(parse_args(argv))
+    assert {k: (a[k], b[k]) for k in a if a[k] != b[k]} == {}
+    assert b["micro_batch_size"] == 2 and b["muon_lr"] == 0.015 and b["save_every"] == 123 and b["fp8"] is True
+    for total, base, frac, pct in [(1000, 16, 0.25, 0.05), (1000, 16, 1.0, 0.05), (500, 7, 0.1, 0.2), (10, 4, 0.5, 0.0), (40, 3, 0.3, 0.5)]:
+        for step in range(0, total, max(total // 50, 1)):
+            assert grad_accum_for_step(step, total, base, frac, pct) == theirs._compute_grad_accum_for_step(
+                step, total, base, initial_batch_fraction=frac, ramp_pct=pct), (step, total, base, frac, pct)
