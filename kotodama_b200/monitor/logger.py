@@ -156,6 +156,8 @@ def scheduler_hook(step: int, **metrics: float) -> None:
         if _scheduler_client is None:
             _scheduler_client = httpx.Client(timeout=2.0)
         url = os.environ.get("HEIMDALL_URL", "http://localhost:7000")
-        _scheduler_client.post(f"{url}/api/v1/jobs/{job}/metrics", json={"step": step, "metrics": metrics})
+        clean = {k: v for k, v in metrics.items() if v is not None}
+        if clean:
+            _scheduler_client.post(f"{url}/api/v1/jobs/{job}/metrics", json={"step": step, "metrics": clean})
     except Exception:                   # noqa: BLE001
         pass

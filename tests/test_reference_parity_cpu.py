@@ -633,3 +633,27 @@ def test_training_flags_defaults_and_batch_ramp_match(ref, monkeypatch, tmp_path
         for step in range(0, total, max(total // 50, 1)):
             assert grad_accum_for_step(step, total, base, frac, pct) == theirs._compute_grad_accum_for_step(
                 step, total, base, initial_batch_fraction=frac, ramp_pct=pct), (step, total, base, frac, pct)
+
+
+def test_model_presets_and_gradient_diagnostics_match(ref):
+    """The size presets (tiny and the profile-only ones aside) carry the reference's dimensions, the parameter-count
+    estimate agrees, and the per-layer attention / MLP gradient norms the trainer logs are the same numbers."""
+    from kotodama_b200.config import MODEL_PRESETS, ModelConfig
+    from kotodama_b200.train import per_layer_grad_norms
+    theirs = _reference_trainer()
+    shared = set(theirs.MODEL_CONFIGS) & set(MODEL_PRESETS)
+    assert {"full", "3b", "8b", "proxy", "intermediate", "smoke"} <= shared
+    for name in shared:
+        a, b = theirs.MODEL_CONFIGS[name], MODEL_PRESETS[name]
+        assert {k: (a[k], b.get(k)) for k in a if a[k] != b.get(k)} == {}, name
+        ca, cb = ref.llama.LuxiaModelConfig(**a), ModelConfig(**b)
+        assert ca.param_count() == cb.param_count(), name
+    t, o = _pair(ref, dtype=torch.float32, layers=9)
+    o.load_state_dict(t.state_dict())
+    ids = torch.randint(0, 211, (2, 16), generator=torch.Generator().manual_seed(8))
+    t(ids, labels=ids)["loss"].backward()
+    o(ids, labels=ids)["loss"].backward()
+    ga, gb = theirs._per_layer_grad_norms(t), per_layer_grad_norms(o)
+    assert set(ga) == set(gb) and {"grad/layer_0/attn", "grad/layer_4/mlp", "grad/layer_8/attn_mlp_ratio"} <= set(ga)
+    for k, v in ga.items():
+        assert gb[k] == pytest.approx(v, rel=1e-4), k
