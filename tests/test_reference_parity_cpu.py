@@ -657,3 +657,42 @@ def test_model_presets_and_gradient_diagnostics_match(ref):
     assert set(ga) == set(gb) and {"grad/layer_0/attn", "grad/layer_4/mlp", "grad/layer_8/attn_mlp_ratio"} <= set(ga)
     for k, v in ga.items():
         assert gb[k] == pytest.approx(v, rel=1e-4), k
+
+
+def test_concept_geometry_statistics_match_the_reference_script(ref):
+    """The structure statistics of the concept-geometry track against the functions of the reference's
+    ``scripts/analysis/analyze_concept_geometry.py``: target distance matrices, Spearman Mantel rho (ties included),
+    cyclic-neighbour hit rate and ordinal window overlap, on a noisy ring, a noisy line and pure noise."""
+    import importlib.util
+    import math
+
+    import numpy as np
+    script = os.path.join(os.environ.get("KOTODAMA_REFERENCE", os.path.join(os.path.dirname(ROOT), "reference")),
+                          "scripts", "analysis", "analyze_concept_geometry.py")
+    if not os.path.isfile(script):
+        pytest.skip("the reference's analysis scripts are not on this machine")
+    spec = importlib.util.spec_from_file_location("reference_concepts", script)
+    theirs = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(theirs)
+    sys.path.insert(0, os.path.join(ROOT, "tools", "analysis"))
+    import analyze_concept_geometry as ours
+    rng = np.random.default_rng(0)
+    n = 12
+    ang = np.arange(n) / n * 2 * math.pi
+    clouds = {"ring": np.stack([np.cos(ang), np.sin(ang)], 1) @ rng.normal(size=(2, 16)) + rng.normal(size=(n, 16)) * 0.15,
+              "line": np.arange(n, dtype=float)[:, None] @ rng.normal(size=(1, 16)) + rng.normal(size=(n, 16)) * 0.8,
+              "noise": rng.normal(size=(n, 16))}
+    assert np.array_equal(theirs.cyclic_distance_matrix(n), ours.target_dist(n, True))
+    assert np.array_equal(theirs.ordinal_distance_matrix(n), ours.target_dist(n, False))
+    for name, x in clouds.items():
+        d = ours.pdist(x - x.mean(0))
+        for cyclic in (True, False):
+            tgt = ours.target_dist(n, cyclic)
+            rho_t, p_t = theirs.mantel_test(d, tgt, n_perm=300, seed=1)
+            got = ours.mantel(d, tgt, 300, np.random.default_rng(1))
+            assert got["r"] == pytest.approx(rho_t, abs=1e-9), (name, cyclic)
+            assert abs(got["p"] - p_t) < 0.08, (name, cyclic, got["p"], p_t)         # same null, different draws
+        for k in (1, 2):
+            assert ours.knn_cyclic_hit(d, k) == pytest.approx(theirs.knn_cyclic(d, n, k)), name
+        assert ours.knn_ordinal_window(d, 3, 2) == pytest.approx(theirs.knn_ordinal_overlap(d, n, 3, 2)), name
+    assert ours.mantel(ours.pdist(clouds["ring"]), ours.target_dist(n, True), 200, np.random.default_rng(2))["p"] < 0.02

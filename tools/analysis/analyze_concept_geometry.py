@@ -3,8 +3,8 @@
 structural metric comes with a null: a permutation null (``--n-perm`` relabellings of the items) or,
 for direction statistics, the closed form for random directions in D dimensions.
 
-  cyclic      Mantel correlation between activation distances and circular item distances, share of
-              items whose nearest neighbours are their cyclic neighbours, and the winding of the
+  cyclic      Mantel test (Spearman's rho) between activation distances and circular item distances, share
+              of items whose nearest neighbours are their cyclic neighbours, and the winding of the
               items in the plane of the two leading principal components
   ordinal     Mantel correlation with |i - j|, k-NN overlap with the ordinal neighbours, and the
               Spearman correlation of the first principal component with the item order
@@ -58,18 +58,32 @@ def corr(a: np.ndarray, b: np.ndarray) -> float:
     return float(np.corrcoef(a, b)[0, 1])
 
 
+def rank_avg(x: np.ndarray) -> np.ndarray:
+    """Ranks 0..n-1 with ties sharing their average rank (what Spearman's rho is defined on)."""
+    _, inv, cnt = np.unique(x, return_inverse=True, return_counts=True)
+    last = np.cumsum(cnt) - 1.0
+    return (last - (cnt - 1) / 2.0)[inv]
+
+
 def mantel(da: np.ndarray, db: np.ndarray, n_perm: int, rng: np.random.Generator) -> dict:
-    """Correlation of two distance matrices over item pairs; the null relabels the items of one of them."""
+    """Mantel test: Spearman's rho between the upper triangles of two distance matrices (rank correlation, as in
+    the reference's ``mantel_test``: distances in activation space need not be linear in the target distance), with
+    the items of one matrix relabelled for the null.  ``pearson_r`` is reported beside it."""
     a, b = upper(da), upper(db)
-    r = corr(a, b)
+    iu = np.triu_indices_from(da, 1)
+    ranks = np.zeros_like(da, dtype=float)
+    ranks[iu] = rank_avg(a)
+    ranks = ranks + ranks.T                               # a relabelled matrix has the same values, hence the same ranks
+    rb = rank_avg(b)
+    r = corr(ranks[iu], rb)
     n = da.shape[0]
     null = np.empty(n_perm)
     for i in range(n_perm):
         p = rng.permutation(n)
-        null[i] = corr(upper(da[np.ix_(p, p)]), b)
+        null[i] = corr(ranks[np.ix_(p, p)][iu], rb)
     sd = float(null.std()) if n_perm else 0.0
-    return {"r": r, "p": float(((null >= r).sum() + 1) / (n_perm + 1)), "null_mean": float(null.mean()) if n_perm else 0.0,
-            "z": float((r - null.mean()) / sd) if sd > 1e-12 else 0.0}
+    return {"r": r, "pearson_r": corr(a, b), "p": float(((null >= r).sum() + 1) / (n_perm + 1)),
+            "null_mean": float(null.mean()) if n_perm else 0.0, "z": float((r - null.mean()) / sd) if sd > 1e-12 else 0.0}
 
 
 def target_dist(n: int, cyclic: bool) -> np.ndarray:
@@ -94,6 +108,30 @@ def knn_overlap(d: np.ndarray, target: np.ndarray, k: int = 2) -> float:
         b = set(np.argsort(target[i] + np.eye(n)[i] * 1e9, kind="stable")[:k])
         hits += len(a & b)
     return hits / (n * k)
+
+
+def knn_cyclic_hit(d: np.ndarray, k: int = 1) -> float:
+    """Share of items with a cyclic neighbour ((i - 1) mod n or (i + 1) mod n) among their ``k`` nearest items."""
+    n = d.shape[0]
+    hits = 0
+    for i in range(n):
+        row = d[i].copy()
+        row[i] = np.inf
+        hits += bool({(i - 1) % n, (i + 1) % n} & set(np.argsort(row)[:k].tolist()))
+    return hits / n
+
+
+def knn_ordinal_window(d: np.ndarray, k: int = 3, window: int = 2) -> float:
+    """Mean share of an item's ``k`` nearest items that lie within ``window`` positions of it in the order."""
+    n = d.shape[0]
+    total = 0.0
+    for i in range(n):
+        row = d[i].copy()
+        row[i] = np.inf
+        near = set(np.argsort(row)[:k].tolist())
+        expected = {j for j in range(max(0, i - window), min(n, i + window + 1)) if j != i}
+        total += len(near & expected) / min(k, len(expected)) if expected else 0.0
+    return total / n
 
 
 def knn_null(target: np.ndarray, k: int, n_perm: int, rng: np.random.Generator) -> float:
@@ -141,7 +179,7 @@ def analyse_cyclic(x: np.ndarray, n_perm: int, rng: np.random.Generator) -> dict
     # items on a circle in order turn by +-2 pi in total; anything else gives a winding far from +-1
     winding = float((ang[-1] - ang[0]) / (2 * math.pi)) if xy.shape[1] == 2 else 0.0
     return {**mantel(d, tgt, n_perm, rng), "knn_overlap": knn_overlap(d, tgt), "knn_null": knn_null(tgt, 2, n_perm, rng),
-            "winding": winding}
+            "knn_cyclic_hit": knn_cyclic_hit(d), "winding": winding}
 
 
 def analyse_ordinal(x: np.ndarray, n_perm: int, rng: np.random.Generator) -> dict:
@@ -150,7 +188,7 @@ def analyse_ordinal(x: np.ndarray, n_perm: int, rng: np.random.Generator) -> dic
     d = pdist(x - x.mean(0))
     xy, _ = pcs(x, 1)
     return {**mantel(d, tgt, n_perm, rng), "knn_overlap": knn_overlap(d, tgt), "knn_null": knn_null(tgt, 2, n_perm, rng),
-            "pc1_rank_correlation": abs(spearman(xy[:, 0], np.arange(n)))}
+            "knn_ordinal_window": knn_ordinal_window(d), "pc1_rank_correlation": abs(spearman(xy[:, 0], np.arange(n)))}
 
 
 def analyse_geographic(x: np.ndarray, coords: np.ndarray, n_perm: int, rng: np.random.Generator) -> dict:
