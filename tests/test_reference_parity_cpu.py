@@ -696,3 +696,55 @@ def test_concept_geometry_statistics_match_the_reference_script(ref):
             assert ours.knn_cyclic_hit(d, k) == pytest.approx(theirs.knn_cyclic(d, n, k)), name
         assert ours.knn_ordinal_window(d, 3, 2) == pytest.approx(theirs.knn_ordinal_overlap(d, n, 3, 2)), name
     assert ours.mantel(ours.pdist(clouds["ring"]), ours.target_dist(n, True), 200, np.random.default_rng(2))["p"] < 0.02
+
+
+def test_text_quality_formulas_match_the_reference_script(ref):
+    """The closed-form pieces of the text-quality track (type/token ratios of a sample's head, Yule's K, Honore's R,
+    n-grams, slope, entropy) against the reference's ``scripts/analysis/analyze_text_quality.py``.  That script needs
+    NLTK for tokenising and tagging; a stand-in module lets it import, and only functions that take word lists are
+    compared (this package tokenises with regular expressions instead, so the full metrics differ by design)."""
+    import importlib.util
+    import types as _types
+    script = os.path.join(os.environ.get("KOTODAMA_REFERENCE", os.path.join(os.path.dirname(ROOT), "reference")),
+                          "scripts", "analysis", "analyze_text_quality.py")
+    if not os.path.isfile(script):
+        pytest.skip("the reference's analysis scripts are not on this machine")
+    added = []
+    if "nltk" not in sys.modules:
+        try:
+            import nltk  # noqa: F401
+        except ImportError:
+            fake = _types.ModuleType("nltk")
+            fake.pos_tag = fake.sent_tokenize = fake.word_tokenize = lambda *a, **k: []
+            fake.download = lambda *a, **k: True
+            fake.data = _types.SimpleNamespace(find=lambda *a, **k: True)
+            tok = _types.ModuleType("nltk.tokenize")
+            tok.RegexpTokenizer = lambda *a, **k: None
+            sys.modules["nltk"], sys.modules["nltk.tokenize"] = fake, tok
+            added = ["nltk", "nltk.tokenize"]
+    try:
+        spec = importlib.util.spec_from_file_location("reference_text_quality", script)
+        theirs = importlib.util.module_from_spec(spec)
+        sys.modules["reference_text_quality"] = theirs          # its dataclasses look their module up by name
+        spec.loader.exec_module(theirs)
+    finally:
+        for m in added:
+            sys.modules.pop(m, None)
+    sys.path.insert(0, os.path.join(ROOT, "tools", "analysis"))
+    import analyze_text_quality as ours
+    import random
+    rnd = random.Random(0)
+    vocab = [f"w{i}" for i in range(60)]
+    samples = [[rnd.choice(vocab[: 5 + i * 11]) for _ in range(40 + 90 * i)] for i in range(6)] + [["a"] * 30, ["a", "b"], []]
+    for ws in samples:
+        for window in (50, 100, 200, 500):
+            assert ours.head_ttr(ws, window) == pytest.approx(theirs.compute_ttr(ws, window)), (len(ws), window)
+        assert ours.yules_k(ws) == pytest.approx(theirs.compute_yules_k(ws)), len(ws)
+        assert ours.honores_r(ws) == pytest.approx(theirs.compute_honores_r(ws)), len(ws)
+        for n in (1, 3, 5):
+            assert ours.ngrams(ws, n) == theirs.get_ngrams(ws, n)
+    for ys in ([1.0, 2.0, 4.0, 8.0], [3.0], [], [5.0, 5.0, 5.0], [9.0, 7.0, 2.0, 2.5, 0.1]):
+        assert ours.slope(ys) == pytest.approx(theirs.linear_slope(ys))
+    for counts in ([1, 1, 1, 1], [10, 1], [7], [3, 0, 5]):
+        tot = sum(counts)
+        assert ours.entropy(counts) == pytest.approx(theirs.entropy([c / tot for c in counts]))

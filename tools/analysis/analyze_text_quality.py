@@ -4,7 +4,8 @@ reference's ``scripts/analysis/analyze_text_quality.py`` (its ``LexicalMetrics``
 ``StructuralMetrics``, ``RepetitionMetrics`` and ``CreativityMetrics``), computed here with regular
 expressions and closed word lists only - no NLTK / tagger models, so it runs offline:
 
-  lexical      windowed type/token ratios (50/100/200/500/all), hapax ratio, Yule's K, Honore's R,
+  lexical      type/token ratios of the first 50/100/200/500 words and of the whole sample, moving-average
+               type/token ratios, hapax ratio, Yule's K, Honore's R,
                part-of-speech shares from closed classes + suffix rules, sentence-length statistics,
                punctuation variety
   coherence    cosine similarity of consecutive sentences (topic drift: mean, spread, slope), novelty
@@ -138,7 +139,15 @@ def guess_pos(w: str) -> str:
 
 
 # ----------------------------------------------------------------------------- the five families
+def head_ttr(ws: Sequence[str], window: int) -> float:
+    """Type/token ratio of the first ``window`` words (the reference's ``compute_ttr``): comparable across samples of
+    different length because every sample is cut to the same number of words."""
+    head = ws[:window]
+    return len(set(head)) / len(head) if head else 0.0
+
+
 def windowed_ttr(ws: Sequence[str], window: int) -> float:
+    """Moving-average type/token ratio: the mean over windows of ``window`` words, half a window apart."""
     if not ws:
         return 0.0
     if len(ws) <= window:
@@ -154,16 +163,16 @@ def yules_k(ws: Sequence[str]) -> float:
     if n < 2:
         return 0.0
     spectrum = Counter(Counter(ws).values())
-    return 1e4 * (sum(i * i * v for i, v in spectrum.items()) - n) / (n * n)
+    return max(1e4 * (sum(i * i * v for i, v in spectrum.items()) - n) / (n * n), 0.0)
 
 
 def honores_r(ws: Sequence[str]) -> float:
-    """100 log N / (1 - V1 / V): rewards types used exactly once."""
+    """100 log(N + 1) / (1 - V1 / V): rewards types used exactly once (N + 1 as in the reference's ``compute_honores_r``)."""
     n, c = len(ws), Counter(ws)
     v, v1 = len(c), sum(1 for x in c.values() if x == 1)
     if n < 2 or v == 0 or v1 == v:
         return 0.0
-    return 100 * math.log(n) / (1 - v1 / v)
+    return 100 * math.log(n + 1) / (1 - v1 / v)
 
 
 def lexical(text: str) -> dict[str, float]:
@@ -173,8 +182,9 @@ def lexical(text: str) -> dict[str, float]:
     slen = [len(words(s)) for s in ss if words(s)] or [0]
     punct = [ch for ch in text if ch in ".,;:!?-—()[]\"'…"]
     n = max(len(ws), 1)
-    return {"tokens": len(ws), "ttr_50": windowed_ttr(ws, 50), "ttr_100": windowed_ttr(ws, 100), "ttr_200": windowed_ttr(ws, 200),
-            "ttr_500": windowed_ttr(ws, 500), "ttr_all": safe_div(len(c), len(ws)),
+    return {"tokens": len(ws), "ttr_50": head_ttr(ws, 50), "ttr_100": head_ttr(ws, 100), "ttr_200": head_ttr(ws, 200),
+            "ttr_500": head_ttr(ws, 500), "ttr_all": safe_div(len(c), len(ws)),
+            "mattr_50": windowed_ttr(ws, 50), "mattr_100": windowed_ttr(ws, 100),
             "hapax_ratio": safe_div(sum(1 for v in c.values() if v == 1), len(c)), "yules_k": yules_k(ws), "honores_r": honores_r(ws),
             "pos_noun_ratio": pos["noun"] / n, "pos_verb_ratio": pos["verb"] / n, "pos_adj_ratio": pos["adj"] / n,
             "pos_adv_ratio": pos["adv"] / n, "pos_pronoun_ratio": pos["pron"] / n,

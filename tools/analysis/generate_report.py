@@ -218,7 +218,7 @@ def quality_radar(tq: dict[str, Any], fg: str, ac: str) -> str:
     g = lambda fam, k, d=0.0: float(o.get(fam, {}).get(k, d))
     clamp = lambda v: max(0.0, min(1.0, v))
     scores = {
-        "diversity": clamp(g("lexical", "ttr_100", g("lexical", "mattr50"))),
+        "diversity": clamp(g("lexical", "ttr_100", g("lexical", "mattr_100"))),
         "non-repetition": clamp(g("repetition", "unique_3gram_ratio", g("repetition", "distinct_3"))),
         "coherence": clamp(g("coherence", "topic_similarity_mean", g("coherence", "adjacent_jaccard")) * 2.5),
         "structure": clamp(g("structural", "clause_depth_mean", 1.0) / 3.0),
