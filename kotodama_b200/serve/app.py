@@ -20,6 +20,7 @@ import threading
 import time
 from typing import Any, Optional, Union
 
+from ..data.tokenizer import ByteTokenizer, load_tokenizer  # noqa: F401  (re-exported: the server's public names)
 from .engine import Request, SamplingParams, ServingEngine
 
 
@@ -54,31 +55,6 @@ class CompletionRequest(BaseModel):
     n: int = Field(1, ge=1, le=8)
     stop: Union[list[str], str, None] = None          # a single string or a list, as the OpenAI API allows
 
-
-class ByteTokenizer:
-    """Fallback tokenizer (UTF-8 bytes + BOS/EOS) used when no Hugging Face tokenizer files are
-    available offline.  ids 0..255 are bytes, 256 = BOS, 257 = EOS."""
-
-    bos_token_id, eos_token_id, vocab_size = 256, 257, 258
-    name = "bytes"
-
-    def encode(self, text: str) -> list[int]:
-        return list(text.encode("utf-8"))
-
-    def decode(self, ids: list[int], skip_special_tokens: bool = True) -> str:
-        return bytes(i for i in ids if i < 256).decode("utf-8", errors="replace")
-
-
-def load_tokenizer(name: Optional[str]) -> Any:
-    """Hugging Face tokenizer from local files when present (the reference uses
-    ``HuggingFaceTB/SmolLM2-135M``, ``serve.py:227-230``); the byte tokenizer otherwise."""
-    if name:
-        try:
-            from transformers import AutoTokenizer
-            return AutoTokenizer.from_pretrained(name, local_files_only=True)
-        except Exception:       # noqa: BLE001 - no network / no files
-            pass
-    return ByteTokenizer()
 
 
 class Ticket:

@@ -14,7 +14,7 @@ import torch  # noqa: E402
 import yaml  # noqa: E402
 
 from kotodama_b200.eval import load_checkpoint_registry, load_model  # noqa: E402
-from kotodama_b200.serve.app import load_tokenizer  # noqa: E402
+from kotodama_b200.data.tokenizer import load_tokenizer  # noqa: E402
 
 
 def add_checkpoint_args(ap) -> None:

@@ -27,7 +27,7 @@ import numpy as np
 
 sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), ".."))
 from kotodama_b200.data.dataset import verify_token_file  # noqa: E402
-from kotodama_b200.serve.app import load_tokenizer  # noqa: E402
+from kotodama_b200.data.tokenizer import load_tokenizer  # noqa: E402
 
 
 def iter_documents(a: argparse.Namespace) -> Iterator[str]:
