@@ -70,3 +70,51 @@ def test_quantisers_refuse_ragged_shapes(lib):
     assert lib.kb_quant_rows(VP(PTR), LL(200), VP(PTR), LL(200), VP(PTR), I(4), I(200), I(0), VP(None)) == 5      # K % 128
     assert lib.kb_quant_blocks(VP(PTR), LL(256), VP(PTR), VP(PTR), VP(None), VP(None), I(100), I(256), I(0), VP(None)) == 5
     assert lib.kb_quant_cols_t(VP(PTR), LL(256), VP(PTR), VP(PTR), I(100), I(256), I(0), VP(None)) == 5           # M % 128
+
+
+def _skinny(lib, M=64, N=3072, K=3072, lda=None, ldb=None, a=PTR, b=PTR, bn=0, flags=0):
+    return lib.kb_gemm_skinny(VP(a), VP(b), VP(PTR), VP(None), I(M), I(N), I(K), LL(lda if lda is not None else K),
+                              LL(ldb if ldb is not None else K), LL(N), LL(0), F(1.0), F(0.0), I(0), I(bn), I(flags), VP(None), VP(None))
+
+
+def test_decode_size_gemm_refuses_bad_arguments(lib):
+    assert _skinny(lib, M=0) == 5 and _skinny(lib, M=129) == 5 and _skinny(lib, N=0) == 5 and _skinny(lib, K=0) == 5
+    assert _skinny(lib, lda=3076) == 6                               # row stride of A is not a multiple of 8 elements
+    assert _skinny(lib, ldb=3076) == 6
+    assert _skinny(lib, a=PTR + 2) == 6 and _skinny(lib, b=PTR + 8) == 6     # operands must be 16-byte aligned for TMA
+    assert _skinny(lib, bn=64) == 5                                  # tile widths are 128 or 256
+    assert _skinny(lib, K=3100, flags=1) == 6                        # the tile-major weight copy needs whole 64-deep k-blocks
+
+
+def _skinny_ar(lib, M=64, N=3072, world=2, rank=0, slot=64 * 3072, recv=None, flags=None, out=PTR, epoch=PTR, counters=PTR):
+    arr = lambda v: (VP * 8)(*(list(v) + [None] * (8 - len(v))))
+    recv = recv if recv is not None else [PTR] * max(world, 0)
+    flags = flags if flags is not None else [PTR] * max(world, 0)
+    return lib.kb_gemm_skinny_allreduce(VP(PTR), VP(PTR), VP(out), VP(None), I(M), I(N), I(1024), LL(1024), LL(1024), I(0), arr(recv),
+                                        arr(flags), I(world), I(rank), LL(slot), VP(epoch), VP(counters), D(1.0), VP(None), VP(None))
+
+
+def test_fused_gemm_allreduce_refuses_bad_arguments(lib):
+    assert _skinny_ar(lib, world=0) == 5 and _skinny_ar(lib, world=9, recv=[PTR] * 8, flags=[PTR] * 8) == 5
+    assert _skinny_ar(lib, rank=2) == 5 and _skinny_ar(lib, rank=-1) == 5
+    assert _skinny_ar(lib, N=3076) == 5                              # rows are pushed as 16-byte pieces
+    assert _skinny_ar(lib, slot=1000) == 5                           # M * N does not fit a receive slot
+    assert _skinny_ar(lib, epoch=None) == 5 and _skinny_ar(lib, counters=None) == 5
+    assert _skinny_ar(lib, recv=[PTR, None]) == 6 and _skinny_ar(lib, flags=[None, PTR]) == 6      # a peer buffer is missing
+    assert _skinny_ar(lib, recv=[PTR, PTR + 4]) == 6 and _skinny_ar(lib, out=PTR + 8) == 6         # or misaligned
+
+
+def test_serving_kernels_refuse_bad_arguments(lib):
+    qk = lambda hd=128, kp=PTR, vp=PTR, slot=PTR: lib.kb_qknorm_rope_append(
+        VP(PTR), VP(PTR), VP(PTR), VP(PTR), VP(PTR), VP(PTR), VP(PTR), I(4), I(4), I(24), I(8), I(hd), I(0), F(1e-5), VP(None),
+        VP(kp), VP(vp), VP(slot), LL(1024), VP(None), VP(None))
+    assert qk(kp=None) == 5 and qk(vp=None) == 5 and qk(slot=None) == 5       # the append needs pages and slots
+    assert qk(hd=96) == 5                                                     # head sizes 64 and 128
+    dec = lambda n_q=24, n_kv=8, split=512: lib.kb_paged_decode_merged(
+        VP(PTR), LL(3072), VP(PTR), VP(PTR), VP(PTR), I(80), VP(PTR), I(4), I(n_q), I(n_kv), I(128), I(1024), I(split), F(0.088),
+        VP(PTR), VP(PTR), VP(PTR), LL(3072), I(64), VP(PTR), VP(None))
+    assert dec(n_q=25) == 5 and dec(split=500) == 5 and dec(split=4096) == 5  # whole head groups, whole pages, at most 2048 tokens per split
+    assert lib.kb_kv_append(VP(PTR), VP(PTR), LL(1024), LL(1024), VP(PTR), VP(PTR), VP(PTR), I(4), I(1020), I(128), LL(1024), VP(None),
+                            VP(None)) == 5                                    # rows are copied as 16-byte pieces
+    assert lib.kb_swiglu_fwd(VP(PTR), VP(PTR), LL(4), I(8188), VP(None)) == 5
+    assert lib.kb_pack_weight_tiles(VP(PTR), LL(3100), VP(PTR), I(3072), I(3100), VP(None)) == 5
