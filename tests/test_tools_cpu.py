@@ -180,3 +180,26 @@ def test_benchmark_matrix_on_the_tiny_cpu_configuration(tmp_path):
     import benchmark_matrix as bm
     text = bm.estimates([{"name": "3b", "tok_s_median": 360000.0, "gpu_mem_gb_max": 120.0}])
     assert "50 B tokens ->   1.6 days" in text and "250 B tokens" in text
+
+
+def test_run_sweep_runs_arms_skips_finished_ones_and_compares(tmp_path):
+    import yaml
+    import run_sweep
+    assert run_sweep.flags_of({"muon_lr": 0.02, "attn_res": True, "fp8": False, "x": None}) == ["--muon_lr", "0.02", "--attn_res"]
+    for f in sorted((ROOT / "configs" / "sweeps").glob("*.yaml")):          # the shipped sweeps parse and build commands
+        dry = tool("run_sweep.py", f, "--gpus", 8, "--dry-run", "--out", tmp_path / f.stem)
+        spec = yaml.safe_load(f.read_text())
+        assert dry.count("--checkpoint_dir") == len(spec["experiments"]) and "--nproc-per-node 8" in dry
+    sweep = tmp_path / "s.yaml"
+    sweep.write_text(yaml.safe_dump({"base": str(ROOT / "configs" / "tiny-cpu.yaml"),
+                                     "common": {"total_steps": 4, "log_every": 1, "save_every": 999999},
+                                     "experiments": {"adamw": {"adamw_only": True}, "muon": {"muon_lr": 0.02}, "unused": {}}}))
+    out = tool("run_sweep.py", sweep, "--gpus", 1, "--only", "adamw,muon", "--out", tmp_path / "o")
+    assert "ranking on train/loss" in out and "unused" not in out
+    summary = json.loads((tmp_path / "o" / "sweep_summary.json").read_text())
+    assert [r["name"] for r in summary["arms"]] == ["adamw", "muon"] and summary["comparison"]["baseline"] == "adamw"
+    assert all((tmp_path / "o" / n / "DONE").exists() and (tmp_path / "o" / n / "metrics.jsonl").exists() for n in ("adamw", "muon"))
+    again = tool("run_sweep.py", sweep, "--gpus", 1, "--only", "adamw,muon", "--out", tmp_path / "o")
+    assert again.count("already done, skipped") == 2
+    r = subprocess.run([sys.executable, str(ROOT / "tools" / "run_sweep.py"), str(sweep), "--only", "nope"], capture_output=True, text=True)
+    assert r.returncode != 0 and "unknown arms" in r.stderr
