@@ -203,3 +203,14 @@ def test_run_sweep_runs_arms_skips_finished_ones_and_compares(tmp_path):
     assert again.count("already done, skipped") == 2
     r = subprocess.run([sys.executable, str(ROOT / "tools" / "run_sweep.py"), str(sweep), "--only", "nope"], capture_output=True, text=True)
     assert r.returncode != 0 and "unknown arms" in r.stderr
+
+
+def test_attnres_step_bench_compares_the_formulations_on_cpu():
+    r = subprocess.run([sys.executable, str(ROOT / "benchmarks" / "attnres_step_bench.py"), "--model", "tiny", "--device", "cpu",
+                        "--seq", "64", "--micro_batch", "2", "--iters", "2", "--warmup", "1", "--json",
+                        "--arms", "baseline,blocked,per_call,module,blocks=1"], capture_output=True, text=True, cwd=ROOT, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    arms = json.loads(r.stdout.strip().splitlines()[-1])["arms"]
+    assert list(arms) == ["baseline", "blocked", "per_call", "module", "blocks=1"]
+    assert arms["blocked"]["blocked_groups"] > 0 and arms["per_call"]["blocked_groups"] == 0 and arms["baseline"]["overhead_pct"] == 0.0
+    assert all(v["ms"] > 0 and v["tokens_per_s"] > 0 for v in arms.values())
