@@ -61,3 +61,25 @@ def test_yaml_config_and_cli_override(tmp_path):
     a = parse_args(["--config", str(cfg), "--muon_lr", "0.5"])
     assert a.model_size == "smoke" and a.sequence_length == 128 and a.muon_lr == 0.5 and a.attn_res is True
     assert not hasattr(a, "bogus_key")
+
+
+def test_every_shipped_trainer_configuration_parses_without_unknown_keys(caplog):
+    import logging
+    from pathlib import Path
+    import yaml
+    root = Path(__file__).resolve().parents[1] / "configs"
+    not_trainer = {"model.yaml", "checkpoints.yaml", "concepts.yaml", "prompts.yaml"}     # read by the eval loader / analysis tracks
+    seen = 0
+    for f in sorted(root.glob("*.yaml")):
+        if f.name in not_trainer:
+            continue
+        with caplog.at_level(logging.WARNING):
+            caplog.clear()
+            a = parse_args(["--config", str(f)])
+        assert not [r for r in caplog.records if "Unknown keys" in r.getMessage()], (f.name, caplog.text)
+        keys = yaml.safe_load(f.read_text())
+        assert all(getattr(a, k.replace("-", "_")) == v for k, v in keys.items()), f.name
+        seen += 1
+    assert seen >= 10
+    full = parse_args(["--config", str(root / "training.yaml")])
+    assert full.total_tokens == 80_000_000_000 and full.global_batch_tokens == 2_097_152 and full.batch_ramp_initial == 0.25
