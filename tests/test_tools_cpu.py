@@ -214,3 +214,25 @@ def test_attnres_step_bench_compares_the_formulations_on_cpu():
     assert list(arms) == ["baseline", "blocked", "per_call", "module", "blocks=1"]
     assert arms["blocked"]["blocked_groups"] > 0 and arms["per_call"]["blocked_groups"] == 0 and arms["baseline"]["overhead_pct"] == 0.0
     assert all(v["ms"] > 0 and v["tokens_per_s"] > 0 for v in arms.values())
+
+
+def test_roofline_floors_follow_from_the_shapes(tmp_path):
+    peaks = tmp_path / "p.json"
+    peaks.write_text(json.dumps({"hbm_gbs": 6451.8, "bf16_tflops_sustained": 1418.9}))
+    t = json.loads(tool("roofline.py", "train", "--model", "3b", "--micro_batch", 8, "--seq", 4096, "--peaks", peaks, "--json",
+                        "--measured_ms", 840))
+    by = {r["op"]: r for r in t["ops"]}
+    n, proj = 8 * 4096, 28 * (2 * 3072 * 3072 + 2 * 3072 * 1024 + 3 * 3072 * 8192)
+    assert by["projections (fwd, dgrad, wgrad)"]["flops"] == pytest.approx(6.0 * proj * n)
+    assert by["attention forward"]["flops"] == pytest.approx(2 * 2 * 28 * 3072 * 2048 * n)
+    assert t["floor_ms"] == pytest.approx(sum(r["ms"] for r in t["ops"])) and 0.5 < t["fraction_of_floor"] < 1.0
+    t8 = json.loads(tool("roofline.py", "train", "--model", "3b", "--gpus", 8, "--peaks", peaks, "--json"))
+    ns1, ns8 = by["Newton-Schulz"]["flops"], {r["op"]: r for r in t8["ops"]}["Newton-Schulz"]["flops"]
+    assert ns8 == pytest.approx(ns1 / 8) and "dp gradient reduction + parameter publish" in t8["comm_floor_ms"]
+    d = json.loads(tool("roofline.py", "decode", "--model", "3b", "--batch", 64, "--context", 1220, "--peaks", peaks, "--json"))
+    kv = 2.0 * 64 * 1220 * 28 * 2 * 1024
+    assert {r["op"]: r["bytes"] for r in d["ops"]}["kv cache"] == pytest.approx(kv) and 2.2 < d["floor_ms"] < 2.4
+    d8 = json.loads(tool("roofline.py", "decode", "--tp", 8, "--peaks", peaks, "--json"))
+    assert d8["floor_ms"] == pytest.approx(d["floor_ms"] / 8)
+    nominal = tool("roofline.py", "decode", "--peaks", tmp_path / "missing.json")
+    assert "MEASURED_PEAKS.json" in nominal or "nominal" in nominal
