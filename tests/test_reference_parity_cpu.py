@@ -748,3 +748,76 @@ def test_text_quality_formulas_match_the_reference_script(ref):
     for counts in ([1, 1, 1, 1], [10, 1], [7], [3, 0, 5]):
         tot = sum(counts)
         assert ours.entropy(counts) == pytest.approx(theirs.entropy([c / tot for c in counts]))
+
+
+def _reference_tool(name: str) -> str:
+    path = os.path.join(os.environ.get("KOTODAMA_REFERENCE", os.path.join(os.path.dirname(ROOT), "reference")), "tools", name)
+    if not os.path.isfile(path):
+        pytest.skip("the reference's tools are not on this machine")
+    return path
+
+
+def test_training_log_is_read_alike_by_the_reference_log_tool_and_ours(tmp_path):
+    """A log written by this package's trainer goes through the reference's ``tools/extract_benchmark_results.py``
+    (its ``extract_metrics`` takes the log text) and through ``tools/extract_benchmark_results.py`` here: both see the
+    same tokens/s samples and memory figure, i.e. the step line keeps the reference's format."""
+    import importlib.util
+    import logging
+    from kotodama_b200.train import parse_args, train
+    spec = importlib.util.spec_from_file_location("reference_extract", _reference_tool("extract_benchmark_results.py"))
+    theirs = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(theirs)
+    sys.path.insert(0, os.path.join(ROOT, "tools"))
+    import extract_benchmark_results as ours
+    log = tmp_path / "train.log"
+    handler = logging.FileHandler(log)
+    handler.setFormatter(logging.Formatter("%(message)s"))
+    logging.getLogger("kotodama_b200.train").addHandler(handler)
+    try:
+        train(parse_args(["--config", os.path.join(ROOT, "configs", "tiny-cpu.yaml"), "--total_steps", "9", "--log_every", "1",
+                          "--save_every", "999999", "--checkpoint_dir", str(tmp_path / "ck")]))
+    finally:
+        logging.getLogger("kotodama_b200.train").removeHandler(handler)
+        handler.close()
+    text = log.read_text()
+    got_theirs = theirs.extract_metrics(text)
+    got_ours = ours.summarise(str(log), skip=5)
+    import re
+    import numpy as np
+    samples = [float(v) for v in re.findall(r"tok/s=(\d+\.?\d*)", text)]
+    assert len(samples) == 9 and got_ours["lines"] == 9
+    assert got_theirs["n_samples"] == 4 and got_theirs["peak_tok_per_sec"] == int(max(samples))
+    assert got_theirs["min_tok_per_sec"] == int(min(samples[5:])) and got_theirs["avg_tok_per_sec"] == int(sum(samples[5:]) / 4)
+    assert got_ours["tok_s_median"] == pytest.approx(float(np.median(samples[5:])))
+    assert got_theirs["peak_gpu_mem_gb"] == got_ours["gpu_mem_gb_max"] == 0.0
+
+
+def test_trace_summary_matches_the_reference_trace_tool(tmp_path):
+    """The same chrome trace through the reference's ``tools/parse_profile.py`` (run as the script it is) and through
+    ``tools/parse_profile.py`` here: kernel order, totals, counts and the host-op table agree."""
+    import json
+    import subprocess
+    import numpy as np
+    rng = np.random.default_rng(0)
+    events = []
+    for i in range(200):
+        events.append({"cat": "kernel", "name": f"kernel_{int(rng.integers(0, 12))}", "dur": int(rng.integers(1, 5000)), "ts": i})
+        events.append({"cat": "cpu_op", "name": f"aten::op_{int(rng.integers(0, 6))}", "dur": int(rng.integers(1, 900)), "ts": i})
+    events += [{"cat": "user_annotation", "name": "FORWARD", "dur": 123456, "ts": 0}, {"cat": "kernel", "name": "zero_dur", "dur": 0},
+               {"cat": "gpu_memcpy", "name": "Memcpy HtoD", "dur": 77}]
+    trace = tmp_path / "t.json"
+    trace.write_text(json.dumps({"traceEvents": events}))
+    theirs = subprocess.run([sys.executable, _reference_tool("parse_profile.py"), str(trace)], capture_output=True, text=True, check=True).stdout
+    sys.path.insert(0, os.path.join(ROOT, "tools"))
+    import parse_profile as ours
+    rows = ours.parse(str(trace), top=30)
+    their_rows = [l.split() for l in theirs.split("-" * 125)[1].split("\nTop 30")[0].strip().splitlines()]
+    assert [r[0] for r in their_rows] == [r[0] for r in rows]
+    for (name, total_us, count), t in zip(rows, their_rows):
+        assert float(t[1]) == pytest.approx(total_us / 1e3, abs=0.051) and int(t[2]) == count
+    total_s = sum(r[1] for r in rows) / 1e6
+    assert f"Total CUDA kernel time: {total_s:.1f}s" in theirs and f"Unique CUDA kernels: {len(rows)}" in theirs
+    host = ours.parse_cpu(str(trace))
+    their_host = [l.split() for l in theirs.split("\n" + "-" * 110 + "\n")[1].strip().splitlines()]
+    assert [r[0] for r in their_host] == [r[0] for r in host] and host[0][0] == "FORWARD"
+    assert all(int(t[2]) == h[2] for t, h in zip(their_host, host))

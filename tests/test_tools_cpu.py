@@ -71,6 +71,7 @@ def test_log_and_trace_summaries(tmp_path):
     out = tool("parse_profile.py", trace)
     rows = [l.split() for l in out.splitlines()[1:]]
     assert rows[0][0] == "gemm_kernel" and rows[0][1] == "4.00" and rows[0][2] == "2" and rows[1][0] == "attn_kernel"
+    assert "device time 6.00 ms over 2 kernels" in out and "aten::mm" in out.split("host op")[1]
 
 
 @pytest.mark.parametrize("optimizer", ["muon", "adamw"])
