@@ -111,18 +111,37 @@ def _plateaus(series: list[tuple[int, float]], window: int = 10, rel_tol: float 
     return out
 
 
-def _jumps(series: list[tuple[int, float]], z: float = 4.0) -> list[dict[str, Any]]:
-    diffs = [series[i + 1][1] - series[i][1] for i in range(len(series) - 1)]
-    sd = _std(diffs)
-    if sd == 0:
+def _jumps(series: list[tuple[int, float]], sigma_threshold: float = 3.0, warmup_frac: float = 0.05) -> list[dict[str, Any]]:
+    """Step-over-step changes that stand out from the changes seen so far: after a warm-up (5 % of the points, at
+    least 10) a change counts as a jump when it lies more than ``sigma_threshold`` standard deviations from the mean of
+    all earlier changes (the reference's rule, ``src/eval/run_analysis.py:355-388``; running sums instead of its
+    quadratic rescan).  The spread has a floor of 1e-9 of the series' scale, so rounding noise on a smooth curve is
+    not a jump."""
+    if len(series) < 20:
         return []
-    m = sum(diffs) / len(diffs)
-    return [{"step": series[i + 1][0], "delta": d, "z": (d - m) / sd} for i, d in enumerate(diffs) if abs(d - m) > z * sd]
+    vals = [v for _, v in series]
+    deltas = [vals[i] - vals[i - 1] for i in range(1, len(vals))]
+    floor = max(1e-10, 1e-9 * sum(abs(v) for v in vals) / len(vals))
+    warm = max(10, int(len(series) * warmup_frac))
+    out = []
+    s1 = sum(deltas[:warm])
+    s2 = sum(d * d for d in deltas[:warm])
+    for i in range(warm, len(deltas)):
+        mean = s1 / i
+        sd = max(max(s2 / i - mean * mean, 0.0) ** 0.5, floor)
+        dev = abs(deltas[i] - mean) / sd
+        if dev > sigma_threshold:
+            out.append({"step": series[i + 1][0], "delta": deltas[i], "sigma": round(dev, 2)})
+        s1 += deltas[i]
+        s2 += deltas[i] * deltas[i]
+    return out
 
 
 def _slope_at(series: list[tuple[int, float]], step: int, window: int) -> Optional[float]:
-    """Least-squares slope over the points within ``window`` steps before ``step``."""
-    return _slope([p for p in series if step - window <= p[0] <= step])
+    """Least-squares slope over the points within ``window // 2`` steps on either side of ``step`` (at least three)."""
+    half = window // 2
+    pts = [p for p in series if step - half <= p[0] <= step + half]
+    return _slope(pts) if len(pts) >= 3 else None
 
 
 def _windowed_slopes(series: list[tuple[int, float]], window: int) -> list[tuple[int, float]]:
@@ -153,13 +172,14 @@ def _percentile(v: list[float], q: float) -> float:
 
 
 def _rolling_stats(series: list[tuple[int, float]], window: int) -> list[dict[str, float]]:
-    """Mean, spread and quartiles over consecutive stretches of ``window`` steps."""
+    """Mean, sample spread and quartiles over consecutive stretches of ``window`` steps (stretches with fewer than two
+    points are left out)."""
     out, lo = [], series[0][0] if series else 0
-    while series and lo <= series[-1][0]:
+    while series and lo < max(series[-1][0], series[0][0] + 1):
         w = [v for st, v in series if lo <= st < lo + window]
         if len(w) >= 2:
-            out.append({"step": lo + window, "mean": sum(w) / len(w), "std": _std(w), "p25": _percentile(w, 0.25),
-                        "p75": _percentile(w, 0.75)})
+            out.append({"step": lo + window, "step_center": lo + window // 2, "mean": sum(w) / len(w), "std": _std(w),
+                        "p25": _percentile(w, 0.25), "p75": _percentile(w, 0.75), "n": len(w)})
         lo += window
     return out
 
@@ -189,11 +209,13 @@ def training_dynamics(data: StepData, metric_keys: Optional[list[str]] = None) -
         coarse = _windowed_slopes(series, max(span // 20, 1))
         curv_floor = 1e-6 * max((abs(v) for _, v in coarse), default=0.0) / span
         m["inflection_points"] = _sign_changes(_windowed_slopes(coarse, max(span // 5, 1)), curv_floor) if len(coarse) >= 5 else []
-        roll_w = _rolling_stats(series, max(span // 20, 1))
+        # 500-step stretches as in the reference once the run has at least ten of them, a twentieth of the run before
+        roll_w = _rolling_stats(series, 500 if span >= 5000 else max(span // 20, 1))
         if roll_w:
             m["rolling_stats"] = roll_w
-            q = len(roll_w) // 4
-            early, late = [r["std"] for r in roll_w[:max(q, 1)] if r["std"] > 0], [r["std"] for r in roll_w[-max(q, 1):] if r["std"] > 0]
+            n = len(roll_w)
+            early = [r["std"] for r in roll_w[:max(n // 4, 1)] if r["std"] > 0]
+            late = [r["std"] for r in roll_w[min(3 * n // 4, n - 1):] if r["std"] > 0]
             if early and late:
                 m["stability_score"] = (sum(late) / len(late)) / max(sum(early) / len(early), 1e-10)
         m["plateaus"] = _plateaus(series)
@@ -258,8 +280,8 @@ def geometric_health(data: StepData) -> dict[str, Any]:
     flags = []
     rk = extract_series(data, "geo/rankme_last")
     if len(rk) >= 8:
-        q = len(rk) // 4
-        out["rankme_stability"] = _std([v for _, v in rk[-q:]]) / max(_std([v for _, v in rk[:q]]), 1e-10)
+        n = len(rk)                                  # first quarter against last quarter, cut as the reference cuts them
+        out["rankme_stability"] = _std([v for _, v in rk[3 * n // 4:]]) / max(_std([v for _, v in rk[:n // 4]]), 1e-10)
     if rk and rk[-1][1] < 0.5 * max(v for _, v in rk):
         flags.append("rankme_collapse")
     for layer, rec in out["layers"].items():
@@ -300,8 +322,14 @@ def compare_runs(runs: dict[str, StepData], metric: str = "train/loss", at_steps
                 row[k] = {"delta": d, "relative": d / abs(a) if a else None,
                           "verdict": "same" if d == 0 else ("better" if better else "worse")}
         deltas[n] = row
+    best_per_metric = {}
+    for k in COMPARISON_KEYS:                       # which run wins each endpoint figure, by the figure's direction
+        have = {n: sm[k] for n, sm in summaries.items() if isinstance(sm.get(k), (int, float))}
+        if have:
+            best_per_metric[k] = (min if k in LOWER_IS_BETTER else max)(have, key=have.get)
     return {"summaries": summaries, "metric": metric, "steps": steps, "table": table, "ranking": ranking,
-            "best": ranking[0] if ranking else None, "baseline": names[0] if names else None, "deltas": deltas}
+            "best": ranking[0] if ranking else None, "best_per_metric": best_per_metric,
+            "baseline": names[0] if names else None, "deltas": deltas}
 
 
 def _factorial_cell(y: dict[tuple[int, int], float]) -> dict[str, Any]:
@@ -312,17 +340,21 @@ def _factorial_cell(y: dict[tuple[int, int], float]) -> dict[str, Any]:
     scale = max(abs(y[(1, 0)] - y[(0, 0)]), abs(y[(0, 1)] - y[(0, 0)]), 1e-12)
     rel = inter / scale
     kind = "additive" if abs(rel) < 0.1 else ("reinforcing" if (inter < 0) == (a + b < 0) else "offsetting")
+    # the reference's label: by the sign of the interaction, additive below 5 % of the summed main effects
+    sign = "additive" if abs(inter) < 0.05 * abs(a + b) else ("super-additive" if inter > 0 else "sub-additive")
     return {"values": {f"{k[0]}{k[1]}": v for k, v in y.items()}, "main_effect_a": a, "main_effect_b": b, "interaction": inter,
-            "additive_prediction": additive, "relative_interaction": rel, "classification": kind}
+            "additive_prediction": additive, "relative_interaction": rel, "classification": kind, "additivity": sign}
 
 
 def factorial_analysis(runs: dict[tuple[int, int], StepData], metric: str = "train/loss", step: Optional[int] = None,
-                       extra_metrics: Optional[list[str]] = None) -> dict[str, Any]:
+                       extra_metrics: Optional[list[str]] = None, all_metrics: bool = False) -> dict[str, Any]:
     """2x2 design ``{(a, b): run}`` with a, b in {0, 1}: main effects and the interaction
     ``(y11 - y10) - (y01 - y00)`` of ``metric`` at ``step`` (default: last common step), what a purely
     additive model predicts for the cell with both factors, the interaction relative to the larger
     single-factor effect and its classification (additive below 10 %; reinforcing when it pushes the same
-    way as the main effects, offsetting otherwise).  ``extra_metrics``: the same for further metrics."""
+    way as the main effects, offsetting otherwise; ``additivity`` is the reference's sign-based label).
+    ``extra_metrics``: the same for further metrics; ``all_metrics``: for every numeric metric that all four runs
+    logged at that step, as the reference's ``factorial_analysis`` reports."""
     need = [(0, 0), (0, 1), (1, 0), (1, 1)]
     if any(k not in runs for k in need):
         raise ValueError("factorial_analysis needs runs for (0,0), (0,1), (1,0), (1,1)")
@@ -333,7 +365,15 @@ def factorial_analysis(runs: dict[tuple[int, int], StepData], metric: str = "tra
         return {"step": step, "values": y, "error": "metric missing for some cell"}
     out = {"step": step, "metric": metric, **_factorial_cell(y)}
     others = {}
-    for key in extra_metrics or []:
+    keys = list(extra_metrics or [])
+    if all_metrics:
+        found: set[str] = set()
+        for k in need:
+            near = min(runs[k], key=lambda st: abs(st - step)) if runs[k] else None
+            if near is not None:
+                found.update(name for name, v in runs[k][near].items() if isinstance(v, (int, float)) and not isinstance(v, bool))
+        keys += sorted(found - set(keys) - {metric})
+    for key in keys:
         ys = {k: _at(runs[k], step, key, tolerance=tol) for k in need}
         if all(v is not None for v in ys.values()):
             others[key] = _factorial_cell(ys)
@@ -342,9 +382,32 @@ def factorial_analysis(runs: dict[tuple[int, int], StepData], metric: str = "tra
     return out
 
 
-def reference_comparison(run: StepData, reference: StepData, metrics: Optional[list[str]] = None) -> dict[str, Any]:
+def summary_comparison(run: StepData, reference: dict[str, Any], threshold_pct: float = 10.0) -> dict[str, Any]:
+    """The run's endpoint summary against a reference *summary* (the output of `endpoint_summary` for another run, or
+    hand-written target values): per shared numeric figure the delta and the change in per cent, and the figures that
+    moved by more than ``threshold_pct`` (the reference's ``reference_comparison``, ``src/eval/run_analysis.py:722-777``)."""
+    current = endpoint_summary(run)
+    comparisons: dict[str, dict[str, Any]] = {}
+    flagged: list[dict[str, Any]] = []
+    for key, ref_val in reference.items():
+        cur = current.get(key)
+        if isinstance(ref_val, bool) or not isinstance(ref_val, (int, float)) or cur is None:
+            continue
+        delta = cur - ref_val
+        pct = delta / abs(ref_val) * 100 if abs(ref_val) > 1e-10 else 0.0
+        comparisons[key] = {"reference": ref_val, "current": cur, "delta": delta, "pct_change": round(pct, 2)}
+        if abs(pct) > threshold_pct:
+            flagged.append({"metric": key, **comparisons[key]})
+    return {"comparisons": comparisons, "flagged": flagged, "threshold_pct": threshold_pct}
+
+
+def reference_comparison(run: StepData, reference: Any, metrics: Optional[list[str]] = None,
+                         threshold_pct: float = 10.0) -> dict[str, Any]:
     """Differences run - reference at matched steps for the given metrics, plus the step at which the
-    run first reaches the reference's final loss."""
+    run first reaches the reference's final loss.  When ``reference`` is a summary (figure name -> value) instead of
+    step-indexed metrics, the endpoint summaries are compared (`summary_comparison`)."""
+    if reference and all(isinstance(k, str) for k in reference):
+        return summary_comparison(run, reference, threshold_pct)
     metrics = metrics or ["train/loss", "geo/rankme_last"]
     common = min(max(run) if run else 0, max(reference) if reference else 0)
     out: dict[str, Any] = {"common_step": common, "metrics": {}}

@@ -821,3 +821,111 @@ def test_trace_summary_matches_the_reference_trace_tool(tmp_path):
     their_host = [l.split() for l in theirs.split("\n" + "-" * 110 + "\n")[1].strip().splitlines()]
     assert [r[0] for r in their_host] == [r[0] for r in host] and host[0][0] == "FORWARD"
     assert all(int(t[2]) == h[2] for t, h in zip(their_host, host))
+
+
+def test_training_dynamics_figures_match_the_reference_engine(ref):
+    """The shared definitions of the run-analysis engine on one noisy 20 000-step run with two planted jumps: slopes in
+    centred windows at the landmark steps (all four window sizes), 500-step rolling mean / spread / count, the stability
+    score, and the jump detector (step, size, sigma) against ``src/eval/run_analysis.py``."""
+    import numpy as np
+    theirs = importlib.import_module("src.eval.run_analysis")
+    from kotodama_b200.eval import run_analysis as ours
+    rng = np.random.default_rng(3)
+    data = {}
+    for s in range(0, 20001, 10):
+        loss = 2.5 + 4.0 * np.exp(-s / 3000.0) + rng.normal(0, 0.02 * (1.0 + 3.0 * np.exp(-s / 2000.0)))
+        loss += 0.6 if s == 7000 else 0.0
+        loss -= 0.5 if s >= 15000 else 0.0
+        data[s] = {"train/loss": float(loss), "geo/rankme_last": float(40 + 0.001 * s + rng.normal(0, 0.3))}
+    a = theirs.training_dynamics(data, ["train/loss", "geo/rankme_last"])["metrics"]
+    b = ours.training_dynamics(data, ["train/loss", "geo/rankme_last"])
+    for key in ("train/loss", "geo/rankme_last"):
+        for pct in (10, 25, 50, 75, 90):
+            for w in (100, 500, 1000, 5000):
+                x, y = a[key]["slopes_at_landmarks"][f"pct_{pct}"][f"w{w}"], b[key]["slopes_at_landmarks"][f"{pct}%"][f"w{w}"]
+                assert (x is None) == (y is None) and (x is None or abs(x - y) <= 1e-9 * max(abs(x), 1e-6)), (key, pct, w, x, y)
+        ra, rb = a[key]["rolling_stats"], b[key]["rolling_stats"]
+        assert len(ra) == len(rb) == 40
+        for x, y in zip(ra, rb):
+            assert x["step_center"] == y["step_center"] and x["n"] == y["n"]
+            assert abs(x["mean"] - y["mean"]) < 1e-12 and abs(x["std"] - y["std"]) < 1e-12
+        assert abs(a[key]["stability_score"] - b[key]["stability_score"]) < 1e-9
+        ja, jb = a[key]["jumps"], b[key]["jumps"]
+        assert [j["step"] for j in ja] == [j["step"] for j in jb]
+        assert all(abs(x["delta"] - y["delta"]) < 1e-12 and abs(x["sigma"] - y["sigma"]) <= 0.011 for x, y in zip(ja, jb))
+    steps = [j["step"] for j in b["train/loss"]["jumps"]]
+    assert 7000 in steps and 7010 in steps and 15000 in steps
+
+
+def test_run_comparison_and_factorial_effects_match_the_reference_engine(ref):
+    """Deltas against the first run and the per-figure winners of ``compare_runs``, and main effects, interaction and
+    the sign-based label of the 2 x 2 factorial for every logged metric, against ``src/eval/run_analysis.py``."""
+    import numpy as np
+    theirs = importlib.import_module("src.eval.run_analysis")
+    from kotodama_b200.eval import run_analysis as ours
+    rng = np.random.default_rng(5)
+
+    def run(gain: float, rank_gain: float) -> dict:
+        d = {}
+        for s in range(0, 6001, 50):
+            d[s] = {"train/loss": float(2.5 - gain + 3.0 * np.exp(-s / 1500.0) + rng.normal(0, 0.003)),
+                    "train/perplexity": float(np.exp(2.5 - gain)), "perf/tokens_per_sec": float(40000 + 1000 * gain),
+                    "train/tokens_consumed": float(s * 2 ** 21)}
+            if s % 500 == 0:
+                d[s].update({"geo/rankme_last": float(60 + rank_gain + 0.002 * s), "geo/twonn_id": float(20 + rank_gain),
+                             "geo/ww_alpha_mean": float(3.0 - gain)})
+        return d
+    runs = {"P3": run(0.0, 0.0), "NCA": run(0.10, 4.0), "P3-AR": run(0.05, -2.0), "NCA-AR": run(0.21, 2.5)}
+    a, b = theirs.compare_runs(runs), ours.compare_runs(runs)
+    assert a["baseline"] == b["baseline"] == "P3"
+    for name, row in a["deltas"].items():
+        for key, d in row.items():
+            if d is None:
+                assert key not in b["deltas"][name]
+            else:
+                assert abs(b["deltas"][name][key]["delta"] - d) < 1e-12, (name, key)
+    assert a["best"] == b["best_per_metric"] and b["best"] == "NCA-AR"
+    fa = theirs.factorial_analysis(runs, {"NCA": ("P3", "NCA"), "AttnRes": ("P3", "P3-AR")}, step=6000)
+    fb = ours.factorial_analysis({(0, 0): runs["P3"], (1, 0): runs["NCA"], (0, 1): runs["P3-AR"], (1, 1): runs["NCA-AR"]},
+                                 step=6000, all_metrics=True)
+    mine = {"train/loss": fb, **fb["other_metrics"]}
+    assert set(fa["effects"]) == set(mine)
+    for key, e in fa["effects"].items():
+        m = mine[key]
+        assert abs(e["NCA_main"] - m["main_effect_a"]) < 1e-9 and abs(e["AttnRes_main"] - m["main_effect_b"]) < 1e-9, key
+        assert abs(e["interaction"] - m["interaction"]) < 1e-9 and e["classification"] == m["additivity"], key
+    assert fb["additivity"] == "sub-additive" and fb["classification"] == "reinforcing"       # both together gain more than the sum
+
+
+def test_geometric_health_and_summary_comparison_match_the_reference_engine(ref):
+    """Layer discovery, landmark steps snapped to steps that have geometric records, the per-layer profile at every
+    landmark, the depth gradient at the last one and the RankMe stability figure; and the endpoint summary against a
+    reference summary with the figures that moved by more than the threshold - against ``src/eval/run_analysis.py``."""
+    import numpy as np
+    theirs = importlib.import_module("src.eval.run_analysis")
+    from kotodama_b200.eval import run_analysis as ours
+    rng = np.random.default_rng(9)
+    data = {}
+    for s in range(0, 12001, 100):
+        data[s] = {"train/loss": float(3.0 + 2.0 * np.exp(-s / 3000.0)), "train/perplexity": float(np.exp(3.0)),
+                   "perf/tokens_per_sec": 38000.0, "train/tokens_consumed": float(s) * 2 ** 21}
+        if s % 700 == 0:                                   # geometric records on a grid that misses the landmark steps
+            data[s]["geo/rankme_last"] = float(80 - 30 * np.exp(-s / 2000.0) + rng.normal(0, 0.5 + 2.0 * np.exp(-s / 1500.0)))
+            for layer in (0, 7, 14, 21, 27):
+                for proj in ("q_proj", "k_proj", "o_proj", "gate_proj", "down_proj"):
+                    data[s][f"geo/layer_{layer}/stable_rank_{proj}"] = float(10 + layer + rng.normal(0, 0.1))
+                data[s][f"geo/layer_{layer}/attn_entropy_mean"] = float(3.0 - 0.02 * layer + rng.normal(0, 0.01))
+                data[s][f"geo/layer_{layer}/attn_entropy_std"] = float(0.3 + rng.normal(0, 0.01))
+                data[s][f"geo/layer_{layer}/anisotropy"] = float(0.1 + 0.01 * layer)
+                data[s][f"geo/layer_{layer}/dead_units"] = 0.0
+    a, b = theirs.geometric_health(data), ours.geometric_health(data)
+    assert a["layers"] == sorted(b["layers"]) == [0, 7, 14, 21, 27] and a["landmarks"] == b["landmarks"]
+    for lm, prof in a["profiles"].items():
+        assert prof["step"] == b["profiles"][lm]["step"]
+        for layer in a["layers"]:
+            assert prof[f"layer_{layer}"] == b["profiles"][lm][f"layer_{layer}"], (lm, layer)
+    assert a["depth_gradient"] == b["depth_gradient"] and abs(a["rankme_stability"] - b["rankme_stability"]) < 1e-12
+    other = {s: {**v, "train/loss": v["train/loss"] * 1.2} for s, v in data.items()}
+    target = theirs.endpoint_summary(other)
+    ca, cb = theirs.reference_comparison(data, target, threshold_pct=5.0), ours.reference_comparison(data, target, threshold_pct=5.0)
+    assert ca == cb and {f["metric"] for f in cb["flagged"]} >= {"loss_final", "loss_min"}
