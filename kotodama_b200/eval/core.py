@@ -40,6 +40,17 @@ class CheckpointInfo:
     attn_res_boundaries: Optional[list[int]] = None
     description: str = ""
     extra: dict[str, Any] = field(default_factory=dict)
+    attn_res_n_blocks: Optional[int] = None
+    group: Optional[str] = None
+    tags: list[str] = field(default_factory=list)
+
+    @property
+    def attn_res_config(self) -> Optional[dict[str, Any]]:
+        """The entry's explicit AttnRes settings (what `load_model` takes as ``attn_res_config``), or None when the
+        entry names none and the loader should look at the checkpoint's keys."""
+        given = {k: v for k, v in (("attn_res", self.attn_res or None), ("attn_res_n_blocks", self.attn_res_n_blocks),
+                                   ("attn_res_boundaries", self.attn_res_boundaries)) if v is not None}
+        return given or None
 
 
 def load_model_config(config_path: Optional[str | Path] = None, section: str = "proxy", **overrides: Any) -> ModelConfig:
@@ -60,18 +71,32 @@ def load_model_config(config_path: Optional[str | Path] = None, section: str = "
 
 
 def load_checkpoint_registry(path: str | Path) -> dict[str, CheckpointInfo]:
-    """``checkpoints.yaml``: ``{name: {path, model_section, attn_res, attn_res_boundaries, description}}``."""
+    """Named checkpoints from a YAML file, in either of two layouts:
+
+    * flat: ``checkpoints: {name: {path, model_section, attn_res, attn_res_n_blocks, attn_res_boundaries, description}}``;
+    * grouped, the reference's (``src/eval/model_loader.py:68-106``): ``{group: {checkpoints: {name: {path, tags,
+      attn_res, attn_res_n_blocks, attn_res_boundaries}}}}`` - the group name and the tags are kept on the entry.
+    """
     import yaml
-    raw = yaml.safe_load(open(path)) or {}
-    raw = raw.get("checkpoints", raw)
-    out = {}
-    known = {"path", "model_section", "attn_res", "attn_res_boundaries", "description"}
-    for name, e in raw.items():
+    with open(path) as fh:
+        raw = yaml.safe_load(fh) or {}
+    known = {"path", "model_section", "attn_res", "attn_res_n_blocks", "attn_res_boundaries", "description", "tags"}
+    out: dict[str, CheckpointInfo] = {}
+
+    def add(name: str, e: dict[str, Any], group: Optional[str]) -> None:
         out[name] = CheckpointInfo(name=name, path=e["path"], model_section=e.get("model_section", "proxy"),
-                                   attn_res=bool(e.get("attn_res", False)),
-                                   attn_res_boundaries=e.get("attn_res_boundaries"),
-                                   description=e.get("description", ""),
+                                   attn_res=bool(e.get("attn_res", False)), attn_res_boundaries=e.get("attn_res_boundaries"),
+                                   attn_res_n_blocks=e.get("attn_res_n_blocks"), description=e.get("description", ""),
+                                   group=group, tags=list(e.get("tags", [])),
                                    extra={k: v for k, v in e.items() if k not in known})
+    grouped = [g for g, v in raw.items() if g != "checkpoints" and isinstance(v, dict) and isinstance(v.get("checkpoints"), dict)]
+    for g in grouped:
+        for name, e in raw[g]["checkpoints"].items():
+            add(name, e, g)
+    flat = raw.get("checkpoints") if isinstance(raw.get("checkpoints"), dict) else (None if grouped else raw)
+    for name, e in (flat or {}).items():
+        if isinstance(e, dict) and "path" in e:
+            add(name, e, None)
     return out
 
 
@@ -81,13 +106,22 @@ def detect_attn_res(state_dict: dict[str, torch.Tensor]) -> bool:
 
 def load_model(checkpoint: str | Path, config: Optional[ModelConfig] = None, device: str = "cpu",
                dtype: Optional[torch.dtype] = None, section: str = "proxy", config_path: Optional[str] = None,
-               attn_res_boundaries: Optional[list[int]] = None) -> tuple[KotodamaModel, dict[str, Any]]:
-    """Load a checkpoint (``.pt`` / ``.pt.zst``) into a model; AttnRes is auto-detected from the keys.
-    Wrapper prefixes (``_orig_mod.``, ``module.``) are stripped, loading is non-strict."""
+               attn_res_boundaries: Optional[list[int]] = None,
+               attn_res_config: Optional[dict[str, Any]] = None) -> tuple[KotodamaModel, dict[str, Any]]:
+    """Load a checkpoint (``.pt`` / ``.pt.zst``) into a model.  AttnRes comes from ``attn_res_config`` when given
+    (``attn_res``, ``attn_res_n_blocks``, ``attn_res_boundaries``; naming blocks or boundaries implies ``attn_res``),
+    else it is detected from the checkpoint's keys with seven uniform blocks - the reference's order of precedence
+    (``src/eval/model_loader.py:109-175``).  Wrapper prefixes (``_orig_mod.``, ``module.``) are stripped, loading is
+    non-strict."""
     ckpt = load_checkpoint_file(Path(checkpoint), map_location="cpu")
     sd = clean_state_dict(ckpt.get("model", ckpt))
     if config is None:
-        config = load_model_config(config_path, section, attn_res=detect_attn_res(sd))
+        if attn_res_config:
+            explicit = dict(attn_res_config)
+            explicit.setdefault("attn_res", True)
+            config = load_model_config(config_path, section, **explicit)
+        else:
+            config = load_model_config(config_path, section, attn_res=detect_attn_res(sd))
         if attn_res_boundaries is not None:
             config.attn_res_boundaries = list(attn_res_boundaries)
         emb = sd.get("embed_tokens.weight")
@@ -200,14 +234,20 @@ def _top_p_filter(logits: torch.Tensor, top_p: float) -> torch.Tensor:
 
 @torch.no_grad()
 def generate(model: KotodamaModel, input_ids: torch.Tensor, max_new_tokens: int = 64, temperature: float = 0.8,
-             top_k: int = 50, top_p: float = 0.0, repetition_penalty: float = 1.0, eos_token_id: Optional[int] = None,
-             use_cache: bool = True) -> torch.Tensor:
-    """Batch-1 autoregressive generation with the model's own KV cache; returns prompt + new tokens."""
+             top_k: int = 50, top_p: Optional[float] = 0.0, repetition_penalty: float = 1.0, eos_token_id: Optional[int] = None,
+             use_cache: bool = True, eos_tokens: Optional[list[int]] = None, max_seq_len: Optional[int] = None) -> torch.Tensor:
+    """Batch-1 autoregressive generation with the model's own KV cache; returns prompt + new tokens.  Sampling order:
+    repetition penalty, temperature, top-k, top-p, multinomial (``temperature <= 0``: greedy).  Generation ends at
+    ``eos_token_id`` or any of ``eos_tokens``, after ``max_new_tokens``, or at ``max_seq_len`` / the model's context.
+    With ``top_k=0`` and no repetition penalty this is the reference's ``generate`` (``src/eval/generate.py:24-101``)."""
     ids = input_ids.clone()
     past = None
     cur = ids
+    stop = set(eos_tokens or []) | ({eos_token_id} if eos_token_id is not None else set())
+    limit = min(max_seq_len or model.config.max_position_embeddings, model.config.max_position_embeddings)
+    top_p = top_p or 0.0
     for _ in range(max_new_tokens):
-        if ids.shape[1] >= model.config.max_position_embeddings:
+        if ids.shape[1] >= limit:
             break
         out = model(cur if use_cache else ids, use_cache=use_cache, past_kv=past)
         past = out.get("past_kv") if use_cache else None
@@ -228,7 +268,7 @@ def generate(model: KotodamaModel, input_ids: torch.Tensor, max_new_tokens: int 
             nxt = torch.multinomial(torch.softmax(lg, -1), 1)
         ids = torch.cat([ids, nxt], 1)
         cur = nxt
-        if eos_token_id is not None and int(nxt) == eos_token_id:
+        if int(nxt) in stop:
             break
     return ids
 
@@ -245,9 +285,11 @@ def generate_text(model: KotodamaModel, tokenizer: Any, prompt: str, details: bo
     text = tokenizer.decode(new, skip_special_tokens=True)
     if not details:
         return text
-    if new and eos is not None and new[-1] == eos:
+    stop = set(kw.get("eos_tokens") or []) | ({eos} if eos is not None else set())
+    ctx = model.config.max_position_embeddings
+    if new and new[-1] in stop:
         why = "eos"
-    elif out.shape[1] >= model.config.max_position_embeddings:
+    elif out.shape[1] >= min(kw.get("max_seq_len") or ctx, ctx):
         why = "context"
     else:
         why = "max_tokens"

@@ -929,3 +929,58 @@ def test_geometric_health_and_summary_comparison_match_the_reference_engine(ref)
     target = theirs.endpoint_summary(other)
     ca, cb = theirs.reference_comparison(data, target, threshold_pct=5.0), ours.reference_comparison(data, target, threshold_pct=5.0)
     assert ca == cb and {f["metric"] for f in cb["flagged"]} >= {"loss_final", "loss_min"}
+
+
+def test_checkpoint_registry_loader_and_generation_match_the_reference_eval_modules(ref, tmp_path):
+    """``src/eval/model_loader.py`` and ``src/eval/generate.py`` against this package's evaluation helpers: the
+    reference's own grouped ``configs/checkpoints.yaml`` gives the same entries (paths, groups, tags, AttnRes settings),
+    its ``configs/model.yaml`` the same shapes, one checkpoint (with wrapper prefixes, AttnRes with explicit
+    boundaries) loads into the same weights and logits through both loaders - explicitly configured and auto-detected -
+    and seeded sampling (temperature, nucleus, end-of-sequence set, length limit) draws the same tokens."""
+    import yaml
+    loader = importlib.import_module("src.eval.model_loader")
+    gen = importlib.import_module("src.eval.generate")
+    from kotodama_b200 import eval as ours
+    refdir = os.environ.get("KOTODAMA_REFERENCE", os.path.join(os.path.dirname(ROOT), "reference"))
+    reg_file = os.path.join(refdir, "configs", "checkpoints.yaml")
+    if not os.path.isfile(reg_file):
+        pytest.skip("the reference's configs are not on this machine")
+    a, b = loader.load_checkpoint_registry(reg_file), ours.load_checkpoint_registry(reg_file)
+    assert list(a) == list(b) and len(a) >= 5
+    for name, e in a.items():
+        assert str(e.path) == b[name].path and e.group == b[name].group and e.tags == b[name].tags
+        assert e.attn_res_config == b[name].attn_res_config, name
+    for section in ("proxy", "intermediate", "model"):
+        theirs_kw = loader.load_model_config(os.path.join(refdir, "configs", "model.yaml"), section)
+        mine = ours.load_model_config(os.path.join(refdir, "configs", "model.yaml"), section)
+        assert all(getattr(mine, k) == v for k, v in theirs_kw.items() if hasattr(mine, k)), section
+    # one small model under both loaders
+    shape = dict(hidden_size=64, num_layers=6, num_attention_heads=4, num_kv_heads=2, head_dim=16, intermediate_size=128,
+                 vocab_size=211, max_position_embeddings=128)
+    model_yaml = tmp_path / "model.yaml"
+    model_yaml.write_text(yaml.safe_dump({"proxy": {**shape, "attn_impl": "sdpa"}}))       # no flash-attention library on the CPU
+    torch.manual_seed(0)
+    src_model = ref.llama.LuxiaBaseModel(ref.llama.LuxiaModelConfig(**shape, attn_impl="sdpa", attn_res=True,
+                                                                    attn_res_boundaries=[0, 2, 5]))
+    with torch.no_grad():
+        for n, p_ in src_model.named_parameters():
+            if "res_query" in n:
+                p_.normal_(0, 0.3)
+    ck = tmp_path / "step_00000010.pt"
+    torch.save({"step": 10, "model": {"_orig_mod.module." + k: v for k, v in src_model.state_dict().items()}}, ck)
+    explicit = {"attn_res": True, "attn_res_boundaries": [0, 2, 5]}
+    ids = torch.randint(0, 211, (1, 12), generator=torch.Generator().manual_seed(1))
+    for cfg_kw in (explicit, None):
+        m_a = loader.load_model(ck, config_path=model_yaml, config_section="proxy", attn_res_config=cfg_kw, device="cpu")
+        m_b, meta = ours.load_model(ck, config_path=str(model_yaml), section="proxy", attn_res_config=cfg_kw, device="cpu")
+        assert meta["step"] == 10 and m_b.config.attn_res and sorted(m_b.config.boundaries()) == sorted(m_a._attn_res_boundary_set)
+        sd_a, sd_b = m_a.state_dict(), m_b.state_dict()
+        assert list(sd_a) == list(sd_b) and all(torch.equal(sd_a[k], sd_b[k]) for k in sd_a)
+        with torch.no_grad():
+            assert torch.allclose(m_a(ids)["logits"], m_b(ids)["logits"], atol=1e-5)
+    for kw in (dict(temperature=0.9, top_p=None), dict(temperature=0.7, top_p=0.8), dict(temperature=1.3, top_p=0.95)):
+        torch.manual_seed(7)
+        out_a = gen.generate(m_a, ids, max_new_tokens=24, eos_tokens=[3, 5], max_seq_len=30, **kw)
+        torch.manual_seed(7)
+        out_b = ours.generate(m_b, ids, max_new_tokens=24, top_k=0, eos_tokens=[3, 5], max_seq_len=30, **kw)
+        assert out_a.tolist() == out_b.tolist() and (out_a.shape[1] == 30 or int(out_a[0, -1]) in (3, 5)), kw

@@ -39,8 +39,7 @@ def select_checkpoints(args) -> list[tuple[str, dict[str, Any]]]:
         if n not in reg:
             raise SystemExit(f"unknown checkpoint '{n}'; registry has {sorted(reg)}")
         info = reg[n]
-        out.append((n, dict(checkpoint=info.path, section=info.model_section,
-                            attn_res_boundaries=info.attn_res_boundaries)))
+        out.append((n, dict(checkpoint=info.path, section=info.model_section, attn_res_config=info.attn_res_config)))
     return out
 
 
