@@ -148,7 +148,11 @@ class EngineWorker:
         self._thread.join(timeout=5)
 
 
-def create_app(engine: ServingEngine, tokenizer: Any = None, model_name: str = "kotodama") -> Any:
+def create_app(engine: ServingEngine, tokenizer: Any = None, model_name: str = "kotodama", checkpoint: str = "",
+               trim_stop_strings: bool = False) -> Any:
+    """The HTTP application.  A stop string ends a request as in the reference server (``serve.py:375-378,455-457``): the
+    text keeps everything up to and including the token that completed the stop string, and the first generated token
+    is not checked; ``trim_stop_strings=True`` cuts the text in front of the stop string instead (OpenAI semantics)."""
     from fastapi import FastAPI, HTTPException
     from fastapi.responses import StreamingResponse
 
@@ -191,13 +195,16 @@ def create_app(engine: ServingEngine, tokenizer: Any = None, model_name: str = "
                 ids.append(val)
                 new_text = tok.decode(ids, skip_special_tokens=True)
                 delta, text = new_text[len(text):], new_text
-                hit = next((s for s in stop_strings if s and s in text), None)
-                if hit is not None:
+                hit = next((s for s in stop_strings if s and s in text), None) if len(ids) > 1 or trim_stop_strings else None
+                if hit is not None and trim_stop_strings:
                     cut = text.index(hit)
                     yield "token", delta[: max(0, len(delta) - (len(text) - cut))], text[:cut]
                     yield "done", "stop", text[:cut]
                     return
                 yield "token", delta, text
+                if hit is not None:
+                    yield "done", "stop", text
+                    return
         finally:
             if not finished:
                 worker.cancel(ticket)
@@ -209,7 +216,10 @@ def create_app(engine: ServingEngine, tokenizer: Any = None, model_name: str = "
     @app.get("/info")
     def info() -> dict[str, Any]:
         c = engine.cfg
-        return {"model": model_name, "hidden_size": c.hidden_size, "num_layers": c.num_layers,
+        # the reference's fields (``serve.py:255-262,494-505``: name, params, config, device, checkpoint, fast_attnres),
+        # then what this engine adds
+        return {"name": model_name, "params": c.param_count(), "config": c.to_dict(), "checkpoint": checkpoint,
+                "model": model_name, "hidden_size": c.hidden_size, "num_layers": c.num_layers,
                 "vocab_size": c.vocab_size, "max_position_embeddings": c.max_position_embeddings,
                 "attn_res": c.attn_res, "fast_attnres": True, "device": str(engine.device),
                 "dtype": str(engine.dtype).replace("torch.", ""), "kv_cache": "paged-16",
@@ -280,7 +290,7 @@ def create_app(engine: ServingEngine, tokenizer: Any = None, model_name: str = "
         results = [await loop.run_in_executor(None, run, q) for q in queues]
         total = sum(r[1] for r in results)
         return {"id": f"cmpl-{int(time.time() * 1000)}", "object": "text_completion", "created": int(time.time()),
-                "model": req.model,
+                "model": model_name,
                 "choices": [{"text": t, "index": i, "logprobs": None, "finish_reason": fr}
                             for i, (t, _, fr) in enumerate(results)],
                 "usage": {"prompt_tokens": len(ids), "completion_tokens": total, "total_tokens": len(ids) + total}}

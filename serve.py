@@ -102,7 +102,7 @@ def main() -> None:
     logger.info("Device %s, tokenizer %s, paged KV cache with %d pages", device, type(tok).__name__,
                 engine.cache.num_pages)
     import uvicorn
-    uvicorn.run(create_app(engine, tok, model_name=f"kotodama-{args.model_size}"), host=args.host, port=args.port)
+    uvicorn.run(create_app(engine, tok, model_name=f"kotodama-{args.model_size}", checkpoint=args.checkpoint or ""), host=args.host, port=args.port)
 
 
 if __name__ == "__main__":

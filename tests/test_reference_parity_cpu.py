@@ -984,3 +984,76 @@ def test_checkpoint_registry_loader_and_generation_match_the_reference_eval_modu
         torch.manual_seed(7)
         out_b = ours.generate(m_b, ids, max_new_tokens=24, top_k=0, eos_tokens=[3, 5], max_seq_len=30, **kw)
         assert out_a.tolist() == out_b.tolist() and (out_a.shape[1] == 30 or int(out_a[0, -1]) in (3, 5)), kw
+
+
+def test_http_routes_answer_like_the_reference_server(ref):
+    """The same requests to the reference's FastAPI app (its globals pointed at a small model) and to this package's
+    app (paged engine) on the same weights: ``/health``, ``/v1/models``, ``/info``, ``/generate`` (plain, with a stop
+    string, streamed), ``/v1/completions`` (n = 2, stop as a string) and the validation errors - same status codes,
+    same keys, and with greedy decoding the same text, token counts, stream frames and usage figures."""
+    import importlib.util
+    import json
+    fastapi_testclient = pytest.importorskip("fastapi.testclient")
+    serve_py = os.path.join(os.environ.get("KOTODAMA_REFERENCE", os.path.join(os.path.dirname(ROOT), "reference")), "serve.py")
+    if not os.path.isfile(serve_py):
+        pytest.skip("the reference's serve.py is not on this machine")
+    spec = importlib.util.spec_from_file_location("reference_serve_app", serve_py)
+    theirs = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(theirs)
+    from kotodama_b200.serve.app import create_app
+    from kotodama_b200.serve.engine import ServingEngine
+    m_a, m_b = _pair(ref, dtype=torch.float32, boundaries=[0, 1, 3])
+    m_b.load_state_dict(m_a.state_dict())
+    m_a.eval(), m_b.eval()
+
+    class Letters:                                # id -> one letter, so every token is one character of text
+        eos_token_id, bos_token_id, vocab_size, name = 210, 209, 211, "letters"
+
+        def encode(self, text, return_tensors=None):
+            ids = [ord(c) - 97 for c in text]
+            return torch.tensor([ids]) if return_tensors == "pt" else ids
+
+        def decode(self, ids, skip_special_tokens=True):
+            return "".join(chr(97 + int(i) % 26) for i in ids)
+    theirs._model, theirs._tokenizer, theirs._device = m_a, Letters(), torch.device("cpu")
+    ca = fastapi_testclient.TestClient(theirs.app)                      # no context manager: its start-up hook would load a checkpoint
+    eng = ServingEngine(m_b, device="cpu", dtype=torch.float32, max_batch=4, max_ctx=m_b.config.max_position_embeddings)
+    app = create_app(eng, Letters(), model_name="luxia-base-proxy-ddv1")
+    with fastapi_testclient.TestClient(app) as cb:
+        ha, hb = ca.get("/health").json(), cb.get("/health").json()
+        assert ha["status"] == hb["status"] == "ok"
+        ma, mb = ca.get("/v1/models").json(), cb.get("/v1/models").json()
+        assert ma["object"] == mb["object"] and set(ma["data"][0]) <= set(mb["data"][0]) and ma["data"][0]["id"] == mb["data"][0]["id"]
+        ia, ib = ca.get("/info").json(), cb.get("/info").json()
+        assert set(ia) <= set(ib) and ia["params"] == ib["params"] and ia["name"] == ib["name"]
+        assert set(ia["config"]) <= set(ib["config"]) and all(ib["config"][k] == v for k, v in ia["config"].items() if k != "attn_impl")
+        body = {"prompt": "thequickbrownfox", "max_new_tokens": 12, "temperature": 0.0}
+        ga, gb = ca.post("/generate", json=body), cb.post("/generate", json=body)
+        assert ga.status_code == gb.status_code == 200 and set(ga.json()) == set(gb.json())
+        for k in ("text", "prompt_tokens", "completion_tokens"):
+            assert ga.json()[k] == gb.json()[k], k
+        text = ga.json()["text"]
+        stop = {**body, "stop_strings": [text[4:6]], "repetition_penalty": 1.0}
+        sa, sb = ca.post("/generate", json=stop).json(), cb.post("/generate", json=stop).json()
+        assert sa["text"] == sb["text"] and sa["completion_tokens"] == sb["completion_tokens"] < 12
+        pen = {**body, "repetition_penalty": 1.7}
+        assert ca.post("/generate", json=pen).json()["text"] == cb.post("/generate", json=pen).json()["text"]
+
+        def frames(client):
+            with client.stream("POST", "/generate", json={**body, "stream": True}) as r:
+                return [json.loads(l[6:]) for l in r.iter_lines() if l.startswith("data: ")]
+        fa, fb = frames(ca), frames(cb)
+        assert "".join(f["token"] for f in fa[:-1]) == "".join(f["token"] for f in fb[:-1]) == text
+        assert fa[-1] == {k: fb[-1][k] for k in fa[-1]} and fa[-1]["done"] is True
+        oai = {"prompt": "lazydog", "max_tokens": 9, "n": 2, "temperature": 0.0, "frequency_penalty": 0.4, "stop": text[1:2]}
+        oa, ob = ca.post("/v1/completions", json=oai), cb.post("/v1/completions", json=oai)
+        assert oa.status_code == ob.status_code == 200
+        oa, ob = oa.json(), ob.json()
+        assert set(oa) <= set(ob) and oa["object"] == ob["object"] and oa["model"] == ob["model"] and oa["usage"] == ob["usage"]
+        assert [(c["text"], c["index"], c["finish_reason"]) for c in oa["choices"]] == [(c["text"], c["index"], c["finish_reason"]) for c in ob["choices"]]
+        for bad in ({"prompt": "a", "temperature": 3.0}, {"prompt": "a", "max_new_tokens": 0}, {"prompt": "a", "repetition_penalty": 0.5},
+                    {"max_new_tokens": 4}):
+            assert ca.post("/generate", json=bad).status_code == cb.post("/generate", json=bad).status_code == 422, bad
+        long = {"prompt": "a" * (m_b.config.max_position_embeddings + 3)}
+        assert ca.post("/generate", json=long).status_code == cb.post("/generate", json=long).status_code == 400
+    app.state.worker.shutdown()

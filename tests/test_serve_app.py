@@ -75,7 +75,10 @@ def test_stop_as_string_cancels_the_request_in_the_engine(client):
         pytest.skip("model produced no printable character to stop on")
     r = client.post("/v1/completions", json={"prompt": "hi", "max_tokens": 40, "temperature": 0, "stop": stop})
     body = r.json()
-    assert r.status_code == 200 and stop not in body["choices"][0]["text"][1:] and body["choices"][0]["finish_reason"] == "stop"
+    got = body["choices"][0]["text"]
+    # as in the reference server the text runs up to and including the stop string (looked for from the second token on)
+    assert r.status_code == 200 and got.endswith(stop) and len(got) < len(text) and body["choices"][0]["finish_reason"] == "stop"
+    assert stop not in got[1:-len(stop)]
     for _ in range(100):                                      # the cancel travels through the worker's inbox
         st = client.get("/stats").json()
         if st["free_pages"] == st["num_pages"] and st["running"] == 0:
@@ -103,3 +106,20 @@ def test_worker_survives_a_failing_step(client):
     assert calls["n"] == 1 and worker.errors == 1 and not eng.has_work()
     ok = client.post("/generate", json={"prompt": "hello", "max_new_tokens": 3, "temperature": 0})
     assert ok.status_code == 200 and ok.json()["completion_tokens"] >= 1
+
+
+def test_trimmed_stop_strings_are_an_option():
+    """``trim_stop_strings=True``: the text ends in front of the stop string, and the first token is checked too."""
+    torch.manual_seed(0)
+    cfg = ModelConfig(hidden_size=64, num_layers=2, num_attention_heads=2, num_kv_heads=1, head_dim=32,
+                      intermediate_size=96, vocab_size=300, max_position_embeddings=64)
+    eng = ServingEngine(KotodamaModel(cfg), device="cpu", dtype=torch.float32, max_batch=2, max_ctx=64)
+    app = create_app(eng, ByteTokenizer(), model_name="test", trim_stop_strings=True)
+    with TestClient(app) as c:
+        text = c.post("/generate", json={"prompt": "hi", "max_new_tokens": 30, "temperature": 0}).json()["text"]
+        stop = next((ch for ch in text if ch.strip()), None)
+        if stop is None:
+            pytest.skip("model produced no printable character to stop on")
+        got = c.post("/generate", json={"prompt": "hi", "max_new_tokens": 30, "temperature": 0, "stop_strings": [stop]}).json()["text"]
+        assert got == text[: text.index(stop)]
+    app.state.worker.shutdown()
