@@ -219,33 +219,60 @@ def generate_nca_dataset(config: NCAConfig, output_path: str | Path, max_tokens:
     return total
 
 
+def verify_file(path: str | Path, config: Optional[NCAConfig] = None) -> dict[str, Any]:
+    """Size and id range of a written token file (and, with a configuration, whether every id is in its vocabulary)."""
+    arr = np.memmap(path, dtype=np.uint16, mode="r")
+    out: dict[str, Any] = {"tokens": int(len(arr)), "max_id": int(arr.max()) if len(arr) else 0,
+                           "min_id": int(arr.min()) if len(arr) else 0}
+    if config is not None:
+        out["in_vocab"] = bool(out["max_id"] < config.vocab_size)
+        out["whole_timesteps"] = int(len(arr) // config.tokens_per_timestep)
+    return out
+
+
 def main(argv: Optional[list[str]] = None) -> None:
+    """Command line with the reference's flags (``src/nca/generator.py:576-658``); ``--max_tokens`` is kept as a second
+    name of ``--tokens``, and ``--verify`` takes an optional path (without one it checks the file just written)."""
     ap = argparse.ArgumentParser(description="Generate NCA pre-pre-training tokens")
-    ap.add_argument("--output", required=True)
-    ap.add_argument("--max_tokens", type=int, default=300_000_000)
+    ap.add_argument("--output", default=None)
+    ap.add_argument("--tokens", "--max_tokens", dest="tokens", type=int, default=300_000_000)
     ap.add_argument("--num_rules", type=int, default=5000)
     ap.add_argument("--sims_per_rule", type=int, default=8)
     ap.add_argument("--grid_size", type=int, default=32)
     ap.add_argument("--d_state", type=int, default=10)
     ap.add_argument("--n_groups", type=int, default=4)
-    ap.add_argument("--num_steps", type=int, default=128)
+    ap.add_argument("--kernel_size", type=int, default=3, choices=[3, 5])
+    ap.add_argument("--hidden_dim", type=int, default=32)
+    ap.add_argument("--num_hidden_layers", type=int, default=2)
+    ap.add_argument("--identity_bias", type=float, default=1.0)
+    ap.add_argument("--temperature", type=float, default=0.5)
+    ap.add_argument("--gzip_lower", type=float, default=0.4)
+    ap.add_argument("--gzip_upper", type=float, default=0.7)
     ap.add_argument("--no_filter", action="store_true")
     ap.add_argument("--no_mixed", action="store_true")
+    ap.add_argument("--num_steps", type=int, default=128)
+    ap.add_argument("--burn_in", type=int, default=10)
     ap.add_argument("--device", default="cuda" if torch.cuda.is_available() else "cpu")
     ap.add_argument("--seed", type=int, default=42)
-    ap.add_argument("--verify", action="store_true", help="check the written file: size and id range")
+    ap.add_argument("--verify", nargs="?", const="", default=None,
+                    help="check a token file: the given path, or the file just written when no path follows")
     a = ap.parse_args(argv)
     logging.basicConfig(level=logging.INFO, format="%(asctime)s %(message)s")
+    cfg = NCAConfig(grid_size=a.grid_size, d_state=a.d_state, n_groups=a.n_groups, kernel_size=a.kernel_size,
+                    hidden_dim=a.hidden_dim, num_hidden_layers=a.num_hidden_layers, identity_bias=a.identity_bias,
+                    temperature=a.temperature, num_steps=a.num_steps, burn_in=a.burn_in, filter_enabled=not a.no_filter,
+                    gzip_lower=a.gzip_lower, gzip_upper=a.gzip_upper, mixed_complexity=not a.no_mixed)
+    if a.verify:                                    # a path: only check that file
+        logger.info("verify %s: %s", a.verify, verify_file(a.verify, cfg))
+        return
+    if not a.output:
+        ap.error("--output is required unless --verify names a file")
     random.seed(a.seed)
     torch.manual_seed(a.seed)
-    cfg = NCAConfig(grid_size=a.grid_size, d_state=a.d_state, n_groups=a.n_groups, num_steps=a.num_steps,
-                    filter_enabled=not a.no_filter, mixed_complexity=not a.no_mixed)
-    n = generate_nca_dataset(cfg, a.output, a.max_tokens, a.num_rules, a.sims_per_rule, a.device)
-    if a.verify:
-        arr = np.memmap(a.output, dtype=np.uint16, mode="r")
-        ok = len(arr) == n and int(arr.max()) < cfg.vocab_size
-        logger.info("verify: %d tokens, max id %d, vocab %d -> %s", len(arr), int(arr.max()), cfg.vocab_size,
-                    "OK" if ok else "MISMATCH")
+    n = generate_nca_dataset(cfg, a.output, a.tokens, a.num_rules, a.sims_per_rule, a.device)
+    if a.verify is not None:
+        rep = verify_file(a.output, cfg)
+        logger.info("verify: %s -> %s", rep, "OK" if rep["tokens"] == n and rep["in_vocab"] else "MISMATCH")
 
 
 if __name__ == "__main__":

@@ -1057,3 +1057,28 @@ def test_http_routes_answer_like_the_reference_server(ref):
         long = {"prompt": "a" * (m_b.config.max_position_embeddings + 3)}
         assert ca.post("/generate", json=long).status_code == cb.post("/generate", json=long).status_code == 400
     app.state.worker.shutdown()
+
+
+def test_nca_generator_command_line_takes_the_reference_flags(ref, tmp_path):
+    """Every flag of the reference's ``python -m src.nca.generator`` exists here with the same default, and a small
+    generation + ``--verify <path>`` runs through this package's command line."""
+    import re
+    from kotodama_b200.nca import generator as ours
+    src = open(os.path.join(REF, "nca", "generator.py")).read()
+    theirs = {m.group(1): m.group(2) for m in re.finditer(r'add_argument\(\s*"--(\w+)"([^)]*)\)', src)}
+    assert len(theirs) >= 20
+    own = open(ours.__file__).read()
+    mine = {m.group(1): m.group(2) for m in re.finditer(r'add_argument\(\s*"--(\w+)"([^)]*)\)', own)}
+    for flag, rest in theirs.items():
+        assert flag in mine, flag
+        d = re.search(r"default=([^,\s)]+)", rest)
+        if d and flag not in ("device", "verify", "output"):
+            assert re.search(r"default=([^,\s)]+)", mine[flag]).group(1) == d.group(1), flag
+    out = tmp_path / "nca.bin"
+    ours.main(["--output", str(out), "--tokens", "3000", "--num_rules", "2", "--sims_per_rule", "1", "--grid_size", "8", "--d_state", "3",
+               "--n_groups", "1", "--num_steps", "6", "--burn_in", "2", "--kernel_size", "5", "--hidden_dim", "8", "--num_hidden_layers", "1",
+               "--identity_bias", "0.5", "--temperature", "0.8", "--gzip_lower", "0.0", "--gzip_upper", "1.0", "--no_mixed", "--device", "cpu",
+               "--seed", "1", "--verify"])
+    rep = ours.verify_file(out, ours.NCAConfig(grid_size=8, d_state=3, n_groups=1))
+    assert 0 < rep["tokens"] <= 3000 and rep["in_vocab"] and rep["max_id"] < 3 ** 4 + 2
+    ours.main(["--verify", str(out), "--d_state", "3", "--grid_size", "8", "--n_groups", "1"])
