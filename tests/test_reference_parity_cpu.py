@@ -1082,3 +1082,26 @@ def test_nca_generator_command_line_takes_the_reference_flags(ref, tmp_path):
     rep = ours.verify_file(out, ours.NCAConfig(grid_size=8, d_state=3, n_groups=1))
     assert 0 < rep["tokens"] <= 3000 and rep["in_vocab"] and rep["max_id"] < 3 ** 4 + 2
     ours.main(["--verify", str(out), "--d_state", "3", "--grid_size", "8", "--n_groups", "1"])
+
+
+def test_command_line_tools_take_the_reference_scripts_flags():
+    """Every ``--flag`` of the reference's utility, analysis and serving scripts is accepted by its counterpart here
+    (read from the parsers' source; shared checkpoint arguments live in ``tools/analysis/_common.py``)."""
+    import re
+    refdir = os.environ.get("KOTODAMA_REFERENCE", os.path.join(os.path.dirname(ROOT), "reference"))
+    if not os.path.isdir(os.path.join(refdir, "scripts", "analysis")):
+        pytest.skip("the reference's scripts are not on this machine")
+    pairs = {"scripts/utils/" + f: "tools/" + f for f in ("tokenize_data.py", "smoke_test.py", "profile_step.py", "pull_metrics.py",
+                                                          "visualize_nca.py")}
+    pairs["serve.py"] = "serve.py"
+    pairs.update({"scripts/analysis/" + f: "tools/analysis/" + f for f in os.listdir(os.path.join(refdir, "scripts", "analysis"))
+                  if f.endswith(".py")})
+    common = open(os.path.join(ROOT, "tools", "analysis", "_common.py")).read()
+    checked = 0
+    for theirs, mine in pairs.items():
+        flags = set(re.findall(r'add_argument\(\s*(?:"-\w",\s*)?"(--[\w-]+)"', open(os.path.join(refdir, theirs)).read()))
+        own = open(os.path.join(ROOT, mine)).read() + (common if "analysis" in mine else "")
+        missing = sorted(f for f in flags if f'"{f}"' not in own)
+        assert not missing, (mine, missing)
+        checked += len(flags)
+    assert checked >= 100

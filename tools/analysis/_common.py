@@ -22,16 +22,33 @@ def add_checkpoint_args(ap) -> None:
     ap.add_argument("--name", default=None, help="run name for --checkpoint")
     ap.add_argument("--checkpoints", default=None, help="comma-separated names from the registry")
     ap.add_argument("--registry", default=str(ROOT / "configs" / "checkpoints.yaml"))
-    ap.add_argument("--section", default="proxy", help="model section of configs/model.yaml")
+    ap.add_argument("--section", "--config-section", dest="section", default="proxy", help="model section of the model YAML")
+    ap.add_argument("--config", default=None, help="model YAML with named sections (default: the built-in size presets)")
+    ap.add_argument("--attn-res", default=None, help="explicit AttnRes settings for --checkpoint: 'n_blocks=7' or 'boundaries=0,3,7,12'")
     ap.add_argument("--device", default="cpu")
     ap.add_argument("--output-dir", default="analysis")
     ap.add_argument("--tokenizer", default="HuggingFaceTB/SmolLM2-135M")
 
 
+def parse_attn_res(spec: Optional[str]) -> Optional[dict[str, Any]]:
+    """``'n_blocks=7'`` or ``'boundaries=0,3,7,12'`` -> the loader's explicit AttnRes settings."""
+    if not spec:
+        return None
+    key, _, val = spec.partition("=")
+    if key.strip() == "n_blocks":
+        return {"attn_res": True, "attn_res_n_blocks": int(val)}
+    if key.strip() == "boundaries":
+        return {"attn_res": True, "attn_res_boundaries": [int(v) for v in val.split(",") if v.strip()]}
+    raise SystemExit(f"--attn-res: expected 'n_blocks=N' or 'boundaries=a,b,c', got {spec!r}")
+
+
 def select_checkpoints(args) -> list[tuple[str, dict[str, Any]]]:
     """[(run name, load_model kwargs)] from --checkpoint/--name or --checkpoints (registry)."""
+    shared = {"config_path": args.config} if getattr(args, "config", None) else {}
     if args.checkpoint:
-        return [(args.name or Path(args.checkpoint).stem, dict(checkpoint=args.checkpoint, section=args.section))]
+        return [(args.name or Path(args.checkpoint).stem,
+                 dict(checkpoint=args.checkpoint, section=args.section, attn_res_config=parse_attn_res(getattr(args, "attn_res", None)),
+                      **shared))]
     reg = load_checkpoint_registry(args.registry)
     names = [n.strip() for n in args.checkpoints.split(",")] if args.checkpoints else list(reg)
     out = []
@@ -39,7 +56,7 @@ def select_checkpoints(args) -> list[tuple[str, dict[str, Any]]]:
         if n not in reg:
             raise SystemExit(f"unknown checkpoint '{n}'; registry has {sorted(reg)}")
         info = reg[n]
-        out.append((n, dict(checkpoint=info.path, section=info.model_section, attn_res_config=info.attn_res_config)))
+        out.append((n, dict(checkpoint=info.path, section=info.model_section, attn_res_config=info.attn_res_config, **shared)))
     return out
 
 

@@ -40,12 +40,16 @@ def main() -> None:
     ap.add_argument("--max-tokens", type=int, default=256)
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--no-ppl", action="store_true")
-    ap.add_argument("--ppl-data", default="data/heldout.bin")
+    ap.add_argument("--ppl-data", "--eval-data", dest="ppl_data", default="data/heldout.bin")
+    ap.add_argument("--max-seqs", type=int, default=None, help="perplexity over this many sequences (sets --ppl-tokens to max-seqs x seq-len)")
+    ap.add_argument("-o", "--output", default=None, help="also write the last run's generations file to this path")
     ap.add_argument("--ppl-tokens", type=int, default=1_000_000)
     ap.add_argument("--seq-len", type=int, default=2048)
     ap.add_argument("--temperatures", default=None, help="comma-separated: run the whole set at each of these temperatures")
     ap.add_argument("--combined", action="store_true", help="also write one file with all runs side by side")
     a = ap.parse_args()
+    if a.max_seqs:
+        a.ppl_tokens = a.max_seqs * a.seq_len
     prompts = load_yaml(a.prompts_file)[a.prompt_set]
     tok = tokenizer(a.tokenizer)
     temps = [float(t) for t in a.temperatures.split(",")] if a.temperatures else [a.temperature]
@@ -110,6 +114,9 @@ def main() -> None:
         path = run_dir(a.output_dir, "_vs_".join(names[:3])) / "generations.json"
         write_json(path, {"config": done[0]["config"], "runs": done})
         print(f"combined -> {path}")
+    if a.output and done:
+        write_json(Path(a.output), done[-1] if len({d["run"] for d in done}) == 1 else {"config": done[0]["config"], "runs": done})
+        print(f"-> {a.output}")
 
 
 if __name__ == "__main__":

@@ -139,7 +139,7 @@ def extract_set(model: Any, tok: Any, cs: ConceptSet, templates: list[str], devi
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     add_checkpoint_args(ap)
-    ap.add_argument("--concepts-file", default=str(ROOT / "configs" / "concepts.yaml"))
+    ap.add_argument("--concepts-file", "--concepts-config", dest="concepts_file", default=str(ROOT / "configs" / "concepts.yaml"))
     ap.add_argument("--concept-sets", default=None, help="comma-separated names (default: all)")
     ap.add_argument("--tier", type=int, default=None, help="only sets of this tier or lower")
     ap.add_argument("--templates", default=None, help="comma-separated template indices (default: all)")

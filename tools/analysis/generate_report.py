@@ -359,7 +359,7 @@ def build(run: str, rd: Path, theme: str, metrics: Optional[Path] = None) -> str
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("run")
-    ap.add_argument("--output-dir", default="analysis")
+    ap.add_argument("--output-dir", "--analysis-dir", dest="output_dir", default="analysis")
     ap.add_argument("--metrics", default=None, help="metrics.jsonl of the run (default: <output-dir>/<run>/metrics.jsonl if present)")
     ap.add_argument("--theme", default="dark", choices=list(THEMES))
     ap.add_argument("-o", "--output", default=None)

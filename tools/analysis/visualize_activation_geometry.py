@@ -163,16 +163,28 @@ def main() -> None:
     ap.add_argument("--run", default=None)
     ap.add_argument("--runs", default=None, help="comma-separated runs to overlay (comparison plots go to <output-dir>/_pairs)")
     ap.add_argument("--output-dir", default="analysis")
+    ap.add_argument("--input", default=None, help="the directory with one run's extracted files (instead of --run / --output-dir)")
+    ap.add_argument("--only", default=None, help="comma-separated series names (or prefixes) to draw; default: all")
+    ap.add_argument("--style", default="publication", choices=["publication", "dark", "notebook"], help="matplotlib style of the PNG figures")
     a = ap.parse_args()
     runs = [r.strip() for r in a.runs.split(",")] if a.runs else ([a.run] if a.run else [])
-    if not runs:
-        raise SystemExit("give --run or --runs")
-    loaded = {r: load_run(a.output_dir, r) for r in runs}
+    if a.input:
+        d = Path(a.input)
+        runs = [d.parent.name if d.name == "activation_geometry" else d.name]
+        loaded = {runs[0]: (d, json.loads((d / "geometry.json").read_text()))}
+    elif not runs:
+        raise SystemExit("give --run, --runs or --input")
+    else:
+        loaded = {r: load_run(a.output_dir, r) for r in runs}
     all_series = {r: series(geo) for r, (_, geo) in loaded.items()}
+    if a.only:
+        want = tuple(w.strip() for w in a.only.split(",") if w.strip())
+        all_series = {r: {k: v for k, v in s.items() if k.startswith(want)} for r, s in all_series.items()}
     try:
         import matplotlib
         matplotlib.use("Agg")
         import matplotlib.pyplot as plt
+        pu.apply_style(plt, dark=a.style == "dark")
     except ImportError:
         plt = None
     for r, (d, _) in loaded.items():

@@ -64,7 +64,10 @@ def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--input", required=True)
     ap.add_argument("--view", default="acts", choices=["acts", "pooled", "last_tok"])
+    ap.add_argument("--only", default=None, help="comma-separated concept sets to draw; default: all")
+    ap.add_argument("--style", default="publication", help="'dark' switches the matplotlib figures to a dark background")
     a = ap.parse_args()
+    only = {w.strip() for w in a.only.split(",")} if a.only else None
     d = Path(a.input)
     meta = json.loads((d / "meta.json").read_text())
     af = d / ("analysis.json" if a.view == "acts" else f"analysis_{a.view}.json")
@@ -73,10 +76,13 @@ def main() -> None:
         import matplotlib
         matplotlib.use("Agg")
         import matplotlib.pyplot as plt
+        pu.apply_style(plt, dark=a.style == "dark")
     except ImportError:
         plt = None
     curves: dict[str, list[float]] = {}
     for name, info in meta["sets"].items():
+        if only is not None and name not in only:
+            continue
         with np.load(d / f"{name}.npz") as z:
             acts = (z[a.view] if a.view in z.files else z["acts"]).mean(0)             # [items, layers, D]
         s = ana["sets"].get(name, {})

@@ -78,6 +78,7 @@ def main() -> None:
     ap.add_argument("--attn_res_n_blocks", type=int, default=7)
     ap.add_argument("--warmup_steps", type=int, default=2)
     ap.add_argument("--steps", "--profile_steps", dest="steps", type=int, default=3)
+    ap.add_argument("--compile", action="store_true", help="accepted for command-line compatibility; there is no tracing compiler here")
     ap.add_argument("--trace", default=None, help="also record a torch.profiler trace of the timed steps to this file")
     a = ap.parse_args()
     dev = a.device
